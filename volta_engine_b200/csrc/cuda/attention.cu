@@ -1,0 +1,383 @@
+// Paged GQA attention for decode, speculative-verify blocks and chunked prefill in one kernel family.
+//
+// Semantics (reference: src/kernels/slang/ref_attention.slang:1-10,47-50,65-70 and
+// inc/engine/modules/attention.h:40-57): causal softmax(q.k * scale) with a running fp32 maximum, optional
+// sliding window counted back from the row position, optional per-row key_end for bidirectional image
+// rows, optional sigmoid output gate. KV lives in a paged pool shared by all sequences:
+//   K/V pool  [pages, kv_heads, 64 tokens, head_dim] bf16, page_table [slots, max_pages] int32.
+//
+// B200 design: a key tile is exactly one page, fetched by two (K, V) sets of TMA tiled loads into
+// 128B-swizzled shared memory, double buffered on mbarriers; the G = q_heads / kv_heads query heads of a
+// token share the CTA so K/V are read once per kv head. A query tile packs (token, head-in-group) pairs
+// into 16-row MMA slabs (one per warp). Decode uses 1 warp per CTA and splits the key range over
+// blockIdx.z with a grid that does not depend on the sequence position (CUDA-graph replay reads the
+// positions from device memory); partial (o, lse) are merged by attn_reduce in split order.
+// Tensor-core path here is mma.sync.m16n8k16 (bf16, fp32 accumulate).
+#include "common.cuh"
+#include "tmap.h"
+#include <float.h>
+
+namespace ve {
+
+constexpr int kPageTok = 64;
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  long q_stride;       // elements between rows of q
+  __nv_bfloat16* out;  // [rows, nq*HD]
+  long out_stride;
+  const __nv_bfloat16* gate;  // optional [rows, nq*HD]
+  long gate_stride;
+  float* o_part;    // [rows, nq, nsplit, HD]
+  float* lse_part;  // [rows, nq, nsplit]
+  const int* pos;
+  const int* slot;
+  const int* key_end;     // optional
+  const int* tile_first;  // optional (identity when null)
+  const int* tile_count;
+  const int* page_table;
+  int max_pages;
+  int nq, nkv, nsplit;
+  float scale_log2;  // softmax scale * log2(e)
+  int window;
+  int* status;
+};
+
+VE_DEVINL void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+VE_DEVINL void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+VE_DEVINL void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+VE_DEVINL uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
+                                                       const __grid_constant__ CUtensorMap vmap) {
+  constexpr int TILE_BYTES = kPageTok * HD * 2;
+  constexpr int NCH = HD / 64;   // 128-byte column chunks per row
+  constexpr int KSTEPS = HD / 16;
+  constexpr int NT_O = HD / 8;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full[2];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int tile = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
+  const int G = p.nq / p.nkv;
+  const int first = p.tile_first ? p.tile_first[tile] : tile;
+  const int count = p.tile_count ? p.tile_count[tile] : 1;
+  const int s = p.slot ? p.slot[first] : 0;
+  if (count <= 0 || s < 0) return;
+
+  // key range of the tile
+  int lim_max = -1, pos_min = 0x7fffffff;
+  for (int i = 0; i < count; ++i) {
+    const int ps = p.pos[first + i];
+    const int lm = p.key_end ? p.key_end[first + i] : ps;
+    lim_max = max(lim_max, lm);
+    pos_min = min(pos_min, ps);
+  }
+  const int kt_end_all = lim_max / kPageTok + 1;
+  const int kt_begin_all = p.window > 0 ? max(0, pos_min - p.window + 1) / kPageTok : 0;
+  const int ntile_all = kt_end_all - kt_begin_all;
+  const int tps = (ntile_all + p.nsplit - 1) / p.nsplit;
+  const int kt_begin = kt_begin_all + z * tps;
+  const int kt_end = min(kt_end_all, kt_begin + tps);
+
+  // this thread's two rows
+  int r_tok[2], r_head[2], r_pos[2], r_lim[2];
+  bool r_ok[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + h * 8;
+    r_ok[h] = r < count * G;
+    const int rr = r_ok[h] ? r : 0;
+    r_tok[h] = first + rr / G;
+    r_head[h] = kvh * G + rr % G;
+    r_pos[h] = p.pos[r_tok[h]];
+    r_lim[h] = p.key_end ? p.key_end[r_tok[h]] : r_pos[h];
+  }
+
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](int kt, int stage) {
+    const int page = p.page_table[(long)s * p.max_pages + kt];
+    const int row = (page * p.nkv + kvh) * kPageTok;
+    uint8_t* kb = smem + stage * 2 * TILE_BYTES;
+    uint8_t* vb = kb + TILE_BYTES;
+    mbar_expect_tx(&full[stage], 2 * TILE_BYTES);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      tma_load_2d(kb + c * 8192, &kmap, &full[stage], c * 64, row);
+      tma_load_2d(vb + c * 8192, &vmap, &full[stage], c * 64, row);
+    }
+  };
+  if (tid == 0 && kt_begin < kt_end) issue(kt_begin, 0);
+
+  // Q fragments straight from global memory
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_bfloat16* qr = p.q + (long)r_tok[h] * p.q_stride + (long)r_head[h] * HD + kk * 16 + 2 * t;
+      qf[kk][h] = r_ok[h] ? *reinterpret_cast<const uint32_t*>(qr) : 0u;
+      qf[kk][2 + h] = r_ok[h] ? *reinterpret_cast<const uint32_t*>(qr + 8) : 0u;
+    }
+  }
+
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.f, 0.f};
+
+  const uint32_t smem_base = smem_u32(smem);
+  bool failed = false;
+  for (int kt = kt_begin; kt < kt_end; ++kt) {
+    const int it = kt - kt_begin, stage = it & 1;
+    const bool ok = mbar_wait(&full[stage], (it >> 1) & 1);
+    if (!__syncthreads_and(ok)) {
+      failed = true;
+      break;
+    }
+    if (tid == 0 && kt + 1 < kt_end) issue(kt + 1, stage ^ 1);
+    const uint32_t kb = smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+
+    // S = Q K^T  (16 rows x 64 keys per warp)
+    float sacc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      const int c = (kk * 16) / 64, ci = ((kk * 16) % 64) / 8;
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        const int mi = lane >> 3, rr = lane & 7;
+        const int key = np * 16 + (mi >> 1) * 8 + rr;
+        const int ch = ci + (mi & 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kb + c * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16(sacc[2 * np], qf[kk], b0, b1);
+        mma_bf16(sacc[2 * np + 1], qf[kk], b2, b3);
+      }
+    }
+    // mask + online softmax
+    float mx[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int key = kt * kPageTok + nt * 8 + 2 * t + (e & 1);
+        const bool allow = r_ok[h] && key <= r_lim[h] && (p.window <= 0 || key > r_pos[h] - p.window);
+        const float v = allow ? sacc[nt][e] * p.scale_log2 : -FLT_MAX;
+        sacc[nt][e] = v;
+        mx[h] = fmaxf(mx[h], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      corr[h] = (m_run[h] == -FLT_MAX) ? 0.f : exp2f(m_run[h] - m_new);
+      m_run[h] = m_new;
+      l_run[h] *= corr[h];
+    }
+    uint32_t pf[4][4];  // P as A fragments for 4 k-steps of 16 keys
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      float pv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        pv[e] = (sacc[nt][e] == -FLT_MAX) ? 0.f : exp2f(sacc[nt][e] - m_run[h]);
+        l_run[h] += pv[e];
+      }
+      const int ks = nt >> 1, hi = nt & 1;
+      pf[ks][hi * 2 + 0] = pack_bf16(pv[0], pv[1]);
+      pf[ks][hi * 2 + 1] = pack_bf16(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    // O += P V
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        const int mi = lane >> 3, rr = lane & 7;
+        const int key = ks * 16 + (mi & 1) * 8 + rr;
+        const int d = dp * 16 + (mi >> 1) * 8;
+        const int c = d / 64, ch = (d % 64) / 8;
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(vb + c * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16(o[2 * dp], pf[ks], b0, b1);
+        mma_bf16(o[2 * dp + 1], pf[ks], b2, b3);
+      }
+    }
+  }
+  if (failed) {
+    if (tid == 0 && p.status) atomicExch(p.status, (int)kErrMbarTimeout);
+    return;
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!r_ok[h]) continue;
+    const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+    if (p.nsplit == 1) {
+      __nv_bfloat16* orow = p.out + (long)r_tok[h] * p.out_stride + (long)r_head[h] * HD;
+      const __nv_bfloat16* grow = p.gate ? p.gate + (long)r_tok[h] * p.gate_stride + (long)r_head[h] * HD : nullptr;
+#pragma unroll
+      for (int nt = 0; nt < NT_O; ++nt) {
+        float a = o[nt][2 * h] * inv, b = o[nt][2 * h + 1] * inv;
+        const int d = nt * 8 + 2 * t;
+        if (grow) {
+          a *= 1.f / (1.f + __expf(-bf2f(grow[d])));
+          b *= 1.f / (1.f + __expf(-bf2f(grow[d + 1])));
+        }
+        *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16(a, b);
+      }
+    } else {
+      const long base = ((long)r_tok[h] * p.nq + r_head[h]) * p.nsplit + z;
+      float* orow = p.o_part + base * HD;
+#pragma unroll
+      for (int nt = 0; nt < NT_O; ++nt) {
+        const int d = nt * 8 + 2 * t;
+        *reinterpret_cast<float2*>(orow + d) = make_float2(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+      }
+      if (t == 0) p.lse_part[base] = l_run[h] > 0.f ? m_run[h] + log2f(l_run[h]) : -FLT_MAX;
+    }
+  }
+}
+
+// Merge split partials in split order. grid (rows * nq), block HD threads.
+__global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part,
+                                   __nv_bfloat16* __restrict__ out, long out_stride,
+                                   const __nv_bfloat16* __restrict__ gate, long gate_stride, const int* __restrict__ slot,
+                                   int nq, int nsplit, int HD) {
+  const int row = blockIdx.x / nq, head = blockIdx.x % nq, d = threadIdx.x;
+  if (slot && slot[row] < 0) return;
+  const long base = ((long)row * nq + head) * nsplit;
+  float mx = -FLT_MAX;
+  for (int i = 0; i < nsplit; ++i) mx = fmaxf(mx, lse_part[base + i]);
+  float acc = 0.f, wsum = 0.f;
+  for (int i = 0; i < nsplit; ++i) {
+    const float l = lse_part[base + i];
+    const float w = (l == -FLT_MAX) ? 0.f : exp2f(l - mx);
+    wsum += w;
+    acc += w * o_part[(base + i) * HD + d];
+  }
+  float v = wsum > 0.f ? acc / wsum : 0.f;
+  if (gate) v *= 1.f / (1.f + __expf(-bf2f(gate[(long)row * gate_stride + (long)head * HD + d])));
+  out[(long)row * out_stride + (long)head * HD + d] = f2bf(v);
+}
+
+template <int HD, int NW>
+static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
+                       cudaStream_t st) {
+  constexpr int smem = 2 * 2 * kPageTok * HD * 2 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid(ntiles, p.nkv, p.nsplit);
+  attn_kernel<HD, NW><<<grid, NW * 32, smem, st>>>(p, kmap, vmap);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ve
+
+using namespace ve;
+
+extern "C" {
+
+// rows_per_tile_warps: 1 (decode / verify: <= 16 packed rows per tile) or 4 (prefill: <= 64 packed rows).
+int ve_attention(const void* q, long q_stride, void* out, long out_stride, const void* gate, long gate_stride,
+                 void* o_part, void* lse_part, const void* pos, const void* slot, const void* key_end,
+                 const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
+                 int max_pages, void* kpool, void* vpool, long pool_pages, int nq, int nkv, int hd, int nsplit,
+                 float scale, int window, int warps, void* status, cudaStream_t st) {
+  if (ntiles <= 0) return 0;
+  if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q;
+  p.q_stride = q_stride;
+  p.out = (__nv_bfloat16*)out;
+  p.out_stride = out_stride;
+  p.gate = (const __nv_bfloat16*)gate;
+  p.gate_stride = gate_stride;
+  p.o_part = (float*)o_part;
+  p.lse_part = (float*)lse_part;
+  p.pos = (const int*)pos;
+  p.slot = (const int*)slot;
+  p.key_end = (const int*)key_end;
+  p.tile_first = (const int*)tile_first;
+  p.tile_count = (const int*)tile_count;
+  p.page_table = (const int*)page_table;
+  p.max_pages = max_pages;
+  p.nq = nq;
+  p.nkv = nkv;
+  p.nsplit = nsplit;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
+  p.status = (int*)status;
+  CUtensorMap kmap, vmap;
+  const uint64_t total_rows = (uint64_t)pool_pages * nkv * kPageTok;
+  int rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok,
+                        64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = make_tmap_2d(&vmap, vpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+#define VE_ATTN(HD_)                                                             \
+  if (hd == HD_) {                                                               \
+    rc = warps == 1 ? launch_attn<HD_, 1>(p, kmap, vmap, ntiles, st)             \
+                    : launch_attn<HD_, 4>(p, kmap, vmap, ntiles, st);            \
+  } else
+  VE_ATTN(64) VE_ATTN(128) VE_ATTN(256) { return cudaErrorInvalidValue; }
+#undef VE_ATTN
+  if (rc) return rc;
+  if (nsplit > 1) {
+    attn_reduce_kernel<<<rows * nq, hd, 0, st>>>((const float*)o_part, (const float*)lse_part, (__nv_bfloat16*)out,
+                                                 out_stride, (const __nv_bfloat16*)gate, gate_stride,
+                                                 (const int*)slot, nq, nsplit, hd);
+    rc = (int)cudaGetLastError();
+  }
+  return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,215 @@
+"""Dense GQA decoder (Llama / Qwen3 / Gemma-style block: RMSNorm -> GQA attention with RoPE -> RMSNorm ->
+gated FFN), tensor-parallel over ``comm.size`` GPUs.
+
+Counterpart of the reference's dense pipelines (simplest: src/models/gemma4.cpp:413-521; the plain
+hd-128 GQA decoder: src/video/h3_text.cu). TP layout as in the reference (src/models/gemma4.cpp:42-48,
+216-270): column-parallel fused qkv and gate/up, row-parallel o_proj / down_proj, residual replicated,
+two fused all-reduce + residual + RMSNorm per layer, vocabulary-parallel LM head with shard argmax
+merge. KV heads are replicated when there are fewer of them than ranks.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, asdict
+
+import torch
+
+from ..ops import kernels as K
+from ..ops.linear import LinearBF16, LinearNVFP4
+from ..parallel.comm import LocalComm
+from ..runtime.batch import BatchRows, LOGITS_ALL, LOGITS_LAST, LOGITS_NONE
+
+
+@dataclass
+class DenseConfig:
+    n_layers: int = 4
+    hidden: int = 512
+    n_q: int = 8
+    n_kv: int = 2
+    head_dim: int = 64
+    ffn: int = 1408
+    vocab: int = 32000
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+    norm_bias: float = 0.0        # 1.0 for "1 + w" style weights
+    rot_dim: int = 0              # 0 = full head_dim
+    rope_interleaved: bool = False
+    qk_norm: bool = False
+    act: str = "silu"             # or "gelu_tanh"
+    act_limit: float = 0.0
+    tie_embeddings: bool = False
+    embed_scale: float = 1.0
+    sliding_window: int = 0
+    attn_scale: float = 0.0       # 0 = 1/sqrt(head_dim)
+    logit_softcap: float = 0.0
+    quant: str = "nvfp4"          # nvfp4 | bf16
+    gemm_mode: str = "w4a16"      # prefill arithmetic for nvfp4 weights
+    model_type: str = "dense"
+
+    @classmethod
+    def baseline_27b(cls):
+        """Dense 27B-class decoder of the NVFP4 benchmark configuration."""
+        return cls(n_layers=64, hidden=5120, n_q=40, n_kv=8, head_dim=128, ffn=17408, vocab=151936,
+                   rope_theta=1e6)
+
+    @classmethod
+    def tiny(cls, **kw):
+        c = cls(n_layers=2, hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, vocab=1024)
+        for k, v in kw.items():
+            setattr(c, k, v)
+        return c
+
+    def to_dict(self):
+        return asdict(self)
+
+
+def _pad_to(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class DenseLayer:
+    __slots__ = ("attn_norm", "qkv", "o_proj", "ffn_norm", "gate_up", "down", "q_norm", "k_norm")
+
+
+class DenseModel:
+    def __init__(self, cfg: DenseConfig, device, comm=None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.comm = comm or LocalComm()
+        tp = self.comm.size
+        assert cfg.n_q % tp == 0 and cfg.ffn % tp == 0
+        self.nq = cfg.n_q // tp
+        self.nkv = max(1, cfg.n_kv // tp)
+        self.kv_rep = max(1, tp // cfg.n_kv)   # ranks sharing one kv head
+        self.ffn = cfg.ffn // tp
+        self.hd = cfg.head_dim
+        self.rot = cfg.rot_dim or cfg.head_dim
+        self.scale = cfg.attn_scale or 1.0 / math.sqrt(cfg.head_dim)
+        self.vocab_pad = _pad_to(cfg.vocab, 256 * tp)
+        self.vocab_local = self.vocab_pad // tp
+        self.layers: list[DenseLayer] = []
+        self.embed = None
+        self.final_norm = None
+        self.lm_head = None
+        self.attn_ws = None
+
+    # ------------------------------------------------------------------------------------- weights
+    def _make_linear(self, w: torch.Tensor, search: bool):
+        if self.cfg.quant == "nvfp4":
+            return LinearNVFP4.from_dense(w, self.cfg.gemm_mode, search=search).prepare()
+        return LinearBF16(w.to(torch.bfloat16))
+
+    def init_random(self, seed: int = 1, std: float = 0.02, search: bool = False):
+        """Random N(0, std) weights of the full architecture; this rank keeps its TP shard.
+
+        Every rank draws the same full matrices from the same generator state so shards agree.
+        """
+        cfg, dev = self.cfg, self.device
+        r, tp = self.comm.rank, self.comm.size
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+
+        def rnd(n, k):
+            return torch.randn(n, k, generator=gen, device=dev, dtype=torch.float32) * std
+
+        H, hd = cfg.hidden, cfg.head_dim
+        self.embed = rnd(cfg.vocab, H).to(torch.bfloat16)
+        ones = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        nw = ones * (1.0 - cfg.norm_bias)
+        for _ in range(cfg.n_layers):
+            L = DenseLayer()
+            wq, wk, wv = rnd(cfg.n_q * hd, H), rnd(cfg.n_kv * hd, H), rnd(cfg.n_kv * hd, H)
+            kv0 = (r // self.kv_rep) * self.nkv if cfg.n_kv < tp else r * self.nkv
+            wqkv = torch.cat([wq[r * self.nq * hd:(r + 1) * self.nq * hd],
+                              wk[kv0 * hd:(kv0 + self.nkv) * hd], wv[kv0 * hd:(kv0 + self.nkv) * hd]], 0)
+            L.qkv = self._make_linear(wqkv, search)
+            del wq, wk, wv, wqkv
+            wo = rnd(H, cfg.n_q * hd)
+            L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search)
+            del wo
+            wg, wu = rnd(cfg.ffn, H), rnd(cfg.ffn, H)
+            L.gate_up = self._make_linear(torch.cat([wg[r * self.ffn:(r + 1) * self.ffn],
+                                                     wu[r * self.ffn:(r + 1) * self.ffn]], 0), search)
+            del wg, wu
+            wd = rnd(H, cfg.ffn)
+            L.down = self._make_linear(wd[:, r * self.ffn:(r + 1) * self.ffn].contiguous(), search)
+            del wd
+            L.attn_norm, L.ffn_norm = nw.clone(), nw.clone()
+            L.q_norm = L.k_norm = None
+            if cfg.qk_norm:
+                L.q_norm = torch.ones(hd, device=dev, dtype=torch.bfloat16) * (1.0 - cfg.norm_bias)
+                L.k_norm = L.q_norm.clone()
+            self.layers.append(L)
+        self.final_norm = nw.clone()
+        if cfg.tie_embeddings:
+            full = self.embed
+        else:
+            full = rnd(cfg.vocab, H).to(torch.bfloat16)
+        head = torch.zeros(self.vocab_local, H, device=dev, dtype=torch.bfloat16)
+        lo = r * self.vocab_local
+        hi = min(cfg.vocab, lo + self.vocab_local)
+        if hi > lo:
+            head[: hi - lo] = full[lo:hi]
+        self.lm_head = LinearBF16(head)
+        return self
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * 2 + self.lm_head.nbytes()
+        for L in self.layers:
+            n += L.qkv.nbytes() + L.o_proj.nbytes() + L.gate_up.nbytes() + L.down.nbytes()
+        return n
+
+    def decode_bytes_per_token(self) -> int:
+        """Weight bytes every decode step must stream from HBM (embedding row excluded)."""
+        n = self.lm_head.nbytes()
+        for L in self.layers:
+            n += L.qkv.nbytes() + L.o_proj.nbytes() + L.gate_up.nbytes() + L.down.nbytes()
+        return n
+
+    # ------------------------------------------------------------------------------------- forward
+    def forward(self, b: BatchRows, kv) -> torch.Tensor | None:
+        """Runs all layers for the rows of ``b``; returns fp32 logits of this rank's vocabulary shard for
+        the rows selected by ``b.logits`` (None for LOGITS_NONE)."""
+        cfg = self.cfg
+        comm = self.comm
+        act = 0 if cfg.act == "silu" else 1
+        h = K.embed(b.ids, self.embed, scale=cfg.embed_scale)          # residual stream [n, H] bf16
+        L0 = self.layers[0]
+        x = K.rmsnorm(h, L0.attn_norm, cfg.rms_eps, cfg.norm_bias)
+        prefill = b.tiles is not None
+        for li, L in enumerate(self.layers):
+            kpool, vpool = kv.layer(li)
+            qkv = L.qkv.forward(x)
+            if cfg.qk_norm:
+                stride = qkv.stride(0)
+                K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
+                K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
+                                 self.nq * self.hd)
+            K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
+                         cfg.rope_theta, cfg.rope_interleaved)
+            att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
+                              self.scale, window=cfg.sliding_window, key_end=b.key_end, tiles=b.tiles,
+                              nsplit=1 if prefill else b.nsplit, ws=self.attn_ws)
+            o = L.o_proj.forward(att)
+            x = comm.allreduce_add_norm(o, h, L.ffn_norm, cfg.rms_eps, cfg.norm_bias)
+            gu = L.gate_up.forward(x)
+            a = K.gated_act(gu, self.ffn, act, cfg.act_limit)
+            d = L.down.forward(a)
+            nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
+            x = comm.allreduce_add_norm(d, h, nxt, cfg.rms_eps, cfg.norm_bias)
+        if b.logits == LOGITS_NONE:
+            return None
+        if b.logits == LOGITS_LAST:
+            x = x[b.n - 1: b.n]
+        logits = self.lm_head.forward(x, out_f32=True)
+        if cfg.logit_softcap > 0:
+            if logits.is_cuda:
+                from .._lib import call, ptr
+                call("softcap", "plf", ptr(logits), logits.numel(), float(cfg.logit_softcap))
+            else:
+                logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
+        return logits
+
+    def ensure_workspace(self, max_rows: int, max_splits: int):
+        if self.device.type == "cuda" and (self.attn_ws is None or self.attn_ws.max_splits < max_splits):
+            self.attn_ws = K.AttnWorkspace(max_rows, self.nq, self.hd, max_splits, self.device)

@@ -1,0 +1,291 @@
+"""Op entry points. CUDA tensors go to the hand-written sm_100a kernels (libvolta_kernels.so, mandatory on
+a GPU machine: a missing library raises); CPU tensors run the fp32 PyTorch oracle in
+:mod:`volta_engine_b200.ops.reference` so host-side logic can be tested without a GPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from .._lib import call, ptr
+from . import reference as ref
+
+PAGE = ref.PAGE
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait expires (0 = healthy)."""
+    key = str(device)
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def check_status(device) -> int:
+    t = _status.get(str(device))
+    return int(t.item()) if t is not None else 0
+
+
+# ---------------------------------------------------------------------------------------------- norms
+def rmsnorm(x, w, eps, wbias=0.0, residual=None, out=None):
+    """out = RMSNorm(residual + x) * (w + wbias); residual updated in place when given."""
+    if not x.is_cuda:
+        o, r = ref.rmsnorm(x, w, eps, wbias, residual)
+        if residual is not None:
+            residual.copy_(r)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    rows, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    call("rmsnorm", "ppippiiffll", ptr(x), ptr(residual),
+         1 if (residual is not None and residual.dtype == torch.float32) else 0, ptr(w), ptr(out), rows, H,
+         float(eps), float(wbias), x.stride(0), out.stride(0))
+    return out
+
+
+def rmsnorm_heads_(x, w, rows, heads, hd, row_stride, eps, wbias=0.0, offset=0):
+    """In-place per-head RMSNorm over ``heads`` heads starting ``offset`` elements into each row."""
+    if not x.is_cuda:
+        v = x[:, offset: offset + heads * hd]
+        x[:, offset: offset + heads * hd] = ref.rmsnorm_heads(v, w, heads, hd, eps, wbias)
+        return x
+    call("rmsnorm_heads", "ppiiilff", x.data_ptr() + offset * x.element_size(), ptr(w), rows, heads, hd,
+         row_stride, float(eps), float(wbias))
+    return x
+
+
+def embed(ids, table, out=None, scale=1.0):
+    if not table.is_cuda:
+        o = (table[ids.long()].float() * scale).to(table.dtype)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    rows = ids.numel()
+    V, H = table.shape
+    if out is None:
+        out = torch.empty(rows, H, dtype=table.dtype, device=table.device)
+    call("embed", "pppiiif", ptr(ids), ptr(table), ptr(out), rows, H, V, float(scale))
+    return out
+
+
+def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved=False,
+               pos_scale=1.0):
+    """Rotate q, k inside ``qkv`` in place and write k, v rows into the paged cache."""
+    if not qkv.is_cuda:
+        ref.rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved,
+                       pos_scale)
+        return
+    rows = qkv.shape[0]
+    call("rope_store", "ppppippiiiiifif", ptr(qkv), ptr(pos), ptr(slot), ptr(page_table), page_table.shape[1],
+         ptr(kpool), ptr(vpool), rows, nq, nkv, hd, rot_dim, float(theta), 1 if interleaved else 0,
+         float(pos_scale))
+
+
+def gated_act(gu, I, act=0, limit=0.0, out=None):
+    if not gu.is_cuda:
+        o = ref.gated_act(gu, I, act, limit)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    rows = gu.shape[0]
+    if out is None:
+        out = torch.empty(rows, I, dtype=gu.dtype, device=gu.device)
+    call("gated_act", "ppliif", ptr(gu), ptr(out), rows, I, act, float(limit))
+    return out
+
+
+def add_(a, b):
+    if not a.is_cuda:
+        a.add_(b)
+        return a
+    call("add", "ppl", ptr(a), ptr(b), a.numel())
+    return a
+
+
+# ---------------------------------------------------------------------------------------------- attention
+class AttnWorkspace:
+    """Split-KV partial buffers, allocated once (stable pointers for CUDA-graph replay)."""
+
+    def __init__(self, max_rows, nq, hd, max_splits, device):
+        self.max_splits = max_splits
+        self.o_part = torch.empty(max_rows * nq * max_splits * hd, dtype=torch.float32, device=device)
+        self.lse_part = torch.empty(max_rows * nq * max_splits, dtype=torch.float32, device=device)
+
+
+def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out=None, window=0, key_end=None,
+              gate=None, tiles=None, nsplit=1, ws: AttnWorkspace | None = None):
+    """Paged GQA attention. ``q`` is the (rotated) fused qkv buffer [rows, >= nq*hd].
+
+    ``tiles`` = (tile_first, tile_count, ntiles) int32 device tensors grouping consecutive rows of one
+    sequence for prefill (<= 64 // G tokens per tile); None = one row per tile (decode / verify).
+    """
+    rows = q.shape[0]
+    if not q.is_cuda:
+        o = ref.attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window, key_end, gate)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    if out is None:
+        out = torch.empty(rows, nq * hd, dtype=q.dtype, device=q.device)
+    if tiles is None:
+        tf = tc = None
+        ntiles, warps = rows, 1
+    else:
+        tf, tc, ntiles = tiles
+        warps = 4
+    if nsplit > 1 and ws is None:
+        raise ValueError("split-KV attention needs a workspace")
+    call("attention", "plplplpppppppiipippliiiifiip",
+         ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
+         ptr(ws.o_part) if ws else 0, ptr(ws.lse_part) if ws else 0, ptr(pos), ptr(slot), ptr(key_end),
+         ptr(tf), ptr(tc), ntiles, rows, ptr(page_table), page_table.shape[1], ptr(kpool), ptr(vpool),
+         kpool.shape[0], nq, nkv, hd, nsplit, float(scale), window, warps, ptr(status_word(q.device)))
+    return out
+
+
+def make_prefill_tiles(slots, G, device, max_rows_per_tile=64):
+    """Host helper: group consecutive rows with the same slot into tiles of <= 64 // G tokens."""
+    per = max(1, max_rows_per_tile // G)
+    first, count = [], []
+    i, n = 0, len(slots)
+    while i < n:
+        j = i
+        while j < n and slots[j] == slots[i] and j - i < per:
+            j += 1
+        first.append(i)
+        count.append(j - i)
+        i = j
+    tf = torch.tensor(first, dtype=torch.int32, device=device)
+    tc = torch.tensor(count, dtype=torch.int32, device=device)
+    return tf, tc, len(first)
+
+
+# ---------------------------------------------------------------------------------------------- sampling
+def argmax(logits, id_offset=0, idx_out=None, val_out=None):
+    if not logits.is_cuda:
+        i, v = ref.argmax(logits, id_offset)
+        if idx_out is not None:
+            idx_out.copy_(i)
+            if val_out is not None:
+                val_out.copy_(v)
+            return idx_out, val_out
+        return i, v
+    rows, V = logits.shape
+    if idx_out is None:
+        idx_out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if val_out is None:
+        val_out = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    call("argmax", "pliiipp", ptr(logits), logits.stride(0), rows, V, id_offset, ptr(idx_out), ptr(val_out))
+    return idx_out, val_out
+
+
+def topk(logits, k=16, id_offset=0):
+    """-> (ids [rows,k] int32, vals [rows,k] fp32 descending, lse [rows])."""
+    if not logits.is_cuda:
+        return ref.topk(logits, k, id_offset)
+    rows, V = logits.shape
+    ids = torch.empty(rows, k, dtype=torch.int32, device=logits.device)
+    vals = torch.empty(rows, k, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    call("topk", "pliiiippp", ptr(logits), logits.stride(0), rows, V, id_offset, k, ptr(ids), ptr(vals), ptr(lse))
+    return ids, vals, lse
+
+
+# ---------------------------------------------------------------------------------------------- NVFP4
+def nvfp4_dequant(packed, scales, gscale, out=None):
+    N, K2 = packed.shape
+    K = K2 * 2
+    if not packed.is_cuda:
+        from ..quant import nvfp4 as q
+        return q.dequantize_nvfp4(packed, scales, gscale).to(torch.bfloat16)
+    if out is None:
+        out = torch.empty(N, K, dtype=torch.bfloat16, device=packed.device)
+    call("nvfp4_dequant", "ppfpli", ptr(packed), ptr(scales), float(gscale), ptr(out), N, K)
+    return out
+
+
+def nvfp4_quant_rows(x, blocked=True):
+    """Activation rows -> (packed [T,K/2], scales). blocked=True gives 512 B tensor-core atoms."""
+    T, K = x.shape
+    if not x.is_cuda:
+        from ..quant import nvfp4 as q
+        p, s = q.quantize_rows_nvfp4(x)
+        return p, (q.scales_atoms_512(s) if blocked else s)
+    xp = torch.empty(T, K // 2, dtype=torch.uint8, device=x.device)
+    if blocked:
+        xs = torch.zeros((T + 127) // 128, K // 64, 512, dtype=torch.uint8, device=x.device)
+    else:
+        xs = torch.empty(T, K // 16, dtype=torch.uint8, device=x.device)
+    call("nvfp4_quant_rows", "plppiifi", ptr(x), x.stride(0), ptr(xp), ptr(xs), T, K, 1.0, 1 if blocked else 0)
+    return xp, xs
+
+
+def nvfp4_gemv(packed, scales, gscale, x, out=None, residual=None):
+    """x [M<=16.., K] bf16 -> out [M, N] bf16 (CUDA-core streaming mat-vec)."""
+    N, K2 = packed.shape
+    K = K2 * 2
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    call("nvfp4_gemv", "ppfplplpliii", ptr(packed), ptr(scales), float(gscale), ptr(x), x.stride(0), ptr(out),
+         out.stride(0), ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K)
+    return out
+
+
+def bf16_gemv_f32(W, x, out=None):
+    N, K = W.shape
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+    call("bf16_gemv_f32", "pplpliii", ptr(W), ptr(x), x.stride(0), ptr(out), out.stride(0), M, N, K)
+    return out
+
+
+def gemm_bf16(W, x, out=None, residual=None, alpha=1.0, out_f32=False):
+    """out[t, n] = alpha * sum_k W[n,k] x[t,k] on tcgen05 (bf16 x bf16, fp32 accumulate)."""
+    N, K = W.shape
+    T = x.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    f32 = out.dtype == torch.float32
+    call("gemm_bf16", "plplplppliiifp", ptr(W), W.stride(0), ptr(x), x.stride(0), 0 if f32 else ptr(out),
+         out.stride(0), ptr(out) if f32 else 0, ptr(residual), residual.stride(0) if residual is not None else 0,
+         T, N, K, float(alpha), ptr(status_word(x.device)))
+    return out
+
+
+def gemm_w4a16(packed, sf_blocked, gscale, x, out=None, residual=None):
+    N, K2 = packed.shape
+    K = K2 * 2
+    T = x.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    call("gemm_w4a16", "ppplplppliiifp", ptr(packed), ptr(sf_blocked), ptr(x), x.stride(0), ptr(out),
+         out.stride(0), 0, ptr(residual), residual.stride(0) if residual is not None else 0, T, N, K,
+         float(gscale), ptr(status_word(x.device)))
+    return out
+
+
+def gemm_w4a4(packed, sf_atoms, gscale, xp, xs_atoms, T, out=None, residual=None):
+    N, K2 = packed.shape
+    K = K2 * 2
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=packed.device)
+    call("gemm_w4a4", "pppppl" + "ppliiifp", ptr(packed), ptr(sf_atoms), ptr(xp), ptr(xs_atoms), ptr(out),
+         out.stride(0), 0, ptr(residual), residual.stride(0) if residual is not None else 0, T, N, K,
+         float(gscale), ptr(status_word(packed.device)))
+    return out
+
+
+def native_launches() -> int:
+    return _lib.launch_count

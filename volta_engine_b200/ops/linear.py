@@ -1,0 +1,101 @@
+"""Linear layers over the supported weight formats (reference: inc/engine/modules/linear.h:143-190
+dispatches on QuantType {FP16, TRELLIS, NVFP4, FP8, GGUF}).
+
+Kernel choice by row count on a GPU:
+  * rows <= GEMV_MAX_ROWS : HBM-streaming mat-vec (one pass over the weights for up to 4 rows)
+  * otherwise            : tcgen05 GEMM, weights as the UMMA A operand
+``gemm_mode`` selects the prefill arithmetic for NVFP4 weights:
+  ``w4a16``  bf16 activations, weights dequantised to f16 inside the tile loader (exact products)
+  ``w4a4``   activations quantised to NVFP4 per 16 elements, native block-scaled FP4 MMA
+  ``dequant`` weights expanded to bf16 in global memory + bf16 tcgen05 GEMM (debug / oracle)
+"""
+from __future__ import annotations
+
+import torch
+
+from ..quant import nvfp4 as qn
+from . import kernels as K
+
+GEMV_MAX_ROWS = 16
+# A/B switch: "cublas" routes every multi-row product through torch.matmul on dequantised weights (library
+# baseline / bring-up aid); unset = hand-written kernels only.
+import os
+GEMM_BACKEND = os.environ.get("VOLTA_GEMM_BACKEND", "native")
+
+
+class LinearBF16:
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight.contiguous()  # [N, K]
+        self.out_features, self.in_features = weight.shape
+
+    def forward(self, x, residual=None, out=None, out_f32=False):
+        if not x.is_cuda:
+            y = x.float() @ self.weight.float().t()
+            if residual is not None:
+                y = y + residual.float()
+            return y if out_f32 else y.to(x.dtype)
+        if x.shape[0] <= GEMV_MAX_ROWS and out_f32 and residual is None:
+            return K.bf16_gemv_f32(self.weight, x, out)
+        if GEMM_BACKEND == "cublas":
+            y = torch.matmul(x, self.weight.t())
+            if residual is not None:
+                y = y + residual
+            return y.float() if out_f32 else y
+        return K.gemm_bf16(self.weight, x, out=out, residual=residual, out_f32=out_f32)
+
+    def nbytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+
+class LinearNVFP4:
+    """NVFP4 weight: packed codes [N, K/2], E4M3 block scales [N, K/16], fp32 tensor scale."""
+
+    def __init__(self, packed, scales, gscale: float, gemm_mode: str = "w4a16"):
+        self.packed, self.scales, self.gscale = packed.contiguous(), scales.contiguous(), float(gscale)
+        self.out_features, self.in_features = packed.shape[0], packed.shape[1] * 2
+        self.gemm_mode = gemm_mode
+        self._sf_k128 = None
+        self._sf_atoms = None
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor, gemm_mode="w4a16", search=True):
+        p, s, g = qn.quantize_nvfp4(w, search=search)
+        return cls(p, s, g, gemm_mode)
+
+    def prepare(self):
+        """Build the loader-side scale layouts once (load time, not on the hot path)."""
+        if self.gemm_mode == "w4a16" and self._sf_k128 is None and self.out_features % 128 == 0:
+            self._sf_k128 = qn.scales_blocked_k128(self.scales)
+        if self.gemm_mode == "w4a4" and self._sf_atoms is None:
+            self._sf_atoms = qn.scales_atoms_512(self.scales)
+        return self
+
+    def dequant(self):
+        return K.nvfp4_dequant(self.packed, self.scales, self.gscale)
+
+    def forward(self, x, residual=None, out=None):
+        if not x.is_cuda:
+            y = x.float() @ qn.dequantize_nvfp4(self.packed, self.scales, self.gscale).t()
+            if residual is not None:
+                y = y + residual.float()
+            return y.to(x.dtype)
+        rows = x.shape[0]
+        if rows <= GEMV_MAX_ROWS:
+            return K.nvfp4_gemv(self.packed, self.scales, self.gscale, x, out=out, residual=residual)
+        mode = self.gemm_mode
+        if GEMM_BACKEND == "cublas":
+            y = torch.matmul(x, self.dequant().t())
+            return y + residual if residual is not None else y
+        if mode == "w4a16" and self.out_features % 128 == 0 and self.in_features % 128 == 0:
+            if self._sf_k128 is None:
+                self.prepare()
+            return K.gemm_w4a16(self.packed, self._sf_k128, self.gscale, x, out=out, residual=residual)
+        if mode == "w4a4" and self.out_features % 128 == 0 and self.in_features % 256 == 0:
+            if self._sf_atoms is None:
+                self.prepare()
+            xp, xs = K.nvfp4_quant_rows(x, blocked=True)
+            return K.gemm_w4a4(self.packed, self._sf_atoms, self.gscale, xp, xs, rows, out=out, residual=residual)
+        return K.gemm_bf16(self.dequant(), x, out=out, residual=residual)
+
+    def nbytes(self):
+        return self.packed.numel() + self.scales.numel()

@@ -1,0 +1,202 @@
+"""Single-rank execution engine: chunked prefill, CUDA-graph decode, greedy sampling on the device.
+
+Plays the role of the reference's ``ModelCluster::forward / prefill / sample`` for one rank
+(src/runtime/cluster.cpp:328-337,498-556,610-646) with its ``GraphCache`` policy
+(inc/engine/core/graph_cache.h:21-89): the first call of a row count runs eagerly, the second is
+captured, later calls replay. Row ids / positions / slots live in static device buffers, so a replay
+never depends on host arguments; attention grids are position independent.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import kernels as K
+from .batch import BatchRows, LOGITS_ALL, LOGITS_LAST, LOGITS_NONE, MAX_GRAPH_ROWS
+from .kv_cache import PagedKVCache
+
+
+@dataclass
+class GenStats:
+    prompt_tokens: int = 0
+    new_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+
+    @property
+    def prefill_tok_s(self):
+        return self.prompt_tokens / (self.prefill_ms / 1e3) if self.prefill_ms > 0 else 0.0
+
+    @property
+    def decode_tok_s(self):
+        return self.new_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
+
+
+class _Graph:
+    __slots__ = ("graph", "calls", "tokens", "logits")
+
+    def __init__(self):
+        self.graph = None
+        self.calls = 0
+        self.tokens = None
+        self.logits = None
+
+
+class Engine:
+    def __init__(self, model, kv: PagedKVCache, *, use_graphs: bool = True, prefill_chunk: int = 2048,
+                 feedback: bool = True):
+        self.model, self.kv = model, kv
+        self.device = model.device
+        self.cuda = self.device.type == "cuda"
+        self.use_graphs = use_graphs and self.cuda
+        self.prefill_chunk = prefill_chunk
+        self.feedback = feedback
+        self.comm = model.comm
+        dev = self.device
+        R = MAX_GRAPH_ROWS
+        # static step descriptor (device) + pinned host staging
+        self.s_ids = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.s_pos = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.s_slot = torch.full((R,), -1, dtype=torch.int32, device=dev)
+        self.s_tok = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.s_val = torch.zeros(R, dtype=torch.float32, device=dev)
+        pin = self.cuda
+        self.h_in = torch.zeros(3, R, dtype=torch.int32, pin_memory=pin)
+        self.h_tok = torch.zeros(R, dtype=torch.int32, pin_memory=pin)
+        self.graphs: dict[tuple, _Graph] = {}
+        self.nsplit_cap = 32
+        if self.cuda:
+            model.ensure_workspace(R, self.nsplit_cap)
+
+    # ------------------------------------------------------------------------------------------ helpers
+    def _nsplit(self, rows: int) -> int:
+        if not self.cuda:
+            return 1
+        per = 148 * 3 // max(1, rows * self.model.nkv)
+        return max(1, min(self.nsplit_cap, per))
+
+    def _sample_greedy(self, logits: torch.Tensor, out_tok: torch.Tensor, out_val: torch.Tensor, rows: int):
+        off = self.comm.rank * self.model.vocab_local
+        K.argmax(logits, off, out_tok[:rows], out_val[:rows])
+        if self.comm.size > 1:
+            merged = self.comm.merge_argmax(out_tok[:rows], out_val[:rows])
+            out_tok[:rows].copy_(merged)
+
+    # ------------------------------------------------------------------------------------------ prefill
+    def prefill(self, slot: int, tokens: list[int], start_pos: int = 0) -> int:
+        """Run the prompt rows [start_pos, start_pos + len(tokens)) of ``slot`` through the model in chunks
+        and return the greedy next token (host int)."""
+        n = len(tokens)
+        self.kv.reserve(slot, start_pos + n + 1)
+        G = self.model.nq // self.model.nkv
+        done = 0
+        tok = -1
+        while done < n:
+            c = min(self.prefill_chunk, n - done)
+            last = done + c == n
+            ids = tokens[done:done + c]
+            pos = list(range(start_pos + done, start_pos + done + c))
+            if c <= MAX_GRAPH_ROWS:
+                b = BatchRows.make(ids, pos, [slot] * c, self.device, LOGITS_ALL if last else LOGITS_NONE, G,
+                                   prefill=False, nsplit=self._nsplit(c))
+            else:
+                b = BatchRows.make(ids, pos, [slot] * c, self.device, LOGITS_LAST if last else LOGITS_NONE, G,
+                                   prefill=True)
+            logits = self.model.forward(b, self.kv)
+            if last:
+                rows = logits.shape[0]
+                self._sample_greedy(logits, self.s_tok, self.s_val, rows)
+                tok = int(self.s_tok[rows - 1].item())
+            done += c
+        return tok
+
+    # ------------------------------------------------------------------------------------------ decode
+    def _forward_static(self, rows: int, nsplit: int) -> torch.Tensor:
+        b = BatchRows(self.s_ids[:rows], self.s_pos[:rows], self.s_slot[:rows], rows, LOGITS_ALL, None, nsplit)
+        logits = self.model.forward(b, self.kv)
+        self._sample_greedy(logits, self.s_tok, self.s_val, rows)
+        if self.feedback:
+            # feed the sampled token back and advance positions on the device: replays chain with no host work
+            self.s_ids[:rows].copy_(self.s_tok[:rows])
+            self.s_pos[:rows].add_(1)
+        return logits
+
+    def _run_rows(self, rows: int):
+        nsplit = self._nsplit(rows)
+        key = (rows, nsplit, self.feedback)
+        if not self.use_graphs:
+            self._forward_static(rows, nsplit)
+            return
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = _Graph()
+        g.calls += 1
+        if g.graph is not None:
+            g.graph.replay()
+        elif g.calls == 1:
+            self._forward_static(rows, nsplit)
+        else:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._forward_static(rows, nsplit)
+            g.graph = graph
+            graph.replay()
+
+    def set_rows(self, ids: list[int], pos: list[int], slots: list[int]):
+        """Upload one step's row descriptor from pinned host memory (async on the current stream)."""
+        n = len(ids)
+        self.h_in[0, :n] = torch.tensor(ids, dtype=torch.int32)
+        self.h_in[1, :n] = torch.tensor(pos, dtype=torch.int32)
+        self.h_in[2, :n] = torch.tensor(slots, dtype=torch.int32)
+        self.s_ids[:n].copy_(self.h_in[0, :n], non_blocking=True)
+        self.s_pos[:n].copy_(self.h_in[1, :n], non_blocking=True)
+        self.s_slot[:n].copy_(self.h_in[2, :n], non_blocking=True)
+
+    def step(self, ids: list[int], pos: list[int], slots: list[int]) -> list[int]:
+        """One batched decode / verify step with host round trip: H2D rows, forward, D2H tokens."""
+        n = len(ids)
+        for s, p in zip(slots, pos):
+            self.kv.reserve(s, p + 2)
+        self.set_rows(ids, pos, slots)
+        self._run_rows(n)
+        self.h_tok[:n].copy_(self.s_tok[:n], non_blocking=True)
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()
+        return self.h_tok[:n].tolist()
+
+    def decode_chain(self, first_ids: list[int], pos: list[int], slots: list[int], steps: int) -> torch.Tensor:
+        """``steps`` greedy steps for the given rows with the token fed back on the device (no host sync
+        between steps). Returns the generated tokens [steps, rows] (device tensor)."""
+        assert self.feedback
+        n = len(first_ids)
+        for s, p in zip(slots, pos):
+            self.kv.reserve(s, p + steps + 2)
+        self.set_rows(first_ids, pos, slots)
+        out = torch.empty(steps, n, dtype=torch.int32, device=self.device)
+        for i in range(steps):
+            self._run_rows(n)
+            out[i].copy_(self.s_tok[:n])
+        return out
+
+    # ------------------------------------------------------------------------------------------ generate
+    def generate(self, prompt: list[int], max_new: int, slot: int = 0, eos: int | None = None):
+        """Greedy generation for one sequence. Returns (tokens, GenStats)."""
+        st = GenStats(prompt_tokens=len(prompt))
+        t0 = time.perf_counter()
+        tok = self.prefill(slot, prompt)
+        if self.cuda:
+            torch.cuda.synchronize()
+        st.prefill_ms = (time.perf_counter() - t0) * 1e3
+        out = [tok]
+        pos = len(prompt)
+        t1 = time.perf_counter()
+        while len(out) < max_new and (eos is None or out[-1] != eos):
+            tok = self.step([out[-1]], [pos], [slot])[0]
+            out.append(tok)
+            pos += 1
+        st.decode_ms = (time.perf_counter() - t1) * 1e3
+        st.new_tokens = len(out)
+        return out, st

@@ -1,0 +1,90 @@
+"""Paged KV cache shared by every sequence slot.
+
+One pool per layer ``[pages, kv_heads, 64, head_dim]`` (a page is exactly one attention key tile), one
+device page table ``[slots, max_pages]`` read by the kernels, and a host free list. The reference keeps
+a dense ``[slot][layer][max_seq]`` pool for most models and pages only the GLM latent cache
+(src/runtime/kv_cache.cpp, inc/engine/core/kv_format.h:51-93); here every model is paged so 262144-token
+contexts and many short slots share the same 180 GB.
+"""
+from __future__ import annotations
+
+import torch
+
+PAGE = 64
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PagedKVCache:
+    def __init__(self, n_layers: int, n_kv: int, head_dim: int, num_pages: int, max_slots: int, max_seq: int,
+                 device, dtype=torch.bfloat16, v_head_dim: int | None = None):
+        self.n_layers, self.n_kv, self.head_dim = n_layers, n_kv, head_dim
+        self.v_head_dim = v_head_dim or head_dim
+        self.num_pages, self.max_slots = num_pages, max_slots
+        self.max_pages = (max_seq + PAGE - 1) // PAGE
+        self.device = device
+        # page 0 is the null page: unassigned table entries point at it
+        self.k = torch.zeros(n_layers, num_pages, n_kv, PAGE, head_dim, dtype=dtype, device=device)
+        self.v = torch.zeros(n_layers, num_pages, n_kv, PAGE, self.v_head_dim, dtype=dtype, device=device)
+        self.page_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32, device=device)
+        self.host_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32)
+        self.free = list(range(num_pages - 1, 0, -1))
+        self.slot_pages = [0] * max_slots  # pages held per slot
+
+    @staticmethod
+    def pages_for(n_tokens: int) -> int:
+        return (n_tokens + PAGE - 1) // PAGE
+
+    def free_pages(self) -> int:
+        return len(self.free)
+
+    def can_reserve(self, slot: int, n_tokens: int) -> bool:
+        return self.pages_for(n_tokens) - self.slot_pages[slot] <= len(self.free)
+
+    def reserve(self, slot: int, n_tokens: int) -> None:
+        """Make sure ``slot`` owns pages covering positions [0, n_tokens)."""
+        need = self.pages_for(n_tokens)
+        if need > self.max_pages:
+            raise OutOfPages(f"sequence of {n_tokens} tokens exceeds max_seq")
+        have = self.slot_pages[slot]
+        if need <= have:
+            return
+        if need - have > len(self.free):
+            raise OutOfPages(f"need {need - have} pages, {len(self.free)} free")
+        for i in range(have, need):
+            self.host_table[slot, i] = self.free.pop()
+        self.slot_pages[slot] = need
+        self.page_table[slot, have:need].copy_(self.host_table[slot, have:need], non_blocking=True)
+
+    def release(self, slot: int, keep_tokens: int = 0) -> None:
+        keep = self.pages_for(keep_tokens)
+        for i in range(keep, self.slot_pages[slot]):
+            self.free.append(int(self.host_table[slot, i]))
+            self.host_table[slot, i] = 0
+        if self.slot_pages[slot] > keep:
+            self.page_table[slot, keep:self.slot_pages[slot]].zero_()
+        self.slot_pages[slot] = keep
+
+    def layer(self, i: int):
+        return self.k[i], self.v[i]
+
+    # ---- snapshots (prefix cache): copy the rows [from_tok, to_tok) of a slot to / from host memory
+    def save_rows(self, slot: int, from_tok: int, to_tok: int) -> dict:
+        p0, p1 = from_tok // PAGE, self.pages_for(to_tok)
+        pages = self.host_table[slot, p0:p1].long().to(self.device)
+        return {"from": from_tok, "to": to_tok, "p0": p0,
+                "k": self.k[:, pages].to("cpu", non_blocking=False),
+                "v": self.v[:, pages].to("cpu", non_blocking=False)}
+
+    def load_rows(self, slot: int, snap: dict) -> None:
+        self.reserve(slot, snap["to"])
+        p0 = snap["p0"]
+        n = snap["k"].shape[1]
+        pages = self.host_table[slot, p0:p0 + n].long().to(self.device)
+        self.k[:, pages] = snap["k"].to(self.device)
+        self.v[:, pages] = snap["v"].to(self.device)
+
+    def bytes_per_token(self) -> int:
+        return self.n_layers * self.n_kv * (self.head_dim + self.v_head_dim) * self.k.element_size()
