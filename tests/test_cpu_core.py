@@ -1,0 +1,70 @@
+"""Host-side tests (no GPU): NVFP4 codec, paged KV bookkeeping, dense model on the CPU oracle path."""
+import torch
+
+from volta_engine_b200.models.dense import DenseConfig, DenseModel
+from volta_engine_b200.quant import nvfp4 as qn
+from volta_engine_b200.runtime.engine import Engine
+from volta_engine_b200.runtime.kv_cache import OutOfPages, PagedKVCache
+
+
+def test_e2m1_ties_and_saturation():
+    x = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -0.3, 0.0, -6.5])
+    want = torch.tensor([0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0, -0.5, 0.0, -6.0])
+    assert torch.equal(qn.e2m1_decode(qn.e2m1_encode(x)), want)
+
+
+def test_nvfp4_roundtrip_and_search_improves():
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(128, 256, generator=g) * 0.02
+    p, s, gs = qn.quantize_nvfp4(w, search=True)
+    p0, s0, gs0 = qn.quantize_nvfp4(w, search=False)
+    e1 = (qn.dequantize_nvfp4(p, s, gs) - w).norm() / w.norm()
+    e0 = (qn.dequantize_nvfp4(p0, s0, gs0) - w).norm() / w.norm()
+    assert e1 <= e0 and e1 < 0.1
+    assert p.shape == (128, 128) and s.shape == (128, 16)
+    # largest block scale maps near the E4M3 maximum
+    assert qn.e4m3_decode(s).max() >= 224
+
+
+def test_scale_layouts():
+    s = torch.arange(256 * 32, dtype=torch.int32).remainder(251).to(torch.uint8).reshape(256, 32)
+    a = qn.scales_atoms_512(s)
+    assert a.shape == (2, 8, 512)
+    r, kb = 200, 13
+    assert a[r // 128, kb // 4, ((r % 128) % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4] == s[r, kb]
+    b = qn.scales_blocked_k128(s)
+    assert b[r // 128, kb // 8, r % 128, kb % 8] == s[r, kb]
+
+
+def test_paged_kv_alloc_release():
+    kv = PagedKVCache(2, 2, 64, num_pages=6, max_slots=2, max_seq=512, device="cpu")
+    kv.reserve(0, 130)
+    assert kv.slot_pages[0] == 3 and kv.free_pages() == 2
+    assert len(set(kv.host_table[0, :3].tolist())) == 3 and 0 not in kv.host_table[0, :3].tolist()
+    assert not kv.can_reserve(1, 64 * 3)
+    try:
+        kv.reserve(1, 64 * 3)
+        assert False
+    except OutOfPages:
+        pass
+    kv.release(0, keep_tokens=64)
+    assert kv.slot_pages[0] == 1 and kv.free_pages() == 4
+
+
+def test_dense_cpu_prefill_equals_decode():
+    cfg = DenseConfig.tiny()
+    m = DenseModel(cfg, "cpu").init_random(seed=0, search=True)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (70,), generator=g).tolist()
+    kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    out, st = Engine(m, kv, use_graphs=False, prefill_chunk=32).generate(prompt, 6)
+    kv2 = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    nxt = Engine(m, kv2, use_graphs=False, prefill_chunk=1000).prefill(0, prompt + out[:4])
+    assert nxt == out[4]
+    assert st.new_tokens == 6
+
+
+def test_native_build_present():
+    from volta_engine_b200 import _build
+    libs = _build.build_all()
+    assert libs["kernels"].exists()

