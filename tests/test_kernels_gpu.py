@@ -180,3 +180,40 @@ def test_bf16_gemv_f32():
     W, x = rnd(4096 + 3, 1024, std=0.05, seed=20), rnd(6, 1024, seed=21)
     got = K.bf16_gemv_f32(W, x)
     assert_close(got.cpu(), x.cpu().float() @ W.cpu().float().t(), rel=1e-3, name="lm head gemv")
+
+
+@pytest.mark.parametrize("N,Kd", [(5120, 5120), (1024, 17408), (7168, 5120), (48, 128)])
+def test_nvfp4_gemv_mma_exact_and_batch_invariant(N, Kd):
+    w = rnd(N, Kd, std=0.02, seed=27, dtype=torch.float32)
+    p, s, g = qn.quantize_nvfp4(w, search=False)
+    s[0, 0] = 3       # force E4M3 subnormal scales and zero scales through the decode path
+    s[1, 1] = 0
+    wd = qn.dequantize_nvfp4(p.cpu(), s.cpu(), g)
+    wg, sg = qn.prepack_gv(p, s)
+    x = rnd(16, Kd, seed=28)
+    x[0, :8] = 0
+    res = rnd(16, N, seed=29)
+    want = x.cpu().float() @ wd.t()
+    full = K.nvfp4_gemv_mma(wg, sg, g, x, N, Kd)
+    assert_close(full.cpu(), want, name="gemv mma M=16")
+    for m in (1, 2, 5, 8, 9):
+        part = K.nvfp4_gemv_mma(wg, sg, g, x[:m], N, Kd)
+        assert torch.equal(part, full[:m]), f"row result depends on batch size (M={m})"
+    for ks in (1, 2, 4):
+        if ks <= (Kd // 64) // 4 or ks == 1:
+            alt = K.nvfp4_gemv_mma(wg, sg, g, x[:3], N, Kd, ks=ks)
+            assert_close(alt.cpu(), want[:3], name=f"gemv mma ks={ks}")
+    wres = K.nvfp4_gemv_mma(wg, sg, g, x[:3], N, Kd, residual=res[:3])
+    assert_close(wres.cpu(), want[:3] + res[:3].cpu().float(), name="gemv mma residual")
+    # products are exact and accumulated in fp32: compare against the fp64 product at fp32-level tolerance
+    one = K.nvfp4_gemv_mma(wg, sg, g, x[:1], N, Kd).float().cpu()
+    ref64 = (x[:1].cpu().double() @ wd.double().t()).float()
+    assert (one - ref64.to(torch.bfloat16).float()).abs().max() <= 2 * ref64.abs().max() * 2 ** -8
+
+
+def test_argmax_wide_two_stage():
+    logits = rnd(3, 151936, seed=30, dtype=torch.float32)
+    logits[1, 151935] = 99.0
+    idx, val = K.argmax(logits, id_offset=5)
+    ridx, rval = ref.argmax(logits.cpu(), 5)
+    assert torch.equal(idx.cpu(), ridx) and torch.equal(val.cpu(), rval)

@@ -56,6 +56,34 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   }
 }
 
+// Two-stage argmax for wide vocabularies: grid (rows, NB) partial winners, then one small CTA per row.
+__global__ void __launch_bounds__(256) argmax_part_kernel(const float* __restrict__ logits, long stride, int V,
+                                                          float* __restrict__ pval, int* __restrict__ pidx) {
+  __shared__ ArgVal red[33];
+  const float* row = logits + blockIdx.x * stride;
+  const int nb = gridDim.y, per = (V + nb - 1) / nb;
+  const int lo = blockIdx.y * per, hi = min(V, lo + per);
+  ArgVal a{-FLT_MAX, 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) a = better(a, ArgVal{row[i], i});
+  a = block_argmax(a, red);
+  if (threadIdx.x == 0) {
+    pval[blockIdx.x * nb + blockIdx.y] = a.v;
+    pidx[blockIdx.x * nb + blockIdx.y] = a.i;
+  }
+}
+__global__ void __launch_bounds__(64) argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
+                                                          int nb, int id_offset, int* __restrict__ idx,
+                                                          float* __restrict__ val) {
+  __shared__ ArgVal red[33];
+  ArgVal a{-FLT_MAX, 0x7fffffff};
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) a = better(a, ArgVal{pval[blockIdx.x * nb + i], pidx[blockIdx.x * nb + i]});
+  a = block_argmax(a, red);
+  if (threadIdx.x == 0) {
+    idx[blockIdx.x] = a.i + id_offset;
+    if (val) val[blockIdx.x] = a.v;
+  }
+}
+
 // Top-K (K <= 16) by K rounds of block argmax with a "strictly after the previous pick" filter, so the
 // logits are never modified: pick j is the best (value, id) pair ordered after pick j-1.
 __global__ void __launch_bounds__(1024) topk_kernel(const float* __restrict__ logits, long stride, int V,
@@ -99,6 +127,16 @@ int ve_argmax(const void* logits, long stride, int rows, int V, int id_offset, v
               cudaStream_t st) {
   if (rows <= 0) return 0;
   argmax_kernel<<<rows, 1024, 0, st>>>((const float*)logits, stride, V, id_offset, (int*)idx, (float*)val);
+  VE_CHECK_LAUNCH();
+}
+
+// scratch: rows * nb floats + rows * nb ints
+int ve_argmax2(const void* logits, long stride, int rows, int V, int id_offset, void* idx, void* val, void* pval,
+               void* pidx, int nb, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  dim3 grid(rows, nb);
+  argmax_part_kernel<<<grid, 256, 0, st>>>((const float*)logits, stride, V, (float*)pval, (int*)pidx);
+  argmax_final_kernel<<<rows, 64, 0, st>>>((const float*)pval, (const int*)pidx, nb, id_offset, (int*)idx, (float*)val);
   VE_CHECK_LAUNCH();
 }
 

@@ -171,6 +171,8 @@ def make_prefill_tiles(slots, G, device, max_rows_per_tile=64):
 
 
 # ---------------------------------------------------------------------------------------------- sampling
+_argmax_scratch = {}
+ARGMAX_NB = 64
 def argmax(logits, id_offset=0, idx_out=None, val_out=None):
     if not logits.is_cuda:
         i, v = ref.argmax(logits, id_offset)
@@ -185,7 +187,17 @@ def argmax(logits, id_offset=0, idx_out=None, val_out=None):
         idx_out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     if val_out is None:
         val_out = torch.empty(rows, dtype=torch.float32, device=logits.device)
-    call("argmax", "pliiipp", ptr(logits), logits.stride(0), rows, V, id_offset, ptr(idx_out), ptr(val_out))
+    if V >= 8192 and rows <= 64:
+        key = str(logits.device)
+        sc = _argmax_scratch.get(key)
+        if sc is None:
+            sc = (torch.empty(64 * ARGMAX_NB, dtype=torch.float32, device=logits.device),
+                  torch.empty(64 * ARGMAX_NB, dtype=torch.int32, device=logits.device))
+            _argmax_scratch[key] = sc
+        call("argmax2", "pliiippppi", ptr(logits), logits.stride(0), rows, V, id_offset, ptr(idx_out), ptr(val_out),
+             ptr(sc[0]), ptr(sc[1]), ARGMAX_NB)
+    else:
+        call("argmax", "pliiipp", ptr(logits), logits.stride(0), rows, V, id_offset, ptr(idx_out), ptr(val_out))
     return idx_out, val_out
 
 
@@ -239,6 +251,47 @@ def nvfp4_gemv(packed, scales, gscale, x, out=None, residual=None):
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     call("nvfp4_gemv", "ppfplplpliii", ptr(packed), ptr(scales), float(gscale), ptr(x), x.stride(0), ptr(out),
          out.stride(0), ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K)
+    return out
+
+
+_gv_scratch = {}
+
+
+def gv_scratch(device):
+    """Per-device split-K scratch of the tensor-core mat-vec: (fp32 partials, zeroed arrival counters)."""
+    key = str(device)
+    t = _gv_scratch.get(key)
+    if t is None:
+        t = (torch.empty(GV_WS_ROWS * 16, dtype=torch.float32, device=device),
+             torch.zeros(4096, dtype=torch.int32, device=device))
+        _gv_scratch[key] = t
+    return t
+
+
+GV_WS_ROWS = 1 << 16  # KS * N may not exceed this
+
+
+def gv_splits(N: int, K: int) -> int:
+    ctas = N // 16
+    ks = max(1, min(8, -(-148 * 6 // ctas)))
+    ks = min(ks, max(1, (K // 64) // 4))
+    while ks > 1 and ks * N > GV_WS_ROWS:
+        ks -= 1
+    return ks
+
+
+def nvfp4_gemv_mma(wg, sg, gscale, x, N, K, out=None, residual=None, ks=None):
+    """Decode / verify mat-vec (M <= 16) on the prepacked GV layout: out [M, N] bf16."""
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if ks is None:
+        ks = gv_splits(N, K)
+    ws, cnt = gv_scratch(x.device)
+    assert N // 16 <= cnt.numel()
+    call("nvfp4_gemv_mma", "ppfplplpliiiipp", ptr(wg), ptr(sg), float(gscale), ptr(x), x.stride(0), ptr(out),
+         out.stride(0), ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, ks, ptr(ws),
+         ptr(cnt))
     return out
 
 

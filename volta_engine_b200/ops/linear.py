@@ -21,6 +21,7 @@ GEMV_MAX_ROWS = 16
 # baseline / bring-up aid); unset = hand-written kernels only.
 import os
 GEMM_BACKEND = os.environ.get("VOLTA_GEMM_BACKEND", "native")
+GEMV_KERNEL = os.environ.get("VOLTA_GEMV", "auto")  # auto | mma (prepacked tensor-core mat-vec) | simt
 
 
 class LinearBF16:
@@ -56,6 +57,7 @@ class LinearNVFP4:
         self.gemm_mode = gemm_mode
         self._sf_k128 = None
         self._sf_atoms = None
+        self._gv = None
 
     @classmethod
     def from_dense(cls, w: torch.Tensor, gemm_mode="w4a16", search=True):
@@ -68,6 +70,8 @@ class LinearNVFP4:
             self._sf_k128 = qn.scales_blocked_k128(self.scales)
         if self.gemm_mode == "w4a4" and self._sf_atoms is None:
             self._sf_atoms = qn.scales_atoms_512(self.scales)
+        if self._gv is None and self.packed.is_cuda and self.out_features % 16 == 0 and self.in_features % 64 == 0:
+            self._gv = qn.prepack_gv(self.packed, self.scales)
         return self
 
     def dequant(self):
@@ -81,6 +85,11 @@ class LinearNVFP4:
             return y.to(x.dtype)
         rows = x.shape[0]
         if rows <= GEMV_MAX_ROWS:
+            # one row: the SIMT streaming kernel is faster; 2..16 rows: the tensor-core kernel costs the same
+            # as one row. Both sum exact products in fp32, so they agree to fp32 rounding.
+            if self._gv is not None and (GEMV_KERNEL == "mma" or (GEMV_KERNEL == "auto" and rows > 1)):
+                return K.nvfp4_gemv_mma(self._gv[0], self._gv[1], self.gscale, x, self.out_features,
+                                        self.in_features, out=out, residual=residual)
             return K.nvfp4_gemv(self.packed, self.scales, self.gscale, x, out=out, residual=residual)
         mode = self.gemm_mode
         if GEMM_BACKEND == "cublas":

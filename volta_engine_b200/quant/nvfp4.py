@@ -124,3 +124,53 @@ def scales_atoms_512(scales: torch.Tensor) -> torch.Tensor:
     pad[:R] = scales
     t = pad.reshape(RB, 4, 32, KB // 4, 4)          # rb, r//32, r%32, kg, j
     return t.permute(0, 3, 2, 1, 4).reshape(RB, KB // 4, 512).contiguous()
+
+
+# ---------------------------------------------------------------------------------------------------
+# Decode ("GV") layout: weights re-ordered at load time into the register order of the tensor-core
+# mat-vec kernel. One 32-bit word per lane per 16x16 (rows x k) block holds that lane's 8 codes as four
+# (first, second) pairs p = 0..3:
+#     bits [3p+2 : 3p]      magnitude of the pair's first code     bit 12+p   its sign
+#     bits [16+3p+2 : 16+3p] magnitude of the second code           bit 28+p   its sign
+# so that ((W << 6) >> 3p) & 0x01C001C0 | (W << (3-p)) & 0x80008000 is the bf16x2 register holding
+# code * 2^-126 (an E2M1 magnitude m placed at bf16 bits [8:6] is exactly m * 2^-126, subnormal included).
+# Lane (g, t) of block kb owns rows g, g+8 and k = 16*kb + 4t .. 4t+3:
+#     p0 = row g   (k+0, k+1)   p1 = row g+8 (k+0, k+1)   p2 = row g (k+2, k+3)   p3 = row g+8 (k+2, k+3)
+# Words of 4 consecutive k blocks are adjacent, so a warp reads 512 contiguous bytes per 16 rows x 64 k.
+# ---------------------------------------------------------------------------------------------------
+def prepack_gv(packed: torch.Tensor, scales: torch.Tensor):
+    """(packed [N,K/2], scales [N,K/16]) -> (Wg int32 [N/16, K/64, 32, 4], Sg uint8 [N/16, K/64, 16, 4])."""
+    N, K = packed.shape[0], packed.shape[1] * 2
+    assert N % 16 == 0 and K % 64 == 0
+    codes = unpack_codes(packed).to(torch.int64)              # [N, K]
+    c = codes.reshape(N // 16, 2, 8, K // 64, 4, 4, 4)         # rb, half(h), g, kg, kb, t, j (k = 16kb + 4t + j)
+    mag, sgn = c & 7, (c >> 3) & 1
+    word = torch.zeros(N // 16, 8, K // 64, 4, 4, dtype=torch.int64, device=packed.device)  # rb, g, kg, kb, t
+    for p in range(4):
+        h, j0 = p & 1, (p >> 1) * 2
+        m0, s0 = mag[:, h, :, :, :, :, j0], sgn[:, h, :, :, :, :, j0]
+        m1, s1 = mag[:, h, :, :, :, :, j0 + 1], sgn[:, h, :, :, :, :, j0 + 1]
+        word |= (m0 << (3 * p)) | (s0 << (12 + p)) | (m1 << (16 + 3 * p)) | (s1 << (28 + p))
+    # -> [rb, kg, lane = g*4 + t, kb]
+    wg = word.permute(0, 2, 1, 4, 3).reshape(N // 16, K // 64, 32, 4)
+    wg = torch.where(wg >= 2 ** 31, wg - 2 ** 32, wg).to(torch.int32).contiguous()
+    sg = scales.reshape(N // 16, 16, K // 64, 4).permute(0, 2, 1, 3).contiguous()
+    return wg, sg
+
+
+def unpack_gv(wg: torch.Tensor, sg: torch.Tensor):
+    """Inverse of :func:`prepack_gv` (test helper): -> (packed [N,K/2], scales [N,K/16])."""
+    RB, KG = wg.shape[0], wg.shape[1]
+    N, K = RB * 16, KG * 64
+    w = wg.to(torch.int64) & 0xFFFFFFFF
+    w = w.reshape(RB, KG, 8, 4, 4)                              # rb, kg, g, t, kb
+    codes = torch.zeros(RB, 2, 8, KG, 4, 4, 4, dtype=torch.int64, device=wg.device)
+    for p in range(4):
+        h, j0 = p & 1, (p >> 1) * 2
+        m0, s0 = (w >> (3 * p)) & 7, (w >> (12 + p)) & 1
+        m1, s1 = (w >> (16 + 3 * p)) & 7, (w >> (28 + p)) & 1
+        codes[:, h, :, :, :, :, j0] = (m0 | (s0 << 3)).permute(0, 2, 1, 4, 3)
+        codes[:, h, :, :, :, :, j0 + 1] = (m1 | (s1 << 3)).permute(0, 2, 1, 4, 3)
+    packed = pack_codes(codes.reshape(N, K).to(torch.uint8))
+    scales = sg.permute(0, 2, 1, 3).reshape(N, K // 16).contiguous()
+    return packed, scales
