@@ -184,3 +184,58 @@ int ve_nvfp4_gemv_mma(const void* Wg, const void* Sg, float gscale, const void* 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in volta_noalloc.h; the reference has nothing like it).
+//
+// Some hosts of this library must not touch the CUDA allocator while they serve: an engine that took one
+// arena at boot and promised "no allocation while decoding", a plugin living inside another runtime's
+// memory pool, a latency-critical loop that cannot afford the device-wide synchronisation cudaMalloc and
+// cudaFree imply. For them the split-K scratch of the mat-vec lives in the two file-scope device arrays
+// below, which every GPU that loads this library holds until the process exits (2 MiB + 16 KiB).
+// ------------------------------------------------------------------------------------------------
+namespace ve {
+constexpr int kStaticWsRows = 32768;      // limit on KS * N
+constexpr int kStaticCounters = 4096;     // limit on N / 16
+static __device__ __align__(256) float g_static_ws[(size_t)kStaticWsRows * 16];
+static __device__ __align__(256) int g_static_counters[kStaticCounters];
+constexpr int kMaxDevices = 64;
+static float* g_ws_addr[kMaxDevices];     // device addresses of the arrays above, resolved per device
+static int* g_cnt_addr[kMaxDevices];
+}  // namespace ve
+
+extern "C" {
+
+int ve_nvfp4_gemv_mma_static(const void* Wg, const void* Sg, float gscale, const void* x, long x_stride, void* out,
+                             long out_stride, const void* residual, long res_stride, int M, int N, int K, int KS,
+                             cudaStream_t st) {
+  if (M <= 0 || M > 16 || N <= 0 || N % 16 || K <= 0 || K % 64 || KS < 1) return cudaErrorInvalidValue;
+  // sizes beyond the built-in scratch are refused, never truncated
+  if ((long)KS * N > kStaticWsRows || N / 16 > kStaticCounters) return cudaErrorInvalidValue;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!g_ws_addr[dev]) {
+    // In host code the array names are only handles; the kernel needs the addresses the current device
+    // gave them. Resolved on the first call for each device.
+    float* ws = nullptr;
+    int* cnt = nullptr;
+    e = cudaGetSymbolAddress((void**)&ws, g_static_ws);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetSymbolAddress((void**)&cnt, g_static_counters);
+    if (e != cudaSuccess) return (int)e;
+    g_cnt_addr[dev] = cnt;
+    g_ws_addr[dev] = ws;
+  }
+  if (KS > 1) {
+    // the arrival counters must read zero when the kernel starts; the partial sums need no clearing
+    // because every slot that is read has been written by this call
+    e = cudaMemsetAsync(g_cnt_addr[dev], 0, (size_t)(N / 16) * sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return ve_nvfp4_gemv_mma(Wg, Sg, gscale, x, x_stride, out, out_stride, residual, res_stride, M, N, K, KS,
+                           g_ws_addr[dev], g_cnt_addr[dev], st);
+}
+
+}  // extern "C"
