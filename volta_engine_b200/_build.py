@@ -107,7 +107,7 @@ def build_host(force: bool = False) -> Path:
             return lib
         raise RuntimeError("g++ not found and libvolta_host.so is not built")
     srcs = sorted((CSRC / "host").glob("*.cpp"))
-    headers = sorted((CSRC / "host").glob("*.h"))
+    headers = sorted((CSRC / "host").glob("*.h")) + sorted((CSRC / "host").glob("*.inc"))
     if not srcs:
         return lib
     return _build_lib("volta_host", srcs, headers, [cxx], CXX_FLAGS, ["-pthread", "-ldl"], force)
