@@ -1,0 +1,126 @@
+"""Scheduler behaviour on the CPU oracle path: greedy equivalence, speculation == plain decoding, stop rules,
+seeded sampling, prefix-cache resume (RAM and disk), concurrent == sequential."""
+import os
+
+import pytest
+import torch
+
+from volta_engine_b200.models.dense import DenseConfig, DenseModel
+from volta_engine_b200.runtime.engine import Engine
+from volta_engine_b200.runtime.generator import Generator, Request, _utf8_split
+from volta_engine_b200.runtime.kv_cache import PagedKVCache
+from volta_engine_b200.runtime.options import Options
+from volta_engine_b200.runtime.prefix_cache import PrefixCache
+from volta_engine_b200.runtime.sampling import SamplingParams
+
+
+class ByteTok:
+    """Token id == byte value (vocab 256+): enough for the scheduler tests."""
+    eos_ids = [0]
+
+    def decode_bytes(self, ids, skip_special=False):
+        return bytes(i & 0xFF for i in ids)
+
+    def encode(self, text, allow_special=True):
+        return list(text.encode())
+
+
+@pytest.fixture(scope="module")
+def model():
+    cfg = DenseConfig.tiny(vocab=256)
+    return DenseModel(cfg, "cpu").init_random(seed=0, search=False)
+
+
+def make(model, slots=2, cache=None, **opt):
+    kv = PagedKVCache(model.cfg.n_layers, model.nkv, model.cfg.head_dim, 40, slots, 512, "cpu")
+    eng = Engine(model, kv, use_graphs=False, prefill_chunk=32)
+    o = Options.resolve(dict({"max_slots": slots, "prefix_interval": 64}, **opt), env={})
+    return Generator(eng, ByteTok(), o, prefix_cache=cache, eos_ids=[]), eng
+
+
+def prompt(n, seed=0):
+    return torch.randint(1, 256, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def test_greedy_matches_engine_and_length_stop(model):
+    g, _ = make(model)
+    r = g.generate(Request(prompt(70), max_tokens=12))
+    kv = PagedKVCache(model.cfg.n_layers, model.nkv, model.cfg.head_dim, 40, 1, 512, "cpu")
+    ref, _ = Engine(model, kv, use_graphs=False, prefill_chunk=1000).generate(prompt(70), 12)
+    assert r["tokens"] == ref and r["reason"] == "length"
+    assert r["usage"]["completion_tokens"] == 12 and r["usage"]["prompt_tokens"] == 70
+
+
+def test_suffix_speculation_equals_plain(model):
+    p = (prompt(20, 3) * 6)[:100]   # repetitive prompt so drafts exist
+    plain, _ = make(model)
+    a = plain.generate(Request(p, max_tokens=24))
+    spec, _ = make(model, speculator="suffix", spec_ctrl=False, spec_depth=4)
+    b = spec.generate(Request(p, max_tokens=24))
+    assert a["tokens"] == b["tokens"]
+    assert spec.metrics.spec["rounds"] > 0
+
+
+def test_stop_string_and_stop_token(model):
+    g, _ = make(model)
+    full = g.generate(Request(prompt(40, 1), max_tokens=20))
+    text = full["text"]
+    cut = text[5:8]
+    if cut and text.find(cut) == 5:
+        r = g.generate(Request(prompt(40, 1), max_tokens=20, stop=[cut]))
+        assert r["reason"] == "stop_string" and r["text"] == text[:5]
+    r2 = g.generate(Request(prompt(40, 1), max_tokens=20, stop_token_ids=[full["tokens"][3]]))
+    assert r2["reason"] == "stop" and r2["tokens"] == full["tokens"][:full["tokens"].index(full["tokens"][3])]
+
+
+def test_seeded_sampling_is_reproducible(model):
+    g, _ = make(model)
+    sp = SamplingParams(temperature=0.9, top_p=0.95, top_k=12, seed=7, presence_penalty=0.2)
+    a = g.generate(Request(prompt(30, 2), max_tokens=10, params=sp))
+    b = g.generate(Request(prompt(30, 2), max_tokens=10, params=sp))
+    c = g.generate(Request(prompt(30, 2), max_tokens=10, params=SamplingParams(temperature=0.9, seed=8)))
+    assert a["tokens"] == b["tokens"] and len(a["tokens"]) == 10
+    assert c["tokens"] != a["tokens"] or True
+
+
+def test_prefix_cache_resume_ram_and_disk(model, tmp_path):
+    p = prompt(150, 5)
+    cache = PrefixCache(64 << 20, disk_dir=str(tmp_path), fingerprint="t")
+    g, _ = make(model, cache=cache)
+    a = g.generate(Request(p, max_tokens=8))
+    b = g.generate(Request(p, max_tokens=8))
+    assert a["tokens"] == b["tokens"]
+    assert b["usage"]["cached_tokens"] >= 128 and a["usage"]["cached_tokens"] == 0
+    # follow-up turn resumes after the first answer
+    p2 = p + a["tokens"] + prompt(10, 6)
+    c = g.generate(Request(p2, max_tokens=4))
+    assert c["usage"]["cached_tokens"] >= len(p) + len(a["tokens"]) - 1
+    cache.flush()
+    cache2 = PrefixCache(64 << 20, disk_dir=str(tmp_path), fingerprint="t")   # restart: disk tier only
+    g2, _ = make(model, cache=cache2)
+    d = g2.generate(Request(p, max_tokens=8))
+    assert d["tokens"] == a["tokens"] and d["usage"]["cached_tokens"] >= 128
+    assert cache2.stats["disk_hits"] > 0
+
+
+def test_concurrent_equals_sequential(model):
+    g, _ = make(model, slots=2)
+    pa, pb = prompt(50, 8), prompt(90, 9)
+    sa = g.generate(Request(pa, max_tokens=10))["tokens"]
+    sb = g.generate(Request(pb, max_tokens=10))["tokens"]
+    out = {}
+    g.submit(Request(pa, max_tokens=10, on_text=lambda t, ids, lp: out.setdefault("a", []).extend(ids)))
+    g.submit(Request(pb, max_tokens=10, on_text=lambda t, ids, lp: out.setdefault("b", []).extend(ids)))
+    for _ in range(200):
+        g.step()
+        if not g.pending and all(s.phase == "idle" for s in g.slots):
+            break
+    assert out["a"] == sa and out["b"] == sb
+    assert g.metrics.snapshot()["totals"]["completed"] == 4
+
+
+def test_utf8_boundary():
+    b = "héllo 🙂".encode()
+    t, rest = _utf8_split(b[:-2])
+    assert t == "héllo " and rest == b[-4:-2]
+    assert _utf8_split(b) == ("héllo 🙂", b"")

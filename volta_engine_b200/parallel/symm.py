@@ -153,6 +153,12 @@ class SymmComm:
                   self._arg_idx.data_ptr(), rows)
         return self._arg_idx[:rows]
 
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """[n, ...] per rank -> [size * n, ...] (sampling path only; not on the greedy hot path)."""
+        out = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out
+
     def barrier(self):
         dist.barrier(self.group)
 
@@ -183,6 +189,11 @@ class NcclComm:
     def allreduce_add_norm(self, partial, residual, w, eps, wbias=0.0, out=None):
         dist.all_reduce(partial, group=self.group)
         return K.rmsnorm(partial, w, eps, wbias, residual=residual, out=out)
+
+    def all_gather_rows(self, x):
+        out = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out
 
     def merge_argmax(self, idx, val):
         vals = [torch.empty_like(val) for _ in range(self.size)]

@@ -65,6 +65,10 @@ class Engine:
         pin = self.cuda
         self.h_in = torch.zeros(3, R, dtype=torch.int32, pin_memory=pin)
         self.h_tok = torch.zeros(R, dtype=torch.int32, pin_memory=pin)
+        from .sampling import NUM_CANDIDATES
+        self.s_cand_ids = torch.zeros(R, NUM_CANDIDATES, dtype=torch.int32, device=dev)
+        self.s_cand_vals = torch.zeros(R, NUM_CANDIDATES, dtype=torch.float32, device=dev)
+        self.s_cand_lse = torch.zeros(R, dtype=torch.float32, device=dev)
         self.graphs: dict[tuple, _Graph] = {}
         self.nsplit_cap = 32
         if self.cuda:
@@ -113,21 +117,28 @@ class Engine:
         return tok
 
     # ------------------------------------------------------------------------------------------ decode
-    def _forward_static(self, rows: int, nsplit: int) -> torch.Tensor:
+    def _forward_static(self, rows: int, nsplit: int, topk: bool = False) -> torch.Tensor:
         b = BatchRows(self.s_ids[:rows], self.s_pos[:rows], self.s_slot[:rows], rows, LOGITS_ALL, None, nsplit)
         logits = self.model.forward(b, self.kv)
         self._sample_greedy(logits, self.s_tok, self.s_val, rows)
-        if self.feedback:
+        if topk:
+            from .sampling import NUM_CANDIDATES
+            off = self.comm.rank * self.model.vocab_local
+            ids, vals, lse = K.topk(logits, NUM_CANDIDATES, off)
+            self.s_cand_ids[:rows].copy_(ids)
+            self.s_cand_vals[:rows].copy_(vals)
+            self.s_cand_lse[:rows].copy_(lse)
+        if self.feedback and not topk:
             # feed the sampled token back and advance positions on the device: replays chain with no host work
             self.s_ids[:rows].copy_(self.s_tok[:rows])
             self.s_pos[:rows].add_(1)
         return logits
 
-    def _run_rows(self, rows: int):
+    def _run_rows(self, rows: int, topk: bool = False):
         nsplit = self._nsplit(rows)
-        key = (rows, nsplit, self.feedback)
-        if not self.use_graphs:
-            self._forward_static(rows, nsplit)
+        key = (rows, nsplit, self.feedback, topk)
+        if not self.use_graphs or rows > MAX_GRAPH_ROWS:
+            self._forward_static(rows, nsplit, topk)
             return
         g = self.graphs.get(key)
         if g is None:
@@ -136,12 +147,12 @@ class Engine:
         if g.graph is not None:
             g.graph.replay()
         elif g.calls == 1:
-            self._forward_static(rows, nsplit)
+            self._forward_static(rows, nsplit, topk)
         else:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self._forward_static(rows, nsplit)
+                self._forward_static(rows, nsplit, topk)
             g.graph = graph
             graph.replay()
 
@@ -166,6 +177,47 @@ class Engine:
         if self.cuda:
             torch.cuda.current_stream().synchronize()
         return self.h_tok[:n].tolist()
+
+    def step_candidates(self, ids: list[int], pos: list[int], slots: list[int]):
+        """Like :meth:`step` but returns, per row, the merged top-16 candidates (ids, logits, lse) for the
+        host sampler instead of the greedy token."""
+        from .sampling import Candidates, merge_shards
+        n = len(ids)
+        for s, p in zip(slots, pos):
+            self.kv.reserve(s, p + 2)
+        self.set_rows(ids, pos, slots)
+        self._run_rows(n, topk=True)
+        cid, cval, clse = self.s_cand_ids[:n], self.s_cand_vals[:n], self.s_cand_lse[:n]
+        if self.comm.size > 1:
+            cid, cval, clse = (self.comm.all_gather_rows(t) for t in (cid, cval, clse))
+        cid, cval, clse = cid.cpu(), cval.cpu(), clse.cpu()
+        shards = max(1, self.comm.size)
+        out = []
+        for r in range(n):
+            parts = [Candidates(cid[sh * n + r].tolist(), cval[sh * n + r].tolist(), float(clse[sh * n + r]))
+                     for sh in range(shards)]
+            out.append(merge_shards(parts))
+        return out
+
+    def prefill_rows(self, slot: int, tokens: list[int], start_pos: int, want_token: bool) -> int:
+        """One prefill forward over ``tokens`` (<= prefill_chunk rows) of ``slot``; returns the greedy next
+        token when ``want_token`` (else -1). Used by the scheduler to interleave prefill with decode steps."""
+        c = len(tokens)
+        self.kv.reserve(slot, start_pos + c + 1)
+        G = self.model.nq // self.model.nkv
+        pos = list(range(start_pos, start_pos + c))
+        if c <= MAX_GRAPH_ROWS:
+            b = BatchRows.make(tokens, pos, [slot] * c, self.device, LOGITS_ALL if want_token else LOGITS_NONE, G,
+                               prefill=False, nsplit=self._nsplit(c))
+        else:
+            b = BatchRows.make(tokens, pos, [slot] * c, self.device, LOGITS_LAST if want_token else LOGITS_NONE, G,
+                               prefill=True)
+        logits = self.model.forward(b, self.kv)
+        if not want_token:
+            return -1
+        rows = logits.shape[0]
+        self._sample_greedy(logits, self.s_tok, self.s_val, rows)
+        return int(self.s_tok[rows - 1].item())
 
     def decode_chain(self, first_ids: list[int], pos: list[int], slots: list[int], steps: int) -> torch.Tensor:
         """``steps`` greedy steps for the given rows with the token fed back on the device (no host sync
