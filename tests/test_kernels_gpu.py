@@ -217,3 +217,22 @@ def test_argmax_wide_two_stage():
     idx, val = K.argmax(logits, id_offset=5)
     ridx, rval = ref.argmax(logits.cpu(), 5)
     assert torch.equal(idx.cpu(), ridx) and torch.equal(val.cpu(), rval)
+
+
+@pytest.mark.parametrize("gtype", [8, 2, 12, 14])
+def test_gguf_fused_gemv_and_dequant(gtype):
+    from volta_engine_b200.ops.linear_gguf import LinearGGUF
+    from volta_engine_b200.quant import gguf as gq
+    N, Kd = 1000, 2048
+    w = rnd(N, Kd, std=0.02, seed=40, dtype=torch.float32)
+    lin = LinearGGUF.from_dense(w, gtype)
+    wd = gq.dequantize(lin.raw.cpu(), gtype, Kd)
+    assert_close(lin.dequant().cpu(), wd, cos_min=0.9999, rel=0.004, name="gguf dequant")
+    x = rnd(16, Kd, seed=41)
+    want = x.cpu().float() @ wd.t()
+    full = lin.forward(x)
+    assert_close(full.cpu(), want, name=f"gguf gemv type {gtype}")
+    one = lin.forward(x[:1])
+    assert torch.equal(one, full[:1]), "first row differs between M=1 and M=16"
+    big = lin.forward(rnd(40, Kd, seed=42))
+    assert_close(big.cpu(), rnd(40, Kd, seed=42).cpu().float() @ wd.t(), name="gguf prefill path")

@@ -97,6 +97,12 @@ class DenseModel:
     def _make_linear(self, w: torch.Tensor, search: bool):
         if self.cfg.quant == "nvfp4":
             return LinearNVFP4.from_dense(w, self.cfg.gemm_mode, search=search).prepare()
+        if self.cfg.quant.startswith("gguf_"):
+            from ..ops.linear_gguf import LinearGGUF
+            from ..quant import gguf as gq
+            gtype = {"gguf_q8_0": gq.GGML_Q8_0, "gguf_q4_0": gq.GGML_Q4_0, "gguf_q4_k": gq.GGML_Q4_K,
+                     "gguf_q6_k": gq.GGML_Q6_K}[self.cfg.quant]
+            return LinearGGUF.from_dense(w, gtype, act_q8=self.cfg.gemm_mode == "q8_act")
         return LinearBF16(w.to(torch.bfloat16))
 
     def init_random(self, seed: int = 1, std: float = 0.02, search: bool = False):
@@ -150,7 +156,7 @@ class DenseModel:
         hi = min(cfg.vocab, lo + self.vocab_local)
         if hi > lo:
             head[: hi - lo] = full[lo:hi]
-        self.lm_head = LinearBF16(head)
+        self.lm_head = self._make_linear(head.float(), search) if cfg.quant.startswith("gguf_") else LinearBF16(head)
         return self
 
     def weight_bytes(self) -> int:
