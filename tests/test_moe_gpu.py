@@ -1,0 +1,87 @@
+"""MoE kernels and model on the GPU against the fp32 CPU statement."""
+import pytest
+import torch
+
+from volta_engine_b200._lib import call, ptr
+from volta_engine_b200.models.moe import MoEConfig, MoEModel, route_reference
+from volta_engine_b200.runtime.batch import BatchRows
+from volta_engine_b200.runtime.engine import Engine
+from volta_engine_b200.runtime.kv_cache import PagedKVCache
+from util import assert_close, cos
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("router,n_group,topk_group,E,k", [("softmax", 1, 1, 512, 10), ("sigmoid", 1, 1, 128, 8),
+                                                          ("sigmoid", 8, 4, 256, 8)])
+def test_router_select(router, n_group, topk_group, E, k):
+    cfg = MoEConfig(n_experts=E, top_k=k, router=router, router_scale=2.5 if router == "sigmoid" else 1.0,
+                    n_group=n_group, topk_group=topk_group)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    logits = torch.randn(7, E, generator=g, device=DEV)
+    logits[3, 5] = logits[3, 9]                      # a tie: lowest index first
+    bias = torch.randn(E, generator=g, device=DEV) * 0.1 if router == "sigmoid" else None
+    ids = torch.empty(7, k, dtype=torch.int32, device=DEV)
+    w = torch.empty(7, k, dtype=torch.float32, device=DEV)
+    call("router_select", "pliiiipfiipp", ptr(logits), logits.stride(0), 7, E, k, 1 if router == "sigmoid" else 0,
+         ptr(bias), float(cfg.router_scale), n_group, topk_group, ptr(ids), ptr(w))
+    rid, rw = route_reference(logits.cpu(), cfg, bias.cpu() if bias is not None else None)
+    assert torch.equal(ids.cpu(), rid)
+    assert_close(w.cpu(), rw, rel=1e-4, abs_=1e-5, name="router weights")
+
+
+def _models(**kw):
+    cfg = MoEConfig.tiny_moe(**kw)
+    m_gpu = MoEModel(cfg, DEV).init_random(seed=4)
+    m_cpu = MoEModel(MoEConfig.tiny_moe(**kw), "cpu")
+    # same weights on the CPU: copy tensors instead of re-drawing (CPU and CUDA generators differ)
+    m_cpu.embed, m_cpu.final_norm = m_gpu.embed.cpu(), m_gpu.final_norm.cpu()
+    import copy
+    for L in m_gpu.layers:
+        Lc = copy.copy(L)
+        for name in ("qkv", "o_proj", "shared_gu", "shared_dn", "gate_up", "down"):
+            lin = getattr(L, name, None)
+            if lin is not None:
+                c = copy.copy(lin)
+                c.packed, c.scales = lin.packed.cpu(), lin.scales.cpu()
+                c._gv = c._sf_k128 = c._sf_atoms = None
+                setattr(Lc, name, c)
+        Lc.attn_norm, Lc.ffn_norm = L.attn_norm.cpu(), L.ffn_norm.cpu()
+        if not L.dense_ffn:
+            Lc.router = type(L.router)(L.router.weight.cpu())
+            Lc.router_bias = L.router_bias.cpu() if L.router_bias is not None else None
+            b = copy.copy(L.bank)
+            for n in ("gu_p", "gu_s", "gu_g", "dn_p", "dn_s", "dn_g"):
+                setattr(b, n, getattr(L.bank, n).cpu())
+            b.gu_sf = b.dn_sf = None
+            Lc.bank = b
+        m_cpu.layers.append(Lc)
+    m_cpu.lm_head = type(m_gpu.lm_head)(m_gpu.lm_head.weight.cpu())
+    return m_gpu, m_cpu
+
+
+@pytest.mark.parametrize("rows", [1, 5, 200])
+def test_moe_ffn_block_matches_reference(rows):
+    m_gpu, m_cpu = _models()
+    g = torch.Generator(device=DEV).manual_seed(rows)
+    x = torch.randn(rows, m_gpu.cfg.hidden, generator=g, device=DEV).to(torch.bfloat16)
+    L, Lc = m_gpu.layers[0], m_cpu.layers[0]
+    got = m_gpu.ffn_block(0, L, x, None, None)
+    want = m_cpu.ffn_block(0, Lc, x.cpu(), None, None)
+    assert_close(got.cpu(), want, rel=0.02, name=f"moe ffn rows={rows}")
+
+
+def test_moe_model_generates_like_reference_and_zipf_bias():
+    m_gpu, m_cpu = _models(router_bias_zipf=1.2)
+    prompt = torch.randint(0, m_gpu.cfg.vocab, (90,), generator=torch.Generator().manual_seed(1)).tolist()
+    kv = PagedKVCache(2, m_gpu.nkv, 64, 16, 1, 512, DEV)
+    kvc = PagedKVCache(2, m_cpu.nkv, 64, 16, 1, 512, "cpu")
+    b = BatchRows.make(prompt, list(range(90)), [0] * 90, DEV, "last", m_gpu.nq // m_gpu.nkv, prefill=True)
+    bc = BatchRows.make(prompt, list(range(90)), [0] * 90, "cpu", "last", m_cpu.nq // m_cpu.nkv, prefill=True)
+    kv.reserve(0, 128)
+    kvc.reserve(0, 128)
+    lg, lc = m_gpu.forward(b, kv), m_cpu.forward(bc, kvc)
+    assert cos(lg.cpu(), lc) > 0.995
+    out, _ = Engine(m_gpu, PagedKVCache(2, m_gpu.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64).generate(prompt, 6)
+    assert len(out) == 6

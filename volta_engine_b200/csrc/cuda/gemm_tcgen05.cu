@@ -30,6 +30,12 @@ struct GemmParams {
   const uint8_t* sfa;     // MODE 1: [N/128][K/128][128][8]; MODE 2: [N/128][K/64][512]
   const uint8_t* sfb;     // MODE 2: [ceil(T/128)][K/64][512]
   int* status;
+  // Grouped (mixture-of-experts) form: weights of all experts stacked along N, activation rows sorted by
+  // expert. tile_tab[tile] = {expert, first row, row count, 0}; blockIdx.y indexes tiles (count 0 = idle).
+  const int* tile_tab;        // null for the plain GEMM
+  int n_per_expert;           // rows of one expert inside the stacked weight
+  const float* alpha_tab;     // per-expert tensor scale (null: alpha)
+  int n_tiles;                // grid.y of the grouped form
 };
 
 template <int MODE>
@@ -74,7 +80,20 @@ gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap, const 
   __shared__ int s_fail;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * 128, t0 = blockIdx.y * BN;
+  const int n0 = blockIdx.x * 128;            // output feature of TMEM lane 0 (within the expert when grouped)
+  int t0 = blockIdx.y * BN, t_end = p.T;      // token rows of this tile
+  int a_row0 = n0;                            // first row of the weight tile in the (stacked) weight matrix
+  size_t sf_tile = blockIdx.x;                // index of the 128-row scale tile
+  float alpha = p.alpha;
+  if (p.tile_tab) {
+    const int4 tt = reinterpret_cast<const int4*>(p.tile_tab)[blockIdx.y];
+    if (tt.z <= 0) return;                    // idle tile: uniform exit before any barrier or TMEM use
+    t0 = tt.y;
+    t_end = tt.y + tt.z;
+    a_row0 = tt.x * p.n_per_expert + n0;
+    sf_tile = (size_t)tt.x * (p.n_per_expert / 128) + blockIdx.x;
+    if (p.alpha_tab) alpha = p.alpha_tab[tt.x];
+  }
   const int nkt = p.K / KT;
 
   if (threadIdx.x == 0) {
@@ -113,17 +132,17 @@ gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap, const 
         uint8_t* st = stage_ptr(s);
         mbar_expect_tx(&full[s], A_RAW + B_BYTES + SFA_BYTES + SFB_BYTES);
         if (MODE == 0) {
-          tma_load_2d(st, &amap, &full[s], kt * 64, n0);
+          tma_load_2d(st, &amap, &full[s], kt * 64, a_row0);
           tma_load_2d(st + A_RAW + A_DEQ, &bmap, &full[s], kt * 64, t0);
         } else if (MODE == 1) {
-          tma_load_2d(st, &amap, &full[s], kt * 64, n0);  // 64 bytes = 128 fp4 per row, unswizzled
+          tma_load_2d(st, &amap, &full[s], kt * 64, a_row0);  // 64 bytes = 128 fp4 per row, unswizzled
           tma_load_2d(st + A_RAW + A_DEQ, &bmap, &full[s], kt * 128, t0);
           tma_load_2d(st + A_RAW + A_DEQ + B_SUB, &bmap, &full[s], kt * 128 + 64, t0);
-          bulk_load(st + A_RAW + A_DEQ + B_BYTES, p.sfa + ((size_t)blockIdx.x * nkt + kt) * 1024, 1024, &full[s]);
+          bulk_load(st + A_RAW + A_DEQ + B_BYTES, p.sfa + (sf_tile * nkt + kt) * 1024, 1024, &full[s]);
         } else {
-          tma_load_2d(st, &amap, &full[s], kt * 128, n0);  // 128 bytes = 256 fp4 per row
+          tma_load_2d(st, &amap, &full[s], kt * 128, a_row0);  // 128 bytes = 256 fp4 per row
           tma_load_2d(st + A_RAW, &bmap, &full[s], kt * 128, t0);
-          bulk_load(st + A_RAW + B_BYTES, p.sfa + ((size_t)blockIdx.x * nkt + kt) * 2048, 2048, &full[s]);
+          bulk_load(st + A_RAW + B_BYTES, p.sfa + (sf_tile * nkt + kt) * 2048, 2048, &full[s]);
 #pragma unroll
           for (int b = 0; b < NB128; ++b)
             bulk_load(st + A_RAW + B_BYTES + SFA_BYTES + b * 2048,
@@ -240,8 +259,8 @@ gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap, const 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = t0 + c0 + j;
-            if (t < p.T) {
-              float v = __uint_as_float(r[j]) * p.alpha;
+            if (t < t_end) {
+              float v = __uint_as_float(r[j]) * alpha;
               if (p.residual) v += bf2f(p.residual[(long)t * p.ldr + n]);
               if (p.out_f32) p.out_f32[(long)t * p.ldo + n] = v;
               else p.out[(long)t * p.ldo + n] = f2bf(v);
@@ -276,7 +295,7 @@ static int launch_gemm(const GemmParams& p, const CUtensorMap& amap, const CUten
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((p.N + 127) / 128, (p.T + BN - 1) / BN);
+  dim3 grid((p.N + 127) / 128, p.tile_tab ? p.n_tiles : (p.T + BN - 1) / BN);
   gemm_kernel<MODE, BN, STAGES><<<grid, 192, smem, st>>>(p, amap, bmap);
   return (int)cudaGetLastError();
 }
@@ -356,6 +375,41 @@ int ve_gemm_w4a4(const void* Wp, const void* sfa, const void* Xp, const void* sf
   GemmParams p{N, T, K, alpha, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)residual, ldr, (float*)out_f32,
                (const uint8_t*)sfa, (const uint8_t*)sfb, (int*)status};
   return dispatch_gemm<2>(p, amap, bmap, bn, st);
+}
+
+// Grouped (mixture-of-experts) GEMMs. Weights of all experts are stacked along N ([E * N, K]); X holds the
+// routed rows sorted by expert ([R, K]); tile_tab [n_tiles][4] ints = {expert, first row, rows, 0} with every
+// tile covering at most `bn` rows of one expert (bn in {16, 32, 64, 128, 256}); out [R, N].
+int ve_gemm_grouped_bf16(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int R, int E, int N,
+                         int K, int bn, const void* tile_tab, int n_tiles, void* status, cudaStream_t st) {
+  if (R <= 0 || n_tiles <= 0) return 0;
+  CUtensorMap amap, bmap;
+  int rc = make_tmap_2d(&amap, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)E * N, K, (uint64_t)ldw * 2, 128, 64,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = make_tmap_2d(&bmap, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, (uint64_t)ldx * 2, bn, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  GemmParams p{N, R, K, 1.f, (__nv_bfloat16*)out, ldo, nullptr, 0, nullptr, nullptr, nullptr, (int*)status,
+               (const int*)tile_tab, N, nullptr, n_tiles};
+  return dispatch_gemm<0>(p, amap, bmap, bn, st);
+}
+
+int ve_gemm_grouped_w4a16(const void* Wp, const void* sfa, const void* alpha_tab, const void* X, long ldx, void* out,
+                          long ldo, int R, int E, int N, int K, int bn, const void* tile_tab, int n_tiles,
+                          void* status, cudaStream_t st) {
+  if (R <= 0 || n_tiles <= 0) return 0;
+  if (N % 128) return cudaErrorInvalidValue;
+  CUtensorMap amap, bmap;
+  int rc = make_tmap_2d(&amap, Wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)E * N, K / 2, (uint64_t)K / 2, 128, 64,
+                        CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_tmap_2d(&bmap, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, (uint64_t)ldx * 2, bn, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  GemmParams p{N, R, K, 1.f, (__nv_bfloat16*)out, ldo, nullptr, 0, nullptr, (const uint8_t*)sfa, nullptr,
+               (int*)status, (const int*)tile_tab, N, (const float*)alpha_tab, n_tiles};
+  return dispatch_gemm<1>(p, amap, bmap, bn, st);
 }
 
 }  // extern "C"

@@ -178,11 +178,9 @@ class DenseModel:
         the rows selected by ``b.logits`` (None for LOGITS_NONE)."""
         cfg = self.cfg
         comm = self.comm
-        act = 0 if cfg.act == "silu" else 1
         h = K.embed(b.ids, self.embed, scale=cfg.embed_scale)          # residual stream [n, H] bf16
         L0 = self.layers[0]
         x = K.rmsnorm(h, L0.attn_norm, cfg.rms_eps, cfg.norm_bias)
-        prefill = b.tiles is not None
         # multi-GPU chunks: the residual stream is row-sharded over ranks (sequence-parallel) and the
         # row-parallel GEMMs write straight into the communicator's symmetric input region
         sp = comm.size > 1 and b.n > 16
@@ -190,25 +188,12 @@ class DenseModel:
         if sp:
             h = comm.shard_rows(h)
         for li, L in enumerate(self.layers):
-            kpool, vpool = kv.layer(li)
-            qkv = L.qkv.forward(x)
-            if cfg.qk_norm:
-                stride = qkv.stride(0)
-                K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
-                K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
-                                 self.nq * self.hd)
-            K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
-                         cfg.rope_theta, cfg.rope_interleaved)
-            att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
-                              self.scale, window=cfg.sliding_window, key_end=b.key_end, tiles=b.tiles,
-                              nsplit=1 if prefill else b.nsplit, ws=self.attn_ws)
-            o = L.o_proj.forward(att, out=pbuf)
+            o = self.attn_block(li, L, x, b, kv, pbuf)
             x = comm.allreduce_add_norm(o, h, L.ffn_norm, cfg.rms_eps, cfg.norm_bias)
-            gu = L.gate_up.forward(x)
-            a = K.gated_act(gu, self.ffn, act, cfg.act_limit)
-            d = L.down.forward(a, out=pbuf)
+            d = self.ffn_block(li, L, x, b, pbuf)
             nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
             x = comm.allreduce_add_norm(d, h, nxt, cfg.rms_eps, cfg.norm_bias)
+        self.last_hidden = x
         if b.logits == LOGITS_NONE:
             return None
         if b.logits == LOGITS_LAST:
@@ -221,6 +206,30 @@ class DenseModel:
             else:
                 logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
         return logits
+
+    def attn_block(self, li, L, x, b: BatchRows, kv, pbuf):
+        """Attention sub-layer: returns this rank's partial of the o_proj output [n, H]."""
+        cfg = self.cfg
+        kpool, vpool = kv.layer(li)
+        qkv = L.qkv.forward(x)
+        if cfg.qk_norm:
+            stride = qkv.stride(0)
+            K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
+            K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
+                             self.nq * self.hd)
+        K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
+                     cfg.rope_theta, cfg.rope_interleaved)
+        att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
+                          self.scale, window=cfg.sliding_window, key_end=b.key_end, tiles=b.tiles,
+                          nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
+        return L.o_proj.forward(att, out=pbuf)
+
+    def ffn_block(self, li, L, x, b: BatchRows, pbuf):
+        """Feed-forward sub-layer: returns this rank's partial of the down projection [n, H]."""
+        cfg = self.cfg
+        gu = L.gate_up.forward(x)
+        a = K.gated_act(gu, self.ffn, 0 if cfg.act == "silu" else 1, cfg.act_limit)
+        return L.down.forward(a, out=pbuf)
 
     def ensure_workspace(self, max_rows: int, max_splits: int):
         if self.device.type == "cuda" and (self.attn_ws is None or self.attn_ws.max_splits < max_splits):
