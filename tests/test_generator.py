@@ -124,3 +124,21 @@ def test_utf8_boundary():
     t, rest = _utf8_split(b[:-2])
     assert t == "héllo " and rest == b[-4:-2]
     assert _utf8_split(b) == ("héllo 🙂", b"")
+
+
+def test_mtp_speculation_equals_plain_greedy():
+    from volta_engine_b200.models.mla import MLAConfig, MLAModel
+    cfg = MLAConfig.tiny_mla(vocab=256)
+    m = MLAModel(cfg, "cpu").init_random(seed=1)
+
+    def gen(**opt):
+        kv = PagedKVCache(cfg.n_layers + 1, 1, 576, 24, 2, 512, "cpu", v_head_dim=8)
+        eng = Engine(m, kv, use_graphs=False, prefill_chunk=32)
+        o = Options.resolve(dict({"max_slots": 2, "prefix_interval": 0}, **opt), env={})
+        return Generator(eng, ByteTok(), o, eos_ids=[])
+    p = prompt(45, 12)
+    plain = gen().generate(Request(p, max_tokens=14, cache_prefix=False))
+    g = gen(speculator="mtp", spec_ctrl=False, spec_depth=3)
+    spec = g.generate(Request(p, max_tokens=14, cache_prefix=False))
+    assert spec["tokens"] == plain["tokens"]
+    assert g.metrics.spec["rounds"] > 0 and g.metrics.spec["proposed"] == 3 * g.metrics.spec["rounds"]

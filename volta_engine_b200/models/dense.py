@@ -193,7 +193,7 @@ class DenseModel:
             d = self.ffn_block(li, L, x, b, pbuf)
             nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
             x = comm.allreduce_add_norm(d, h, nxt, cfg.rms_eps, cfg.norm_bias)
-        self.last_hidden = x
+        self.last_hidden, self.last_residual = x, h
         if b.logits == LOGITS_NONE:
             return None
         if b.logits == LOGITS_LAST:

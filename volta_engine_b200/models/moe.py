@@ -99,6 +99,8 @@ class MoELayer(DenseLayer):
 
 
 class MoEModel(DenseModel):
+    layer_cls = MoELayer
+
     def __init__(self, cfg: MoEConfig, device, comm=None):
         if cfg.ffn == 0:
             cfg.ffn = max(cfg.shared_ffn, 128) * (comm.size if comm else 1)
@@ -123,16 +125,8 @@ class MoEModel(DenseModel):
         nw = torch.ones(H, device=dev, dtype=torch.bfloat16) * (1.0 - cfg.norm_bias)
         self.heat = torch.zeros(cfg.n_layers, cfg.n_experts, dtype=torch.float32, device=dev)
         for li in range(cfg.n_layers):
-            L = MoELayer()
-            wq, wk, wv = rnd(cfg.n_q * hd, H), rnd(cfg.n_kv * hd, H), rnd(cfg.n_kv * hd, H)
-            kv0 = (r // self.kv_rep) * self.nkv if cfg.n_kv < tp else r * self.nkv
-            L.qkv = self._make_linear(torch.cat([wq[r * self.nq * hd:(r + 1) * self.nq * hd],
-                                                 wk[kv0 * hd:(kv0 + self.nkv) * hd],
-                                                 wv[kv0 * hd:(kv0 + self.nkv) * hd]], 0), search)
-            del wq, wk, wv
-            wo = rnd(H, cfg.n_q * hd)
-            L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search)
-            del wo
+            L = self.layer_cls()
+            self._init_attention(L, rnd, search)
             L.attn_norm, L.ffn_norm = nw.clone(), nw.clone()
             L.q_norm = L.k_norm = None
             L.gate_up = L.down = None
@@ -181,11 +175,26 @@ class MoEModel(DenseModel):
         self.lm_head = LinearBF16(head)
         return self
 
+    def _init_attention(self, L, rnd, search):
+        """GQA attention weights of one layer (overridden by the latent-attention model)."""
+        cfg = self.cfg
+        r, tp, H, hd = self.comm.rank, self.comm.size, cfg.hidden, cfg.head_dim
+        wq, wk, wv = rnd(cfg.n_q * hd, H), rnd(cfg.n_kv * hd, H), rnd(cfg.n_kv * hd, H)
+        kv0 = (r // self.kv_rep) * self.nkv if cfg.n_kv < tp else r * self.nkv
+        L.qkv = self._make_linear(torch.cat([wq[r * self.nq * hd:(r + 1) * self.nq * hd],
+                                             wk[kv0 * hd:(kv0 + self.nkv) * hd],
+                                             wv[kv0 * hd:(kv0 + self.nkv) * hd]], 0), search)
+        wo = rnd(H, cfg.n_q * hd)
+        L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search)
+
+    def _attn_bytes(self, L) -> int:
+        return L.qkv.nbytes() + L.o_proj.nbytes()
+
     def decode_bytes_per_token(self) -> int:
         n = self.lm_head.nbytes()
         cfg = self.cfg
         for L in self.layers:
-            n += L.qkv.nbytes() + L.o_proj.nbytes()
+            n += self._attn_bytes(L)
             if L.dense_ffn:
                 n += L.gate_up.nbytes() + L.down.nbytes()
             else:

@@ -145,6 +145,10 @@ class Generator:
         self.loop_detect = getattr(options, "loop_detect", True) if options else True
         self.prefix_interval = getattr(options, "prefix_interval", 16384) if options else 16384
         self.budget_ms = getattr(options, "prefill_budget_ms", 50.0) if options else 50.0
+        self.mtp = None
+        if self.speculator == "mtp":
+            from .mtp_runner import MtpRunner
+            self.mtp = MtpRunner(engine, self.spec_depth)
 
     # ------------------------------------------------------------------------------------------ API
     def submit(self, req: Request) -> int:
@@ -296,7 +300,10 @@ class Generator:
                     end = p
                     break
             last = end == len(prompt)
-            tok = self.engine.prefill_rows(s.idx, prompt[s.cursor:end], s.cursor, last)
+            if self.mtp is not None:
+                tok = self.mtp.prefill_rows(s.idx, prompt, s.cursor, end, last)
+            else:
+                tok = self.engine.prefill_rows(s.idx, prompt[s.cursor:end], s.cursor, last)
             done_rows += end - s.cursor
             s.cursor = s.pos = end
             if self.cache is not None and s.req.cache_prefix and (end in self._snapshot_points(s)):
@@ -343,6 +350,10 @@ class Generator:
                 n = self._suffix_round(s)
                 if n:
                     return n
+        if self.mtp is not None and len(act) == 1 and act[0].req.params.greedy and act[0].idx in self.mtp.hidden:
+            s = act[0]
+            if s.ctrl is None or s.ctrl.use_speculation():
+                return self._mtp_round(s)
         t0 = time.time()
         ids = [s.next_tok for s in act]
         pos = [s.pos for s in act]
@@ -358,6 +369,12 @@ class Generator:
                 c2 = penalize(c, s.req.params, s.counts.counts)
                 toks.append(sample_token(c2, s.req.params, s.rng))
         ms = (time.time() - t0) * 1e3
+        if self.mtp is not None:
+            if len(act) == 1:
+                self.mtp.after_plain_step(act[0].idx, ids[0], pos[0], toks[0])
+            else:
+                for s in act:            # batched plain steps do not maintain the head: drop its state
+                    self.mtp.release(s.idx)
         for s, t, c in zip(act, toks, cands):
             s.pos += 1
             s.next_tok = t
@@ -369,6 +386,27 @@ class Generator:
                        "top": [(i, l - c.lse) for i, l in list(zip(c.ids, c.logits))[: s.req.params.logprobs]]}]
             self._emit(s, [t], lp)
         return len(act)
+
+    def _mtp_round(self, s: SlotState) -> int:
+        t0 = time.time()
+        new = self.mtp.round(s.idx, s.next_tok, s.pos)
+        ms = (time.time() - t0) * 1e3
+        acc = len(new) - 1
+        s.pos += acc + 1
+        s.next_tok = new[-1]
+        m = self.metrics.spec
+        m["rounds"] += 1
+        m["proposed"] += self.mtp.depth
+        m["accepted"] += acc
+        while len(m["steps"]) < self.mtp.depth:
+            m["steps"].append({"attempts": 0, "hits": 0})
+        for i in range(self.mtp.depth):
+            m["steps"][i]["attempts"] += 1
+            m["steps"][i]["hits"] += 1 if i < acc else 0
+        if s.ctrl:
+            s.ctrl.record_round(len(new), self.mtp.depth, acc, ms)
+        self._emit(s, new)
+        return len(new)
 
     def _suffix_round(self, s: SlotState) -> int:
         depth = s.ctrl.depth(self.spec_depth) if s.ctrl else self.spec_depth
@@ -505,6 +543,8 @@ class Generator:
         if error:
             usage["error"] = error
         self.engine.kv.release(s.idx)
+        if self.mtp is not None:
+            self.mtp.release(s.idx)
         s.req, s.phase = None, "idle"
         if req.on_finish:
             req.on_finish(reason, usage)
