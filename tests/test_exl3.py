@@ -1,0 +1,105 @@
+"""EXL3 trellis format: CPU oracle properties, Viterbi encoder quality, and the CUDA kernels against the oracle."""
+import pytest
+import torch
+
+from volta_engine_b200.quant import exl3 as ex
+
+
+def test_had128_is_an_orthonormal_involution():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(5, 384, generator=g)
+    y = ex.had128(x)
+    assert torch.allclose(ex.had128(y), x, atol=1e-5)
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), rtol=1e-5)
+    # natural (Sylvester) order: row 1 of H alternates signs
+    e = torch.zeros(128); e[1] = 1
+    h = ex.had128(e) * 128 ** 0.5
+    assert torch.allclose(h, torch.tensor([1.0, -1.0]).repeat(64), atol=1e-5)
+
+
+def test_window_extraction_matches_a_bit_by_bit_reader():
+    g = torch.Generator().manual_seed(1)
+    for bits in (2, 3, 4, 5, 8):
+        codes = ex.random_codes(16, 16, bits, g)[0, 0]
+        words = [(int(codes[2 * i]) & 0xFFFF) | ((int(codes[2 * i + 1]) & 0xFFFF) << 16) for i in range(8 * bits)]
+        stream = [(w >> (31 - b)) & 1 for w in words for b in range(32)]
+        total = 256 * bits
+        win = ex.tile_windows(codes[None], bits)[0]
+        for p in (0, 1, 7, 100, 255):
+            s = (p * bits + bits - 16) % total
+            v = 0
+            for j in range(16):
+                v = (v << 1) | stream[(s + j) % total]
+            assert int(win[p]) == v
+
+
+def test_codebooks_are_near_unit_gaussians():
+    w = torch.arange(65536)
+    for cb, lo, hi in ((ex.CB_MUL1, 0.95, 1.05), (ex.CB_3INST, 1.1, 1.4), (ex.CB_MCG, 1.1, 1.4)):
+        v = ex.decode_windows(w, cb)
+        assert abs(float(v.mean())) < 0.05 and lo < float(v.std()) < hi
+
+
+def test_viterbi_encoder_reaches_trellis_quality_and_round_trips():
+    g = torch.Generator().manual_seed(2)
+    t = torch.randn(256, generator=g)
+    for bits, bound in ((2, 0.09), (4, 0.008)):
+        code = ex.viterbi_encode_tile(t, bits)
+        w = ex.decode_windows(ex.tile_windows(code[None], bits))[0]
+        assert float(((w - t) ** 2).mean()) < bound
+
+
+def test_quantize_small_matrix_reproduces_the_linear_map():
+    g = torch.Generator().manual_seed(3)
+    W = torch.randn(128, 128, generator=g) * 0.05
+    codes, suh, svh = ex.quantize(W, 2)
+    x = torch.randn(4, 128, generator=g)
+    y = ex.linear_reference(x, codes, 2, suh, svh)
+    ref = x @ W
+    cos = torch.nn.functional.cosine_similarity(y.flatten(), ref.flatten(), dim=0)
+    assert cos > 0.96
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 5, 6, 8])
+def test_gpu_reconstruct_and_gemv_match_oracle(bits):
+    from volta_engine_b200.ops import linear_exl3 as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(bits)
+    Kf, N = 640, 384          # 40 k-tiles: the warps' last iteration is a partial one
+    for cb in (0, 1, 2):
+        codes = ex.random_codes(Kf, N, bits, g)
+        Wref = ex.reconstruct(codes, bits, cb)                   # [K, N]
+        w = L.exl3_reconstruct(codes.to(dev), Kf, N, bits, cb).float().cpu()
+        assert torch.equal(w, Wref.t().to(torch.bfloat16).float())
+        for M in (1, 5, 16):
+            x = (torch.randn(M, Kf, generator=g)).to(torch.float16)
+            y = L.exl3_gemv(codes.to(dev), x.to(dev), M, Kf, N, bits, cb).cpu()
+            ref = x.float() @ Wref
+            assert torch.allclose(y, ref, atol=2e-2, rtol=2e-3), (bits, cb, M, float((y - ref).abs().max()))
+
+
+@pytest.mark.gpu
+def test_gpu_had128_and_linear_paths():
+    from volta_engine_b200.ops import linear_exl3 as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(7, 640, generator=g).to(torch.bfloat16)
+    s = (torch.rand(640, generator=g) + 0.5).to(torch.float16)
+    y = L.had128(x.to(dev), s.to(dev), out_dtype=torch.float16).float().cpu()
+    assert torch.allclose(y, ex.had128(x.float() * s.float()), atol=2e-2, rtol=1e-2)
+    y2 = L.had128(x.float().to(dev), s.to(dev), post=True, out_dtype=torch.bfloat16).float().cpu()
+    assert torch.allclose(y2, ex.had128(x.float()) * s.float(), atol=3e-2, rtol=2e-2)
+    lin = L.LinearEXL3.synth(640, 512, bits=4, std=0.05, gen=g)
+    ref1 = lin.forward(x[:3].float(), out_f32=True)
+    xl = torch.randn(48, 640, generator=g).to(torch.bfloat16)
+    ref2 = lin.forward(xl.float(), out_f32=True)
+    lin.to(dev)
+    o1 = lin.forward(x[:3].to(dev)).float().cpu()
+    o2 = lin.forward(xl.to(dev)).float().cpu()
+    cs = torch.nn.functional.cosine_similarity
+    assert cs(o1.flatten(), ref1.flatten(), dim=0) > 0.9995
+    assert cs(o2.flatten(), ref2.flatten(), dim=0) > 0.999
+    # decode rows are batch-invariant: row 0 alone equals row 0 inside a 3-row batch
+    a = lin.forward(x[:1].to(dev)); b = lin.forward(x[:3].to(dev))[:1]
+    assert torch.equal(a, b)

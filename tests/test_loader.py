@@ -1,0 +1,176 @@
+"""Checkpoint containers and the model factory: safetensors (sharded, sliced, quantised dialects), GGUF files,
+and a model directory round trip through ``load_model``."""
+import json
+
+import pytest
+import torch
+
+from volta_engine_b200.loader.gguf_file import GGUFFile, hf_name, unpermute_rope_rows, write_gguf
+from volta_engine_b200.loader.safetensors import SafeTensorsRepo, write_safetensors
+from volta_engine_b200.models.dense import DenseConfig
+from volta_engine_b200.models.factory import load_model, save_dense_checkpoint
+from volta_engine_b200.quant import gguf as gq, nvfp4 as qn
+from volta_engine_b200.runtime.engine import Engine
+from volta_engine_b200.runtime.kv_cache import PagedKVCache
+
+
+def test_safetensors_roundtrip_slices_and_padding(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(8, 12, generator=g).to(torch.bfloat16)
+    b = torch.randint(-30000, 30000, (4, 2, 32), generator=g, dtype=torch.int32).to(torch.int16)
+    emb = torch.randn(1000, 16, generator=g).to(torch.float16)
+    write_safetensors(tmp_path / "model-00001-of-00002.safetensors", {"a": a, "b.trellis": b}, unsigned16=("b.trellis",))
+    write_safetensors(tmp_path / "model-00002-of-00002.safetensors", {"emb": emb}, metadata={"format": "pt"})
+    repo = SafeTensorsRepo(tmp_path)
+    assert set(repo.names()) == {"a", "b.trellis", "emb"}
+    assert torch.equal(repo.load("a"), a) and torch.equal(repo.load("b.trellis"), b)
+    assert torch.equal(repo.load_slice("a", 1, 2, 3), a[:, 8:12])
+    assert torch.equal(repo.load_slice("a", 0, 1, 2), a[4:8])
+    with pytest.raises(ValueError):
+        repo.load_slice("a", 1, 0, 5)
+    sh = repo.load_rows_padded("emb", 3, 4, 256)
+    assert sh.shape == (256, 16) and torch.equal(sh[:232], emb[768:]) and float(sh[232:].abs().sum()) == 0.0
+
+
+def test_nvfp4_dialects_and_tp_slices_agree(tmp_path):
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(64, 128, generator=g) * 0.05
+    p, s, gs = qn.quantize_nvfp4(w)
+    write_safetensors(tmp_path / "m.safetensors", {
+        "x.weight_packed": p, "x.weight_scale": s.view(torch.float8_e4m3fn), "x.weight_global_scale": torch.tensor([1 / gs]),
+        "y.weight": p, "y.weight_scale": s.view(torch.float8_e4m3fn), "y.weight_scale_2": torch.tensor([gs]),
+        "z.weight": w.to(torch.bfloat16)})
+    repo = SafeTensorsRepo(tmp_path)
+    assert [repo.linear_kind(n) for n in "xyz"] == ["nvfp4_ct", "nvfp4_mo", "dense"]
+    ref = qn.dequantize_nvfp4(p, s, gs)
+    lx, ly = repo.load_linear("x"), repo.load_linear("y")
+    assert torch.allclose(qn.dequantize_nvfp4(lx.packed, lx.scales, lx.gscale), ref, rtol=1e-6)
+    assert torch.allclose(qn.dequantize_nvfp4(ly.packed, ly.scales, ly.gscale), ref, rtol=1e-6)
+    x = torch.randn(3, 128, generator=g)
+    full = lx.forward(x)
+    cols = torch.cat([repo.load_linear("x", "col", r, 2).forward(x) for r in range(2)], -1)
+    rows = sum(repo.load_linear("x", "row", r, 2).forward(x[:, r * 64:(r + 1) * 64]) for r in range(2))
+    assert torch.allclose(cols, full, atol=1e-5) and torch.allclose(rows, full, atol=1e-4)
+    zq = repo.load_linear("z", quantize="nvfp4")
+    assert zq.packed.shape == (64, 64)
+
+
+def test_exl3_linear_loads_and_slices_keep_hadamard_spans(tmp_path):
+    from volta_engine_b200.quant import exl3 as ex
+    g = torch.Generator().manual_seed(2)
+    codes, suh, svh = ex.synth_linear(256, 256, 3, 0.05, g)
+    write_safetensors(tmp_path / "m.safetensors", {"l.trellis": codes, "l.suh": suh, "l.svh": svh,
+                                                  "l.mcg": torch.zeros(1, dtype=torch.int32)}, unsigned16=("l.trellis",))
+    repo = SafeTensorsRepo(tmp_path)
+    lin = repo.load_linear("l")
+    assert (lin.bits, lin.cb) == (3, ex.CB_MCG)
+    x = torch.randn(2, 256, generator=g)
+    full = lin.forward(x, out_f32=True)
+    cols = torch.cat([repo.load_linear("l", "col", r, 2).forward(x, out_f32=True) for r in range(2)], -1)
+    rows = sum(repo.load_linear("l", "row", r, 2).forward(x[:, r * 128:(r + 1) * 128], out_f32=True) for r in range(2))
+    assert torch.allclose(cols, full, atol=1e-4) and torch.allclose(rows, full, atol=1e-3)
+    with pytest.raises(ValueError):
+        repo.load_linear("l", "col", 0, 4)          # 64-wide slices would cut a 128-wide rotation
+
+
+def test_gguf_file_roundtrip_and_name_map(tmp_path):
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(32, 64, generator=g)
+    q8 = gq.quantize(w, gq.GGML_Q8_0)
+    norm = torch.ones(64)
+    write_gguf(tmp_path / "m.gguf", {"general.architecture": "qwen3", "qwen3.block_count": 1, "tokenizer.ggml.tokens": ["a", "b"],
+                                     "general.alignment": 32, "x.scale": 0.5},
+               {"blk.0.attn_q.weight": (q8, gq.GGML_Q8_0, (32, 64)), "output_norm.weight": (norm, 0, (64,)),
+                "token_embd.weight": (w.to(torch.float16), 1, (32, 64))})
+    f = GGUFFile(tmp_path / "m.gguf")
+    assert f.arch == "qwen3" and f.metadata["qwen3.block_count"] == 1 and f.metadata["tokenizer.ggml.tokens"] == ["a", "b"]
+    assert abs(f.metadata["x.scale"] - 0.5) < 1e-7
+    assert f.tensors["blk.0.attn_q.weight"].shape == (32, 64)
+    assert torch.equal(f.load("blk.0.attn_q.weight"), q8.reshape(32, -1))
+    assert torch.allclose(f.dequantize("blk.0.attn_q.weight"), gq.dequantize(q8, gq.GGML_Q8_0, 64).reshape(32, 64))
+    assert torch.equal(f.load("token_embd.weight"), w.to(torch.float16))
+    assert hf_name("blk.7.ffn_down.weight") == "model.layers.7.mlp.down_proj.weight"
+    assert hf_name("output.weight") == "lm_head.weight" and hf_name("rope_freqs.weight") is None
+    # the converter permutation interleaves the two rotary halves of every head; the inverse restores them
+    hd, nh = 8, 2
+    orig = torch.arange(nh * hd * 3.0).reshape(nh * hd, 3)
+    perm = orig.reshape(nh, 2, hd // 2, 3).transpose(1, 2).reshape(nh * hd, 3)
+    assert torch.equal(unpermute_rope_rows(perm, nh), orig)
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4", "nvfp4_modelopt", "exl3"])
+def test_model_directory_roundtrip(tmp_path, fmt):
+    cfg = DenseConfig(n_layers=2, hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, vocab=512, qk_norm=True)
+    save_dense_checkpoint(tmp_path, cfg, seed=4, fmt=fmt, std=0.05)
+    model, hf = load_model(tmp_path, "cpu")
+    assert hf["model_type"] == "qwen3" and model.cfg.qk_norm and len(model.layers) == 2
+    kv = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, 8, 2, 256, "cpu")
+    out, st = Engine(model, kv, use_graphs=False, prefill_chunk=32).generate(list(range(40)), 4)
+    assert len(out) == 4 and all(0 <= t < cfg.vocab for t in out)
+    # loading the same directory twice is deterministic
+    model2, _ = load_model(tmp_path, "cpu")
+    kv2 = PagedKVCache(cfg.n_layers, model2.nkv, cfg.head_dim, 8, 2, 256, "cpu")
+    out2, _ = Engine(model2, kv2, use_graphs=False, prefill_chunk=64).generate(list(range(40)), 4)
+    assert out2 == out
+
+
+def test_unknown_model_type_is_refused(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "not_a_model"}))
+    write_safetensors(tmp_path / "m.safetensors", {"a": torch.zeros(1)})
+    with pytest.raises(NotImplementedError):
+        load_model(tmp_path, "cpu")
+
+
+def _moe_dir(tmp_path, mla: bool):
+    g = torch.Generator().manual_seed(7)
+    H, E, I, V, hd = 256, 4, 128, 512, 64
+    hf = {"model_type": "deepseek_v3" if mla else "qwen3_moe", "num_hidden_layers": 2, "hidden_size": H,
+          "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": hd, "intermediate_size": 256,
+          "moe_intermediate_size": I, "vocab_size": V, "num_experts_per_tok": 2, "rms_norm_eps": 1e-6,
+          "first_k_dense_replace": 1 if mla else 0}
+    hf.update({"n_routed_experts": E, "n_shared_experts": 1, "scoring_func": "sigmoid", "routed_scaling_factor": 2.5,
+               "q_lora_rank": 128, "kv_lora_rank": 512, "qk_nope_head_dim": 64, "qk_rope_head_dim": 64, "v_head_dim": 64,
+               "n_group": 2, "topk_group": 1} if mla else {"num_experts": E})
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    t = {}
+    rnd = lambda *s: (torch.randn(*s, generator=g) * 0.05).to(torch.bfloat16)
+    t["model.embed_tokens.weight"], t["lm_head.weight"], t["model.norm.weight"] = rnd(V, H), rnd(V, H), torch.ones(H).bfloat16()
+    for li in range(2):
+        p = f"model.layers.{li}."
+        t[p + "input_layernorm.weight"] = t[p + "post_attention_layernorm.weight"] = torch.ones(H).bfloat16()
+        if mla:
+            t[p + "self_attn.q_a_proj.weight"], t[p + "self_attn.q_a_layernorm.weight"] = rnd(128, H), torch.ones(128).bfloat16()
+            t[p + "self_attn.kv_a_proj_with_mqa.weight"], t[p + "self_attn.kv_a_layernorm.weight"] = rnd(576, H), torch.ones(512).bfloat16()
+            t[p + "self_attn.q_b_proj.weight"], t[p + "self_attn.kv_b_proj.weight"] = rnd(4 * 128, 128), rnd(4 * 128, 512)
+            t[p + "self_attn.o_proj.weight"] = rnd(H, 4 * 64)
+        else:
+            for n, rows in (("q", 4 * hd), ("k", 2 * hd), ("v", 2 * hd)):
+                t[p + f"self_attn.{n}_proj.weight"] = rnd(rows, H)
+            t[p + "self_attn.o_proj.weight"] = rnd(H, 4 * hd)
+            t[p + "self_attn.q_norm.weight"] = t[p + "self_attn.k_norm.weight"] = torch.ones(hd).bfloat16()
+        if mla and li == 0:
+            t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"], t[p + "mlp.down_proj.weight"] = rnd(256, H), rnd(256, H), rnd(H, 256)
+            continue
+        t[p + "mlp.gate.weight"] = rnd(E, H)
+        if mla:
+            t[p + "mlp.gate.e_score_correction_bias"] = torch.zeros(E)
+            for n, shp in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+                t[p + f"mlp.shared_experts.{n}_proj.weight"] = rnd(*shp)
+        for e in range(E):
+            for n, shp in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+                t[p + f"mlp.experts.{e}.{n}_proj.weight"] = rnd(*shp)
+    write_safetensors(tmp_path / "model.safetensors", t)
+    return hf
+
+
+@pytest.mark.parametrize("mla", [False, True])
+def test_moe_family_directories_load_and_generate(tmp_path, mla):
+    _moe_dir(tmp_path, mla)
+    model, hf = load_model(tmp_path, "cpu")
+    cfg = model.cfg
+    assert cfg.n_experts == 4 and cfg.top_k == 2 and (cfg.router == "sigmoid") == mla
+    assert model.layers[0].dense_ffn == mla and not model.layers[1].dense_ffn
+    kv = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, 8, 2, 256, "cpu",
+                      **({"v_head_dim": 0} if mla else {}))
+    out, _ = Engine(model, kv, use_graphs=False, prefill_chunk=16).generate(list(range(20)), 3)
+    assert len(out) == 3

@@ -1,0 +1,229 @@
+"""Model directory -> running model. ``config.json``'s ``model_type`` alone decides the model family; weights come
+from sharded safetensors (dense / NVFP4 / EXL3 / FP8-block) or from a GGUF file in the same directory.
+
+Reference: src/models/model.cpp:82 (``create_model_pipeline`` switch on model_type), src/server/config.cpp (model
+directory contract), src/loader/gguf_arch.h:21-66 (GGUF adapters).
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+from ..loader.gguf_file import GGUFFile, _NORM_PLUS_ONE, _ROPE_PERMUTED, name_index, unpermute_rope_rows, _PLAIN
+from ..loader.safetensors import SafeTensorsRepo, write_safetensors
+from ..ops.linear import LinearBF16, fuse_linears
+from ..ops.linear_gguf import LinearGGUF
+from ..quant import gguf as gq
+from .dense import DenseConfig, DenseLayer, DenseModel
+
+DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3", "gemma2", "gemma3_text", "glm4", "dense"}
+MOE_TYPES = {"qwen3_moe", "glm4_moe", "mixtral", "moe"}
+MLA_TYPES = {"deepseek_v2", "deepseek_v3", "kimi_k2", "mla"}
+
+
+def dense_config_from_hf(c: dict) -> DenseConfig:
+    mt = c.get("model_type", "dense")
+    hd = c.get("head_dim") or c["hidden_size"] // c["num_attention_heads"]
+    gemma = mt.startswith("gemma")
+    return DenseConfig(
+        n_layers=c["num_hidden_layers"], hidden=c["hidden_size"], n_q=c["num_attention_heads"],
+        n_kv=c.get("num_key_value_heads", c["num_attention_heads"]), head_dim=hd, ffn=c["intermediate_size"],
+        vocab=c["vocab_size"], rope_theta=float(c.get("rope_theta", 10000.0)), rms_eps=float(c.get("rms_norm_eps", 1e-6)),
+        norm_bias=1.0 if gemma else 0.0, rot_dim=int(hd * c.get("partial_rotary_factor", 1.0)) if c.get("partial_rotary_factor") else 0,
+        qk_norm=mt in ("qwen3", "qwen3_moe", "gemma3_text"), act="gelu_tanh" if gemma else "silu",
+        tie_embeddings=bool(c.get("tie_word_embeddings", False)),
+        embed_scale=float(c["hidden_size"]) ** 0.5 if gemma else 1.0,
+        sliding_window=int(c.get("sliding_window") or 0) if c.get("use_sliding_window", mt == "mistral") else 0,
+        attn_scale=float(c["query_pre_attn_scalar"]) ** -0.5 if c.get("query_pre_attn_scalar") else 0.0,
+        logit_softcap=float(c.get("final_logit_softcapping") or 0.0), quant=c.get("volta_quant", "bf16"),
+        model_type=mt)
+
+
+class TensorSource:
+    """Checkpoint-name view over a safetensors repository or a GGUF file."""
+
+    def __init__(self, model_dir, prefer: str | None = None):
+        d = Path(model_dir)
+        ggufs = [p for p in d.glob("*.gguf") if "mmproj" not in p.name.lower()]
+        sts = list(d.glob("*.safetensors"))
+        self.gguf = self.repo = None
+        if ggufs and (prefer == "gguf" or not sts):
+            self.gguf = GGUFFile(d)
+            self.names = name_index(self.gguf)
+            self.arch = self.gguf.arch
+        elif sts:
+            self.repo = SafeTensorsRepo(d)
+        else:
+            raise FileNotFoundError(f"{d}: neither *.safetensors nor *.gguf found")
+
+    def has(self, name: str) -> bool:
+        return name in self.names if self.gguf else self.repo.has(name)
+
+    def tensor(self, name: str, device=None, dtype=None) -> torch.Tensor:
+        if self.gguf:
+            t = self.gguf.dequantize(self.names[name])
+            if name.endswith("norm.weight") and self.arch in _NORM_PLUS_ONE:
+                t = t - 1.0
+        else:
+            t = self.repo.load(name)
+        if dtype is not None:
+            t = t.to(dtype)
+        return t.to(device) if device is not None else t
+
+    def linear(self, base: str, split=None, rank=0, world=1, device=None, gemm_mode="w4a16", quantize=None,
+               rope_heads: int = 0):
+        """``rope_heads``: number of heads of a q/k projection (needed to undo the GGUF rope row permutation)."""
+        if self.repo:
+            return self.repo.load_linear(base, split, rank, world, device, gemm_mode, quantize)
+        g = self.gguf
+        info = g.tensors[self.names[base + ".weight"]]
+        N, K = info.shape
+        permuted = rope_heads and self.arch in _ROPE_PERMUTED
+        if info.ggml_type in _PLAIN or permuted and split == "row":
+            w = g.dequantize(info.name)
+            if permuted:
+                w = unpermute_rope_rows(w, rope_heads)
+            n0, n1 = SafeTensorsRepo._range(N, "col" if split == "col" else None, rank, world, 1)
+            k0, k1 = SafeTensorsRepo._range(K, "row" if split == "row" else None, rank, world, 1)
+            w = w[n0:n1, k0:k1].to(torch.bfloat16).contiguous()
+            return LinearBF16(w.to(device) if device is not None else w)
+        raw = g.load(info.name)                                        # [N, row_bytes]
+        if permuted:
+            raw = unpermute_rope_rows(raw, rope_heads)
+        n0, n1 = SafeTensorsRepo._range(N, "col" if split == "col" else None, rank, world, 1)
+        blk = 256 if info.ggml_type in (gq.GGML_Q4_K, gq.GGML_Q6_K) else 32
+        k0, k1 = SafeTensorsRepo._range(K, "row" if split == "row" else None, rank, world, blk)
+        bpb = gq.row_bytes(info.ggml_type, blk)
+        raw = raw[n0:n1, k0 // blk * bpb:k1 // blk * bpb].contiguous()
+        if device is not None:
+            raw = raw.to(device)
+        return LinearGGUF(raw, info.ggml_type, n1 - n0, k1 - k0)
+
+
+def load_dense_weights(model: DenseModel, src: TensorSource, gemm_mode="w4a16", quantize=None) -> DenseModel:
+    """Fill a DenseModel from a checkpoint with the usual decoder names (``model.layers.N.self_attn.q_proj`` ...);
+    this rank keeps its tensor-parallel shard (q/k/v/gate/up column-split, o/down row-split, vocabulary rows)."""
+    cfg, dev = model.cfg, model.device
+    r, tp = model.comm.rank, model.comm.size
+    kw = dict(rank=r, world=tp, device=dev, gemm_mode=gemm_mode, quantize=quantize)
+    bf = torch.bfloat16
+    model.embed = src.tensor("model.embed_tokens.weight", dev, bf)
+    model.layers = []
+    for li in range(cfg.n_layers):
+        p = f"model.layers.{li}."
+        L = DenseLayer()
+        q = src.linear(p + "self_attn.q_proj", "col", rope_heads=cfg.n_q, **kw)
+        if cfg.n_kv >= tp:
+            k = src.linear(p + "self_attn.k_proj", "col", rope_heads=cfg.n_kv, **kw)
+            v = src.linear(p + "self_attn.v_proj", "col", **kw)
+        else:                                       # fewer kv heads than ranks: ranks share heads
+            kwr = dict(kw, rank=r // model.kv_rep, world=cfg.n_kv)
+            k = src.linear(p + "self_attn.k_proj", "col", rope_heads=cfg.n_kv, **kwr)
+            v = src.linear(p + "self_attn.v_proj", "col", **kwr)
+        L.qkv = fuse_linears([q, k, v])
+        L.o_proj = src.linear(p + "self_attn.o_proj", "row", **kw)
+        L.gate_up = fuse_linears([src.linear(p + "mlp.gate_proj", "col", **kw), src.linear(p + "mlp.up_proj", "col", **kw)])
+        L.down = src.linear(p + "mlp.down_proj", "row", **kw)
+        L.attn_norm = src.tensor(p + "input_layernorm.weight", dev, bf)
+        L.ffn_norm = src.tensor(p + "post_attention_layernorm.weight", dev, bf)
+        L.q_norm = L.k_norm = None
+        if cfg.qk_norm:
+            L.q_norm = src.tensor(p + "self_attn.q_norm.weight", dev, bf)
+            L.k_norm = src.tensor(p + "self_attn.k_norm.weight", dev, bf)
+        model.layers.append(L)
+    model.final_norm = src.tensor("model.norm.weight", dev, bf)
+    head_name = "model.embed_tokens.weight" if cfg.tie_embeddings or not src.has("lm_head.weight") else "lm_head.weight"
+    full = src.tensor(head_name, None, bf)
+    head = torch.zeros(model.vocab_local, cfg.hidden, dtype=bf)
+    lo = r * model.vocab_local
+    hi = min(cfg.vocab, lo + model.vocab_local)
+    if hi > lo:
+        head[: hi - lo] = full[lo:hi]
+    model.lm_head = LinearBF16(head.to(dev))
+    return model
+
+
+def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantize=None, prefer=None):
+    """-> (model, hf_config dict). Raises for model types this build has no pipeline for."""
+    d = Path(model_dir)
+    hf = json.loads((d / "config.json").read_text())
+    if "text_config" in hf and "num_hidden_layers" not in hf:
+        hf = dict(hf["text_config"], **{k: v for k, v in hf.items() if k != "text_config"})
+    mt = hf.get("model_type", "")
+    src = TensorSource(d, prefer)
+    if mt in DENSE_TYPES:
+        cfg = dense_config_from_hf(hf)
+        cfg.gemm_mode = gemm_mode
+        model = DenseModel(cfg, device, comm)
+        return load_dense_weights(model, src, gemm_mode, quantize), hf
+    if mt in MOE_TYPES or mt in MLA_TYPES:
+        from .moe_loader import load_moe_family
+        return load_moe_family(hf, src, device, comm, gemm_mode, quantize), hf
+    raise NotImplementedError(f"model_type {mt!r} has no pipeline in this build")
+
+
+def save_dense_checkpoint(model_dir, cfg: DenseConfig, seed: int = 0, std: float = 0.02, fmt: str = "bf16",
+                          shards: int = 2, model_type: str = "qwen3"):
+    """Write a random-weight model directory (config.json + sharded safetensors) in format ``fmt``:
+    bf16 | nvfp4 (compressed-tensors names) | nvfp4_modelopt | exl3. For tests and synthetic benchmarks."""
+    from ..quant import exl3 as ex, nvfp4 as qn
+    d = Path(model_dir)
+    d.mkdir(parents=True, exist_ok=True)
+    g = torch.Generator().manual_seed(seed)
+    hf = {"model_type": model_type, "num_hidden_layers": cfg.n_layers, "hidden_size": cfg.hidden,
+          "num_attention_heads": cfg.n_q, "num_key_value_heads": cfg.n_kv, "head_dim": cfg.head_dim,
+          "intermediate_size": cfg.ffn, "vocab_size": cfg.vocab, "rope_theta": cfg.rope_theta,
+          "rms_norm_eps": cfg.rms_eps, "tie_word_embeddings": cfg.tie_embeddings}
+    (d / "config.json").write_text(json.dumps(hf, indent=1))
+    tensors, u16 = {}, []
+
+    def put_linear(base, n, k):
+        w = torch.randn(n, k, generator=g) * std
+        if fmt == "bf16":
+            tensors[base + ".weight"] = w.to(torch.bfloat16)
+        elif fmt in ("nvfp4", "nvfp4_modelopt"):
+            p, s, gs = qn.quantize_nvfp4(w, search=False)
+            if fmt == "nvfp4":
+                tensors[base + ".weight_packed"] = p
+                tensors[base + ".weight_scale"] = s.view(torch.float8_e4m3fn)
+                tensors[base + ".weight_global_scale"] = torch.tensor([1.0 / gs])
+            else:
+                tensors[base + ".weight"] = p
+                tensors[base + ".weight_scale"] = s.view(torch.float8_e4m3fn)
+                tensors[base + ".weight_scale_2"] = torch.tensor([gs])
+        elif fmt == "exl3":
+            codes, suh, svh = ex.synth_linear(k, n, 4, std, g)
+            tensors[base + ".trellis"], tensors[base + ".suh"], tensors[base + ".svh"] = codes, suh, svh
+            tensors[base + ".mul1"] = torch.zeros(1, dtype=torch.int32)
+            u16.append(base + ".trellis")
+        else:
+            raise ValueError(fmt)
+
+    H, hd = cfg.hidden, cfg.head_dim
+    tensors["model.embed_tokens.weight"] = (torch.randn(cfg.vocab, H, generator=g) * std).to(torch.bfloat16)
+    for li in range(cfg.n_layers):
+        p = f"model.layers.{li}."
+        put_linear(p + "self_attn.q_proj", cfg.n_q * hd, H)
+        put_linear(p + "self_attn.k_proj", cfg.n_kv * hd, H)
+        put_linear(p + "self_attn.v_proj", cfg.n_kv * hd, H)
+        put_linear(p + "self_attn.o_proj", H, cfg.n_q * hd)
+        put_linear(p + "mlp.gate_proj", cfg.ffn, H)
+        put_linear(p + "mlp.up_proj", cfg.ffn, H)
+        put_linear(p + "mlp.down_proj", H, cfg.ffn)
+        tensors[p + "input_layernorm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+        tensors[p + "post_attention_layernorm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+        if model_type == "qwen3":
+            tensors[p + "self_attn.q_norm.weight"] = torch.ones(hd, dtype=torch.bfloat16)
+            tensors[p + "self_attn.k_norm.weight"] = torch.ones(hd, dtype=torch.bfloat16)
+    tensors["model.norm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+    if not cfg.tie_embeddings:
+        tensors["lm_head.weight"] = (torch.randn(cfg.vocab, H, generator=g) * std).to(torch.bfloat16)
+    names = sorted(tensors)
+    per = (len(names) + shards - 1) // shards
+    for si in range(shards):
+        part = {n: tensors[n] for n in names[si * per:(si + 1) * per]}
+        if part:
+            write_safetensors(d / f"model-{si + 1:05d}-of-{shards:05d}.safetensors", part, unsigned16=tuple(u16))
+    return hf

@@ -108,3 +108,48 @@ class LinearNVFP4:
 
     def nbytes(self):
         return self.packed.numel() + self.scales.numel()
+
+
+class LinearGroup:
+    """Several linears over the same input whose outputs are concatenated along the feature axis (q/k/v or gate/up
+    stored as separate quantised tensors with scales that cannot be merged)."""
+
+    def __init__(self, parts):
+        self.parts = list(parts)
+        self.in_features = self.parts[0].in_features
+        self.out_features = sum(p.out_features for p in self.parts)
+
+    def forward(self, x, residual=None, out=None, **kw):
+        ys = [p.forward(x, **kw) for p in self.parts]
+        y = torch.cat(ys, dim=-1)
+        if residual is not None:
+            y = y + residual.to(y.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def nbytes(self):
+        return sum(p.nbytes() for p in self.parts)
+
+
+def fuse_linears(parts):
+    """One linear computing the concatenated outputs of ``parts``: a true merge where the formats allow it
+    (dense rows; NVFP4 tensors sharing one tensor scale; EXL3 tensors sharing the input scales and codebook),
+    otherwise a LinearGroup."""
+    parts = list(parts)
+    if len(parts) == 1:
+        return parts[0]
+    if all(isinstance(p, LinearBF16) for p in parts):
+        return LinearBF16(torch.cat([p.weight for p in parts], 0))
+    if all(isinstance(p, LinearNVFP4) for p in parts) and len({p.gscale for p in parts}) == 1 \
+            and len({p.gemm_mode for p in parts}) == 1:
+        m = LinearNVFP4(torch.cat([p.packed for p in parts], 0), torch.cat([p.scales for p in parts], 0),
+                        parts[0].gscale, parts[0].gemm_mode)
+        return m.prepare() if m.packed.is_cuda else m
+    from .linear_exl3 import LinearEXL3
+    if all(isinstance(p, LinearEXL3) for p in parts) and len({(p.bits, p.cb, p.layout) for p in parts}) == 1 \
+            and all(p.bias is None for p in parts) and all(torch.equal(p.suh, parts[0].suh) for p in parts[1:]):
+        return LinearEXL3(torch.cat([p.codes for p in parts], 1), parts[0].suh, torch.cat([p.svh for p in parts]),
+                          bits=parts[0].bits, cb=parts[0].cb, layout=parts[0].layout)
+    return LinearGroup(parts)
