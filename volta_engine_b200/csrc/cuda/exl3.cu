@@ -82,12 +82,13 @@ constexpr int kExl3Warps = 8;
 
 // x: fp16 [groups][M][K] rotated activations (read through L1: at most 16 x K halves, re-used by every warp);
 // y: fp32 [groups][M][N]; group = blockIdx.y, its weights start at codes + expert[group] * expert_stride
-// (expert == nullptr: one shared matrix).
-template <int BITS, int CB, int MH>   // MH: 8 or 16 activation rows held by the A fragment
+// (expert == nullptr: one shared matrix). A warp walks its share of K and, per k-tile, NTW adjacent column tiles
+// (NTW * 32 * BITS contiguous bytes per request); the CTA owns 16 * NTW output columns.
+template <int BITS, int CB, int MH, int NTW>   // MH: 8 or 16 activation rows held by the A fragment
 __global__ void __launch_bounds__(kExl3Warps * 32)
 exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ x, float* __restrict__ y,
                  int M, int K, int N, const int* __restrict__ expert, long expert_stride) {
-  __shared__ float red[kExl3Warps * 256];                           // [warps][16 rows][16 cols]
+  __shared__ float red[kExl3Warps * 256 * NTW];                     // [warps][16 rows][16 * NTW cols]
   const int grp = blockIdx.y;
   if (expert) { const int e = expert[grp]; if (e < 0) return; codes += (size_t)e * expert_stride; }
   x += (size_t)grp * M * K; y += (size_t)grp * M * N;
@@ -96,52 +97,66 @@ exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ 
   const __half* xlo = x + (size_t)(row_lo ? g : 0) * K + 2 * t;
   const __half* xhi = x + (size_t)(row_hi ? g + 8 : 0) * K + 2 * t;
 
-  const int KT = K >> 4, NT = N >> 4, nt = blockIdx.x;
+  const int KT = K >> 4, NT = N >> 4, nt0 = blockIdx.x * NTW;
   const int per = (KT + kExl3Warps - 1) / kExl3Warps;
   const int kt0 = warp * per, kt1 = min(KT, kt0 + per);
   const Exl3Lane<BITS> L(lane);
   constexpr int NW = Exl3Lane<BITS>::NW;
-  const uint32_t* base = reinterpret_cast<const uint32_t*>(codes) + (size_t)nt * (8 * BITS);
+  const uint32_t* base = reinterpret_cast<const uint32_t*>(codes) + (size_t)nt0 * (8 * BITS);
   const size_t tstride = (size_t)NT * (8 * BITS);
-  float c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
-  constexpr int U = NW == 2 ? 8 : 4;                                // tiles in flight per warp
-  for (int kt = kt0; kt < kt1; kt += U) {
-    uint32_t w[U][NW];
+  float acc[NTW][2][4];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+  for (int j = 0; j < NTW; ++j)
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][h][i] = 0.f;
+  constexpr int UK = (NW == 2 ? 8 : 4) / NTW > 0 ? (NW == 2 ? 8 : 4) / NTW : 1;   // k-tiles in flight per warp
+  for (int kt = kt0; kt < kt1; kt += UK) {
+    uint32_t w[UK][NTW][NW];
+#pragma unroll
+    for (int u = 0; u < UK; ++u) {
       const int k = min(kt + u, kt1 - 1);                           // tail: re-read the last tile, skip its math
-      L.load(base + (size_t)k * tstride, w[u]);
+#pragma unroll
+      for (int j = 0; j < NTW; ++j) L.load(base + (size_t)k * tstride + j * (8 * BITS), w[u][j]);
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < UK; ++u) {
       if (kt + u < kt1) {
-        uint32_t f[4], a[4];
-        L.template decode<CB>(w[u], f);
+        uint32_t a[4];
         const int ko = (kt + u) * 16;
         a[0] = row_lo ? __ldg(reinterpret_cast<const uint32_t*>(xlo + ko)) : 0u;
         a[2] = row_lo ? __ldg(reinterpret_cast<const uint32_t*>(xlo + ko + 8)) : 0u;
         a[1] = row_hi ? __ldg(reinterpret_cast<const uint32_t*>(xhi + ko)) : 0u;
         a[3] = row_hi ? __ldg(reinterpret_cast<const uint32_t*>(xhi + ko + 8)) : 0u;
-        mma_f16(c0, a, f[0], f[1]);
-        mma_f16(c1, a, f[2], f[3]);
+#pragma unroll
+        for (int j = 0; j < NTW; ++j) {
+          uint32_t f[4];
+          L.template decode<CB>(w[u][j], f);
+          mma_f16(acc[j][0], a, f[0], f[1]);
+          mma_f16(acc[j][1], a, f[2], f[3]);
+        }
       }
     }
   }
   // C fragment: c[0],c[1] -> row g, cols 2t,2t+1; c[2],c[3] -> row g+8.
-  float* r = red + warp * 256;
-  r[g * 16 + 2 * t] = c0[0]; r[g * 16 + 2 * t + 1] = c0[1];
-  r[g * 16 + 8 + 2 * t] = c1[0]; r[g * 16 + 8 + 2 * t + 1] = c1[1];
-  r[(g + 8) * 16 + 2 * t] = c0[2]; r[(g + 8) * 16 + 2 * t + 1] = c0[3];
-  r[(g + 8) * 16 + 8 + 2 * t] = c1[2]; r[(g + 8) * 16 + 8 + 2 * t + 1] = c1[3];
-  __syncthreads();
-  {
-    const int m = tid >> 4, n = tid & 15;
-    if (m < M) {
-      float s = 0.f;
+  constexpr int W = 16 * NTW;
+  float* r = red + warp * 16 * W;
 #pragma unroll
-      for (int wv = 0; wv < kExl3Warps; ++wv) s += red[wv * 256 + tid];
-      y[(size_t)m * N + nt * 16 + n] = s;
+  for (int j = 0; j < NTW; ++j)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = j * 16 + h * 8 + 2 * t;
+      r[g * W + c] = acc[j][h][0]; r[g * W + c + 1] = acc[j][h][1];
+      r[(g + 8) * W + c] = acc[j][h][2]; r[(g + 8) * W + c + 1] = acc[j][h][3];
     }
+  __syncthreads();
+  for (int i = tid; i < M * W; i += blockDim.x) {
+    const int m = i / W, n = i % W;
+    float s = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < kExl3Warps; ++wv) s += red[wv * 16 * W + m * W + n];
+    y[(size_t)m * N + nt0 * 16 + n] = s;
   }
 }
 
@@ -272,16 +287,26 @@ __global__ void __launch_bounds__(256) exl3_reconstruct_kernel(const uint16_t* _
 
 using namespace ve;
 
+template <int BITS, int CB, int NTW>
+static void exl3_gemv_launch_n(const void* codes, const void* x, void* y, int M, int K, int N, const int* expert,
+                               long stride, int groups, cudaStream_t st) {
+  const dim3 grid(N / (16 * NTW), groups);
+  if (M <= 8)
+    exl3_gemv_kernel<BITS, CB, 8, NTW><<<grid, kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x,
+                                                                         (float*)y, M, K, N, expert, stride);
+  else
+    exl3_gemv_kernel<BITS, CB, 16, NTW><<<grid, kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x,
+                                                                          (float*)y, M, K, N, expert, stride);
+}
+
+// Column tiles per warp: as wide as the request can be (up to 512 B) while the grid still fills the GPU.
 template <int BITS, int CB>
 static int exl3_gemv_launch(const void* codes, const void* x, void* y, int M, int K, int N, const int* expert,
                             long stride, int groups, cudaStream_t st) {
-  const dim3 grid(N / 16, groups);
-  if (M <= 8)
-    exl3_gemv_kernel<BITS, CB, 8><<<grid, kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x, (float*)y,
-                                                                    M, K, N, expert, stride);
-  else
-    exl3_gemv_kernel<BITS, CB, 16><<<grid, kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x, (float*)y,
-                                                                     M, K, N, expert, stride);
+  const long ctas1 = (long)(N / 16) * groups;
+  if (N % 64 == 0 && ctas1 / 4 >= 2 * 148) exl3_gemv_launch_n<BITS, CB, 4>(codes, x, y, M, K, N, expert, stride, groups, st);
+  else if (N % 32 == 0 && ctas1 / 2 >= 2 * 148) exl3_gemv_launch_n<BITS, CB, 2>(codes, x, y, M, K, N, expert, stride, groups, st);
+  else exl3_gemv_launch_n<BITS, CB, 1>(codes, x, y, M, K, N, expert, stride, groups, st);
   VE_CHECK_LAUNCH();
 }
 

@@ -1,4 +1,4 @@
-"""Linear layer over EXL3 trellis-coded weights: ``y = had128((had128(x * suh) @ W) * svh)``.
+"""Linear layer over EXL3 trellis-coded weights: ``y = had128(had128(x * suh) @ W) * svh``.
 
 GPU: rows <= 16 run rotate -> fused decode mat-vec (mma.sync with the tile's native fragment order) -> rotate
 (csrc/cuda/exl3.cu); larger row counts reconstruct W to bf16 once per call and run the tcgen05 GEMM between the

@@ -7,7 +7,7 @@ holds 256 codes of ``bits`` bits as one cyclic bit stream (uint16 pairs form lit
 read MSB first). Position p owns the 16-bit window starting at stream bit ``(p*bits + bits - 16) mod 256*bits``;
 the window goes through a multiply-and-mask codebook to one fp16 value. Position p = 8*L + i sits at
 ``row = (L&3)*2 + (i&1) + 8*((i>>1)&1)``, ``col = 2*(L//8 + 4*(i>>2)) + ((L>>2)&1)`` of the tile.
-``Linear(x) = had128((had128(x * suh) @ W) * svh)`` with the normalised 128-point Walsh-Hadamard transform.
+``Linear(x) = had128(had128(x * suh) @ W) * svh`` with the normalised 128-point Walsh-Hadamard transform.
 Codebooks: 0 = 3INST, 1 = MCG, 2 = MUL1.
 """
 from __future__ import annotations
@@ -100,7 +100,7 @@ def linear_reference(x: torch.Tensor, codes: torch.Tensor, bits: int, suh: torch
     """fp32 statement of the EXL3 linear: x [M, K] -> [M, N]."""
     W = reconstruct(codes, bits, cb, layout)
     t = had128(x.float() * suh.float())
-    return had128((t @ W) * svh.float())
+    return had128(t @ W) * svh.float()
 
 
 def effective_weight(codes, bits, suh, svh, cb=CB_MUL1, layout="stock") -> torch.Tensor:
@@ -185,8 +185,8 @@ def quantize(W: torch.Tensor, bits: int, cb: int = CB_MUL1, seed: int = 0):
     g = torch.Generator().manual_seed(seed)
     su = (torch.randint(0, 2, (K,), generator=g).float() * 2 - 1).to(W.device)
     sv = (torch.randint(0, 2, (N,), generator=g).float() * 2 - 1).to(W.device)
-    # x W = x Su H Wq Sv H  =>  Wq = H (Su W) H Sv   (H symmetric orthonormal, sign matrices self-inverse)
-    Wr = had128((had128((W.float() * su[:, None]).t().contiguous())).t().contiguous()) * sv[None, :]
+    # x W = x Su H Wq H Sv  =>  Wq = H (Su W Sv) H   (H symmetric orthonormal, sign matrices self-inverse)
+    Wr = had128((had128((W.float() * su[:, None] * sv[None, :]).t().contiguous())).t().contiguous())
     scale = Wr.std().clamp(min=1e-12)          # codebook values have ~unit variance
     Wn = Wr / scale
     row, col = _tile_positions()

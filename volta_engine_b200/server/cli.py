@@ -1,0 +1,268 @@
+"""``volta_server``: launch configuration and process start-up.
+
+Precedence: command-line flags > JSON launch file > ``ENGINE_*`` environment > defaults; unknown keys are fatal;
+the model type is never configured (``config.json`` of the model directory decides).
+One process per GPU: with ``tp_size`` > 1 and no rank environment the launcher re-executes itself under
+``torch.distributed.run`` on 127.0.0.1; rank 0 then hosts the HTTP front end and the scheduler, the other ranks
+mirror its engine calls (runtime/tp_control.py).
+Reference: inc/engine/server/config.h:21-52 (launch struct), src/server/config.cpp, docs/CONFIG.md:5-26,
+src/server/main.cpp (start-up order: config -> cluster -> tokenizer / template -> generator -> HTTP).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import signal
+import sys
+import threading
+from dataclasses import asdict, dataclass, field
+
+from ..runtime.options import Options, config_docs
+
+_TOP_KEYS = {
+    "model_dir": (str, ""), "draft_model_dir": (str, ""), "use_speculation": (bool, False), "tui": (bool, False),
+    "tp_size": (int, 1), "host": (str, "127.0.0.1"), "port": (int, 8080), "api_key": (str, ""),
+    "max_batch_size": (int, 8), "default_max_tokens": (int, 1024), "default_temperature": (float, 0.7),
+    "default_top_p": (float, 0.95), "default_top_k": (int, 0), "default_enable_thinking": (bool, True),
+    "request_timeout_s": (int, 300), "model_name": (str, ""), "video": (dict, None), "options": (dict, None),
+}
+
+
+@dataclass
+class LaunchConfig:
+    model_dir: str = ""
+    draft_model_dir: str = ""
+    use_speculation: bool = False
+    tui: bool = False
+    tp_size: int = 1
+    host: str = "127.0.0.1"
+    port: int = 8080
+    api_key: str = ""
+    max_batch_size: int = 8
+    default_max_tokens: int = 1024
+    default_temperature: float = 0.7
+    default_top_p: float = 0.95
+    default_top_k: int = 0
+    default_enable_thinking: bool = True
+    request_timeout_s: int = 300
+    model_name: str = ""
+    video: dict = field(default_factory=dict)
+    options: Options = None
+
+    def to_dict(self):
+        d = asdict(self)
+        d["options"] = dict(self.options.values)
+        return d
+
+
+def _coerce(key, val):
+    t = _TOP_KEYS[key][0]
+    if t is bool and not isinstance(val, bool):
+        return str(val).strip().lower() in ("1", "true", "yes", "on")
+    if t is dict:
+        if not isinstance(val, dict):
+            raise ValueError(f"'{key}' must be an object")
+        return val
+    return t(val)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="volta_server", description="OpenAI / Anthropic compatible LLM server for B200")
+    p.add_argument("config", nargs="?", help="JSON launch file")
+    p.add_argument("--config", dest="config_flag", help="JSON launch file")
+    p.add_argument("--model-dir")
+    p.add_argument("--draft-model-dir")
+    p.add_argument("--use-speculation", action="store_true", default=None)
+    p.add_argument("--tui", action="store_true", default=None)
+    p.add_argument("--tp", "--tp-size", dest="tp_size", type=int)
+    p.add_argument("--host")
+    p.add_argument("--port", type=int)
+    p.add_argument("--api-key")
+    p.add_argument("--max-batch-size", type=int)
+    p.add_argument("--default-max-tokens", type=int)
+    p.add_argument("--model-name")
+    p.add_argument("--request-timeout-s", type=int)
+    p.add_argument("--set", action="append", default=[], metavar="KEY=VALUE", help="runtime option (repeatable)")
+    p.add_argument("--print-config", action="store_true", help="print the resolved configuration and exit")
+    p.add_argument("--print-config-docs", action="store_true", help="print the option reference (markdown) and exit")
+    return p
+
+
+def resolve_config(argv: list[str], env=None) -> tuple[LaunchConfig, argparse.Namespace]:
+    env = os.environ if env is None else env
+    args = build_parser().parse_args(argv)
+    vals = {k: d for k, (t, d) in _TOP_KEYS.items()}
+    for k in vals:                                     # environment (lowest)
+        raw = env.get("ENGINE_" + k.upper())
+        if raw is not None and _TOP_KEYS[k][0] is not dict:
+            vals[k] = _coerce(k, raw)
+    path = args.config_flag or args.config
+    json_options = None
+    if path:
+        with open(path) as f:
+            doc = json.load(f)
+        for k, v in doc.items():
+            if k not in _TOP_KEYS:
+                raise KeyError(f"unknown key '{k}' in {path}")
+            vals[k] = _coerce(k, v)
+        json_options = vals.get("options")
+    for k in ("model_dir", "draft_model_dir", "use_speculation", "tui", "tp_size", "host", "port", "api_key",
+              "max_batch_size", "default_max_tokens", "model_name", "request_timeout_s"):
+        v = getattr(args, k, None)
+        if v is not None:
+            vals[k] = v
+    sets = list(args.set)
+    if not any(s.startswith("tp=") for s in sets) and (args.tp_size is not None or "tp" not in (json_options or {})):
+        sets.append(f"tp={vals['tp_size']}")
+    opts = Options.resolve(json_options, sets, env)
+    vals["tp_size"] = opts.tp
+    vals["options"] = opts
+    vals["video"] = vals["video"] or {}
+    if vals["use_speculation"] and opts.speculator == "none":
+        opts.values["speculator"] = "draft" if vals["draft_model_dir"] else "mtp"
+    return LaunchConfig(**vals), args
+
+
+def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
+    """Model directory -> (model, hf_config, Engine, kv pool tokens) on this rank. ``agree(n)`` returns the value all
+    ranks settle on for the KV pool size (minimum over ranks); ``None`` for a single rank."""
+    import torch
+    from ..models.factory import load_model
+    from ..runtime.engine import Engine
+    from ..runtime.kv_cache import PagedKVCache
+    o = cfg.options
+    device = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
+    model, hf = load_model(cfg.model_dir, device, comm, gemm_mode=o.gemm_mode)
+    mcfg = model.cfg
+    bpt = mcfg.n_layers * model.nkv * 2 * mcfg.head_dim * 2
+    if o.kv_pool:
+        pool_tokens = o.kv_pool
+    elif torch.device(device).type == "cuda":
+        free, _ = torch.cuda.mem_get_info(torch.device(device))
+        pool_tokens = max(4096, int((free - (o.vram_reserve_mib << 20)) * 0.9) // bpt)
+    else:
+        pool_tokens = min(o.max_seq * 2, 16384)
+    pool_tokens = min(pool_tokens, o.max_seq * o.max_slots)
+    if agree is not None:
+        pool_tokens = agree(pool_tokens)
+    kv = PagedKVCache(mcfg.n_layers, model.nkv, mcfg.head_dim, max(2, pool_tokens // 64), o.max_slots, o.max_seq, device)
+    engine = Engine(model, kv, use_graphs=not o.no_graphs and torch.device(device).type == "cuda",
+                    prefill_chunk=o.prefill_chunk)
+    return model, hf, engine, pool_tokens
+
+
+def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=None):
+    """Model directory -> (VoltaServer, Generator, Engine) on this rank (rank 0 of a world, or the only rank)."""
+    from ..loader.chat_template import ChatTemplate
+    from ..loader.tokenizer import Tokenizer
+    from ..runtime.generator import Generator
+    from ..runtime.prefix_cache import PrefixCache
+    from .app import VoltaServer
+
+    o = cfg.options
+    model, hf, engine, pool_tokens = build_engine(cfg, device, comm, agree)
+    if chan is not None:
+        from ..runtime.tp_control import LeaderEngine
+        engine = LeaderEngine(engine, chan)
+    tok = Tokenizer.load(cfg.model_dir)
+    try:
+        template = ChatTemplate.load(cfg.model_dir)
+    except (FileNotFoundError, KeyError):
+        template = None
+    cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None) if o.prefix_cache_mib > 0 else None
+    gen = Generator(engine, tok, o, prefix_cache=cache)
+    defaults = {"temperature": cfg.default_temperature, "top_p": cfg.default_top_p, "top_k": cfg.default_top_k,
+                "enable_thinking": cfg.default_enable_thinking}
+    gc_path = os.path.join(cfg.model_dir, "generation_config.json")
+    if os.path.exists(gc_path):
+        with open(gc_path) as f:
+            gc = json.load(f)
+        for k in ("temperature", "top_p", "top_k"):
+            if k in gc:
+                defaults[k] = gc[k]
+    name = cfg.model_name or os.path.basename(os.path.normpath(cfg.model_dir))
+    srv = VoltaServer(gen, tok, template, model_name=name, model_type=hf.get("model_type", "dense"), host=cfg.host,
+                      port=cfg.port, api_key=cfg.api_key, defaults=defaults, max_context=o.max_seq,
+                      default_max_tokens=cfg.default_max_tokens, request_timeout_s=cfg.request_timeout_s,
+                      info={"tp": o.tp, "kv_tokens": pool_tokens, "options": dict(o.values)})
+    return srv, gen, engine
+
+
+def _run_rank(cfg: LaunchConfig) -> int:
+    import datetime
+    import torch
+    import torch.distributed as dist
+    from ..parallel import make_comm
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    cuda = torch.cuda.is_available()
+    device = f"cuda:{local}" if cuda else "cpu"
+    if cuda:
+        torch.cuda.set_device(local)
+    dist.init_process_group("nccl" if cuda else "gloo", timeout=datetime.timedelta(seconds=600))
+    ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=3600))
+    from ..runtime.tp_control import ControlChannel, follower_loop
+    if cuda:
+        comm = make_comm(cfg.options.comm, device)
+    else:
+        from ..parallel.host import HostComm
+        comm = HostComm()
+    chan = ControlChannel(ctl)
+
+    def agree(n: int) -> int:
+        t = torch.tensor([n], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=ctl)
+        return int(t.item())
+    if rank == 0:
+        srv, gen, engine = build_server(cfg, device, comm, chan, agree)
+        return _serve_forever(cfg, srv, engine)
+    _, _, engine, _ = build_engine(cfg, device, comm, agree)
+    follower_loop(engine, chan)
+    return 0
+
+
+def _serve_forever(cfg: LaunchConfig, srv, engine) -> int:
+    srv.start()
+    print(f"volta_server: listening on http://{cfg.host}:{srv.port}  model={srv.model_name}  tp={cfg.tp_size}", flush=True)
+    stop = threading.Event()
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        try:
+            signal.signal(sig, lambda *_: stop.set())
+        except ValueError:
+            pass
+    if cfg.tui:
+        from .tui import run_tui
+        run_tui(f"http://{cfg.host}:{srv.port}", stop)
+    stop.wait()
+    srv.stop()
+    if hasattr(engine, "shutdown"):
+        engine.shutdown()
+    return 0
+
+
+def main(argv: list[str] | None = None) -> int:
+    argv = sys.argv[1:] if argv is None else argv
+    cfg, args = resolve_config(argv)
+    if args.print_config_docs:
+        print(config_docs())
+        return 0
+    if args.print_config:
+        print(json.dumps(cfg.to_dict(), indent=1))
+        return 0
+    if not cfg.model_dir:
+        print("volta_server: model_dir is required (flag --model-dir or key model_dir)", file=sys.stderr)
+        return 2
+    if cfg.tp_size > 1:
+        if "RANK" not in os.environ:
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={cfg.tp_size}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000),
+                   "-m", "volta_engine_b200.server.cli"] + argv
+            os.execv(sys.executable, cmd)
+        return _run_rank(cfg)
+    srv, gen, engine = build_server(cfg)
+    return _serve_forever(cfg, srv, engine)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
