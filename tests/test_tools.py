@@ -1,0 +1,54 @@
+"""Host-side tools: terminal dashboard frames and the HTTP load generator's self-test against its mock server."""
+import io
+import threading
+
+from volta_engine_b200.server import tui
+from volta_engine_b200.tools import bench_serve
+
+STATS = {
+    "server": {"model": "m27", "model_type": "dense", "uptime_s": 3723, "slots": 2, "max_context": 32768, "tp": 4,
+               "queued": 1, "speculation": True, "speculator": "mtp", "kv_format": "bf16"},
+    "totals": {"requests": 12, "completed": 11, "tokens_out": 3456, "tokens_prefilled": 99999, "cached_tokens": 2048},
+    "averages": {"ttft_ms": 812.4, "prefill_tok_s": 12839.0, "decode_tok_s": 136.4},
+    "latency": {"gap_ms": [7.3, 7.9, 9.1, 15.0, 41.0], "gap_samples": 3400, "ttft_ms": [500, 900, 1500]},
+    "speculation": {"rounds": 100, "accept_rate": 0.71, "tokens_per_round": 2.4},
+    "history": {"t": list(range(30)), "decode": [i % 7 for i in range(30)], "prefill": [0] * 30, "active": [1] * 30},
+    "prefix_cache": {"lookups": 12, "hits": 5, "hit_tokens": 2048, "inserts": 9, "evictions": 1, "entries": 8,
+                     "bytes": 1 << 30, "budget_bytes": 4 << 30, "disk": {"hits": 0, "entries": 0, "bytes": 0}},
+    "slots": [{"slot": 0, "active": True, "phase": "decode", "req_id": 12, "pos": 16500, "prompt_tokens": 16384,
+               "cached_tokens": 0, "generated": 116, "max_tokens": 128, "age_s": 3.2, "decode_tok_s": 135.9},
+              {"slot": 1, "active": False, "phase": "idle"}],
+    "gpus": [{"index": 0, "name": "NVIDIA B200", "power_w": 612.0, "power_limit_w": 1000.0, "temp_c": 54, "util_gpu": 97,
+              "sm_mhz": 1830, "mem_used": 40 << 30, "mem_total": 179 << 30, "throttle": ["sw_power_cap"]}],
+    "host": {"cpu_pct": 12.0, "load1": 1.5, "mem_used": 8 << 30, "mem_total": 64 << 30, "rss": 3 << 30},
+    "recent": [{"req_id": 11, "prompt_tokens": 16384, "cached_tokens": 2048, "generated": 128, "queue_ms": 1.0,
+                "ttft_ms": 1290.0, "total_ms": 2230.0, "decode_tok_s": 136.0, "reason": "length"}],
+}
+
+
+def test_tui_frame_contents_and_width():
+    frame = tui.render_frame(STATS, width=120)
+    lines = frame.splitlines()
+    assert all(len(ln) <= 120 for ln in lines)
+    assert "m27 [dense]" in lines[0] and "tp=4" in lines[0] and "up 01:02:03" in lines[0]
+    assert "decode 136.4 tok/s" in frame and "accept 71.0%" in frame
+    assert "p50 7.3" in frame and "max 41.0" in frame
+    assert "prefix cache" in frame and "1.0 GiB / 4.0 GiB" in frame
+    assert "sw_power_cap" in frame and "NVIDIA B200" in frame
+    assert any(ln.split()[:2] == ["0", "decode"] for ln in lines)
+    assert any(ln.split()[:2] == ["1", "idle"] for ln in lines)
+    assert tui.spark([0, 1, 2, 4, 8], 5)[-1] == "█" and len(tui.spark(range(100), 10)) == 10
+    assert tui.render_frame({}, 60).startswith("volta_top")      # an empty document still renders
+
+
+def test_tui_loop_survives_an_unreachable_server():
+    out = io.StringIO()
+    n = tui.run_tui("http://127.0.0.1:9", stop=threading.Event(), interval=0.01, out=out, frames=2)
+    assert n == 2 and "volta_top: http://127.0.0.1:9" in out.getvalue()
+
+
+def test_bench_serve_selftest():
+    rep = bench_serve.selftest()
+    assert rep["selftest"] == "pass", rep
+    assert rep["failed"] == 0 and rep["req_per_s"] > 0 and rep["tok_per_s"] > 0
+    assert bench_serve.percentile([1, 2, 3, 4, 5], 0.5) == 3 and bench_serve.percentile([], 0.9) == 0.0

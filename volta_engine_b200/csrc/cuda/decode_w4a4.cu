@@ -1,0 +1,351 @@
+// Decode / verify-row linear on the block-scaled FP4 tensor-core path with bf16-grade activations:
+//   out[m, n] = alpha * sum_k W[n, k] * x[m, k],   W in NVFP4, x in bf16, M <= 16 rows.
+//
+// The weights stream through TMA into swizzled shared memory in their packed checkpoint form and are decoded by
+// the tensor core itself (tcgen05.mma kind::mxf4nvf4, E4M3 scale per 16), so no ALU or conversion work is spent
+// per weight and many 16 KB tiles are in flight per SM. kind::mxf4nvf4 wants FP4 on both sides; each activation
+// row is therefore expanded into TERMS residual NVFP4 rows
+//   x ~= sum_t 8^-t * q_t,   q_t = nvfp4( 8^t * (x - sum_{u<t} 8^-u q_u) )
+// (relative error 7e-4 at 3 terms, 5e-5 at 4: below bf16 rounding) that ride as extra MMA columns for free; the
+// epilogue folds the TERMS columns of a row back together. Weights are the UMMA A operand (128 features = TMEM
+// lanes per CTA), the expanded rows the B operand (BN = 16 / 32 / 64 columns).
+// Small layers do not fill 148 SMs with one CTA per 128 features, so K is split over gridDim.y CTAs; partial
+// sums go to an fp32 workspace and the CTA that arrives last (per-tile ticket) adds them in split order, which
+// keeps the result independent of timing. Every wait is bounded and reports through the status word.
+// Reference kernels this replaces: src/kernels/cuda/nvfp4/skinny_kernels.cu:445-562 (decode GEMV on mma.sync
+// fragments with in-register decode).
+#include "common.cuh"
+#include "tmap.h"
+
+namespace ve {
+
+// Programmatic dependent launch: block until the grids this launch depends on have finished and their writes
+// are visible (no-op for a normal launch); let dependents of this grid start their prologue.
+VE_DEVINL void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+VE_DEVINL void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+VE_DEVINL float dq_e4m3_dec(uint32_t b) {
+  uint32_t r;
+  asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(r) : "r"(b & 0xffu));
+  return __half2float(__ushort_as_half((unsigned short)(r & 0xffffu)));
+}
+VE_DEVINL uint32_t dq_e4m3_enc(float v) {
+  unsigned short r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.f), "f"(v));
+  return r & 0xffu;
+}
+VE_DEVINL uint32_t dq_e2m1x2_enc(float lo, float hi) {
+  uint32_t r;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+VE_DEVINL float2 dq_e2m1x2_dec(uint32_t byte) {
+  uint32_t r;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "r"(byte));
+  return __half22float2(*reinterpret_cast<const __half2*>(&r));
+}
+
+// x [M, K] bf16 (pitch ldx) -> Xp [M * TERMS, K/2] codes (virtual row m * TERMS + t) and scales in 512 B atoms
+// [K/64][512] (atom byte (r%32)*16 + (r/32)*4 + j = scale of virtual row r, 16-block j of the 64-wide group).
+template <int TERMS>
+__global__ void nvfp4_expand_rows_kernel(const __nv_bfloat16* __restrict__ X, long ldx, uint8_t* __restrict__ Xp,
+                                         uint8_t* __restrict__ Xs, int M, int K) {
+  grid_dep_launch();       // the decode linear behind this kernel may set up and prefetch weights meanwhile
+  const int kb = K >> 4;
+  const int total = M * kb;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int m = idx / kb, b = idx % kb;
+    const __nv_bfloat16* src = X + (long)m * ldx + b * 16;
+    float r[16];
+    const bf16x8 t0 = *reinterpret_cast<const bf16x8*>(src), t1 = *reinterpret_cast<const bf16x8*>(src + 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(t0.v[j]);
+      r[2 * j] = f.x; r[2 * j + 1] = f.y;
+      f = __bfloat1622float2(t1.v[j]);
+      r[8 + 2 * j] = f.x; r[8 + 2 * j + 1] = f.y;
+    }
+    float up = 1.f, down = 1.f;
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(r[j]));
+      const uint32_t sb = dq_e4m3_enc(amax * up * (1.f / 6.f));
+      const float sd = dq_e4m3_dec(sb);
+      const float inv = sd > 0.f ? up / sd : 0.f;
+      const float back = sd * down;
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t byte = dq_e2m1x2_enc(r[2 * j] * inv, r[2 * j + 1] * inv);
+        w[j >> 2] |= byte << (8 * (j & 3));
+        const float2 d = dq_e2m1x2_dec(byte);
+        r[2 * j] -= d.x * back;
+        r[2 * j + 1] -= d.y * back;
+      }
+      const int v = m * TERMS + t;
+      *reinterpret_cast<uint2*>(Xp + (long)v * (K >> 1) + b * 8) = make_uint2(w[0], w[1]);
+      Xs[(long)(b >> 2) * 512 + (v & 31) * 16 + (v >> 5) * 4 + (b & 3)] = (uint8_t)sb;
+      up *= 8.f; down *= 0.125f;
+    }
+  }
+}
+
+struct DecodeParams {
+  int N, M, K;
+  float alpha;
+  __nv_bfloat16* out; long ldo;
+  const __nv_bfloat16* residual; long ldr;
+  float* out_f32;
+  const uint8_t* sfa;     // [N/128][K/64][512]
+  const uint8_t* sfb;     // [K/64][512]
+  float* ws;              // [N/128][KS][16][128] partial sums (KS > 1)
+  int* tickets;           // [N/128], zero between launches
+  int* status;
+};
+
+template <int BN, int TERMS, int STAGES>
+__global__ void __launch_bounds__(192, 2)
+decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap) {
+  constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, SF_BYTES = 2048;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+  constexpr int ACC_COLS = BN < 32 ? 32 : BN;
+  constexpr int TMEM_COLS = ACC_COLS + 32 <= 64 ? 64 : 128;
+  constexpr int MROWS = BN / TERMS;
+  static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024 B alignment");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full[STAGES], empty[STAGES], acc_full;
+  __shared__ uint32_t tmem_holder;
+  __shared__ int s_fail, s_ticket;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, n0 = tile * 128;
+  const int KS = gridDim.y, ks = blockIdx.y;
+  const int nkt_all = p.K >> 8;
+  const int kt0 = (int)((long)ks * nkt_all / KS), kt1 = (int)((long)(ks + 1) * nkt_all / KS);
+  const int nkt = kt1 - kt0;
+  const int nkg = p.K >> 6;                       // 64-wide k groups (scale atoms) along K
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(&acc_full, 1);
+    s_fail = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&tmem_holder, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_holder;
+  auto stage_ptr = [&](int s) { return smem + (size_t)s * STAGE_BYTES; };   // [A][B][SFA][SFB]
+
+  if (warp == 0) {
+    if (elect_one()) {
+      prefetch_tmap(&amap);
+      prefetch_tmap(&bmap);
+      // Weights and their scales do not depend on the upstream kernel: the first STAGES tiles are requested before
+      // the grid dependency resolves (programmatic dependent launch), the activations after it.
+      const int pre = nkt < STAGES ? nkt : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = stage_ptr(i);
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        tma_load_2d(st, &amap, &full[i], (kt0 + i) * 128, n0);
+        bulk_load(st + A_BYTES + B_BYTES, p.sfa + ((size_t)tile * nkg + (kt0 + i) * 4) * 512, SF_BYTES, &full[i]);
+      }
+      grid_dep_wait();
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = stage_ptr(i);
+        tma_load_2d(st + A_BYTES, &bmap, &full[i], (kt0 + i) * 128, 0);
+        bulk_load(st + A_BYTES + B_BYTES + SF_BYTES, p.sfb + (size_t)(kt0 + i) * 4 * 512, SF_BYTES, &full[i]);
+      }
+      for (int i = pre; i < nkt; ++i) {
+        const int s = i % STAGES, kt = kt0 + i;
+        if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) { atomicExch(&s_fail, 1); break; }
+        uint8_t* st = stage_ptr(s);
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(st, &amap, &full[s], kt * 128, n0);
+        tma_load_2d(st + A_BYTES, &bmap, &full[s], kt * 128, 0);
+        bulk_load(st + A_BYTES + B_BYTES, p.sfa + ((size_t)tile * nkg + kt * 4) * 512, SF_BYTES, &full[s]);
+        bulk_load(st + A_BYTES + B_BYTES + SF_BYTES, p.sfb + (size_t)kt * 4 * 512, SF_BYTES, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_nvf4(128, BN);
+      const uint32_t tmem_sfa = tmem_base + ACC_COLS, tmem_sfb = tmem_base + ACC_COLS + 16;
+      bool ok = true;
+      for (int i = 0; i < nkt && ok; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(&full[s], (i / STAGES) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* st = stage_ptr(s);
+        const uint32_t sfa_s = smem_u32(st + A_BYTES + B_BYTES), sfb_s = sfa_s + SF_BYTES;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          tc_cp_sf(tmem_sfa + kb * 4, make_desc_sf(sfa_s + kb * 512));
+          tc_cp_sf(tmem_sfb + kb * 4, make_desc_sf(sfb_s + kb * 512));
+        }
+        const uint64_t ad = make_desc_sw128(smem_u32(st)), bd = make_desc_sw128(smem_u32(st + A_BYTES));
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)
+          tc_mma_nvf4(tmem_base, ad + kb * 2, bd + kb * 2, idesc, (i | kb) ? 1u : 0u, tmem_sfa + kb * 4, tmem_sfb + kb * 4);
+        tc_commit(&empty[s]);
+      }
+      if (!ok) atomicExch(&s_fail, 1);
+      tc_commit(&acc_full);
+    }
+  } else {
+    // epilogue: TMEM lane = output feature, column m * TERMS + t = term t of row m
+    const int q = warp & 3;                      // TMEM lane quarter this warp may touch
+    const int f = q * 32 + lane;                 // feature inside the tile
+    const int n = n0 + f;
+    grid_dep_wait();                             // this thread reads / writes buffers of upstream kernels below
+    const bool ok = nkt > 0 ? mbar_wait(&acc_full, 0) : true;
+    if (!ok) atomicExch(&s_fail, 1);
+    tc_fence_after();
+    float acc[MROWS];
+#pragma unroll
+    for (int m = 0; m < MROWS; ++m) acc[m] = 0.f;
+    if (ok && !s_fail && nkt > 0) {
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j += TERMS) {
+          float v = 0.f, c = 1.f;
+#pragma unroll
+          for (int t = 0; t < TERMS; ++t) { v = fmaf(__uint_as_float(r[j + t]), c, v); c *= 0.125f; }
+          acc[(c0 + j) / TERMS] = v;
+        }
+      }
+    }
+    bool write = true;
+    if (KS > 1) {
+      float* mine = p.ws + ((size_t)tile * KS + ks) * 16 * 128;
+#pragma unroll
+      for (int m = 0; m < MROWS; ++m)
+        if (m < p.M) mine[m * 128 + f] = acc[m];
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) s_ticket = atomicAdd(p.tickets + tile, 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      write = s_ticket == KS - 1;
+      if (write) {
+        __threadfence();
+        const float* all = p.ws + (size_t)tile * KS * 16 * 128;
+#pragma unroll
+        for (int m = 0; m < MROWS; ++m) {
+          if (m < p.M) {
+            float s = 0.f;
+            for (int k2 = 0; k2 < KS; ++k2) s += __ldcg(all + ((size_t)k2 * 16 + m) * 128 + f);
+            acc[m] = s;
+          }
+        }
+        if (warp == 2 && lane == 0) p.tickets[tile] = 0;      // ready for the next launch
+      }
+    }
+    if (write && n < p.N && !s_fail) {
+#pragma unroll
+      for (int m = 0; m < MROWS; ++m) {
+        if (m < p.M) {
+          float v = acc[m] * p.alpha;
+          if (p.residual) v += bf2f(p.residual[(long)m * p.ldr + n]);
+          if (p.out_f32) p.out_f32[(long)m * p.ldo + n] = v;
+          else p.out[(long)m * p.ldo + n] = f2bf(v);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if (threadIdx.x == 0 && s_fail && p.status) atomicExch(p.status, (int)kErrMbarTimeout);
+}
+
+template <int BN, int TERMS, int STAGES>
+static int launch_decode(const DecodeParams& p, const CUtensorMap& amap, const CUtensorMap& bmap, int KS, int pdl,
+                         cudaStream_t st) {
+  constexpr int smem = STAGES * (128 * 128 + BN * 128 + 4096) + 1024;
+  static_assert(smem <= 113 * 1024, "two CTAs per SM");
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(decode_w4a4_kernel<BN, TERMS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.N / 128, KS);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, decode_w4a4_kernel<BN, TERMS, STAGES>, p, amap, bmap);
+}
+
+}  // namespace ve
+
+using namespace ve;
+
+extern "C" {
+
+// Rows of x -> TERMS residual NVFP4 rows each. Xs must hold K/64 atoms of 512 B (zero-initialised once).
+int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int K, int terms, cudaStream_t st) {
+  if (M < 1 || K % 64 || M * terms > 128) return cudaErrorInvalidValue;
+  const int total = M * (K / 16);
+  const int blocks = (total + 127) / 128;
+  if (terms == 4) nvfp4_expand_rows_kernel<4><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)X, ldx, (uint8_t*)Xp, (uint8_t*)Xs, M, K);
+  else if (terms == 2) nvfp4_expand_rows_kernel<2><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)X, ldx, (uint8_t*)Xp, (uint8_t*)Xs, M, K);
+  else if (terms == 1) nvfp4_expand_rows_kernel<1><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)X, ldx, (uint8_t*)Xp, (uint8_t*)Xs, M, K);
+  else return cudaErrorInvalidValue;
+  VE_CHECK_LAUNCH();
+}
+
+// Split count that fills the GPU: about two waves of CTAs, at least two k-tiles per CTA.
+int ve_decode_w4a4_splits(int N, int K) {
+  const int tiles = N / 128, nkt = K / 256;
+  int ks = (2 * 148) / tiles;          // all CTAs resident at once (two per SM)
+  if (ks > nkt / 2) ks = nkt / 2;
+  if (ks < 1) ks = 1;
+  if (ks > 32) ks = 32;
+  return ks;
+}
+
+// Wp [N, K/2] codes, sfa [N/128][K/64][512]; Xp / sfb from ve_nvfp4_expand_rows with the same `terms`.
+// ws: fp32 [N/128][ks][16][128]; tickets: int [N/128] zeroed once. ks <= 0 picks ve_decode_w4a4_splits.
+// pdl != 0 launches with programmatic stream serialization: set-up and the first weight tiles overlap the
+// kernel in front (which must be the one producing Xp / sfb, or any kernel when that one has long finished).
+int ve_decode_w4a4(const void* Wp, const void* sfa, const void* Xp, const void* sfb, void* out, long ldo, void* out_f32,
+                   const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, void* ws,
+                   void* tickets, void* status, cudaStream_t st) {
+  if (M < 1 || N % 128 || K % 256 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64) return cudaErrorInvalidValue;
+  if (ks <= 0) ks = ve_decode_w4a4_splits(N, K);
+  if (ks > K / 256) ks = K / 256;
+  if (ks > 1 && (!ws || !tickets)) return cudaErrorInvalidValue;
+  const int cols = M * terms, bn = cols <= 16 ? 16 : cols <= 32 ? 32 : 64;
+  CUtensorMap amap, bmap;
+  int rc = make_tmap_2d(&amap, Wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, (uint64_t)K / 2, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = make_tmap_2d(&bmap, Xp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, cols, K / 2, (uint64_t)K / 2, bn, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  DecodeParams p{N, M, K, alpha, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)residual, ldr, (float*)out_f32,
+                 (const uint8_t*)sfa, (const uint8_t*)sfb, (float*)ws, (int*)tickets, (int*)status};
+#define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, bmap, ks, pdl, st)
+  if (terms == 4) { if (bn == 16) VE_DW(16, 4, 4); if (bn == 32) VE_DW(32, 4, 4); VE_DW(64, 4, 3); }
+  if (terms == 2) { if (bn == 16) VE_DW(16, 2, 4); if (bn == 32) VE_DW(32, 2, 4); VE_DW(64, 2, 3); }
+  if (bn == 16) VE_DW(16, 1, 4);
+  if (bn == 32) VE_DW(32, 1, 4);
+  VE_DW(64, 1, 3);
+#undef VE_DW
+}
+
+}  // extern "C"

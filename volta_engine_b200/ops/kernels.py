@@ -4,6 +4,8 @@ a GPU machine: a missing library raises); CPU tensors run the fp32 PyTorch oracl
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _lib
@@ -292,6 +294,71 @@ def nvfp4_gemv_mma(wg, sg, gscale, x, N, K, out=None, residual=None, ks=None):
     call("nvfp4_gemv_mma", "ppfplplpliiiipp", ptr(wg), ptr(sg), float(gscale), ptr(x), x.stride(0), ptr(out),
          out.stride(0), ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, ks, ptr(ws),
          ptr(cnt))
+    return out
+
+
+_dw_scratch = {}
+DW_MAX_K = 1 << 16
+DW_TERMS = 4
+
+
+def dw_scratch(device):
+    """Per-device buffers of the tcgen05 decode linear: expanded activation codes [64, DW_MAX_K/2], their scale atoms
+    (zero-initialised: unused virtual rows keep scale 0), fp32 split-K partials and per-tile tickets."""
+    key = str(device)
+    t = _dw_scratch.get(key)
+    if t is None:
+        t = (torch.zeros(64, DW_MAX_K // 2, dtype=torch.uint8, device=device),
+             torch.zeros(DW_MAX_K // 64 * 512, dtype=torch.uint8, device=device),
+             torch.empty(1024 * 16 * 128, dtype=torch.float32, device=device),
+             torch.zeros(1024, dtype=torch.int32, device=device))
+        _dw_scratch[key] = t
+    return t
+
+
+def dw_splits(N: int, K: int) -> int:
+    """K splits of the decode linear: about two waves of CTAs, at least two 256-wide k-tiles each."""
+    tiles, nkt = N // 128, K // 256
+    ks = (2 * 148) // tiles                    # all CTAs resident at once (two per SM)
+    ks = max(1, min(ks, nkt // 2, 32))
+    while ks > 1 and ks * tiles > 1024:
+        ks -= 1
+    return ks
+
+
+def nvfp4_expand_rows(x, terms=DW_TERMS):
+    """bf16 rows -> residual NVFP4 expansion in the shared scratch; returns (codes, scale atoms) views."""
+    M, K = x.shape
+    xp, xs, _, _ = dw_scratch(x.device)
+    assert K <= DW_MAX_K and M * terms <= 64
+    xpv = xp.view(-1)[: 64 * (K // 2)].view(64, K // 2)
+    call("nvfp4_expand_rows", "plppiii", ptr(x), x.stride(0), ptr(xpv), ptr(xs), M, K, terms)
+    return xpv, xs
+
+
+DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
+
+
+def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None,
+                expanded=None, pdl=None):
+    """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path with activations expanded
+    into ``terms`` residual NVFP4 rows (bf16-grade accuracy): out [M, N]."""
+    N, K = packed.shape[0], packed.shape[1] * 2
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    f32 = out.dtype == torch.float32
+    xpv, xs = expanded if expanded is not None else nvfp4_expand_rows(x, terms)
+    _, _, ws, tickets = dw_scratch(x.device)
+    if ks is None:
+        ks = dw_splits(N, K)
+    assert ks * (N // 128) <= 1024
+    if pdl is None:
+        pdl = DW_PDL and expanded is None      # the expansion kernel right in front releases this launch early
+    call("decode_w4a4", "pppp" + "plppl" + "iiifiii" + "ppp", ptr(packed), ptr(sf_atoms), ptr(xpv), ptr(xs),
+         0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
+         residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,
+         ptr(ws), ptr(tickets), ptr(status_word(x.device)))
     return out
 
 

@@ -21,7 +21,8 @@ GEMV_MAX_ROWS = 16
 # baseline / bring-up aid); unset = hand-written kernels only.
 import os
 GEMM_BACKEND = os.environ.get("VOLTA_GEMM_BACKEND", "native")
-GEMV_KERNEL = os.environ.get("VOLTA_GEMV", "auto")  # auto | mma (prepacked tensor-core mat-vec) | simt
+# auto | tc (tcgen05 block-scaled FP4 with residual-expanded activations) | mma (prepacked mma.sync mat-vec) | simt
+GEMV_KERNEL = os.environ.get("VOLTA_GEMV", "auto")
 
 
 class LinearBF16:
@@ -68,11 +69,18 @@ class LinearNVFP4:
         """Build the loader-side scale layouts once (load time, not on the hot path)."""
         if self.gemm_mode == "w4a16" and self._sf_k128 is None and self.out_features % 128 == 0:
             self._sf_k128 = qn.scales_blocked_k128(self.scales)
-        if self.gemm_mode == "w4a4" and self._sf_atoms is None:
+        tc = self._tc_ok() and GEMV_KERNEL in ("auto", "tc")
+        if (self.gemm_mode == "w4a4" or tc) and self._sf_atoms is None and self.out_features % 128 == 0 \
+                and self.in_features % 64 == 0:
             self._sf_atoms = qn.scales_atoms_512(self.scales)
-        if self._gv is None and self.packed.is_cuda and self.out_features % 16 == 0 and self.in_features % 64 == 0:
+        if self._gv is None and self.packed.is_cuda and self.out_features % 16 == 0 and self.in_features % 64 == 0 \
+                and (GEMV_KERNEL == "mma" or (GEMV_KERNEL == "auto" and not tc)):
             self._gv = qn.prepack_gv(self.packed, self.scales)
         return self
+
+    def _tc_ok(self) -> bool:
+        return (self.packed.is_cuda and self.out_features % 128 == 0 and self.in_features % 256 == 0
+                and self.in_features <= K.DW_MAX_K)
 
     def dequant(self):
         return K.nvfp4_dequant(self.packed, self.scales, self.gscale)
@@ -85,6 +93,10 @@ class LinearNVFP4:
             return y.to(x.dtype)
         rows = x.shape[0]
         if rows <= GEMV_MAX_ROWS:
+            # tcgen05 path: the tensor core decodes the FP4 weights itself; activations ride as 4 residual NVFP4
+            # terms per row (error below bf16 rounding), cost independent of the row count
+            if GEMV_KERNEL in ("auto", "tc") and self._sf_atoms is not None and self._tc_ok():
+                return K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, out=out, residual=residual)
             # one row: the SIMT streaming kernel is faster; 2..16 rows: the tensor-core kernel costs the same
             # as one row. Both sum exact products in fp32, so they agree to fp32 rounding.
             if self._gv is not None and (GEMV_KERNEL == "mma" or (GEMV_KERNEL == "auto" and rows > 1)):
