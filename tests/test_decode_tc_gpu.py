@@ -1,0 +1,82 @@
+"""tcgen05 block-scaled FP4 decode linear: in-kernel residual expansion of bf16 activations, split-K tickets,
+residual / fp32 outputs, agreement with the stand-alone expansion kernel and with the fp32 reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dequant_expansion(xp, xs, M, K, terms):
+    from volta_engine_b200.quant import nvfp4 as qn
+    codes = qn.e2m1_decode(qn.unpack_codes(xp[: M * terms].cpu())).reshape(M * terms, K // 16, 16)
+    atoms = xs.cpu().reshape(-1, 512)[: K // 64]
+    v = torch.arange(M * terms)
+    idx = (v % 32) * 16 + (v // 32) * 4
+    sc = torch.stack([atoms[:, idx + j] for j in range(4)], dim=-1)          # [K/64, rows, 4]
+    sc = qn.e4m3_decode(sc.permute(1, 0, 2).reshape(M * terms, K // 16))
+    rows = (codes * sc[..., None]).reshape(M, terms, K)
+    coef = torch.tensor([8.0 ** -t for t in range(terms)])
+    return (rows * coef[None, :, None]).sum(1)
+
+
+def test_expansion_reaches_bf16_accuracy():
+    from volta_engine_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = (torch.randn(5, 1024, generator=g) * torch.rand(5, 1024, generator=g).pow(3) * 4).to(torch.bfloat16)
+    for terms, bound in ((1, 0.12), (2, 0.012), (4, 1e-4)):
+        xp, xs = K.nvfp4_expand_rows(x.to(dev), terms)
+        torch.cuda.synchronize()
+        xh = _dequant_expansion(xp, xs, 5, 1024, terms)
+        rel = float((xh - x.float()).norm() / x.float().norm())
+        assert rel < bound, (terms, rel)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+def test_decode_linear_matches_reference(M):
+    from volta_engine_b200.ops import kernels as K
+    from volta_engine_b200.quant import nvfp4 as qn
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(M)
+    N, Kd = 384, 3072          # 12 k-tiles: with one split every pipeline stage is reused three times
+    w = torch.randn(N, Kd, generator=g) * 0.05
+    p, s, gs = qn.quantize_nvfp4(w, search=False)
+    wd = qn.dequantize_nvfp4(p, s, gs).double()
+    at = qn.scales_atoms_512(s).to(dev)
+    x = (torch.randn(M, Kd, generator=g) * torch.rand(M, Kd, generator=g) * 3).to(torch.bfloat16)
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    ref = x.double() @ wd.t()
+    xp, xs = K.nvfp4_expand_rows(x.to(dev), 4)
+    torch.cuda.synchronize()
+    ref_exp = _dequant_expansion(xp, xs, M, Kd, 4).double() @ wd.t()     # what the tensor core is asked to compute
+    outs = {}
+    for ks in (1, 2, 3, None):
+        for pdl in (False, True):
+            y = K.decode_w4a4(p.to(dev), at, gs, x.to(dev), out_f32=True, ks=ks, pdl=pdl).double().cpu()
+            assert float((y - ref_exp).abs().max()) < 2e-5 * float(ref.abs().max()) + 1e-6, (ks, pdl)
+            assert float((y - ref).norm() / ref.norm()) < 2e-4
+            outs[(ks, pdl)] = y
+    assert torch.equal(outs[(2, False)], outs[(2, True)])       # split order is fixed, launch mode does not matter
+    yb = K.decode_w4a4(p.to(dev), at, gs, x.to(dev), residual=res.to(dev), ks=2).float().cpu()
+    want = (ref + res.double()).float()
+    assert torch.allclose(yb, want, atol=2e-2 * float(want.abs().max()), rtol=1e-2)
+    # rows are independent of the batch they ride in
+    y1 = K.decode_w4a4(p.to(dev), at, gs, x[:1].to(dev), out_f32=True, ks=2).cpu()
+    assert torch.equal(y1[0], outs[(2, False)][0].float())
+    assert K.check_status(dev) == 0
+
+
+def test_linear_layer_uses_the_tensor_core_path_for_decode_rows():
+    from volta_engine_b200.ops import kernels as K, linear as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(9)
+    w = torch.randn(256, 512, generator=g) * 0.05
+    lin = L.LinearNVFP4.from_dense(w.to(dev), search=False).prepare()
+    assert lin._sf_atoms is not None or L.GEMV_KERNEL not in ("auto", "tc")
+    x = torch.randn(2, 512, generator=g).to(torch.bfloat16).to(dev)
+    ref = x.float().cpu() @ lin.dequant().float().cpu().t()
+    before = K.native_launches()
+    y = lin.forward(x).float().cpu()
+    assert torch.allclose(y, ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    if L.GEMV_KERNEL in ("auto", "tc"):
+        assert K.native_launches() - before == 1       # one launch: expansion happens inside the kernel

@@ -67,6 +67,7 @@ VE_DEVINL uint32_t pack_bf16(float lo, float hi) {
 template <int HD, int NW>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
+  grid_dep_launch();
   constexpr int TILE_BYTES = kPageTok * HD * 2;
   constexpr int NCH = HD / 64;   // 128-byte column chunks per row
   constexpr int KSTEPS = HD / 16;
@@ -287,6 +288,7 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
                                    __nv_bfloat16* __restrict__ out, long out_stride,
                                    const __nv_bfloat16* __restrict__ gate, long gate_stride, const int* __restrict__ slot,
                                    int nq, int nsplit, int HD) {
+  grid_dep_launch();
   const int row = blockIdx.x / nq, head = blockIdx.x % nq, d = threadIdx.x;
   if (slot && slot[row] < 0) return;
   const long base = ((long)row * nq + head) * nsplit;

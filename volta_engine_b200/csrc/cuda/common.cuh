@@ -96,6 +96,12 @@ VE_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Programmatic dependent launch: block until the grids this launch depends on have finished and their writes
+// are visible (no-op for a normal launch) / let a dependent launched with programmatic stream serialization start
+// its prologue now (no-op when the next kernel in the stream is a normal launch).
+VE_DEVINL void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+VE_DEVINL void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 VE_DEVINL uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -7,8 +7,9 @@
 // row is therefore expanded into TERMS residual NVFP4 rows
 //   x ~= sum_t 8^-t * q_t,   q_t = nvfp4( 8^t * (x - sum_{u<t} 8^-u q_u) )
 // (relative error 7e-4 at 3 terms, 5e-5 at 4: below bf16 rounding) that ride as extra MMA columns for free; the
-// epilogue folds the TERMS columns of a row back together. Weights are the UMMA A operand (128 features = TMEM
-// lanes per CTA), the expanded rows the B operand (BN = 16 / 32 / 64 columns).
+// epilogue folds the TERMS columns of a row back together. The expansion is done inside the kernel by the warps
+// that are idle during the main loop, straight into the swizzled B operand of each pipeline stage. Weights are
+// the UMMA A operand (128 features = TMEM lanes per CTA), the expanded rows the B operand (BN = 16 / 32 / 64).
 // Small layers do not fill 148 SMs with one CTA per 128 features, so K is split over gridDim.y CTAs; partial
 // sums go to an fp32 workspace and the CTA that arrives last (per-tile ticket) adds them in split order, which
 // keeps the result independent of timing. Every wait is bounded and reports through the status word.
@@ -18,11 +19,6 @@
 #include "tmap.h"
 
 namespace ve {
-
-// Programmatic dependent launch: block until the grids this launch depends on have finished and their writes
-// are visible (no-op for a normal launch); let dependents of this grid start their prologue.
-VE_DEVINL void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-VE_DEVINL void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 VE_DEVINL float dq_e4m3_dec(uint32_t b) {
   uint32_t r;
@@ -92,22 +88,63 @@ __global__ void nvfp4_expand_rows_kernel(const __nv_bfloat16* __restrict__ X, lo
   }
 }
 
+// One 16-element block of a bf16 row -> TERMS residual NVFP4 blocks: 8 code bytes and one E4M3 scale per term.
+template <int TERMS>
+VE_DEVINL void expand_block16(const __nv_bfloat16* __restrict__ src, uint2* codes, uint32_t* scales) {
+  float r[16];
+  const bf16x8 t0 = *reinterpret_cast<const bf16x8*>(src), t1 = *reinterpret_cast<const bf16x8*>(src + 8);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = __bfloat1622float2(t0.v[j]);
+    r[2 * j] = f.x; r[2 * j + 1] = f.y;
+    f = __bfloat1622float2(t1.v[j]);
+    r[8 + 2 * j] = f.x; r[8 + 2 * j + 1] = f.y;
+  }
+  float up = 1.f, down = 1.f;
+#pragma unroll
+  for (int t = 0; t < TERMS; ++t) {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(r[j]));
+    const uint32_t sb = dq_e4m3_enc(amax * up * (1.f / 6.f));
+    const float sd = dq_e4m3_dec(sb);
+    const float inv = sd > 0.f ? up / sd : 0.f;
+    const float back = sd * down;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t byte = dq_e2m1x2_enc(r[2 * j] * inv, r[2 * j + 1] * inv);
+      w[j >> 2] |= byte << (8 * (j & 3));
+      const float2 d = dq_e2m1x2_dec(byte);
+      r[2 * j] -= d.x * back;
+      r[2 * j + 1] -= d.y * back;
+    }
+    codes[t] = make_uint2(w[0], w[1]);
+    scales[t] = sb;
+    up *= 8.f; down *= 0.125f;
+  }
+}
+
 struct DecodeParams {
   int N, M, K;
   float alpha;
+  const __nv_bfloat16* x; long ldx;   // activations [M, K]
   __nv_bfloat16* out; long ldo;
   const __nv_bfloat16* residual; long ldr;
   float* out_f32;
   const uint8_t* sfa;     // [N/128][K/64][512]
-  const uint8_t* sfb;     // [K/64][512]
   float* ws;              // [N/128][KS][16][128] partial sums (KS > 1)
   int* tickets;           // [N/128], zero between launches
   int* status;
+  int tpt;                // epilogue threads that build one activation tile (16, 32, 64 or 128)
 };
 
+// Warp roles (192 threads): warp 0 = TMA producer of weight tiles and their scale atoms; warp 1 = TMEM owner and
+// MMA issuer; warps 2..5 = activation producers during the main loop (expand x into the B operand of each stage,
+// straight into swizzled shared memory) and epilogue afterwards.
 template <int BN, int TERMS, int STAGES>
 __global__ void __launch_bounds__(192, 2)
-decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap) {
+decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap amap) {
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, SF_BYTES = 2048;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
   constexpr int ACC_COLS = BN < 32 ? 32 : BN;
@@ -128,48 +165,40 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
   const int kt0 = (int)((long)ks * nkt_all / KS), kt1 = (int)((long)(ks + 1) * nkt_all / KS);
   const int nkt = kt1 - kt0;
   const int nkg = p.K >> 6;                       // 64-wide k groups (scale atoms) along K
+  const int tpt = p.tpt;
 
+  auto stage_ptr = [&](int s) { return smem + (size_t)s * STAGE_BYTES; };   // [A][B][SFA][SFB]
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    // a stage is full after the TMA bytes (one arrive.expect_tx) and the tpt activation writers have arrived
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1 + tpt); mbar_init(&empty[s], 1); }
     mbar_init(&acc_full, 1);
     s_fail = 0;
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(&tmem_holder, TMEM_COLS); tmem_relinquish(); }
+  if (warp >= 2) {
+    // scales of the unused columns stay zero (their accumulator columns are never read)
+    const int etid = threadIdx.x - 64;
+    for (int s = 0; s < STAGES; ++s)
+      *reinterpret_cast<uint4*>(stage_ptr(s) + A_BYTES + B_BYTES + SF_BYTES + etid * 16) = make_uint4(0, 0, 0, 0);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_holder;
-  auto stage_ptr = [&](int s) { return smem + (size_t)s * STAGE_BYTES; };   // [A][B][SFA][SFB]
 
   if (warp == 0) {
     if (elect_one()) {
       prefetch_tmap(&amap);
-      prefetch_tmap(&bmap);
-      // Weights and their scales do not depend on the upstream kernel: the first STAGES tiles are requested before
-      // the grid dependency resolves (programmatic dependent launch), the activations after it.
-      const int pre = nkt < STAGES ? nkt : STAGES;
-      for (int i = 0; i < pre; ++i) {
-        uint8_t* st = stage_ptr(i);
-        mbar_expect_tx(&full[i], STAGE_BYTES);
-        tma_load_2d(st, &amap, &full[i], (kt0 + i) * 128, n0);
-        bulk_load(st + A_BYTES + B_BYTES, p.sfa + ((size_t)tile * nkg + (kt0 + i) * 4) * 512, SF_BYTES, &full[i]);
-      }
-      grid_dep_wait();
-      for (int i = 0; i < pre; ++i) {
-        uint8_t* st = stage_ptr(i);
-        tma_load_2d(st + A_BYTES, &bmap, &full[i], (kt0 + i) * 128, 0);
-        bulk_load(st + A_BYTES + B_BYTES + SF_BYTES, p.sfb + (size_t)(kt0 + i) * 4 * 512, SF_BYTES, &full[i]);
-      }
-      for (int i = pre; i < nkt; ++i) {
+      // weights do not depend on the kernel in front: with a programmatic dependent launch they start streaming
+      // while that kernel is still running
+      for (int i = 0; i < nkt; ++i) {
         const int s = i % STAGES, kt = kt0 + i;
         if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) { atomicExch(&s_fail, 1); break; }
         uint8_t* st = stage_ptr(s);
-        mbar_expect_tx(&full[s], STAGE_BYTES);
+        mbar_expect_tx(&full[s], A_BYTES + SF_BYTES);
         tma_load_2d(st, &amap, &full[s], kt * 128, n0);
-        tma_load_2d(st + A_BYTES, &bmap, &full[s], kt * 128, 0);
         bulk_load(st + A_BYTES + B_BYTES, p.sfa + ((size_t)tile * nkg + kt * 4) * 512, SF_BYTES, &full[s]);
-        bulk_load(st + A_BYTES + B_BYTES + SF_BYTES, p.sfb + (size_t)kt * 4 * 512, SF_BYTES, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -199,11 +228,46 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
       tc_commit(&acc_full);
     }
   } else {
-    // epilogue: TMEM lane = output feature, column m * TERMS + t = term t of row m
+    const int etid = threadIdx.x - 64;           // 0..127
+    grid_dep_wait();                             // x, residual and out belong to upstream kernels
+    // ---- activation producer: groups of tpt threads own k-tiles g, g + ngroups, ...; inside a tile the 16 * M
+    // blocks (row m, 16-block b) are dealt round-robin to the group's threads
+    {
+      // At most STAGES groups, and a count that divides STAGES: every stage is then always filled by the same
+      // group, which meets the stage's phases in order (a parity wait cannot tell phases two apart).
+      int ngroups = 128 / tpt;
+      if (ngroups > STAGES) ngroups = STAGES;
+      while (STAGES % ngroups) --ngroups;
+      const int grp = etid / tpt, gt = etid % tpt;
+      const int items = 16 * p.M;
+      bool ok = true;
+      for (int i = grp; i < nkt && ok && grp < ngroups; i += ngroups) {
+        const int s = i % STAGES, kt = kt0 + i;
+        ok = mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1);
+        if (!ok) break;
+        uint8_t* bt = stage_ptr(s) + A_BYTES;
+        uint8_t* sf = bt + B_BYTES + SF_BYTES;
+        for (int it = gt; it < items; it += tpt) {
+          const int m = it >> 4, b = it & 15;
+          uint2 codes[TERMS];
+          uint32_t sc[TERMS];
+          expand_block16<TERMS>(p.x + (long)m * p.ldx + kt * 256 + b * 16, codes, sc);
+#pragma unroll
+          for (int t = 0; t < TERMS; ++t) {
+            const int v = m * TERMS + t;
+            *reinterpret_cast<uint2*>(bt + v * 128 + ((((b >> 1) ^ (v & 7))) << 4) + (b & 1) * 8) = codes[t];
+            sf[(b >> 2) * 512 + (v & 31) * 16 + (v >> 5) * 4 + (b & 3)] = (uint8_t)sc[t];
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&full[s]);
+      }
+      if (!ok) atomicExch(&s_fail, 1);
+    }
+    // ---- epilogue: TMEM lane = output feature, column m * TERMS + t = term t of row m
     const int q = warp & 3;                      // TMEM lane quarter this warp may touch
     const int f = q * 32 + lane;                 // feature inside the tile
     const int n = n0 + f;
-    grid_dep_wait();                             // this thread reads / writes buffers of upstream kernels below
     const bool ok = nkt > 0 ? mbar_wait(&acc_full, 0) : true;
     if (!ok) atomicExch(&s_fail, 1);
     tc_fence_after();
@@ -233,7 +297,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
         if (m < p.M) mine[m * 128 + f] = acc[m];
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) s_ticket = atomicAdd(p.tickets + tile, 1);
+      if (etid == 0) s_ticket = atomicAdd(p.tickets + tile, 1);
       asm volatile("bar.sync 1, 128;" ::: "memory");
       write = s_ticket == KS - 1;
       if (write) {
@@ -247,7 +311,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
             acc[m] = s;
           }
         }
-        if (warp == 2 && lane == 0) p.tickets[tile] = 0;      // ready for the next launch
+        if (etid == 0) p.tickets[tile] = 0;      // ready for the next launch
       }
     }
     if (write && n < p.N && !s_fail) {
@@ -269,8 +333,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
 }
 
 template <int BN, int TERMS, int STAGES>
-static int launch_decode(const DecodeParams& p, const CUtensorMap& amap, const CUtensorMap& bmap, int KS, int pdl,
-                         cudaStream_t st) {
+static int launch_decode(const DecodeParams& p, const CUtensorMap& amap, int KS, int pdl, cudaStream_t st) {
   constexpr int smem = STAGES * (128 * 128 + BN * 128 + 4096) + 1024;
   static_assert(smem <= 113 * 1024, "two CTAs per SM");
   static bool attr_set = false;
@@ -289,7 +352,7 @@ static int launch_decode(const DecodeParams& p, const CUtensorMap& amap, const C
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = pdl ? 1 : 0;
-  return (int)cudaLaunchKernelEx(&cfg, decode_w4a4_kernel<BN, TERMS, STAGES>, p, amap, bmap);
+  return (int)cudaLaunchKernelEx(&cfg, decode_w4a4_kernel<BN, TERMS, STAGES>, p, amap);
 }
 
 }  // namespace ve
@@ -298,7 +361,8 @@ using namespace ve;
 
 extern "C" {
 
-// Rows of x -> TERMS residual NVFP4 rows each. Xs must hold K/64 atoms of 512 B (zero-initialised once).
+// Stand-alone form of the expansion the decode linear does in its producer warps (same arithmetic; used to test
+// it). Xs must hold K/64 atoms of 512 B (zero-initialised once).
 int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int K, int terms, cudaStream_t st) {
   if (M < 1 || K % 64 || M * terms > 128) return cudaErrorInvalidValue;
   const int total = M * (K / 16);
@@ -310,36 +374,27 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
   VE_CHECK_LAUNCH();
 }
 
-// Split count that fills the GPU: about two waves of CTAs, at least two k-tiles per CTA.
-int ve_decode_w4a4_splits(int N, int K) {
-  const int tiles = N / 128, nkt = K / 256;
-  int ks = (2 * 148) / tiles;          // all CTAs resident at once (two per SM)
-  if (ks > nkt / 2) ks = nkt / 2;
-  if (ks < 1) ks = 1;
-  if (ks > 32) ks = 32;
-  return ks;
-}
-
-// Wp [N, K/2] codes, sfa [N/128][K/64][512]; Xp / sfb from ve_nvfp4_expand_rows with the same `terms`.
-// ws: fp32 [N/128][ks][16][128]; tickets: int [N/128] zeroed once. ks <= 0 picks ve_decode_w4a4_splits.
-// pdl != 0 launches with programmatic stream serialization: set-up and the first weight tiles overlap the
-// kernel in front (which must be the one producing Xp / sfb, or any kernel when that one has long finished).
-int ve_decode_w4a4(const void* Wp, const void* sfa, const void* Xp, const void* sfb, void* out, long ldo, void* out_f32,
+// Wp [N, K/2] codes, sfa [N/128][K/64][512], X [M, K] bf16 (pitch ldx elements, rows 16-byte aligned).
+// ws: fp32 [N/128][ks][16][128]; tickets: int [N/128] zeroed once; ks = K splits (>= 1).
+// pdl != 0 launches with programmatic stream serialization: set-up and the first weight tiles overlap the kernel
+// in front of it in the stream (the kernel waits for that kernel before it touches X, residual or out).
+int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, void* out, long ldo, void* out_f32,
                    const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, void* ws,
                    void* tickets, void* status, cudaStream_t st) {
-  if (M < 1 || N % 128 || K % 256 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64) return cudaErrorInvalidValue;
-  if (ks <= 0) ks = ve_decode_w4a4_splits(N, K);
+  if (M < 1 || N % 128 || K % 256 || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
+    return cudaErrorInvalidValue;
+  if (ks < 1) ks = 1;
   if (ks > K / 256) ks = K / 256;
   if (ks > 1 && (!ws || !tickets)) return cudaErrorInvalidValue;
   const int cols = M * terms, bn = cols <= 16 ? 16 : cols <= 32 ? 32 : 64;
-  CUtensorMap amap, bmap;
+  CUtensorMap amap;
   int rc = make_tmap_2d(&amap, Wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, (uint64_t)K / 2, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  rc = make_tmap_2d(&bmap, Xp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, cols, K / 2, (uint64_t)K / 2, bn, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc) return rc;
-  DecodeParams p{N, M, K, alpha, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)residual, ldr, (float*)out_f32,
-                 (const uint8_t*)sfa, (const uint8_t*)sfb, (float*)ws, (int*)tickets, (int*)status};
-#define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, bmap, ks, pdl, st)
+  int tpt = 16;
+  while (tpt < 16 * M && tpt < 128) tpt <<= 1;
+  DecodeParams p{N, M, K, alpha, (const __nv_bfloat16*)X, ldx, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)residual, ldr,
+                 (float*)out_f32, (const uint8_t*)sfa, (float*)ws, (int*)tickets, (int*)status, tpt};
+#define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, ks, pdl, st)
   if (terms == 4) { if (bn == 16) VE_DW(16, 4, 4); if (bn == 32) VE_DW(32, 4, 4); VE_DW(64, 4, 3); }
   if (terms == 2) { if (bn == 16) VE_DW(16, 2, 4); if (bn == 32) VE_DW(32, 2, 4); VE_DW(64, 2, 3); }
   if (bn == 16) VE_DW(16, 1, 4);

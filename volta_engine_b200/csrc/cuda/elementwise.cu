@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                       float wbias, long x_stride, long out_stride) {
   __shared__ float red[33];
   extern __shared__ float rowbuf[];  // H floats
+  grid_dep_launch();                 // a decode linear behind this kernel may set up and prefetch weights now
   const long row = blockIdx.x;
   const __nv_bfloat16* xr = x ? x + row * x_stride : nullptr;
   float ss = 0.f;
@@ -200,6 +201,7 @@ VE_DEVINL float act_gelu_tanh(float g) {
 
 __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long rows,
                                  int I, int act, float limit) {
+  grid_dep_launch();
   const long n8 = rows * (long)(I / 8);
   for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n8; idx += (long)gridDim.x * blockDim.x) {
     const long r = idx / (I / 8);

@@ -339,23 +339,21 @@ def nvfp4_expand_rows(x, terms=DW_TERMS):
 DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
 
 
-def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None,
-                expanded=None, pdl=None):
-    """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path with activations expanded
-    into ``terms`` residual NVFP4 rows (bf16-grade accuracy): out [M, N]."""
+def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None):
+    """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path; the kernel expands each bf16
+    activation row into ``terms`` residual NVFP4 rows itself (bf16-grade accuracy): out [M, N]."""
     N, K = packed.shape[0], packed.shape[1] * 2
     M = x.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     f32 = out.dtype == torch.float32
-    xpv, xs = expanded if expanded is not None else nvfp4_expand_rows(x, terms)
     _, _, ws, tickets = dw_scratch(x.device)
     if ks is None:
         ks = dw_splits(N, K)
     assert ks * (N // 128) <= 1024
     if pdl is None:
-        pdl = DW_PDL and expanded is None      # the expansion kernel right in front releases this launch early
-    call("decode_w4a4", "pppp" + "plppl" + "iiifiii" + "ppp", ptr(packed), ptr(sf_atoms), ptr(xpv), ptr(xs),
+        pdl = DW_PDL
+    call("decode_w4a4", "pppl" + "plppl" + "iiifiii" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
          0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
          residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,
          ptr(ws), ptr(tickets), ptr(status_word(x.device)))

@@ -128,6 +128,11 @@ class VoltaServer:
                 msgs[0] = dict(msgs[0], content=msgs[0]["content"] + "\n\n" + m["content"])
             else:
                 msgs.append(m)
+        if self.template is None or self.model_type in ("deepseek_v4", "deepseek_v41", "deepseek41"):
+            # these models ship no chat template: their prompt format is built in
+            from ..loader import deepseek_encoding as ds
+            return ds.encode(msgs, cr.tools or None, thinking=bool(extra.get("enable_thinking", True)),
+                             reasoning_effort=str(getattr(cr, "reasoning_effort", "") or ""))
         return self.template.apply(msgs, tools=cr.tools, add_generation_prompt=True, **extra)
 
     def _parse(self, req: HttpRequest, proto: str) -> ChatRequest:
