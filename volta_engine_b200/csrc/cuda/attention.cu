@@ -68,6 +68,7 @@ template <int HD, int NW>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
   grid_dep_launch();
+  grid_dep_wait();
   constexpr int TILE_BYTES = kPageTok * HD * 2;
   constexpr int NCH = HD / 64;   // 128-byte column chunks per row
   constexpr int KSTEPS = HD / 16;
@@ -289,6 +290,7 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
                                    const __nv_bfloat16* __restrict__ gate, long gate_stride, const int* __restrict__ slot,
                                    int nq, int nsplit, int HD) {
   grid_dep_launch();
+  grid_dep_wait();
   const int row = blockIdx.x / nq, head = blockIdx.x % nq, d = threadIdx.x;
   if (slot && slot[row] < 0) return;
   const long base = ((long)row * nq + head) * nsplit;
@@ -317,7 +319,7 @@ static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUten
     attr_set = true;
   }
   dim3 grid(ntiles, p.nkv, p.nsplit);
-  attn_kernel<HD, NW><<<grid, NW * 32, smem, st>>>(p, kmap, vmap);
+  launch_pdl(attn_kernel<HD, NW>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
   return (int)cudaGetLastError();
 }
 
@@ -374,9 +376,8 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
 #undef VE_ATTN
   if (rc) return rc;
   if (nsplit > 1) {
-    attn_reduce_kernel<<<rows * nq, hd, 0, st>>>((const float*)o_part, (const float*)lse_part, (__nv_bfloat16*)out,
-                                                 out_stride, (const __nv_bfloat16*)gate, gate_stride,
-                                                 (const int*)slot, nq, nsplit, hd);
+    launch_pdl(attn_reduce_kernel, dim3(rows * nq), dim3(hd), 0, st, (const float*)o_part, (const float*)lse_part,
+               (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, (const int*)slot, nq, nsplit, hd);
     rc = (int)cudaGetLastError();
   }
   return rc;

@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define VE_DEVINL __device__ __forceinline__
 
@@ -101,6 +102,26 @@ VE_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // its prologue now (no-op when the next kernel in the stream is a normal launch).
 VE_DEVINL void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 VE_DEVINL void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host side: launch with programmatic stream serialization, so the kernel's launch and set-up overlap the kernel in
+// front of it. Kernels launched this way call grid_dep_wait() before they touch memory written by earlier kernels.
+// VOLTA_PDL=0 turns every such launch into a plain one.
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("VOLTA_PDL"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v != 0;
+}
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 VE_DEVINL uint64_t globaltimer_ns() {
   uint64_t t;

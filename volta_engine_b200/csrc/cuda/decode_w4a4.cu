@@ -168,6 +168,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
   const int tpt = p.tpt;
 
   auto stage_ptr = [&](int s) { return smem + (size_t)s * STAGE_BYTES; };   // [A][B][SFA][SFB]
+  grid_dep_launch();                              // the kernel behind this one may be scheduled now
   if (threadIdx.x == 0) {
     // a stage is full after the TMA bytes (one arrive.expect_tx) and the tpt activation writers have arrived
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1 + tpt); mbar_init(&empty[s], 1); }

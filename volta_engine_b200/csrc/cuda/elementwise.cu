@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                       float wbias, long x_stride, long out_stride) {
   __shared__ float red[33];
   extern __shared__ float rowbuf[];  // H floats
-  grid_dep_launch();                 // a decode linear behind this kernel may set up and prefetch weights now
+  grid_dep_launch();                 // the kernel behind this one may be scheduled and set up now
+  grid_dep_wait();                   // inputs come from the kernel in front
   const long row = blockIdx.x;
   const __nv_bfloat16* xr = x ? x + row * x_stride : nullptr;
   float ss = 0.f;
@@ -112,6 +113,8 @@ __global__ void rmsnorm_heads_kernel(__nv_bfloat16* __restrict__ x, const __nv_b
 // ------------------------------------------------------------------------------------------------
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int H, int vocab, float scale) {
+  grid_dep_launch();
+  grid_dep_wait();
   const long row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -144,6 +147,8 @@ __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __
                                   const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
                                   __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nq,
                                   int nkv, int hd, int rot_dim, float theta, int interleaved, float pos_scale) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int row = blockIdx.x, head = blockIdx.y;
   const int p = pos[row];
   const int s = slot ? slot[row] : 0;
@@ -202,6 +207,7 @@ VE_DEVINL float act_gelu_tanh(float g) {
 __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long rows,
                                  int I, int act, float limit) {
   grid_dep_launch();
+  grid_dep_wait();
   const long n8 = rows * (long)(I / 8);
   for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n8; idx += (long)gridDim.x * blockDim.x) {
     const long r = idx / (I / 8);
@@ -253,9 +259,9 @@ int ve_rmsnorm(const void* x, void* res, int res_f32, const void* w, void* out, 
                float wbias, long x_stride, long out_stride, cudaStream_t st) {
   if (H % 8) return cudaErrorInvalidValue;
   if (rows <= 0) return 0;
-  rmsnorm_kernel<8><<<rows, 256, H * sizeof(float), st>>>((const __nv_bfloat16*)x, res, res_f32,
-                                                         (const __nv_bfloat16*)w, (__nv_bfloat16*)out, H, eps,
-                                                         wbias, x_stride ? x_stride : H, out_stride ? out_stride : H);
+  launch_pdl(rmsnorm_kernel<8>, dim3(rows), dim3(256), H * sizeof(float), st, (const __nv_bfloat16*)x, res, res_f32,
+             (const __nv_bfloat16*)w, (__nv_bfloat16*)out, H, eps, wbias, x_stride ? x_stride : (long)H,
+             out_stride ? out_stride : (long)H);
   VE_CHECK_LAUNCH();
 }
 
@@ -272,8 +278,8 @@ int ve_embed(const void* ids, const void* table, void* out, int rows, int H, int
              cudaStream_t st) {
   if (H % 8) return cudaErrorInvalidValue;
   if (rows <= 0) return 0;
-  embed_kernel<<<rows, 128, 0, st>>>((const int*)ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, H, vocab,
-                                     scale);
+  launch_pdl(embed_kernel, dim3(rows), dim3(128), 0, st, (const int*)ids, (const __nv_bfloat16*)table,
+             (__nv_bfloat16*)out, H, vocab, scale);
   VE_CHECK_LAUNCH();
 }
 
@@ -283,10 +289,9 @@ int ve_rope_store(void* qkv, const void* pos, const void* slot, const void* page
   if (hd % 2 || rot_dim % 2 || rot_dim > hd || hd / 2 > 1024) return cudaErrorInvalidValue;
   if (rows <= 0) return 0;
   dim3 grid(rows, nq + nkv);
-  rope_store_kernel<<<grid, hd / 2, 0, st>>>((__nv_bfloat16*)qkv, (const int*)pos, (const int*)slot,
-                                             (const int*)page_table, max_pages, (__nv_bfloat16*)kpool,
-                                             (__nv_bfloat16*)vpool, nq, nkv, hd, rot_dim, theta, interleaved,
-                                             pos_scale);
+  launch_pdl(rope_store_kernel, grid, dim3(hd / 2), 0, st, (__nv_bfloat16*)qkv, (const int*)pos, (const int*)slot,
+             (const int*)page_table, max_pages, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, nq, nkv, hd, rot_dim,
+             theta, interleaved, pos_scale);
   VE_CHECK_LAUNCH();
 }
 
@@ -295,7 +300,8 @@ int ve_gated_act(const void* gu, void* out, long rows, int I, int act, float lim
   if (rows <= 0) return 0;
   const long n8 = rows * (long)(I / 8);
   const int blocks = (int)((n8 + 255) / 256 < 148 * 8 ? (n8 + 255) / 256 : 148 * 8);
-  gated_act_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, I, act, limit);
+  launch_pdl(gated_act_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, I,
+             act, limit);
   VE_CHECK_LAUNCH();
 }
 

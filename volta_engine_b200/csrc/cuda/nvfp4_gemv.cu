@@ -47,6 +47,8 @@ nvfp4_gemv_kernel(const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ Ws
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = blockIdx.x * kGemvRows;
   __shared__ float part[kGemvWarps][kGemvRows][MR];
+  grid_dep_launch();
+  grid_dep_wait();
   const int kchunks = K >> 5;  // 32-element (16 B) chunks per row
   float acc[kGemvRows][MR];
 #pragma unroll
@@ -232,8 +234,8 @@ int ve_bf16_gemv_f32(const void* W, const void* x, long x_stride, void* out, lon
   while (m0 < M) {
     const int left = M - m0;
 #define VE_LAUNCH(MR)                                                                                        \
-  bf16_gemv_f32_kernel<MR><<<blocks, kGemvWarps * 32, 0, st>>>((const __nv_bfloat16*)W, (const __nv_bfloat16*)x, \
-                                                               x_stride, (float*)out, out_stride, M, N, K, m0)
+  launch_pdl(bf16_gemv_f32_kernel<MR>, dim3(blocks), dim3(kGemvWarps * 32), 0, st, (const __nv_bfloat16*)W, \
+             (const __nv_bfloat16*)x, x_stride, (float*)out, out_stride, M, N, K, m0)
     if (left >= 4) {
       VE_LAUNCH(4);
       m0 += 4;

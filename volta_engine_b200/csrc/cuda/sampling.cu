@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 __global__ void __launch_bounds__(256) argmax_part_kernel(const float* __restrict__ logits, long stride, int V,
                                                           float* __restrict__ pval, int* __restrict__ pidx) {
   __shared__ ArgVal red[33];
+  grid_dep_launch();
+  grid_dep_wait();
   const float* row = logits + blockIdx.x * stride;
   const int nb = gridDim.y, per = (V + nb - 1) / nb;
   const int lo = blockIdx.y * per, hi = min(V, lo + per);
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(256) argmax_part_kernel(const float* __restric
 __global__ void __launch_bounds__(64) argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
                                                           int nb, int id_offset, int* __restrict__ idx,
                                                           float* __restrict__ val) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ ArgVal red[33];
   ArgVal a{-FLT_MAX, 0x7fffffff};
   for (int i = threadIdx.x; i < nb; i += blockDim.x) a = better(a, ArgVal{pval[blockIdx.x * nb + i], pidx[blockIdx.x * nb + i]});
@@ -135,8 +139,9 @@ int ve_argmax2(const void* logits, long stride, int rows, int V, int id_offset, 
                void* pidx, int nb, cudaStream_t st) {
   if (rows <= 0) return 0;
   dim3 grid(rows, nb);
-  argmax_part_kernel<<<grid, 256, 0, st>>>((const float*)logits, stride, V, (float*)pval, (int*)pidx);
-  argmax_final_kernel<<<rows, 64, 0, st>>>((const float*)pval, (const int*)pidx, nb, id_offset, (int*)idx, (float*)val);
+  launch_pdl(argmax_part_kernel, grid, dim3(256), 0, st, (const float*)logits, stride, V, (float*)pval, (int*)pidx);
+  launch_pdl(argmax_final_kernel, dim3(rows), dim3(64), 0, st, (const float*)pval, (const int*)pidx, nb, id_offset,
+             (int*)idx, (float*)val);
   VE_CHECK_LAUNCH();
 }
 
