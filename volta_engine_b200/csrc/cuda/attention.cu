@@ -64,7 +64,10 @@ VE_DEVINL uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
-template <int HD, int NW>
+// KS (key-split, decode / verify tiles of <= 16 packed rows): all NW warps work on the same 16 rows and each takes
+// its own 16-key slice of every 64-key page, so a page costs a quarter of the per-warp work; the warps' softmax
+// states are merged through shared memory at the end.
+template <int HD, int NW, bool KS>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
   grid_dep_launch();
@@ -106,7 +109,7 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   bool r_ok[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + g + h * 8;
+    const int r = (KS ? 0 : warp * 16) + g + h * 8;
     r_ok[h] = r < count * G;
     const int rr = r_ok[h] ? r : 0;
     r_tok[h] = first + rr / G;
@@ -166,16 +169,18 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
     const uint32_t kb = smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
 
     // S = Q K^T  (16 rows x 64 keys per warp)
-    float sacc[8][4];
+    constexpr int NP = KS ? 1 : 4;           // 16-key slices this warp scores per page
+    const int key0 = KS ? warp * 16 : 0;     // first key of the warp's slice inside the page
+    float sacc[2 * NP][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+    for (int i = 0; i < 2 * NP; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
       const int c = (kk * 16) / 64, ci = ((kk * 16) % 64) / 8;
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {
+      for (int np = 0; np < NP; ++np) {
         const int mi = lane >> 3, rr = lane & 7;
-        const int key = np * 16 + (mi >> 1) * 8 + rr;
+        const int key = key0 + np * 16 + (mi >> 1) * 8 + rr;
         const int ch = ci + (mi & 1);
         uint32_t b0, b1, b2, b3;
         ldsm_x4(kb + c * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
@@ -186,11 +191,11 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
     // mask + online softmax
     float mx[2] = {-FLT_MAX, -FLT_MAX};
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 2 * NP; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        const int key = kt * kPageTok + nt * 8 + 2 * t + (e & 1);
+        const int key = kt * kPageTok + key0 + nt * 8 + 2 * t + (e & 1);
         const bool allow = r_ok[h] && key <= r_lim[h] && (p.window <= 0 || key > r_pos[h] - p.window);
         const float v = allow ? sacc[nt][e] * p.scale_log2 : -FLT_MAX;
         sacc[nt][e] = v;
@@ -207,9 +212,9 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
       m_run[h] = m_new;
       l_run[h] *= corr[h];
     }
-    uint32_t pf[4][4];  // P as A fragments for 4 k-steps of 16 keys
+    uint32_t pf[NP][4];  // P as A fragments, one k-step of 16 keys per slice
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 2 * NP; ++nt) {
       float pv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -230,11 +235,11 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
     }
     // O += P V
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
+    for (int ks = 0; ks < NP; ++ks) {
 #pragma unroll
       for (int dp = 0; dp < HD / 16; ++dp) {
         const int mi = lane >> 3, rr = lane & 7;
-        const int key = ks * 16 + (mi & 1) * 8 + rr;
+        const int key = key0 + ks * 16 + (mi & 1) * 8 + rr;
         const int d = dp * 16 + (mi >> 1) * 8;
         const int c = d / 64, ch = (d % 64) / 8;
         uint32_t b0, b1, b2, b3;
@@ -253,6 +258,51 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   for (int h = 0; h < 2; ++h) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  if (KS) {
+    // merge the warps' (m, l, O) states; the page buffers are free now
+    __syncthreads();
+    float* ms = reinterpret_cast<float*>(smem);   // [NW][16]
+    float* ls = ms + NW * 16;                       // [NW][16]
+    float* os = ls + NW * 16;                       // [NW][16][HD]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = g + h * 8;
+      if (t == 0) { ms[warp * 16 + row] = m_run[h]; ls[warp * 16 + row] = l_run[h]; }
+#pragma unroll
+      for (int nt = 0; nt < NT_O; ++nt)
+        *reinterpret_cast<float2*>(os + (size_t)(warp * 16 + row) * HD + nt * 8 + 2 * t) =
+            make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+    }
+    __syncthreads();
+    const int nrows = count * G;
+    for (int idx = tid; idx < nrows * HD; idx += NW * 32) {
+      const int row = idx / HD, d = idx % HD;
+      float m = -FLT_MAX;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) m = fmaxf(m, ms[w * 16 + row]);
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float mw = ms[w * 16 + row];
+        if (mw != -FLT_MAX) {
+          const float c = exp2f(mw - m);
+          acc += os[(size_t)(w * 16 + row) * HD + d] * c;
+          l += ls[w * 16 + row] * c;
+        }
+      }
+      const int tok = first + row / G, head = kvh * G + row % G;
+      float v = l > 0.f ? acc / l : 0.f;
+      if (p.nsplit == 1) {
+        if (p.gate) v *= 1.f / (1.f + __expf(-bf2f(p.gate[(long)tok * p.gate_stride + (long)head * HD + d])));
+        p.out[(long)tok * p.out_stride + (long)head * HD + d] = f2bf(v);
+      } else {
+        const long base = ((long)tok * p.nq + head) * p.nsplit + z;
+        p.o_part[base * HD + d] = v;
+        if (d == 0) p.lse_part[base] = l > 0.f ? m + log2f(l) : -FLT_MAX;
+      }
+    }
+    return;
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -308,18 +358,18 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
   out[(long)row * out_stride + (long)head * HD + d] = f2bf(v);
 }
 
-template <int HD, int NW>
+template <int HD, int NW, bool KS>
 static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
                        cudaStream_t st) {
   constexpr int smem = 2 * 2 * kPageTok * HD * 2 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   dim3 grid(ntiles, p.nkv, p.nsplit);
-  launch_pdl(attn_kernel<HD, NW>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
+  launch_pdl(attn_kernel<HD, NW, KS>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
   return (int)cudaGetLastError();
 }
 
@@ -329,7 +379,8 @@ using namespace ve;
 
 extern "C" {
 
-// rows_per_tile_warps: 1 (decode / verify: <= 16 packed rows per tile) or 4 (prefill: <= 64 packed rows).
+// warps: 1 (decode / verify: <= 16 packed rows per tile, one warp), 104 (same tiles, four warps that split the
+// keys of every page) or 4 (prefill: <= 64 packed rows, 16 per warp).
 int ve_attention(const void* q, long q_stride, void* out, long out_stride, const void* gate, long gate_stride,
                  void* o_part, void* lse_part, const void* pos, const void* slot, const void* key_end,
                  const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
@@ -369,8 +420,9 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   if (rc) return rc;
 #define VE_ATTN(HD_)                                                             \
   if (hd == HD_) {                                                               \
-    rc = warps == 1 ? launch_attn<HD_, 1>(p, kmap, vmap, ntiles, st)             \
-                    : launch_attn<HD_, 4>(p, kmap, vmap, ntiles, st);            \
+    rc = warps == 1     ? launch_attn<HD_, 1, false>(p, kmap, vmap, ntiles, st)  \
+         : warps == 104 ? launch_attn<HD_, 4, true>(p, kmap, vmap, ntiles, st)   \
+                        : launch_attn<HD_, 4, false>(p, kmap, vmap, ntiles, st); \
   } else
   VE_ATTN(64) VE_ATTN(128) VE_ATTN(256) { return cudaErrorInvalidValue; }
 #undef VE_ATTN

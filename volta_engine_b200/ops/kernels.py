@@ -114,6 +114,10 @@ def add_(a, b):
 
 
 # ---------------------------------------------------------------------------------------------- attention
+# decode / verify tiles: 104 = four warps that split the keys of every page (default), 1 = one warp per tile
+ATTN_DECODE_WARPS = 1 if os.environ.get("VOLTA_ATTN_DECODE", "ksplit") == "1warp" else 104
+
+
 class AttnWorkspace:
     """Split-KV partial buffers, allocated once (stable pointers for CUDA-graph replay)."""
 
@@ -141,7 +145,7 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
         out = torch.empty(rows, nq * hd, dtype=q.dtype, device=q.device)
     if tiles is None:
         tf = tc = None
-        ntiles, warps = rows, 1
+        ntiles, warps = rows, ATTN_DECODE_WARPS
     else:
         tf, tc, ntiles = tiles
         warps = 4

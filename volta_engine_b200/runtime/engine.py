@@ -8,6 +8,8 @@ never depends on host arguments; attention grids are position independent.
 """
 from __future__ import annotations
 
+import os
+
 import time
 from dataclasses import dataclass
 
@@ -70,7 +72,7 @@ class Engine:
         self.s_cand_vals = torch.zeros(R, NUM_CANDIDATES, dtype=torch.float32, device=dev)
         self.s_cand_lse = torch.zeros(R, dtype=torch.float32, device=dev)
         self.graphs: dict[tuple, _Graph] = {}
-        self.nsplit_cap = 32
+        self.nsplit_cap = int(os.environ.get("VOLTA_NSPLIT_CAP", "32"))   # most key splits of a decode row
         if self.cuda:
             model.ensure_workspace(R, self.nsplit_cap)
 
