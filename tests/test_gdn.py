@@ -1,0 +1,100 @@
+"""Gated DeltaNet mixer and the hybrid model: oracle properties on CPU, CUDA kernels against the oracle."""
+import pytest
+import torch
+
+from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+from volta_engine_b200.ops.gdn import GDNDims, GDNState, gdn_forward, gdn_reference
+from volta_engine_b200.runtime.engine import Engine
+from volta_engine_b200.runtime.kv_cache import PagedKVCache
+
+
+def _params(d, g):
+    return dict(conv_w=torch.randn(d.conv_dim, d.conv_k, generator=g) * 0.5,
+                A_log=torch.log(torch.linspace(1.0, 4.0, d.n_v)), dt_bias=torch.linspace(-1, 1, d.n_v),
+                norm_w=torch.rand(d.dv, generator=g) + 0.5)
+
+
+def test_oracle_chunking_and_slot_independence():
+    d = GDNDims(n_k=2, n_v=4, dk=64, dv=64, conv_k=4)
+    g = torch.Generator().manual_seed(0)
+    P = _params(d, g)
+    T = 9
+    proj = (torch.randn(T, d.proj_out, generator=g)).to(torch.bfloat16)
+    pos = torch.arange(T, dtype=torch.int32)
+    whole = gdn_reference(proj, pos, torch.zeros(T, dtype=torch.int32), GDNState(d, 2, "cpu"), d, eps=1e-6, **P)
+    st = GDNState(d, 2, "cpu")
+    parts = [gdn_reference(proj[a:b], pos[a:b], torch.ones(b - a, dtype=torch.int32), st, d, eps=1e-6, **P)
+             for a, b in ((0, 4), (4, 5), (5, 9))]
+    assert torch.allclose(torch.cat(parts), whole, atol=1e-5)
+    # two slots interleaved in one batch behave like two separate sequences
+    st2 = GDNState(d, 2, "cpu")
+    both = gdn_reference(torch.cat([proj[:3], proj[:3]]), torch.tensor([0, 1, 2, 0, 1, 2], dtype=torch.int32),
+                         torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32), st2, d, eps=1e-6, **P)
+    assert torch.allclose(both[:3], whole[:3], atol=1e-5) and torch.allclose(both[3:], whole[:3], atol=1e-5)
+    # a new sequence in a used slot starts from zero state
+    again = gdn_reference(proj[:3], pos[:3], torch.zeros(3, dtype=torch.int32), st2, d, eps=1e-6, **P)
+    assert torch.allclose(again, whole[:3], atol=1e-5)
+
+
+def test_hybrid_model_prefill_equals_decode_on_cpu():
+    cfg = HybridConfig.tiny_hybrid()
+    m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+    assert m.kv_layers == 2 and [L.gdn is not None for L in m.layers] == [True, False, True, False]
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    out, _ = Engine(m, kv, use_graphs=False, prefill_chunk=16).generate(prompt, 5)
+    m.gdn_states = None
+    kv2 = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    nxt = Engine(m, kv2, use_graphs=False, prefill_chunk=1000).prefill(0, prompt + out[:3])
+    assert nxt == out[3]
+
+
+@pytest.mark.gpu
+def test_gpu_gdn_matches_oracle():
+    dev = torch.device("cuda:0")
+    for d in (GDNDims(2, 4, 64, 64, 4), GDNDims(2, 4, 128, 128, 4)):
+        g = torch.Generator().manual_seed(1)
+        P = _params(d, g)
+        Pg = {k: v.float().to(dev).contiguous() for k, v in P.items()}
+        # batch 1: slot 1 rows 0..5 and slot 0 rows 0..2; batch 2 continues both (state carried), batch 3 restarts slot 1
+        batches = [([0, 1, 2, 3, 4, 5, 0, 1, 2], [1] * 6 + [0] * 3), ([6, 3], [1, 0]), ([0, 1, 4], [1, 1, 0])]
+        st_c, st_g = GDNState(d, 3, "cpu"), GDNState(d, 3, dev)
+        for pos, slot in batches:
+            n = len(pos)
+            proj = torch.randn(n, d.proj_out, generator=g).to(torch.bfloat16)
+            pt, sl = torch.tensor(pos, dtype=torch.int32), torch.tensor(slot, dtype=torch.int32)
+            ref = gdn_reference(proj, pt, sl, st_c, d, eps=1e-6, **P)
+            out = gdn_forward(proj.to(dev), pt.to(dev), sl.to(dev), st_g, d, eps=1e-6, **Pg).float().cpu()
+            assert torch.allclose(out, ref, atol=2e-2, rtol=2e-2), float((out - ref).abs().max())
+            assert torch.allclose(st_g.rec.cpu(), st_c.rec, atol=1e-3, rtol=1e-3)
+            assert torch.allclose(st_g.conv.cpu(), st_c.conv, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_gpu_hybrid_model_generates_and_matches_whole_prefill():
+    dev = torch.device("cuda:0")
+    cfg = HybridConfig.tiny_hybrid()
+    m = HybridModel(cfg, dev).init_random(seed=0, search=False)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (150,), generator=g).tolist()
+    kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, dev)
+    eng = Engine(m, kv, use_graphs=True, prefill_chunk=64)
+    t1 = eng.prefill(0, prompt)
+    h1 = m.last_hidden[-1].float().cpu()
+    out, _ = eng.generate(prompt, 8, slot=1)
+    m.gdn_states = None
+    kv2 = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, dev)
+    t2 = Engine(m, kv2, use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
+    h2 = m.last_hidden[-1].float().cpu()
+    cos = torch.nn.functional.cosine_similarity(h1, h2, dim=0)
+    assert cos > 0.995, float(cos)            # chunked and whole prefill agree up to attention tile rounding
+    assert len(out) == 8 and out[0] == t1
+    # the CPU oracle sees the same last hidden state
+    from volta_engine_b200.models.util import to_device
+    mc = to_device(m, "cpu")
+    mc.gdn_states = None
+    kvc = PagedKVCache(mc.kv_layers, mc.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    Engine(mc, kvc, use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
+    cosc = torch.nn.functional.cosine_similarity(mc.last_hidden[-1].float(), h2, dim=0)
+    assert cosc > 0.98, float(cosc)

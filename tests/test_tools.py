@@ -52,3 +52,38 @@ def test_bench_serve_selftest():
     assert rep["selftest"] == "pass", rep
     assert rep["failed"] == 0 and rep["req_per_s"] > 0 and rep["tok_per_s"] > 0
     assert bench_serve.percentile([1, 2, 3, 4, 5], 0.5) == 3 and bench_serve.percentile([], 0.9) == 0.0
+
+
+def test_quantize_tool_round_trip(tmp_path):
+    import torch
+    from volta_engine_b200.models.dense import DenseConfig
+    from volta_engine_b200.models.factory import load_model, save_dense_checkpoint
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.tools.quantize import plan, quantize_dir
+    from volta_engine_b200.loader.safetensors import SafeTensorsRepo
+    cfg = DenseConfig(n_layers=1, hidden=128, n_q=2, n_kv=1, head_dim=64, ffn=256, vocab=300, qk_norm=True)
+    src = tmp_path / "src"
+    save_dense_checkpoint(src, cfg, seed=3, fmt="bf16", std=0.05)
+    pl = plan(SafeTensorsRepo(src), "nvfp4", min_dim=64)
+    acts = pl["actions"]
+    assert acts["model.layers.0.mlp.down_proj.weight"] == "quantize" and acts["model.embed_tokens.weight"] == "copy"
+    assert acts["model.layers.0.input_layernorm.weight"] == "copy" and acts["lm_head.weight"] == "copy"
+    ref_model, _ = load_model(src, "cpu")
+    kv = PagedKVCache(1, 1, 64, 8, 1, 256, "cpu")
+    ref, _ = Engine(ref_model, kv, use_graphs=False, prefill_chunk=32).generate(list(range(24)), 3)
+    for fmt in ("nvfp4", "nvfp4_modelopt"):
+        dst = tmp_path / fmt
+        rep = quantize_dir(src, dst, fmt, min_dim=64, log=lambda *_: None)
+        assert rep["quantized"] == 7 and (dst / "config.json").exists() and (dst / "quantization_config.json").exists()
+        m, _ = load_model(dst, "cpu")
+        assert type(m.layers[0].down).__name__ == "LinearNVFP4"
+        kv2 = PagedKVCache(1, 1, 64, 8, 1, 256, "cpu")
+        out, _ = Engine(m, kv2, use_graphs=False, prefill_chunk=32).generate(list(range(24)), 3)
+        assert len(out) == 3
+    # the dequantised weights stay close to the source
+    w0 = ref_model.layers[0].down.weight.float()
+    wq = m.layers[0].down
+    from volta_engine_b200.quant import nvfp4 as qn
+    rel = (qn.dequantize_nvfp4(wq.packed, wq.scales, wq.gscale) - w0).norm() / w0.norm()
+    assert rel < 0.12

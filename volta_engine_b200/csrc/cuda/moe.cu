@@ -237,8 +237,11 @@ __global__ void __launch_bounds__(128) nvfp4_moe_gemv_kernel(const uint8_t* __re
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ d, long d_stride, const float* __restrict__ w,
                                    const int* __restrict__ ids, const int* __restrict__ inv, int e0, int e_local,
                                    const __nv_bfloat16* __restrict__ shared, long sh_stride,
+                                   const float* __restrict__ sh_gate, long sh_gate_stride,
                                    __nv_bfloat16* __restrict__ y, long y_stride, int topk, int H) {
   const int t = blockIdx.x;
+  // optional sigmoid gate of the shared expert: its logit is one extra column of the router product
+  const float sg = (shared && sh_gate) ? 1.f / (1.f + __expf(-sh_gate[(long)t * sh_gate_stride])) : 1.f;
   for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
     float acc[8];
 #pragma unroll
@@ -262,8 +265,8 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ d, long d_s
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __bfloat1622float2(v.v[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+        acc[2 * j] = fmaf(sg, f.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(sg, f.y, acc[2 * j + 1]);
       }
     }
     bf16x8 o;
@@ -381,12 +384,13 @@ int ve_nvfp4_moe_gemv(const void* Wp, const void* Ws, const void* gs, const void
 }
 
 int ve_moe_combine(const void* d, long d_stride, const void* w, const void* ids, const void* inv, int e0, int e_local,
-                   const void* shared, long sh_stride, void* y, long y_stride, int rows, int topk, int H, cudaStream_t st) {
+                   const void* shared, long sh_stride, const void* sh_gate, long sh_gate_stride, void* y, long y_stride,
+                   int rows, int topk, int H, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (H % 8) return cudaErrorInvalidValue;
   moe_combine_kernel<<<rows, 256, 0, st>>>((const __nv_bfloat16*)d, d_stride, (const float*)w, (const int*)ids,
                                            (const int*)inv, e0, e_local, (const __nv_bfloat16*)shared, sh_stride,
-                                           (__nv_bfloat16*)y, y_stride, topk, H);
+                                           (const float*)sh_gate, sh_gate_stride, (__nv_bfloat16*)y, y_stride, topk, H);
   VE_CHECK_LAUNCH();
 }
 

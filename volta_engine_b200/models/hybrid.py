@@ -1,0 +1,162 @@
+"""Hybrid decoder: Gated-DeltaNet linear-attention layers interleaved with gated full-attention layers (every
+``full_interval``-th layer), dense or mixture-of-experts FFN. Covers the Qwen3.5 / Qwen3-Next family shape:
+GDN layers keep a convolution state and a recurrent state per slot instead of KV pages; full layers use
+q/k RMSNorm, partial rotary embedding and a sigmoid output gate computed from the layer input.
+
+Reference: src/models/qwen3_5.cpp (48 GDN + 16 gated full-attention layers, MTP head), src/models/qwen4exp.cpp
+(GDN + sparse attention + routed experts), inc/engine/modules/gdn.h.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import kernels as K
+from ..ops.gdn import GDNDims, GDNState, gdn_forward
+from ..ops.linear import LinearBF16
+from ..runtime.batch import BatchRows
+from .moe import MoEConfig, MoELayer, MoEModel
+
+
+@dataclass
+class HybridConfig(MoEConfig):
+    full_interval: int = 4         # layers li with (li + 1) % full_interval == 0 are full attention
+    gdn_k_heads: int = 16
+    gdn_v_heads: int = 32
+    gdn_dk: int = 128
+    gdn_dv: int = 128
+    gdn_conv: int = 4
+    attn_gate: bool = True
+    model_type: str = "hybrid_gdn"
+
+    @classmethod
+    def baseline_next80b(cls):
+        """80B-A3B-class hybrid MoE: 48 layers (36 GDN + 12 gated attention), hidden 2048, 512 experts top-10."""
+        return cls(n_layers=48, hidden=2048, n_q=16, n_kv=2, head_dim=256, ffn=0, vocab=151936, n_experts=512, top_k=10,
+                   expert_ffn=512, shared_ffn=512, router="softmax", rot_dim=64, qk_norm=True, norm_bias=1.0,
+                   rope_theta=1e7)
+
+    @classmethod
+    def dense_27b(cls):
+        """27B-class hybrid with a dense FFN: 64 layers (48 GDN + 16 gated attention), hidden 5120, ffn 17408."""
+        return cls(n_layers=64, hidden=5120, n_q=24, n_kv=4, head_dim=256, ffn=17408, vocab=151936, n_experts=1, top_k=1,
+                   expert_ffn=128, shared_ffn=0, first_dense_layers=64, rot_dim=64, qk_norm=True, gdn_v_heads=48,
+                   norm_bias=1.0, rope_theta=1e7)
+
+    @classmethod
+    def tiny_hybrid(cls, **kw):
+        c = cls(n_layers=4, hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, vocab=1024, n_experts=8, top_k=2, expert_ffn=128,
+                shared_ffn=128, full_interval=2, gdn_k_heads=2, gdn_v_heads=4, gdn_dk=64, gdn_dv=64, rot_dim=32, qk_norm=True)
+        for k, v in kw.items():
+            setattr(c, k, v)
+        return c
+
+    def is_full(self, li: int) -> bool:
+        return (li + 1) % self.full_interval == 0
+
+
+class HybridLayer(MoELayer):
+    __slots__ = ("gdn", "gate_proj", "kv_index")
+
+
+class HybridModel(MoEModel):
+    layer_cls = HybridLayer
+
+    def __init__(self, cfg: HybridConfig, device, comm=None):
+        super().__init__(cfg, device, comm)
+        assert self.comm.size == 1, "the hybrid model runs on one GPU in this build"
+        self.dims = GDNDims(cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, cfg.gdn_conv)
+        self.n_full = sum(1 for li in range(cfg.n_layers) if cfg.is_full(li))
+        self.gdn_states: list[GDNState] | None = None
+        self._li = 0
+        self._scratch = None
+
+    @property
+    def kv_layers(self) -> int:
+        """KV-cache layers this model needs (only the full-attention layers hold keys and values)."""
+        return self.n_full
+
+    def init_random(self, seed: int = 4, std: float = 0.02, search: bool = False):
+        self._li = 0
+        super().init_random(seed, std, search)
+        cfg = self.cfg
+        if cfg.qk_norm:
+            for L in self.layers:
+                if L.gdn is None:
+                    L.q_norm = torch.ones(cfg.head_dim, device=self.device, dtype=torch.bfloat16) * (1.0 - cfg.norm_bias)
+                    L.k_norm = L.q_norm.clone()
+        return self
+
+    def _init_attention(self, L, rnd, search):
+        cfg, d, dev = self.cfg, self.dims, self.device
+        li = self._li
+        self._li += 1
+        L.gdn = L.gate_proj = None
+        L.kv_index = -1
+        if cfg.is_full(li):
+            super()._init_attention(L, rnd, search)
+            L.kv_index = sum(1 for j in range(li) if cfg.is_full(j))
+            if cfg.attn_gate:
+                L.gate_proj = self._make_linear(rnd(cfg.n_q * cfg.head_dim, cfg.hidden), search)
+            return
+        H = cfg.hidden
+        w_in = torch.zeros(d.proj_out, H, device=dev)
+        real = d.conv_dim + d.n_v * d.dv + 2 * d.n_v
+        w_in[:real] = rnd(real, H)
+        g = {"in_proj": self._make_linear(w_in, search),
+             "conv_w": (rnd(d.conv_dim, d.conv_k) * (0.5 / 0.02)).float().contiguous(),
+             "A_log": torch.log(torch.linspace(1.0, 8.0, d.n_v, device=dev)).float(),
+             "dt_bias": torch.linspace(-1.0, 1.0, d.n_v, device=dev).float(),
+             "norm_w": torch.ones(d.dv, device=dev, dtype=torch.float32),
+             "out_proj": self._make_linear(rnd(H, d.n_v * d.dv), search)}
+        L.gdn = g
+        L.qkv = L.o_proj = None
+
+    def _attn_bytes(self, L) -> int:
+        if L.gdn is not None:
+            return L.gdn["in_proj"].nbytes() + L.gdn["out_proj"].nbytes()
+        n = L.qkv.nbytes() + L.o_proj.nbytes()
+        return n + (L.gate_proj.nbytes() if L.gate_proj is not None else 0)
+
+    def state_bytes_per_slot(self) -> int:
+        d = self.dims
+        per = ((d.conv_k - 1) * d.conv_dim + d.n_v * d.dk * d.dv) * 4
+        return per * (self.cfg.n_layers - self.n_full)
+
+    def _states(self, kv):
+        if self.gdn_states is None:
+            self.gdn_states = [GDNState(self.dims, kv.max_slots, self.device) if L.gdn is not None else None
+                               for L in self.layers]
+        return self.gdn_states
+
+    def attn_block(self, li, L, x, b: BatchRows, kv, pbuf):
+        cfg = self.cfg
+        if L.gdn is not None:
+            g = L.gdn
+            proj = g["in_proj"].forward(x)
+            y = gdn_forward(proj, b.pos, b.slot, self._states(kv)[li], self.dims, g["conv_w"], g["A_log"], g["dt_bias"],
+                            g["norm_w"], cfg.rms_eps)
+            return g["out_proj"].forward(y.to(x.dtype), out=pbuf)
+        kpool, vpool = kv.layer(L.kv_index)
+        qkv = L.qkv.forward(x)
+        if cfg.qk_norm:
+            stride = qkv.stride(0)
+            K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
+            K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias, self.nq * self.hd)
+        K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
+                     cfg.rope_theta, cfg.rope_interleaved)
+        gate = L.gate_proj.forward(x) if L.gate_proj is not None else None
+        att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.scale,
+                          window=cfg.sliding_window, key_end=b.key_end, gate=gate, tiles=b.tiles,
+                          nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
+        return L.o_proj.forward(att, out=pbuf)
+
+    # recurrent state travels with sequence snapshots
+    def snapshot_state(self, slot: int) -> list:
+        return [s.snapshot(slot) if s is not None else None for s in (self.gdn_states or [])]
+
+    def restore_state(self, slot: int, snaps: list):
+        for s, snap in zip(self.gdn_states or [], snaps):
+            if s is not None and snap is not None:
+                s.restore(slot, snap)

@@ -34,6 +34,7 @@ class MoEConfig(DenseConfig):
     topk_group: int = 1
     first_dense_layers: int = 0    # leading layers with a dense FFN of width cfg.ffn
     router_bias_zipf: float = 0.0  # synthetic skew: expert bias ~ Zipf(s)
+    shared_gate: bool = False      # shared expert output scaled by sigmoid(x . w): one more row of the router weight
     model_type: str = "moe"
 
     @classmethod
@@ -95,7 +96,7 @@ def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | N
 
 
 class MoELayer(DenseLayer):
-    __slots__ = ("router", "router_bias", "bank", "shared_gu", "shared_dn", "dense_ffn")
+    __slots__ = ("router", "router_bias", "bank", "shared_gu", "shared_dn", "dense_ffn", "shared_gated")
 
 
 class MoEModel(DenseModel):
@@ -138,7 +139,8 @@ class MoEModel(DenseModel):
                 L.down = self._make_linear(wd[:, r * f:(r + 1) * f].contiguous(), search)
                 self.layers.append(L)
                 continue
-            L.router = LinearBF16(rnd(cfg.n_experts, H).to(torch.bfloat16))
+            L.shared_gated = bool(cfg.shared_gate and cfg.shared_ffn)
+            L.router = LinearBF16(rnd(cfg.n_experts + (1 if L.shared_gated else 0), H).to(torch.bfloat16))
             L.router_bias = None
             if cfg.router_bias_zipf > 0:
                 ranks = torch.arange(1, cfg.n_experts + 1, device=dev, dtype=torch.float32)
@@ -219,7 +221,9 @@ class MoEModel(DenseModel):
             if not getattr(self, "_shared_sliced", False) and self.comm.size > 1 and self.comm.rank != 0:
                 shared = None            # replicated shared expert: only one rank contributes it to the sum
         if not x.is_cuda:
-            return self._ffn_reference(L, x, logits, shared)
+            if getattr(L, "shared_gated", False) and shared is not None:
+                shared = (shared.float() * torch.sigmoid(logits[:, cfg.n_experts:cfg.n_experts + 1])).to(x.dtype)
+            return self._ffn_reference(L, x, logits[:, :cfg.n_experts], shared)
         bank = L.bank
         k = cfg.top_k
         ids = torch.empty(rows, k, dtype=torch.int32, device=x.device)
@@ -240,8 +244,11 @@ class MoEModel(DenseModel):
             inv = None
         else:
             d, inv = self._grouped(bank, x, ids, routes, k, act)
-        call("moe_combine", "plpppiiplpliii", ptr(d), d.stride(0), ptr(w), ptr(ids), ptr(inv), bank.e0, bank.e_local,
-             ptr(shared), shared.stride(0) if shared is not None else 0, ptr(y), y.stride(0), rows, k, H)
+        gate = logits[:, cfg.n_experts:] if getattr(L, "shared_gated", False) else None     # extra router column
+        call("moe_combine", "plpppiiplplpliii", ptr(d), d.stride(0), ptr(w), ptr(ids), ptr(inv), bank.e0, bank.e_local,
+             ptr(shared), shared.stride(0) if shared is not None else 0,
+             gate.data_ptr() if gate is not None else 0, logits.stride(0) if gate is not None else 0,
+             ptr(y), y.stride(0), rows, k, H)
         return y
 
     def _grouped(self, bank, x, ids, routes, k, act):

@@ -75,7 +75,11 @@ def _load_ffn(model, src, L, p, li, kw):
         L.gate_up = fuse_linears([src.linear(p + "mlp.gate_proj", "col", **kw), src.linear(p + "mlp.up_proj", "col", **kw)])
         L.down = src.linear(p + "mlp.down_proj", "row", **kw)
         return
-    L.router = LinearBF16(src.tensor(p + "mlp.gate.weight", dev, torch.bfloat16))
+    rw = src.tensor(p + "mlp.gate.weight", dev, torch.bfloat16)
+    L.shared_gated = src.has(p + "mlp.shared_expert_gate.weight")
+    if L.shared_gated:                      # the gate's logit rides as one more router row
+        rw = torch.cat([rw, src.tensor(p + "mlp.shared_expert_gate.weight", dev, torch.bfloat16).reshape(1, -1)], 0)
+    L.router = LinearBF16(rw.contiguous())
     L.router_bias = None
     if src.has(p + "mlp.gate.e_score_correction_bias"):
         L.router_bias = src.tensor(p + "mlp.gate.e_score_correction_bias", dev, torch.float32)
