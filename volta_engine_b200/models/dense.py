@@ -193,6 +193,11 @@ class DenseModel:
             d = self.ffn_block(li, L, x, b, pbuf)
             nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
             x = comm.allreduce_add_norm(d, h, nxt, cfg.rms_eps, cfg.norm_bias)
+            steer = getattr(self, "steer", None)
+            if steer is not None and not sp and steer.first <= li < steer.first + steer.layers:
+                # runtime steering edits the residual after this layer; the next layer's input is re-normalised
+                steer.apply(h, b.pos, b.slot, li)
+                x = K.rmsnorm(h, nxt, cfg.rms_eps, cfg.norm_bias, out=x)
         self.last_hidden, self.last_residual = x, h
         if b.logits == LOGITS_NONE:
             return None
