@@ -68,3 +68,27 @@ def test_native_build_present():
     from volta_engine_b200 import _build
     libs = _build.build_all()
     assert libs["kernels"].exists()
+
+
+def test_sandwich_norm_windowed_model_prefill_equals_decode():
+    """Gemma-style block: pre / post norms around both sub-layers, (1 + w) norm weights, alternating sliding-window and
+    full-attention layers with their own rotary base, GELU gate, scaled embedding, logit soft-cap."""
+    cfg = DenseConfig.tiny(n_layers=4, sandwich_norm=True, window_pattern=2, sliding_window=24, rope_theta_local=1e4,
+                           norm_bias=1.0, act="gelu_tanh", embed_scale=16.0, logit_softcap=30.0, qk_norm=True)
+    m = DenseModel(cfg, "cpu").init_random(seed=3, search=False)
+    assert [m.layer_window(i) for i in range(4)] == [24, 0, 24, 0]
+    assert m.layer_theta(0) == 1e4 and m.layer_theta(1) == cfg.rope_theta
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab, (90,), generator=g).tolist()
+    kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    out, _ = Engine(m, kv, use_graphs=False, prefill_chunk=32).generate(prompt, 5)
+    kv2 = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    nxt = Engine(m, kv2, use_graphs=False, prefill_chunk=1000).prefill(0, prompt + out[:3])
+    assert nxt == out[3]
+    # the window matters: the same weights without it give a different continuation state
+    cfg2 = DenseConfig.tiny(**{**cfg.to_dict(), "window_pattern": 0, "sliding_window": 0})
+    m2 = DenseModel(cfg2, "cpu").init_random(seed=3, search=False)
+    kv3 = PagedKVCache(cfg.n_layers, m2.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    Engine(m2, kv3, use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
+    Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu"), use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
+    assert not torch.allclose(m.last_hidden[-1].float(), m2.last_hidden[-1].float(), atol=1e-3)

@@ -40,6 +40,10 @@ class DenseConfig:
     tie_embeddings: bool = False
     embed_scale: float = 1.0
     sliding_window: int = 0
+    window_pattern: int = 0       # > 0: layers with (li + 1) % window_pattern == 0 attend to everything, the others
+                                  # only to the last ``sliding_window`` keys; 0: ``sliding_window`` on every layer
+    rope_theta_local: float = 0.0 # rotary base of the windowed layers (0 = rope_theta)
+    sandwich_norm: bool = False   # extra RMSNorm on the output of the attention and FFN blocks before the residual add
     attn_scale: float = 0.0       # 0 = 1/sqrt(head_dim)
     logit_softcap: float = 0.0
     quant: str = "nvfp4"          # nvfp4 | bf16
@@ -68,7 +72,8 @@ def _pad_to(n: int, m: int) -> int:
 
 
 class DenseLayer:
-    __slots__ = ("attn_norm", "qkv", "o_proj", "ffn_norm", "gate_up", "down", "q_norm", "k_norm")
+    __slots__ = ("attn_norm", "qkv", "o_proj", "ffn_norm", "gate_up", "down", "q_norm", "k_norm", "post_attn_norm",
+                 "post_ffn_norm")
 
 
 class DenseModel:
@@ -141,6 +146,9 @@ class DenseModel:
             L.down = self._make_linear(wd[:, r * self.ffn:(r + 1) * self.ffn].contiguous(), search)
             del wd
             L.attn_norm, L.ffn_norm = nw.clone(), nw.clone()
+            L.post_attn_norm = L.post_ffn_norm = None
+            if cfg.sandwich_norm:
+                L.post_attn_norm, L.post_ffn_norm = nw.clone(), nw.clone()
             L.q_norm = L.k_norm = None
             if cfg.qk_norm:
                 L.q_norm = torch.ones(hd, device=dev, dtype=torch.bfloat16) * (1.0 - cfg.norm_bias)
@@ -183,16 +191,16 @@ class DenseModel:
         x = K.rmsnorm(h, L0.attn_norm, cfg.rms_eps, cfg.norm_bias)
         # multi-GPU chunks: the residual stream is row-sharded over ranks (sequence-parallel) and the
         # row-parallel GEMMs write straight into the communicator's symmetric input region
-        sp = comm.size > 1 and b.n > 16
+        sp = comm.size > 1 and b.n > 16 and not cfg.sandwich_norm
         pbuf = comm.partial_buffer(b.n, cfg.hidden) if sp else None
         if sp:
             h = comm.shard_rows(h)
         for li, L in enumerate(self.layers):
             o = self.attn_block(li, L, x, b, kv, pbuf)
-            x = comm.allreduce_add_norm(o, h, L.ffn_norm, cfg.rms_eps, cfg.norm_bias)
+            x = self._add_norm(o, h, getattr(L, "post_attn_norm", None), L.ffn_norm)
             d = self.ffn_block(li, L, x, b, pbuf)
             nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
-            x = comm.allreduce_add_norm(d, h, nxt, cfg.rms_eps, cfg.norm_bias)
+            x = self._add_norm(d, h, getattr(L, "post_ffn_norm", None), nxt)
             steer = getattr(self, "steer", None)
             if steer is not None and not sp and steer.first <= li < steer.first + steer.layers:
                 # runtime steering edits the residual after this layer; the next layer's input is re-normalised
@@ -212,6 +220,26 @@ class DenseModel:
                 logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
         return logits
 
+    def _add_norm(self, part, h, post_norm, next_norm):
+        """h += sum over ranks of ``part`` (through ``post_norm`` first for sandwich-norm models); returns the next
+        block's input RMSNorm(h)."""
+        cfg, comm = self.cfg, self.comm
+        if post_norm is None:
+            return comm.allreduce_add_norm(part, h, next_norm, cfg.rms_eps, cfg.norm_bias)
+        full = comm.allreduce_(part) if comm.size > 1 else part
+        normed = K.rmsnorm(full, post_norm, cfg.rms_eps, cfg.norm_bias)
+        return K.rmsnorm(normed, next_norm, cfg.rms_eps, cfg.norm_bias, residual=h)
+
+    def layer_window(self, li: int) -> int:
+        cfg = self.cfg
+        if cfg.window_pattern > 0 and (li + 1) % cfg.window_pattern == 0:
+            return 0
+        return cfg.sliding_window
+
+    def layer_theta(self, li: int) -> float:
+        cfg = self.cfg
+        return cfg.rope_theta_local if cfg.rope_theta_local > 0 and self.layer_window(li) > 0 else cfg.rope_theta
+
     def attn_block(self, li, L, x, b: BatchRows, kv, pbuf):
         """Attention sub-layer: returns this rank's partial of the o_proj output [n, H]."""
         cfg = self.cfg
@@ -223,9 +251,9 @@ class DenseModel:
             K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
                              self.nq * self.hd)
         K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
-                     cfg.rope_theta, cfg.rope_interleaved)
+                     self.layer_theta(li), cfg.rope_interleaved)
         att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
-                          self.scale, window=cfg.sliding_window, key_end=b.key_end, tiles=b.tiles,
+                          self.scale, window=self.layer_window(li), key_end=b.key_end, tiles=b.tiles,
                           nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
         return L.o_proj.forward(att, out=pbuf)
 

@@ -35,10 +35,11 @@ def dense_config_from_hf(c: dict) -> DenseConfig:
         qk_norm=mt in ("qwen3", "qwen3_moe", "gemma3_text"), act="gelu_tanh" if gemma else "silu",
         tie_embeddings=bool(c.get("tie_word_embeddings", False)),
         embed_scale=float(c["hidden_size"]) ** 0.5 if gemma else 1.0,
-        sliding_window=int(c.get("sliding_window") or 0) if c.get("use_sliding_window", mt == "mistral") else 0,
+        sliding_window=int(c.get("sliding_window") or 0) if c.get("use_sliding_window", mt == "mistral" or gemma) else 0,
         attn_scale=float(c["query_pre_attn_scalar"]) ** -0.5 if c.get("query_pre_attn_scalar") else 0.0,
         logit_softcap=float(c.get("final_logit_softcapping") or 0.0), quant=c.get("volta_quant", "bf16"),
-        model_type=mt)
+        window_pattern=int(c.get("sliding_window_pattern") or (2 if mt == "gemma2" else 0)) if gemma else 0,
+        rope_theta_local=float(c.get("rope_local_base_freq") or 0.0), sandwich_norm=gemma, model_type=mt)
 
 
 class TensorSource:
@@ -127,7 +128,13 @@ def load_dense_weights(model: DenseModel, src: TensorSource, gemm_mode="w4a16", 
         L.gate_up = fuse_linears([src.linear(p + "mlp.gate_proj", "col", **kw), src.linear(p + "mlp.up_proj", "col", **kw)])
         L.down = src.linear(p + "mlp.down_proj", "row", **kw)
         L.attn_norm = src.tensor(p + "input_layernorm.weight", dev, bf)
-        L.ffn_norm = src.tensor(p + "post_attention_layernorm.weight", dev, bf)
+        L.post_attn_norm = L.post_ffn_norm = None
+        if cfg.sandwich_norm:      # pre / post norms around both blocks
+            L.post_attn_norm = src.tensor(p + "post_attention_layernorm.weight", dev, bf)
+            L.ffn_norm = src.tensor(p + "pre_feedforward_layernorm.weight", dev, bf)
+            L.post_ffn_norm = src.tensor(p + "post_feedforward_layernorm.weight", dev, bf)
+        else:
+            L.ffn_norm = src.tensor(p + "post_attention_layernorm.weight", dev, bf)
         L.q_norm = L.k_norm = None
         if cfg.qk_norm:
             L.q_norm = src.tensor(p + "self_attn.q_norm.weight", dev, bf)
