@@ -1,0 +1,67 @@
+"""Vision tower: patch positions in merge-block order, 2-D rope properties, CPU forward shapes, GPU vs CPU."""
+import numpy as np
+import pytest
+import torch
+
+from volta_engine_b200.loader.image import VisionParams, prepare_image
+from volta_engine_b200.models.util import to_device
+from volta_engine_b200.models.vision import VisionConfig, VisionTower, rope2d
+
+
+def test_patch_positions_follow_the_merge_block_order():
+    t = VisionTower(VisionConfig(), "cpu")
+    r, c = t.patch_positions(4, 6)
+    assert r[:4].tolist() == [0, 0, 1, 1] and c[:4].tolist() == [0, 1, 0, 1]          # first 2x2 block
+    assert r[4:8].tolist() == [0, 0, 1, 1] and c[4:8].tolist() == [2, 3, 2, 3]        # next block to the right
+    assert r[12:16].tolist() == [2, 2, 3, 3] and c[12:16].tolist() == [0, 1, 0, 1]    # first block of the second band
+    assert sorted(zip(r.tolist(), c.tolist())) == [(i, j) for i in range(4) for j in range(6)]
+
+
+def test_rope2d_is_a_rotation_that_depends_on_row_and_column():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(3, 2 * 64, generator=g)
+    zero = torch.zeros(3, dtype=torch.int32)
+    assert torch.allclose(rope2d(x.clone(), zero, zero, 2, 64, 1e4), x, atol=1e-6)
+    rows = torch.tensor([1, 5, 9], dtype=torch.int32)
+    y = rope2d(x.clone(), rows, zero, 2, 64, 1e4)
+    assert torch.allclose(y.reshape(3, 2, 64).norm(dim=-1), x.reshape(3, 2, 64).norm(dim=-1), atol=1e-4)
+    yh, xh = y.reshape(3, 2, 2, 32), x.reshape(3, 2, 2, 32)
+    assert not torch.allclose(yh[..., :16], xh[..., :16]) and torch.allclose(yh[..., 16:], xh[..., 16:], atol=1e-6)
+    # relative property: <rope(q, p), rope(k, p)> does not depend on p
+    q, k = torch.randn(1, 64, generator=g), torch.randn(1, 64, generator=g)
+    dots = []
+    for p in (0, 7):
+        pp = torch.tensor([p], dtype=torch.int32)
+        dots.append(float((rope2d(q.clone(), pp, pp, 1, 64, 1e4) * rope2d(k.clone(), pp, pp, 1, 64, 1e4)).sum()))
+    assert abs(dots[0] - dots[1]) < 1e-3
+
+
+def _image_patches():
+    rgb = np.random.default_rng(0).integers(0, 255, (96, 160, 3), dtype=np.uint8)
+    return prepare_image(rgb, VisionParams(patch_size=16, merge_size=2, min_pixels=1024, max_pixels=65536))
+
+
+def test_cpu_forward_shapes_and_determinism():
+    pre = _image_patches()
+    cfg = VisionConfig()
+    t = VisionTower(cfg, "cpu").init_random(seed=1)
+    out = t.forward(pre.patches, pre.grid_h, pre.grid_w)
+    assert out.shape == (pre.tokens(2), cfg.out_hidden) and torch.isfinite(out.float()).all()
+    assert torch.equal(out, t.forward(pre.patches, pre.grid_h, pre.grid_w))
+    # every patch influences every token (bidirectional attention): perturb the last patch, the first token moves
+    p2 = pre.patches.clone()
+    p2[-1] += 1.0
+    out2 = t.forward(p2, pre.grid_h, pre.grid_w)
+    assert not torch.allclose(out2[0].float(), out[0].float(), atol=1e-4)
+
+
+@pytest.mark.gpu
+def test_gpu_tower_matches_cpu():
+    pre = _image_patches()
+    cfg = VisionConfig(depth=2, hidden=128, heads=2, mlp=256, out_hidden=256)      # head_dim 64: the paged attention kernel
+    tc = VisionTower(cfg, "cpu").init_random(seed=2, std=0.05)
+    tg = to_device(tc, "cuda:0")
+    want = tc.forward(pre.patches, pre.grid_h, pre.grid_w).float()
+    got = tg.forward(pre.patches, pre.grid_h, pre.grid_w).float().cpu()
+    cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
+    assert cos > 0.998, float(cos)

@@ -67,12 +67,15 @@ VE_DEVINL uint32_t pack_bf16(float lo, float hi) {
 // KS (key-split, decode / verify tiles of <= 16 packed rows): all NW warps work on the same 16 rows and each takes
 // its own 16-key slice of every 64-key page, so a page costs a quarter of the per-warp work; the warps' softmax
 // states are merged through shared memory at the end.
-template <int HD, int NW, bool KS>
+// F8: the cache holds E5M2 bytes (half the traffic); pages land in a staging buffer and the CTA expands them to bf16
+// tiles in the layout the tensor-core loads expect, so the arithmetic is the same as for a bf16 cache.
+template <int HD, int NW, bool KS, bool F8>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
   grid_dep_launch();
   grid_dep_wait();
   constexpr int TILE_BYTES = kPageTok * HD * 2;
+  constexpr int T8 = kPageTok * HD;   // one E5M2 tile
   constexpr int NCH = HD / 64;   // 128-byte column chunks per row
   constexpr int KSTEPS = HD / 16;
   constexpr int NT_O = HD / 8;
@@ -128,6 +131,13 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   auto issue = [&](int kt, int stage) {
     const int page = p.page_table[(long)s * p.max_pages + kt];
     const int row = (page * p.nkv + kvh) * kPageTok;
+    if (F8) {
+      uint8_t* k8 = smem + stage * 2 * T8;
+      mbar_expect_tx(&full[stage], 2 * T8);
+      tma_load_2d(k8, &kmap, &full[stage], 0, row);
+      tma_load_2d(k8 + T8, &vmap, &full[stage], 0, row);
+      return;
+    }
     uint8_t* kb = smem + stage * 2 * TILE_BYTES;
     uint8_t* vb = kb + TILE_BYTES;
     mbar_expect_tx(&full[stage], 2 * TILE_BYTES);
@@ -166,7 +176,36 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
       break;
     }
     if (tid == 0 && kt + 1 < kt_end) issue(kt + 1, stage ^ 1);
-    const uint32_t kb = smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+    if (F8) {
+      // expand the page: 16 E5M2 bytes -> two 16-byte bf16 chunks at their swizzled place
+      const uint8_t* st8 = smem + stage * 2 * T8;
+      uint8_t* conv = smem + 4 * T8;
+      constexpr int CPT = kPageTok * (HD / 16);
+      for (int idx = tid; idx < 2 * CPT; idx += NW * 32) {
+        const int tile = idx / CPT, rem = idx % CPT;
+        const int key = rem / (HD / 16), j = rem % (HD / 16);
+        const uint4 raw = *reinterpret_cast<const uint4*>(st8 + tile * T8 + key * HD + j * 16);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t h2;
+            const unsigned short pair = (unsigned short)(w[q4] >> (16 * hh));
+            asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(pair));
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            o[q4 * 2 + hh] = pack_bf16(f.x, f.y);
+          }
+        }
+        uint8_t* dst = conv + tile * TILE_BYTES + (j >> 2) * 8192 + key * 128;
+        const int ch0 = (j & 3) * 2;
+        *reinterpret_cast<uint4*>(dst + ((ch0 ^ (key & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(dst + (((ch0 + 1) ^ (key & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      __syncthreads();
+    }
+    const uint32_t kb = F8 ? smem_base + 4 * T8 : smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
 
     // S = Q K^T  (16 rows x 64 keys per warp)
     constexpr int NP = KS ? 1 : 4;           // 16-key slices this warp scores per page
@@ -358,18 +397,18 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
   out[(long)row * out_stride + (long)head * HD + d] = f2bf(v);
 }
 
-template <int HD, int NW, bool KS>
+template <int HD, int NW, bool KS, bool F8>
 static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
                        cudaStream_t st) {
   constexpr int smem = 2 * 2 * kPageTok * HD * 2 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   dim3 grid(ntiles, p.nkv, p.nsplit);
-  launch_pdl(attn_kernel<HD, NW, KS>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
+  launch_pdl(attn_kernel<HD, NW, KS, F8>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
   return (int)cudaGetLastError();
 }
 
@@ -385,7 +424,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
                  void* o_part, void* lse_part, const void* pos, const void* slot, const void* key_end,
                  const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
                  int max_pages, void* kpool, void* vpool, long pool_pages, int nq, int nkv, int hd, int nsplit,
-                 float scale, int window, int warps, void* status, cudaStream_t st) {
+                 float scale, int window, int warps, int kv_fp8, void* status, cudaStream_t st) {
   if (ntiles <= 0) return 0;
   if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
   AttnParams p;
@@ -412,19 +451,31 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   p.status = (int*)status;
   CUtensorMap kmap, vmap;
   const uint64_t total_rows = (uint64_t)pool_pages * nkv * kPageTok;
-  int rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok,
-                        64, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc;
+  if (kv_fp8) {   // E5M2 cache: whole rows of hd bytes, unswizzled staging tiles
+    rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, hd, (uint64_t)hd, kPageTok, hd,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tmap_2d(&vmap, vpool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, hd, (uint64_t)hd, kPageTok, hd,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+  } else {
+    rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok,
+                      64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&vmap, vpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok, 64,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+  }
   if (rc) return rc;
-  rc = make_tmap_2d(&vmap, vpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok, 64,
-                    CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc) return rc;
+#define VE_ATTN2(HD_, F8_)                                                                  \
+    rc = warps == 1     ? launch_attn<HD_, 1, false, F8_>(p, kmap, vmap, ntiles, st)        \
+         : warps == 104 ? launch_attn<HD_, 4, true, F8_>(p, kmap, vmap, ntiles, st)         \
+                        : launch_attn<HD_, 4, false, F8_>(p, kmap, vmap, ntiles, st);
 #define VE_ATTN(HD_)                                                             \
   if (hd == HD_) {                                                               \
-    rc = warps == 1     ? launch_attn<HD_, 1, false>(p, kmap, vmap, ntiles, st)  \
-         : warps == 104 ? launch_attn<HD_, 4, true>(p, kmap, vmap, ntiles, st)   \
-                        : launch_attn<HD_, 4, false>(p, kmap, vmap, ntiles, st); \
+    if (kv_fp8) { VE_ATTN2(HD_, true) } else { VE_ATTN2(HD_, false) }            \
   } else
   VE_ATTN(64) VE_ATTN(128) VE_ATTN(256) { return cudaErrorInvalidValue; }
+#undef VE_ATTN2
 #undef VE_ATTN
   if (rc) return rc;
   if (nsplit > 1) {

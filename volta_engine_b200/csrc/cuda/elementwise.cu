@@ -5,6 +5,7 @@
 // interleaved pairing, partial rotary), src/backend/cuda/modules/swiglu.cu:10-30 (clamped SwiGLU,
 // GELU-tanh variant). All arithmetic is fp32; storage is bf16.
 #include "common.cuh"
+#include <cuda_fp8.h>
 
 namespace ve {
 
@@ -146,7 +147,8 @@ constexpr int kPage = 64;
 __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
                                   const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
                                   __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nq,
-                                  int nkv, int hd, int rot_dim, float theta, int interleaved, float pos_scale) {
+                                  int nkv, int hd, int rot_dim, float theta, int interleaved, float pos_scale,
+                                  int kv_fp8) {
   grid_dep_launch();
   grid_dep_wait();
   const int row = blockIdx.x, head = blockIdx.y;
@@ -185,11 +187,20 @@ __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __
   const int kvh = head - nq;
   const int page = page_table[(long)s * max_pages + p / kPage];
   const long dst = (((long)page * nkv + kvh) * kPage + (p % kPage)) * hd;
-  kpool[dst + i0] = b0;
-  kpool[dst + i1] = b1;
   h[i0] = b0;
   h[i1] = b1;
   const __nv_bfloat16* v = qkv + row_off + (long)(nq + nkv + kvh) * hd;
+  if (kv_fp8) {   // E5M2 cache: one byte per element, rounded from the bf16 values
+    uint8_t* k8 = reinterpret_cast<uint8_t*>(kpool);
+    uint8_t* v8 = reinterpret_cast<uint8_t*>(vpool);
+    k8[dst + i0] = (uint8_t)__nv_cvt_float_to_fp8(bf2f(b0), __NV_SATFINITE, __NV_E5M2);
+    k8[dst + i1] = (uint8_t)__nv_cvt_float_to_fp8(bf2f(b1), __NV_SATFINITE, __NV_E5M2);
+    v8[dst + 2 * i] = (uint8_t)__nv_cvt_float_to_fp8(bf2f(v[2 * i]), __NV_SATFINITE, __NV_E5M2);
+    v8[dst + 2 * i + 1] = (uint8_t)__nv_cvt_float_to_fp8(bf2f(v[2 * i + 1]), __NV_SATFINITE, __NV_E5M2);
+    return;
+  }
+  kpool[dst + i0] = b0;
+  kpool[dst + i1] = b1;
   vpool[dst + 2 * i] = v[2 * i];
   vpool[dst + 2 * i + 1] = v[2 * i + 1];
 }
@@ -285,13 +296,13 @@ int ve_embed(const void* ids, const void* table, void* out, int rows, int H, int
 
 int ve_rope_store(void* qkv, const void* pos, const void* slot, const void* page_table, int max_pages, void* kpool,
                   void* vpool, int rows, int nq, int nkv, int hd, int rot_dim, float theta, int interleaved,
-                  float pos_scale, cudaStream_t st) {
+                  float pos_scale, int kv_fp8, cudaStream_t st) {
   if (hd % 2 || rot_dim % 2 || rot_dim > hd || hd / 2 > 1024) return cudaErrorInvalidValue;
   if (rows <= 0) return 0;
   dim3 grid(rows, nq + nkv);
   launch_pdl(rope_store_kernel, grid, dim3(hd / 2), 0, st, (__nv_bfloat16*)qkv, (const int*)pos, (const int*)slot,
              (const int*)page_table, max_pages, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, nq, nkv, hd, rot_dim,
-             theta, interleaved, pos_scale);
+             theta, interleaved, pos_scale, kv_fp8);
   VE_CHECK_LAUNCH();
 }
 

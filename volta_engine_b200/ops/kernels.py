@@ -86,9 +86,9 @@ def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, t
                        pos_scale)
         return
     rows = qkv.shape[0]
-    call("rope_store", "ppppippiiiiifif", ptr(qkv), ptr(pos), ptr(slot), ptr(page_table), page_table.shape[1],
+    call("rope_store", "ppppippiiiiififi", ptr(qkv), ptr(pos), ptr(slot), ptr(page_table), page_table.shape[1],
          ptr(kpool), ptr(vpool), rows, nq, nkv, hd, rot_dim, float(theta), 1 if interleaved else 0,
-         float(pos_scale))
+         float(pos_scale), 1 if kpool.dtype == torch.float8_e5m2 else 0)
 
 
 def gated_act(gu, I, act=0, limit=0.0, out=None):
@@ -151,11 +151,12 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
         warps = 4
     if nsplit > 1 and ws is None:
         raise ValueError("split-KV attention needs a workspace")
-    call("attention", "plplplpppppppiipippliiiifiip",
+    call("attention", "plplplpppppppiipippliiiifiiip",
          ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
          ptr(ws.o_part) if ws else 0, ptr(ws.lse_part) if ws else 0, ptr(pos), ptr(slot), ptr(key_end),
          ptr(tf), ptr(tc), ntiles, rows, ptr(page_table), page_table.shape[1], ptr(kpool), ptr(vpool),
-         kpool.shape[0], nq, nkv, hd, nsplit, float(scale), window, warps, ptr(status_word(q.device)))
+         kpool.shape[0], nq, nkv, hd, nsplit, float(scale), window, warps,
+         1 if kpool.dtype == torch.float8_e5m2 else 0, ptr(status_word(q.device)))
     return out
 
 

@@ -17,9 +17,15 @@ class OutOfPages(RuntimeError):
     pass
 
 
+# whole-cache element formats: bf16, or E5M2 bytes (half the memory and traffic; attention expands pages to bf16 on chip)
+KV_FORMATS = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp8": torch.float8_e5m2}
+
+
 class PagedKVCache:
     def __init__(self, n_layers: int, n_kv: int, head_dim: int, num_pages: int, max_slots: int, max_seq: int,
                  device, dtype=torch.bfloat16, v_head_dim: int | None = None):
+        if isinstance(dtype, str):
+            dtype = KV_FORMATS[dtype]
         self.n_layers, self.n_kv, self.head_dim = n_layers, n_kv, head_dim
         self.v_head_dim = v_head_dim or head_dim
         self.num_pages, self.max_slots = num_pages, max_slots

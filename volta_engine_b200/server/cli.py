@@ -135,7 +135,11 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     device = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
     model, hf = load_model(cfg.model_dir, device, comm, gemm_mode=o.gemm_mode)
     mcfg = model.cfg
-    bpt = getattr(model, "kv_layers", mcfg.n_layers) * model.nkv * 2 * mcfg.head_dim * 2
+    from ..runtime.kv_cache import KV_FORMATS
+    if o.kv_format not in KV_FORMATS:
+        raise ValueError(f"kv_format '{o.kv_format}': this build has {sorted(KV_FORMATS)}")
+    kv_bytes = 1 if o.kv_format == "fp8" else 2
+    bpt = getattr(model, "kv_layers", mcfg.n_layers) * model.nkv * 2 * mcfg.head_dim * kv_bytes
     if o.kv_pool:
         pool_tokens = o.kv_pool
     elif torch.device(device).type == "cuda":
@@ -147,7 +151,8 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     if agree is not None:
         pool_tokens = agree(pool_tokens)
     kv_layers = getattr(model, "kv_layers", mcfg.n_layers)       # hybrid models keep KV only for their attention layers
-    kv = PagedKVCache(kv_layers, model.nkv, mcfg.head_dim, max(2, pool_tokens // 64), o.max_slots, o.max_seq, device)
+    kv = PagedKVCache(kv_layers, model.nkv, mcfg.head_dim, max(2, pool_tokens // 64), o.max_slots, o.max_seq, device,
+                      dtype=o.kv_format)
     engine = Engine(model, kv, use_graphs=not o.no_graphs and torch.device(device).type == "cuda",
                     prefill_chunk=o.prefill_chunk)
     return model, hf, engine, pool_tokens
