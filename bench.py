@@ -93,6 +93,7 @@ def main():
     ap.add_argument("--gemm-mode", default=os.environ.get("VOLTA_GEMM_MODE", "w4a16"))
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--comm", default=os.environ.get("VOLTA_COMM", "symm"))
+    ap.add_argument("--kv-format", default="bf16", help="bf16 (the configuration of record) | fp8 (E5M2 cache, A/B)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -131,7 +132,7 @@ def main():
     t_init = time.time()
     model = DenseModel(cfg, dev, comm).init_random(seed=1, search=False)
     pages = (max_seq + 63) // 64 + 2
-    kv = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, pages, 1, max_seq, dev)
+    kv = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, pages, 1, max_seq, dev, dtype=args.kv_format)
     # the NCCL A/B arm runs eagerly: its capture inside a CUDA graph did not finish within 7 minutes on 2 GPUs
     eng = Engine(model, kv, use_graphs=(getattr(comm, 'name', 'local') != 'nccl'), prefill_chunk=args.prefill_chunk, feedback=True)
     torch.cuda.synchronize()
@@ -219,7 +220,7 @@ def main():
             "data": "synthetic (random token ids, random-init N(0,0.02) weights quantised to NVFP4)",
             "config": {"model": "dense-27B-class NVFP4 (64L, hidden 5120, 40q/8kv hd128, ffn 17408, vocab 151936)",
                        "global_batch": 1, "seq_len": prompt_len, "parallelism": f"tp{world}",
-                       "layers": cfg.n_layers, "decode_after_prompt": prompt_len, "gemm_mode": cfg.gemm_mode,
+                       "layers": cfg.n_layers, "decode_after_prompt": prompt_len, "gemm_mode": cfg.gemm_mode, "kv_format": args.kv_format,
                        "l2": "inputs larger than L2 (weights streamed per step >> 126 MB)",
                        "comm": getattr(comm, "name", "local")},
             "prefill_tok_s": round(prompt_len / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 2),

@@ -80,3 +80,22 @@ def test_linear_layer_uses_the_tensor_core_path_for_decode_rows():
     assert torch.allclose(y, ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
     if L.GEMV_KERNEL in ("auto", "tc"):
         assert K.native_launches() - before == 1       # one launch: expansion happens inside the kernel
+
+
+@pytest.mark.parametrize("act", [0, 1])
+def test_fused_gated_activation_matches_separate_kernels(act):
+    from volta_engine_b200.ops import kernels as K, linear as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(21)
+    I, H = 384, 512
+    w = torch.randn(2 * I, H, generator=g) * 0.05
+    plain = L.LinearNVFP4.from_dense(w.to(dev), search=False).prepare()
+    fused = L.LinearNVFP4.from_dense(w.to(dev), search=False).prepare().interleave_gated()
+    assert fused.gated and torch.equal(fused.packed[:64], plain.packed[:64]) and torch.equal(fused.packed[64:128], plain.packed[I:I + 64])
+    for rows in (1, 5, 40):                       # decode kernel epilogue, and the GEMM + interleaved activation kernel
+        x = torch.randn(rows, H, generator=g).to(torch.bfloat16).to(dev)
+        want = K.gated_act(plain.forward(x), I, act, 2.0).float().cpu()
+        got = fused.forward_gated(x, act, 2.0).float().cpu()
+        assert got.shape == (rows, I)
+        assert torch.allclose(got, want, atol=2e-2 * float(want.abs().max()) + 1e-3, rtol=2e-2), rows
+    assert K.check_status(dev) == 0

@@ -128,3 +128,24 @@ def test_gpu_kernels_match_cpu_forms():
     s = torch.rand(5, generator=gen)
     assert torch.allclose(G.scale_rows_(x.clone().to(dev), s.to(dev)).cpu(), x * s[:, None])
     assert torch.allclose(G.exp_scale(x.to(dev), (x * 0.1).to(dev)).cpu(), x * torch.exp(x * 0.1), atol=1e-5)
+
+
+def test_hessian_accumulator_cpu():
+    from volta_engine_b200.ops.hessian import HessianAccumulator
+    g = torch.Generator().manual_seed(5)
+    a, b = torch.randn(10, 16, generator=g), torch.randn(7, 16, generator=g)
+    h = HessianAccumulator(16, "cpu").add(a).add(b)
+    x = torch.cat([a, b])
+    assert torch.allclose(h.H, x.t() @ x, atol=1e-4) and h.rows == 17
+    assert torch.allclose(h.mean(), x.t() @ x / 17, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_hessian_accumulator_gpu():
+    from volta_engine_b200.ops.hessian import HessianAccumulator
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(200, 256, generator=g).to(torch.bfloat16)
+    h = HessianAccumulator(256, dev).add(x[:70].to(dev)).add(x[70:].to(dev))
+    ref = x.float().t() @ x.float()
+    assert torch.allclose(h.H.cpu(), ref, atol=0.05, rtol=1e-2)

@@ -41,6 +41,8 @@ struct AttnParams {
   float scale_log2;  // softmax scale * log2(e)
   int window;
   int* status;
+  int* tickets;     // optional [tiles * nkv], zero between launches: the CTA that finishes a (tile, kv head) last merges
+                    // the split partials itself (key-split kernel only), so no separate merge launch is needed
 };
 
 VE_DEVINL void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -341,6 +343,35 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
         if (d == 0) p.lse_part[base] = l > 0.f ? m + log2f(l) : -FLT_MAX;
       }
     }
+    if (p.nsplit > 1 && p.tickets) {
+      __shared__ int s_last;
+      __threadfence();
+      __syncthreads();
+      int* tk = p.tickets + (long)tile * p.nkv + kvh;
+      if (tid == 0) s_last = atomicAdd(tk, 1) == p.nsplit - 1;
+      __syncthreads();
+      if (!s_last) return;
+      __threadfence();
+      // merge in split order (the same arithmetic as the stand-alone merge kernel)
+      for (int idx = tid; idx < nrows * HD; idx += NW * 32) {
+        const int row = idx / HD, d = idx % HD;
+        const int tok = first + row / G, head = kvh * G + row % G;
+        const long base = ((long)tok * p.nq + head) * p.nsplit;
+        float mx = -FLT_MAX;
+        for (int i = 0; i < p.nsplit; ++i) mx = fmaxf(mx, __ldcg(p.lse_part + base + i));
+        float acc = 0.f, wsum = 0.f;
+        for (int i = 0; i < p.nsplit; ++i) {
+          const float l = __ldcg(p.lse_part + base + i);
+          const float w = (l == -FLT_MAX) ? 0.f : exp2f(l - mx);
+          wsum += w;
+          acc += w * __ldcg(p.o_part + (base + i) * HD + d);
+        }
+        float v = wsum > 0.f ? acc / wsum : 0.f;
+        if (p.gate) v *= 1.f / (1.f + __expf(-bf2f(p.gate[(long)tok * p.gate_stride + (long)head * HD + d])));
+        p.out[(long)tok * p.out_stride + (long)head * HD + d] = f2bf(v);
+      }
+      if (tid == 0) *tk = 0;
+    }
     return;
   }
 #pragma unroll
@@ -424,7 +455,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
                  void* o_part, void* lse_part, const void* pos, const void* slot, const void* key_end,
                  const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
                  int max_pages, void* kpool, void* vpool, long pool_pages, int nq, int nkv, int hd, int nsplit,
-                 float scale, int window, int warps, int kv_fp8, void* status, cudaStream_t st) {
+                 float scale, int window, int warps, int kv_fp8, void* tickets, void* status, cudaStream_t st) {
   if (ntiles <= 0) return 0;
   if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
   AttnParams p;
@@ -449,6 +480,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   p.status = (int*)status;
+  p.tickets = (warps == 104 && nsplit > 1) ? (int*)tickets : nullptr;
   CUtensorMap kmap, vmap;
   const uint64_t total_rows = (uint64_t)pool_pages * nkv * kPageTok;
   int rc;
@@ -478,7 +510,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
 #undef VE_ATTN2
 #undef VE_ATTN
   if (rc) return rc;
-  if (nsplit > 1) {
+  if (nsplit > 1 && !p.tickets) {
     launch_pdl(attn_reduce_kernel, dim3(rows * nq), dim3(hd), 0, st, (const float*)o_part, (const float*)lse_part,
                (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, (const int*)slot, nq, nsplit, hd);
     rc = (int)cudaGetLastError();

@@ -137,6 +137,9 @@ struct DecodeParams {
   int* tickets;           // [N/128], zero between launches
   int* status;
   int tpt;                // epilogue threads that build one activation tile (16, 32, 64 or 128)
+  int act;                // 0: plain output. 1 / 2: gated activation (SiLU / tanh-GELU): every 128-row weight tile holds
+                          // 64 gate rows followed by their 64 up rows, the output has N/2 columns act(gate) * up
+  float act_limit;        // > 0: gate clamped from above, up clamped to +-limit
 };
 
 // Warp roles (192 threads): warp 0 = TMA producer of weight tiles and their scale atoms; warp 1 = TMEM owner and
@@ -315,7 +318,30 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
         if (etid == 0) p.tickets[tile] = 0;      // ready for the next launch
       }
     }
-    if (write && n < p.N && !s_fail) {
+    if (p.act) {
+      // gate and up of one feature sit in lanes f and f + 64 of the tile: meet through shared memory (the pipeline
+      // stages are idle by now)
+      float* sb = reinterpret_cast<float*>(smem);
+      if (write) {
+#pragma unroll
+        for (int m = 0; m < MROWS; ++m)
+          if (m < p.M) sb[m * 128 + f] = acc[m] * p.alpha;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (write && f < 64 && !s_fail) {
+        const int col = tile * 64 + f;
+#pragma unroll
+        for (int m = 0; m < MROWS; ++m) {
+          if (m < p.M) {
+            float g = sb[m * 128 + f], u = sb[m * 128 + 64 + f];
+            if (p.act_limit > 0.f) { g = fminf(g, p.act_limit); u = fminf(fmaxf(u, -p.act_limit), p.act_limit); }
+            const float a = p.act == 1 ? g / (1.f + __expf(-g))
+                                       : 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+            p.out[(long)m * p.ldo + col] = f2bf(a * u);
+          }
+        }
+      }
+    } else if (write && n < p.N && !s_fail) {
 #pragma unroll
       for (int m = 0; m < MROWS; ++m) {
         if (m < p.M) {
@@ -380,8 +406,9 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
 // pdl != 0 launches with programmatic stream serialization: set-up and the first weight tiles overlap the kernel
 // in front of it in the stream (the kernel waits for that kernel before it touches X, residual or out).
 int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, void* out, long ldo, void* out_f32,
-                   const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, void* ws,
-                   void* tickets, void* status, cudaStream_t st) {
+                   const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, int act,
+                   float act_limit, void* ws, void* tickets, void* status, cudaStream_t st) {
+  if (act && (out_f32 || residual || !out)) return cudaErrorInvalidValue;
   if (M < 1 || N % 128 || K % 256 || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
     return cudaErrorInvalidValue;
   if (ks < 1) ks = 1;
@@ -394,7 +421,7 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
   int tpt = 16;
   while (tpt < 16 * M && tpt < 128) tpt <<= 1;
   DecodeParams p{N, M, K, alpha, (const __nv_bfloat16*)X, ldx, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)residual, ldr,
-                 (float*)out_f32, (const uint8_t*)sfa, (float*)ws, (int*)tickets, (int*)status, tpt};
+                 (float*)out_f32, (const uint8_t*)sfa, (float*)ws, (int*)tickets, (int*)status, tpt, act, act_limit};
 #define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, ks, pdl, st)
   if (terms == 4) { if (bn == 16) VE_DW(16, 4, 4); if (bn == 32) VE_DW(32, 4, 4); VE_DW(64, 4, 3); }
   if (terms == 2) { if (bn == 16) VE_DW(16, 2, 4); if (bn == 32) VE_DW(32, 2, 4); VE_DW(64, 2, 3); }

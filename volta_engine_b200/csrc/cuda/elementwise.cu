@@ -216,15 +216,18 @@ VE_DEVINL float act_gelu_tanh(float g) {
 }
 
 __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long rows,
-                                 int I, int act, float limit) {
+                                 int I, int act, float limit, int interleave) {
   grid_dep_launch();
   grid_dep_wait();
   const long n8 = rows * (long)(I / 8);
   for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n8; idx += (long)gridDim.x * blockDim.x) {
     const long r = idx / (I / 8);
     const int c = (int)(idx % (I / 8)) * 8;
-    bf16x8 g = *reinterpret_cast<const bf16x8*>(gu + r * 2L * I + c);
-    bf16x8 u = *reinterpret_cast<const bf16x8*>(gu + r * 2L * I + I + c);
+    // interleave == 64: the row holds [64 gate | 64 up] per 128 columns (layout of the fused decode linear's weights)
+    const long go = interleave ? (long)(c / 64) * 128 + (c % 64) : c;
+    const long uo = interleave ? go + 64 : (long)I + c;
+    bf16x8 g = *reinterpret_cast<const bf16x8*>(gu + r * 2L * I + go);
+    bf16x8 u = *reinterpret_cast<const bf16x8*>(gu + r * 2L * I + uo);
     bf16x8 o;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -306,13 +309,13 @@ int ve_rope_store(void* qkv, const void* pos, const void* slot, const void* page
   VE_CHECK_LAUNCH();
 }
 
-int ve_gated_act(const void* gu, void* out, long rows, int I, int act, float limit, cudaStream_t st) {
-  if (I % 8) return cudaErrorInvalidValue;
+int ve_gated_act(const void* gu, void* out, long rows, int I, int act, float limit, int interleave, cudaStream_t st) {
+  if (I % 8 || (interleave && (interleave != 64 || I % 64))) return cudaErrorInvalidValue;
   if (rows <= 0) return 0;
   const long n8 = rows * (long)(I / 8);
   const int blocks = (int)((n8 + 255) / 256 < 148 * 8 ? (n8 + 255) / 256 : 148 * 8);
   launch_pdl(gated_act_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, I,
-             act, limit);
+             act, limit, interleave);
   VE_CHECK_LAUNCH();
 }
 

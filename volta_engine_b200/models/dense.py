@@ -10,6 +10,7 @@ merge. KV heads are replicated when there are fewer of them than ranks.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, asdict
 
 import torch
@@ -65,6 +66,10 @@ class DenseConfig:
 
     def to_dict(self):
         return asdict(self)
+
+
+# decode: act(gate) * up inside the gate/up linear's epilogue (VOLTA_FUSE_ACT=0 keeps the separate activation kernel)
+FUSE_GATED_ACT = os.environ.get("VOLTA_FUSE_ACT", "1") != "0"
 
 
 def _pad_to(n: int, m: int) -> int:
@@ -141,6 +146,8 @@ class DenseModel:
             wg, wu = rnd(cfg.ffn, H), rnd(cfg.ffn, H)
             L.gate_up = self._make_linear(torch.cat([wg[r * self.ffn:(r + 1) * self.ffn],
                                                      wu[r * self.ffn:(r + 1) * self.ffn]], 0), search)
+            if isinstance(L.gate_up, LinearNVFP4) and FUSE_GATED_ACT:
+                L.gate_up.interleave_gated()
             del wg, wu
             wd = rnd(H, cfg.ffn)
             L.down = self._make_linear(wd[:, r * self.ffn:(r + 1) * self.ffn].contiguous(), search)
@@ -260,8 +267,11 @@ class DenseModel:
     def ffn_block(self, li, L, x, b: BatchRows, pbuf):
         """Feed-forward sub-layer: returns this rank's partial of the down projection [n, H]."""
         cfg = self.cfg
-        gu = L.gate_up.forward(x)
-        a = K.gated_act(gu, self.ffn, 0 if cfg.act == "silu" else 1, cfg.act_limit)
+        act = 0 if cfg.act == "silu" else 1
+        if getattr(L.gate_up, "gated", False):        # gate / up rows interleaved: activation fused into the decode linear
+            a = L.gate_up.forward_gated(x, act, cfg.act_limit)
+        else:
+            a = K.gated_act(L.gate_up.forward(x), self.ffn, act, cfg.act_limit)
         return L.down.forward(a, out=pbuf)
 
     def ensure_workspace(self, max_rows: int, max_splits: int):

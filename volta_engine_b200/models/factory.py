@@ -126,6 +126,8 @@ def load_dense_weights(model: DenseModel, src: TensorSource, gemm_mode="w4a16", 
         L.qkv = fuse_linears([q, k, v])
         L.o_proj = src.linear(p + "self_attn.o_proj", "row", **kw)
         L.gate_up = fuse_linears([src.linear(p + "mlp.gate_proj", "col", **kw), src.linear(p + "mlp.up_proj", "col", **kw)])
+        if hasattr(L.gate_up, "interleave_gated"):
+            L.gate_up.interleave_gated()
         L.down = src.linear(p + "mlp.down_proj", "row", **kw)
         L.attn_norm = src.tensor(p + "input_layernorm.weight", dev, bf)
         L.post_attn_norm = L.post_ffn_norm = None

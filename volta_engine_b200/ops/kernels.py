@@ -91,8 +91,12 @@ def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, t
          float(pos_scale), 1 if kpool.dtype == torch.float8_e5m2 else 0)
 
 
-def gated_act(gu, I, act=0, limit=0.0, out=None):
+def gated_act(gu, I, act=0, limit=0.0, out=None, interleave=0):
+    """act(gate) * up. ``interleave=64``: the row holds [64 gate | 64 up] per 128 columns instead of [all gate | all up]."""
     if not gu.is_cuda:
+        if interleave:
+            v = gu.reshape(gu.shape[0], -1, 2, interleave)
+            gu = torch.cat([v[:, :, 0].reshape(gu.shape[0], I), v[:, :, 1].reshape(gu.shape[0], I)], 1)
         o = ref.gated_act(gu, I, act, limit)
         if out is not None:
             out.copy_(o)
@@ -101,7 +105,7 @@ def gated_act(gu, I, act=0, limit=0.0, out=None):
     rows = gu.shape[0]
     if out is None:
         out = torch.empty(rows, I, dtype=gu.dtype, device=gu.device)
-    call("gated_act", "ppliif", ptr(gu), ptr(out), rows, I, act, float(limit))
+    call("gated_act", "ppliifi", ptr(gu), ptr(out), rows, I, act, float(limit), interleave)
     return out
 
 
@@ -116,6 +120,9 @@ def add_(a, b):
 # ---------------------------------------------------------------------------------------------- attention
 # decode / verify tiles: 104 = four warps that split the keys of every page (default), 1 = one warp per tile
 ATTN_DECODE_WARPS = 1 if os.environ.get("VOLTA_ATTN_DECODE", "ksplit") == "1warp" else 104
+# "fused": the split CTA that finishes last merges the partials itself. Measured slower than the parallel merge kernel
+# (one CTA walks 32 splits x 5 heads serially: 166 vs 192 tok/s on the 27B decode), so the kernel form is the default.
+ATTN_FUSED_MERGE = os.environ.get("VOLTA_ATTN_MERGE", "kernel") == "fused"
 
 
 class AttnWorkspace:
@@ -125,6 +132,7 @@ class AttnWorkspace:
         self.max_splits = max_splits
         self.o_part = torch.empty(max_rows * nq * max_splits * hd, dtype=torch.float32, device=device)
         self.lse_part = torch.empty(max_rows * nq * max_splits, dtype=torch.float32, device=device)
+        self.tickets = torch.zeros(max_rows * nq, dtype=torch.int32, device=device)   # (tile, kv head) arrival counters
 
 
 def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out=None, window=0, key_end=None,
@@ -151,12 +159,13 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
         warps = 4
     if nsplit > 1 and ws is None:
         raise ValueError("split-KV attention needs a workspace")
-    call("attention", "plplplpppppppiipippliiiifiiip",
+    call("attention", "plplplpppppppiipippliiiifiiipp",
          ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
          ptr(ws.o_part) if ws else 0, ptr(ws.lse_part) if ws else 0, ptr(pos), ptr(slot), ptr(key_end),
          ptr(tf), ptr(tc), ntiles, rows, ptr(page_table), page_table.shape[1], ptr(kpool), ptr(vpool),
          kpool.shape[0], nq, nkv, hd, nsplit, float(scale), window, warps,
-         1 if kpool.dtype == torch.float8_e5m2 else 0, ptr(status_word(q.device)))
+         1 if kpool.dtype == torch.float8_e5m2 else 0,
+         ptr(ws.tickets) if (ws is not None and ATTN_FUSED_MERGE) else 0, ptr(status_word(q.device)))
     return out
 
 
@@ -344,13 +353,14 @@ def nvfp4_expand_rows(x, terms=DW_TERMS):
 DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
 
 
-def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None):
+def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None,
+                act=0, act_limit=0.0):
     """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path; the kernel expands each bf16
     activation row into ``terms`` residual NVFP4 rows itself (bf16-grade accuracy): out [M, N]."""
     N, K = packed.shape[0], packed.shape[1] * 2
     M = x.shape[0]
     if out is None:
-        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+        out = torch.empty(M, N // 2 if act else N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     f32 = out.dtype == torch.float32
     _, _, ws, tickets = dw_scratch(x.device)
     if ks is None:
@@ -358,10 +368,10 @@ def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=Fa
     assert ks * (N // 128) <= 1024
     if pdl is None:
         pdl = DW_PDL
-    call("decode_w4a4", "pppl" + "plppl" + "iiifiii" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
+    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
          0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
          residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,
-         ptr(ws), ptr(tickets), ptr(status_word(x.device)))
+         act, float(act_limit), ptr(ws), ptr(tickets), ptr(status_word(x.device)))
     return out
 
 

@@ -118,6 +118,28 @@ class LinearNVFP4:
             return K.gemm_w4a4(self.packed, self._sf_atoms, self.gscale, xp, xs, rows, out=out, residual=residual)
         return K.gemm_bf16(self.dequant(), x, out=out, residual=residual)
 
+    def interleave_gated(self):
+        """For a stacked [gate | up] projection: reorder the rows to [64 gate | 64 up] per 128-row tile, so that the decode
+        kernel can apply act(gate) * up in its epilogue (the prefill path reads the same layout through ``gated_act``)."""
+        N = self.out_features
+        I = N // 2
+        if getattr(self, "gated", False) or N % 128 or I % 64:
+            return self
+        idx = torch.arange(I, device=self.packed.device).reshape(-1, 64)
+        order = torch.stack([idx, idx + I], 1).reshape(-1)
+        self.packed, self.scales = self.packed[order].contiguous(), self.scales[order].contiguous()
+        self._sf_k128 = self._sf_atoms = self._gv = None
+        self.gated = True
+        return self.prepare() if self.packed.is_cuda else self
+
+    def forward_gated(self, x, act: int = 0, limit: float = 0.0):
+        """act(gate) * up of a ``interleave_gated`` projection: [rows, N/2]."""
+        assert getattr(self, "gated", False)
+        if x.is_cuda and x.shape[0] <= GEMV_MAX_ROWS and GEMV_KERNEL in ("auto", "tc") and self._sf_atoms is not None \
+                and self._tc_ok():
+            return K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, act=1 + act, act_limit=limit)
+        return K.gated_act(self.forward(x), self.out_features // 2, act, limit, interleave=64)
+
     def nbytes(self):
         return self.packed.numel() + self.scales.numel()
 

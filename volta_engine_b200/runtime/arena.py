@@ -45,7 +45,8 @@ class Arena:
             raise ArenaError(f"arena is frozen (serving): allocation '{name}' refused")
         shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,)))
         n = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
-        start = (self.top + _ALIGN - 1) // _ALIGN * _ALIGN
+        base = self.buf.data_ptr()
+        start = (base + self.top + _ALIGN - 1) // _ALIGN * _ALIGN - base        # aligned address, not just offset
         if start + n > self.capacity:
             raise ArenaError(f"arena exhausted: '{name}' needs {n} B, {self.capacity - start} B left of {self.capacity}")
         self.top = start + n
