@@ -99,3 +99,54 @@ def test_fused_gated_activation_matches_separate_kernels(act):
         assert got.shape == (rows, I)
         assert torch.allclose(got, want, atol=2e-2 * float(want.abs().max()) + 1e-3, rtol=2e-2), rows
     assert K.check_status(dev) == 0
+
+
+def test_fused_prenorm_matches_norm_kernel_then_linear():
+    from volta_engine_b200.ops import kernels as K, linear as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(31)
+    H, N = 1024, 512
+    lin = L.LinearNVFP4.from_dense((torch.randn(N, H, generator=g) * 0.05).to(dev), search=False).prepare()
+    gated = L.LinearNVFP4.from_dense((torch.randn(N, H, generator=g) * 0.05).to(dev), search=False).prepare().interleave_gated()
+    w = (torch.rand(H, generator=g) + 0.5).to(torch.bfloat16).to(dev)
+    for M in (1, 3, 4):
+        resid = torch.randn(M, H, generator=g).to(torch.bfloat16).to(dev)
+        delta = (torch.randn(M, H, generator=g) * 0.3).to(torch.bfloat16).to(dev)
+        # reference: the norm kernel (updates the residual in place), then the plain decode linear
+        r_ref = resid.clone()
+        x_ref = K.rmsnorm(delta, w, 1e-6, 0.0, residual=r_ref)
+        want = lin.forward(x_ref).float().cpu()
+        r_out = torch.empty_like(resid)
+        got = lin.forward_prenorm(resid, delta, w, 1e-6, 0.0, r_out).float().cpu()
+        assert torch.equal(r_out, r_ref)
+        assert torch.allclose(got, want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)
+        # no delta: plain norm of the residual, nothing written
+        x0 = K.rmsnorm(resid, w, 1e-6, 1.0)
+        got0 = lin.forward_prenorm(resid, None, w, 1e-6, 1.0, None).float().cpu()
+        assert torch.allclose(got0, lin.forward(x0).float().cpu(), atol=2e-2 * float(want.abs().max()), rtol=2e-2)
+        # together with the gated activation
+        wantg = gated.forward_gated(x_ref, 0, 0.0).float().cpu()
+        gotg = gated.forward_prenorm(resid, delta, w, 1e-6, 0.0, torch.empty_like(resid), act=0).float().cpu()
+        assert torch.allclose(gotg, wantg, atol=2e-2 * float(wantg.abs().max()) + 1e-3, rtol=3e-2)
+    assert K.check_status(dev) == 0
+
+
+def test_dense_model_step_agrees_with_and_without_fused_norms(monkeypatch):
+    from volta_engine_b200.models import dense
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    dev = torch.device("cuda:0")
+    cfg = dense.DenseConfig(n_layers=3, hidden=512, n_q=4, n_kv=2, head_dim=128, ffn=1024, vocab=2048)
+    m = dense.DenseModel(cfg, dev).init_random(seed=5)
+    prompt = list(range(100, 180))
+    hidden = []
+    for fuse in (True, False):
+        monkeypatch.setattr(dense, "FUSE_PRENORM", fuse)
+        assert m._prenorm_ok(type("B", (), {"n": 1})()) == fuse
+        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 1, 512, dev)
+        eng = Engine(m, kv, use_graphs=False, prefill_chunk=64)
+        eng.prefill(0, prompt)                          # prefill rows never take the fused path
+        eng.step([7], [len(prompt)], [0])               # one decode row on top of identical caches
+        hidden.append(m.last_hidden.float().cpu().clone())
+    cos = torch.nn.functional.cosine_similarity(hidden[0].flatten(), hidden[1].flatten(), dim=0)
+    assert cos > 0.999, float(cos)

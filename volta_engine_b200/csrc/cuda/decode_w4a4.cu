@@ -43,55 +43,8 @@ VE_DEVINL float2 dq_e2m1x2_dec(uint32_t byte) {
 
 // x [M, K] bf16 (pitch ldx) -> Xp [M * TERMS, K/2] codes (virtual row m * TERMS + t) and scales in 512 B atoms
 // [K/64][512] (atom byte (r%32)*16 + (r/32)*4 + j = scale of virtual row r, 16-block j of the 64-wide group).
-template <int TERMS>
-__global__ void nvfp4_expand_rows_kernel(const __nv_bfloat16* __restrict__ X, long ldx, uint8_t* __restrict__ Xp,
-                                         uint8_t* __restrict__ Xs, int M, int K) {
-  grid_dep_launch();       // the decode linear behind this kernel may set up and prefetch weights meanwhile
-  const int kb = K >> 4;
-  const int total = M * kb;
-  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-    const int m = idx / kb, b = idx % kb;
-    const __nv_bfloat16* src = X + (long)m * ldx + b * 16;
-    float r[16];
-    const bf16x8 t0 = *reinterpret_cast<const bf16x8*>(src), t1 = *reinterpret_cast<const bf16x8*>(src + 8);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 f = __bfloat1622float2(t0.v[j]);
-      r[2 * j] = f.x; r[2 * j + 1] = f.y;
-      f = __bfloat1622float2(t1.v[j]);
-      r[8 + 2 * j] = f.x; r[8 + 2 * j + 1] = f.y;
-    }
-    float up = 1.f, down = 1.f;
-#pragma unroll
-    for (int t = 0; t < TERMS; ++t) {
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(r[j]));
-      const uint32_t sb = dq_e4m3_enc(amax * up * (1.f / 6.f));
-      const float sd = dq_e4m3_dec(sb);
-      const float inv = sd > 0.f ? up / sd : 0.f;
-      const float back = sd * down;
-      uint32_t w[2] = {0u, 0u};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t byte = dq_e2m1x2_enc(r[2 * j] * inv, r[2 * j + 1] * inv);
-        w[j >> 2] |= byte << (8 * (j & 3));
-        const float2 d = dq_e2m1x2_dec(byte);
-        r[2 * j] -= d.x * back;
-        r[2 * j + 1] -= d.y * back;
-      }
-      const int v = m * TERMS + t;
-      *reinterpret_cast<uint2*>(Xp + (long)v * (K >> 1) + b * 8) = make_uint2(w[0], w[1]);
-      Xs[(long)(b >> 2) * 512 + (v & 31) * 16 + (v >> 5) * 4 + (b & 3)] = (uint8_t)sb;
-      up *= 8.f; down *= 0.125f;
-    }
-  }
-}
-
 // One 16-element block of a bf16 row -> TERMS residual NVFP4 blocks: 8 code bytes and one E4M3 scale per term.
-template <int TERMS>
-VE_DEVINL void expand_block16(const __nv_bfloat16* __restrict__ src, uint2* codes, uint32_t* scales) {
-  float r[16];
+VE_DEVINL void load16(const __nv_bfloat16* __restrict__ src, float* r) {
   const bf16x8 t0 = *reinterpret_cast<const bf16x8*>(src), t1 = *reinterpret_cast<const bf16x8*>(src + 8);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -100,6 +53,11 @@ VE_DEVINL void expand_block16(const __nv_bfloat16* __restrict__ src, uint2* code
     f = __bfloat1622float2(t1.v[j]);
     r[8 + 2 * j] = f.x; r[8 + 2 * j + 1] = f.y;
   }
+}
+VE_DEVINL float round_bf16(float x) { return bf2f(f2bf(x)); }
+
+template <int TERMS>
+VE_DEVINL void expand_block16(float* r, uint2* codes, uint32_t* scales) {
   float up = 1.f, down = 1.f;
 #pragma unroll
   for (int t = 0; t < TERMS; ++t) {
@@ -125,6 +83,30 @@ VE_DEVINL void expand_block16(const __nv_bfloat16* __restrict__ src, uint2* code
   }
 }
 
+// Stand-alone form of the expansion (tests): x [M, K] bf16 (pitch ldx) -> Xp [M * TERMS, K/2] codes (virtual row
+// m * TERMS + t) and scales in 512 B atoms [K/64][512] (atom byte (r%32)*16 + (r/32)*4 + j = scale of virtual row r,
+// 16-block j of the 64-wide group).
+template <int TERMS>
+__global__ void nvfp4_expand_rows_kernel(const __nv_bfloat16* __restrict__ X, long ldx, uint8_t* __restrict__ Xp,
+                                         uint8_t* __restrict__ Xs, int M, int K) {
+  const int kb = K >> 4;
+  const int total = M * kb;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int m = idx / kb, b = idx % kb;
+    float r[16];
+    uint2 codes[TERMS];
+    uint32_t sc[TERMS];
+    load16(X + (long)m * ldx + b * 16, r);
+    expand_block16<TERMS>(r, codes, sc);
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+      const int v = m * TERMS + t;
+      *reinterpret_cast<uint2*>(Xp + (long)v * (K >> 1) + b * 8) = codes[t];
+      Xs[(long)(b >> 2) * 512 + (v & 31) * 16 + (v >> 5) * 4 + (b & 3)] = (uint8_t)sc[t];
+    }
+  }
+}
+
 struct DecodeParams {
   int N, M, K;
   float alpha;
@@ -140,6 +122,14 @@ struct DecodeParams {
   int act;                // 0: plain output. 1 / 2: gated activation (SiLU / tanh-GELU): every 128-row weight tile holds
                           // 64 gate rows followed by their 64 up rows, the output has N/2 columns act(gate) * up
   float act_limit;        // > 0: gate clamped from above, up clamped to +-limit
+  // Optional fused pre-norm (M <= 4): the input of the product is RMSNorm(resid + delta) * (w + wbias), computed by the
+  // producer warps while the weights stream; CTAs of tile 0 also write the updated residual (resid + delta, bf16) to
+  // resid_out (a different buffer than resid: other CTAs still read the old one). x is not read in this mode.
+  const __nv_bfloat16* pn_w;
+  const __nv_bfloat16* pn_resid;
+  const __nv_bfloat16* pn_delta;      // may be null (plain RMSNorm of resid)
+  __nv_bfloat16* pn_resid_out;        // may be null when delta is null
+  float pn_eps, pn_wbias;
 };
 
 // Warp roles (192 threads): warp 0 = TMA producer of weight tiles and their scale atoms; warp 1 = TMEM owner and
@@ -245,6 +235,30 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
       const int grp = etid / tpt, gt = etid % tpt;
       const int items = 16 * p.M;
       bool ok = true;
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.pn_w) {
+        // row statistics over the whole row (every CTA needs them; 128 threads, fixed summation order)
+        __shared__ float s_red[4][4];
+        for (int m = 0; m < p.M; ++m) {
+          float ss = 0.f;
+          for (int i = etid * 16; i < p.K; i += 128 * 16) {
+            float v[16], d[16];
+            load16(p.pn_resid + (long)m * p.K + i, v);
+            if (p.pn_delta) {
+              load16(p.pn_delta + (long)m * p.K + i, d);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = round_bf16(v[j] + d[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ss = fmaf(v[j], v[j], ss);
+          }
+          ss = warp_sum(ss);
+          if (lane == 0) s_red[warp - 2][m] = ss;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int m = 0; m < p.M; ++m)
+          rs[m] = rsqrtf((s_red[0][m] + s_red[1][m] + s_red[2][m] + s_red[3][m]) / (float)p.K + p.pn_eps);
+      }
       for (int i = grp; i < nkt && ok && grp < ngroups; i += ngroups) {
         const int s = i % STAGES, kt = kt0 + i;
         ok = mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1);
@@ -255,7 +269,34 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
           const int m = it >> 4, b = it & 15;
           uint2 codes[TERMS];
           uint32_t sc[TERMS];
-          expand_block16<TERMS>(p.x + (long)m * p.ldx + kt * 256 + b * 16, codes, sc);
+          float r16[16];
+          const int k0 = kt * 256 + b * 16;
+          if (p.pn_w) {
+            float d[16], w16[16];
+            load16(p.pn_resid + (long)m * p.K + k0, r16);
+            if (p.pn_delta) {
+              load16(p.pn_delta + (long)m * p.K + k0, d);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r16[j] = round_bf16(r16[j] + d[j]);
+              if (tile == 0 && p.pn_resid_out) {
+                bf16x8 o0, o1;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  o0.v[j] = __floats2bfloat162_rn(r16[2 * j], r16[2 * j + 1]);
+                  o1.v[j] = __floats2bfloat162_rn(r16[8 + 2 * j], r16[8 + 2 * j + 1]);
+                }
+                *reinterpret_cast<bf16x8*>(p.pn_resid_out + (long)m * p.K + k0) = o0;
+                *reinterpret_cast<bf16x8*>(p.pn_resid_out + (long)m * p.K + k0 + 8) = o1;
+              }
+            }
+            load16(p.pn_w + k0, w16);
+            const float rm = m == 0 ? rs[0] : m == 1 ? rs[1] : m == 2 ? rs[2] : rs[3];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r16[j] = round_bf16(r16[j] * rm * (w16[j] + p.pn_wbias));
+          } else {
+            load16(p.x + (long)m * p.ldx + k0, r16);
+          }
+          expand_block16<TERMS>(r16, codes, sc);
 #pragma unroll
           for (int t = 0; t < TERMS; ++t) {
             const int v = m * TERMS + t;
@@ -407,8 +448,10 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
 // in front of it in the stream (the kernel waits for that kernel before it touches X, residual or out).
 int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, void* out, long ldo, void* out_f32,
                    const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, int act,
-                   float act_limit, void* ws, void* tickets, void* status, cudaStream_t st) {
+                   float act_limit, const void* pn_w, const void* pn_resid, const void* pn_delta, void* pn_resid_out,
+                   float pn_eps, float pn_wbias, void* ws, void* tickets, void* status, cudaStream_t st) {
   if (act && (out_f32 || residual || !out)) return cudaErrorInvalidValue;
+  if (pn_w && (M > 4 || !pn_resid || K % 16 || (pn_delta && pn_resid_out == pn_resid))) return cudaErrorInvalidValue;
   if (M < 1 || N % 128 || K % 256 || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
     return cudaErrorInvalidValue;
   if (ks < 1) ks = 1;
@@ -421,7 +464,9 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
   int tpt = 16;
   while (tpt < 16 * M && tpt < 128) tpt <<= 1;
   DecodeParams p{N, M, K, alpha, (const __nv_bfloat16*)X, ldx, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)residual, ldr,
-                 (float*)out_f32, (const uint8_t*)sfa, (float*)ws, (int*)tickets, (int*)status, tpt, act, act_limit};
+                 (float*)out_f32, (const uint8_t*)sfa, (float*)ws, (int*)tickets, (int*)status, tpt, act, act_limit,
+                 (const __nv_bfloat16*)pn_w, (const __nv_bfloat16*)pn_resid, (const __nv_bfloat16*)pn_delta,
+                 (__nv_bfloat16*)pn_resid_out, pn_eps, pn_wbias};
 #define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, ks, pdl, st)
   if (terms == 4) { if (bn == 16) VE_DW(16, 4, 4); if (bn == 32) VE_DW(32, 4, 4); VE_DW(64, 4, 3); }
   if (terms == 2) { if (bn == 16) VE_DW(16, 2, 4); if (bn == 32) VE_DW(32, 2, 4); VE_DW(64, 2, 3); }

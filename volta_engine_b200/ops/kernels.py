@@ -354,10 +354,15 @@ DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
 
 
 def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None,
-                act=0, act_limit=0.0):
+                act=0, act_limit=0.0, prenorm=None):
     """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path; the kernel expands each bf16
     activation row into ``terms`` residual NVFP4 rows itself (bf16-grade accuracy): out [M, N]."""
     N, K = packed.shape[0], packed.shape[1] * 2
+    # prenorm = (norm_w, resid, delta | None, resid_out | None, eps, wbias): the kernel's input is
+    # RMSNorm(resid + delta) * (norm_w + wbias) and it writes resid + delta to resid_out; ``x`` is ignored (M <= 4)
+    pn_w, pn_resid, pn_delta, pn_out, pn_eps, pn_bias = prenorm if prenorm is not None else (None, None, None, None, 0.0, 0.0)
+    if prenorm is not None:
+        x = pn_resid
     M = x.shape[0]
     if out is None:
         out = torch.empty(M, N // 2 if act else N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
@@ -368,10 +373,11 @@ def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=Fa
     assert ks * (N // 128) <= 1024
     if pdl is None:
         pdl = DW_PDL
-    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
+    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppppff" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
          0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
          residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,
-         act, float(act_limit), ptr(ws), ptr(tickets), ptr(status_word(x.device)))
+         act, float(act_limit), ptr(pn_w), ptr(pn_resid), ptr(pn_delta), ptr(pn_out), float(pn_eps), float(pn_bias),
+         ptr(ws), ptr(tickets), ptr(status_word(x.device)))
     return out
 
 

@@ -52,7 +52,7 @@ def graph_time(fn, reps: int, flush: torch.Tensor, rounds: int = 5) -> float:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="bench_kernels")
-    ap.add_argument("--only", default="", help="comma list: decode_w4a4,nvfp4_gemv,exl3_gemv,gemm_w4a4,gemm_w4a16,gemm_bf16")
+    ap.add_argument("--only", default="", help="comma list: decode_w4a4,nvfp4_gemv,exl3_gemv,gemm_w4a4,gemm_w4a16,gemm_bf16,attention")
     ap.add_argument("--shape", action="append", default=[], help="NxK (repeatable); default: the 27B layer shapes")
     ap.add_argument("--rows", default="1,4,16")
     ap.add_argument("--tokens", type=int, default=4096, help="rows of the GEMM benchmarks")
@@ -67,6 +67,8 @@ def main(argv=None) -> int:
     only = set(x for x in a.only.split(",") if x)
     shapes = [tuple(int(v) for v in s.lower().split("x")) for s in a.shape] or \
         [(7168, 5120), (5120, 5120), (34816, 5120), (5120, 17408)]
+    if only == {"attention"}:
+        shapes = []
     rows = [int(r) for r in a.rows.split(",")]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     print(f"kernel,N,K,rows,us,rate,unit,frac_of_{src}_peak")
@@ -134,6 +136,27 @@ def main(argv=None) -> int:
                 print(f"gemm_bf16,{N},{Kd},{T},{r}", flush=True)
             del wb
         del packed
+    if not only or "attention" in only:
+        # decode attention of the 27B shape: 40 q / 8 kv heads, head_dim 128, one row, `ctx` keys in 64-token pages
+        import math
+        nq, nkv, hd = 40, 8, 128
+        for ctx in (4096, 16384, 65536):
+            pages = ctx // 64 + 2
+            kpool = torch.randn(pages, nkv, 64, hd, device=dev).to(torch.bfloat16)
+            vpool = torch.randn(pages, nkv, 64, hd, device=dev).to(torch.bfloat16)
+            table = torch.arange(1, pages, dtype=torch.int32, device=dev)[None].contiguous()
+            pos = torch.tensor([ctx - 1], dtype=torch.int32, device=dev)
+            slot = torch.zeros(1, dtype=torch.int32, device=dev)
+            q = torch.randn(1, (nq + 2 * nkv) * hd, device=dev).to(torch.bfloat16)
+            ws = K.AttnWorkspace(1, nq, hd, 64, dev)
+            out = torch.empty(1, nq * hd, dtype=torch.bfloat16, device=dev)
+            nsplit = min(32, max(1, 148 * 3 // nkv))
+            fn = lambda: K.attention(q, pos, slot, table, kpool, vpool, nq, nkv, hd, 1 / math.sqrt(hd), out=out,
+                                     nsplit=nsplit, ws=ws)
+            r = run("attention", fn, 1 if a.no_graph else 4, nbytes=2 * ctx * nkv * hd * 2)
+            if r:
+                print(f"attention_decode_ctx,{ctx},{hd},1,{r}", flush=True)
+            del kpool, vpool
     st = K.check_status(dev)
     print(f"# device_status {st}")
     return 0 if st == 0 else 1
