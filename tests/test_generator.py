@@ -142,3 +142,20 @@ def test_mtp_speculation_equals_plain_greedy():
     spec = g.generate(Request(p, max_tokens=14, cache_prefix=False))
     assert spec["tokens"] == plain["tokens"]
     assert g.metrics.spec["rounds"] > 0 and g.metrics.spec["proposed"] == 3 * g.metrics.spec["rounds"]
+
+
+def test_reasoning_budget_forces_the_closing_sequence(model):
+    gen, _ = make(model)
+    prompt = [(11 * i + 5) % 250 for i in range(30)]
+    free = gen.generate(Request(prompt=prompt, max_tokens=24))["tokens"]
+    close = [201, 202, 203]
+    assert not any(t in close for t in free)
+    out = gen.generate(Request(prompt=prompt, max_tokens=24, think_open=True, think_end_id=202, think_close=close,
+                               thinking_budget=5))["tokens"]
+    k = out.index(close[0])
+    assert out[:k] == free[:k] and 3 <= k <= 5       # untouched while inside the budget
+    assert out[k:k + 3] == close and len(out) == 24  # then the closing sequence, then the model goes on
+    # a block that closes by itself is left alone
+    own = gen.generate(Request(prompt=prompt, max_tokens=12, think_open=True, think_end_id=free[2], think_close=close,
+                               thinking_budget=8))["tokens"]
+    assert own == free[:12]

@@ -41,6 +41,7 @@ struct AttnParams {
   float scale_log2;  // softmax scale * log2(e)
   int window;
   int* status;
+  int nst;          // pipeline stages of the page loads (2 or 3)
   int* tickets;     // optional [tiles * nkv], zero between launches: the CTA that finishes a (tile, kv head) last merges
                     // the split partials itself (key-split kernel only), so no separate merge launch is needed
 };
@@ -83,7 +84,8 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   constexpr int NT_O = HD / 8;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full[2];
+  __shared__ uint64_t full[3];
+  const int nst = p.nst;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -126,6 +128,7 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   if (tid == 0) {
     mbar_init(&full[0], 1);
     mbar_init(&full[1], 1);
+    mbar_init(&full[2], 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -149,7 +152,8 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
       tma_load_2d(vb + c * 8192, &vmap, &full[stage], c * 64, row);
     }
   };
-  if (tid == 0 && kt_begin < kt_end) issue(kt_begin, 0);
+  if (tid == 0)
+    for (int i = 0; i < nst - 1 && kt_begin + i < kt_end; ++i) issue(kt_begin + i, i);
 
   // Q fragments straight from global memory
   uint32_t qf[KSTEPS][4];
@@ -171,17 +175,18 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   const uint32_t smem_base = smem_u32(smem);
   bool failed = false;
   for (int kt = kt_begin; kt < kt_end; ++kt) {
-    const int it = kt - kt_begin, stage = it & 1;
-    const bool ok = mbar_wait(&full[stage], (it >> 1) & 1);
+    const int it = kt - kt_begin, stage = it % nst;
+    const bool ok = mbar_wait(&full[stage], (it / nst) & 1);
     if (!__syncthreads_and(ok)) {
       failed = true;
       break;
     }
-    if (tid == 0 && kt + 1 < kt_end) issue(kt + 1, stage ^ 1);
+    // the stage of the previous iteration is free now (every warp passed the barrier above): refill it
+    if (tid == 0 && kt + nst - 1 < kt_end) issue(kt + nst - 1, (it + nst - 1) % nst);
     if (F8) {
       // expand the page: 16 E5M2 bytes -> two 16-byte bf16 chunks at their swizzled place
       const uint8_t* st8 = smem + stage * 2 * T8;
-      uint8_t* conv = smem + 4 * T8;
+      uint8_t* conv = smem + nst * 2 * T8;
       constexpr int CPT = kPageTok * (HD / 16);
       for (int idx = tid; idx < 2 * CPT; idx += NW * 32) {
         const int tile = idx / CPT, rem = idx % CPT;
@@ -207,7 +212,7 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
       }
       __syncthreads();
     }
-    const uint32_t kb = F8 ? smem_base + 4 * T8 : smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+    const uint32_t kb = F8 ? smem_base + nst * 2 * T8 : smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
 
     // S = Q K^T  (16 rows x 64 keys per warp)
     constexpr int NP = KS ? 1 : 4;           // 16-key slices this warp scores per page
@@ -431,12 +436,14 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
 template <int HD, int NW, bool KS, bool F8>
 static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
                        cudaStream_t st) {
-  constexpr int smem = 2 * 2 * kPageTok * HD * 2 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  constexpr int TILE = kPageTok * HD * 2;
+  const int smem = (F8 ? p.nst * TILE + 2 * TILE : p.nst * 2 * TILE) + 1024;
+  if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+  static int attr_smem = 0;
+  if (smem > attr_smem) {
     cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_smem = smem;
   }
   dim3 grid(ntiles, p.nkv, p.nsplit);
   launch_pdl(attn_kernel<HD, NW, KS, F8>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
@@ -481,6 +488,11 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   p.window = window;
   p.status = (int*)status;
   p.tickets = (warps == 104 && nsplit > 1) ? (int*)tickets : nullptr;
+  {
+    static int stages = 0;      // VOLTA_ATTN_STAGES: page-load pipeline depth of the key-split decode kernel
+    if (!stages) { const char* e = getenv("VOLTA_ATTN_STAGES"); stages = (e && e[0] == '2') ? 2 : 3; }   // 3: -8 % at 16K keys
+    p.nst = (warps == 104 && hd <= 128) ? stages : 2;
+  }
   CUtensorMap kmap, vmap;
   const uint64_t total_rows = (uint64_t)pool_pages * nkv * kPageTok;
   int rc;

@@ -35,6 +35,15 @@ class Request:
     cache_prefix: bool = True
     checkpoints: list[int] = field(default_factory=list)   # extra snapshot positions (system prompt / turn ends)
     ignore_eos: bool = False
+    # reasoning block control: the request starts inside an open block when the template opened it; after
+    # ``thinking_budget`` reasoning tokens the closing sequence ``think_close`` is forced (soft close)
+    think_open: bool = False
+    think_end_id: int = -1        # id of the token that closes the block
+    think_close: list[int] = field(default_factory=list)
+    thinking_budget: int = 0      # 0 = unlimited
+    steer: object = None          # runtime.steering.SteerFile applied to this request's slot
+    steer_scale: float = 1.0
+    steer_scope: int | None = None
     id: int = 0
     cancelled: bool = False
     t_submit: float = 0.0
@@ -63,6 +72,9 @@ class SlotState:
     t_restore_ms: float = 0.0
     t_store_ms: float = 0.0
     last_emit: float = 0.0
+    think_open: bool = False      # currently inside the reasoning block
+    think_count: int = 0          # reasoning tokens produced so far
+    forced: list = field(default_factory=list)   # tokens that replace the next sampled ones
 
 
 class Metrics:
@@ -256,6 +268,13 @@ class Generator:
         s.pending_bytes, s.held = b"", ""
         s.t_start, s.t_first, s.t_prefill_ms, s.t_restore_ms, s.t_store_ms = time.time(), 0.0, 0.0, 0.0, 0.0
         s.cached_tokens = 0
+        s.think_open, s.think_count, s.forced = req.think_open, 0, []
+        steer = getattr(getattr(self.engine, "model", None), "steer", None)
+        if steer is not None:
+            if req.steer is not None:
+                steer.set_slot(s.idx, req.steer, prompt_len=len(req.prompt), scale=req.steer_scale, scope=req.steer_scope)
+            else:
+                steer.clear_slot(s.idx)
         if len(req.prompt) == 0:
             req.prompt = [0]
         if self.cache is not None and req.cache_prefix:
@@ -344,13 +363,14 @@ class Generator:
         if not act:
             return 0
         # speculative round for one slot at a time when it is the only decoder (single-stream latency mode)
-        if self.speculator == "suffix" and len(act) == 1 and act[0].req.params.greedy:
+        budgeted = any(s.think_open and s.req.thinking_budget > 0 or s.forced for s in act)   # plain steps while a budget runs
+        if not budgeted and self.speculator == "suffix" and len(act) == 1 and act[0].req.params.greedy:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
                 n = self._suffix_round(s)
                 if n:
                     return n
-        if self.mtp is not None and len(act) == 1 and act[0].req.params.greedy and act[0].idx in self.mtp.hidden:
+        if not budgeted and self.mtp is not None and len(act) == 1 and act[0].req.params.greedy and act[0].idx in self.mtp.hidden:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
                 return self._mtp_round(s)
@@ -376,6 +396,7 @@ class Generator:
                 for s in act:            # batched plain steps do not maintain the head: drop its state
                     self.mtp.release(s.idx)
         for s, t, c in zip(act, toks, cands):
+            t = self._think_gate(s, t)
             s.pos += 1
             s.next_tok = t
             if s.ctrl is not None:
@@ -386,6 +407,26 @@ class Generator:
                        "top": [(i, l - c.lse) for i, l in list(zip(c.ids, c.logits))[: s.req.params.logprobs]]}]
             self._emit(s, [t], lp)
         return len(act)
+
+    def _think_gate(self, s: SlotState, t: int) -> int:
+        """Reasoning budget: counts tokens inside the open block and, once the budget is spent, replaces the sampled
+        tokens by the closing sequence (the model then continues with its answer)."""
+        req = s.req
+        if s.forced:
+            t = s.forced.pop(0)
+        elif s.think_open and req.thinking_budget > 0 and req.think_close:
+            if t != req.think_end_id and s.think_count + 1 >= req.thinking_budget:
+                s.forced = list(req.think_close)
+                t = s.forced.pop(0)
+        if s.think_open:
+            if t == req.think_end_id:
+                s.think_open = False
+                steer = getattr(getattr(self.engine, "model", None), "steer", None)
+                if steer is not None and req.steer is not None:
+                    steer.set_think_end(s.idx, s.pos + 1)
+            else:
+                s.think_count += 1
+        return t
 
     def _mtp_round(self, s: SlotState) -> int:
         t0 = time.time()
@@ -545,6 +586,9 @@ class Generator:
         self.engine.kv.release(s.idx)
         if self.mtp is not None:
             self.mtp.release(s.idx)
+        steer = getattr(getattr(self.engine, "model", None), "steer", None)
+        if steer is not None and req.steer is not None:
+            steer.clear_slot(s.idx)
         s.req, s.phase = None, "idle"
         if req.on_finish:
             req.on_finish(reason, usage)
