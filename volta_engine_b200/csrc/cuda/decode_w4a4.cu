@@ -468,7 +468,13 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
                  (const __nv_bfloat16*)pn_w, (const __nv_bfloat16*)pn_resid, (const __nv_bfloat16*)pn_delta,
                  (__nv_bfloat16*)pn_resid_out, pn_eps, pn_wbias};
 #define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, ks, pdl, st)
-  if (terms == 4) { if (bn == 16) VE_DW(16, 4, 4); if (bn == 32) VE_DW(32, 4, 4); VE_DW(64, 4, 3); }
+  static int stages3 = -1;       // VOLTA_DW_STAGES=3: three pipeline stages (three CTAs per SM) for the one-row shapes
+  if (stages3 < 0) { const char* e = getenv("VOLTA_DW_STAGES"); stages3 = (e && e[0] == '3') ? 1 : 0; }
+  if (terms == 4) {
+    if (bn == 16) { if (stages3) VE_DW(16, 4, 3); VE_DW(16, 4, 4); }
+    if (bn == 32) VE_DW(32, 4, 4);
+    VE_DW(64, 4, 3);
+  }
   if (terms == 2) { if (bn == 16) VE_DW(16, 2, 4); if (bn == 32) VE_DW(32, 2, 4); VE_DW(64, 2, 3); }
   if (bn == 16) VE_DW(16, 1, 4);
   if (bn == 32) VE_DW(32, 1, 4);

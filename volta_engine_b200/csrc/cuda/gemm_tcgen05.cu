@@ -48,6 +48,28 @@ VE_DEVINL uint32_t e2m1x2_to_f16x2(uint32_t byte) {
   asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "r"(byte));
   return r;
 }
+// Eight E2M1 codes (nibble i = element i) -> four bf16x2 words, by table lookup on the byte-permute unit instead of
+// conversion instructions: the bf16 patterns of {0, .5, 1, 1.5, 2, 3, 4, 6} are 0x0000 3F00 3F80 3FC0 4000 4040 4080
+// 40C0; prmt picks their low and high bytes with the codes' magnitudes as selector, a third lookup turns the sign
+// bits into 0x80 bytes, and two more permutes interleave low and high bytes.
+VE_DEVINL void e2m1x8_to_bf16x8(uint32_t w, uint32_t* o) {
+  const uint32_t mags = w & 0x77777777u, sg = (w >> 3) & 0x11111111u;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t sel = mags >> (16 * h), ssel = sg >> (16 * h);
+    const uint32_t lo4 = __byte_perm(0xC0800000u, 0xC0804000u, sel);
+    const uint32_t hi4 = __byte_perm(0x3F3F3F00u, 0x40404040u, sel) | __byte_perm(0x00008000u, 0u, ssel);
+    o[2 * h] = __byte_perm(lo4, hi4, 0x5140);
+    o[2 * h + 1] = __byte_perm(lo4, hi4, 0x7362);
+  }
+}
+VE_DEVINL uint32_t e4m3_to_bf16x2_dup(uint32_t byte) {  // both halves = the scale (exact: 3 mantissa bits)
+  uint32_t r;
+  asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(r) : "r"(byte | (byte << 8)));
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&r));
+  const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+  return *reinterpret_cast<const uint32_t*>(&b);
+}
 VE_DEVINL uint32_t e4m3_to_f16x2_dup(uint32_t byte) {  // both halves = the scale
   uint32_t r;
   asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(r) : "r"(byte | (byte << 8)));
@@ -217,19 +239,18 @@ gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap, const 
           const uint4 w = *reinterpret_cast<const uint4*>(raw + q * 16);
           const uint32_t words[4] = {w.x, w.y, w.z, w.w};
           const uint32_t s2 = *reinterpret_cast<const unsigned short*>(sc + row * 8 + part * 2);
-          const uint32_t sca = e4m3_to_f16x2_dup(s2 & 0xffu), scb = e4m3_to_f16x2_dup(s2 >> 8);
+          const uint32_t sca = e4m3_to_bf16x2_dup(s2 & 0xffu), scb = e4m3_to_bf16x2_dup(s2 >> 8);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {  // 8 elements -> one 16 B chunk of f16
+          for (int j = 0; j < 4; ++j) {  // 8 elements -> one 16 B chunk of bf16
             const uint32_t scale = j < 2 ? sca : scb;
             uint32_t o4[4];
+            e2m1x8_to_bf16x8(words[j], o4);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-              const uint32_t h2 = e2m1x2_to_f16x2((words[j] >> (8 * b)) & 0xffu);
-              // code x scale has <= 6 significant bits: exact in f16 and in bf16
-              const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&h2), *reinterpret_cast<const __half2*>(&scale));
-              const float2 rf = __half22float2(r);
-              const __nv_bfloat162 rb = __floats2bfloat162_rn(rf.x, rf.y);
-              o4[b] = *reinterpret_cast<const uint32_t*>(&rb);
+              // code x scale has <= 6 significant bits: the bf16 product is exact
+              const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o4[b]),
+                                               *reinterpret_cast<const __nv_bfloat162*>(&scale));
+              o4[b] = *reinterpret_cast<const uint32_t*>(&r);
             }
             const int chunk = part * 4 + j;  // 0..15 along K (8 elements each)
             const int sub = chunk >> 3, ch = chunk & 7;
