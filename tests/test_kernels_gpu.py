@@ -236,3 +236,25 @@ def test_gguf_fused_gemv_and_dequant(gtype):
     assert torch.equal(one, full[:1]), "first row differs between M=1 and M=16"
     big = lin.forward(rnd(40, Kd, seed=42))
     assert_close(big.cpu(), rnd(40, Kd, seed=42).cpu().float() @ wd.t(), name="gguf prefill path")
+
+
+def test_rope_store_multimodal_sections():
+    nq, nkv, hd, rows = 8, 2, 128, 5
+    kpool, vpool, table = _kv_setup(nkv, hd, 2, 256, 16)
+    qkv = rnd(rows, (nq + 2 * nkv) * hd, seed=26)
+    pos = torch.tensor([0, 1, 2, 3, 40], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([0, 0, 0, 0, 1], dtype=torch.int32, device=DEV)
+    pos3 = torch.tensor([[0, 1, 1, 1, 9], [0, 0, 1, 1, 9], [0, 0, 0, 5, 9]], dtype=torch.int32, device=DEV)
+    q_ref, k_ref, v_ref = qkv.cpu().clone(), kpool.cpu().clone(), vpool.cpu().clone()
+    ref.rope_store(q_ref, pos.cpu(), slot.cpu(), table.cpu(), k_ref, v_ref, nq, nkv, hd, 128, 1e6, False, 1.0,
+                   (pos3.cpu(), (16, 24)))
+    K.rope_store(qkv, pos, slot, table, kpool, vpool, nq, nkv, hd, 128, 1e6, False, 1.0, (pos3, (16, 24)))
+    assert_close(qkv.cpu(), q_ref, name="mrope q/k")
+    assert_close(kpool.cpu(), k_ref, name="mrope k cache")
+    # equal positions in the three rows reduce to the ordinary rotary embedding
+    q2 = rnd(rows, (nq + 2 * nkv) * hd, seed=26)
+    same = torch.stack([pos, pos, pos]).contiguous()
+    a, b = q2.clone(), q2.clone()
+    K.rope_store(a, pos, slot, table, kpool.clone(), vpool.clone(), nq, nkv, hd, 128, 1e6, False, 1.0, (same, (16, 24)))
+    K.rope_store(b, pos, slot, table, kpool.clone(), vpool.clone(), nq, nkv, hd, 128, 1e6, False)
+    assert torch.equal(a, b)

@@ -174,3 +174,41 @@ def test_moe_family_directories_load_and_generate(tmp_path, mla):
                       **({"v_head_dim": 0} if mla else {}))
     out, _ = Engine(model, kv, use_graphs=False, prefill_chunk=16).generate(list(range(20)), 3)
     assert len(out) == 3
+
+
+def test_gguf_model_directory_loads_and_matches_the_safetensors_twin(tmp_path):
+    """The same random weights stored as bf16 safetensors and as a GGUF file (Q8_0 linears, F32 norms, llama.cpp tensor
+    names) give the same first token; the GGUF linears stay block-quantised in memory."""
+    cfg = DenseConfig(n_layers=2, hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, vocab=512, qk_norm=True)
+    st_dir, gg_dir = tmp_path / "st", tmp_path / "gg"
+    save_dense_checkpoint(st_dir, cfg, seed=9, fmt="bf16", std=0.05)
+    repo = SafeTensorsRepo(st_dir)
+    gg_dir.mkdir()
+    (gg_dir / "config.json").write_text((st_dir / "config.json").read_text())
+    inv = {"input_layernorm": "attn_norm", "post_attention_layernorm": "ffn_norm", "self_attn.q_proj": "attn_q",
+           "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v", "self_attn.o_proj": "attn_output",
+           "self_attn.q_norm": "attn_q_norm", "self_attn.k_norm": "attn_k_norm", "mlp.gate_proj": "ffn_gate",
+           "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down"}
+    tensors = {}
+    for name in repo.names():
+        t = repo.load(name).float()
+        if name.startswith("model.layers."):
+            _, _, li, rest = name.split(".", 3)
+            inner, kind = rest.rsplit(".", 1)
+            gname = f"blk.{li}.{inv[inner]}.{kind}"
+        else:
+            gname = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+                     "lm_head.weight": "output.weight"}[name]
+        if t.dim() == 2 and "embd" not in gname and gname != "output.weight":
+            tensors[gname] = (gq.quantize(t, gq.GGML_Q8_0), gq.GGML_Q8_0, tuple(t.shape))
+        else:
+            tensors[gname] = (t.contiguous(), 0, tuple(t.shape))
+    write_gguf(gg_dir / "model.gguf", {"general.architecture": "qwen3", "qwen3.block_count": 2}, tensors)
+    mg, _ = load_model(gg_dir, "cpu")
+    ms, _ = load_model(st_dir, "cpu")
+    assert type(mg.layers[0].qkv).__name__ in ("LinearGroup", "LinearGGUF")
+    outs = []
+    for m in (mg, ms):
+        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 2, 256, "cpu")
+        outs.append(Engine(m, kv, use_graphs=False, prefill_chunk=32).generate(list(range(30)), 3)[0])
+    assert outs[0][0] == outs[1][0]

@@ -148,7 +148,7 @@ __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __
                                   const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
                                   __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nq,
                                   int nkv, int hd, int rot_dim, float theta, int interleaved, float pos_scale,
-                                  int kv_fp8) {
+                                  int kv_fp8, const int* __restrict__ pos3, int sec0, int sec1) {
   grid_dep_launch();
   grid_dep_wait();
   const int row = blockIdx.x, head = blockIdx.y;
@@ -172,7 +172,9 @@ __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __
   if (i < half) {
     const float inv_freq = exp2f(-log2f(theta) * (2.f * (float)i / (float)rot_dim));
     float sn, cs;
-    sincosf((float)p * pos_scale * inv_freq, &sn, &cs);
+    // multimodal rotary embedding: the pair's section picks the time / height / width position of the row
+    const int pr = pos3 ? pos3[(i < sec0 ? 0 : (i < sec0 + sec1 ? 1 : 2)) * (long)gridDim.x + row] : p;
+    sincosf((float)pr * pos_scale * inv_freq, &sn, &cs);
     const float r0 = a0 * cs - a1 * sn, r1 = a1 * cs + a0 * sn;
     a0 = r0;
     a1 = r1;
@@ -299,13 +301,13 @@ int ve_embed(const void* ids, const void* table, void* out, int rows, int H, int
 
 int ve_rope_store(void* qkv, const void* pos, const void* slot, const void* page_table, int max_pages, void* kpool,
                   void* vpool, int rows, int nq, int nkv, int hd, int rot_dim, float theta, int interleaved,
-                  float pos_scale, int kv_fp8, cudaStream_t st) {
+                  float pos_scale, int kv_fp8, const void* pos3, int sec0, int sec1, cudaStream_t st) {
   if (hd % 2 || rot_dim % 2 || rot_dim > hd || hd / 2 > 1024) return cudaErrorInvalidValue;
   if (rows <= 0) return 0;
   dim3 grid(rows, nq + nkv);
   launch_pdl(rope_store_kernel, grid, dim3(hd / 2), 0, st, (__nv_bfloat16*)qkv, (const int*)pos, (const int*)slot,
              (const int*)page_table, max_pages, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, nq, nkv, hd, rot_dim,
-             theta, interleaved, pos_scale, kv_fp8);
+             theta, interleaved, pos_scale, kv_fp8, (const int*)pos3, sec0, sec1);
   VE_CHECK_LAUNCH();
 }
 

@@ -79,16 +79,18 @@ def embed(ids, table, out=None, scale=1.0):
 
 
 def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved=False,
-               pos_scale=1.0):
-    """Rotate q, k inside ``qkv`` in place and write k, v rows into the paged cache."""
+               pos_scale=1.0, mrope=None):
+    """Rotate q, k inside ``qkv`` in place and write k, v rows into the paged cache. ``mrope`` = (pos3 [3, rows] int32,
+    (s0, s1)): multimodal rotary embedding with time / height / width sections of s0 / s1 / rest rotary pairs."""
     if not qkv.is_cuda:
         ref.rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved,
-                       pos_scale)
+                       pos_scale, mrope)
         return
     rows = qkv.shape[0]
-    call("rope_store", "ppppippiiiiififi", ptr(qkv), ptr(pos), ptr(slot), ptr(page_table), page_table.shape[1],
+    pos3, (s0, s1) = mrope if mrope is not None else (None, (0, 0))
+    call("rope_store", "ppppippiiiiififipii", ptr(qkv), ptr(pos), ptr(slot), ptr(page_table), page_table.shape[1],
          ptr(kpool), ptr(vpool), rows, nq, nkv, hd, rot_dim, float(theta), 1 if interleaved else 0,
-         float(pos_scale), 1 if kpool.dtype == torch.float8_e5m2 else 0)
+         float(pos_scale), 1 if kpool.dtype == torch.float8_e5m2 else 0, ptr(pos3), s0, s1)
 
 
 def gated_act(gu, I, act=0, limit=0.0, out=None, interleave=0):

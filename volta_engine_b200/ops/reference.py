@@ -39,13 +39,20 @@ def rmsnorm_heads(x, w, heads, hd, eps, wbias=0.0):
     return (v * inv * (w.float() + wbias)).to(x.dtype).reshape(rows, heads * hd)
 
 
-def rope_rotate(v, pos, rot_dim, theta, interleaved=False, pos_scale=1.0):
-    """v [rows, heads, hd] -> rotated copy (fp32 math, rounded to v.dtype)."""
+def rope_rotate(v, pos, rot_dim, theta, interleaved=False, pos_scale=1.0, mrope=None):
+    """v [rows, heads, hd] -> rotated copy (fp32 math, rounded to v.dtype). ``mrope`` = (pos3 [3, rows], (s0, s1)):
+    rotary pairs [0, s0) turn with pos3[0] (time), [s0, s0+s1) with pos3[1] (height), the rest with pos3[2] (width)."""
     rows, heads, hd = v.shape
     half = rot_dim // 2
     i = torch.arange(half, device=v.device, dtype=torch.float32)
     inv_freq = torch.exp2(-math.log2(theta) * (2.0 * i / rot_dim))
-    ang = pos.float()[:, None] * pos_scale * inv_freq[None, :]
+    if mrope is not None:
+        pos3, (s0, s1) = mrope
+        sec = torch.where(torch.arange(half) < s0, 0, torch.where(torch.arange(half) < s0 + s1, 1, 2))
+        pp = pos3.float()[sec].t()                                  # [rows, half]
+        ang = pp * pos_scale * inv_freq[None, :]
+    else:
+        ang = pos.float()[:, None] * pos_scale * inv_freq[None, :]
     cs, sn = ang.cos()[:, None, :], ang.sin()[:, None, :]
     vf = v.float().clone()
     if interleaved:
@@ -63,13 +70,13 @@ def rope_rotate(v, pos, rot_dim, theta, interleaved=False, pos_scale=1.0):
 
 
 def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved=False,
-               pos_scale=1.0):
+               pos_scale=1.0, mrope=None):
     rows = qkv.shape[0]
     q = qkv[:, : nq * hd].reshape(rows, nq, hd)
     k = qkv[:, nq * hd:(nq + nkv) * hd].reshape(rows, nkv, hd)
     v = qkv[:, (nq + nkv) * hd:].reshape(rows, nkv, hd)
-    qr = rope_rotate(q, pos, rot_dim, theta, interleaved, pos_scale)
-    kr = rope_rotate(k, pos, rot_dim, theta, interleaved, pos_scale)
+    qr = rope_rotate(q, pos, rot_dim, theta, interleaved, pos_scale, mrope)
+    kr = rope_rotate(k, pos, rot_dim, theta, interleaved, pos_scale, mrope)
     qkv[:, : nq * hd] = qr.reshape(rows, -1)
     qkv[:, nq * hd:(nq + nkv) * hd] = kr.reshape(rows, -1)
     for r in range(rows):
