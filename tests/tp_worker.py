@@ -71,6 +71,20 @@ def main():
         if hi > lo:
             assert cos(shard[: hi - lo], ref_res[lo:hi]) > 0.9999
     # --- shard argmax merge
+    # --- decode linear that sends its result rows from its own epilogue == linear, then all-reduce that sends
+    from volta_engine_b200.ops.linear import LinearNVFP4
+    gl = torch.Generator(device=dev).manual_seed(100 + rank)
+    lin = LinearNVFP4.from_dense(torch.randn(H, 512, device=dev, generator=gl) * 0.05, search=False).prepare()
+    for rows in (1, 3, 16):
+        xin = torch.randn(rows, 512, device=dev, generator=gl).bfloat16()
+        r1 = torch.randn(rows, H, device=dev, generator=torch.Generator(device=dev).manual_seed(11)).bfloat16()
+        r2 = r1.clone()
+        y_push = lin.forward(xin, push=comm)
+        assert comm.pushed == (comm.push_target(rows, H) != 0)
+        a_out = comm.allreduce_add_norm(y_push, r1, w, 1e-6, 0.0).clone()
+        b_out = comm.allreduce_add_norm(lin.forward(xin), r2, w, 1e-6, 0.0)
+        assert torch.equal(a_out, b_out) and torch.equal(r1, r2), f"fused send differs at rows={rows}"
+        same_on_all_ranks(a_out, "fused send")
     val = torch.randn(4, device=dev, generator=g)
     idx = torch.randint(0, 1000, (4,), device=dev, generator=g, dtype=torch.int32) + rank * 1000
     merged = comm.merge_argmax(idx, val).clone()

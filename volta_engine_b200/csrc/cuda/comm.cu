@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
                                                             long part_stride, __nv_bfloat16* __restrict__ residual,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             __nv_bfloat16* __restrict__ out, long out_stride, int H,
-                                                            float eps, float wbias) {
+                                                            float eps, float wbias, int pushed) {
   extern __shared__ float rowbuf[];  // H floats (MODE 1)
   __shared__ float red[33];
   __shared__ int s_timeout;
@@ -103,8 +103,8 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
   __syncthreads();
   const __nv_bfloat16* prow = partial + (long)row * part_stride;
   const size_t slot_me = a.off_ll + ((size_t)(stage * a.size + a.rank) * kLLMaxRows + row) * a.ll_row_bytes;
-  // push
-  for (int l = tid; l < lines; l += blockDim.x) {
+  // push (skipped when the kernel that produced ``partial`` already sent the lines from its epilogue)
+  for (int l = tid; l < lines && !pushed; l += blockDim.x) {
     const uint2 d = *reinterpret_cast<const uint2*>(prow + l * 4);
     const uint4 pkt = make_uint4(d.x, seq, d.y, seq);
 #pragma unroll
@@ -388,13 +388,14 @@ int ve_ll_allreduce(const void* args, int mode, const void* partial, long part_s
   if (rows > kLLMaxRows || H % 4 || (size_t)(H / 4) * 16 > a.ll_row_bytes) return cudaErrorInvalidValue;
   int threads = ((H / 4 + 31) / 32) * 32;
   threads = threads > 1024 ? 1024 : threads;
-  if (mode == 0)
+  const int pushed = (mode >> 1) & 1;      // bit 1: the producer of ``partial`` already sent this rank's lines
+  if ((mode & 1) == 0)
     ll_allreduce_kernel<0><<<rows, threads, 0, st>>>(a, (const __nv_bfloat16*)partial, part_stride, nullptr, nullptr,
-                                                     (__nv_bfloat16*)out, out_stride, H, eps, wbias);
+                                                     (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed);
   else
     ll_allreduce_kernel<1><<<rows, threads, H * sizeof(float), st>>>(
         a, (const __nv_bfloat16*)partial, part_stride, (__nv_bfloat16*)residual, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)out, out_stride, H, eps, wbias);
+        (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed);
   VE_CHECK_LAUNCH();
 }
 

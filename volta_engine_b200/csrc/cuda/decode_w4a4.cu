@@ -130,6 +130,13 @@ struct DecodeParams {
   const __nv_bfloat16* pn_delta;      // may be null (plain RMSNorm of resid)
   __nv_bfloat16* pn_resid_out;        // may be null when delta is null
   float pn_eps, pn_wbias;
+  // Optional fused all-reduce send (tensor parallel decode): the CTA that holds a tile's final sums also writes them,
+  // as low-latency lines {data, seq, data, seq}, into this rank's slot of every peer's staging area, so the
+  // all-reduce kernel behind only has to wait, add and normalise. Null peers[0]: off.
+  uint8_t* ll_peer[8];
+  const uint32_t* ll_seq;
+  int ll_rank, ll_size;
+  size_t ll_off, ll_row_bytes;
 };
 
 // Warp roles (192 threads): warp 0 = TMA producer of weight tiles and their scale atoms; warp 1 = TMEM owner and
@@ -390,6 +397,24 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
           if (p.residual) v += bf2f(p.residual[(long)m * p.ldr + n]);
           if (p.out_f32) p.out_f32[(long)m * p.ldo + n] = v;
           else p.out[(long)m * p.ldo + n] = f2bf(v);
+          if (p.ll_seq) {
+            // four neighbouring features make one 16-byte line; lane 4j sends it to every peer
+            const uint32_t bits = (uint32_t)__bfloat16_as_ushort(f2bf(v));
+            const uint32_t b1 = __shfl_down_sync(0xffffffffu, bits, 1), b2 = __shfl_down_sync(0xffffffffu, bits, 2),
+                           b3 = __shfl_down_sync(0xffffffffu, bits, 3);
+            if ((lane & 3) == 0) {
+              const uint32_t seq = *p.ll_seq;
+              const int stage = seq & 3;
+              const size_t slot = p.ll_off + ((size_t)(stage * p.ll_size + p.ll_rank) * 16 + m) * p.ll_row_bytes +
+                                  (size_t)(n >> 2) * 16;
+              const uint4 pkt = make_uint4(bits | (b1 << 16), seq, b2 | (b3 << 16), seq);
+              for (int i = 1; i < p.ll_size; ++i) {
+                uint8_t* dst = p.ll_peer[(p.ll_rank + i) % p.ll_size] + slot;
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(pkt.x), "r"(pkt.y),
+                             "r"(pkt.z), "r"(pkt.w) : "memory");
+              }
+            }
+          }
         }
       }
     }
@@ -449,7 +474,8 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
 int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, void* out, long ldo, void* out_f32,
                    const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, int act,
                    float act_limit, const void* pn_w, const void* pn_resid, const void* pn_delta, void* pn_resid_out,
-                   float pn_eps, float pn_wbias, void* ws, void* tickets, void* status, cudaStream_t st) {
+                   float pn_eps, float pn_wbias, const void* comm_args, void* ws, void* tickets, void* status,
+                   cudaStream_t st) {
   if (act && (out_f32 || residual || !out)) return cudaErrorInvalidValue;
   if (pn_w && (M > 4 || !pn_resid || K % 16 || (pn_delta && pn_resid_out == pn_resid))) return cudaErrorInvalidValue;
   if (M < 1 || N % 128 || K % 256 || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
@@ -467,6 +493,17 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
                  (float*)out_f32, (const uint8_t*)sfa, (float*)ws, (int*)tickets, (int*)status, tpt, act, act_limit,
                  (const __nv_bfloat16*)pn_w, (const __nv_bfloat16*)pn_resid, (const __nv_bfloat16*)pn_delta,
                  (__nv_bfloat16*)pn_resid_out, pn_eps, pn_wbias};
+  p.ll_seq = nullptr;
+  for (int i = 0; i < 8; ++i) p.ll_peer[i] = nullptr;
+  if (comm_args) {
+    // leading fields of ve::CommArgs (csrc/cuda/comm.cu): peer[8], mc, rank, size, seq, status, budget, off_ll, ll_row_bytes
+    struct Lead { uint8_t* peer[8]; uint8_t* mc; int rank, size; uint32_t* seq; int* status; unsigned long long budget;
+                  size_t off_ll, ll_row_bytes; };
+    const Lead& a = *reinterpret_cast<const Lead*>(comm_args);
+    if (act || out_f32 || residual || M > 16 || (size_t)N * 4 > a.ll_row_bytes) return cudaErrorInvalidValue;
+    for (int i = 0; i < 8; ++i) p.ll_peer[i] = a.peer[i];
+    p.ll_seq = a.seq; p.ll_rank = a.rank; p.ll_size = a.size; p.ll_off = a.off_ll; p.ll_row_bytes = a.ll_row_bytes;
+  }
 #define VE_DW(BN, T, S) return launch_decode<BN, T, S>(p, amap, ks, pdl, st)
   static int stages3 = -1;       // VOLTA_DW_STAGES=3: three pipeline stages (three CTAs per SM) for the one-row shapes
   if (stages3 < 0) { const char* e = getenv("VOLTA_DW_STAGES"); stages3 = (e && e[0] == '3') ? 1 : 0; }

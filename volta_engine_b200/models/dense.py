@@ -318,7 +318,14 @@ class DenseModel:
         att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
                           self.scale, window=self.layer_window(li), key_end=b.key_end, tiles=b.tiles,
                           nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
-        return L.o_proj.forward(att, out=pbuf)
+        return self._row_parallel(L.o_proj, att, pbuf)
+
+    def _row_parallel(self, lin, x, pbuf):
+        """Row-parallel projection whose output goes into the layer's all-reduce: on decode rows the NVFP4 decode linear
+        sends its result to the peers from its own epilogue (communicators that offer ``push_target``)."""
+        if pbuf is None and self.comm.size > 1 and hasattr(self.comm, "push_target") and isinstance(lin, LinearNVFP4):
+            return lin.forward(x, push=self.comm)
+        return lin.forward(x, out=pbuf)
 
     def ffn_block(self, li, L, x, b: BatchRows, pbuf):
         """Feed-forward sub-layer: returns this rank's partial of the down projection [n, H]."""
@@ -328,7 +335,7 @@ class DenseModel:
             a = L.gate_up.forward_gated(x, act, cfg.act_limit)
         else:
             a = K.gated_act(L.gate_up.forward(x), self.ffn, act, cfg.act_limit)
-        return L.down.forward(a, out=pbuf)
+        return self._row_parallel(L.down, a, pbuf)
 
     def ensure_workspace(self, max_rows: int, max_splits: int):
         if self.device.type == "cuda" and (self.attn_ws is None or self.attn_ws.max_splits < max_splits):

@@ -356,7 +356,7 @@ DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
 
 
 def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None,
-                act=0, act_limit=0.0, prenorm=None):
+                act=0, act_limit=0.0, prenorm=None, push_args=0):
     """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path; the kernel expands each bf16
     activation row into ``terms`` residual NVFP4 rows itself (bf16-grade accuracy): out [M, N]."""
     N, K = packed.shape[0], packed.shape[1] * 2
@@ -375,11 +375,13 @@ def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=Fa
     assert ks * (N // 128) <= 1024
     if pdl is None:
         pdl = DW_PDL
-    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppppff" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
+    # push_args: address of the communicator's argument block: the epilogue also sends the result rows to every peer's
+    # all-reduce staging area (the all-reduce behind is then called with ``pushed=True``)
+    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppppff" + "pppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
          0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
          residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,
          act, float(act_limit), ptr(pn_w), ptr(pn_resid), ptr(pn_delta), ptr(pn_out), float(pn_eps), float(pn_bias),
-         ptr(ws), ptr(tickets), ptr(status_word(x.device)))
+         int(push_args), ptr(ws), ptr(tickets), ptr(status_word(x.device)))
     return out
 
 

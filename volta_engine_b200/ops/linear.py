@@ -85,7 +85,11 @@ class LinearNVFP4:
     def dequant(self):
         return K.nvfp4_dequant(self.packed, self.scales, self.gscale)
 
-    def forward(self, x, residual=None, out=None):
+    def forward(self, x, residual=None, out=None, push=None):
+        """``push``: a communicator with ``push_target(rows, N)``; when the decode kernel runs, its epilogue also sends
+        the rows into the peers' all-reduce staging area and ``push.pushed`` is set for the collective behind."""
+        if push is not None:
+            push.pushed = False
         if not x.is_cuda:
             y = x.float() @ qn.dequantize_nvfp4(self.packed, self.scales, self.gscale).t()
             if residual is not None:
@@ -96,7 +100,11 @@ class LinearNVFP4:
             # tcgen05 path: the tensor core decodes the FP4 weights itself; activations ride as 4 residual NVFP4
             # terms per row (error below bf16 rounding), cost independent of the row count
             if GEMV_KERNEL in ("auto", "tc") and self._sf_atoms is not None and self._tc_ok():
-                return K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, out=out, residual=residual)
+                target = push.push_target(rows, self.out_features) if (push is not None and residual is None) else 0
+                y = K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, out=out, residual=residual, push_args=target)
+                if target:
+                    push.pushed = True
+                return y
             # one row: the SIMT streaming kernel is faster; 2..16 rows: the tensor-core kernel costs the same
             # as one row. Both sum exact products in fp32, so they agree to fp32 rounding.
             if self._gv is not None and (GEMV_KERNEL == "mma" or (GEMV_KERNEL == "auto" and rows > 1)):

@@ -81,6 +81,8 @@ class SymmComm:
         self.off_part, self.off_xout = off_part, off_xout
         assert _lib.kernels().ve_comm_args_size() == ctypes.sizeof(CommArgs)
         self._arg_idx = torch.empty(LL_MAX_ROWS, dtype=torch.int32, device=self.device)
+        self.pushed = False        # set by a linear whose epilogue already sent its rows (see push_target)
+        self.fuse_push = os.environ.get("VOLTA_FUSE_PUSH", "1") != "0"
         dist.barrier(self.group)
         torch.cuda.synchronize(self.device)
 
@@ -106,6 +108,13 @@ class SymmComm:
         if hi > lo:
             out[: hi - lo] = x[lo:hi]
         return out
+
+    def push_target(self, rows: int, H: int) -> int:
+        """Address of the argument block for a producer kernel that sends its [rows, H] result into the peers' low-latency
+        staging area itself (decode rows only), or 0 when the fused send does not apply."""
+        if not self.fuse_push or rows > LL_MAX_ROWS or H * 4 > self.args.ll_row_bytes or H % 4:
+            return 0
+        return self._args_ptr
 
     # ---- collectives ---------------------------------------------------------------------------
     def allreduce_(self, x: torch.Tensor) -> torch.Tensor:
@@ -134,10 +143,11 @@ class SymmComm:
         rank's row shard [ceil(rows/size), H] and ``partial`` should be ``partial_buffer(rows, H)``.
         Returns the normalised activations [rows, H] (replicated)."""
         rows, H = partial.shape
+        pushed, self.pushed = self.pushed, False
         if rows <= LL_MAX_ROWS:
             if out is None:
                 out = torch.empty_like(partial)
-            _lib.call("ll_allreduce", "piplpppliiff", self._args_ptr, 1, partial.data_ptr(), partial.stride(0),
+            _lib.call("ll_allreduce", "piplpppliiff", self._args_ptr, 3 if pushed else 1, partial.data_ptr(), partial.stride(0),
                       residual.data_ptr(), w.data_ptr(), out.data_ptr(), out.stride(0), rows, H, float(eps),
                       float(wbias))
             return out
