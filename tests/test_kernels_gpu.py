@@ -258,3 +258,23 @@ def test_rope_store_multimodal_sections():
     K.rope_store(a, pos, slot, table, kpool.clone(), vpool.clone(), nq, nkv, hd, 128, 1e6, False, 1.0, (same, (16, 24)))
     K.rope_store(b, pos, slot, table, kpool.clone(), vpool.clone(), nq, nkv, hd, 128, 1e6, False)
     assert torch.equal(a, b)
+
+
+def test_bounded_wait_reports_through_the_status_word():
+    """A wait on a flag that nothing sets runs out after its budget, records the peer-timeout code in the status word and
+    returns; the context stays usable and a wait whose flag is already set finishes clean."""
+    from volta_engine_b200._lib import call, ptr
+    import time
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    t0 = time.time()
+    call("wait_flag", "pilp", ptr(flag), 1, 50_000_000, ptr(status))          # 50 ms budget
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2 and time.time() - t0 < 2.0                   # kErrPeerTimeout
+    status.zero_()
+    flag.fill_(1)
+    call("wait_flag", "pilp", ptr(flag), 1, 50_000_000, ptr(status))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    x = torch.ones(4, device=DEV)
+    assert float((x + 1).sum()) == 8.0                                          # the context still works
