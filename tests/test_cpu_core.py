@@ -92,3 +92,27 @@ def test_sandwich_norm_windowed_model_prefill_equals_decode():
     Engine(m2, kv3, use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
     Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu"), use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
     assert not torch.allclose(m.last_hidden[-1].float(), m2.last_hidden[-1].float(), atol=1e-3)
+
+
+def test_gguf_block_decoders_match_ggml_goldens():
+    """(sum, one element, max |x|) of the decoded synthetic blocks; the numbers were produced by the ggml C row
+    dequantisers on the same bytes (bit-equal to this decoder for all twelve formats when they were taken)."""
+    from volta_engine_b200.quant import gguf as G
+    golden = {
+        3: (5.891298294067383, -0.13057708740234375, 0.30628204345703125),
+        6: (-0.6080513000488281, 0.2533721923828125, 0.313232421875),
+        7: (44.34039878845215, 0.1629791259765625, 0.627166748046875),
+        10: (132.822509765625, -0.012451171875, 0.9476165771484375),
+        11: (9.363227844238281, 0.231536865234375, 1.7039794921875),
+        13: (-4511.329105377197, 0.2799797058105469, 24.929656982421875),
+        20: (17.381572723388672, -0.029878616333007812, 2.507598876953125),
+        23: (1052.876178741455, -0.05899810791015625, 44.815093994140625),
+    }
+    for t, (s, e, m) in golden.items():
+        y = G.dequantize(G.random_blocks(t, 2, 512, seed=100 + t), t, 512).double()
+        assert abs(float(y.sum()) - s) < 1e-6 and float(y[1, 300]) == e and float(y.abs().max()) == m, G.NAMES[t]
+    # the formats with a quantiser round-trip within their step size
+    x = torch.randn(4, 256, generator=torch.Generator().manual_seed(0)) * 0.1
+    for t, tol in ((G.GGML_Q4_1, 0.03), (G.GGML_Q5_0, 0.03), (G.GGML_Q5_1, 0.015), (G.GGML_IQ4_NL, 0.05)):
+        back = G.dequantize(G.quantize(x, t), t, 256)
+        assert float((back - x).abs().max()) < tol, G.NAMES[t]

@@ -219,6 +219,21 @@ def test_argmax_wide_two_stage():
     assert torch.equal(idx.cpu(), ridx) and torch.equal(val.cpu(), rval)
 
 
+@pytest.mark.parametrize("gtype", [3, 6, 7, 10, 11, 13, 20, 23])
+def test_gguf_read_only_formats_on_synthetic_blocks(gtype):
+    """Q4_1, Q5_0/1, Q2_K, Q3_K, Q5_K, IQ4_NL/XS: random payload bytes with finite scales; fused mat-vec and the
+    dequantise kernel against the PyTorch block decoder."""
+    from volta_engine_b200.ops.linear_gguf import LinearGGUF
+    from volta_engine_b200.quant import gguf as gq
+    N, Kd = 520, 1024
+    raw = gq.random_blocks(gtype, N, Kd, seed=gtype, amp=0.01)
+    lin = LinearGGUF(raw.to(DEV), gtype, N, Kd)
+    wd = gq.dequantize(raw, gtype, Kd)
+    assert_close(lin.dequant().cpu(), wd, cos_min=0.9999, rel=0.004, name=f"gguf dequant type {gtype}")
+    x = rnd(5, Kd, seed=43)
+    assert_close(lin.forward(x).cpu(), x.cpu().float() @ wd.t(), name=f"gguf gemv type {gtype}")
+
+
 @pytest.mark.parametrize("gtype", [8, 2, 12, 14])
 def test_gguf_fused_gemv_and_dequant(gtype):
     from volta_engine_b200.ops.linear_gguf import LinearGGUF

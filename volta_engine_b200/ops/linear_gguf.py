@@ -1,4 +1,4 @@
-"""Linear layer over GGUF block-quantised weights (Q8_0, Q4_0, Q4_K, Q6_K; F16/BF16 pass through).
+"""Linear layer over GGUF block-quantised weights (Q8_0, Q4_0/1, Q5_0/1, Q2_K..Q6_K, IQ4_NL/XS; F16/BF16 pass through).
 
 GPU: rows <= 16 use the fused dequant mat-vec (csrc/cuda/gguf_gemv.cu); larger row counts dequantise to bf16
 and run the tcgen05 GEMM. CPU: fp32 oracle, optionally with the CPU backend's Q8_0 activation semantics
@@ -11,6 +11,10 @@ import torch
 from .._lib import call, ptr
 from ..quant import gguf as gq
 from . import kernels as K
+
+
+FUSED_TYPES = frozenset((gq.GGML_Q8_0, gq.GGML_Q4_0, gq.GGML_Q4_K, gq.GGML_Q6_K, gq.GGML_Q4_1, gq.GGML_Q5_0, gq.GGML_Q5_1,
+                         gq.GGML_Q2_K, gq.GGML_Q3_K, gq.GGML_Q5_K, gq.GGML_IQ4_NL, gq.GGML_IQ4_XS))
 
 
 class LinearGGUF:
@@ -26,7 +30,7 @@ class LinearGGUF:
         return cls(gq.quantize(w, ggml_type), ggml_type, w.shape[0], w.shape[1], act_q8)
 
     def dequant(self) -> torch.Tensor:
-        if self.raw.is_cuda and self.ggml_type in (gq.GGML_Q8_0, gq.GGML_Q4_0, gq.GGML_Q4_K, gq.GGML_Q6_K):
+        if self.raw.is_cuda and self.ggml_type in FUSED_TYPES:
             out = torch.empty(self.out_features, self.in_features, dtype=torch.bfloat16, device=self.raw.device)
             call("gguf_dequant", "pilpli", ptr(self.raw), self.ggml_type, self.row_bytes, ptr(out), self.out_features,
                  self.in_features)
@@ -43,7 +47,7 @@ class LinearGGUF:
                 y = y + residual.float()
             return y if out_f32 else y.to(x.dtype)
         rows = x.shape[0]
-        quant = self.ggml_type in (gq.GGML_Q8_0, gq.GGML_Q4_0, gq.GGML_Q4_K, gq.GGML_Q6_K)
+        quant = self.ggml_type in FUSED_TYPES
         if rows <= 16 and quant and residual is None:
             if out is None:
                 out = torch.empty(rows, self.out_features, dtype=torch.float32 if out_f32 else torch.bfloat16,
