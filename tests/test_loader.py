@@ -212,3 +212,68 @@ def test_gguf_model_directory_loads_and_matches_the_safetensors_twin(tmp_path):
         kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 2, 256, "cpu")
         outs.append(Engine(m, kv, use_graphs=False, prefill_chunk=32).generate(list(range(30)), 3)[0])
     assert outs[0][0] == outs[1][0]
+
+
+def test_ngram_table_hashing_and_the_three_row_formats(tmp_path):
+    import numpy as np
+    from volta_engine_b200.loader.ngram_table import ROW_DIM, NgramTable, encode_trellis_row
+    from volta_engine_b200.quant import exl3 as qx
+    rng = np.random.default_rng(0)
+    ngram, hpn = 3, 2
+    sizes = np.array([11, 13, 17, 19], dtype=np.int64)
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64)
+    mult = np.array([0x9E3779B97F4A7C15 - (1 << 64), 1000003, -7046029254386353131], dtype=np.int64)
+    total = int(sizes.sum())
+    # trellis form: random rings decode to codebook values; scale and per-head bias on top
+    K = 6
+    cb = qx.decode_windows(torch.arange(65536), qx.CB_MUL1).numpy()
+    rows = np.zeros((total, 1 + ROW_DIM * K // 16), dtype=np.uint16)
+    plain = np.zeros((total, ROW_DIM), dtype=np.float32)
+    for r in range(total):
+        words, vals = encode_trellis_row(np.zeros(ROW_DIM), K, cb, rng)
+        rows[r, 0] = np.float16(0.5 + 0.01 * r).view(np.uint16)
+        rows[r, 1:] = words
+        plain[r] = vals * np.float32(np.float16(0.5 + 0.01 * r))
+    bias = (torch.randn(4, ROW_DIM) * 0.1).to(torch.float16)
+    write_safetensors(tmp_path / "ngram.safetensors", {
+        "t.head_offsets": torch.from_numpy(offs), "t.head_vocab_sizes": torch.from_numpy(sizes),
+        "t.layer_multipliers": torch.from_numpy(mult), "t.head_bias": bias,
+        "t.shard_0.trellis": torch.from_numpy(rows[:30].view(np.int16)), "t.shard_1.trellis": torch.from_numpy(rows[30:].view(np.int16)),
+    }, metadata={"K": str(K)})
+    t = NgramTable.open_trellis(tmp_path / "ngram.safetensors")
+    assert (t.ngram_size, t.heads_per_ngram, t.num_heads, t.rows_per_shard) == (3, 2, 4, 30)
+    # hashing: wrapping int64 products, xor over the n-gram, non-negative remainder
+    toks = [151643, 77, 123456789]
+    M = (1 << 64)
+    p = [(toks[i] * int(mult[i])) % M for i in range(3)]
+    s64 = lambda v: v - M if v >= (1 << 63) else v
+    mixed2, mixed3 = s64(p[0] ^ p[1]), s64(p[0] ^ p[1] ^ p[2])
+    want = [mixed2 % 11 + 0, mixed2 % 13 + 11, mixed3 % 17 + 24, mixed3 % 19 + 41]
+    ids = t.row_ids(toks)
+    assert ids.tolist() == want
+    for h in range(4):
+        got = t.decode_row(ids[h], h)
+        assert np.allclose(got, plain[ids[h]] + bias[h].float().numpy(), atol=1e-6)
+    assert t.lookup(toks).shape == (4 * ROW_DIM,)
+    seq = t.lookup_sequence([5, 6, 2, 7, 8], eos_id=2)
+    assert seq.shape == (5, 4 * ROW_DIM)
+    assert torch.equal(seq[3], torch.from_numpy(t.lookup([7, 2, 2])))       # history stops at the eos before position 3
+    # fp8 form
+    codes = torch.randint(0, 120, (total, ROW_DIM), dtype=torch.uint8)
+    write_safetensors(tmp_path / "fp8.safetensors", {
+        "m.ngram_heads_offsets": torch.from_numpy(offs), "m.ngram_heads_vocab_sizes": torch.from_numpy(sizes),
+        "m.layer_multipliers": torch.from_numpy(mult), "m.ngram_embedding.weight_scale": torch.tensor([0.25], dtype=torch.bfloat16),
+        "m.ngram_embedding.shard_0.weight": codes.view(torch.float8_e4m3fn)})
+    f = NgramTable.open_fp8(SafeTensorsRepo(tmp_path / "fp8.safetensors"), "m")
+    assert f.row_ids(toks).tolist() == want
+    assert np.allclose(f.decode_row(7, 0), qn.e4m3_decode(codes[7]).float().numpy() * 0.25)
+    # gguf form (IQ4_NL rows)
+    dense = torch.randn(total, ROW_DIM) * 0.05
+    raw = gq.quantize(dense, gq.GGML_IQ4_NL)
+    write_gguf(tmp_path / "t.gguf", {"general.architecture": "qwen4exp", "qwen4exp.ple.head_offsets": offs.tolist(),
+                                     "qwen4exp.ple.head_vocab_sizes": sizes.tolist(), "qwen4exp.ple.layer_multipliers": mult.tolist(),
+                                     "qwen4exp.ple.ngram_size": 3, "qwen4exp.ple.heads_per_ngram": 2},
+               {"per_layer_token_embd.weight": (raw, gq.GGML_IQ4_NL, (total, ROW_DIM))})
+    gt = NgramTable.open_gguf(GGUFFile(tmp_path / "t.gguf"), "per_layer_token_embd.weight")
+    assert gt.row_ids(toks).tolist() == want
+    assert np.allclose(gt.decode_row(9, 0), gq.dequantize(raw[9:10], gq.GGML_IQ4_NL, ROW_DIM)[0].numpy())

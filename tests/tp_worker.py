@@ -85,6 +85,34 @@ def main():
         b_out = comm.allreduce_add_norm(lin.forward(xin), r2, w, 1e-6, 0.0)
         assert torch.equal(a_out, b_out) and torch.equal(r1, r2), f"fused send differs at rows={rows}"
         same_on_all_ranks(a_out, "fused send")
+    # --- all-reduce with a stream epilogue in the same launch == all-reduce, then the epilogue kernel
+    from volta_engine_b200.ops import streams as S
+    ge = torch.Generator(device=dev).manual_seed(21)                       # replicated state: same seed on every rank
+    w2 = (torch.randn(H, device=dev, generator=ge) * 0.1).bfloat16()
+    nw = (torch.randn(4, H, device=dev, generator=ge) * 0.1).bfloat16()
+    for rows in (1, 4, 16):
+        x = torch.randn(rows, H, device=dev, generator=g).bfloat16()
+        y = comm.allreduce_(x.clone())
+        post = torch.rand(rows, 4, device=dev, generator=ge)
+        comb = torch.rand(rows, 4, 4, device=dev, generator=ge)
+        xs = torch.randn(rows, 4, H, device=dev, generator=ge)
+        a, b = xs.clone(), xs.clone()
+        S.hc_update(x, a, post, comb, comm=comm)
+        S.hc_update(y, b, post, comb)
+        assert torch.equal(a, b), f"fused hyper-connection update differs at rows={rows}"
+        add = torch.randn(rows, H, device=dev, generator=ge).bfloat16()
+        gate = torch.rand(rows, device=dev, generator=ge)
+        a, b = xs.clone(), xs.clone()
+        na = S.gated_stream_update(x, a, post, nw, 1e-6, add, gate, comm=comm)
+        nb = S.gated_stream_update(y, b, post, nw, 1e-6, add, gate)
+        assert torch.equal(a, b) and torch.equal(na, nb), f"fused gated stream update differs at rows={rows}"
+        for dt in (torch.float32, torch.bfloat16):
+            r = torch.randn(rows, H, device=dev, generator=ge).to(dt)
+            ra, rb = r.clone(), r.clone()
+            oa = S.sandwich_add_norm(x, ra, w, w2, 1e-6, 1.0, 0.5, comm=comm)
+            ob = S.sandwich_add_norm(y, rb, w, w2, 1e-6, 1.0, 0.5)
+            assert torch.equal(ra, rb) and torch.equal(oa, ob), f"fused sandwich norm differs at rows={rows}"
+        same_on_all_ranks(a, "gated streams")
     val = torch.randn(4, device=dev, generator=g)
     idx = torch.randint(0, 1000, (4,), device=dev, generator=g, dtype=torch.int32) + rank * 1000
     merged = comm.merge_argmax(idx, val).clone()

@@ -6,7 +6,9 @@
 // all-reduce + residual + RMSNorm :136-298, staged pull :300-363, sequence protocol :14-51):
 //   ll_allreduce      one-shot push for <= 16 rows: each 8 B of payload travels as a 16 B line
 //                     {d0, seq, d1, seq}; the reader spins on its own memory until both tags match.
-//                     mode 0: y = sum ; mode 1: residual += bf16(sum); out = RMSNorm(residual) * (w + b).
+//                     mode 0: y = sum ; mode 1: residual += bf16(sum); out = RMSNorm(residual) * (w + b);
+//                     modes 2-4: the sandwich-norm, gated-stream and hyper-connection epilogues of
+//                     stream_epilogues.cuh applied to bf16(sum) in the same launch.
 //   rs_norm_ag        two-shot for prefill chunks: every rank owns T/N rows; it pulls that slice from all
 //                     peers (plain peer loads, or one multimem.ld_reduce through the switch), adds its
 //                     residual shard, normalises, and pushes the normalised rows to every rank
@@ -18,6 +20,7 @@
 // safe). Every wait has a wall-clock budget; on expiry the kernel records kErrPeerTimeout in the status
 // word and completes.
 #include "common.cuh"
+#include "stream_epilogues.cuh"
 
 namespace ve {
 
@@ -91,8 +94,8 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
                                                             long part_stride, __nv_bfloat16* __restrict__ residual,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             __nv_bfloat16* __restrict__ out, long out_stride, int H,
-                                                            float eps, float wbias, int pushed) {
-  extern __shared__ float rowbuf[];  // H floats (MODE 1)
+                                                            float eps, float wbias, int pushed, const EpiArgs epi) {
+  extern __shared__ float rowbuf[];  // H floats (MODE >= 1)
   __shared__ float red[33];
   __shared__ int s_timeout;
   const int row = blockIdx.x, tid = threadIdx.x;
@@ -137,6 +140,12 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
       o.x = *reinterpret_cast<uint32_t*>(&y01);
       o.y = *reinterpret_cast<uint32_t*>(&y23);
       *reinterpret_cast<uint2*>(out + (long)row * out_stride + l * 4) = o;
+    } else if (MODE >= 2) {
+      const float2 f01 = __bfloat1622float2(y01), f23 = __bfloat1622float2(y23);
+      rowbuf[l * 4 + 0] = f01.x;
+      rowbuf[l * 4 + 1] = f01.y;
+      rowbuf[l * 4 + 2] = f23.x;
+      rowbuf[l * 4 + 3] = f23.y;
     } else {
       __nv_bfloat16* rr = residual + (long)row * H + l * 4;
       const uint2 rv = *reinterpret_cast<const uint2*>(rr);
@@ -173,6 +182,10 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
       o.y = *reinterpret_cast<uint32_t*>(&o23);
       *reinterpret_cast<uint2*>(out + (long)row * out_stride + l * 4) = o;
     }
+  }
+  if (MODE >= 2) {
+    __syncthreads();
+    row_epilogue<MODE>(rowbuf, row, epi, red);
   }
   __syncthreads();
   if (tid == 0) {
@@ -391,11 +404,50 @@ int ve_ll_allreduce(const void* args, int mode, const void* partial, long part_s
   const int pushed = (mode >> 1) & 1;      // bit 1: the producer of ``partial`` already sent this rank's lines
   if ((mode & 1) == 0)
     ll_allreduce_kernel<0><<<rows, threads, 0, st>>>(a, (const __nv_bfloat16*)partial, part_stride, nullptr, nullptr,
-                                                     (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed);
+                                                     (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed, EpiArgs{});
   else
     ll_allreduce_kernel<1><<<rows, threads, H * sizeof(float), st>>>(
         a, (const __nv_bfloat16*)partial, part_stride, (__nv_bfloat16*)residual, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed);
+        (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed, EpiArgs{});
+  VE_CHECK_LAUNCH();
+}
+
+// All-reduce of <= 16 decode rows with one of the stream epilogues (mode 2 sandwich, 3 gated streams, 4 hyper-connection)
+// applied to the reduced row in the same launch.
+int ve_ll_allreduce_epi(const void* args, int mode, int pushed, const void* partial, long part_stride, void* xs,
+                        void* res16, const void* post, const void* comb, const void* w, const void* w2,
+                        const void* addend, const void* addend_gate, void* out, void* outf, int rows, int H, int hc, float eps,
+                        float wbias, float scale, cudaStream_t st) {
+  const CommArgs& a = *reinterpret_cast<const CommArgs*>(args);
+  if (rows <= 0) return 0;
+  if (rows > kLLMaxRows || H % 4 || (size_t)(H / 4) * 16 > a.ll_row_bytes) return cudaErrorInvalidValue;
+  EpiArgs e;
+  e.xs = (float*)xs; e.res16 = (__nv_bfloat16*)res16; e.post = (const float*)post; e.comb = (const float*)comb;
+  e.w = (const __nv_bfloat16*)w; e.w2 = (const __nv_bfloat16*)w2; e.addend = (const __nv_bfloat16*)addend;
+  e.addend_gate = (const float*)addend_gate; e.out = (__nv_bfloat16*)out; e.outf = (float*)outf;
+  e.eps = eps; e.wbias = wbias; e.scale = scale; e.hc = hc; e.H = H;
+  int threads = ((H / 4 + 31) / 32) * 32;
+  threads = threads > 1024 ? 1024 : threads;
+  const size_t smem = (size_t)H * sizeof(float);
+#define VE_LLE(M)                                                                                                    \
+  ll_allreduce_kernel<M><<<rows, threads, smem, st>>>(a, (const __nv_bfloat16*)partial, part_stride, nullptr, nullptr, \
+                                                      nullptr, 0, H, eps, wbias, pushed, e)
+  switch (mode) {
+    case kEpiSandwich:
+      if ((!xs && !res16) || !w || !w2 || !out) return cudaErrorInvalidValue;
+      VE_LLE(kEpiSandwich);
+      break;
+    case kEpiGated:
+      if (!xs || !post || hc <= 0 || ((out || outf) && !w)) return cudaErrorInvalidValue;
+      VE_LLE(kEpiGated);
+      break;
+    case kEpiHc:
+      if (!xs || !post || !comb) return cudaErrorInvalidValue;
+      VE_LLE(kEpiHc);
+      break;
+    default: return cudaErrorInvalidValue;
+  }
+#undef VE_LLE
   VE_CHECK_LAUNCH();
 }
 

@@ -167,7 +167,9 @@ def _w_value(v) -> bytes:
         if all(isinstance(e, str) for e in v):
             return struct.pack("<IIQ", T_ARRAY, T_STRING, len(v)) + b"".join(_w_string(e) for e in v)
         if all(isinstance(e, int) for e in v):
-            return struct.pack("<IIQ", T_ARRAY, 5, len(v)) + struct.pack("<%di" % len(v), *v)
+            if all(-(1 << 31) <= e < (1 << 31) for e in v):
+                return struct.pack("<IIQ", T_ARRAY, 5, len(v)) + struct.pack("<%di" % len(v), *v)
+            return struct.pack("<IIQ", T_ARRAY, 11, len(v)) + struct.pack("<%dq" % len(v), *v)
         return struct.pack("<IIQ", T_ARRAY, 6, len(v)) + struct.pack("<%df" % len(v), *[float(e) for e in v])
     raise TypeError(f"unsupported GGUF metadata value {type(v)}")
 

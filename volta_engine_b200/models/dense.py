@@ -16,6 +16,7 @@ from dataclasses import dataclass, asdict
 import torch
 
 from ..ops import kernels as K
+from ..ops.streams import sandwich_add_norm
 from ..ops.linear import LinearBF16, LinearNVFP4
 from ..parallel.comm import LocalComm
 from ..runtime.batch import BatchRows, LOGITS_ALL, LOGITS_LAST, LOGITS_NONE
@@ -289,9 +290,8 @@ class DenseModel:
         cfg, comm = self.cfg, self.comm
         if post_norm is None:
             return comm.allreduce_add_norm(part, h, next_norm, cfg.rms_eps, cfg.norm_bias)
-        full = comm.allreduce_(part) if comm.size > 1 else part
-        normed = K.rmsnorm(full, post_norm, cfg.rms_eps, cfg.norm_bias)
-        return K.rmsnorm(normed, next_norm, cfg.rms_eps, cfg.norm_bias, residual=h)
+        # decode rows: one launch (the all-reduce kernel applies both norms); otherwise all-reduce, then the same epilogue
+        return sandwich_add_norm(part, h, post_norm, next_norm, cfg.rms_eps, cfg.norm_bias, 1.0, comm=comm)
 
     def layer_window(self, li: int) -> int:
         cfg = self.cfg

@@ -94,7 +94,7 @@ class TensorSource:
         if permuted:
             raw = unpermute_rope_rows(raw, rope_heads)
         n0, n1 = SafeTensorsRepo._range(N, "col" if split == "col" else None, rank, world, 1)
-        blk = 256 if info.ggml_type in (gq.GGML_Q4_K, gq.GGML_Q6_K) else 32
+        blk = gq.BLOCK[info.ggml_type][0]
         k0, k1 = SafeTensorsRepo._range(K, "row" if split == "row" else None, rank, world, blk)
         bpb = gq.row_bytes(info.ggml_type, blk)
         raw = raw[n0:n1, k0 // blk * bpb:k1 // blk * bpb].contiguous()

@@ -157,6 +157,14 @@ class SymmComm:
         self._two_shot(residual, w, rows, H, eps, wbias, 1)
         return self._xout(rows, H)
 
+    def allreduce_epilogue(self, mode: int, partial: torch.Tensor, epi_args: tuple) -> None:
+        """All-reduce of <= 16 decode rows with a stream epilogue (ops/streams.py: 2 sandwich norm, 3 gated streams,
+        4 hyper-connection update) applied to the reduced rows in the same launch; ``epi_args`` as packed there."""
+        from ..ops.streams import LL_EPI_SIG
+        pushed, self.pushed = self.pushed, False
+        _lib.call("ll_allreduce_epi", LL_EPI_SIG, self._args_ptr, mode, 1 if pushed else 0, partial.data_ptr(),
+                  partial.stride(0), *epi_args)
+
     def merge_argmax(self, idx: torch.Tensor, val: torch.Tensor) -> torch.Tensor:
         rows = idx.numel()
         _lib.call("ll_argmax_merge", "ppppi", self._args_ptr, idx.data_ptr(), val.data_ptr(),
