@@ -116,3 +116,16 @@ def test_gguf_block_decoders_match_ggml_goldens():
     for t, tol in ((G.GGML_Q4_1, 0.03), (G.GGML_Q5_0, 0.03), (G.GGML_Q5_1, 0.015), (G.GGML_IQ4_NL, 0.05)):
         back = G.dequantize(G.quantize(x, t), t, 256)
         assert float((back - x).abs().max()) < tol, G.NAMES[t]
+
+
+def test_kv_release_prefix_recycles_pages_below_a_window():
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    kv = PagedKVCache(1, 1, 8, 9, 2, 4096, "cpu")
+    kv.reserve(0, 64 * 6)
+    assert kv.free_pages() == 2
+    assert kv.release_prefix(0, 64 * 4 + 10) == 4 and kv.free_pages() == 6
+    assert kv.host_table[0, :4].tolist() == [0, 0, 0, 0] and int(kv.host_table[0, 4]) != 0
+    kv.reserve(0, 64 * 10)                                  # positions keep growing over the same eight physical pages
+    assert kv.free_pages() == 2 and kv.release_prefix(0, 64 * 4) == 0
+    kv.release(0)
+    assert kv.free_pages() == 8 and kv.slot_first[0] == 0 and kv.slot_pages[0] == 0

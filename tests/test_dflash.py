@@ -1,0 +1,181 @@
+"""Block drafter speculation: tap ring contents, drafting rounds that leave greedy output unchanged, the candidate walk,
+the dynamic convolution and the sparse draft head (CPU statements; the CUDA kernels against them on a GPU)."""
+import pytest
+import torch
+
+from volta_engine_b200.models.dense import DenseConfig, DenseModel
+from volta_engine_b200.ops.linear import LinearBF16
+from volta_engine_b200.runtime import dflash_runner as D
+from volta_engine_b200.runtime.engine import Engine
+from volta_engine_b200.runtime.generator import Generator, Request
+from volta_engine_b200.runtime.kv_cache import PagedKVCache
+from volta_engine_b200.runtime.options import Options
+
+
+class ByteTok:
+    eos_ids = [0]
+
+    def decode_bytes(self, ids, skip_special=False):
+        return bytes(i & 0xFF for i in ids)
+
+    def encode(self, text, allow_special=True):
+        return list(text.encode())
+
+
+def _setup(device="cpu", block=4, use_graphs=False):
+    cfg = DenseConfig.tiny(vocab=256)
+    m = DenseModel(cfg, device).init_random(seed=0)
+    kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 40, 2, 512, device)
+    eng = Engine(m, kv, use_graphs=use_graphs, prefill_chunk=32)
+    dc = D.DFlashConfig(block_size=block, n_layers=2, hidden=cfg.hidden, n_q=cfg.n_q, n_kv=cfg.n_kv, head_dim=cfg.head_dim,
+                        ffn=cfg.ffn, target_layer_ids=(0, cfg.n_layers - 1), sliding_window=64, rope_theta=1e4, mask_token_id=255,
+                        tap_cap=64, quant="bf16")
+    return cfg, m, eng, dc
+
+
+def _prompt(n, seed=0):
+    return torch.randint(1, 255, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def test_drafter_rounds_leave_greedy_output_unchanged_and_taps_follow_the_target():
+    cfg, m, eng, dc = _setup()
+    p = _prompt(45, 5)
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0}, env={})
+    plain = Generator(eng, ByteTok(), o, eos_ids=[]).generate(Request(p, max_tokens=12, cache_prefix=False))
+    cfg2, m2, eng2, _ = _setup()
+    o2 = Options.resolve({"max_slots": 2, "prefix_interval": 0, "speculator": "draft", "spec_ctrl": False, "spec_depth": 3}, env={})
+    g = Generator(eng2, ByteTok(), o2, eos_ids=[])
+    g.drafter = D.DFlashRunner(eng2, dc)
+    spec = g.generate(Request(p, max_tokens=12, cache_prefix=False))
+    assert spec["tokens"] == plain["tokens"]
+    assert g.metrics.spec["rounds"] > 0 and g.metrics.spec["proposed"] == 3 * g.metrics.spec["rounds"]
+    # the ring holds the tapped layers' outputs of the prompt positions: replay the prompt on a fresh model and compare
+    cfg3, m3, eng3, _ = _setup()
+    ring = D.TapRing(2, 64, (0, cfg.n_layers - 1), cfg.hidden, "cpu")
+    m3.tap_ring = ring
+    eng3.prefill(0, p)
+    assert torch.equal(ring.rows(0, 0, len(p)), g.drafter.ring.rows(0, 0, len(p)))
+    last = m3.last_residual[-1].to(torch.bfloat16)                       # last layer's output of the last prompt row
+    H = cfg.hidden
+    assert torch.equal(ring.taps[0, (len(p) - 1) % 64, H:2 * H], last)
+
+
+def test_ingest_window_and_release():
+    cfg, m, eng, dc = _setup()
+    r = D.DFlashRunner(eng, dc)
+    p = _prompt(100, 6)
+    eng.prefill(0, p)
+    assert r.ingest(0, 100) == 64 and r.ctx_len[0] == 100                # only the ring's span is still available
+    assert r.ingest(0, 100) == 0
+    d = r.draft(0, 7, 100)
+    assert len(d) == dc.block_size - 1 and all(0 <= t < 256 for t in d)
+    assert len(r.draft(0, 7, 100, depth=2)) == 2
+    r.release(0)
+    assert r.ctx_len[0] == 0 and r.kv.slot_pages[0] == 0
+
+
+def _walk_inputs(dev="cpu"):
+    g = torch.Generator().manual_seed(3)
+    bsz, rows, k, rank, vocab = 2, 5, 6, 32, 100
+    unary = torch.randn(bsz, rows, k, generator=g)
+    cands = torch.randint(0, vocab, (bsz, rows, k), generator=g, dtype=torch.int32)
+    gate = torch.randn(bsz, rows, rank, generator=g).to(torch.bfloat16)
+    pred = torch.randn(vocab, rank, generator=g).to(torch.bfloat16)
+    succ = torch.randn(vocab, rank, generator=g).to(torch.bfloat16)
+    anchor = torch.tensor([3, 77], dtype=torch.int32)
+    return [t.to(dev) for t in (unary, cands, gate, pred, succ, anchor)]
+
+
+def test_candidate_walk_without_pairwise_term_picks_the_best_unary():
+    cfg, m, eng, dc = _setup()
+    r = D.DFlashRunner(eng, dc)
+    unary, cands, gate, pred, succ, anchor = _walk_inputs()
+    out, conf = r.walk_candidates(unary, cands, torch.zeros_like(gate), pred, succ, anchor)
+    want = cands.gather(2, unary.argmax(-1, keepdim=True)).squeeze(-1)
+    assert torch.equal(out[:, 1:], want) and torch.equal(out[:, 0], anchor)
+    assert torch.all((conf > 0) & (conf <= 1))
+
+
+def test_dynconv_and_sparse_head_cpu():
+    g = torch.Generator().manual_seed(4)
+    T, C, gs, taps = 6, 32, 8, 2
+    x = torch.randn(T, C, generator=g)
+    dyn = torch.randn(T, taps, C // gs, generator=g).to(torch.bfloat16)
+    base = torch.randn(taps, C, generator=g).to(torch.bfloat16)
+    out = D.dynconv(x, dyn, base, gs)
+    t, c = 3, 17
+    want = sum((float(base[k, c]) + float(dyn[t, k, c // gs])) * float(x[t - k, c]) for k in range(taps))
+    assert abs(float(out[t, c]) - want) < 1e-5
+    assert abs(float(out[0, c]) - (float(base[0, c]) + float(dyn[0, 0, c // gs])) * float(x[0, c])) < 1e-5
+    W = (torch.randn(300, 64, generator=g) * 0.1).to(torch.bfloat16)
+    cols = torch.tensor(D.SparseHead.choose_columns({5: 10, 9: 7, 200: 7, 3: 1}, 3, always=[299]), dtype=torch.int32)
+    assert cols.tolist() == [5, 9, 299]
+    sh = D.SparseHead.extract(LinearBF16(W), 64, 300, cols, ident_rows=48)
+    assert torch.equal(sh.w_sub, W[cols.long()])
+    xq = torch.randn(2, 64, generator=g).to(torch.bfloat16)
+    lg = sh.logits(xq)
+    assert lg.shape == (2, 300) and int(lg[0].float().argmax()) in cols.tolist()
+    assert torch.allclose(lg[:, cols.long()].float(), (xq.float() @ W[cols.long()].float().t()), atol=0.02, rtol=0.02)
+
+
+# ------------------------------------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+def test_spec_kernels_match_cpu():
+    dev = torch.device("cuda:0")
+    cfg, m, eng, dc = _setup()
+    r = D.DFlashRunner(eng, dc)
+    ins = _walk_inputs()
+    want, wconf = r.walk_candidates(*ins)
+    got, gconf = r.walk_candidates(*[t.to(dev) for t in ins])
+    assert torch.equal(got.cpu(), want) and torch.allclose(gconf.cpu(), wconf, atol=1e-3)
+    g = torch.Generator().manual_seed(8)
+    T, C, gs, taps = 8, 5120, 16, 2
+    x = torch.randn(T, C, generator=g)
+    dyn = torch.randn(T, taps, C // gs, generator=g).to(torch.bfloat16)
+    base = torch.randn(taps, C, generator=g).to(torch.bfloat16)
+    acc0 = torch.randn(T, C, generator=g)
+    assert torch.allclose(D.dynconv(x.to(dev), dyn.to(dev), base.to(dev), gs).cpu(), D.dynconv(x, dyn, base, gs), atol=1e-5)
+    a, b = acc0.clone(), acc0.to(dev)
+    D.dynconv(x, dyn, base, gs, out=a, accumulate=True)
+    D.dynconv(x.to(dev), dyn.to(dev), base.to(dev), gs, out=b, accumulate=True)
+    assert torch.allclose(b.cpu(), a, atol=1e-5)
+    xs = torch.randn(3, 4, 640, generator=g)
+    for mode in (0, 1, 4):
+        assert torch.equal(D.reduce_streams(xs.to(dev), mode).cpu(), D.reduce_streams(xs, mode))
+    # tap ring: bf16 and fp32 sources, rows of idle slots skipped
+    ring = D.TapRing(2, 16, (3, 7), 640, dev)
+    h = torch.randn(4, 640, generator=g)
+    pos = torch.tensor([5, 21, 2, 9], dtype=torch.int32, device=dev)
+    slot = torch.tensor([0, 1, -1, 1], dtype=torch.int32, device=dev)
+    ring.publish(7, h.to(dev), pos, slot, 4)
+    ring.publish(3, h.to(dev).to(torch.bfloat16), pos, slot, 4)
+    ring.publish(5, h.to(dev), pos, slot, 4)                              # not a tapped layer: ignored
+    t = ring.taps.cpu()
+    hb = h.to(torch.bfloat16)
+    assert torch.equal(t[0, 5, 640:], hb[0]) and torch.equal(t[1, 21 % 16, :640], hb[1]) and torch.equal(t[1, 9, 640:], hb[3])
+    assert float(t[0, 2].abs().sum()) == 0 and float(t[1, 2].abs().sum()) == 0
+    # sparse head on the device
+    W = (torch.randn(1024, 256, generator=g) * 0.1).to(torch.bfloat16)
+    cols = torch.tensor([1, 17, 500, 1023], dtype=torch.int32)
+    sh = D.SparseHead.extract(LinearBF16(W.to(dev)), 256, 1024, cols.to(dev), ident_rows=100)
+    assert torch.equal(sh.w_sub.cpu(), W[cols.long()])
+    xq = torch.randn(3, 256, generator=g).to(torch.bfloat16)
+    lg = sh.logits(xq.to(dev)).cpu()
+    ref = D.SparseHead(cols, W[cols.long()], 1024).logits(xq)
+    assert torch.allclose(lg.float()[:, cols.long()], ref.float()[:, cols.long()], atol=0.03, rtol=0.02)
+    assert torch.equal(lg.float().argmax(-1), ref.float().argmax(-1))
+
+
+@pytest.mark.gpu
+def test_drafter_rounds_on_gpu_equal_plain_greedy():
+    dev = torch.device("cuda:0")
+    p = _prompt(45, 5)
+    cfg, m, eng, dc = _setup(dev)
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0}, env={})
+    plain = Generator(eng, ByteTok(), o, eos_ids=[]).generate(Request(p, max_tokens=16, cache_prefix=False))
+    cfg2, m2, eng2, _ = _setup(dev)
+    o2 = Options.resolve({"max_slots": 2, "prefix_interval": 0, "speculator": "draft", "spec_ctrl": False, "spec_depth": 3}, env={})
+    g = Generator(eng2, ByteTok(), o2, eos_ids=[])
+    g.drafter = D.DFlashRunner(eng2, dc)
+    spec = g.generate(Request(p, max_tokens=16, cache_prefix=False))
+    assert spec["tokens"] == plain["tokens"] and g.metrics.spec["rounds"] > 0

@@ -215,6 +215,9 @@ class DenseModel:
             d = self.ffn_block(li, L, x, b, pbuf)
             nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
             x = self._add_norm(d, h, getattr(L, "post_ffn_norm", None), nxt)
+            tap = getattr(self, "tap_ring", None)
+            if tap is not None and li in tap.index:        # a block drafter reads this layer's output (per-slot position ring)
+                tap.publish(li, comm.all_gather_rows(h)[:b.n] if sp else h, b.pos, b.slot, b.n)
             steer = getattr(self, "steer", None)
             if steer is not None and not sp and steer.first <= li < steer.first + steer.layers:
                 # runtime steering edits the residual after this layer; the next layer's input is re-normalised

@@ -1,0 +1,266 @@
+"""Block drafter speculation (DFlash): a small decoder that reads tapped hidden states of the target model and proposes a
+whole block of tokens in one forward.
+
+Round (reference: inc/engine/runtime/dflash2_runner.h:26-60, inc/engine/spec/dflash.h:20-62, src/spec/tap_ring.cu):
+  * the target publishes the output of ``target_layer_ids`` for every row it forwards into a per-slot position ring
+    (``TapRing``; slot and position come from device memory, so the launch replays in CUDA graphs);
+  * the drafter projects the concatenated taps of every known position through ``fc`` + RMSNorm into its context and
+    stores that context's keys and values, layer by layer, in its own paged cache;
+  * a block of ``block_size`` rows (the anchor token followed by mask tokens) runs through the drafter with attention over
+    the context and, bidirectionally, over the block itself; row i of the block proposes the token at position pos + i
+    (version 1: the head's argmax per row; version 2 adds the dynamic convolutions' kernels and the candidate walk,
+    csrc/cuda/spec.cu, which ``walk_candidates`` exposes);
+  * the target verifies ``[anchor, drafts...]`` in ONE forward and keeps the longest agreeing prefix (generator).
+The drafter shares the target's embedding and LM head. Drafter context belongs to a slot; every slot has its own ring.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .._lib import call, ptr
+from ..models.dense import DenseConfig, DenseModel
+from ..ops import kernels as K
+from ..ops.linear import LinearBF16
+from .batch import BatchRows, LOGITS_ALL
+from .kv_cache import PagedKVCache
+
+
+@dataclass
+class DFlashConfig:
+    block_size: int = 8
+    n_layers: int = 5
+    hidden: int = 5120
+    n_q: int = 32
+    n_kv: int = 8
+    head_dim: int = 128
+    ffn: int = 17408
+    target_layer_ids: tuple = (5, 19, 33, 47, 61)
+    sliding_window: int = 2048
+    rope_theta: float = 1.0e7
+    rms_eps: float = 1e-6
+    mask_token_id: int = 0
+    tap_cap: int = 2048
+    version: int = 1
+    quant: str = "bf16"
+
+
+class TapRing:
+    """[slots, cap, n_taps * H] bf16: tap t of position p of a slot lives in row p % cap."""
+
+    def __init__(self, slots: int, cap: int, layer_ids, hidden: int, device):
+        self.layer_ids = tuple(layer_ids)
+        self.index = {l: i for i, l in enumerate(self.layer_ids)}
+        self.cap, self.H, self.n = cap, hidden, len(self.layer_ids)
+        self.taps = torch.zeros(slots, cap, self.n * hidden, dtype=torch.bfloat16, device=device)
+
+    def publish(self, li: int, h: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, rows: int):
+        t = self.index.get(li)
+        if t is None:
+            return
+        if not h.is_cuda:
+            for r in range(rows):
+                s, p = int(slot[r]), int(pos[r])
+                if s >= 0 and p >= 0:
+                    self.taps[s, p % self.cap, t * self.H:(t + 1) * self.H] = h[r].to(torch.bfloat16)
+            return
+        call("publish_taps", "pplippp" + "iiiili", ptr(self.taps), ptr(h), h.stride(0), 1 if h.dtype == torch.float32 else 0,
+             ptr(slot), ptr(pos), 0, rows, t, self.H, self.cap, self.taps.stride(0), self.n)
+
+    def rows(self, slot: int, p0: int, p1: int) -> torch.Tensor:
+        idx = torch.arange(p0, p1, device=self.taps.device) % self.cap
+        return self.taps[slot, idx]
+
+
+class DFlashRunner:
+    def __init__(self, engine, cfg: DFlashConfig, seed: int = 11):
+        self.e, self.cfg = engine, cfg
+        tgt = engine.model
+        dev = engine.device
+        tc = tgt.cfg
+        assert cfg.hidden == tc.hidden, "the drafter works at the target's hidden size"
+        self.ring = TapRing(engine.kv.max_slots, cfg.tap_cap, cfg.target_layer_ids, cfg.hidden, dev)
+        tgt.tap_ring = self.ring
+        dcfg = DenseConfig(n_layers=cfg.n_layers, hidden=cfg.hidden, n_q=cfg.n_q, n_kv=cfg.n_kv, head_dim=cfg.head_dim, ffn=cfg.ffn,
+                           vocab=tc.vocab, rope_theta=cfg.rope_theta, rms_eps=cfg.rms_eps, qk_norm=True,
+                           sliding_window=cfg.sliding_window, quant=cfg.quant)
+        self.model = DenseModel(dcfg, dev).init_random(seed=seed)
+        self.model.embed, self.model.lm_head = tgt.embed, tgt.lm_head            # shared with the target
+        self.model.vocab_local = tgt.vocab_local
+        g = torch.Generator(device=dev).manual_seed(seed + 1)
+        self.fc = LinearBF16((torch.randn(cfg.hidden, self.ring.n * cfg.hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16))
+        self.hidden_norm = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev)
+        span = max(cfg.tap_cap, cfg.sliding_window) + 2 * cfg.block_size
+        pages = engine.kv.max_slots * (PagedKVCache.pages_for(span) + 3) + 1
+        self.kv = PagedKVCache(cfg.n_layers, self.model.nkv, cfg.head_dim, pages, engine.kv.max_slots,
+                               engine.kv.max_pages * 64, dev)
+        self.ctx_len = [0] * engine.kv.max_slots
+        self.model.ensure_workspace(max(64, cfg.block_size), 8)
+        self.stats = {"rounds": 0, "proposed": 0, "accepted": 0}
+
+    # ---- weights of a trained drafter: same tensor names as a dense decoder plus ``fc`` and ``hidden_norm``
+    def load(self, src) -> None:
+        from ..models.factory import load_dense_weights
+        keep = self.model.embed, self.model.lm_head
+        load_dense_weights(self.model, src)
+        self.model.embed, self.model.lm_head = keep
+        self.fc = LinearBF16(src.tensor("fc.weight", self.e.device, torch.bfloat16))
+        self.hidden_norm = src.tensor("hidden_norm.weight", self.e.device, torch.bfloat16)
+
+    def release(self, slot: int) -> None:
+        self.ctx_len[slot] = 0
+        self.kv.release(slot)
+
+    # ---- context: keys and values of every layer from the projected taps of positions [ctx_len, upto)
+    def ingest(self, slot: int, upto: int) -> int:
+        cfg, m = self.cfg, self.model
+        lo = max(self.ctx_len[slot], upto - cfg.tap_cap, 0)
+        if upto <= lo:
+            return 0
+        n = upto - lo
+        taps = self.ring.rows(slot, lo, upto)
+        ctx = K.rmsnorm(self.fc.forward(taps), self.hidden_norm, cfg.rms_eps, 0.0)
+        self._reserve(slot, upto + cfg.block_size)
+        pos = torch.arange(lo, upto, dtype=torch.int32, device=ctx.device)
+        sl = torch.full((n,), slot, dtype=torch.int32, device=ctx.device)
+        for li, L in enumerate(m.layers):
+            kpool, vpool = self.kv.layer(li)
+            qkv = L.qkv.forward(ctx)
+            K.rmsnorm_heads_(qkv, L.k_norm, n, m.nkv, m.hd, qkv.stride(0), cfg.rms_eps, 0.0, m.nq * m.hd)
+            K.rope_store(qkv, pos, sl, self.kv.page_table, kpool, vpool, m.nq, m.nkv, m.hd, m.rot, cfg.rope_theta, False)
+        self.ctx_len[slot] = upto
+        return n
+
+    def _reserve(self, slot: int, n_tokens: int) -> None:
+        # pages of positions that left the sliding window (and the ring's span) are recycled before new ones are taken
+        cfg = self.cfg
+        self.kv.release_prefix(slot, n_tokens - max(cfg.tap_cap, cfg.sliding_window) - 2 * cfg.block_size)
+        self.kv.reserve(slot, n_tokens)
+
+    # ---- one block: returns block_size - 1 proposed tokens for positions pos + 1 ...
+    def draft(self, slot: int, anchor: int, pos: int, depth: int | None = None) -> list[int]:
+        cfg, m, e = self.cfg, self.model, self.e
+        B = cfg.block_size
+        self.ingest(slot, pos)
+        self._reserve(slot, pos + B + 1)
+        ids = [anchor] + [cfg.mask_token_id] * (B - 1)
+        b = BatchRows.make(ids, [pos + i for i in range(B)], [slot] * B, e.device, LOGITS_ALL, 1, nsplit=1)
+        b.key_end = torch.full((B,), pos + B - 1, dtype=torch.int32, device=e.device)     # the block sees all of itself
+        logits = m.forward(b, self.kv)
+        if logits.is_cuda:
+            idx, _ = K.argmax(logits, id_offset=e.comm.rank * m.vocab_local)
+            idx = e.comm.merge_argmax(idx, _) if e.comm.size > 1 else idx
+        else:
+            idx = logits.float().argmax(-1)
+        toks = [int(t) for t in idx.tolist()]
+        n = B - 1 if depth is None else max(0, min(B - 1, depth))
+        return toks[1:1 + n]
+
+    def walk_candidates(self, unary, cands, gate, pred_cb, succ_cb, anchor):
+        """Version 2 token choice: chained greedy walk over per-row candidate sets (top-k of the head) with the low-rank
+        pairwise term pred_cb[prev] * gate[row] . succ_cb[cand]. Returns (tokens [bsz, rows + 1], confidence)."""
+        bsz, rows, k = cands.shape
+        rank = gate.shape[-1]
+        if not cands.is_cuda:
+            out = torch.zeros(bsz, rows + 1, dtype=torch.int32)
+            conf = torch.ones(bsz, rows + 1)
+            for b_ in range(bsz):
+                prev = int(anchor[b_])
+                out[b_, 0] = prev
+                for i in range(rows):
+                    ag = pred_cb[prev].float() * gate[b_, i].float()
+                    sc = unary[b_, i] + succ_cb[cands[b_, i].long()].float() @ ag
+                    best = int(sc.argmax())
+                    prev = int(cands[b_, i, best])
+                    out[b_, i + 1] = prev
+                    conf[b_, i + 1] = 1.0 / float(torch.exp(sc - sc[best]).sum())
+            return out, conf
+        out = torch.empty(bsz, rows + 1, dtype=torch.int32, device=cands.device)
+        conf = torch.empty(bsz, rows + 1, dtype=torch.float32, device=cands.device)
+        call("selector_walk", "ppppppppiiii", ptr(unary), ptr(cands), ptr(gate), ptr(pred_cb), ptr(succ_cb), ptr(anchor), ptr(out),
+             ptr(conf), bsz, rows, k, rank)
+        return out, conf
+
+
+def dynconv(x, dyn, base, group_size, out=None, accumulate=False):
+    """Grouped dynamic causal convolution inside a block: out[t, c] (+)= sum_k (base[k, c] + dyn[t, k, c // gs]) * x[t - k, c]."""
+    T, C = x.shape
+    taps = base.shape[0]
+    if out is None:
+        out = torch.zeros(T, C, dtype=torch.float32, device=x.device)
+        accumulate = False
+    if not x.is_cuda:
+        res = torch.zeros(T, C)
+        w = base.float()[None] + dyn.float().repeat_interleave(group_size, dim=-1)          # [T, taps, C]
+        for k in range(taps):
+            res[k:] += w[k:, k] * x[:T - k].float()
+        out.copy_(out + res if accumulate else res)
+        return out
+    call("dynconv", "ppppiiiii", ptr(x), ptr(dyn), ptr(base), ptr(out), T, C, taps, group_size, 1 if accumulate else 0)
+    return out
+
+
+def reduce_streams(streams, mode=0):
+    """fp32 streams [m, hc, H] -> bf16 [m, H]: mode 0 the mean of the streams, mode k the stream k - 1."""
+    m, hc, H = streams.shape
+    if not streams.is_cuda:
+        return (streams.mean(1) if mode == 0 else streams[:, mode - 1]).to(torch.bfloat16)
+    out = torch.empty(m, H, dtype=torch.bfloat16, device=streams.device)
+    call("reduce_streams", "ppiiii", ptr(streams), ptr(out), m, H, hc, mode)
+    return out
+
+
+@dataclass
+class SparseHead:
+    """bf16 copy of a subset of the LM head's columns, so a draft step reads a few MB instead of the whole head; its logits
+    are scattered into a full-width row whose other columns hold the lowest value, so the shard argmax / top-k that follows
+    is unchanged (reference: inc/engine/modules/sparse_head.h:9-33). The subset comes from running the head (any weight
+    format) on blocks of identity rows."""
+    cols: torch.Tensor                     # int32 [count], shard-local column ids
+    w_sub: torch.Tensor                    # bf16 [count, hidden]
+    width: int = 0
+    counts: dict = field(default_factory=dict)
+
+    @classmethod
+    def extract(cls, head, hidden: int, width: int, cols: torch.Tensor, ident_rows: int = 128) -> "SparseHead":
+        dev = cols.device
+        count = cols.numel()
+        w_sub = torch.zeros(count, hidden, dtype=torch.bfloat16, device=dev)
+        for k0 in range(0, hidden, ident_rows):
+            rows = min(ident_rows, hidden - k0)
+            if cols.is_cuda:
+                ident = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+                call("identity_rows", "piii", ptr(ident), rows, hidden, k0)
+                chunk = head.forward(ident).to(torch.bfloat16).contiguous()
+                call("sparse_gather", "pliipipi", ptr(chunk), chunk.stride(0), rows, k0, ptr(cols), count, ptr(w_sub), hidden)
+            else:
+                ident = torch.zeros(rows, hidden, dtype=torch.bfloat16)
+                ident[torch.arange(rows), k0 + torch.arange(rows)] = 1
+                chunk = head.forward(ident).to(torch.bfloat16)
+                w_sub[:, k0:k0 + rows] = chunk[:, cols.long()].t()
+        return cls(cols, w_sub, width)
+
+    def logits(self, x: torch.Tensor) -> torch.Tensor:
+        """x [rows, hidden] bf16 -> bf16 logits [rows, width]: the subset's logits in place, every other column lowest."""
+        rows = x.shape[0]
+        if not x.is_cuda:
+            sub = (x.float() @ self.w_sub.float().t()).to(torch.bfloat16)
+            out = torch.full((rows, self.width), -3.0e38, dtype=torch.bfloat16)
+            out[:, self.cols.long()] = sub
+            return out
+        sub = K.gemm_bf16(self.w_sub, x) if rows > 16 else K.bf16_gemv_f32(self.w_sub, x).to(torch.bfloat16)
+        out = torch.empty(rows, self.width, dtype=torch.bfloat16, device=x.device)
+        call("sparse_scatter", "pipplii", ptr(sub), self.cols.numel(), ptr(self.cols), ptr(out), out.stride(0), self.width, rows)
+        return out
+
+    @staticmethod
+    def choose_columns(token_counts: dict, budget: int, always=()) -> list[int]:
+        """Policy: the ``budget`` most frequent token ids of a usage histogram, plus ids that must stay (eos, specials)."""
+        keep = list(dict.fromkeys(int(t) for t in always))
+        for t, _ in sorted(token_counts.items(), key=lambda kv: (-kv[1], kv[0])):
+            if len(keep) >= budget:
+                break
+            if int(t) not in keep:
+                keep.append(int(t))
+        return sorted(keep)

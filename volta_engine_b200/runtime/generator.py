@@ -157,6 +157,7 @@ class Generator:
         self.loop_detect = getattr(options, "loop_detect", True) if options else True
         self.prefix_interval = getattr(options, "prefix_interval", 16384) if options else 16384
         self.budget_ms = getattr(options, "prefill_budget_ms", 50.0) if options else 50.0
+        self.drafter = None                    # block drafter (speculator "dflash"): object with draft(slot, anchor, pos, depth)
         self.mtp = None
         if self.speculator == "mtp":
             from .mtp_runner import MtpRunner
@@ -370,6 +371,13 @@ class Generator:
                 n = self._suffix_round(s)
                 if n:
                     return n
+        if not budgeted and self.drafter is not None and len(act) == 1 and act[0].req.params.greedy:
+            s = act[0]
+            if s.ctrl is None or s.ctrl.use_speculation():
+                depth = s.ctrl.depth(self.spec_depth) if s.ctrl else self.spec_depth
+                n = self._verify_round(s, self.drafter.draft(s.idx, s.next_tok, s.pos, depth), "drafter")
+                if n:
+                    return n
         if not budgeted and self.mtp is not None and len(act) == 1 and act[0].req.params.greedy and act[0].idx in self.mtp.hidden:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
@@ -451,7 +459,10 @@ class Generator:
 
     def _suffix_round(self, s: SlotState) -> int:
         depth = s.ctrl.depth(self.spec_depth) if s.ctrl else self.spec_depth
-        drafts = s.suffix.draft(depth)
+        return self._verify_round(s, s.suffix.draft(depth), "suffix")
+
+    def _verify_round(self, s: SlotState, drafts: list[int], kind: str) -> int:
+        """One target forward over [next token, drafts...]; keeps the longest prefix the target agrees with."""
         if not drafts:
             return 0
         t0 = time.time()
@@ -468,7 +479,7 @@ class Generator:
         s.next_tok = new[-1]
         m = self.metrics.spec
         m["rounds"] += 1
-        m["suffix_rounds"] += 1
+        m["suffix_rounds"] += 1 if kind == "suffix" else 0
         m["proposed"] += len(drafts)
         m["accepted"] += acc
         while len(m["steps"]) < len(drafts):
@@ -586,6 +597,8 @@ class Generator:
         self.engine.kv.release(s.idx)
         if self.mtp is not None:
             self.mtp.release(s.idx)
+        if self.drafter is not None:
+            self.drafter.release(s.idx)
         steer = getattr(getattr(self.engine, "model", None), "steer", None)
         if steer is not None and req.steer is not None:
             steer.clear_slot(s.idx)

@@ -37,7 +37,8 @@ class PagedKVCache:
         self.page_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32, device=device)
         self.host_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32)
         self.free = list(range(num_pages - 1, 0, -1))
-        self.slot_pages = [0] * max_slots  # pages held per slot
+        self.slot_pages = [0] * max_slots  # logical pages covered per slot (high-water mark)
+        self.slot_first = [0] * max_slots  # first logical page still held (pages below were recycled by release_prefix)
 
     @staticmethod
     def pages_for(n_tokens: int) -> int:
@@ -67,11 +68,32 @@ class PagedKVCache:
     def release(self, slot: int, keep_tokens: int = 0) -> None:
         keep = self.pages_for(keep_tokens)
         for i in range(keep, self.slot_pages[slot]):
-            self.free.append(int(self.host_table[slot, i]))
+            if int(self.host_table[slot, i]):
+                self.free.append(int(self.host_table[slot, i]))
             self.host_table[slot, i] = 0
+        self.slot_first[slot] = min(self.slot_first[slot], keep)
         if self.slot_pages[slot] > keep:
             self.page_table[slot, keep:self.slot_pages[slot]].zero_()
         self.slot_pages[slot] = keep
+
+    def release_prefix(self, slot: int, below_tokens: int) -> int:
+        """Recycle the pages that lie wholly below position ``below_tokens`` (a sliding-window consumer never reads them
+        again): the cache then behaves as a ring of window-sized storage over an unbounded position range. The table
+        entries point at the null page afterwards. Returns the number of pages freed."""
+        first = self.slot_first[slot]
+        upto = min(below_tokens // PAGE, self.slot_pages[slot])
+        if upto <= first:
+            return 0
+        n = 0
+        for i in range(first, upto):
+            pg = int(self.host_table[slot, i])
+            if pg:
+                self.free.append(pg)
+                n += 1
+            self.host_table[slot, i] = 0
+        self.page_table[slot, first:upto].zero_()
+        self.slot_first[slot] = upto
+        return n
 
     def layer(self, i: int):
         return self.k[i], self.v[i]

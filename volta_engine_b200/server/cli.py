@@ -124,6 +124,26 @@ def resolve_config(argv: list[str], env=None) -> tuple[LaunchConfig, argparse.Na
     return LaunchConfig(**vals), args
 
 
+def load_drafter(engine, draft_dir: str):
+    """Block drafter from a checkpoint directory: ``config.json`` carries the geometry under ``dflash_config`` (block size,
+    target layer ids, mask token) beside the usual decoder keys; tensors use the dense decoder names plus ``fc`` and
+    ``hidden_norm``."""
+    from ..models.factory import TensorSource
+    from ..runtime.dflash_runner import DFlashConfig, DFlashRunner
+    with open(os.path.join(draft_dir, "config.json")) as f:
+        hf = json.load(f)
+    d = hf.get("dflash_config", {})
+    cfg = DFlashConfig(block_size=int(hf.get("block_size", d.get("block_size", 8))), n_layers=int(hf["num_hidden_layers"]),
+                       hidden=int(hf["hidden_size"]), n_q=int(hf["num_attention_heads"]), n_kv=int(hf["num_key_value_heads"]),
+                       head_dim=int(hf.get("head_dim", hf["hidden_size"] // hf["num_attention_heads"])),
+                       ffn=int(hf["intermediate_size"]), target_layer_ids=tuple(d.get("target_layer_ids", hf.get("target_layer_ids", ()))),
+                       sliding_window=int(hf.get("sliding_window") or 2048), rope_theta=float(hf.get("rope_theta", 1e7)),
+                       rms_eps=float(hf.get("rms_norm_eps", 1e-6)), mask_token_id=int(d.get("mask_token_id", hf.get("mask_token_id", 0))))
+    runner = DFlashRunner(engine, cfg)
+    runner.load(TensorSource(draft_dir))
+    return runner
+
+
 def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     """Model directory -> (model, hf_config, Engine, kv pool tokens) on this rank. ``agree(n)`` returns the value all
     ranks settle on for the KV pool size (minimum over ranks); ``None`` for a single rank."""
@@ -178,6 +198,8 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         template = None
     cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None) if o.prefix_cache_mib > 0 else None
     gen = Generator(engine, tok, o, prefix_cache=cache)
+    if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size == 1:
+        gen.drafter = load_drafter(engine, cfg.draft_model_dir)
     defaults = {"temperature": cfg.default_temperature, "top_p": cfg.default_top_p, "top_k": cfg.default_top_k,
                 "enable_thinking": cfg.default_enable_thinking}
     gc_path = os.path.join(cfg.model_dir, "generation_config.json")
