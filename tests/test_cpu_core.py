@@ -129,3 +129,22 @@ def test_kv_release_prefix_recycles_pages_below_a_window():
     assert kv.free_pages() == 2 and kv.release_prefix(0, 64 * 4) == 0
     kv.release(0)
     assert kv.free_pages() == 8 and kv.slot_first[0] == 0 and kv.slot_pages[0] == 0
+
+
+def test_expert_tier_policy_swaps_the_hottest_cold_expert_in():
+    from types import SimpleNamespace
+    from volta_engine_b200.runtime.expert_tier import ExpertTier
+    E = 6
+    bank = SimpleNamespace(e_local=E, gu_p=torch.arange(E * 4, dtype=torch.uint8).reshape(E, 2, 2),
+                           gu_s=torch.zeros(E, 2, 1, dtype=torch.uint8), dn_p=torch.ones(E, 2, 2, dtype=torch.uint8),
+                           dn_s=torch.zeros(E, 2, 1, dtype=torch.uint8), gu_sf=None, dn_sf=None)
+    t = ExpertTier(bank, 2, decay=0.5, margin=1.25)
+    assert t.resident() == [0, 1] and bank.gu_p is None
+    assert int(t.tab_gu[0]) == t.slots["gu_p"][0].data_ptr() and int(t.tab_gu[2 * 4]) == t.cold["gu_p"][4].data_ptr()
+    counts = torch.tensor([5.0, 1.0, 0.0, 9.0, 0.0, 4.0])
+    assert t.rebalance(counts, max_swaps=1) == 1 and t.resident() == [0, 3]              # 3 replaces the coldest hot expert
+    assert torch.equal(t.slots["gu_p"][t.slot_of[3]], t.cold["gu_p"][3])
+    assert int(t.tab_gu[2 * 1]) == t.cold["gu_p"][1].data_ptr()                          # the evicted expert reads from the host copy
+    assert t.rebalance(counts, max_swaps=4) == 0                                           # no new routing: heat only decays
+    counts2 = counts + torch.tensor([0.0, 0.0, 30.0, 0.0, 0.0, 0.0])
+    assert t.rebalance(counts2, max_swaps=4) == 1 and 2 in t.resident() and t.swaps == 2

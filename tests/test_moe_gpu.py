@@ -24,8 +24,10 @@ def test_router_select(router, n_group, topk_group, E, k):
     bias = torch.randn(E, generator=g, device=DEV) * 0.1 if router == "sigmoid" else None
     ids = torch.empty(7, k, dtype=torch.int32, device=DEV)
     w = torch.empty(7, k, dtype=torch.float32, device=DEV)
-    call("router_select", "pliiiipfiipp", ptr(logits), logits.stride(0), 7, E, k, 1 if router == "sigmoid" else 0,
-         ptr(bias), float(cfg.router_scale), n_group, topk_group, ptr(ids), ptr(w))
+    heat = torch.zeros(E, dtype=torch.float32, device=DEV)
+    call("router_select", "pliiiipfiippp", ptr(logits), logits.stride(0), 7, E, k, 1 if router == "sigmoid" else 0,
+         ptr(bias), float(cfg.router_scale), n_group, topk_group, ptr(ids), ptr(w), ptr(heat))
+    assert torch.equal(heat.cpu(), torch.bincount(ids.cpu().flatten().long(), minlength=E).float())
     rid, rw = route_reference(logits.cpu(), cfg, bias.cpu() if bias is not None else None)
     assert torch.equal(ids.cpu(), rid)
     assert_close(w.cpu(), rw, rel=1e-4, abs_=1e-5, name="router weights")
@@ -85,3 +87,29 @@ def test_moe_model_generates_like_reference_and_zipf_bias():
     assert cos(lg.cpu(), lc) > 0.995
     out, _ = Engine(m_gpu, PagedKVCache(2, m_gpu.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64).generate(prompt, 6)
     assert len(out) == 6
+
+
+def test_expert_tier_reads_cold_experts_in_place_and_rebalances():
+    """Two of eight experts resident: the tiered layer (cold experts read from pinned host memory through the pointer
+    table) gives the stacked bank's bits; the routing histogram moves the busiest experts into the device slots."""
+    m_gpu, _ = _models()
+    m_ref, _ = _models()
+    E = m_gpu.cfg.n_experts
+    tiers = m_gpu.enable_expert_tier(2)
+    assert tiers and all(t.resident() == [0, 1] for _, t in tiers) and m_gpu.layers[0].bank.gu_p is None
+    g = torch.Generator(device=DEV).manual_seed(5)
+    for rows in (1, 6, 40):
+        x = torch.randn(rows, m_gpu.cfg.hidden, generator=g, device=DEV).to(torch.bfloat16)
+        got = m_gpu.ffn_block(0, m_gpu.layers[0], x, None, None)
+        m_ref.layers[0].bank.gu_sf = None                      # same route-indexed kernel on the stacked bank
+        want = m_ref.ffn_block(0, m_ref.layers[0], x, None, None)
+        assert torch.equal(got, want), f"tiered != stacked at rows={rows}"
+    assert float(m_gpu.heat[0].sum()) == (1 + 6 + 40) * m_gpu.cfg.top_k
+    swaps = m_gpu.rebalance_experts(max_swaps=2)
+    tier = tiers[0][1]
+    top2 = sorted(torch.topk(m_gpu.heat[0].cpu(), 2).indices.tolist())
+    assert swaps >= 1 and len(tier.resident()) == 2 and set(tier.resident()) & set(top2)
+    x = torch.randn(3, m_gpu.cfg.hidden, generator=g, device=DEV).to(torch.bfloat16)
+    assert torch.equal(m_gpu.ffn_block(0, m_gpu.layers[0], x, None, None), m_ref.ffn_block(0, m_ref.layers[0], x, None, None))
+    torch.cuda.synchronize()
+    assert tier.device_bytes() * (E // 2) == tier.host_bytes()

@@ -48,7 +48,7 @@ VE_DEVINL RV block_best(RV a, RV* red) {
 __global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, long stride, int E, int topk,
                                                             int mode, const float* __restrict__ bias, float scale,
                                                             int n_group, int topk_group, int* __restrict__ ids,
-                                                            float* __restrict__ weights) {
+                                                            float* __restrict__ weights, float* __restrict__ heat) {
   __shared__ float s_raw[1024], s_sel[1024];
   __shared__ float s_gscore[64];
   __shared__ RV red[33];
@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
     for (int k = 0; k < topk; ++k) {
       ids[blockIdx.x * topk + k] = s_id[k];
       weights[blockIdx.x * topk + k] = s_w[k];
+      if (heat) atomicAdd(&heat[s_id[k]], 1.f);      // routing histogram: monitor page and expert residency decisions
     }
   }
 }
@@ -162,8 +163,10 @@ __global__ void __launch_bounds__(128) nvfp4_moe_gemv_kernel(const uint8_t* __re
   rows[1] = o0 + 1;
   rows[2] = o0 + half_n;
   rows[3] = o0 + 1 + half_n;
-  const uint8_t* wp = Wp + (size_t)e * N * (K >> 1);
-  const uint8_t* ws = Ws + (size_t)e * N * (K >> 4);
+  // Ws == nullptr: Wp is a device table of per-expert base pointers {packed, scales} (tiered residency: an entry may
+  // point into device slots or into pinned host memory that the GPU reads in place)
+  const uint8_t* wp = Ws ? Wp + (size_t)e * N * (K >> 1) : reinterpret_cast<const uint8_t* const*>(Wp)[2 * e];
+  const uint8_t* ws = Ws ? Ws + (size_t)e * N * (K >> 4) : reinterpret_cast<const uint8_t* const*>(Wp)[2 * e + 1];
   const __nv_bfloat16* xr = x + (long)(route / x_div) * x_stride;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const int kchunks = K >> 5;
@@ -357,11 +360,11 @@ using namespace ve;
 extern "C" {
 
 int ve_router_select(const void* logits, long stride, int rows, int E, int topk, int mode, const void* bias, float scale,
-                     int n_group, int topk_group, void* ids, void* weights, cudaStream_t st) {
+                     int n_group, int topk_group, void* ids, void* weights, void* heat, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (E > 1024 || topk > 32 || topk < 1 || n_group > 64 || (n_group > 1 && E % n_group)) return cudaErrorInvalidValue;
   router_select_kernel<<<rows, 256, 0, st>>>((const float*)logits, stride, E, topk, mode, (const float*)bias, scale,
-                                             n_group, topk_group, (int*)ids, (float*)weights);
+                                             n_group, topk_group, (int*)ids, (float*)weights, (float*)heat);
   VE_CHECK_LAUNCH();
 }
 

@@ -46,6 +46,10 @@ class DenseConfig:
                                   # only to the last ``sliding_window`` keys; 0: ``sliding_window`` on every layer
     rope_theta_local: float = 0.0 # rotary base of the windowed layers (0 = rope_theta)
     sandwich_norm: bool = False   # extra RMSNorm on the output of the attention and FFN blocks before the residual add
+    residual: str = "plain"       # plain | gated (fp32 gated residual streams) | hc (4 fp32 hyper-connection streams)
+    hc_mult: int = 4              # residual streams of the gated form
+    hc_rank: int = 64             # width of the gated residual's low-rank gate
+    hc_sinkhorn: int = 20         # Sinkhorn rounds of the hyper-connection mixing matrix
     attn_scale: float = 0.0       # 0 = 1/sqrt(head_dim)
     logit_softcap: float = 0.0
     quant: str = "nvfp4"          # nvfp4 | bf16
@@ -83,7 +87,7 @@ def _pad_to(n: int, m: int) -> int:
 
 class DenseLayer:
     __slots__ = ("attn_norm", "qkv", "o_proj", "ffn_norm", "gate_up", "down", "q_norm", "k_norm", "post_attn_norm",
-                 "post_ffn_norm")
+                 "post_ffn_norm", "attn_hc", "mlp_hc")
 
 
 class DenseModel:
@@ -198,6 +202,8 @@ class DenseModel:
         the rows selected by ``b.logits`` (None for LOGITS_NONE)."""
         cfg = self.cfg
         comm = self.comm
+        if cfg.residual != "plain":
+            return self._forward_streams(b, kv)
         if self._prenorm_ok(b):
             return self._forward_prenorm(b, kv)
         h = K.embed(b.ids, self.embed, scale=cfg.embed_scale)          # residual stream [n, H] bf16
@@ -236,6 +242,71 @@ class DenseModel:
             else:
                 logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
         return logits
+
+    # ------------------------------------------------------------------------------------- multi-stream residuals
+    def init_stream_weights(self, seed: int = 9, std: float = 0.02):
+        """Weights of the multi-stream residual forms (``cfg.residual``): per sublayer a gated-residual mixer
+        (norm, low-rank gate, inject) or a hyper-connection mixer (24 x 4H projection, base, scale); replicated on
+        every rank. Call after the layers exist."""
+        from ..ops.streams import GatedResidualWeights
+        cfg, dev = self.cfg, self.device
+        H, hc, rank = cfg.hidden, (cfg.hc_mult if cfg.residual == "gated" else 4), cfg.hc_rank
+        g = torch.Generator(device=dev).manual_seed(seed)
+
+        def rnd(*shape, s=std):
+            return torch.randn(*shape, generator=g, device=dev) * s
+
+        def mixer(inject=True):
+            if cfg.residual == "gated":
+                return GatedResidualWeights(norm=rnd(hc, H, s=0.05).to(torch.bfloat16), down=rnd(rank, hc * H).to(torch.bfloat16),
+                                            up=rnd(hc * H, rank, s=0.2).to(torch.bfloat16),
+                                            inject=rnd(hc, hc * H).to(torch.bfloat16) if inject else None)
+            return (rnd(24, 4 * H, s=0.02).contiguous(), rnd(24, s=0.5).contiguous(),
+                    torch.tensor([0.5, 0.5, 0.5], device=dev))
+        for L in self.layers:
+            L.attn_hc, L.mlp_hc = mixer(), mixer()
+        self.final_hc = mixer(inject=False)
+        return self
+
+    def _forward_streams(self, b: BatchRows, kv):
+        """Forward with fp32 residual streams [n, hc, H]. gated: every sublayer reads mean_s(gate_s * norm(stream_s)) and
+        writes stream_s += post_s * y, the update fused with the all-reduce and the next mixer's norm. hc: every sublayer
+        reads sum_h pre_h * stream_h (normalised) and writes stream_h = post_h * y + sum_g comb[g][h] * stream_g."""
+        from ..ops import streams as S
+        cfg, comm = self.cfg, self.comm
+        h0 = K.embed(b.ids, self.embed, scale=cfg.embed_scale)
+        gated = cfg.residual == "gated"
+        xs = S.init_streams(h0, cfg.hc_mult if gated else 4)
+        eps = cfg.rms_eps
+        if gated:
+            normed = S.gr_norm(xs, self.layers[0].attn_hc.norm, eps)
+            for li, L in enumerate(self.layers):
+                mixed, post = S.gr_mix_prenormed(normed, L.attn_hc)
+                o = self.attn_block(li, L, mixed, b, kv, None)
+                normed = S.gated_stream_update(o, xs, post, L.mlp_hc.norm, eps, comm=comm)
+                mixed, post = S.gr_mix_prenormed(normed, L.mlp_hc)
+                d = self.ffn_block(li, L, mixed, b, None)
+                nxt = self.layers[li + 1].attn_hc if li + 1 < len(self.layers) else self.final_hc
+                normed = S.gated_stream_update(d, xs, post, nxt.norm, eps, comm=comm)
+            hid, _ = S.gr_mix_prenormed(normed, self.final_hc)
+            x = K.rmsnorm(hid, self.final_norm, eps, cfg.norm_bias)
+        else:
+            for li, L in enumerate(self.layers):
+                fn, base, scale = L.attn_hc
+                mix = S.hc_collapse(xs, fn, base, scale, cfg.hc_sinkhorn, norm_w=L.attn_norm, norm_eps=eps, norm_bias=cfg.norm_bias)
+                o = self.attn_block(li, L, mix.collapsed, b, kv, None)
+                S.hc_update(o, xs, mix.post, mix.comb, comm=comm)
+                fn, base, scale = L.mlp_hc
+                mix = S.hc_collapse(xs, fn, base, scale, cfg.hc_sinkhorn, norm_w=L.ffn_norm, norm_eps=eps, norm_bias=cfg.norm_bias)
+                d = self.ffn_block(li, L, mix.collapsed, b, None)
+                S.hc_update(d, xs, mix.post, mix.comb, comm=comm)
+            x = K.rmsnorm(S.head_mean(xs), self.final_norm, eps, cfg.norm_bias)
+        self.last_hidden, self.last_residual, self.last_streams = x, None, xs
+        if b.logits == LOGITS_NONE:
+            return None
+        if b.logits == LOGITS_LAST:
+            x = x[b.n - 1: b.n]
+        return self.lm_head.forward(x, out_f32=True)
 
     def _prenorm_ok(self, b: BatchRows) -> bool:
         """Decode steps of the plain dense model on one GPU: the two RMSNorms of a layer are computed inside the

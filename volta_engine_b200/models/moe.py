@@ -96,7 +96,7 @@ def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | N
 
 
 class MoELayer(DenseLayer):
-    __slots__ = ("router", "router_bias", "bank", "shared_gu", "shared_dn", "dense_ffn", "shared_gated")
+    __slots__ = ("router", "router_bias", "bank", "shared_gu", "shared_dn", "dense_ffn", "shared_gated", "tier")
 
 
 class MoEModel(DenseModel):
@@ -228,18 +228,22 @@ class MoEModel(DenseModel):
         k = cfg.top_k
         ids = torch.empty(rows, k, dtype=torch.int32, device=x.device)
         w = torch.empty(rows, k, dtype=torch.float32, device=x.device)
-        call("router_select", "pliiiipfiipp", ptr(logits), logits.stride(0), rows, cfg.n_experts, k,
+        call("router_select", "pliiiipfiippp", ptr(logits), logits.stride(0), rows, cfg.n_experts, k,
              1 if cfg.router == "sigmoid" else 0, ptr(L.router_bias), float(cfg.router_scale), cfg.n_group,
-             cfg.topk_group, ptr(ids), ptr(w))
+             cfg.topk_group, ptr(ids), ptr(w), self.heat[li].data_ptr() if self.heat is not None else 0)
         routes = rows * k
         y = pbuf if pbuf is not None else torch.empty(rows, H, dtype=x.dtype, device=x.device)
         I = bank.inter
-        if rows <= 16 or bank.gu_sf is None:
+        tier = getattr(L, "tier", None)
+        if tier is not None or rows <= 16 or bank.gu_sf is None:
+            # tiered residency: per-expert base pointers (device slot or pinned host memory) instead of the stacked bank
+            gu = (tier.tab_gu.data_ptr(), 0) if tier is not None else (ptr(bank.gu_p), ptr(bank.gu_s))
+            dn = (tier.tab_dn.data_ptr(), 0) if tier is not None else (ptr(bank.dn_p), ptr(bank.dn_s))
             a = torch.empty(routes, I, dtype=x.dtype, device=x.device)
-            call("nvfp4_moe_gemv", "ppppiiplipliiiiif", ptr(bank.gu_p), ptr(bank.gu_s), ptr(bank.gu_g), ptr(ids), bank.e0,
+            call("nvfp4_moe_gemv", "ppppiiplipliiiiif", gu[0], gu[1], ptr(bank.gu_g), ptr(ids), bank.e0,
                  bank.e_local, ptr(x), x.stride(0), k, ptr(a), a.stride(0), routes, 2 * I, H, 1, act, float(cfg.act_limit))
             d = torch.empty(routes, H, dtype=x.dtype, device=x.device)
-            call("nvfp4_moe_gemv", "ppppiiplipliiiiif", ptr(bank.dn_p), ptr(bank.dn_s), ptr(bank.dn_g), ptr(ids), bank.e0,
+            call("nvfp4_moe_gemv", "ppppiiplipliiiiif", dn[0], dn[1], ptr(bank.dn_g), ptr(ids), bank.e0,
                  bank.e_local, ptr(a), a.stride(0), 1, ptr(d), d.stride(0), routes, H, I, 0, act, 0.0)
             inv = None
         else:
@@ -294,6 +298,25 @@ class MoEModel(DenseModel):
         if shared is not None:
             y += shared.float()
         return y.to(x.dtype)
+
+    def enable_expert_tier(self, hot_slots: int, decay: float = 0.9):
+        """Keep only ``hot_slots`` experts of every MoE layer in device memory; the rest stay in pinned host memory and are
+        read in place by the mat-vec kernel. Returns the tiers (``ExpertTier.rebalance`` moves experts between the two)."""
+        from ..runtime.expert_tier import ExpertTier
+        tiers = []
+        for li, L in enumerate(self.layers):
+            if getattr(L, "bank", None) is not None and not L.dense_ffn:
+                L.tier = ExpertTier(L.bank, hot_slots, decay)
+                tiers.append((li, L.tier))
+        self.tiers = tiers
+        return tiers
+
+    def rebalance_experts(self, max_swaps: int = 2) -> int:
+        """Fold the routing histogram of every tiered layer into its decayed heat and swap experts whose heat says so."""
+        n = 0
+        for li, tier in getattr(self, "tiers", []):
+            n += tier.rebalance(self.heat[li, self.e0:self.e0 + self.e_local], max_swaps)
+        return n
 
     def expert_heat(self) -> dict:
         cfg = self.cfg

@@ -1,0 +1,99 @@
+"""Expert residency tier: hot experts in device slots, cold experts in pinned host memory read in place over PCIe.
+
+Every expert's packed weights and scales always have a pinned host copy; ``hot_slots`` device slots hold the experts that
+are routed to most. The mat-vec kernel takes a device table of per-expert base pointers, so residency changes are two
+stream-ordered copies (weights into the slot, then the table entries) and CUDA graphs that captured the kernel keep
+working. ``rebalance`` folds the router's histogram into a decayed heat and swaps the hottest cold experts with the
+coldest hot ones when the heat ratio exceeds a margin.
+
+Reference: inc/engine/modules/expert_tier.h:14-112 (hot slots, mapped cold experts, decayed heat, online rebalancing);
+the prefill path of a tiered layer runs the same route-indexed kernel (no staging a layer ahead).
+"""
+from __future__ import annotations
+
+import torch
+
+
+class ExpertTier:
+    NAMES = ("gu_p", "gu_s", "dn_p", "dn_s")
+
+    def __init__(self, bank, hot_slots: int, decay: float = 0.9, margin: float = 1.25):
+        E = bank.e_local
+        self.bank, self.E = bank, E
+        self.hot_slots = max(0, min(hot_slots, E))
+        self.decay, self.margin = decay, margin
+        dev = bank.gu_p.device
+        self.device = dev
+        pin = dev.type == "cuda"
+        self.cold = {}
+        for n in self.NAMES:
+            t = getattr(bank, n).cpu().contiguous()
+            self.cold[n] = t.pin_memory() if pin else t
+        self.slots = {n: torch.empty((self.hot_slots,) + tuple(self.cold[n].shape[1:]), dtype=self.cold[n].dtype, device=dev)
+                      for n in self.NAMES}
+        self.slot_of = [-1] * E                    # expert -> device slot, or -1 (cold)
+        self.expert_in = [-1] * self.hot_slots     # slot -> expert
+        self.tab_gu = torch.zeros(2 * E, dtype=torch.int64, device=dev)
+        self.tab_dn = torch.zeros(2 * E, dtype=torch.int64, device=dev)
+        self.heat = torch.zeros(E, dtype=torch.float32)
+        self._seen = torch.zeros(E, dtype=torch.float32)
+        self.swaps = 0
+        for e in range(E):
+            self._point_cold(e)
+        for s in range(self.hot_slots):
+            self._load(s, s)
+        # the stacked device bank is no longer read by the mat-vec path
+        for n in self.NAMES:
+            setattr(bank, n, None)
+        bank.gu_sf = bank.dn_sf = None
+
+    # ---- pointer tables -----------------------------------------------------------------------------------------------
+    def _set(self, e: int, gu_p: int, gu_s: int, dn_p: int, dn_s: int) -> None:
+        self.tab_gu[2 * e:2 * e + 2] = torch.tensor([gu_p, gu_s], dtype=torch.int64).to(self.device, non_blocking=False)
+        self.tab_dn[2 * e:2 * e + 2] = torch.tensor([dn_p, dn_s], dtype=torch.int64).to(self.device, non_blocking=False)
+
+    def _point_cold(self, e: int) -> None:
+        c = self.cold
+        self._set(e, c["gu_p"][e].data_ptr(), c["gu_s"][e].data_ptr(), c["dn_p"][e].data_ptr(), c["dn_s"][e].data_ptr())
+
+    def _load(self, e: int, slot: int) -> None:
+        """Expert ``e`` becomes resident in ``slot`` (whose previous occupant turns cold first)."""
+        old = self.expert_in[slot]
+        if old >= 0:
+            self._point_cold(old)
+            self.slot_of[old] = -1
+        for n in self.NAMES:
+            self.slots[n][slot].copy_(self.cold[n][e], non_blocking=True)      # stream-ordered behind the readers of the slot
+        s = self.slots
+        self._set(e, s["gu_p"][slot].data_ptr(), s["gu_s"][slot].data_ptr(), s["dn_p"][slot].data_ptr(), s["dn_s"][slot].data_ptr())
+        self.slot_of[e], self.expert_in[slot] = slot, e
+
+    # ---- policy -------------------------------------------------------------------------------------------------------
+    def rebalance(self, counts: torch.Tensor, max_swaps: int = 2) -> int:
+        """``counts``: the router's cumulative histogram over this rank's experts. Returns the number of swaps made."""
+        c = counts.detach().float().cpu()
+        self.heat = self.heat * self.decay + (c - self._seen)
+        self._seen = c.clone()
+        if self.hot_slots == 0 or self.hot_slots == self.E:
+            return 0
+        n = 0
+        for _ in range(max_swaps):
+            cold = [e for e in range(self.E) if self.slot_of[e] < 0]
+            hot = [e for e in range(self.E) if self.slot_of[e] >= 0]
+            up = max(cold, key=lambda e: (float(self.heat[e]), -e))
+            down = min(hot, key=lambda e: (float(self.heat[e]), e))
+            if float(self.heat[up]) <= float(self.heat[down]) * self.margin or float(self.heat[up]) <= 0:
+                break
+            self._load(up, self.slot_of[down])
+            n += 1
+        self.swaps += n
+        return n
+
+    def resident(self) -> list[int]:
+        return sorted(e for e in range(self.E) if self.slot_of[e] >= 0)
+
+    def device_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.slots.values())
+
+    def host_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.cold.values())
