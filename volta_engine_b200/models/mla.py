@@ -34,6 +34,7 @@ class MLAConfig(MoEConfig):
     qk_rope: int = 64
     v_head_dim: int = 128
     mtp_layers: int = 0
+    dsa: bool = False              # sparse attention: a pooled-key indexer picks the 2048 tokens a decode row attends to
     model_type: str = "mla_moe"
 
     @classmethod
@@ -59,7 +60,7 @@ class MLAConfig(MoEConfig):
 
 
 class MLALayer(MoELayer):
-    __slots__ = ("qkv_a", "q_a_norm", "kv_a_norm", "q_b", "w_uk", "w_uv", "w_ukv")
+    __slots__ = ("qkv_a", "q_a_norm", "kv_a_norm", "q_b", "w_uk", "w_uv", "w_ukv", "dsa")
 
 
 class MLAModel(MoEModel):
@@ -75,6 +76,8 @@ class MLAModel(MoEModel):
         self.a_rows = (cfg.q_lora_rank + LAT + ROPE + 127) // 128 * 128
         self.mtp = None
         self.mla_ws = None
+        self.dsa_states: dict = {}
+        self.dsa_scratch = None
 
     # ------------------------------------------------------------------------------------------ weights
     def _init_attention(self, L, rnd, search):
@@ -97,6 +100,13 @@ class MLAModel(MoEModel):
         wo = rnd(H, cfg.n_q * cfg.v_head_dim)
         L.o_proj = self._make_linear(wo[:, r * hl * cfg.v_head_dim:(r + 1) * hl * cfg.v_head_dim].contiguous(), search)
         L.qkv = None
+        L.dsa = None
+        if cfg.dsa:                                  # indexer weights (replicated on every rank: the list must agree)
+            from ..ops import dsa as D
+            bf = torch.bfloat16
+            L.dsa = D.DSAWeights(proj=LinearBF16(rnd(D.PROJ, H).to(bf) * 8), q_proj=LinearBF16(rnd(D.HEADS * D.DIM, cfg.q_lora_rank).to(bf) * 8),
+                                 ln_w=torch.ones(D.DIM, device=self.device, dtype=bf), ln_b=torch.zeros(D.DIM, device=self.device, dtype=bf),
+                                 ape=(rnd(D.POOL, D.DIM) * 10).to(bf))
 
     def _attn_bytes(self, L) -> int:
         return L.qkv_a.nbytes() + L.q_b.nbytes() + L.o_proj.nbytes() + (L.w_uk.numel() + L.w_uv.numel()) * 2
@@ -136,8 +146,15 @@ class MLAModel(MoEModel):
         ckv = K.rmsnorm(a[:, ql:ql + LAT], L.kv_a_norm, cfg.rms_eps, cfg.norm_bias)
         krope = a[:, ql + LAT: ql + LAT + ROPE]
         q = L.q_b.forward(q_lat)                                   # [n, heads * 192]
+        sel = None
+        if L.dsa is not None:
+            from ..ops import dsa as D
+            st = self._dsa_state(li, kv)
+            wts = D.update(st, L.dsa, x, b.slot, b.pos)
+            if b.tiles is None:                                    # decode / verify rows attend to the indexer's list
+                sel = D.select(st, L.dsa.q_proj.forward(q_lat).contiguous(), wts, b.slot, b.pos)
         if not x.is_cuda:
-            att = self._attn_reference(L, q, ckv, krope, b, kv, pool)
+            att = self._attn_reference(L, q, ckv, krope, b, kv, pool, sel)
             return L.o_proj.forward(att, out=pbuf)
         call("mla_rope_store", "pliiplplpppipifi", ptr(q), q.stride(0), self.qd, self.heads, ptr(ckv), ckv.stride(0),
              ptr(krope), krope.stride(0), ptr(b.pos), ptr(b.slot), ptr(kv.page_table), kv.page_table.shape[1], ptr(pool),
@@ -149,8 +166,24 @@ class MLAModel(MoEModel):
             o_part, lse_part, max_splits = self.mla_ws
             nsplit = max(1, min(max_splits, b.nsplit))
             o_lat = torch.empty(n, self.heads, LAT, dtype=x.dtype, device=x.device)
-            call("mla_decode", "pppppppipliiifp", ptr(q_abs), ptr(o_lat), ptr(o_part), ptr(lse_part), ptr(b.pos), ptr(b.slot),
-                 ptr(kv.page_table), kv.page_table.shape[1], ptr(pool), pool.shape[0], n, self.heads, nsplit,
+            a_pos, a_slot, a_table, a_pool = b.pos, b.slot, kv.page_table, pool
+            if sel is not None:
+                # the listed tokens' latent rows form a short virtual sequence per row in scratch pages
+                from ..ops import dsa as D
+                idx, nkeys = sel
+                if self.dsa_scratch is None or self.dsa_scratch[0].shape[0] < n * D.PAGES_PER_ROW:
+                    rows_cap = max(16, n)
+                    self.dsa_scratch = (torch.zeros(rows_cap * D.PAGES_PER_ROW, 1, 64, LAT_ROW, dtype=x.dtype, device=x.device),
+                                        torch.arange(rows_cap * D.PAGES_PER_ROW, dtype=torch.int32, device=x.device)
+                                        .reshape(rows_cap, D.PAGES_PER_ROW).contiguous(),
+                                        torch.arange(rows_cap, dtype=torch.int32, device=x.device))
+                a_pool, a_table, ar = self.dsa_scratch
+                D.gather_rows(pool, kv.page_table, b.slot, idx, nkeys, a_pool)
+                a_pos = nkeys - 1
+                a_slot = torch.where(b.slot < 0, b.slot, ar[:n])
+                nsplit = 1 if nsplit == 1 else min(nsplit, 8)
+            call("mla_decode", "pppppppipliiifp", ptr(q_abs), ptr(o_lat), ptr(o_part), ptr(lse_part), ptr(a_pos), ptr(a_slot),
+                 ptr(a_table), a_table.shape[1], ptr(a_pool), a_pool.shape[0], n, self.heads, nsplit,
                  float(self.scale), ptr(K.status_word(x.device)))
             att = torch.empty(n, self.heads * vd, dtype=x.dtype, device=x.device)
             call("mla_expand_out", "pppliii", ptr(o_lat), ptr(L.w_uv), ptr(att), att.stride(0), n, self.heads, vd)
@@ -183,7 +216,14 @@ class MLAModel(MoEModel):
         out = K.attention(q256.reshape(n, hl * 256), b.pos, slot0, table, kfull, vfull, hl, hl, 256, self.scale, tiles=tiles)
         return out.reshape(n, hl, 256)[..., :vd].reshape(n, hl * vd).contiguous()
 
-    def _attn_reference(self, L, q, ckv, krope, b: BatchRows, kv, pool):
+    def _dsa_state(self, li, kv):
+        st = self.dsa_states.get(li)
+        if st is None:
+            from ..ops import dsa as D
+            st = self.dsa_states[li] = D.DSAState(kv.max_slots, kv.max_pages * 64, self.device)
+        return st
+
+    def _attn_reference(self, L, q, ckv, krope, b: BatchRows, kv, pool, sel=None):
         """fp32 oracle: rotate, store the latent row, per-row softmax over the expanded keys."""
         from ..ops.reference import rope_rotate
         cfg = self.cfg
@@ -208,6 +248,8 @@ class MLAModel(MoEModel):
             p = int(b.pos[r])
             pages = kv.page_table[s, : p // 64 + 1].long()
             lat = pool[pages, 0].reshape(-1, LAT_ROW)[: p + 1].float()
+            if sel is not None:                                                   # sparse rows: only the listed positions
+                lat = lat[sel[0][r, : int(sel[1][r])].long()]
             k_nope = torch.einsum("tc,hdc->htd", lat[:, :LAT], wuk)               # [h, t, nope]
             sc = torch.einsum("hd,htd->ht", qv[r, :, :nope].float(), k_nope)
             sc = sc + qv[r, :, nope:].float() @ lat[:, LAT:].t()
