@@ -87,3 +87,63 @@ def test_quantize_tool_round_trip(tmp_path):
     from volta_engine_b200.quant import nvfp4 as qn
     rel = (qn.dequantize_nvfp4(wq.packed, wq.scales, wq.gscale) - w0).norm() / w0.norm()
     assert rel < 0.12
+
+
+def test_tune_expert_lowers_the_held_out_error_and_matches_exl3_semantics():
+    import torch
+    from volta_engine_b200.quant import exl3 as ex
+    from volta_engine_b200.tools import tune as T
+    from volta_engine_b200.train import grad as G
+    g = torch.Generator().manual_seed(0)
+    H, I, rows = 128, 256, 400
+    orig = {"gate": torch.randn(H, I, generator=g) * 0.08, "up": torch.randn(H, I, generator=g) * 0.08,
+            "down": torch.randn(I, H, generator=g) * 0.08}
+    # a "quantised" expert: the original weights with multiplicative channel noise that scale tuning can undo
+    quant = {}
+    for n, W in orig.items():
+        su = 1.0 + 0.2 * torch.randn(W.shape[0], generator=g)
+        sv = 1.0 + 0.2 * torch.randn(W.shape[1], generator=g)
+        quant[n] = G.ScaledLinear((W / su[:, None] / sv[None, :]).contiguous(), torch.ones(W.shape[0]), torch.ones(W.shape[1]))
+    X = torch.randn(rows, H, generator=g)
+    w = torch.rand(rows, generator=g)
+    res = T.tune_expert(orig, quant, X, w, steps=60, lr=0.02)
+    assert res.err_after < 0.5 * res.err_before and res.best_step > 0
+    assert res.train_curve[-1] < res.train_curve[0]
+    assert set(res.scales) == {"gate", "up", "down"}
+    # the trainable view of an EXL3 tensor computes the same linear map as the kernel-side definition
+    codes = ex.random_codes(128, 128, 3, torch.Generator().manual_seed(1))
+    suh, svh = torch.rand(128) + 0.5, torch.rand(128) + 0.5
+    lin = T.exl3_scaled_linear(codes, 3, suh, svh)
+    x = torch.randn(5, 128, generator=g)
+    y, _ = G.scaled_linear_forward(lin, x)
+    assert torch.allclose(y, ex.linear_reference(x, codes, 3, suh, svh), atol=1e-3, rtol=1e-3)
+
+
+def test_sessions_tool_builds_message_bodies(tmp_path):
+    import json
+    from volta_engine_b200.tools import sessions as S
+    lines = [
+        json.dumps({"type": "system", "message": {"role": "system", "content": "be brief"}}),
+        json.dumps({"type": "user", "message": {"role": "user", "content": "hello"}}),
+        json.dumps({"type": "user", "message": {"role": "user", "content": [{"type": "text", "text": "again"}]}}),
+        json.dumps({"type": "assistant", "isSidechain": True, "message": {"role": "assistant", "content": "side"}}),
+        json.dumps({"type": "assistant", "message": {"role": "assistant", "content": [
+            {"type": "thinking", "thinking": "hm"}, {"type": "tool_use", "id": "t1", "name": "ls", "input": {"p": "."}}]}}),
+        json.dumps({"type": "user", "message": {"role": "user", "content": [{"type": "tool_result", "tool_use_id": "t1", "content": "a b"}]}}),
+        "not json",
+        json.dumps({"type": "assistant", "message": {"role": "assistant", "content": "x" * 50}}),
+        json.dumps({"type": "user", "message": {"role": "user", "content": "tail that is cut"}}),
+    ]
+    body = S.session_to_body(lines, max_chars=40)
+    roles = [m["role"] for m in body["messages"]]
+    assert roles == ["user", "assistant", "user", "assistant"] and body["system"] == "be brief"
+    assert [b["type"] for b in body["messages"][0]["content"]] == ["text", "text"]           # consecutive user entries joined
+    assert body["messages"][1]["content"][1]["name"] == "ls" and body["messages"][2]["content"][0]["type"] == "tool_result"
+    p = tmp_path / "s.jsonl"
+    p.write_text("\n".join(lines))
+    assert S.main(["--out", str(tmp_path / "o"), "--max-chars", "40", str(p)]) == 0
+    assert json.loads((tmp_path / "o" / "req_0.json").read_text())["messages"][0]["role"] == "user"
+    reqs = S.prompts_to_requests(["a", {"prompt": "b"}], "m", 10)
+    assert reqs[1]["messages"][0]["content"] == "b" and reqs[0]["max_tokens"] == 10
+    ex = S.exchange_to_body("q", {"choices": [{"message": {"reasoning_content": "r", "content": "c"}}]})
+    assert [b["type"] for b in ex["messages"][1]["content"]] == ["thinking", "text"]
