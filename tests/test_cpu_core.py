@@ -148,3 +148,29 @@ def test_expert_tier_policy_swaps_the_hottest_cold_expert_in():
     assert t.rebalance(counts, max_swaps=4) == 0                                           # no new routing: heat only decays
     counts2 = counts + torch.tensor([0.0, 0.0, 30.0, 0.0, 0.0, 0.0])
     assert t.rebalance(counts2, max_swaps=4) == 1 and 2 in t.resident() and t.swaps == 2
+
+
+def test_sentencepiece_style_tokenizer(tmp_path):
+    import json
+    from volta_engine_b200.loader.tokenizer import Tokenizer
+    sp = "▁"
+    pieces = ["<unk>", "<bos>", "<eos>"] + [f"<0x{b:02X}>" for b in range(256)] + \
+        [sp, "h", "e", "l", "o", "w", "r", "d", "he", "ll", "hell", "hello", sp + "w", "or", sp + "wor", "ld", sp + "world", sp + sp, "é"]
+    vocab = {p: i for i, p in enumerate(pieces)}
+    merges = [["h", "e"], ["l", "l"], ["he", "ll"], ["hell", "o"], [sp, "w"], ["o", "r"], [sp + "w", "or"], ["l", "d"],
+              [sp + "wor", "ld"], [sp, sp]]
+    tj = {"model": {"type": "BPE", "byte_fallback": True, "vocab": vocab, "merges": merges},
+          "added_tokens": [{"id": 1, "content": "<bos>"}, {"id": 2, "content": "<eos>"}]}
+    (tmp_path / "tokenizer.json").write_text(json.dumps(tj))
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "gemma3"}))
+    t = Tokenizer.load(str(tmp_path))
+    assert t.mode == "spm"
+    ids = t.encode("hello world")
+    assert ids == [vocab["hello"], vocab[sp + "world"]]
+    assert t.decode(ids) == "hello world"
+    ids = t.encode("<bos>hello  wé中")
+    # the lower-ranked merge (space + w) wins over the later (space + space) one
+    want = [1, vocab["hello"], vocab[sp], vocab[sp + "w"], vocab["é"]] + [vocab[f"<0x{b:02X}>"] for b in "中".encode()]
+    assert ids == want and t.decode(ids, skip_special=True) == "hello  wé中"
+    long = ("hello world " * 3000).strip()                     # whole-text merging stays fast on long inputs
+    assert len(t.encode(long)) == 8999 and t.decode(t.encode(long)) == long

@@ -5,8 +5,10 @@
 // implemented as a hand-written scanner over code points instead of a regex engine.
 #include <algorithm>
 #include <cstdint>
+#include <cstdio>
 #include <fstream>
 #include <mutex>
+#include <queue>
 #include <sstream>
 #include <string>
 #include <unordered_map>
@@ -16,7 +18,7 @@
 
 namespace vh {
 
-enum PretokMode { kQwen = 0, kGpt2 = 1, kLlama3 = 2, kDeepseek = 3 };
+enum PretokMode { kQwen = 0, kGpt2 = 1, kLlama3 = 2, kDeepseek = 3, kSpm = 4 };
 
 static uint32_t next_cp(const std::string& s, size_t& i) {
   unsigned char c = (unsigned char)s[i];
@@ -196,8 +198,27 @@ class Tokenizer {
     for (int b = 0; b < 256; ++b) byte_id[b] = -1;
   }
 
+  // SentencePiece-style vocabularies (Gemma): pieces are plain UTF-8 with U+2581 standing for a space, bytes that have no
+  // piece are spelled <0xNN>, merges run over the whole text between special tokens (no pre-token split), ranked by the
+  // merge list or, when the file carries scores instead, by the score of the merged piece.
+  std::vector<float> scores;                               // per id; empty when merges are ranked by the list
+  int spm_byte_id[256];
+  int unk_id = -1;
+
   std::string piece_to_bytes(const std::string& piece) const {
     std::string out;
+    if (mode == kSpm) {
+      unsigned v = 0;
+      if (piece.size() == 6 && piece.compare(0, 3, "<0x") == 0 && piece[5] == '>' && sscanf(piece.c_str() + 3, "%2x", &v) == 1) {
+        out.push_back((char)v);
+        return out;
+      }
+      for (size_t i = 0; i < piece.size();) {
+        if (piece.compare(i, 3, "\xE2\x96\x81") == 0) { out.push_back(' '); i += 3; }
+        else out.push_back(piece[i++]);
+      }
+      return out;
+    }
     for (size_t i = 0; i < piece.size();) {
       uint32_t cp = next_cp(piece, i);
       auto it = cp_to_byte.find(cp);
@@ -217,6 +238,11 @@ class Tokenizer {
     } else {
       piece_to_id[piece] = id;
       id_to_bytes[id] = piece_to_bytes(piece);
+      if (mode == kSpm) {
+        if ((size_t)id >= id_to_piece.size()) id_to_piece.resize(id + 1);
+        id_to_piece[id] = piece;
+        raw_to_id[piece] = id;
+      }
     }
   }
 
@@ -226,8 +252,75 @@ class Tokenizer {
     for (int b = 0; b < 256; ++b) {
       auto it = piece_to_id.find(byte_enc[b]);
       byte_id[b] = it == piece_to_id.end() ? -1 : it->second;
+      char name[8];
+      snprintf(name, sizeof(name), "<0x%02X>", b);
+      auto jt = piece_to_id.find(name);
+      spm_byte_id[b] = jt == piece_to_id.end() ? -1 : jt->second;
     }
+    auto u = piece_to_id.find("<unk>");
+    if (u != piece_to_id.end()) unk_id = u->second;
   }
+
+  // Whole-text BPE for the SentencePiece mode: linked list of symbols + a heap of candidate merges (lazy invalidation),
+  // O(n log n) instead of the per-word quadratic loop.
+  void bpe_spm(const std::string& text, std::vector<int>& out) {
+    std::string norm;
+    norm.reserve(text.size() + 8);
+    for (char c : text) {
+      if (c == ' ') norm += "\xE2\x96\x81";
+      else norm.push_back(c);
+    }
+    struct Sym { int id; int prev, next; bool alive; };
+    std::vector<Sym> sy;
+    for (size_t i = 0; i < norm.size();) {
+      const size_t a = i;
+      next_cp(norm, i);
+      auto it = piece_to_id.find(norm.substr(a, i - a));
+      if (it != piece_to_id.end()) {
+        sy.push_back({it->second, 0, 0, true});
+      } else {
+        for (size_t b = a; b < i; ++b) {
+          const int id = spm_byte_id[(unsigned char)norm[b]];
+          sy.push_back({id >= 0 ? id : unk_id, 0, 0, true});
+        }
+      }
+    }
+    const int n = (int)sy.size();
+    for (int k = 0; k < n; ++k) { sy[k].prev = k - 1; sy[k].next = k + 1 < n ? k + 1 : -1; }
+    struct Cand { double pri; int pos; int left, right, merged; };
+    auto worse = [](const Cand& a, const Cand& b) { return a.pri != b.pri ? a.pri > b.pri : a.pos > b.pos; };
+    std::priority_queue<Cand, std::vector<Cand>, decltype(worse)> heap(worse);
+    auto consider = [&](int k) {
+      if (k < 0 || sy[k].next < 0) return;
+      const int a = sy[k].id, b = sy[sy[k].next].id;
+      if (a < 0 || b < 0) return;
+      if (scores.empty()) {
+        auto it = merge_rank.find({a, b});
+        if (it != merge_rank.end()) heap.push({(double)it->second, k, a, b, merge_to[{a, b}]});
+      } else {
+        auto it = raw_to_id.find(id_to_piece[a] + id_to_piece[b]);
+        if (it != raw_to_id.end()) heap.push({-(double)scores[it->second], k, a, b, it->second});
+      }
+    };
+    for (int k = 0; k < n; ++k) consider(k);
+    while (!heap.empty()) {
+      const Cand c = heap.top();
+      heap.pop();
+      if (!sy[c.pos].alive || sy[c.pos].id != c.left) continue;
+      const int r = sy[c.pos].next;
+      if (r < 0 || !sy[r].alive || sy[r].id != c.right) continue;
+      sy[c.pos].id = c.merged;
+      sy[r].alive = false;
+      sy[c.pos].next = sy[r].next;
+      if (sy[r].next >= 0) sy[sy[r].next].prev = c.pos;
+      consider(sy[c.pos].prev);
+      consider(c.pos);
+    }
+    for (int k = 0; k >= 0 && k < n; k = sy[k].next)
+      if (sy[k].id >= 0) out.push_back(sy[k].id);
+  }
+  std::vector<std::string> id_to_piece;                     // SentencePiece mode: the piece text of every id
+  std::unordered_map<std::string, int> raw_to_id;
 
   void add_merge(const std::string& a, const std::string& b, int rank) {
     auto ia = piece_to_id.find(a), ib = piece_to_id.find(b), ic = piece_to_id.find(a + b);
@@ -274,6 +367,7 @@ class Tokenizer {
   }
 
   void encode_plain(const std::string& text, std::vector<int>& out) {
+    if (mode == kSpm) { bpe_spm(text, out); return; }
     std::vector<std::string> words;
     pretokenize(text, mode, words);
     for (auto& w : words) bpe_word(w, out);
@@ -324,6 +418,17 @@ static Tokenizer* load_tokenizer_json(const std::string& path, int mode) {
   const Json* vocab = model->find("vocab");
   if (vocab && vocab->is_object())
     for (auto& kv : vocab->obj) t->add_piece(kv.first, (int)kv.second.as_int(), false);
+  if (vocab && vocab->is_array()) {                 // unigram-style list of [piece, score]: merges ranked by score
+    int id = 0;
+    for (auto& e : vocab->arr) {
+      if (e.is_array() && e.arr.size() == 2) {
+        t->add_piece(e.arr[0].s, id, false);
+        if ((size_t)id >= t->scores.size()) t->scores.resize(id + 1, -1e30f);
+        t->scores[id] = (float)e.arr[1].as_double();
+      }
+      ++id;
+    }
+  }
   if (const Json* added = j.find("added_tokens"))
     for (auto& a : added->arr) {
       const Json* id = a.find("id");

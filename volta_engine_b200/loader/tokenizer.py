@@ -1,4 +1,5 @@
-"""Python face of the native byte-level BPE tokenizer (csrc/host/tokenizer.cpp).
+"""Python face of the native tokenizer (csrc/host/tokenizer.cpp): byte-level BPE families and the SentencePiece-style
+BPE with byte fallback (Gemma).
 
 Reference surface: ``Tokenizer::load / encode / decode`` over ``tokenizer.json`` or ``vocab.json`` +
 ``merges.txt`` (inc/engine/loader/tokenizer.h:11-88).
@@ -11,7 +12,7 @@ import os
 
 from .. import _lib
 
-MODES = {"qwen": 0, "gpt2": 1, "llama3": 2, "deepseek": 3, "glm": 0}
+MODES = {"qwen": 0, "gpt2": 1, "llama3": 2, "deepseek": 3, "glm": 0, "spm": 4, "gemma": 4}
 
 
 class Tokenizer:
@@ -41,8 +42,14 @@ class Tokenizer:
             if os.path.exists(cp):
                 with open(cp) as f:
                     mt = json.load(f).get("model_type", "")
-            mode = "deepseek" if "deepseek" in mt else "llama3" if "llama" in mt else "qwen"
+            mode = "deepseek" if "deepseek" in mt else "llama3" if "llama" in mt else "spm" if "gemma" in mt else "qwen"
         tj = os.path.join(model_dir, "tokenizer.json")
+        if mode == "qwen" and os.path.exists(tj):
+            # SentencePiece-style vocabularies announce themselves: byte fallback pieces and no byte-level pre-tokenizer
+            with open(tj) as f:
+                head = json.load(f)
+            if head.get("model", {}).get("byte_fallback"):
+                mode = "spm"
         if os.path.exists(tj):
             h = lib.vh_tok_load_json(tj.encode(), MODES[mode])
         else:

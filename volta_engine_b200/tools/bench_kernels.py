@@ -58,6 +58,7 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=4096, help="rows of the GEMM benchmarks")
     ap.add_argument("--iters", type=int, default=0, help="with --no-graph: eager launches per case")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--nsplit", type=int, default=0, help="attention: key splits per kv head (0 = the engine's choice)")
     a = ap.parse_args(argv)
     from ..ops import kernels as K
     from ..ops import linear_exl3 as LX
@@ -150,7 +151,7 @@ def main(argv=None) -> int:
             q = torch.randn(1, (nq + 2 * nkv) * hd, device=dev).to(torch.bfloat16)
             ws = K.AttnWorkspace(1, nq, hd, 64, dev)
             out = torch.empty(1, nq * hd, dtype=torch.bfloat16, device=dev)
-            nsplit = min(32, max(1, 148 * 3 // nkv))
+            nsplit = a.nsplit or min(32, max(1, 148 * 3 // nkv))
             fn = lambda: K.attention(q, pos, slot, table, kpool, vpool, nq, nkv, hd, 1 / math.sqrt(hd), out=out,
                                      nsplit=nsplit, ws=ws)
             r = run("attention", fn, 1 if a.no_graph else 4, nbytes=2 * ctx * nkv * hd * 2)
