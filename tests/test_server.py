@@ -137,3 +137,38 @@ def test_monitor_stats_metrics(server):
     prom = call(server, "GET", "/metrics/prometheus", key=None)[1]
     assert "volta_requests_total" in prom and "volta_prefix_cache_hits_total" in prom
     assert call(server, "GET", "/metrics", key=None)[0] == 200
+
+
+def test_image_parts_reach_the_multimodal_front_end(server):
+    import base64
+    from volta_engine_b200.runtime.multimodal import MmLayout
+    from volta_engine_b200.server.protocol import IMAGE_MARK, parse_anthropic, parse_openai
+    png = base64.b64encode(b"\x89PNG fake").decode()
+    body = {"model": "tiny-test", "max_tokens": 4, "messages": [{"role": "user", "content": [
+        {"type": "text", "text": "what is "}, {"type": "image_url", "image_url": {"url": "data:image/png;base64," + png}},
+        {"type": "text", "text": " ?"}]}]}
+    cr = parse_openai(body, {})
+    assert cr.images == [b"\x89PNG fake"] and cr.messages[0]["content"] == "what is " + IMAGE_MARK + " ?"
+    ab = {"model": "m", "max_tokens": 4, "messages": [{"role": "user", "content": [
+        {"type": "image", "source": {"type": "base64", "media_type": "image/png", "data": png}}, {"type": "text", "text": "hi"}]}]}
+    ca = parse_anthropic(ab, {})
+    assert ca.images == [b"\x89PNG fake"] and ca.messages[0]["content"].startswith(IMAGE_MARK)
+    # without a vision tower the request is refused; with a front end the image bytes arrive there
+    st, data = call(server, "POST", "/v1/chat/completions", body)
+    assert st == 400 and "vision tower" in data
+    seen = []
+
+    class Front:
+        def prepare(self, ids, images):
+            seen.append(list(images))
+            return ids, MmLayout(len(ids), []), None
+    server.gen.mm_frontend = Front()
+    try:
+        st, data = call(server, "POST", "/v1/chat/completions", body)
+        assert st == 200 and seen == [[b"\x89PNG fake"]] and json.loads(data)["usage"]["completion_tokens"] > 0
+        bad = json.loads(json.dumps(body))
+        bad["messages"][0]["content"][1]["image_url"]["url"] = "http://example.com/x.png"
+        st, data = call(server, "POST", "/v1/chat/completions", bad)
+        assert st == 400 and "data: URL" in data
+    finally:
+        server.gen.mm_frontend = None

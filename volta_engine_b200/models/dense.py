@@ -46,6 +46,7 @@ class DenseConfig:
                                   # only to the last ``sliding_window`` keys; 0: ``sliding_window`` on every layer
     rope_theta_local: float = 0.0 # rotary base of the windowed layers (0 = rope_theta)
     sandwich_norm: bool = False   # extra RMSNorm on the output of the attention and FFN blocks before the residual add
+    mrope_sections: tuple = ()    # (time, height) rotary pair counts of multimodal rope; the rest turns with the width axis
     residual: str = "plain"       # plain | gated (fp32 gated residual streams) | hc (4 fp32 hyper-connection streams)
     hc_mult: int = 4              # residual streams of the gated form
     hc_rank: int = 64             # width of the gated residual's low-rank gate
@@ -207,6 +208,8 @@ class DenseModel:
         if self._prenorm_ok(b):
             return self._forward_prenorm(b, kv)
         h = K.embed(b.ids, self.embed, scale=cfg.embed_scale)          # residual stream [n, H] bf16
+        if b.embeds is not None:                                        # image tokens: rows of the vision tower
+            h = torch.where(b.embed_mask[:, None], b.embeds.to(h.dtype), h)
         L0 = self.layers[0]
         x = K.rmsnorm(h, L0.attn_norm, cfg.rms_eps, cfg.norm_bias)
         # multi-GPU chunks: the residual stream is row-sharded over ranks (sequence-parallel) and the
@@ -387,8 +390,9 @@ class DenseModel:
             K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
             K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
                              self.nq * self.hd)
+        mrope = (b.pos3, tuple(cfg.mrope_sections)) if b.pos3 is not None and cfg.mrope_sections else None
         K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
-                     self.layer_theta(li), cfg.rope_interleaved)
+                     self.layer_theta(li), cfg.rope_interleaved, mrope=mrope)
         att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
                           self.scale, window=self.layer_window(li), key_end=b.key_end, tiles=b.tiles,
                           nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)

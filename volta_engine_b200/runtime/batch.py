@@ -30,6 +30,9 @@ class BatchRows:
     key_end: torch.Tensor | None = None
     host_slots: list = field(default_factory=list)
     host_pos: list = field(default_factory=list)
+    pos3: torch.Tensor | None = None        # [3, n] int32 rotary positions (time, height, width) of multimodal prompts
+    embeds: torch.Tensor | None = None      # [n, H] rows that replace the token embedding where embed_mask is set
+    embed_mask: torch.Tensor | None = None  # [n] bool
 
     @classmethod
     def make(cls, ids, pos, slots, device, logits=LOGITS_ALL, G=1, prefill=False, nsplit=1):

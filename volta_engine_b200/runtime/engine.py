@@ -71,6 +71,11 @@ class Engine:
         self.s_cand_ids = torch.zeros(R, NUM_CANDIDATES, dtype=torch.int32, device=dev)
         self.s_cand_vals = torch.zeros(R, NUM_CANDIDATES, dtype=torch.float32, device=dev)
         self.s_cand_lse = torch.zeros(R, dtype=torch.float32, device=dev)
+        # multimodal rotary positions: per-slot offset of the rotary position against the sequence index
+        self.mrope = bool(getattr(getattr(model, "cfg", None), "mrope_sections", ()))
+        self.h_delta = [0] * kv.max_slots
+        self.s_delta = torch.zeros(kv.max_slots, dtype=torch.int32, device=dev)
+        self.s_pos3 = torch.zeros(3 * R, dtype=torch.int32, device=dev)
         self.graphs: dict[tuple, _Graph] = {}
         self.nsplit_cap = int(os.environ.get("VOLTA_NSPLIT_CAP", "32"))   # most key splits of a decode row
         if self.cuda:
@@ -91,7 +96,7 @@ class Engine:
             out_tok[:rows].copy_(merged)
 
     # ------------------------------------------------------------------------------------------ prefill
-    def prefill(self, slot: int, tokens: list[int], start_pos: int = 0) -> int:
+    def prefill(self, slot: int, tokens: list[int], start_pos: int = 0, mm=None) -> int:
         """Run the prompt rows [start_pos, start_pos + len(tokens)) of ``slot`` through the model in chunks
         and return the greedy next token (host int)."""
         n = len(tokens)
@@ -110,6 +115,7 @@ class Engine:
             else:
                 b = BatchRows.make(ids, pos, [slot] * c, self.device, LOGITS_LAST if last else LOGITS_NONE, G,
                                    prefill=True)
+            self._mm_rows(b, slot, start_pos + done, c, mm)
             logits = self.model.forward(b, self.kv)
             if last:
                 rows = logits.shape[0]
@@ -121,6 +127,11 @@ class Engine:
     # ------------------------------------------------------------------------------------------ decode
     def _forward_static(self, rows: int, nsplit: int, topk: bool = False) -> torch.Tensor:
         b = BatchRows(self.s_ids[:rows], self.s_pos[:rows], self.s_slot[:rows], rows, LOGITS_ALL, None, nsplit)
+        if self.mrope:
+            # rotary position = sequence index + the slot's offset left by its multimodal prompt (all three axes alike)
+            d = self.s_delta[self.s_slot[:rows].clamp(min=0).long()]
+            b.pos3 = self.s_pos3[:3 * rows].view(3, rows)
+            b.pos3.copy_((self.s_pos[:rows] + d).unsqueeze(0).expand(3, rows))
         logits = self.model.forward(b, self.kv)
         self._sample_greedy(logits, self.s_tok, self.s_val, rows)
         if topk:
@@ -201,7 +212,24 @@ class Engine:
             out.append(merge_shards(parts))
         return out
 
-    def prefill_rows(self, slot: int, tokens: list[int], start_pos: int, want_token: bool) -> int:
+    def set_rope_delta(self, slot: int, delta: int) -> None:
+        """Rotary offset of a slot's decode rows (multimodal prompts advance the rotary position by less than their token
+        count); 0 for text."""
+        if self.mrope and self.h_delta[slot] != delta:
+            self.h_delta[slot] = delta
+            self.s_delta[slot] = delta
+
+    def _mm_rows(self, b: BatchRows, slot: int, start_pos: int, c: int, mm) -> None:
+        if not self.mrope:
+            return
+        if mm is not None:
+            b.pos3, b.embeds, b.embed_mask = mm.chunk(start_pos, start_pos + c, self.device, self.model.cfg.hidden)
+            self.set_rope_delta(slot, mm.delta)
+        else:
+            p = torch.arange(start_pos + self.h_delta[slot], start_pos + self.h_delta[slot] + c, dtype=torch.int32)
+            b.pos3 = p.unsqueeze(0).expand(3, c).contiguous().to(self.device)
+
+    def prefill_rows(self, slot: int, tokens: list[int], start_pos: int, want_token: bool, mm=None) -> int:
         """One prefill forward over ``tokens`` (<= prefill_chunk rows) of ``slot``; returns the greedy next
         token when ``want_token`` (else -1). Used by the scheduler to interleave prefill with decode steps."""
         c = len(tokens)
@@ -214,6 +242,7 @@ class Engine:
         else:
             b = BatchRows.make(tokens, pos, [slot] * c, self.device, LOGITS_LAST if want_token else LOGITS_NONE, G,
                                prefill=True)
+        self._mm_rows(b, slot, start_pos, c, mm)
         logits = self.model.forward(b, self.kv)
         if not want_token:
             return -1

@@ -41,6 +41,8 @@ class Request:
     think_end_id: int = -1        # id of the token that closes the block
     think_close: list[int] = field(default_factory=list)
     thinking_budget: int = 0      # 0 = unlimited
+    mm: object = None             # runtime.multimodal.MmPrompt: rotary positions + image embedding rows of ``prompt``
+    cache_key: list | None = None # prompt as the prefix cache sees it (image tokens replaced by content-derived ids)
     steer: object = None          # runtime.steering.SteerFile applied to this request's slot
     steer_scale: float = 1.0
     steer_scope: int | None = None
@@ -278,9 +280,11 @@ class Generator:
                 steer.clear_slot(s.idx)
         if len(req.prompt) == 0:
             req.prompt = [0]
+        if getattr(self.engine, "mrope", False):
+            self.engine.set_rope_delta(s.idx, req.mm.delta if req.mm is not None else 0)
         if self.cache is not None and req.cache_prefix:
             t0 = time.time()
-            chain = self.cache.find(req.prompt)
+            chain = self.cache.find(req.cache_key if req.cache_key is not None else req.prompt)
             for node in chain:
                 snap = self.cache.load(node)
                 if snap is None:
@@ -323,7 +327,7 @@ class Generator:
             if self.mtp is not None:
                 tok = self.mtp.prefill_rows(s.idx, prompt, s.cursor, end, last)
             else:
-                tok = self.engine.prefill_rows(s.idx, prompt[s.cursor:end], s.cursor, last)
+                tok = self.engine.prefill_rows(s.idx, prompt[s.cursor:end], s.cursor, last, **({"mm": s.req.mm} if s.req.mm is not None else {}))
             done_rows += end - s.cursor
             s.cursor = s.pos = end
             if self.cache is not None and s.req.cache_prefix and (end in self._snapshot_points(s)):
@@ -350,7 +354,7 @@ class Generator:
 
     def _store_prefix(self, s: SlotState, upto: int, pinned: bool = False):
         t0 = time.time()
-        toks = (s.req.prompt + s.out)[:upto]
+        toks = ((s.req.cache_key if s.req.cache_key is not None else s.req.prompt) + s.out)[:upto]
         self.cache.insert(toks, upto, lambda a, b: self.engine.kv.save_rows(s.idx, a, b), pinned=pinned)
         s.t_store_ms += (time.time() - t0) * 1e3
 

@@ -160,7 +160,8 @@ class VoltaServer:
         conn = req.conn
         try:
             cr = self._parse(req, proto)
-            if cr.n_images:
+            mm_front = getattr(self.gen, "mm_frontend", None)
+            if cr.n_images and mm_front is None:
                 raise ProtocolError("this deployment has no vision tower loaded: image parts are not accepted")
             prompt_text = self.render_prompt(cr)
         except ProtocolError as ex:
@@ -168,6 +169,15 @@ class VoltaServer:
         except Exception as ex:
             return self.http.respond(conn, 400, error_body(proto, f"chat template failed: {ex}"))
         ids = self.tok.encode(prompt_text)
+        mm = cache_key = None
+        if cr.images:
+            # every image part left one placeholder token: it becomes the image's tokens, whose rows come from the tower
+            from ..runtime.multimodal import MmPrompt
+            try:
+                ids, layout, feats = mm_front.prepare(ids, cr.images)
+            except Exception as ex:
+                return self.http.respond(conn, 400, error_body(proto, f"image input failed: {ex}"))
+            mm, cache_key = MmPrompt.build(layout, feats), layout.cache_tokens(ids)
         max_new = cr.max_tokens or self.default_max_tokens
         if len(ids) + 1 > self.max_context:     # strict-context error instead of silent truncation
             return self.http.respond(conn, 400, error_body(
@@ -211,7 +221,7 @@ class VoltaServer:
                 self.http.respond(conn, 200, json.dumps(body, ensure_ascii=False))
 
         sys_end = []
-        r = Request(prompt=ids, max_tokens=max_new, params=cr.params, stop=cr.stop, priority=cr.priority,
+        r = Request(prompt=ids, mm=mm, cache_key=cache_key, max_tokens=max_new, params=cr.params, stop=cr.stop, priority=cr.priority,
                     on_text=on_text, on_finish=on_finish, checkpoints=sys_end)
         rid = self.gen.submit(r)
         with self._lock:

@@ -37,10 +37,33 @@ class ChatRequest:
     include_usage: bool = True
     priority: int = 0
     n_images: int = 0
+    images: list = field(default_factory=list)      # raw bytes of every image part, in prompt order
 
 
-def _text_of(content) -> str:
-    """Flatten OpenAI / Anthropic content parts to text (image parts are counted by the caller)."""
+# what an image part becomes in the rendered text: the tokenizer turns the middle piece into ONE placeholder token, which
+# the multimodal front end expands to the image's token count
+IMAGE_MARK = "<|vision_start|><|image_pad|><|vision_end|>"
+
+
+def _image_bytes(part: dict) -> bytes:
+    """Bytes of an OpenAI ``image_url`` / ``input_image`` part or an Anthropic ``image`` part (base64 only: the server
+    fetches nothing)."""
+    import base64
+    if part.get("type") == "image":
+        src = part.get("source", {})
+        if src.get("type") != "base64":
+            raise ProtocolError("image sources must be base64")
+        return base64.b64decode(src.get("data", ""))
+    url = part.get("image_url", part.get("url", ""))
+    if isinstance(url, dict):
+        url = url.get("url", "")
+    if not url.startswith("data:") or ";base64," not in url:
+        raise ProtocolError("image_url must be a data: URL with base64 content")
+    return base64.b64decode(url.split(";base64,", 1)[1])
+
+
+def _text_of(content, images: list | None = None) -> str:
+    """Flatten OpenAI / Anthropic content parts to text; image parts leave ``IMAGE_MARK`` and their bytes in ``images``."""
     if content is None:
         return ""
     if isinstance(content, str):
@@ -51,6 +74,9 @@ def _text_of(content) -> str:
             out.append(part)
         elif part.get("type") in ("text", "input_text", "output_text"):
             out.append(part.get("text", ""))
+        elif part.get("type") in ("image_url", "input_image", "image") and images is not None:
+            images.append(_image_bytes(part))
+            out.append(IMAGE_MARK)
     return "".join(out)
 
 
@@ -79,7 +105,7 @@ def parse_openai(body: dict, defaults: dict) -> ChatRequest:
     msgs = body.get("messages")
     if not isinstance(msgs, list) or not msgs:
         raise ProtocolError("'messages' must be a non-empty array")
-    out, n_img = [], 0
+    out, n_img, images = [], 0, []
     for m in msgs:
         role = m.get("role")
         if role not in ("system", "developer", "user", "assistant", "tool"):
@@ -89,7 +115,7 @@ def parse_openai(body: dict, defaults: dict) -> ChatRequest:
         content = m.get("content")
         if isinstance(content, list):
             n_img += sum(1 for p in content if isinstance(p, dict) and p.get("type") in ("image_url", "input_image"))
-        e = {"role": role, "content": _text_of(content)}
+        e = {"role": role, "content": _text_of(content, images)}
         if role == "assistant" and m.get("tool_calls"):
             calls = []
             for tc in m["tool_calls"]:
@@ -121,7 +147,7 @@ def parse_openai(body: dict, defaults: dict) -> ChatRequest:
     so = body.get("stream_options") or {}
     return ChatRequest("openai", out, tools, bool(body.get("stream")), int(mt), _sampling(body, defaults), list(stop),
                        think, int(body.get("thinking_budget", 0) or 0), body.get("model", ""),
-                       bool(so.get("include_usage", True)), int(body.get("priority", 0) or 0), n_img)
+                       bool(so.get("include_usage", True)), int(body.get("priority", 0) or 0), n_img, images)
 
 
 def parse_anthropic(body: dict, defaults: dict) -> ChatRequest:
@@ -130,7 +156,7 @@ def parse_anthropic(body: dict, defaults: dict) -> ChatRequest:
         raise ProtocolError("'messages' must be a non-empty array")
     if "max_tokens" not in body:
         raise ProtocolError("'max_tokens' is required")
-    out, n_img = [], 0
+    out, n_img, images = [], 0, []
     sysm = body.get("system")
     if sysm:
         out.append({"role": "system", "content": _text_of(sysm)})
@@ -149,6 +175,8 @@ def parse_anthropic(body: dict, defaults: dict) -> ChatRequest:
                 text.append(part.get("text", ""))
             elif t == "image":
                 n_img += 1
+                images.append(_image_bytes(part))
+                text.append(IMAGE_MARK)
             elif t == "thinking":
                 reasoning.append(part.get("thinking", ""))
             elif t == "tool_use":
@@ -178,7 +206,7 @@ def parse_anthropic(body: dict, defaults: dict) -> ChatRequest:
         think = False
     return ChatRequest("anthropic", out, tools, bool(body.get("stream")), int(body["max_tokens"]),
                        _sampling(body, defaults), list(body.get("stop_sequences") or []), think,
-                       int(th.get("budget_tokens", 0) or 0), body.get("model", ""), True, 0, n_img)
+                       int(th.get("budget_tokens", 0) or 0), body.get("model", ""), True, 0, n_img, images)
 
 
 # ------------------------------------------------------------------------------------------------ responders
