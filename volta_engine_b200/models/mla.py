@@ -147,7 +147,7 @@ class MLAModel(MoEModel):
         krope = a[:, ql + LAT: ql + LAT + ROPE]
         q = L.q_b.forward(q_lat)                                   # [n, heads * 192]
         sel = None
-        if L.dsa is not None:
+        if getattr(L, "dsa", None) is not None:
             from ..ops import dsa as D
             st = self._dsa_state(li, kv)
             wts = D.update(st, L.dsa, x, b.slot, b.pos)
