@@ -129,3 +129,78 @@ def test_latent_attention_model_decodes_over_the_indexer_list():
     assert float(torch.dot(a, b) / (a.norm() * b.norm())) > 0.99
     out, _ = Engine(mg, PagedKVCache(cfg.n_layers, 1, 576, 48, 1, 4096, DEV, v_head_dim=8), prefill_chunk=1024).generate(p, 5)
     assert len(out) == 5
+
+
+# ------------------------------------------------------------------------------------------------ block-sparse indexer
+def _qsa_weights(H, dev="cpu", seed=2):
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    return D.QSAWeights(proj=LinearBF16((torch.randn(5 * D.DIM, H, generator=g) * 0.2).to(bf).to(dev)),
+                        q_norm=(0.1 * torch.randn(D.DIM, generator=g)).to(bf).to(dev),
+                        k_norm=(0.1 * torch.randn(D.DIM, generator=g)).to(bf).to(dev), rot=64, theta=1e4)
+
+
+def test_hybrid_model_with_block_sparse_indexer_equals_dense_on_short_context():
+    from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+    cfg = HybridConfig.tiny_hybrid(vocab=256, qsa=True)
+    m = HybridModel(cfg, "cpu").init_random(seed=1)
+    plain = to_device(m, "cpu")
+    for L in plain.layers:
+        L.qsa = None
+    p = torch.randint(1, 250, (50,), generator=torch.Generator().manual_seed(2)).tolist()
+    outs = []
+    for mod in (m, plain):
+        kv = PagedKVCache(mod.kv_layers, mod.nkv, cfg.head_dim, 8, 1, 256, "cpu")
+        out, _ = Engine(mod, kv, use_graphs=False, prefill_chunk=32).generate(p, 6)
+        outs.append(out)
+    assert outs[0] == outs[1] and m.qsa_states
+
+
+@pytest.mark.gpu
+def test_block_sparse_indexer_kernels_and_model():
+    H, slots, max_seq = 256, 2, 8192
+    Wc, Wg = _qsa_weights(H), _qsa_weights(H, DEV)
+    sc_, sg_ = D.QSAState(slots, max_seq, "cpu"), D.QSAState(slots, max_seq, DEV)
+    g = torch.Generator().manual_seed(5)
+    n0 = 2500
+    x = torch.randn(n0, H, generator=g).to(torch.bfloat16)
+    slot = torch.ones(n0, dtype=torch.int32)
+    pos = torch.arange(n0, dtype=torch.int32)
+    qc = D.qsa_update(sc_, Wc, x, slot, pos)
+    qg = D.qsa_update(sg_, Wg, x.to(DEV), slot.to(DEV), pos.to(DEV))
+    assert torch.allclose(qg.cpu().float(), qc.float(), atol=0.06, rtol=0.03)
+    assert torch.allclose(sg_.pools.cpu().float(), sc_.pools.float(), atol=0.06, rtol=0.03)
+    assert torch.equal(sg_.ring.cpu(), sc_.ring)
+    sg_.pools.copy_(sc_.pools)
+    qs, qp = torch.ones(1, dtype=torch.int32), torch.tensor([n0 - 1], dtype=torch.int32)
+    want = D.qsa_score_reference(qc[-1:], sc_, qs, qp)[0]
+    got = D.score(sg_, qc[-1:].to(DEV), None, qs.to(DEV), qp.to(DEV)).cpu()[0, :len(want)]
+    assert torch.allclose(got, want, atol=2e-3, rtol=2e-3)
+    idx, nk = D.qsa_select(sg_, qc[-1:].to(DEV), qs.to(DEV), qp.to(DEV))
+    assert int(nk[0]) == D.TOPK + n0 % 4 and idx[0, :int(nk[0])].tolist() == D.select_reference(got, n0)
+    # gather with several kv heads
+    pool = torch.randn(50, 2, 64, 64, generator=g).to(torch.bfloat16)
+    table = (torch.randperm(49, generator=g)[:40].to(torch.int32) + 1).reshape(1, 40).repeat(2, 1)
+    scr_c = torch.zeros(D.PAGES_PER_ROW, 2, 64, 64, dtype=torch.bfloat16)
+    scr_g = scr_c.to(DEV)
+    D.gather_rows(pool, table, qs, idx.cpu(), nk.cpu(), scr_c)
+    D.gather_rows(pool.to(DEV), table.to(DEV), qs.to(DEV), idx, nk, scr_g)
+    assert torch.equal(scr_g.cpu(), scr_c)
+    # a hybrid model decoding a row past 2048 tokens: GPU and CPU agree on the logits
+    from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+    cfg = HybridConfig.tiny_hybrid(vocab=256, qsa=True)
+    mg = HybridModel(cfg, DEV).init_random(seed=1)
+    mc = to_device(mg, "cpu")
+    n = 2200
+    p = torch.randint(1, 250, (n,), generator=torch.Generator().manual_seed(4)).tolist()
+    kvg = PagedKVCache(mg.kv_layers, mg.nkv, cfg.head_dim, 48, 1, 4096, DEV)
+    kvc = PagedKVCache(mc.kv_layers, mc.nkv, cfg.head_dim, 48, 1, 4096, "cpu")
+    eg, ec = Engine(mg, kvg, prefill_chunk=1024), Engine(mc, kvc, use_graphs=False, prefill_chunk=1024)
+    tg, tc = eg.prefill(0, p), ec.prefill(0, p)
+    G = mg.nq // mg.nkv
+    kvg.reserve(0, n + 8)
+    kvc.reserve(0, n + 8)
+    lg = mg.forward(BatchRows.make([p[5]], [n], [0], DEV, "all", G, nsplit=2), kvg)
+    lc = mc.forward(BatchRows.make([p[5]], [n], [0], "cpu", "all", G), kvc)
+    a, b = lg.float().cpu().flatten(), lc.float().flatten()
+    assert float(torch.dot(a, b) / (a.norm() * b.norm())) > 0.99

@@ -76,35 +76,43 @@ VE_DEVINL void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (ceil(max_pools / 64), rows), block 256: each warp scores 8 pools. q_idx [rows, 32, 128] bf16, w [rows, 32] fp32.
+// grid (ceil(max_pools / 64), rows), block 256: each warp scores 8 pools. q_idx [rows, HEADS, 128] bf16, w [rows, HEADS]
+// fp32 head weights (nullptr: every head counts 1, the block-sparse indexer's form). HEADS = 32 or 4 (rows of the 16-row
+// tile beyond HEADS are zero).
+template <int HEADS>
 __global__ void __launch_bounds__(256) dsa_score_kernel(const __nv_bfloat16* __restrict__ q_idx, const float* __restrict__ w,
                                                         const __nv_bfloat16* __restrict__ pool_plane, float* __restrict__ scores,
                                                         long score_stride, const int* __restrict__ slot,
                                                         const int* __restrict__ pos, long pool_slot_stride) {
   constexpr int LDQ = kDsaDim + 8;
-  __shared__ __align__(16) __nv_bfloat16 sq[kDsaHeads * LDQ];
-  __shared__ float sw[kDsaHeads];
+  constexpr int MT = (HEADS + 15) / 16, HP = MT * 16;
+  __shared__ __align__(16) __nv_bfloat16 sq[HP * LDQ];
+  __shared__ float sw[HP];
   const int r = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sl = slot[r];
   if (sl < 0) return;
   const int bound = (pos[r] + 1) / kDsaPool;
   if (blockIdx.x * 64 >= bound) return;
-  for (int i = tid; i < kDsaHeads * kDsaDim; i += 256)
-    sq[(i / kDsaDim) * LDQ + (i % kDsaDim)] = q_idx[(long)r * kDsaHeads * kDsaDim + i];
-  if (tid < kDsaHeads) sw[tid] = w[(long)r * kDsaHeads + tid];
+  for (int i = tid; i < HP * kDsaDim; i += 256) {
+    const int h = i / kDsaDim;
+    sq[h * LDQ + (i % kDsaDim)] = h < HEADS ? q_idx[(long)r * HEADS * kDsaDim + i] : __float2bfloat16_rn(0.f);
+  }
+  if (tid < HP) sw[tid] = tid < HEADS ? (w ? w[(long)r * HEADS + tid] : 1.f) : 0.f;
   __syncthreads();
   const int p0 = (blockIdx.x * 8 + warp) * 8;
   if (p0 >= bound) return;
   const int g = lane >> 2, t = lane & 3;
   const int pn = min(p0 + g, bound - 1);
   const __nv_bfloat16* key = pool_plane + (long)sl * pool_slot_stride + (long)pn * kDsaDim;
-  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  float acc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
 #pragma unroll
   for (int kk = 0; kk < kDsaDim / 16; ++kk) {
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(key + kk * 16 + 2 * t);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(key + kk * 16 + 2 * t + 8);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
+    for (int mt = 0; mt < MT; ++mt) {
       uint32_t a[4];
       const __nv_bfloat16* q0 = sq + (mt * 16 + g) * LDQ + kk * 16 + 2 * t;
       a[0] = *reinterpret_cast<const uint32_t*>(q0);
@@ -117,7 +125,7 @@ __global__ void __launch_bounds__(256) dsa_score_kernel(const __nv_bfloat16* __r
   // relu, head weight, sum over the 32 heads (rows of the two tiles), per pool column
   float c0 = 0.f, c1 = 0.f;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt) {
+  for (int mt = 0; mt < MT; ++mt) {
     const float wa = sw[mt * 16 + g], wb = sw[mt * 16 + g + 8];
     c0 += fmaxf(acc[mt][0], 0.f) * wa + fmaxf(acc[mt][2], 0.f) * wb;
     c1 += fmaxf(acc[mt][1], 0.f) * wa + fmaxf(acc[mt][3], 0.f) * wb;
@@ -128,7 +136,7 @@ __global__ void __launch_bounds__(256) dsa_score_kernel(const __nv_bfloat16* __r
     c1 += __shfl_xor_sync(0xffffffffu, c1, off);
   }
   if (g == 0) {
-    const float norm = rsqrtf((float)(kDsaDim * kDsaHeads));
+    const float norm = w ? rsqrtf((float)(kDsaDim * HEADS)) : rsqrtf((float)kDsaDim);
     float* out = scores + (long)r * score_stride + p0 + 2 * t;
     if (p0 + 2 * t < bound) out[0] = c0 * norm;
     if (p0 + 2 * t + 1 < bound) out[1] = c1 * norm;
@@ -233,20 +241,98 @@ __global__ void __launch_bounds__(1024) dsa_select_kernel(const float* __restric
   if (tid == 0) nkeys[r] = kDsaTopk + tail;
 }
 
-// Copy the listed tokens' cache rows into scratch pages: scratch [rows * pages_per_row, 1, 64, row_elems], entry i of row r
-// lands in page r * pages_per_row + i / 64, token i % 64. grid (kDsaKpad / 4, rows), block 256 (64 threads per entry).
+// Copy the listed tokens' cache rows into scratch pages: pool [pages, nkv, 64, row_elems], scratch [rows * pages_per_row,
+// nkv, 64, row_elems]; entry i of row r lands in page r * pages_per_row + i / 64, token i % 64.
+// grid (kDsaKpad / 4, rows, nkv), block 256 (64 threads per entry).
 __global__ void __launch_bounds__(256) dsa_gather_kernel(const __nv_bfloat16* __restrict__ pool, const int* __restrict__ page_table,
                                                          int max_pages, const int* __restrict__ slot, const int* __restrict__ idx,
                                                          const int* __restrict__ nkeys, __nv_bfloat16* __restrict__ scratch,
-                                                         int pages_per_row, int row_elems) {
-  const int r = blockIdx.y, i = blockIdx.x * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63;
+                                                         int pages_per_row, int row_elems, int nkv) {
+  const int r = blockIdx.y, i = blockIdx.x * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63, kvh = blockIdx.z;
   const int sl = slot[r];
   if (sl < 0 || i >= nkeys[r]) return;
   const int tok = idx[(long)r * kDsaKpad + i];
   const int page = page_table[(long)sl * max_pages + tok / kPageTok];
-  const uint4* src = reinterpret_cast<const uint4*>(pool + ((long)page * kPageTok + tok % kPageTok) * row_elems);
-  uint4* dst = reinterpret_cast<uint4*>(scratch + (((long)r * pages_per_row + i / kPageTok) * kPageTok + i % kPageTok) * row_elems);
+  const uint4* src = reinterpret_cast<const uint4*>(pool + (((long)page * nkv + kvh) * kPageTok + tok % kPageTok) * row_elems);
+  uint4* dst = reinterpret_cast<uint4*>(
+      scratch + ((((long)r * pages_per_row + i / kPageTok) * nkv + kvh) * kPageTok + i % kPageTok) * row_elems);
   for (int c = l; c < row_elems / 8; c += 64) dst[c] = src[c];
+}
+
+// ------------------------------------------------------------------------------------------------ block-sparse indexer
+// Variant with 4 indexer heads and unweighted pools (reference: inc/engine/modules/qsa.h:8-33):
+//   per token : [q (4 x 128) | k (128)] = W x; q = rmsnorm(q) * (1 + w_q), rotated on its first rot dims at the row's position;
+//               the raw k enters a ring of the last 1024 positions
+//   per pool  : key = rope_at_pool_start(rmsnorm(mean of the pool's 4 raw keys) * (1 + w_k))
+//   per query : score[p] = 128^-1/2 * sum_h relu(q[h] . key[p])       (dsa_score_kernel<4> without head weights)
+constexpr int kQsaHeads = 4, kQsaProj = (kQsaHeads + 1) * kDsaDim, kQsaRing = 1024;
+
+VE_DEVINL void rope_pair(float& a, float& b, int i, int rot, float theta, int pos) {
+  const float inv = exp2f(-log2f(theta) * (2.f * (float)i / (float)rot));
+  float sn, cs;
+  sincosf((float)pos * inv, &sn, &cs);
+  const float x = a * cs - b * sn, y = b * cs + a * sn;
+  a = x;
+  b = y;
+}
+
+// grid (rows, 5): blockIdx.y < 4 a query head, 4 the key. block 128 (one thread per dim; NeoX pairs (i, i + rot/2)).
+__global__ void __launch_bounds__(128) qsa_prep_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __restrict__ q_norm_w,
+                                                       __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ ring,
+                                                       const int* __restrict__ slot, const int* __restrict__ pos,
+                                                       long ring_slot_stride, int rot, float theta, float eps) {
+  __shared__ float red[33];
+  __shared__ float v[kDsaDim];
+  const int r = blockIdx.x, part = blockIdx.y, d = threadIdx.x;
+  const int sl = slot[r], p = pos[r];
+  if (sl < 0) return;
+  const __nv_bfloat16 raw = qk[(long)r * kQsaProj + part * kDsaDim + d];
+  if (part == kQsaHeads) {
+    ring[(long)sl * ring_slot_stride + (long)(p & (kQsaRing - 1)) * kDsaDim + d] = raw;
+    return;
+  }
+  const float x = __bfloat162float(raw);
+  const float ss = block_sum(x * x, red);
+  v[d] = x * rsqrtf(ss / (float)kDsaDim + eps) * (1.f + __bfloat162float(q_norm_w[d]));
+  __syncthreads();
+  const int half = rot / 2;
+  if (d < half) {
+    float a = v[d], b = v[d + half];
+    rope_pair(a, b, d, rot, theta, p);
+    v[d] = a;
+    v[d + half] = b;
+  }
+  __syncthreads();
+  q_out[((long)r * kQsaHeads + part) * kDsaDim + d] = __float2bfloat16_rn(v[d]);
+}
+
+// grid rows, block 128: the row at position p with p % 4 == 3 builds pool p / 4
+__global__ void __launch_bounds__(128) qsa_pool_kernel(const __nv_bfloat16* __restrict__ ring, __nv_bfloat16* __restrict__ pool_plane,
+                                                       const __nv_bfloat16* __restrict__ k_norm_w, const int* __restrict__ slot,
+                                                       const int* __restrict__ pos, long ring_slot_stride, long pool_slot_stride,
+                                                       int rot, float theta, float eps) {
+  __shared__ float red[33];
+  __shared__ float v[kDsaDim];
+  const int r = blockIdx.x, d = threadIdx.x;
+  const int sl = slot[r], p = pos[r];
+  if (sl < 0 || (p & (kDsaPool - 1)) != kDsaPool - 1) return;
+  float m = 0.f;
+#pragma unroll
+  for (int j = 0; j < kDsaPool; ++j)
+    m += __bfloat162float(ring[(long)sl * ring_slot_stride + (long)((p - (kDsaPool - 1) + j) & (kQsaRing - 1)) * kDsaDim + d]);
+  m *= 1.f / (float)kDsaPool;
+  const float ss = block_sum(m * m, red);
+  v[d] = m * rsqrtf(ss / (float)kDsaDim + eps) * (1.f + __bfloat162float(k_norm_w[d]));
+  __syncthreads();
+  const int half = rot / 2;
+  if (d < half) {
+    float a = v[d], b = v[d + half];
+    rope_pair(a, b, d, rot, theta, p - (kDsaPool - 1));
+    v[d] = a;
+    v[d + half] = b;
+  }
+  __syncthreads();
+  pool_plane[(long)sl * pool_slot_stride + (long)(p / kDsaPool) * kDsaDim + d] = __float2bfloat16_rn(v[d]);
 }
 
 }  // namespace ve
@@ -272,12 +358,40 @@ int ve_dsa_pool_update(const void* plane, void* pool_plane, const void* ape, con
   VE_CHECK_LAUNCH();
 }
 
+// heads = 32 with head weights w (pooled-key indexer) or 4 with w == nullptr (block-sparse indexer)
 int ve_dsa_score(const void* q_idx, const void* w, const void* pool_plane, void* scores, long score_stride, const void* slot,
-                 const void* pos, long pool_slot_stride, int rows, int max_pools, cudaStream_t st) {
+                 const void* pos, long pool_slot_stride, int rows, int max_pools, int heads, cudaStream_t st) {
   if (rows <= 0 || max_pools <= 0) return 0;
-  dsa_score_kernel<<<dim3((max_pools + 63) / 64, rows), 256, 0, st>>>(
-      (const __nv_bfloat16*)q_idx, (const float*)w, (const __nv_bfloat16*)pool_plane, (float*)scores, score_stride,
-      (const int*)slot, (const int*)pos, pool_slot_stride);
+  const dim3 grid((max_pools + 63) / 64, rows);
+  if (heads == kDsaHeads)
+    dsa_score_kernel<kDsaHeads><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q_idx, (const float*)w,
+                                                      (const __nv_bfloat16*)pool_plane, (float*)scores, score_stride,
+                                                      (const int*)slot, (const int*)pos, pool_slot_stride);
+  else if (heads == kQsaHeads)
+    dsa_score_kernel<kQsaHeads><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q_idx, (const float*)w,
+                                                      (const __nv_bfloat16*)pool_plane, (float*)scores, score_stride,
+                                                      (const int*)slot, (const int*)pos, pool_slot_stride);
+  else
+    return cudaErrorInvalidValue;
+  VE_CHECK_LAUNCH();
+}
+
+int ve_qsa_prep(const void* qk, const void* q_norm_w, void* q_out, void* ring, const void* slot, const void* pos,
+                long ring_slot_stride, int rot, float theta, float eps, int rows, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (rot % 2 || rot > kDsaDim) return cudaErrorInvalidValue;
+  qsa_prep_kernel<<<dim3(rows, kQsaHeads + 1), 128, 0, st>>>((const __nv_bfloat16*)qk, (const __nv_bfloat16*)q_norm_w,
+                                                             (__nv_bfloat16*)q_out, (__nv_bfloat16*)ring, (const int*)slot,
+                                                             (const int*)pos, ring_slot_stride, rot, theta, eps);
+  VE_CHECK_LAUNCH();
+}
+
+int ve_qsa_pool_update(const void* ring, void* pool_plane, const void* k_norm_w, const void* slot, const void* pos,
+                       long ring_slot_stride, long pool_slot_stride, int rot, float theta, float eps, int rows,
+                       cudaStream_t st) {
+  if (rows <= 0) return 0;
+  qsa_pool_kernel<<<rows, 128, 0, st>>>((const __nv_bfloat16*)ring, (__nv_bfloat16*)pool_plane, (const __nv_bfloat16*)k_norm_w,
+                                        (const int*)slot, (const int*)pos, ring_slot_stride, pool_slot_stride, rot, theta, eps);
   VE_CHECK_LAUNCH();
 }
 
@@ -290,12 +404,13 @@ int ve_dsa_select(const void* scores, long score_stride, void* idx, void* nkeys,
 }
 
 int ve_dsa_gather(const void* pool, const void* page_table, int max_pages, const void* slot, const void* idx,
-                  const void* nkeys, void* scratch, int pages_per_row, int row_elems, int rows, cudaStream_t st) {
+                  const void* nkeys, void* scratch, int pages_per_row, int row_elems, int nkv, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
-  if (row_elems % 8 || pages_per_row * kPageTok < kDsaKpad) return cudaErrorInvalidValue;
-  dsa_gather_kernel<<<dim3(kDsaKpad / 4, rows), 256, 0, st>>>((const __nv_bfloat16*)pool, (const int*)page_table, max_pages,
-                                                              (const int*)slot, (const int*)idx, (const int*)nkeys,
-                                                              (__nv_bfloat16*)scratch, pages_per_row, row_elems);
+  if (row_elems % 8 || pages_per_row * kPageTok < kDsaKpad || nkv < 1) return cudaErrorInvalidValue;
+  dsa_gather_kernel<<<dim3(kDsaKpad / 4, rows, nkv), 256, 0, st>>>((const __nv_bfloat16*)pool, (const int*)page_table,
+                                                                   max_pages, (const int*)slot, (const int*)idx,
+                                                                   (const int*)nkeys, (__nv_bfloat16*)scratch, pages_per_row,
+                                                                   row_elems, nkv);
   VE_CHECK_LAUNCH();
 }
 

@@ -28,6 +28,7 @@ class HybridConfig(MoEConfig):
     gdn_dv: int = 128
     gdn_conv: int = 4
     attn_gate: bool = True
+    qsa: bool = False              # block-sparse attention: a 4-head indexer over pooled keys picks a decode row's 2048 tokens
     model_type: str = "hybrid_gdn"
 
     @classmethod
@@ -57,7 +58,7 @@ class HybridConfig(MoEConfig):
 
 
 class HybridLayer(MoELayer):
-    __slots__ = ("gdn", "gate_proj", "kv_index")
+    __slots__ = ("gdn", "gate_proj", "kv_index", "qsa")
 
 
 class HybridModel(MoEModel):
@@ -92,13 +93,19 @@ class HybridModel(MoEModel):
         cfg, d, dev = self.cfg, self.dims, self.device
         li = self._li
         self._li += 1
-        L.gdn = L.gate_proj = None
+        L.gdn = L.gate_proj = L.qsa = None
         L.kv_index = -1
         if cfg.is_full(li):
             super()._init_attention(L, rnd, search)
             L.kv_index = sum(1 for j in range(li) if cfg.is_full(j))
             if cfg.attn_gate:
                 L.gate_proj = self._make_linear(rnd(cfg.n_q * cfg.head_dim, cfg.hidden), search)
+            if cfg.qsa:
+                from ..ops import dsa as D
+                from ..ops.linear import LinearBF16
+                z = torch.zeros(D.DIM, device=dev, dtype=torch.bfloat16)
+                L.qsa = D.QSAWeights(proj=LinearBF16((rnd(D.QSA_HEADS * D.DIM + D.DIM, cfg.hidden) * 8).to(torch.bfloat16)),
+                                     q_norm=z.clone(), k_norm=z.clone(), rot=min(64, D.DIM), theta=cfg.rope_theta, eps=cfg.rms_eps)
             return
         H = cfg.hidden
         w_in = torch.zeros(d.proj_out, H, device=dev)
@@ -147,10 +154,46 @@ class HybridModel(MoEModel):
         K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
                      cfg.rope_theta, cfg.rope_interleaved)
         gate = L.gate_proj.forward(x) if L.gate_proj is not None else None
-        att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.scale,
+        a_pos, a_slot, a_table, a_k, a_v, nsplit = b.pos, b.slot, kv.page_table, kpool, vpool, b.nsplit
+        if getattr(L, "qsa", None) is not None:
+            from ..ops import dsa as D
+            st = self._qsa_state(li, kv)
+            qi = D.qsa_update(st, L.qsa, x, b.slot, b.pos)
+            if b.tiles is None and b.key_end is None:
+                # decode rows attend to the indexer's list: the listed keys and values form a short virtual sequence per
+                # row in scratch pages (prefill chunks attend densely)
+                idx, nkeys = D.qsa_select(st, qi, b.slot, b.pos)
+                a_k, a_v, a_table, ar = self._qsa_scratch(b.n, kpool)
+                D.gather_rows(kpool, kv.page_table, b.slot, idx, nkeys, a_k)
+                D.gather_rows(vpool, kv.page_table, b.slot, idx, nkeys, a_v)
+                a_pos = nkeys - 1
+                a_slot = torch.where(b.slot < 0, b.slot, ar[:b.n])
+                nsplit = min(nsplit, 8)
+        att = K.attention(qkv, a_pos, a_slot, a_table, a_k, a_v, self.nq, self.nkv, self.hd, self.scale,
                           window=cfg.sliding_window, key_end=b.key_end, gate=gate, tiles=b.tiles,
-                          nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
+                          nsplit=1 if b.tiles is not None else nsplit, ws=self.attn_ws)
         return L.o_proj.forward(att, out=pbuf)
+
+    def _qsa_state(self, li, kv):
+        if not hasattr(self, "qsa_states"):
+            self.qsa_states, self.qsa_scr = {}, None
+        st = self.qsa_states.get(li)
+        if st is None:
+            from ..ops import dsa as D
+            st = self.qsa_states[li] = D.QSAState(kv.max_slots, kv.max_pages * 64, self.device)
+        return st
+
+    def _qsa_scratch(self, n, kpool):
+        from ..ops import dsa as D
+        if self.qsa_scr is None or self.qsa_scr[3].numel() < n:
+            cap = max(16, n)
+            shape = (cap * D.PAGES_PER_ROW,) + tuple(kpool.shape[1:])
+            self.qsa_scr = (torch.zeros(shape, dtype=kpool.dtype, device=kpool.device),
+                            torch.zeros(shape, dtype=kpool.dtype, device=kpool.device),
+                            torch.arange(cap * D.PAGES_PER_ROW, dtype=torch.int32, device=kpool.device)
+                            .reshape(cap, D.PAGES_PER_ROW).contiguous(),
+                            torch.arange(cap, dtype=torch.int32, device=kpool.device))
+        return self.qsa_scr
 
     # recurrent state travels with sequence snapshots
     def snapshot_state(self, slot: int) -> list:
