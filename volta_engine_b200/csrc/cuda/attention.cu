@@ -42,6 +42,8 @@ struct AttnParams {
   int window;
   int* status;
   int nst;          // pipeline stages of the page loads (2 or 3)
+  const uint8_t* kscale;   // scaled cache formats: scale pools [pages, kv_heads, 64, scale bytes]
+  const uint8_t* vscale;
   int* tickets;     // optional [tiles * nkv], zero between launches: the CTA that finishes a (tile, kv head) last merges
                     // the split partials itself (key-split kernel only), so no separate merge launch is needed
 };
@@ -67,18 +69,46 @@ VE_DEVINL uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
+VE_DEVINL uint32_t a_cvt_e2m1x2(uint32_t byte) {   // two E2M1 nibbles -> f16x2 (low nibble = first element)
+  uint32_t r;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "r"(byte));
+  return r;
+}
+VE_DEVINL float a_e4m3(uint32_t b) {
+  uint32_t r;
+  asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(r) : "r"(b & 0xffu));
+  return __half2float(__ushort_as_half((unsigned short)(r & 0xffffu)));
+}
+// 16 consecutive elements of one key, as bf16, to their place in the swizzled tile the tensor-core loads read
+// (j = index of the 16-element group inside the row)
+VE_DEVINL void put16(uint8_t* tile, int key, int j, const float* f) {
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = pack_bf16(f[2 * i], f[2 * i + 1]);
+  uint8_t* dst = tile + (j >> 2) * 8192 + key * 128;
+  const int ch0 = (j & 3) * 2;
+  *reinterpret_cast<uint4*>(dst + ((ch0 ^ (key & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<uint4*>(dst + (((ch0 + 1) ^ (key & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 // KS (key-split, decode / verify tiles of <= 16 packed rows): all NW warps work on the same 16 rows and each takes
 // its own 16-key slice of every 64-key page, so a page costs a quarter of the per-warp work; the warps' softmax
 // states are merged through shared memory at the end.
-// F8: the cache holds E5M2 bytes (half the traffic); pages land in a staging buffer and the CTA expands them to bf16
-// tiles in the layout the tensor-core loads expect, so the arithmetic is the same as for a bf16 cache.
-template <int HD, int NW, bool KS, bool F8>
+// FMT: cache element format. 0 bf16 (pages land swizzled, ready for the tensor-core loads). 1 E5M2 bytes, 2 k8v4 (int8 keys
+// and 4-bit Hadamard-rotated values with one fp16 scale per 64 elements), 3 nvfp4 (E2M1 with one E4M3 scale per 16):
+// pages and their scales land in a staging buffer and the CTA expands them to bf16 tiles in the same layout, so the
+// arithmetic is that of a bf16 cache whatever the storage (values of the rotated format are rotated back on the way).
+template <int HD, int NW, bool KS, int FMT>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
   grid_dep_launch();
   grid_dep_wait();
   constexpr int TILE_BYTES = kPageTok * HD * 2;
-  constexpr int T8 = kPageTok * HD;   // one E5M2 tile
+  constexpr bool F8 = FMT != 0;       // staged formats
+  constexpr int KB = FMT == 3 ? kPageTok * HD / 2 : kPageTok * HD;               // key bytes of one page
+  constexpr int VB = FMT == 1 ? kPageTok * HD : kPageTok * HD / 2;               // value bytes of one page
+  constexpr int SB = FMT == 2 ? kPageTok * (HD / 64) * 2 : (FMT == 3 ? kPageTok * (HD / 16) : 0);   // scale bytes (K, V alike)
+  constexpr int STG = KB + VB + 2 * SB;                                          // one staging buffer
   constexpr int NCH = HD / 64;   // 128-byte column chunks per row
   constexpr int KSTEPS = HD / 16;
   constexpr int NT_O = HD / 8;
@@ -137,10 +167,15 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
     const int page = p.page_table[(long)s * p.max_pages + kt];
     const int row = (page * p.nkv + kvh) * kPageTok;
     if (F8) {
-      uint8_t* k8 = smem + stage * 2 * T8;
-      mbar_expect_tx(&full[stage], 2 * T8);
+      uint8_t* k8 = smem + stage * STG;
+      mbar_expect_tx(&full[stage], STG);
       tma_load_2d(k8, &kmap, &full[stage], 0, row);
-      tma_load_2d(k8 + T8, &vmap, &full[stage], 0, row);
+      tma_load_2d(k8 + KB, &vmap, &full[stage], 0, row);
+      if (SB) {
+        const size_t so = (size_t)(page * p.nkv + kvh) * SB;
+        bulk_load(k8 + KB + VB, p.kscale + so, SB, &full[stage]);
+        bulk_load(k8 + KB + VB + SB, p.vscale + so, SB, &full[stage]);
+      }
       return;
     }
     uint8_t* kb = smem + stage * 2 * TILE_BYTES;
@@ -184,35 +219,102 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
     // the stage of the previous iteration is free now (every warp passed the barrier above): refill it
     if (tid == 0 && kt + nst - 1 < kt_end) issue(kt + nst - 1, (it + nst - 1) % nst);
     if (F8) {
-      // expand the page: 16 E5M2 bytes -> two 16-byte bf16 chunks at their swizzled place
-      const uint8_t* st8 = smem + stage * 2 * T8;
-      uint8_t* conv = smem + nst * 2 * T8;
-      constexpr int CPT = kPageTok * (HD / 16);
-      for (int idx = tid; idx < 2 * CPT; idx += NW * 32) {
-        const int tile = idx / CPT, rem = idx % CPT;
-        const int key = rem / (HD / 16), j = rem % (HD / 16);
-        const uint4 raw = *reinterpret_cast<const uint4*>(st8 + tile * T8 + key * HD + j * 16);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t o[8];
+      // expand the page into the two bf16 tiles
+      const uint8_t* st8 = smem + stage * STG;
+      uint8_t* conv = smem + nst * STG;
+      constexpr int G16 = HD / 16;                 // 16-element groups per key
+      constexpr int CPT = kPageTok * G16;
+      if (FMT == 1) {
+        for (int idx = tid; idx < 2 * CPT; idx += NW * 32) {
+          const int tile = idx / CPT, rem = idx % CPT;
+          const int key = rem / G16, j = rem % G16;
+          const uint4 raw = *reinterpret_cast<const uint4*>(st8 + tile * KB + key * HD + j * 16);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+          float f[16];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+          for (int q4 = 0; q4 < 4; ++q4) {
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            uint32_t h2;
-            const unsigned short pair = (unsigned short)(w[q4] >> (16 * hh));
-            asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(pair));
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-            o[q4 * 2 + hh] = pack_bf16(f.x, f.y);
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t h2;
+              const unsigned short pair = (unsigned short)(w[q4] >> (16 * hh));
+              asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(pair));
+              const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+              f[q4 * 4 + hh * 2] = v2.x;
+              f[q4 * 4 + hh * 2 + 1] = v2.y;
+            }
           }
+          put16(conv + tile * TILE_BYTES, key, j, f);
         }
-        uint8_t* dst = conv + tile * TILE_BYTES + (j >> 2) * 8192 + key * 128;
-        const int ch0 = (j & 3) * 2;
-        *reinterpret_cast<uint4*>(dst + ((ch0 ^ (key & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4*>(dst + (((ch0 + 1) ^ (key & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      } else if (FMT == 2) {
+        const uint8_t* ksc = st8 + KB + VB;
+        const uint8_t* vsc = ksc + SB;
+        // keys: int8 x fp16 scale per 64
+        for (int idx = tid; idx < CPT; idx += NW * 32) {
+          const int key = idx / G16, j = idx % G16;
+          const uint4 raw = *reinterpret_cast<const uint4*>(st8 + key * HD + j * 16);
+          const float sc = __half2float(*reinterpret_cast<const __half*>(ksc + (key * (HD / 64) + (j >> 2)) * 2));
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+          float f[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = sc * (float)(int8_t)((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
+          put16(conv, key, j, f);
+        }
+        // values: 4-bit codes x fp16 scale per 64, rotated back by the 64-point Walsh-Hadamard transform
+        for (int idx = tid; idx < kPageTok * (HD / 64); idx += NW * 32) {
+          const int key = idx / (HD / 64), blk = idx % (HD / 64);
+          const uint8_t* src = st8 + KB + key * (HD / 2) + blk * 32;
+          const float sc = __half2float(*reinterpret_cast<const __half*>(vsc + (key * (HD / 64) + blk) * 2));
+          float v[64];
+#pragma unroll
+          for (int q4 = 0; q4 < 2; ++q4) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + q4 * 16);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+              v[q4 * 32 + 2 * i] = sc * (float)((int)(byte & 15u) - 8);
+              v[q4 * 32 + 2 * i + 1] = sc * (float)((int)(byte >> 4) - 8);
+            }
+          }
+#pragma unroll
+          for (int h = 1; h < 64; h <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if ((i & h) == 0) {
+                const float a = v[i], b = v[i | h];
+                v[i] = a + b;
+                v[i | h] = a - b;
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] *= 0.125f;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) put16(conv + TILE_BYTES, key, blk * 4 + q4, v + q4 * 16);
+        }
+      } else {
+        // E2M1 codes x E4M3 scale per 16, keys and values alike
+        const uint8_t* sc0 = st8 + KB + VB;
+        for (int idx = tid; idx < 2 * CPT; idx += NW * 32) {
+          const int tile = idx / CPT, rem = idx % CPT;
+          const int key = rem / G16, j = rem % G16;
+          const uint2 raw = *reinterpret_cast<const uint2*>(st8 + tile * KB + key * (HD / 2) + j * 8);
+          const float sc = a_e4m3(sc0[tile * SB + key * G16 + j]);
+          const uint32_t w[2] = {raw.x, raw.y};
+          float f[16];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t h2 = a_cvt_e2m1x2((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
+            const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            f[2 * i] = v2.x * sc;
+            f[2 * i + 1] = v2.y * sc;
+          }
+          put16(conv + tile * TILE_BYTES, key, j, f);
+        }
       }
       __syncthreads();
     }
-    const uint32_t kb = F8 ? smem_base + nst * 2 * T8 : smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+    const uint32_t kb = F8 ? smem_base + nst * STG : smem_base + stage * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
 
     // S = Q K^T  (16 rows x 64 keys per warp)
     constexpr int NP = KS ? 1 : 4;           // 16-key slices this warp scores per page
@@ -433,20 +535,22 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
   out[(long)row * out_stride + (long)head * HD + d] = f2bf(v);
 }
 
-template <int HD, int NW, bool KS, bool F8>
+template <int HD, int NW, bool KS, int FMT>
 static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
                        cudaStream_t st) {
   constexpr int TILE = kPageTok * HD * 2;
-  const int smem = (F8 ? p.nst * TILE + 2 * TILE : p.nst * 2 * TILE) + 1024;
+  constexpr int KB = FMT == 3 ? kPageTok * HD / 2 : kPageTok * HD, VB = FMT == 1 ? kPageTok * HD : kPageTok * HD / 2;
+  constexpr int SB = FMT == 2 ? kPageTok * (HD / 64) * 2 : (FMT == 3 ? kPageTok * (HD / 16) : 0);
+  const int smem = (FMT ? p.nst * (KB + VB + 2 * SB) + 2 * TILE : p.nst * 2 * TILE) + 1024;
   if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
   static int attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
   }
   dim3 grid(ntiles, p.nkv, p.nsplit);
-  launch_pdl(attn_kernel<HD, NW, KS, F8>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
+  launch_pdl(attn_kernel<HD, NW, KS, FMT>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
   return (int)cudaGetLastError();
 }
 
@@ -462,9 +566,11 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
                  void* o_part, void* lse_part, const void* pos, const void* slot, const void* key_end,
                  const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
                  int max_pages, void* kpool, void* vpool, long pool_pages, int nq, int nkv, int hd, int nsplit,
-                 float scale, int window, int warps, int kv_fp8, void* tickets, void* status, cudaStream_t st) {
+                 float scale, int window, int warps, int kv_fp8, const void* kscale, const void* vscale, void* tickets,
+                 void* status, cudaStream_t st) {
   if (ntiles <= 0) return 0;
-  if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
+  if (nq % nkv || nsplit < 1 || kv_fp8 < 0 || kv_fp8 > 3) return cudaErrorInvalidValue;
+  if (kv_fp8 >= 2 && ((hd != 128 && hd != 256) || warps == 1 || !kscale || !vscale)) return cudaErrorInvalidValue;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q;
   p.q_stride = q_stride;
@@ -488,6 +594,8 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   p.window = window;
   p.status = (int*)status;
   p.tickets = (warps == 104 && nsplit > 1) ? (int*)tickets : nullptr;
+  p.kscale = (const uint8_t*)kscale;
+  p.vscale = (const uint8_t*)vscale;
   {
     static int stages = 0;      // VOLTA_ATTN_STAGES: page-load pipeline depth of the key-split decode kernel
     if (!stages) { const char* e = getenv("VOLTA_ATTN_STAGES"); stages = (e && e[0] == '2') ? 2 : 3; }   // 3: -8 % at 16K keys
@@ -496,11 +604,12 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   CUtensorMap kmap, vmap;
   const uint64_t total_rows = (uint64_t)pool_pages * nkv * kPageTok;
   int rc;
-  if (kv_fp8) {   // E5M2 cache: whole rows of hd bytes, unswizzled staging tiles
-    rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, hd, (uint64_t)hd, kPageTok, hd,
+  if (kv_fp8) {   // byte caches: whole rows of the format's bytes per key, unswizzled staging tiles
+    const int krow = kv_fp8 == 3 ? hd / 2 : hd, vrow = kv_fp8 == 1 ? hd : hd / 2;
+    rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, krow, (uint64_t)krow, kPageTok, krow,
                       CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    rc = make_tmap_2d(&vmap, vpool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, hd, (uint64_t)hd, kPageTok, hd,
+    rc = make_tmap_2d(&vmap, vpool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, vrow, (uint64_t)vrow, kPageTok, vrow,
                       CU_TENSOR_MAP_SWIZZLE_NONE);
   } else {
     rc = make_tmap_2d(&kmap, kpool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, hd, (uint64_t)hd * 2, kPageTok,
@@ -514,11 +623,20 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
     rc = warps == 1     ? launch_attn<HD_, 1, false, F8_>(p, kmap, vmap, ntiles, st)        \
          : warps == 104 ? launch_attn<HD_, 4, true, F8_>(p, kmap, vmap, ntiles, st)         \
                         : launch_attn<HD_, 4, false, F8_>(p, kmap, vmap, ntiles, st);
+#define VE_ATTNQ(HD_, F_)                                                                   \
+    rc = warps == 104 ? launch_attn<HD_, 4, true, F_>(p, kmap, vmap, ntiles, st)            \
+                      : launch_attn<HD_, 4, false, F_>(p, kmap, vmap, ntiles, st);
 #define VE_ATTN(HD_)                                                             \
   if (hd == HD_) {                                                               \
-    if (kv_fp8) { VE_ATTN2(HD_, true) } else { VE_ATTN2(HD_, false) }            \
+    if (kv_fp8 == 1) { VE_ATTN2(HD_, 1) } else if (kv_fp8 == 0) { VE_ATTN2(HD_, 0) }            \
   } else
+  if (kv_fp8 == 2 && hd == 128) { VE_ATTNQ(128, 2) }
+  else if (kv_fp8 == 2 && hd == 256) { VE_ATTNQ(256, 2) }
+  else if (kv_fp8 == 3 && hd == 128) { VE_ATTNQ(128, 3) }
+  else if (kv_fp8 == 3 && hd == 256) { VE_ATTNQ(256, 3) }
+  else
   VE_ATTN(64) VE_ATTN(128) VE_ATTN(256) { return cudaErrorInvalidValue; }
+#undef VE_ATTNQ
 #undef VE_ATTN2
 #undef VE_ATTN
   if (rc) return rc;

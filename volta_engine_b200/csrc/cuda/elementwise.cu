@@ -192,6 +192,7 @@ __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __
   h[i0] = b0;
   h[i1] = b1;
   const __nv_bfloat16* v = qkv + row_off + (long)(nq + nkv + kvh) * hd;
+  if (kv_fp8 == 2) return;   // scaled cache formats: the quantising store kernel reads the rotated keys from qkv
   if (kv_fp8) {   // E5M2 cache: one byte per element, rounded from the bf16 values
     uint8_t* k8 = reinterpret_cast<uint8_t*>(kpool);
     uint8_t* v8 = reinterpret_cast<uint8_t*>(vpool);

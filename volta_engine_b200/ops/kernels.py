@@ -82,15 +82,63 @@ def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, t
                pos_scale=1.0, mrope=None):
     """Rotate q, k inside ``qkv`` in place and write k, v rows into the paged cache. ``mrope`` = (pos3 [3, rows] int32,
     (s0, s1)): multimodal rotary embedding with time / height / width sections of s0 / s1 / rest rotary pairs."""
+    fmt = kv_format_of(kpool)
     if not qkv.is_cuda:
+        if fmt >= 2:
+            _rope_store_quant_cpu(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved,
+                                  pos_scale, mrope, fmt)
+            return
         ref.rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved,
                        pos_scale, mrope)
         return
     rows = qkv.shape[0]
     pos3, (s0, s1) = mrope if mrope is not None else (None, (0, 0))
+    # scaled formats: the rotation kernel leaves the rotated keys in ``qkv`` (store code 2 = no cache write) and the
+    # quantising store kernel writes bytes and scales
     call("rope_store", "ppppippiiiiififipii", ptr(qkv), ptr(pos), ptr(slot), ptr(page_table), page_table.shape[1],
          ptr(kpool), ptr(vpool), rows, nq, nkv, hd, rot_dim, float(theta), 1 if interleaved else 0,
-         float(pos_scale), 1 if kpool.dtype == torch.float8_e5m2 else 0, ptr(pos3), s0, s1)
+         float(pos_scale), 2 if fmt >= 2 else fmt, ptr(pos3), s0, s1)
+    if fmt >= 2:
+        call("kv_quant_store", "plppipppppiiiii", ptr(qkv), qkv.stride(0), ptr(pos), ptr(slot), ptr(page_table),
+             page_table.shape[1], ptr(kpool), ptr(vpool), ptr(kpool.kv_scale), ptr(vpool.kv_scale), rows, nq, nkv, hd, fmt)
+
+
+def kv_format_of(pool) -> int:
+    """0 bf16, 1 E5M2, 2 k8v4, 3 nvfp4 (the scaled formats are tagged on the pool tensors by the cache)."""
+    f = getattr(pool, "kv_fmt", None)
+    if f is not None:
+        return f
+    return 1 if pool.dtype == torch.float8_e5m2 else 0
+
+
+def _rope_store_quant_cpu(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, theta, interleaved, pos_scale,
+                          mrope, fmt):
+    from ..quant import kv_codec as C
+    rows = qkv.shape[0]
+    q = qkv[:, : nq * hd].reshape(rows, nq, hd)
+    k = qkv[:, nq * hd:(nq + nkv) * hd].reshape(rows, nkv, hd)
+    v = qkv[:, (nq + nkv) * hd:(nq + 2 * nkv) * hd].reshape(rows, nkv, hd)
+    qkv[:, : nq * hd] = ref.rope_rotate(q, pos, rot_dim, theta, interleaved, pos_scale, mrope).reshape(rows, -1)
+    kr = ref.rope_rotate(k, pos, rot_dim, theta, interleaved, pos_scale, mrope)
+    qkv[:, nq * hd:(nq + nkv) * hd] = kr.reshape(rows, -1)
+    kq, vq = C.FORMATS[fmt]
+    kd, ks = C.encode(kr, kq)
+    vd, vs = C.encode(v, vq)
+    for r in range(rows):
+        s = int(slot[r]) if slot is not None else 0
+        if s < 0:
+            continue
+        p = int(pos[r])
+        page = int(page_table[s, p // 64])
+        kpool[page, :, p % 64], kpool.kv_scale[page, :, p % 64] = kd[r], ks[r]
+        vpool[page, :, p % 64], vpool.kv_scale[page, :, p % 64] = vd[r], vs[r]
+
+
+def _dequant_pools(kpool, vpool, hd):
+    """bf16 copies of scaled-format pools (CPU path)."""
+    from ..quant import kv_codec as C
+    kq, vq = C.FORMATS[kpool.kv_fmt]
+    return (C.decode(kpool, kpool.kv_scale, kq, hd).to(torch.bfloat16), C.decode(vpool, vpool.kv_scale, vq, hd).to(torch.bfloat16))
 
 
 def gated_act(gu, I, act=0, limit=0.0, out=None, interleave=0):
@@ -145,7 +193,10 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
     sequence for prefill (<= 64 // G tokens per tile); None = one row per tile (decode / verify).
     """
     rows = q.shape[0]
+    fmt = kv_format_of(kpool)
     if not q.is_cuda:
+        if fmt >= 2:
+            kpool, vpool = _dequant_pools(kpool, vpool, hd)
         o = ref.attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window, key_end, gate)
         if out is not None:
             out.copy_(o)
@@ -159,14 +210,16 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
     else:
         tf, tc, ntiles = tiles
         warps = 4
+    if fmt >= 2 and warps == 1:
+        warps = 104                      # the scaled formats are built for the four-warp kernels
     if nsplit > 1 and ws is None:
         raise ValueError("split-KV attention needs a workspace")
-    call("attention", "plplplpppppppiipippliiiifiiipp",
+    call("attention", "plplplpppppppiipippliiiifiiipppp",
          ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
          ptr(ws.o_part) if ws else 0, ptr(ws.lse_part) if ws else 0, ptr(pos), ptr(slot), ptr(key_end),
          ptr(tf), ptr(tc), ntiles, rows, ptr(page_table), page_table.shape[1], ptr(kpool), ptr(vpool),
          kpool.shape[0], nq, nkv, hd, nsplit, float(scale), window, warps,
-         1 if kpool.dtype == torch.float8_e5m2 else 0,
+         fmt, ptr(kpool.kv_scale) if fmt >= 2 else 0, ptr(vpool.kv_scale) if fmt >= 2 else 0,
          ptr(ws.tickets) if (ws is not None and ATTN_FUSED_MERGE) else 0, ptr(status_word(q.device)))
     return out
 

@@ -17,8 +17,9 @@ class OutOfPages(RuntimeError):
     pass
 
 
-# whole-cache element formats: bf16, or E5M2 bytes (half the memory and traffic; attention expands pages to bf16 on chip)
-KV_FORMATS = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp8": torch.float8_e5m2}
+# whole-cache element formats: bf16, E5M2 bytes, or the scaled forms "k8v4" (int8 keys + 4-bit Hadamard-rotated values, one
+# fp16 scale per 64 elements) and "nvfp4" (E2M1 with one E4M3 scale per 16). Attention expands pages to bf16 on chip.
+KV_FORMATS = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp8": torch.float8_e5m2, "k8v4": "k8v4", "nvfp4": "nvfp4"}
 
 
 class PagedKVCache:
@@ -32,8 +33,21 @@ class PagedKVCache:
         self.max_pages = (max_seq + PAGE - 1) // PAGE
         self.device = device
         # page 0 is the null page: unassigned table entries point at it
-        self.k = torch.zeros(n_layers, num_pages, n_kv, PAGE, head_dim, dtype=dtype, device=device)
-        self.v = torch.zeros(n_layers, num_pages, n_kv, PAGE, self.v_head_dim, dtype=dtype, device=device)
+        self.fmt = 0
+        self.ks = self.vs = None
+        if isinstance(dtype, str):                  # scaled formats: byte pools plus scale pools
+            from ..quant import kv_codec as C
+            self.fmt = C.FORMAT_CODES[dtype]
+            kq, vq = C.FORMATS[self.fmt]
+            assert head_dim % 64 == 0 and self.v_head_dim % 64 == 0, "scaled KV formats need head dims that are multiples of 64"
+            self.k = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.data_bytes(kq, head_dim), dtype=torch.uint8, device=device)
+            self.v = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.data_bytes(vq, self.v_head_dim), dtype=torch.uint8, device=device)
+            self.ks = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.scale_bytes(kq, head_dim), dtype=torch.uint8, device=device)
+            self.vs = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.scale_bytes(vq, self.v_head_dim), dtype=torch.uint8, device=device)
+        else:
+            self.fmt = 1 if dtype == torch.float8_e5m2 else 0
+            self.k = torch.zeros(n_layers, num_pages, n_kv, PAGE, head_dim, dtype=dtype, device=device)
+            self.v = torch.zeros(n_layers, num_pages, n_kv, PAGE, self.v_head_dim, dtype=dtype, device=device)
         self.page_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32, device=device)
         self.host_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32)
         self.free = list(range(num_pages - 1, 0, -1))
@@ -96,15 +110,23 @@ class PagedKVCache:
         return n
 
     def layer(self, i: int):
-        return self.k[i], self.v[i]
+        k, v = self.k[i], self.v[i]
+        if self.fmt >= 2:      # the ops read the format and the scale pools off the pool tensors
+            k.kv_fmt = v.kv_fmt = self.fmt
+            k.kv_scale, v.kv_scale = self.ks[i], self.vs[i]
+            k.kv_hd, v.kv_hd = self.head_dim, self.v_head_dim
+        return k, v
 
     # ---- snapshots (prefix cache): copy the rows [from_tok, to_tok) of a slot to / from host memory
     def save_rows(self, slot: int, from_tok: int, to_tok: int) -> dict:
         p0, p1 = from_tok // PAGE, self.pages_for(to_tok)
         pages = self.host_table[slot, p0:p1].long().to(self.device)
-        return {"from": from_tok, "to": to_tok, "p0": p0,
+        snap = {"from": from_tok, "to": to_tok, "p0": p0,
                 "k": self.k[:, pages].to("cpu", non_blocking=False),
                 "v": self.v[:, pages].to("cpu", non_blocking=False)}
+        if self.ks is not None:
+            snap["ks"], snap["vs"] = self.ks[:, pages].to("cpu"), self.vs[:, pages].to("cpu")
+        return snap
 
     def load_rows(self, slot: int, snap: dict) -> None:
         self.reserve(slot, snap["to"])
@@ -113,6 +135,12 @@ class PagedKVCache:
         pages = self.host_table[slot, p0:p0 + n].long().to(self.device)
         self.k[:, pages] = snap["k"].to(self.device)
         self.v[:, pages] = snap["v"].to(self.device)
+        if self.ks is not None:
+            self.ks[:, pages] = snap["ks"].to(self.device)
+            self.vs[:, pages] = snap["vs"].to(self.device)
 
     def bytes_per_token(self) -> int:
-        return self.n_layers * self.n_kv * (self.head_dim + self.v_head_dim) * self.k.element_size()
+        per = self.k.shape[-1] * self.k.element_size() + self.v.shape[-1] * self.v.element_size()
+        if self.ks is not None:
+            per += self.ks.shape[-1] + self.vs.shape[-1]
+        return self.n_layers * self.n_kv * per
