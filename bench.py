@@ -93,7 +93,7 @@ def main():
     ap.add_argument("--gemm-mode", default=os.environ.get("VOLTA_GEMM_MODE", "w4a16"))
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--comm", default=os.environ.get("VOLTA_COMM", "symm"))
-    ap.add_argument("--kv-format", default="bf16", help="bf16 (the configuration of record) | fp8 (E5M2 cache, A/B)")
+    ap.add_argument("--kv-format", default="bf16", help="bf16 (the configuration of record) | fp8 | k8v4 | nvfp4 (quantised caches, A/B)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -174,3 +174,37 @@ def test_sentencepiece_style_tokenizer(tmp_path):
     assert ids == want and t.decode(ids, skip_special=True) == "hello  wé中"
     long = ("hello world " * 3000).strip()                     # whole-text merging stays fast on long inputs
     assert len(t.encode(long)) == 8999 and t.decode(t.encode(long)) == long
+
+
+def test_cpu_expert_service_handles_a_mailbox_request():
+    import numpy as np
+    from volta_engine_b200.runtime.cpu_experts import CpuExpertService, HostExpert
+    g = torch.Generator().manual_seed(0)
+    H, I = 32, 16
+    svc = CpuExpertService()
+    mb = svc.mailbox(H, "cpu")
+    e5 = HostExpert(torch.randn(2 * I, H, generator=g) * 0.2, torch.randn(H, I, generator=g) * 0.2)
+    e7 = HostExpert(torch.randn(2 * I, H, generator=g) * 0.2, torch.randn(H, I, generator=g) * 0.2)
+    svc.add_expert(3, 5, e5)
+    svc.add_expert(3, 7, e7)
+    x = torch.randn(2, H, generator=g).to(torch.bfloat16)
+    mb.x[:2] = x
+    mb.hdr[2:6] = [3, 2, 3, H]
+    for r, (row, e, w) in enumerate([(0, 5, 0.25), (1, 7, 0.5), (1, 5, 0.125)]):
+        mb.routes[r, 0], mb.routes[r, 1] = row, e
+        mb.route_w[r, 2] = w
+    svc.start()
+    try:
+        mb.hdr[0] = 1                                        # what the post kernel publishes last
+        for _ in range(200):
+            if int(mb.hdr[1]) == 1:
+                break
+            import time
+            time.sleep(0.01)
+        assert int(mb.hdr[1]) == 1 and svc.served == 1
+    finally:
+        svc.stop()
+    xf = x.float()
+    want0 = 0.25 * e5.forward(xf[0:1])[0]
+    want1 = 0.5 * e7.forward(xf[1:2])[0] + 0.125 * e5.forward(xf[1:2])[0]
+    assert np.allclose(mb.out[0], want0.numpy(), atol=1e-6) and np.allclose(mb.out[1], want1.numpy(), atol=1e-6)

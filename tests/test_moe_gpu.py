@@ -113,3 +113,39 @@ def test_expert_tier_reads_cold_experts_in_place_and_rebalances():
     assert torch.equal(m_gpu.ffn_block(0, m_gpu.layers[0], x, None, None), m_ref.ffn_block(0, m_ref.layers[0], x, None, None))
     torch.cuda.synchronize()
     assert tier.device_bytes() * (E // 2) == tier.host_bytes()
+
+
+def test_cpu_expert_service_answers_through_the_mailbox_and_a_stopped_service_times_out():
+    from volta_engine_b200.ops import kernels as K
+    from volta_engine_b200.runtime.cpu_experts import attach_cpu_experts
+    m_gpu, _ = _models()
+    m_ref, _ = _models()
+    svc = attach_cpu_experts(m_gpu, 0.5, budget_ms=5000.0)
+    try:
+        L = m_gpu.layers[0]
+        assert L.cpu.owner.cpu().tolist() == [0, 0, 0, 0, 1, 1, 1, 1] and float(L.bank.gu_p[4:].float().abs().sum()) == 0
+        g = torch.Generator(device=DEV).manual_seed(9)
+        for rows in (1, 6, 40):
+            x = torch.randn(rows, m_gpu.cfg.hidden, generator=g, device=DEV).to(torch.bfloat16)
+            got = m_gpu.ffn_block(0, L, x, None, None)
+            want = m_ref.ffn_block(0, m_ref.layers[0], x, None, None)
+            torch.cuda.synchronize()
+            assert_close(got.cpu(), want.cpu(), rel=0.03, name=f"host + device experts rows={rows}")
+        assert svc.served >= 3 and K.check_status(torch.device(DEV)) == 0
+        # a whole model generates through CUDA graphs with the host in the loop
+        prompt = torch.randint(0, m_gpu.cfg.vocab, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+        out, _ = Engine(m_gpu, PagedKVCache(2, m_gpu.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64).generate(prompt, 6)
+        ref_out, _ = Engine(m_ref, PagedKVCache(2, m_ref.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64).generate(prompt, 6)
+        assert len(out) == 6 and out[0] == ref_out[0]
+    finally:
+        svc.stop()
+    # nobody answers: the wait runs out after its budget, reports through the status word, and the context lives on
+    for Lx in m_gpu.layers:
+        if getattr(Lx, "cpu", None) is not None:
+            Lx.cpu.budget_ns = 50_000_000
+    x = torch.randn(2, m_gpu.cfg.hidden, device=DEV).to(torch.bfloat16)
+    m_gpu.ffn_block(0, m_gpu.layers[0], x, None, None)
+    torch.cuda.synchronize()
+    assert K.check_status(torch.device(DEV)) == 2
+    K.status_word(torch.device(DEV)).zero_()
+    assert float((x.float() + 1).sum()) != 0

@@ -96,7 +96,7 @@ def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | N
 
 
 class MoELayer(DenseLayer):
-    __slots__ = ("router", "router_bias", "bank", "shared_gu", "shared_dn", "dense_ffn", "shared_gated", "tier")
+    __slots__ = ("router", "router_bias", "bank", "shared_gu", "shared_dn", "dense_ffn", "shared_gated", "tier", "cpu")
 
 
 class MoEModel(DenseModel):
@@ -212,6 +212,13 @@ class MoEModel(DenseModel):
             return super().ffn_block(li, L, x, b, pbuf)
         act = 0 if cfg.act == "silu" else 1
         rows, H = x.shape
+        cpu = getattr(L, "cpu", None) if x.is_cuda else None
+        if cpu is not None and rows > 16:
+            # host-owned experts answer through a 16-row mailbox: larger chunks go through it piece by piece
+            y = pbuf if pbuf is not None else torch.empty(rows, H, dtype=x.dtype, device=x.device)
+            for r0 in range(0, rows, 16):
+                y[r0:r0 + 16] = self.ffn_block(li, L, x[r0:r0 + 16], b, None)
+            return y
         logits = L.router.forward(x, out_f32=True)
         shared = None
         if L.shared_gu is not None:
@@ -232,6 +239,8 @@ class MoEModel(DenseModel):
              1 if cfg.router == "sigmoid" else 0, ptr(L.router_bias), float(cfg.router_scale), cfg.n_group,
              cfg.topk_group, ptr(ids), ptr(w), self.heat[li].data_ptr() if self.heat is not None else 0)
         routes = rows * k
+        if cpu is not None:
+            cpu.post(x, ids, w, bank.e0, bank.e_local)          # routes of host-owned experts leave the table (id -1)
         y = pbuf if pbuf is not None else torch.empty(rows, H, dtype=x.dtype, device=x.device)
         I = bank.inter
         tier = getattr(L, "tier", None)
@@ -253,6 +262,8 @@ class MoEModel(DenseModel):
              ptr(shared), shared.stride(0) if shared is not None else 0,
              gate.data_ptr() if gate is not None else 0, logits.stride(0) if gate is not None else 0,
              ptr(y), y.stride(0), rows, k, H)
+        if cpu is not None:
+            cpu.wait_add(y)                                     # + the host experts' weighted sum, once it is published
         return y
 
     def _grouped(self, bank, x, ids, routes, k, act):

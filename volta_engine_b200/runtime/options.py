@@ -16,7 +16,7 @@ _TABLE = [
     ("max_seq", int, 32768, "maximum tokens per sequence (paged; up to 262144)"),
     ("max_slots", int, 8, "concurrent sequences"),
     ("kv_pool", int, 0, "KV pool size in tokens (0 = size from free memory)"),
-    ("kv_format", str, "bf16", "KV cache element format: bf16 | fp8 | nvfp4"),
+    ("kv_format", str, "bf16", "KV cache element format: bf16 | fp8 | k8v4 | nvfp4"),
     ("vram_reserve_mib", int, 2048, "device memory left unallocated"),
     ("prefill_chunk", int, 2048, "rows per prefill forward"),
     ("prefill_budget_ms", float, 50.0, "prefill time slice between decode steps when sequences are decoding"),

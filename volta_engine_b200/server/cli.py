@@ -158,8 +158,9 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     from ..runtime.kv_cache import KV_FORMATS
     if o.kv_format not in KV_FORMATS:
         raise ValueError(f"kv_format '{o.kv_format}': this build has {sorted(KV_FORMATS)}")
-    kv_bytes = 1 if o.kv_format == "fp8" else 2
-    bpt = getattr(model, "kv_layers", mcfg.n_layers) * model.nkv * 2 * mcfg.head_dim * kv_bytes
+    # bytes per cached element, scales included: bf16 2, E5M2 1, k8v4 (1 + 1/32 + 1/2 + 1/32) / 2, nvfp4 1/2 + 1/16
+    kv_bytes = {"fp8": 1.0, "k8v4": 0.78125, "nvfp4": 0.5625}.get(o.kv_format, 2.0)
+    bpt = int(getattr(model, "kv_layers", mcfg.n_layers) * model.nkv * 2 * mcfg.head_dim * kv_bytes)
     if o.kv_pool:
         pool_tokens = o.kv_pool
     elif torch.device(device).type == "cuda":
