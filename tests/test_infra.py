@@ -57,3 +57,11 @@ def test_logger_levels(capsys):
     log.set_level("info")
     with pytest.raises(ValueError):
         log.set_level("loud")
+
+
+def test_capability_table_covers_every_exported_kernel():
+    from volta_engine_b200.utils import capabilities as C
+    assert C.missing() == []
+    assert [k for k in C.TABLE if k not in C.exported()] == []
+    md = C.markdown()
+    assert "| Attention | `ve_attention` | portable |" in md and "| Collectives | `ve_ll_allreduce` | device |" in md
