@@ -150,3 +150,87 @@ def test_dense_model_step_agrees_with_and_without_fused_norms(monkeypatch):
         hidden.append(m.last_hidden.float().cpu().clone())
     cos = torch.nn.functional.cosine_similarity(hidden[0].flatten(), hidden[1].flatten(), dim=0)
     assert cos > 0.999, float(cos)
+
+
+def test_fused_add_norm_behind_the_linear_matches_linear_then_norm_kernel():
+    """The tile that finishes last adds the product into the residual and normalises the rows: same residual bits as the
+    stand-alone norm kernel, normalised rows to rounding; the launch-wide ticket is back at zero after every call."""
+    from volta_engine_b200.ops import kernels as K, linear as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(41)
+    for (N, Kd) in ((1024, 512), (5120, 3072)):
+        lin = L.LinearNVFP4.from_dense((torch.randn(N, Kd, generator=g) * 0.05).to(dev), search=False).prepare()
+        w = (torch.rand(N, generator=g) + 0.5).to(torch.bfloat16).to(dev)
+        for M in (1, 4, 16):
+            assert lin.addnorm_ready(M)
+            x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).to(dev)
+            resid = torch.randn(M, N, generator=g).to(torch.bfloat16).to(dev)
+            r_ref = resid.clone()
+            want = K.rmsnorm(lin.forward(x), w, 1e-6, 1.0, residual=r_ref)
+            for _ in range(2):                                   # twice: the ticket must have been reset
+                r_got = resid.clone()
+                got = lin.forward_addnorm(x, r_got, w, 1e-6, 1.0)
+                assert torch.equal(r_got, r_ref), f"residual differs N={N} M={M}"
+                assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+            assert int(K.dw_scratch(dev)[3][1024].item()) == 0
+    assert K.check_status(dev) == 0
+
+
+def test_dense_model_decode_agrees_with_and_without_the_fused_add_norm(monkeypatch):
+    from volta_engine_b200.models import dense
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    dev = torch.device("cuda:0")
+    cfg = dense.DenseConfig(n_layers=3, hidden=512, n_q=4, n_kv=2, head_dim=128, ffn=1024, vocab=2048)
+    m = dense.DenseModel(cfg, dev).init_random(seed=5)
+    prompt = list(range(100, 180))
+    outs = []
+    for fuse in (True, False):
+        monkeypatch.setattr(dense, "FUSE_ADDNORM", fuse)
+        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 1, 512, dev)
+        eng = Engine(m, kv, prefill_chunk=64)
+        out, _ = eng.generate(prompt, 8)
+        outs.append((out, m.last_hidden.float().cpu().clone()))
+    cos = torch.nn.functional.cosine_similarity(outs[0][1].flatten(), outs[1][1].flatten(), dim=0)
+    assert outs[0][0][0] == outs[1][0][0] and cos > 0.99, float(cos)
+
+
+@pytest.mark.parametrize("kv_dtype", [torch.bfloat16, torch.float8_e5m2])
+@pytest.mark.parametrize("rot", [128, 64])
+def test_fused_rope_and_cache_write_match_linear_then_rotation_kernel(kv_dtype, rot):
+    from volta_engine_b200.ops import kernels as K, linear as L
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(51)
+    nq, nkv, hd, H = 6, 2, 128, 768
+    lin = L.LinearNVFP4.from_dense((torch.randn((nq + 2 * nkv) * hd, H, generator=g) * 0.05).to(dev), search=False).prepare()
+    table = (torch.randperm(15, generator=g)[:12].to(torch.int32) + 1).reshape(3, 4).to(dev)
+    for M, pos, slot in ((1, [130], [1]), (5, [0, 63, 64, 200, 7], [0, 0, 1, 2, -1]), (16, list(range(100, 116)), [2] * 16)):
+        assert lin.rope_ready(M, hd)
+        x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(dev)
+        p = torch.tensor(pos, dtype=torch.int32, device=dev)
+        s = torch.tensor(slot, dtype=torch.int32, device=dev)
+        k1, v1 = (torch.zeros(16, nkv, 64, hd, dtype=kv_dtype, device=dev) for _ in range(2))
+        k2, v2 = (torch.zeros(16, nkv, 64, hd, dtype=kv_dtype, device=dev) for _ in range(2))
+        want = lin.forward(x)
+        K.rope_store(want, p, s, table, k1, v1, nq, nkv, hd, rot, 1e6, False)
+        got = lin.forward_rope(x, p, s, table, k2, v2, nq, nkv, rot, 1e6)
+        assert torch.equal(got, want), f"rotated rows differ M={M}"
+        assert torch.equal(k2.view(torch.uint8), k1.view(torch.uint8)) and torch.equal(v2.view(torch.uint8), v1.view(torch.uint8))
+    assert K.check_status(dev) == 0
+
+
+def test_dense_model_decode_agrees_with_and_without_the_fused_rope(monkeypatch):
+    from volta_engine_b200.models import dense
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    dev = torch.device("cuda:0")
+    cfg = dense.DenseConfig(n_layers=3, hidden=512, n_q=4, n_kv=2, head_dim=128, ffn=1024, vocab=2048)
+    m = dense.DenseModel(cfg, dev).init_random(seed=5)
+    prompt = list(range(100, 180))
+    outs = []
+    for fuse in (True, False):
+        monkeypatch.setattr(dense, "FUSE_ROPE", fuse)
+        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 1, 512, dev)
+        out, _ = Engine(m, kv, prefill_chunk=64).generate(prompt, 8)
+        outs.append(out)
+    assert outs[0] == outs[1]                               # same bits: same tokens

@@ -170,7 +170,7 @@ def test_block_sparse_indexer_kernels_and_model():
     qg = D.qsa_update(sg_, Wg, x.to(DEV), slot.to(DEV), pos.to(DEV))
     assert torch.allclose(qg.cpu().float(), qc.float(), atol=0.06, rtol=0.03)
     assert torch.allclose(sg_.pools.cpu().float(), sc_.pools.float(), atol=0.06, rtol=0.03)
-    assert torch.equal(sg_.ring.cpu(), sc_.ring)
+    assert torch.allclose(sg_.ring.cpu().float(), sc_.ring.float(), atol=0.06, rtol=0.03)
     sg_.pools.copy_(sc_.pools)
     qs, qp = torch.ones(1, dtype=torch.int32), torch.tensor([n0 - 1], dtype=torch.int32)
     want = D.qsa_score_reference(qc[-1:], sc_, qs, qp)[0]

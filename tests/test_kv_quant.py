@@ -82,9 +82,11 @@ def test_store_and_attention_over_the_scaled_cache(fmt, hd, nq, nkv):
     K.rope_store(qc, pos, slot, kvc.page_table, kc, vc, nq, nkv, hd, hd, 1e6, False)
     K.rope_store(qg, pos.to(DEV), slot.to(DEV), kvg.page_table, kg, vg, nq, nkv, hd, hd, 1e6, False)
     kq, vq = C.FORMATS[kvc.fmt]
-    # values are not rotated by rope: bytes and scales equal the codec's (up to the sign of zero)
+    # values are not rotated by rope: the stored values equal the codec's up to a code step where the butterfly's fp32
+    # rounding moved a scale or a tie
     dv_c, dv_g = C.decode(vc, vc.kv_scale, vq, hd), C.decode(vg.cpu(), vg.kv_scale.cpu(), vq, hd)
-    assert torch.equal(vg.kv_scale.cpu(), vc.kv_scale) and torch.allclose(dv_g, dv_c, atol=1e-6)
+    assert float((dv_g - dv_c).norm() / dv_c.norm()) < 0.02
+    assert float((vg.kv_scale.cpu() != vc.kv_scale).float().mean()) < 0.02
     dk_c, dk_g = C.decode(kc, kc.kv_scale, kq, hd), C.decode(kg.cpu(), kg.kv_scale.cpu(), kq, hd)
     assert float((dk_g - dk_c).norm() / dk_c.norm()) < 0.02                   # rope rounding can move a code by one step
     # attention reads the same bytes on both sides
@@ -119,10 +121,21 @@ def test_store_and_attention_over_the_scaled_cache(fmt, hd, nq, nkv):
 @pytest.mark.gpu
 @pytest.mark.parametrize("fmt", ["k8v4", "nvfp4"])
 def test_engine_with_a_scaled_cache_on_the_gpu(fmt):
+    from volta_engine_b200.runtime.batch import BatchRows
     cfg = DenseConfig(n_layers=2, hidden=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=1024)
     m = DenseModel(cfg, DEV).init_random(seed=3)
     p = torch.randint(1, 1000, (200,), generator=torch.Generator().manual_seed(1)).tolist()
-    ref_out, _ = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 1, 512, DEV), prefill_chunk=64).generate(p, 8)
-    q_out, _ = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 1, 512, DEV, dtype=fmt), prefill_chunk=64).generate(p, 8)
-    assert len(q_out) == 8 and q_out[0] == ref_out[0]          # random weights: later tokens may part ways
+    G = m.nq // m.nkv
+    logits = []
+    for dt in (torch.bfloat16, fmt):
+        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 1, 512, DEV, dtype=dt)
+        eng = Engine(m, kv, prefill_chunk=64)
+        eng.prefill(0, p)
+        kv.reserve(0, 210)
+        lg = m.forward(BatchRows.make([p[3]], [200], [0], DEV, "all", G, nsplit=2), kv)       # a decode row over the cache
+        logits.append(lg.float().cpu().flatten())
+        out, _ = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 16, 1, 512, DEV, dtype=dt), prefill_chunk=64).generate(p, 8)
+        assert len(out) == 8                                   # CUDA-graph decode over the format
+    a, b = logits
+    assert float(torch.dot(a, b) / (a.norm() * b.norm())) > 0.97
     assert K.check_status(DEV) == 0

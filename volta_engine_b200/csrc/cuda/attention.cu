@@ -101,8 +101,10 @@ VE_DEVINL void put16(uint8_t* tile, int key, int j, const float* f) {
 template <int HD, int NW, bool KS, int FMT>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
+  // Everything up to grid_dep_wait() reads only what earlier steps left behind (row descriptors, page table, cache pages
+  // that lie wholly before this launch's first row position), so it overlaps the kernels in front; the query rows and
+  // the pages that hold this launch's own tokens are touched after the wait.
   grid_dep_launch();
-  grid_dep_wait();
   constexpr int TILE_BYTES = kPageTok * HD * 2;
   constexpr bool F8 = FMT != 0;       // staged formats
   constexpr int KB = FMT == 3 ? kPageTok * HD / 2 : kPageTok * HD;               // key bytes of one page
@@ -187,8 +189,14 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
       tma_load_2d(vb + c * 8192, &vmap, &full[stage], c * 64, row);
     }
   };
+  const int safe_end = pos_min / kPageTok;       // pages below hold tokens of earlier launches only
+  int issued = 0;
   if (tid == 0)
-    for (int i = 0; i < nst - 1 && kt_begin + i < kt_end; ++i) issue(kt_begin + i, i);
+    for (; issued < nst - 1 && kt_begin + issued < kt_end && kt_begin + issued < safe_end; ++issued)
+      issue(kt_begin + issued, issued);
+  grid_dep_wait();
+  if (tid == 0)
+    for (int i = issued; i < nst - 1 && kt_begin + i < kt_end; ++i) issue(kt_begin + i, i);
 
   // Q fragments straight from global memory
   uint32_t qf[KSTEPS][4];

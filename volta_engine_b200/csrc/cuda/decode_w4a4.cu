@@ -16,6 +16,7 @@
 // Reference kernels this replaces: src/kernels/cuda/nvfp4/skinny_kernels.cu:445-562 (decode GEMV on mma.sync
 // fragments with in-register decode).
 #include "common.cuh"
+#include <cuda_fp8.h>
 #include "tmap.h"
 
 namespace ve {
@@ -137,6 +138,27 @@ struct DecodeParams {
   const uint32_t* ll_seq;
   int ll_rank, ll_size;
   size_t ll_off, ll_row_bytes;
+  // Optional fused residual add + RMSNorm behind the product (one GPU, decode rows): every tile's final writer counts on a
+  // launch-wide ticket; the CTA that arrives last reads the finished rows back, adds them to the residual stream (in place,
+  // rounded to bf16 like the stand-alone kernel), and writes RMSNorm(residual) * (w + wbias) -- the next block's input --
+  // so the norm costs no launch of its own. an_out null: off.
+  // Optional fused rotary embedding + KV store (a stacked q | k | v projection with head_dim 128, so one weight tile is one
+  // head): the tile's final writer rotates its q or k head at the row positions (NeoX pairs, partial rotary allowed) and
+  // writes k / v rows straight into the paged cache (bf16 or E5M2), the same arithmetic and bits as the stand-alone
+  // rotation kernel run on the rounded product. rp_pos null: off.
+  const int* rp_pos;
+  const int* rp_slot;
+  const int* rp_table;
+  int rp_max_pages;
+  void* rp_kpool;
+  void* rp_vpool;
+  int rp_nq, rp_nkv, rp_rot, rp_fp8;
+  float rp_theta;
+  int* an_ticket;
+  __nv_bfloat16* an_resid;            // [M, N], pitch N
+  const __nv_bfloat16* an_w;          // [N]
+  __nv_bfloat16* an_out;              // [M, N], pitch N
+  float an_eps, an_wbias;
 };
 
 // Warp roles (192 threads): warp 0 = TMA producer of weight tiles and their scale atoms; warp 1 = TMEM owner and
@@ -157,6 +179,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
   __shared__ uint64_t full[STAGES], empty[STAGES], acc_full;
   __shared__ uint32_t tmem_holder;
   __shared__ int s_fail, s_ticket;
+  __shared__ float s_red[4];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, n0 = tile * 128;
@@ -389,6 +412,56 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
           }
         }
       }
+    } else if (p.rp_pos) {
+      // one tile = one head: stage the rounded product, then 64 threads rotate / store the pairs of every row
+      float* sb = reinterpret_cast<float*>(smem);
+      if (write) {
+#pragma unroll
+        for (int m = 0; m < MROWS; ++m)
+          if (m < p.M) sb[m * 128 + f] = bf2f(f2bf(acc[m] * p.alpha));
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (write && f < 64 && !s_fail) {
+        const int head = tile, half = p.rp_rot >> 1;
+        const bool is_v = head >= p.rp_nq + p.rp_nkv, is_k = !is_v && head >= p.rp_nq;
+        int i0, i1;
+        if (is_v) { i0 = 2 * f; i1 = i0 + 1; }
+        else if (f < half) { i0 = f; i1 = f + half; }
+        else { i0 = p.rp_rot + 2 * (f - half); i1 = i0 + 1; }
+        const float inv_freq = exp2f(-log2f(p.rp_theta) * (2.f * (float)f / (float)p.rp_rot));
+#pragma unroll
+        for (int m = 0; m < MROWS; ++m) {
+          if (m < p.M) {
+            float a0 = sb[m * 128 + i0], a1 = sb[m * 128 + i1];
+            const int ps = p.rp_pos[m];
+            if (!is_v && f < half) {
+              float sn, cs;
+              sincosf((float)ps * inv_freq, &sn, &cs);
+              const float r0 = a0 * cs - a1 * sn, r1 = a1 * cs + a0 * sn;
+              a0 = r0;
+              a1 = r1;
+            }
+            const __nv_bfloat16 b0 = f2bf(a0), b1 = f2bf(a1);
+            p.out[(long)m * p.ldo + n0 + i0] = b0;
+            p.out[(long)m * p.ldo + n0 + i1] = b1;
+            const int sl = p.rp_slot ? p.rp_slot[m] : 0;
+            if ((is_k || is_v) && sl >= 0) {
+              const int kvh = head - p.rp_nq - (is_v ? p.rp_nkv : 0);
+              const int page = p.rp_table[(long)sl * p.rp_max_pages + ps / 64];
+              const long dst = (((long)page * p.rp_nkv + kvh) * 64 + (ps % 64)) * 128;
+              if (p.rp_fp8) {
+                uint8_t* pool = reinterpret_cast<uint8_t*>(is_v ? p.rp_vpool : p.rp_kpool);
+                pool[dst + i0] = (uint8_t)__nv_cvt_float_to_fp8(bf2f(b0), __NV_SATFINITE, __NV_E5M2);
+                pool[dst + i1] = (uint8_t)__nv_cvt_float_to_fp8(bf2f(b1), __NV_SATFINITE, __NV_E5M2);
+              } else {
+                __nv_bfloat16* pool = reinterpret_cast<__nv_bfloat16*>(is_v ? p.rp_vpool : p.rp_kpool);
+                pool[dst + i0] = b0;
+                pool[dst + i1] = b1;
+              }
+            }
+          }
+        }
+      }
     } else if (write && n < p.N && !s_fail) {
 #pragma unroll
       for (int m = 0; m < MROWS; ++m) {
@@ -416,6 +489,58 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
             }
           }
         }
+      }
+    }
+    if (p.an_out && write) {
+      // the last tile to finish normalises the rows (write is uniform over the 128 epilogue threads)
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (etid == 0) s_ticket = atomicAdd(p.an_ticket, 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s_ticket == (int)gridDim.x - 1) {
+        __threadfence();
+        const int nv = p.N >> 3;                         // 8-element vectors per row
+        for (int m = 0; m < p.M; ++m) {
+          const uint4* orow = reinterpret_cast<const uint4*>(p.out + (long)m * p.ldo);
+          uint4* rrow = reinterpret_cast<uint4*>(p.an_resid + (long)m * p.N);
+          float ss = 0.f;
+          for (int v = etid; v < nv; v += 128) {
+            const uint4 o = __ldcg(orow + v), r = rrow[v];
+            const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, rw[4] = {r.x, r.y, r.z, r.w};
+            uint32_t hw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[j]));
+              const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
+              const __nv_bfloat162 h2 = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+              const float2 hf = __bfloat1622float2(h2);
+              ss = fmaf(hf.x, hf.x, fmaf(hf.y, hf.y, ss));
+              hw[j] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            rrow[v] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+          }
+          ss = warp_sum(ss);
+          if (lane == 0) s_red[q] = ss;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const float inv = rsqrtf((s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)p.N + p.an_eps);
+          const uint4* wrow = reinterpret_cast<const uint4*>(p.an_w);
+          uint4* xrow = reinterpret_cast<uint4*>(p.an_out + (long)m * p.N);
+          for (int v = etid; v < nv; v += 128) {
+            const uint4 r = rrow[v], w4 = __ldg(wrow + v);
+            const uint32_t rw[4] = {r.x, r.y, r.z, r.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+            uint32_t xw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 h = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
+              const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[j]));
+              const __nv_bfloat162 x2 = __floats2bfloat162_rn(h.x * inv * (g.x + p.an_wbias), h.y * inv * (g.y + p.an_wbias));
+              xw[j] = *reinterpret_cast<const uint32_t*>(&x2);
+            }
+            xrow[v] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (etid == 0) *p.an_ticket = 0;                 // ready for the next launch
       }
     }
   }
@@ -474,9 +599,16 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
 int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, void* out, long ldo, void* out_f32,
                    const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, int act,
                    float act_limit, const void* pn_w, const void* pn_resid, const void* pn_delta, void* pn_resid_out,
-                   float pn_eps, float pn_wbias, const void* comm_args, void* ws, void* tickets, void* status,
-                   cudaStream_t st) {
+                   float pn_eps, float pn_wbias, const void* comm_args, void* an_resid, const void* an_w, void* an_out,
+                   float an_eps, float an_wbias, void* an_ticket, const void* rp_pos, const void* rp_slot,
+                   const void* rp_table, int rp_max_pages, void* rp_kpool, void* rp_vpool, int rp_nq, int rp_nkv, int rp_rot,
+                   float rp_theta, int rp_fp8, void* ws, void* tickets, void* status, cudaStream_t st) {
+  if (rp_pos && (act || out_f32 || residual || comm_args || an_out || !out || !rp_table || !rp_kpool || !rp_vpool ||
+                 N != (rp_nq + 2 * rp_nkv) * 128 || rp_rot < 2 || rp_rot > 128 || rp_rot % 2))
+    return cudaErrorInvalidValue;
   if (act && (out_f32 || residual || !out)) return cudaErrorInvalidValue;
+  if (an_out && (act || out_f32 || residual || comm_args || !out || !an_resid || !an_w || !an_ticket || ldo % 8 || N % 8))
+    return cudaErrorInvalidValue;
   if (pn_w && (M > 4 || !pn_resid || K % 16 || (pn_delta && pn_resid_out == pn_resid))) return cudaErrorInvalidValue;
   if (M < 1 || N % 128 || K % 256 || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
     return cudaErrorInvalidValue;
@@ -495,6 +627,11 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
                  (__nv_bfloat16*)pn_resid_out, pn_eps, pn_wbias};
   p.ll_seq = nullptr;
   for (int i = 0; i < 8; ++i) p.ll_peer[i] = nullptr;
+  p.rp_pos = (const int*)rp_pos; p.rp_slot = (const int*)rp_slot; p.rp_table = (const int*)rp_table;
+  p.rp_max_pages = rp_max_pages; p.rp_kpool = rp_kpool; p.rp_vpool = rp_vpool; p.rp_nq = rp_nq; p.rp_nkv = rp_nkv;
+  p.rp_rot = rp_rot; p.rp_fp8 = rp_fp8; p.rp_theta = rp_theta;
+  p.an_ticket = (int*)an_ticket; p.an_resid = (__nv_bfloat16*)an_resid; p.an_w = (const __nv_bfloat16*)an_w;
+  p.an_out = (__nv_bfloat16*)an_out; p.an_eps = an_eps; p.an_wbias = an_wbias;
   if (comm_args) {
     // leading fields of ve::CommArgs (csrc/cuda/comm.cu): peer[8], mc, rank, size, seq, status, budget, off_ll, ll_row_bytes
     struct Lead { uint8_t* peer[8]; uint8_t* mc; int rank, size; uint32_t* seq; int* status; unsigned long long budget;

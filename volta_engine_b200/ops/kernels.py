@@ -99,7 +99,7 @@ def rope_store(qkv, pos, slot, page_table, kpool, vpool, nq, nkv, hd, rot_dim, t
          ptr(kpool), ptr(vpool), rows, nq, nkv, hd, rot_dim, float(theta), 1 if interleaved else 0,
          float(pos_scale), 2 if fmt >= 2 else fmt, ptr(pos3), s0, s1)
     if fmt >= 2:
-        call("kv_quant_store", "plppipppppiiiii", ptr(qkv), qkv.stride(0), ptr(pos), ptr(slot), ptr(page_table),
+        call("kv_quant_store", "plpppippppiiiii", ptr(qkv), qkv.stride(0), ptr(pos), ptr(slot), ptr(page_table),
              page_table.shape[1], ptr(kpool), ptr(vpool), ptr(kpool.kv_scale), ptr(vpool.kv_scale), rows, nq, nkv, hd, fmt)
 
 
@@ -380,7 +380,7 @@ def dw_scratch(device):
         t = (torch.zeros(64, DW_MAX_K // 2, dtype=torch.uint8, device=device),
              torch.zeros(DW_MAX_K // 64 * 512, dtype=torch.uint8, device=device),
              torch.empty(1024 * 16 * 128, dtype=torch.float32, device=device),
-             torch.zeros(1024, dtype=torch.int32, device=device))
+             torch.zeros(1024 + 8, dtype=torch.int32, device=device))      # [1024] = ticket of the fused add + norm
         _dw_scratch[key] = t
     return t
 
@@ -409,7 +409,7 @@ DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
 
 
 def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None,
-                act=0, act_limit=0.0, prenorm=None, push_args=0):
+                act=0, act_limit=0.0, prenorm=None, push_args=0, addnorm=None, rope=None):
     """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path; the kernel expands each bf16
     activation row into ``terms`` residual NVFP4 rows itself (bf16-grade accuracy): out [M, N]."""
     N, K = packed.shape[0], packed.shape[1] * 2
@@ -430,11 +430,22 @@ def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=Fa
         pdl = DW_PDL
     # push_args: address of the communicator's argument block: the epilogue also sends the result rows to every peer's
     # all-reduce staging area (the all-reduce behind is then called with ``pushed=True``)
-    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppppff" + "pppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
+    # addnorm = (resid [M, N], norm_w [N], normed_out [M, N], eps, wbias): the tile that finishes last adds the product
+    # to ``resid`` in place and writes RMSNorm(resid) * (norm_w + wbias) to ``normed_out`` (no separate norm launch)
+    an_r, an_w, an_o, an_eps, an_bias = addnorm if addnorm is not None else (None, None, None, 0.0, 0.0)
+    # rope = (pos, slot, page_table, kpool, vpool, nq, nkv, rot_dim, theta): a stacked q | k | v projection with head_dim
+    # 128 rotates its q / k heads and writes k / v into the paged cache from its own epilogue
+    rp = rope if rope is not None else (None, None, None, None, None, 0, 0, 0, 0.0)
+    rp_table = rp[2]
+    call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppppff" + "ppppffp" + "pppippiiifi" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
          0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
          residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,
          act, float(act_limit), ptr(pn_w), ptr(pn_resid), ptr(pn_delta), ptr(pn_out), float(pn_eps), float(pn_bias),
-         int(push_args), ptr(ws), ptr(tickets), ptr(status_word(x.device)))
+         int(push_args), ptr(an_r), ptr(an_w), ptr(an_o), float(an_eps), float(an_bias),
+         tickets.data_ptr() + 4096 if addnorm is not None else 0,
+         ptr(rp[0]), ptr(rp[1]), ptr(rp_table), rp_table.shape[1] if rp_table is not None else 0, ptr(rp[3]), ptr(rp[4]),
+         rp[5], rp[6], rp[7], float(rp[8]), 1 if (rp[3] is not None and rp[3].dtype == torch.float8_e5m2) else 0,
+         ptr(ws), ptr(tickets), ptr(status_word(x.device)))
     return out
 
 

@@ -85,6 +85,28 @@ class LinearNVFP4:
     def dequant(self):
         return K.nvfp4_dequant(self.packed, self.scales, self.gscale)
 
+    def addnorm_ready(self, rows: int) -> bool:
+        """True when ``forward_addnorm`` runs as one launch for this row count."""
+        return (rows <= GEMV_MAX_ROWS and GEMV_KERNEL in ("auto", "tc") and self._sf_atoms is not None and self._tc_ok()
+                and self.out_features % 8 == 0)
+
+    def rope_ready(self, rows: int, hd: int) -> bool:
+        return hd == 128 and self.addnorm_ready(rows)
+
+    def forward_rope(self, x, pos, slot, page_table, kpool, vpool, nq, nkv, rot_dim, theta):
+        """The stacked q | k | v projection (head_dim 128) with the rotary embedding of q and k and the write of k and v
+        into the paged cache done by the tile that finishes each head: returns the rotated qkv rows."""
+        return K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x,
+                             rope=(pos, slot, page_table, kpool, vpool, nq, nkv, rot_dim, theta))
+
+    def forward_addnorm(self, x, resid, norm_w, eps, wbias=0.0):
+        """resid += x W^T (in place); returns RMSNorm(resid) * (norm_w + wbias): the product, the residual add and the next
+        block's input norm in one launch of the decode kernel (the tile that finishes last normalises the rows)."""
+        rows = x.shape[0]
+        normed = torch.empty(rows, self.out_features, dtype=torch.bfloat16, device=x.device)
+        K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, addnorm=(resid, norm_w, normed, eps, wbias))
+        return normed
+
     def forward(self, x, residual=None, out=None, push=None):
         """``push``: a communicator with ``push_target(rows, N)``; when the decode kernel runs, its epilogue also sends
         the rows into the peers' all-reduce staging area and ``push.pushed`` is set for the collective behind."""
