@@ -176,25 +176,6 @@ def test_fused_add_norm_behind_the_linear_matches_linear_then_norm_kernel():
     assert K.check_status(dev) == 0
 
 
-def test_dense_model_decode_agrees_with_and_without_the_fused_add_norm(monkeypatch):
-    from volta_engine_b200.models import dense
-    from volta_engine_b200.runtime.engine import Engine
-    from volta_engine_b200.runtime.kv_cache import PagedKVCache
-    dev = torch.device("cuda:0")
-    cfg = dense.DenseConfig(n_layers=3, hidden=512, n_q=4, n_kv=2, head_dim=128, ffn=1024, vocab=2048)
-    m = dense.DenseModel(cfg, dev).init_random(seed=5)
-    prompt = list(range(100, 180))
-    outs = []
-    for fuse in (True, False):
-        monkeypatch.setattr(dense, "FUSE_ADDNORM", fuse)
-        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 1, 512, dev)
-        eng = Engine(m, kv, prefill_chunk=64)
-        out, _ = eng.generate(prompt, 8)
-        outs.append((out, m.last_hidden.float().cpu().clone()))
-    cos = torch.nn.functional.cosine_similarity(outs[0][1].flatten(), outs[1][1].flatten(), dim=0)
-    assert outs[0][0][0] == outs[1][0][0] and cos > 0.99, float(cos)
-
-
 @pytest.mark.parametrize("kv_dtype", [torch.bfloat16, torch.float8_e5m2])
 @pytest.mark.parametrize("rot", [128, 64])
 def test_fused_rope_and_cache_write_match_linear_then_rotation_kernel(kv_dtype, rot):

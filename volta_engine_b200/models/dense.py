@@ -76,7 +76,6 @@ class DenseConfig:
 
 # decode: act(gate) * up inside the gate/up linear's epilogue (VOLTA_FUSE_ACT=0 keeps the separate activation kernel)
 FUSE_ROPE = os.environ.get("VOLTA_FUSE_ROPE", "1") != "0"   # rotary embedding + KV store in the qkv decode linear's epilogue
-FUSE_ADDNORM = os.environ.get("VOLTA_FUSE_ADDNORM", "0") == "1"   # residual add + next norm inside the row-parallel decode linear (measured slower: the last tile normalises alone, 182 vs 197 tok/s)
 FUSE_GATED_ACT = os.environ.get("VOLTA_FUSE_ACT", "1") != "0"
 # decode: RMSNorm fused into the linear that consumes it (VOLTA_FUSE_NORM=1). Measured neutral on the 27B decode
 # (194.0 vs 192.5 tok/s: every CTA recomputes the row statistics, which costs what the removed kernels saved), so the
@@ -86,14 +85,6 @@ FUSE_PRENORM = os.environ.get("VOLTA_FUSE_NORM", "0") == "1"
 
 def _pad_to(n: int, m: int) -> int:
     return (n + m - 1) // m * m
-
-
-class _Normed:
-    """Result of a row-parallel linear that already did the residual add and the next norm."""
-    __slots__ = ("x",)
-
-    def __init__(self, x):
-        self.x = x
 
 
 class DenseLayer:
@@ -228,18 +219,11 @@ class DenseModel:
         pbuf = comm.partial_buffer(b.n, cfg.hidden) if sp else None
         if sp:
             h = comm.shard_rows(h)
-        # one GPU, decode rows, plain residual: the row-parallel linears add into the residual and normalise for the next
-        # block themselves (``_row_parallel`` consumes ``self._an`` and hands back the normalised rows)
-        fuse_an = FUSE_ADDNORM and comm.size == 1 and b.n <= 16 and not cfg.sandwich_norm and h.is_cuda
         for li, L in enumerate(self.layers):
-            self._an = (h, L.ffn_norm) if fuse_an else None
             o = self.attn_block(li, L, x, b, kv, pbuf)
-            self._an = None
             x = self._add_norm(o, h, getattr(L, "post_attn_norm", None), L.ffn_norm)
-            nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
-            self._an = (h, nxt) if fuse_an else None
             d = self.ffn_block(li, L, x, b, pbuf)
-            self._an = None
+            nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
             x = self._add_norm(d, h, getattr(L, "post_ffn_norm", None), nxt)
             tap = getattr(self, "tap_ring", None)
             if tap is not None and li in tap.index:        # a block drafter reads this layer's output (per-slot position ring)
@@ -382,8 +366,6 @@ class DenseModel:
         """h += sum over ranks of ``part`` (through ``post_norm`` first for sandwich-norm models); returns the next
         block's input RMSNorm(h)."""
         cfg, comm = self.cfg, self.comm
-        if isinstance(part, _Normed):          # the linear already added into ``h`` and normalised
-            return part.x
         if post_norm is None:
             return comm.allreduce_add_norm(part, h, next_norm, cfg.rms_eps, cfg.norm_bias)
         # decode rows: one launch (the all-reduce kernel applies both norms); otherwise all-reduce, then the same epilogue
@@ -431,10 +413,6 @@ class DenseModel:
         sends its result to the peers from its own epilogue (communicators that offer ``push_target``)."""
         if pbuf is None and self.comm.size > 1 and hasattr(self.comm, "push_target") and isinstance(lin, LinearNVFP4):
             return lin.forward(x, push=self.comm)
-        an = getattr(self, "_an", None)
-        if an is not None and pbuf is None and isinstance(lin, LinearNVFP4) and lin.addnorm_ready(x.shape[0]):
-            self._an = None
-            return _Normed(lin.forward_addnorm(x, an[0], an[1], self.cfg.rms_eps, self.cfg.norm_bias))
         return lin.forward(x, out=pbuf)
 
     def ffn_block(self, li, L, x, b: BatchRows, pbuf):
