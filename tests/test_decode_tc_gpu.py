@@ -215,3 +215,27 @@ def test_dense_model_decode_agrees_with_and_without_the_fused_rope(monkeypatch):
         out, _ = Engine(m, kv, prefill_chunk=64).generate(prompt, 8)
         outs.append(out)
     assert outs[0] == outs[1]                               # same bits: same tokens
+
+
+@pytest.mark.parametrize("shape", ["tiny", "wide"])
+def test_graph_replay_decodes_the_same_tokens_as_eager_launches(shape):
+    """CUDA-graph replay runs the step's kernels back to back (programmatic launches really overlap there); the greedy
+    tokens must be those of eager launches, run after run."""
+    from volta_engine_b200.models import dense
+    from volta_engine_b200.ops import kernels as K
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    dev = torch.device("cuda:0")
+    if shape == "tiny":
+        cfg = dense.DenseConfig(n_layers=3, hidden=512, n_q=4, n_kv=2, head_dim=128, ffn=1024, vocab=2048)
+    else:
+        cfg = dense.DenseConfig(n_layers=4, hidden=2048, n_q=16, n_kv=4, head_dim=128, ffn=8192, vocab=4096)
+    m = dense.DenseModel(cfg, dev).init_random(seed=5)
+    prompt = list(range(100, 180))
+    outs = []
+    for graphs in (False, True, True, True):
+        kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 8, 1, 512, dev)
+        out, _ = Engine(m, kv, prefill_chunk=64, use_graphs=graphs).generate(prompt, 12)
+        outs.append(out)
+    assert outs[1] == outs[0] and outs[2] == outs[0] and outs[3] == outs[0], outs
+    assert K.check_status(dev) == 0

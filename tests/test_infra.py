@@ -65,3 +65,30 @@ def test_capability_table_covers_every_exported_kernel():
     assert [k for k in C.TABLE if k not in C.exported()] == []
     md = C.markdown()
     assert "| Attention | `ve_attention` | portable |" in md and "| Collectives | `ve_ll_allreduce` | device |" in md
+
+
+def test_every_programmatically_launched_kernel_waits_for_its_predecessor():
+    """A kernel launched with programmatic stream serialization starts before the kernel in front has finished; one that
+    never executes the dependency wait reads half-written inputs once launches overlap (CUDA-graph replay) while eager
+    runs look fine. Every kernel named at a launch_pdl call site must contain grid_dep_wait()."""
+    import glob
+    import os
+    import re
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "volta_engine_b200", "csrc", "cuda")
+    seen = 0
+    for path in glob.glob(os.path.join(root, "*.cu")):
+        src = open(path).read()
+        for name in set(re.findall(r"launch_pdl\(\s*([A-Za-z_0-9]+)", src)):
+            m = re.search(r"__global__[^;{]*?\b" + name + r"\s*\(", src)
+            assert m, f"{name}: definition not found in {path}"
+            i = src.index("{", m.end())
+            depth, j = 0, i
+            while True:
+                depth += src[j] == "{"
+                depth -= src[j] == "}"
+                if depth == 0:
+                    break
+                j += 1
+            assert "grid_dep_wait" in src[i:j], f"{os.path.basename(path)}: {name} is launched programmatically but never waits"
+            seen += 1
+    assert seen >= 20

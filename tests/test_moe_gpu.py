@@ -131,7 +131,7 @@ def test_cpu_expert_service_answers_through_the_mailbox_and_a_stopped_service_ti
             want = m_ref.ffn_block(0, m_ref.layers[0], x, None, None)
             torch.cuda.synchronize()
             assert_close(got.cpu(), want.cpu(), rel=0.03, name=f"host + device experts rows={rows}")
-        assert svc.served >= 3 and K.check_status(torch.device(DEV)) == 0
+        assert svc.served >= 3 and K.check_status(x.device) == 0
         # a whole model generates through CUDA graphs with the host in the loop
         prompt = torch.randint(0, m_gpu.cfg.vocab, (40,), generator=torch.Generator().manual_seed(1)).tolist()
         out, _ = Engine(m_gpu, PagedKVCache(2, m_gpu.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64).generate(prompt, 6)
@@ -143,9 +143,9 @@ def test_cpu_expert_service_answers_through_the_mailbox_and_a_stopped_service_ti
     for Lx in m_gpu.layers:
         if getattr(Lx, "cpu", None) is not None:
             Lx.cpu.budget_ns = 50_000_000
-    x = torch.randn(2, m_gpu.cfg.hidden, device=DEV).to(torch.bfloat16)
+    x = torch.randn(8, m_gpu.cfg.hidden, device=DEV).to(torch.bfloat16)       # 16 routes: some go to host-owned experts
     m_gpu.ffn_block(0, m_gpu.layers[0], x, None, None)
     torch.cuda.synchronize()
-    assert K.check_status(torch.device(DEV)) == 2
-    K.status_word(torch.device(DEV)).zero_()
+    assert K.check_status(x.device) == 2
+    K.status_word(x.device).zero_()
     assert float((x.float() + 1).sum()) != 0

@@ -42,6 +42,7 @@ struct AttnParams {
   int window;
   int* status;
   int nst;          // pipeline stages of the page loads (2 or 3)
+  int early;               // 1: the prologue (descriptors, pages of earlier launches) runs ahead of the dependency wait
   const uint8_t* kscale;   // scaled cache formats: scale pools [pages, kv_heads, 64, scale bytes]
   const uint8_t* vscale;
   int* tickets;     // optional [tiles * nkv], zero between launches: the CTA that finishes a (tile, kv head) last merges
@@ -105,6 +106,7 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   // that lie wholly before this launch's first row position), so it overlaps the kernels in front; the query rows and
   // the pages that hold this launch's own tokens are touched after the wait.
   grid_dep_launch();
+  if (!p.early) grid_dep_wait();
   constexpr int TILE_BYTES = kPageTok * HD * 2;
   constexpr bool F8 = FMT != 0;       // staged formats
   constexpr int KB = FMT == 3 ? kPageTok * HD / 2 : kPageTok * HD;               // key bytes of one page
@@ -602,6 +604,11 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   p.window = window;
   p.status = (int*)status;
   p.tickets = (warps == 104 && nsplit > 1) ? (int*)tickets : nullptr;
+  {
+    static int early = -1;
+    if (early < 0) { const char* e = getenv("VOLTA_ATTN_EARLY"); early = (e && e[0] == '0') ? 0 : 1; }
+    p.early = early;
+  }
   p.kscale = (const uint8_t*)kscale;
   p.vscale = (const uint8_t*)vscale;
   {
@@ -649,7 +656,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
 #undef VE_ATTN
   if (rc) return rc;
   if (nsplit > 1 && !p.tickets) {
-    launch_pdl(attn_reduce_kernel, dim3(rows * nq), dim3(hd), 0, st, (const float*)o_part, (const float*)lse_part,
+  launch_pdl(attn_reduce_kernel, dim3(rows * nq), dim3(hd), 0, st, (const float*)o_part, (const float*)lse_part,
                (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, (const int*)slot, nq, nsplit, hd);
     rc = (int)cudaGetLastError();
   }

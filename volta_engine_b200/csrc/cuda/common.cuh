@@ -106,13 +106,16 @@ VE_DEVINL void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependent
 // Host side: launch with programmatic stream serialization, so the kernel's launch and set-up overlap the kernel in
 // front of it. Kernels launched this way call grid_dep_wait() before they touch memory written by earlier kernels.
 // VOLTA_PDL=0 turns every such launch into a plain one.
-inline bool pdl_enabled() {
+// Every kernel launched this way must execute grid_dep_wait() before it reads anything an earlier kernel wrote: a kernel
+// that skips the wait races with its predecessor as soon as launches really overlap on the device (CUDA-graph replay), while
+// eager runs still look right. tests/test_infra.py checks every launch_pdl call site for the wait.
+static inline bool pdl_enabled() {
   static int v = -1;
   if (v < 0) { const char* e = getenv("VOLTA_PDL"); v = (e && e[0] == '0') ? 0 : 1; }
   return v != 0;
 }
 template <typename... KArgs, typename... Args>
-inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];

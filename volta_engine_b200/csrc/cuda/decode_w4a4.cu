@@ -434,7 +434,8 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
           if (m < p.M) {
             float a0 = sb[m * 128 + i0], a1 = sb[m * 128 + i1];
             const int ps = p.rp_pos[m];
-            if (!is_v && f < half) {
+            const int sl = p.rp_slot ? p.rp_slot[m] : 0;
+            if (!is_v && f < half && !(is_k && sl < 0)) {      // padding rows keep their key unrotated, like the rotation kernel
               float sn, cs;
               sincosf((float)ps * inv_freq, &sn, &cs);
               const float r0 = a0 * cs - a1 * sn, r1 = a1 * cs + a0 * sn;
@@ -444,7 +445,6 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
             const __nv_bfloat16 b0 = f2bf(a0), b1 = f2bf(a1);
             p.out[(long)m * p.ldo + n0 + i0] = b0;
             p.out[(long)m * p.ldo + n0 + i1] = b1;
-            const int sl = p.rp_slot ? p.rp_slot[m] : 0;
             if ((is_k || is_v) && sl >= 0) {
               const int kvh = head - p.rp_nq - (is_v ? p.rp_nkv : 0);
               const int page = p.rp_table[(long)sl * p.rp_max_pages + ps / 64];

@@ -20,8 +20,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                       float wbias, long x_stride, long out_stride) {
   __shared__ float red[33];
   extern __shared__ float rowbuf[];  // H floats
-  grid_dep_launch();                 // the kernel behind this one may be scheduled and set up now
   grid_dep_wait();                   // inputs come from the kernel in front
+  grid_dep_launch();                 // the kernel behind this one may be scheduled and set up now
   const long row = blockIdx.x;
   const __nv_bfloat16* xr = x ? x + row * x_stride : nullptr;
   float ss = 0.f;
@@ -114,8 +114,8 @@ __global__ void rmsnorm_heads_kernel(__nv_bfloat16* __restrict__ x, const __nv_b
 // ------------------------------------------------------------------------------------------------
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int H, int vocab, float scale) {
-  grid_dep_launch();
   grid_dep_wait();
+  grid_dep_launch();
   const long row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -149,8 +149,8 @@ __global__ void rope_store_kernel(__nv_bfloat16* __restrict__ qkv, const int* __
                                   __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nq,
                                   int nkv, int hd, int rot_dim, float theta, int interleaved, float pos_scale,
                                   int kv_fp8, const int* __restrict__ pos3, int sec0, int sec1) {
-  grid_dep_launch();
   grid_dep_wait();
+  grid_dep_launch();
   const int row = blockIdx.x, head = blockIdx.y;
   const int p = pos[row];
   const int s = slot ? slot[row] : 0;
@@ -220,8 +220,8 @@ VE_DEVINL float act_gelu_tanh(float g) {
 
 __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long rows,
                                  int I, int act, float limit, int interleave) {
-  grid_dep_launch();
   grid_dep_wait();
+  grid_dep_launch();
   const long n8 = rows * (long)(I / 8);
   for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n8; idx += (long)gridDim.x * blockDim.x) {
     const long r = idx / (I / 8);

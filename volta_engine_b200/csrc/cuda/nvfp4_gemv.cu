@@ -140,6 +140,8 @@ bf16_gemv_f32_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = blockIdx.x * kGemvRows;
   __shared__ float part[kGemvWarps][kGemvRows][MR];
+  grid_dep_launch();
+  grid_dep_wait();                   // x is the output of the kernel in front (this launch is a programmatic dependent)
   float acc[kGemvRows][MR];
 #pragma unroll
   for (int r = 0; r < kGemvRows; ++r)
