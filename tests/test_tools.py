@@ -147,3 +147,44 @@ def test_sessions_tool_builds_message_bodies(tmp_path):
     assert reqs[1]["messages"][0]["content"] == "b" and reqs[0]["max_tokens"] == 10
     ex = S.exchange_to_body("q", {"choices": [{"message": {"reasoning_content": "r", "content": "c"}}]})
     assert [b["type"] for b in ex["messages"][1]["content"]] == ["thinking", "text"]
+
+
+def test_e2e_tuning_recovers_perturbed_scales_and_matches_the_engine_forward():
+    import torch
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime.batch import BatchRows
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.tools import e2e as E
+    cfg = DenseConfig.tiny(vocab=128)
+    cfg.quant = "bf16"
+    m = DenseModel(cfg, "cpu").init_random(seed=0)
+    teacher = E.build_from_engine_model(m).eval()
+    # the training form computes what the engine computes
+    ids = torch.randint(1, 120, (24,), generator=torch.Generator().manual_seed(1))
+    kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 4, 1, 128, "cpu")
+    kv.reserve(0, 64)
+    eng = m.forward(BatchRows.make(ids.tolist(), list(range(24)), [0] * 24, "cpu", "all", m.nq // m.nkv, prefill=True), kv)
+    with torch.no_grad():
+        tl = teacher(ids)
+    a, b = eng[:, : cfg.vocab].float().flatten(), tl.flatten()
+    assert float(torch.dot(a, b) / (a.norm() * b.norm())) > 0.999
+    # student = teacher with perturbed channel scales: tuning brings the held-out KL down
+    student = E.build_from_engine_model(m)
+    g = torch.Generator().manual_seed(2)
+    with torch.no_grad():
+        for L in student.layers:
+            for lin in (L.qkv, L.o, L.gu, L.dn):
+                lin.su.mul_(1.0 + 0.15 * torch.randn(lin.su.shape, generator=g))
+                lin.sv.mul_(1.0 + 0.15 * torch.randn(lin.sv.shape, generator=g))
+    seqs = [torch.randint(1, 120, (32,), generator=g) for _ in range(5)]
+    with torch.no_grad():
+        teachers = [teacher(s) for s in seqs]
+    o = E.E2EOptions(steps=40, batch=2, lr=0.02, warmup=2, eval_every=20)
+    hist = E.tune(student, seqs, teachers, o, held_out=1, log=lambda s: None)
+    assert hist["eval"][-1][1] < 0.5 * hist["eval"][0][1]
+    assert abs(E.lr_at(0, o) - 0.01) < 1e-9 and abs(E.lr_at(o.steps, o) - 0.002) < 1e-6        # warm-up, then cosine to lr_min
+    # two stages: the same numbers with the layers split over two (cpu) devices
+    two = E.build_from_engine_model(m, ("cpu", "cpu")).eval()
+    assert two.stage == [0, 1] or two.stage[0] == 0
+    with torch.no_grad():
+        assert torch.allclose(two(ids), tl, atol=1e-5)

@@ -1,0 +1,257 @@
+"""``volta_e2e``: end-to-end scale tuning of a quantised dense decoder against a teacher.
+
+Every quantised linear is a frozen core between a per-input-channel and a per-output-channel scale
+(``W = diag(su) T diag(sv)``; for EXL3 the core is the Hadamard-rotated trellis decode). The tool trains log deltas on all
+those scales and additive deltas on the norm weights with Adam on KL(teacher || model) over token sequences; codes and
+every other weight stay frozen. The model runs in an fp32 training form written in PyTorch (autograd), each layer
+recomputed from its saved input in the backward (activation checkpointing). Learning rate: linear warm-up, then a cosine
+down to ``lr_min * lr``. ``devices``: the layers are split evenly over the devices as sequential stages with hand-offs
+between them (``--tp 0`` form of the reference tool).
+Reference: docs/QUANTIZATION.md:99 (``volta_e2e``), src/tools/volta_e2e.cpp:473-512 (stage split), inc/engine/train/qwen4_exp.h.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+
+class TunedLinear(torch.nn.Module):
+    """y = ((x * su * exp(a_u)) @ T) * sv * exp(a_v) with T, su, sv frozen and the log deltas trained."""
+
+    def __init__(self, core: torch.Tensor, su: torch.Tensor, sv: torch.Tensor):
+        super().__init__()
+        self.register_buffer("core", core.float().contiguous())          # [in, out]
+        self.register_buffer("su", su.float().clone())
+        self.register_buffer("sv", sv.float().clone())
+        self.a_u = torch.nn.Parameter(torch.zeros_like(self.su))
+        self.a_v = torch.nn.Parameter(torch.zeros_like(self.sv))
+
+    @classmethod
+    def from_exl3(cls, lin) -> "TunedLinear":
+        from ..quant import exl3 as ex
+        W = ex.reconstruct(lin.codes.cpu(), lin.bits, lin.cb, lin.layout)
+        core = ex.had128(ex.had128(W.t()).t())
+        return cls(core, lin.suh.cpu(), lin.svh.cpu())
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor) -> "TunedLinear":
+        """[out, in] dense weight as a core with unit scales (formats without per-channel scales)."""
+        return cls(w.float().t().contiguous(), torch.ones(w.shape[1]), torch.ones(w.shape[0]))
+
+    def forward(self, x):
+        return ((x * (self.su * torch.exp(self.a_u))) @ self.core) * (self.sv * torch.exp(self.a_v))
+
+    def tuned_scales(self):
+        return (self.su * torch.exp(self.a_u)).detach(), (self.sv * torch.exp(self.a_v)).detach()
+
+
+class TunedNorm(torch.nn.Module):
+    def __init__(self, w: torch.Tensor, eps: float, bias: float = 0.0):
+        super().__init__()
+        self.register_buffer("w0", w.float().clone())
+        self.delta = torch.nn.Parameter(torch.zeros_like(self.w0))
+        self.eps, self.bias = eps, bias
+
+    def forward(self, x):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * (self.w0 + self.delta + self.bias)
+
+
+def _rope(x, pos, theta, rot):
+    """x [T, heads, hd], NeoX pairs on the first ``rot`` dims."""
+    half = rot // 2
+    inv = torch.exp2(-math.log2(theta) * (2.0 * torch.arange(half, device=x.device, dtype=torch.float32) / rot))
+    ang = pos.float()[:, None] * inv[None]
+    cs, sn = ang.cos()[:, None], ang.sin()[:, None]
+    a, b = x[..., :half], x[..., half:rot]
+    return torch.cat([a * cs - b * sn, b * cs + a * sn, x[..., rot:]], dim=-1)
+
+
+class TunedLayer(torch.nn.Module):
+    def __init__(self, cfg, lin: dict, norms: dict):
+        super().__init__()
+        self.cfg = cfg
+        self.qkv, self.o, self.gu, self.dn = (lin[k] for k in ("qkv", "o", "gate_up", "down"))
+        self.n1, self.n2 = norms["attn"], norms["ffn"]
+
+    def forward(self, h):
+        c = self.cfg
+        T = h.shape[0]
+        hd, nq, nkv = c.head_dim, c.n_q, c.n_kv
+        qkv = self.qkv(self.n1(h))
+        pos = torch.arange(T, device=h.device)
+        rot = c.rot_dim or hd
+        q = _rope(qkv[:, : nq * hd].reshape(T, nq, hd), pos, c.rope_theta, rot)
+        k = _rope(qkv[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd), pos, c.rope_theta, rot)
+        v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+        g = nq // nkv
+        att = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.repeat_interleave(g, 1).transpose(0, 1)[None],
+                                             v.repeat_interleave(g, 1).transpose(0, 1)[None], is_causal=True,
+                                             scale=c.attn_scale or 1.0 / math.sqrt(hd))[0].transpose(0, 1).reshape(T, nq * hd)
+        h = h + self.o(att)
+        gu = self.gu(self.n2(h))
+        inter = gu.shape[-1] // 2
+        act = F.silu(gu[:, :inter]) if c.act == "silu" else F.gelu(gu[:, :inter], approximate="tanh")
+        return h + self.dn(act * gu[:, inter:])
+
+
+@dataclass
+class E2EOptions:
+    steps: int = 64
+    batch: int = 4
+    lr: float = 1e-3
+    warmup: int = 2
+    lr_min: float = 0.1
+    eval_every: int = 16
+    norms: bool = True
+    devices: list = field(default_factory=lambda: ["cpu"])
+
+
+class TunedModel(torch.nn.Module):
+    """fp32 training form of a dense decoder whose linears are ``TunedLinear`` (stacked qkv / gate_up like the engine)."""
+
+    def __init__(self, cfg, embed, layers, final_norm, head, devices):
+        super().__init__()
+        self.cfg = cfg
+        self.layers = torch.nn.ModuleList(layers)
+        self.final_norm, self.devices = final_norm, devices
+        n = len(layers)
+        self.stage = [min(len(devices) - 1, i * len(devices) // max(1, n)) for i in range(n)]      # even split, in order
+        for i, L in enumerate(self.layers):
+            L.to(devices[self.stage[i]])
+        self.register_buffer("embed", embed.float().to(devices[0]))
+        self.final_norm.to(devices[-1])
+        self.register_buffer("head", head.float().to(devices[-1]))
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        h = self.embed[ids.to(self.devices[0]).long()] * self.cfg.embed_scale
+        for i, L in enumerate(self.layers):
+            h = h.to(self.devices[self.stage[i]])                      # stage hand-off
+            h = checkpoint(L, h, use_reentrant=False) if self.training else L(h)
+        return self.final_norm(h.to(self.devices[-1])) @ self.head.t()
+
+
+def build_from_engine_model(model, devices=("cpu",)) -> TunedModel:
+    """Training form of an engine ``DenseModel`` whose linears are EXL3 (tuned) or anything else (dense core, unit scales)."""
+    from ..ops.linear_exl3 import LinearEXL3
+
+    def tl(lin):
+        if isinstance(lin, LinearEXL3):
+            return TunedLinear.from_exl3(lin)
+        w = lin.weight if hasattr(lin, "weight") else lin.dequant()
+        return TunedLinear.from_dense(w.float().cpu())
+    cfg = model.cfg
+    layers = []
+    for L in model.layers:
+        gu = L.gate_up
+        if getattr(gu, "gated", False):
+            raise ValueError("interleaved gate/up weights are a decode layout; tune the checkpoint form")
+        layers.append(TunedLayer(cfg, {"qkv": tl(L.qkv), "o": tl(L.o_proj), "gate_up": tl(gu), "down": tl(L.down)},
+                                 {"attn": TunedNorm(L.attn_norm.cpu(), cfg.rms_eps, cfg.norm_bias),
+                                  "ffn": TunedNorm(L.ffn_norm.cpu(), cfg.rms_eps, cfg.norm_bias)}))
+    head = model.lm_head.weight if hasattr(model.lm_head, "weight") else model.lm_head.dequant()
+    return TunedModel(cfg, model.embed.cpu(), layers, TunedNorm(model.final_norm.cpu(), cfg.rms_eps, cfg.norm_bias),
+                      head.cpu()[: cfg.vocab], list(devices))
+
+
+def kl_teacher(student_logits: torch.Tensor, teacher_logits: torch.Tensor) -> torch.Tensor:
+    """mean over positions of KL(teacher || student)."""
+    t = F.log_softmax(teacher_logits.float(), dim=-1)
+    s = F.log_softmax(student_logits.float(), dim=-1)
+    return (t.exp() * (t - s)).sum(-1).mean()
+
+
+def lr_at(step: int, o: E2EOptions) -> float:
+    if step < o.warmup:
+        return o.lr * (step + 1) / max(1, o.warmup)
+    p = (step - o.warmup) / max(1, o.steps - o.warmup)
+    return o.lr * (o.lr_min + (1 - o.lr_min) * 0.5 * (1 + math.cos(math.pi * min(1.0, p))))
+
+
+def tune(model: TunedModel, sequences: list, teachers: list, o: E2EOptions, held_out: int = 1, log=print) -> dict:
+    """sequences: list of id tensors; teachers: matching teacher logits [T, vocab]. The last ``held_out`` sequences only
+    evaluate. Returns {"eval": [(step, kl)], "train": [kl per step]}."""
+    params = [p for n, p in model.named_parameters() if o.norms or not n.endswith("delta")]
+    opt = torch.optim.Adam(params, lr=o.lr)
+    train = list(range(len(sequences) - held_out))
+    hist = {"eval": [], "train": []}
+
+    def evaluate(step):
+        model.eval()
+        with torch.no_grad():
+            kl = sum(float(kl_teacher(model(sequences[i]), teachers[i].to(model.devices[-1])))
+                     for i in range(len(sequences) - held_out, len(sequences))) / max(1, held_out)
+        hist["eval"].append((step, kl))
+        log(f"step {step}: held-out KL {kl:.6f}")
+        return kl
+    evaluate(0)
+    for step in range(o.steps):
+        model.train()
+        for g in opt.param_groups:
+            g["lr"] = lr_at(step, o)
+        opt.zero_grad(set_to_none=True)
+        total = 0.0
+        for b in range(o.batch):
+            i = train[(step * o.batch + b) % len(train)]
+            loss = kl_teacher(model(sequences[i]), teachers[i].to(model.devices[-1])) / o.batch
+            loss.backward()
+            total += float(loss.detach())
+        opt.step()
+        hist["train"].append(total)
+        if (step + 1) % o.eval_every == 0 or step + 1 == o.steps:
+            evaluate(step + 1)
+    return hist
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="volta_e2e", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--model", required=True, help="quantised model directory (EXL3 linears are tuned)")
+    ap.add_argument("--inputs", required=True, help="torch file: list of int token tensors")
+    ap.add_argument("--teacher", required=True, help="torch file: list of teacher logits, or a model directory to run")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--devices", default="cpu")
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--lr", type=float, default=1e-3)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--lr-min", type=float, default=0.1)
+    ap.add_argument("--eval-every", type=int, default=16)
+    ap.add_argument("--norms", type=int, default=1)
+    a = ap.parse_args(argv)
+    from pathlib import Path
+    from ..loader.safetensors import write_safetensors
+    from ..models.factory import load_model
+    devices = [d if d.startswith(("cpu", "cuda")) else f"cuda:{d}" for d in a.devices.split(",")]
+    model, _ = load_model(a.model, "cpu", None)
+    tm = build_from_engine_model(model, devices)
+    seqs = torch.load(a.inputs, weights_only=True)
+    if Path(a.teacher).is_dir():
+        tmodel, _ = load_model(a.teacher, "cpu", None)
+        teacher = build_from_engine_model(tmodel, devices).eval()
+        with torch.no_grad():
+            teachers = [teacher(s).cpu() for s in seqs]
+    else:
+        teachers = torch.load(a.teacher, weights_only=True)
+    o = E2EOptions(a.steps, a.batch, a.lr, a.warmup, a.lr_min, a.eval_every, bool(a.norms), devices)
+    hist = tune(tm, seqs, teachers, o)
+    out = Path(a.out) / ".partial"
+    out.mkdir(parents=True, exist_ok=True)
+    tensors = {}
+    for li, L in enumerate(tm.layers):
+        for name, lin in (("qkv", L.qkv), ("o_proj", L.o), ("gate_up", L.gu), ("down", L.dn)):
+            su, sv = lin.tuned_scales()
+            tensors[f"layers.{li}.{name}.suh"], tensors[f"layers.{li}.{name}.svh"] = su.half().cpu(), sv.half().cpu()
+        tensors[f"layers.{li}.attn_norm.weight"] = (L.n1.w0 + L.n1.delta).detach().half().cpu()
+        tensors[f"layers.{li}.ffn_norm.weight"] = (L.n2.w0 + L.n2.delta).detach().half().cpu()
+    write_safetensors(out / "e2e_scales.safetensors", tensors)
+    print(f"held-out KL {hist['eval'][0][1]:.6f} -> {hist['eval'][-1][1]:.6f}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
