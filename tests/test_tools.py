@@ -188,3 +188,154 @@ def test_e2e_tuning_recovers_perturbed_scales_and_matches_the_engine_forward():
     assert two.stage == [0, 1] or two.stage[0] == 0
     with torch.no_grad():
         assert torch.allclose(two(ids), tl, atol=1e-5)
+
+
+def test_hessian_capture_files_ldl_feedback_and_resumable_hessian_aware_quantize(tmp_path):
+    import torch
+    from volta_engine_b200.models.dense import DenseConfig
+    from volta_engine_b200.models.factory import load_model, save_dense_checkpoint
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.ops import hessian as hz
+    from volta_engine_b200.quant import ldlq, nvfp4 as qn
+    from volta_engine_b200.tools.quantize import quantize_dir
+    from volta_engine_b200.loader.safetensors import SafeTensorsRepo
+    # capture file round trip; a short or foreign file is refused
+    H = torch.randn(32, 32)
+    hz.write_hessian(tmp_path / "a.f32", H, 77)
+    got = hz.read_hessian(tmp_path / "a.f32")
+    assert got[1] == 77 and torch.equal(got[0], H)
+    (tmp_path / "bad.f32").write_bytes(b"\0" * 40)
+    assert hz.read_hessian(tmp_path / "bad.f32") is None and hz.read_hessian(tmp_path / "none.f32") is None
+    assert hz.site_of_tensor("model.layers.7.self_attn.o_proj.weight") == (7, 2)
+    assert hz.site_of_tensor("model.layers.3.mlp.up_proj.weight") == (3, 1) and hz.site_of_tensor("lm_head.weight") == (0, 4)
+    assert hz.parse_layer_range("2-5", 8) == (2, 6) and hz.parse_layer_range("", 8) == (0, 8)
+    # block LDL: exact factorisation, unit diagonal blocks
+    g = torch.Generator().manual_seed(0)
+    K, N = 256, 128
+    X = torch.randn(2048, K, generator=g) @ (torch.randn(K, K, generator=g) * 0.3 + torch.eye(K))
+    X[:, :8] *= 6.0
+    Hs = X.t() @ X
+    Hd = ldlq.damp(Hs)
+    L, D = ldlq.block_ldl(Hd, 16)
+    assert float((L @ torch.block_diag(*D) @ L.t() - Hd).abs().max() / Hd.abs().max()) < 1e-12
+    assert torch.allclose(L[16:32, 16:32], torch.eye(16, dtype=torch.float64)) and float(L[0:16, 16:].abs().max()) == 0.0
+    # the feedback lowers the Hessian-metric error below round-to-nearest (which has the lower plain squared error)
+    w = torch.randn(N, K, generator=g) * 0.02
+    p, s, gs = ldlq.quantize_nvfp4_hessian(w, Hs)
+    wq = qn.dequantize_nvfp4(p, s, gs)
+    p0, s0, g0 = qn.quantize_nvfp4(w, search=True)
+    w0 = qn.dequantize_nvfp4(p0, s0, g0)
+    e_ldl, e_rtn = ldlq.proxy_error(w.t(), wq.t(), Hs), ldlq.proxy_error(w.t(), w0.t(), Hs)
+    assert e_ldl < 0.85 * e_rtn and ((w0 - w) ** 2).mean() < ((wq - w) ** 2).mean()
+    # a model's capture: prefill rows are counted, decode rows are not; the sums are those of the taps
+    cfg = DenseConfig(n_layers=2, hidden=128, n_q=2, n_kv=1, head_dim=64, ffn=256, vocab=300)
+    src = tmp_path / "src"
+    save_dense_checkpoint(src, cfg, seed=3, fmt="bf16", std=0.05)
+    model, _ = load_model(src, "cpu")
+    hs = model.enable_hessians(layer_range=(0, 2))
+    kv = PagedKVCache(2, 1, 64, 8, 1, 256, "cpu")
+    Engine(model, kv, use_graphs=False, prefill_chunk=64).generate(list(range(40)), 3)
+    cap = tmp_path / "cap"
+    files = hs.dump(cap)
+    assert "L00_s0_r0.f32" in files and "L01_s3_r0.f32" in files and "L00_s4_r0.f32" in files
+    h0, rows = hz.read_hessian(cap / "L00_s0_r0.f32")
+    assert rows == 40 and h0.shape == (128, 128) and float(h0.diagonal().min()) > 0
+    h3, _ = hz.read_hessian(cap / "L01_s3_r0.f32")
+    assert h3.shape == (256, 256)
+    # Hessian-aware quantise: proxy errors reported, .partial resumes, the result loads and runs
+    dst = tmp_path / "q"
+    logs = []
+    r1 = quantize_dir(src, dst, "nvfp4", min_dim=64, log=logs.append, hess_dir=cap, only=["layers.0."], assemble=False)
+    assert r1["quantized"] == 7 and not r1["shards"] and len(r1["proxy_errors"]) == 7
+    assert all(0 < v < 0.05 for v in r1["proxy_errors"].values())
+    assert (dst / ".partial" / "model.layers.0.mlp.down_proj.weight.safetensors").exists()
+    r2 = quantize_dir(src, dst, "nvfp4", min_dim=64, log=logs.append, hess_dir=cap)
+    assert r2["resumed"] == 7 and r2["quantized"] == 14 and len(r2["proxy_errors"]) == 7
+    m, _ = load_model(dst, "cpu")
+    out, _ = Engine(m, PagedKVCache(2, 1, 64, 8, 1, 256, "cpu"), use_graphs=False, prefill_chunk=64).generate(list(range(24)), 3)
+    assert len(out) == 3
+    # the Hessian-aware result beats the plain one in the capture's metric
+    plain = tmp_path / "plain"
+    quantize_dir(src, plain, "nvfp4", min_dim=64, log=lambda *_: None)
+    from volta_engine_b200.tools.hess_compare import load_quantized
+    base = "model.layers.1.mlp.down_proj"
+    W = SafeTensorsRepo(src).load(base + ".weight").float().t()
+    assert ldlq.proxy_error(W, load_quantized(dst, base), h3) < ldlq.proxy_error(W, load_quantized(plain, base), h3)
+
+
+def test_hess_compare_subcommands(tmp_path, capsys):
+    import torch
+    from volta_engine_b200.ops import hessian as hz
+    from volta_engine_b200.loader.safetensors import write_safetensors
+    from volta_engine_b200.runtime.route_dump import RouteRecorder
+    from volta_engine_b200.tools import hess_compare as hc
+    from volta_engine_b200.tools.quantize import quantize_dir
+    g = torch.Generator().manual_seed(1)
+    K = 128
+    Xa = torch.randn(512, K, generator=g)
+    Xa[:, :4] *= 5
+    Xb = torch.randn(768, K, generator=g)
+    Xb[:, 64:68] *= 5
+    da, db, dm = tmp_path / "a", tmp_path / "b", tmp_path / "m"
+    da.mkdir(); db.mkdir()
+    for d, X in ((da, Xa), (db, Xb)):
+        hz.write_hessian(d / "L00_s0_r0.f32", X.t() @ X, X.shape[0])
+        hz.write_hessian(d / "L00_s1_r0.f32", X.t() @ X * 2, X.shape[0])
+    hz.write_hessian(da / "L01_s0_r0.f32", Xa.t() @ Xa, 512)
+    st = hc.stats(da, db, out=lambda *_: None)
+    assert st["missing"] == 1 and set(st["sites"]) == {"s0", "s1"} and st["sites"]["s0"]["mean"] > 0.3
+    same = hc.stats(da, da, out=lambda *_: None)
+    assert same["sites"]["s0"]["worst"] == 0 and same["files"][0]["trace"] == 1.0
+    assert hz.merge_dirs(dm, [da, db]) == ["L00_s0_r0.f32", "L00_s1_r0.f32"]
+    hm, rows = hz.read_hessian(dm / "L00_s0_r0.f32")
+    assert rows == 1280 and torch.allclose(hm, Xa.t() @ Xa + Xb.t() @ Xb, rtol=1e-5, atol=1e-3)
+    # cross: each Hessian's own quantisation is the best under itself
+    src = tmp_path / "src"
+    src.mkdir()
+    E, H, I = 3, 128, 128
+    tensors = {"model.layers.0.self_attn.q_proj.weight": (torch.randn(128, K, generator=g) * 0.03).bfloat16()}
+    pre = "model.layers.0.mlp.experts.{expert}.{proj}_proj"
+    for e in range(E):
+        for p, shape in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+            tensors[pre.format(expert=e, proj=p) + ".weight"] = (torch.randn(*shape, generator=g) * 0.05).bfloat16()
+    write_safetensors(src / "model.safetensors", tensors)
+    res = hc.cross(src, "model.layers.0.self_attn.q_proj", da / "L00_s0_r0.f32", db / "L00_s0_r0.f32", out=lambda *_: None)
+    assert res["A"]["under_A"] < res["B"]["under_A"] and res["B"]["under_B"] < res["A"]["under_B"] and res["ratio"] > 1.0
+    # score under a capture: the Hessian-aware checkpoint beats the plain one; a .partial directory is readable
+    qa, qp = tmp_path / "qa", tmp_path / "qp"
+    quantize_dir(src, qa, "nvfp4", min_dim=64, log=lambda *_: None, hess_dir=da, assemble=False)
+    quantize_dir(src, qp, "nvfp4", min_dim=64, log=lambda *_: None)
+    tab = hc.score(src, ["model.layers.0.self_attn.q_proj"], [qa, qp], hess_dir=da, out=lambda *_: None)
+    row = tab["model.layers.0.self_attn.q_proj"]
+    assert 0 < row[0] < row[1]
+    # route dump: recorder, busiest experts, expert scores under the activation Hessian, block output error
+    rec = RouteRecorder(max_rows=64)
+    x = torch.randn(200, H, generator=g).bfloat16()
+    ids = torch.stack([torch.randint(0, 2, (200,), generator=g), torch.full((200,), 2)], 1)
+    ids[:150, 0] = 0
+    w = torch.rand(200, 2, generator=g)
+    rec.record(0, x[:8], ids[:8], w[:8])                      # a decode-sized batch is ignored
+    rec.record(0, x, ids, w)
+    dump = rec.result()
+    assert set(dump[0]) == {0, 1, 2} and dump[0][2][0].shape == (64, H) and dump[0][1][0].shape[0] < 64
+    r, c = (ids == 1).nonzero(as_tuple=True)
+    assert torch.equal(dump[0][1][0], x[r]) and torch.allclose(dump[0][1][1], w[r, c])
+    rec.save(tmp_path / "route.pt")
+    rt = hc.routes(str(tmp_path / "route.pt"), [0], top=2, prefix="model.layers.{layer}.mlp.experts.{expert}.{proj}_proj",
+                   out=lambda *_: None)
+    assert [e for e, _ in rt[0]] == [0, 2] or [e for e, _ in rt[0]] == [2, 0]
+    names = [pre.format(expert=1, proj=p) for p in ("gate", "down")]
+    tab = hc.score(src, names, [qp], route=str(tmp_path / "route.pt"), prefix="model.layers.{layer}.mlp.experts.{expert}.{proj}_proj",
+                   out=lambda *_: None)
+    assert all(0 < tab[n][0] < 0.05 for n in names)
+    mo = hc.moe(src, str(tmp_path / "route.pt"), [0], [qp, src], prefix="model.layers.{layer}.mlp.experts.{expert}.{proj}_proj",
+                out=lambda *_: None)
+    assert 0 < mo[0]["mean"][0] < 0.1 and mo[0]["mean"][1] == 0.0 and len(mo[0]["experts"][0]) == 3
+    # the command line
+    assert hc.main(["stats", str(da), str(db)]) == 0
+    assert "files in both" in capsys.readouterr().out
+    assert hc.main(["merge", str(tmp_path / "m2"), str(da), str(db), "--weights", "0.7,0.3"]) == 0
+    h2, rows2 = hz.read_hessian(tmp_path / "m2" / "L00_s0_r0.f32")
+    want = (0.7 * (Xa.t() @ Xa) / 512 + 0.3 * (Xb.t() @ Xb) / 768) * 1280
+    assert rows2 == 1280 and torch.allclose(h2, want, rtol=1e-4, atol=1e-2)

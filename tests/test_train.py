@@ -149,3 +149,26 @@ def test_hessian_accumulator_gpu():
     h = HessianAccumulator(256, dev).add(x[:70].to(dev)).add(x[70:].to(dev))
     ref = x.float().t() @ x.float()
     assert torch.allclose(h.H.cpu(), ref, atol=0.05, rtol=1e-2)
+
+
+@pytest.mark.gpu
+def test_model_hessian_capture_gpu_matches_cpu_capture():
+    """The capture taps of the dense model on the device (tcgen05 x^T x) against the same model's capture on the CPU."""
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    cfg = DenseConfig.tiny(n_layers=2)
+    sums = {}
+    for dev in ("cpu", "cuda"):
+        m = DenseModel(cfg, dev)
+        m.init_random(seed=4)
+        hs = m.enable_hessians()
+        kv = PagedKVCache(cfg.n_layers, cfg.n_kv, cfg.head_dim, 8, 1, 256, dev)
+        Engine(m, kv, use_graphs=False, prefill_chunk=128).generate(list(range(3, 99)), 2)
+        sums[dev] = {k: (a.H.float().cpu(), a.rows) for k, a in hs.sites.items()}
+    assert set(sums["cpu"]) == set(sums["cuda"])
+    for k, (hc, rows) in sums["cpu"].items():
+        hg, rg = sums["cuda"][k]
+        assert rows == rg == 96, k
+        cos = float((hc * hg).sum() / (hc.norm() * hg.norm()))
+        assert cos > 0.995, (k, cos)

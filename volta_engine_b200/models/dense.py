@@ -234,6 +234,8 @@ class DenseModel:
                 steer.apply(h, b.pos, b.slot, li)
                 x = K.rmsnorm(h, nxt, cfg.rms_eps, cfg.norm_bias, out=x)
         self.last_hidden, self.last_residual = x, h
+        if getattr(self, "hess", None) is not None:
+            self.hess.accumulate(0, 4, x)
         if b.logits == LOGITS_NONE:
             return None
         if b.logits == LOGITS_LAST:
@@ -385,6 +387,9 @@ class DenseModel:
         """Attention sub-layer: returns this rank's partial of the o_proj output [n, H]."""
         cfg = self.cfg
         kpool, vpool = kv.layer(li)
+        hs = getattr(self, "hess", None)
+        if hs is not None and b.n >= hs.min_rows:      # calibration capture: the unfused path below, with its taps
+            return self._attn_block_capture(li, L, x, b, kv, pbuf, hs)
         if (FUSE_ROPE and x.is_cuda and not cfg.qk_norm and not cfg.rope_interleaved and b.pos3 is None
                 and isinstance(L.qkv, LinearNVFP4) and L.qkv.rope_ready(b.n, self.hd) and K.kv_format_of(kpool) < 2):
             # decode rows: rotation and cache write happen in the projection's epilogue (one launch less per layer)
@@ -408,6 +413,41 @@ class DenseModel:
                           nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
         return self._row_parallel(L.o_proj, att, pbuf)
 
+    def _attn_block_capture(self, li, L, x, b, kv, pbuf, hs):
+        cfg = self.cfg
+        kpool, vpool = kv.layer(li)
+        hs.accumulate(li, 0, x)
+        qkv = L.qkv.forward(x)
+        if cfg.qk_norm:
+            stride = qkv.stride(0)
+            K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
+            K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
+                             self.nq * self.hd)
+        mrope = (b.pos3, tuple(cfg.mrope_sections)) if b.pos3 is not None and cfg.mrope_sections else None
+        K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
+                     self.layer_theta(li), cfg.rope_interleaved, mrope=mrope)
+        att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
+                          self.scale, window=self.layer_window(li), key_end=b.key_end, tiles=b.tiles,
+                          nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
+        hs.accumulate(li, 2, att)
+        return self._row_parallel(L.o_proj, att, pbuf)
+
+    def enable_hessians(self, layer_range=None, min_rows: int = 17):
+        """Calibration capture: x^T x sums at the inputs of the four projections of every layer in ``layer_range``
+        and of the head (site numbering of src/models/qwen3_5.cpp:678-906 in the reference: 0 qkv input, 1 gate / up
+        input, 2 o_proj input, 3 down input, layer 0 site 4 the head's input). Returns the set; ``dump`` writes it."""
+        from ..ops.hessian import HessianSet
+        cfg = self.cfg
+        hs = HessianSet(cfg.n_layers, 5, min_rows, layer_range)
+        for li, L in enumerate(self.layers):
+            hs.add(li, 0, cfg.hidden, self.device)
+            hs.add(li, 1, cfg.hidden, self.device)
+            hs.add(li, 2, self.nq * self.hd, self.device)
+            hs.add(li, 3, self.ffn, self.device)
+        hs.add(0, 4, cfg.hidden, self.device)
+        self.hess = hs
+        return hs
+
     def _row_parallel(self, lin, x, pbuf):
         """Row-parallel projection whose output goes into the layer's all-reduce: on decode rows the NVFP4 decode linear
         sends its result to the peers from its own epilogue (communicators that offer ``push_target``)."""
@@ -419,10 +459,15 @@ class DenseModel:
         """Feed-forward sub-layer: returns this rank's partial of the down projection [n, H]."""
         cfg = self.cfg
         act = 0 if cfg.act == "silu" else 1
+        hs = getattr(self, "hess", None)
+        if hs is not None:
+            hs.accumulate(li, 1, x)
         if getattr(L.gate_up, "gated", False):        # gate / up rows interleaved: activation fused into the decode linear
             a = L.gate_up.forward_gated(x, act, cfg.act_limit)
         else:
             a = K.gated_act(L.gate_up.forward(x), self.ffn, act, cfg.act_limit)
+        if hs is not None:
+            hs.accumulate(li, 3, a)
         return self._row_parallel(L.down, a, pbuf)
 
     def ensure_workspace(self, max_rows: int, max_splits: int):

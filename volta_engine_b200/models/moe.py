@@ -230,7 +230,7 @@ class MoEModel(DenseModel):
         if not x.is_cuda:
             if getattr(L, "shared_gated", False) and shared is not None:
                 shared = (shared.float() * torch.sigmoid(logits[:, cfg.n_experts:cfg.n_experts + 1])).to(x.dtype)
-            return self._ffn_reference(L, x, logits[:, :cfg.n_experts], shared)
+            return self._ffn_reference(L, x, logits[:, :cfg.n_experts], shared, li)
         bank = L.bank
         k = cfg.top_k
         ids = torch.empty(rows, k, dtype=torch.int32, device=x.device)
@@ -239,6 +239,9 @@ class MoEModel(DenseModel):
              1 if cfg.router == "sigmoid" else 0, ptr(L.router_bias), float(cfg.router_scale), cfg.n_group,
              cfg.topk_group, ptr(ids), ptr(w), self.heat[li].data_ptr() if self.heat is not None else 0)
         routes = rows * k
+        rec = getattr(self, "route_recorder", None)
+        if rec is not None:
+            rec.record(li, x, ids, w)
         if cpu is not None:
             cpu.post(x, ids, w, bank.e0, bank.e_local)          # routes of host-owned experts leave the table (id -1)
         y = pbuf if pbuf is not None else torch.empty(rows, H, dtype=x.dtype, device=x.device)
@@ -291,10 +294,13 @@ class MoEModel(DenseModel):
              ptr(d), d.stride(0), routes, bank.e_local, H, I, bn, ptr(tab), max_tiles, ptr(st))
         return d, inv
 
-    def _ffn_reference(self, L, x, logits, shared):
+    def _ffn_reference(self, L, x, logits, shared, li=-1):
         """fp32 oracle of the routed FFN (same rounding points as the kernels: bf16 between the stages)."""
         cfg, bank = self.cfg, L.bank
         ids, w = route_reference(logits, cfg, L.router_bias)
+        rec = getattr(self, "route_recorder", None)
+        if rec is not None and li >= 0:
+            rec.record(li, x, ids, w)
         rows, H = x.shape
         y = torch.zeros(rows, H, dtype=torch.float32)
         for t in range(rows):
