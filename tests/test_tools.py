@@ -339,3 +339,43 @@ def test_hess_compare_subcommands(tmp_path, capsys):
     h2, rows2 = hz.read_hessian(tmp_path / "m2" / "L00_s0_r0.f32")
     want = (0.7 * (Xa.t() @ Xa) / 512 + 0.3 * (Xb.t() @ Xb) / 768) * 1280
     assert rows2 == 1280 and torch.allclose(h2, want, rtol=1e-4, atol=1e-2)
+
+
+def test_ppl_tool_scores_calibrates_and_measures_kl(tmp_path, capsys):
+    import json
+    import torch
+    from volta_engine_b200.models.dense import DenseConfig
+    from volta_engine_b200.models.factory import save_dense_checkpoint
+    from volta_engine_b200.ops import hessian as hz
+    from volta_engine_b200.tools import ppl
+    from volta_engine_b200.tools.quantize import quantize_dir
+    cfg = DenseConfig(n_layers=2, hidden=128, n_q=2, n_kv=1, head_dim=64, ffn=256, vocab=300)
+    src = tmp_path / "src"
+    save_dense_checkpoint(src, cfg, seed=5, fmt="bf16", std=0.08)
+    g = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(0, 300, (n,), generator=g, dtype=torch.int32) for n in (70, 45)]
+    torch.save(seqs, tmp_path / "tok.pt")
+    cap, teacher = tmp_path / "cap", tmp_path / "teacher.pt"
+    rc = ppl.main(["--model", str(src), "--tokens-file", str(tmp_path / "tok.pt"), "--chunk", "32", "--device", "cpu",
+                   "--calibrate", "--hessian-dir", str(cap), "--hessian-layers", "1-1", "--topk-out", str(teacher),
+                   "--topk", "8", "--inputs-out", str(tmp_path / "inputs.pt")])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["tokens"] == 113 and 100 < out["ppl"] < 900          # random weights: near the vocabulary size
+    files = sorted(f.name for f in cap.iterdir())
+    assert files == ["L00_s4_r0.f32", "L01_s0_r0.f32", "L01_s1_r0.f32", "L01_s2_r0.f32", "L01_s3_r0.f32"]
+    assert hz.read_hessian(cap / "L01_s1_r0.f32")[1] == 32 + 32 + 32       # whole chunks only: 6- and 13-row tails are decode-sized
+    t = torch.load(teacher, weights_only=True)
+    assert t["k"] == 8 and t["ids"][0].shape == (70, 8) and t["tail"][1].shape == (45,)
+    assert torch.allclose(t["logp"][0].exp().sum(-1) + t["tail"][0].exp(), torch.ones(70), atol=1e-4)
+    assert [len(s) for s in torch.load(tmp_path / "inputs.pt", weights_only=True)] == [70, 45]
+    # the model against its own teacher: zero; a quantised copy: small and positive
+    rc = ppl.main(["--model", str(src), "--tokens-file", str(tmp_path / "tok.pt"), "--chunk", "64", "--device", "cpu",
+                   "--kl-teacher", str(teacher)])
+    same = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert abs(same["kl"]) < 1e-4 and abs(same["ppl"] - out["ppl"]) / out["ppl"] < 1e-3
+    q = tmp_path / "q"
+    quantize_dir(src, q, "nvfp4", min_dim=64, log=lambda *_: None)
+    ppl.main(["--model", str(q), "--tokens-file", str(tmp_path / "tok.pt"), "--chunk", "64", "--device", "cpu",
+              "--kl-teacher", str(teacher)])
+    quant = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert 1e-5 < quant["kl"] < 0.2

@@ -38,6 +38,9 @@ _TABLE = [
     ("log_level", str, "info", "error | warn | info | debug"),
     ("dump_requests", str, "", "directory that receives one JSON file per request"),
     ("trace_layers", bool, False, "NVTX range per layer"),
+    ("hessian_dir", str, "", "calibration capture: x^T x of every projection input over the prefill rows, written here at shutdown"),
+    ("hessian_layers", str, "", "lo-hi: capture these layers only (a slice that fits beside the weights)"),
+    ("route_dump", str, "", "file that receives the MoE blocks' routed rows and routing weights at shutdown"),
 ]
 
 _TYPES = {n: t for n, t, _, _ in _TABLE}

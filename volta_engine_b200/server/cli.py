@@ -176,7 +176,27 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
                       dtype=o.kv_format)
     engine = Engine(model, kv, use_graphs=not o.no_graphs and torch.device(device).type == "cuda",
                     prefill_chunk=o.prefill_chunk)
+    if o.hessian_dir and hasattr(model, "enable_hessians"):
+        from ..ops.hessian import parse_layer_range
+        model.enable_hessians(parse_layer_range(o.hessian_layers, mcfg.n_layers))
+    if o.route_dump and hasattr(model, "heat"):
+        from ..runtime.route_dump import RouteRecorder
+        model.route_recorder = RouteRecorder()
     return model, hf, engine, pool_tokens
+
+
+def dump_calibration(model, options, rank: int = 0) -> list[str]:
+    """Writes what the capture options collected (Hessian files per site, the route dump); called at shutdown."""
+    out = []
+    hs = getattr(model, "hess", None)
+    if hs is not None and options.hessian_dir:
+        out += hs.dump(options.hessian_dir, rank)
+    rec = getattr(model, "route_recorder", None)
+    if rec is not None and options.route_dump:
+        path = options.route_dump if rank == 0 else f"{options.route_dump}.r{rank}"
+        rec.save(path)
+        out.append(path)
+    return out
 
 
 def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=None):
@@ -265,6 +285,7 @@ def _serve_forever(cfg: LaunchConfig, srv, engine) -> int:
         run_tui(f"http://{cfg.host}:{srv.port}", stop)
     stop.wait()
     srv.stop()
+    dump_calibration(engine.model, cfg.options, getattr(engine.model.comm, "rank", 0))
     if hasattr(engine, "shutdown"):
         engine.shutdown()
     return 0

@@ -159,11 +159,20 @@ def build_from_engine_model(model, devices=("cpu",)) -> TunedModel:
                       head.cpu()[: cfg.vocab], list(devices))
 
 
-def kl_teacher(student_logits: torch.Tensor, teacher_logits: torch.Tensor) -> torch.Tensor:
-    """mean over positions of KL(teacher || student)."""
+def kl_teacher(student_logits: torch.Tensor, teacher_logits) -> torch.Tensor:
+    """mean over positions of KL(teacher || student). The teacher is a full logits tensor, or the top-K form that
+    ``volta_ppl --topk-out`` writes: (ids [S, K], logp [S, K], tail [S])."""
+    if isinstance(teacher_logits, (tuple, list)):
+        from .ppl import kl_topk
+        ids, logp, tail = (t.to(student_logits.device) for t in teacher_logits)
+        return kl_topk(student_logits[: ids.shape[0]], ids, logp, tail).mean()
     t = F.log_softmax(teacher_logits.float(), dim=-1)
     s = F.log_softmax(student_logits.float(), dim=-1)
     return (t.exp() * (t - s)).sum(-1).mean()
+
+
+def _to(teacher, device):
+    return tuple(t.to(device) for t in teacher) if isinstance(teacher, (tuple, list)) else teacher.to(device)
 
 
 def lr_at(step: int, o: E2EOptions) -> float:
@@ -184,7 +193,7 @@ def tune(model: TunedModel, sequences: list, teachers: list, o: E2EOptions, held
     def evaluate(step):
         model.eval()
         with torch.no_grad():
-            kl = sum(float(kl_teacher(model(sequences[i]), teachers[i].to(model.devices[-1])))
+            kl = sum(float(kl_teacher(model(sequences[i]), _to(teachers[i], model.devices[-1])))
                      for i in range(len(sequences) - held_out, len(sequences))) / max(1, held_out)
         hist["eval"].append((step, kl))
         log(f"step {step}: held-out KL {kl:.6f}")
@@ -198,7 +207,7 @@ def tune(model: TunedModel, sequences: list, teachers: list, o: E2EOptions, held
         total = 0.0
         for b in range(o.batch):
             i = train[(step * o.batch + b) % len(train)]
-            loss = kl_teacher(model(sequences[i]), teachers[i].to(model.devices[-1])) / o.batch
+            loss = kl_teacher(model(sequences[i]), _to(teachers[i], model.devices[-1])) / o.batch
             loss.backward()
             total += float(loss.detach())
         opt.step()
@@ -237,6 +246,8 @@ def main(argv=None) -> int:
             teachers = [teacher(s).cpu() for s in seqs]
     else:
         teachers = torch.load(a.teacher, weights_only=True)
+        if isinstance(teachers, dict):                   # the top-K teacher of volta_ppl
+            teachers = list(zip(teachers["ids"], teachers["logp"], teachers["tail"]))
     o = E2EOptions(a.steps, a.batch, a.lr, a.warmup, a.lr_min, a.eval_every, bool(a.norms), devices)
     hist = tune(tm, seqs, teachers, o)
     out = Path(a.out) / ".partial"
