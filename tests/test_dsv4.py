@@ -1,0 +1,222 @@
+"""DeepSeek-V4-style attention pieces: the fp32 statement against direct arithmetic (CPU) and the kernels against the
+statement (GPU)."""
+import math
+
+import pytest
+import torch
+
+from volta_engine_b200.ops import dsv4 as V
+
+
+def _rows(n, start=0, slot=0, device="cpu"):
+    return (torch.full((n,), slot, dtype=torch.int32, device=device),
+            torch.arange(start, start + n, dtype=torch.int32, device=device))
+
+
+def _fill(st, device, n=300, seed=0, ratio_src=((0, 2), (1, 1))):
+    """Runs the cache writes of ``n`` positions in two chunks for layer 0 and both sources; returns the inputs."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    rope = V.rope_table(1024, 160000.0, 256, 16.0, device=device)
+    kv = (torch.randn(n, V.HD, generator=g) * 1.5).to(bf).to(device)
+    ckv = (torch.randn(n, V.HD, generator=g)).to(bf).to(device)
+    csc = (torch.randn(n, V.HD, generator=g) * 2).to(bf).to(device)
+    cw = (1 + 0.1 * torch.randn(V.HD, generator=g)).to(bf).to(device)
+    kw = (1 + 0.1 * torch.randn(V.IDX_DIM, generator=g)).to(bf).to(device)
+    wk = (torch.randn(V.IDX_DIM, V.HD, generator=g) / math.sqrt(V.HD)).to(device)
+    lat = {}
+    for lo, hi in ((0, 201), (201, n)):
+        slot, pos = _rows(hi - lo, lo, device=device)
+        V.window_store(st, 0, kv[lo:hi], rope, slot, pos)
+        for src in range(len(st.ratios)):
+            latent = V.compress(st, src, ckv[lo:hi], csc[lo:hi], cw, rope, slot, pos, 1e-6)
+            lat.setdefault(src, []).append(latent)
+            kraw = (latent.float() @ wk.t()).to(bf)
+            V.index_key_store(st, src, kraw, kw, rope, slot, pos, 1e-6)
+    return rope, kv, ckv, csc, cw, {s: torch.cat(v) for s, v in lat.items()}
+
+
+def test_grids_and_rotation_round_trips():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(7, 512, generator=g) * 3
+    codes, exps = V.mxfp8_quant(x)
+    back = V.mxfp8_dequant(codes, exps)
+    assert float((back - x).abs().max() / x.abs().max()) < 0.07 and torch.equal(V.mxfp8_round(back), back)   # idempotent
+    assert int(exps.min()) >= 100 and int(exps.max()) <= 127                                                    # 2^e <= 1 here
+    pk, sc = V.nvfp4_quant16(x)
+    b4 = V.nvfp4_dequant16(pk, sc)
+    assert pk.shape == (7, 256) and sc.shape == (7, 32) and float((b4 - x).norm() / x.norm()) < 0.12
+    m4 = V.mxfp4_round(x)
+    assert torch.equal(V.mxfp4_round(m4), m4) and torch.equal(m4.to(torch.bfloat16).float(), m4)               # exact in bf16
+    assert torch.equal(back.to(torch.bfloat16).float(), back) and torch.equal(b4.to(torch.bfloat16).float(), b4)
+    assert V.e2m1_round(torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.26])).tolist() == [0, 1, 1, 2, 2, 4, 4, -0.5]
+    assert V.pow2_ceil(torch.tensor([1.0, 1.1, 0.5, 0.3])).tolist() == [1.0, 2.0, 0.5, 0.5]
+    rope = V.rope_table(64, 10000.0)
+    y = V.rope_tail(V.rope_tail(x, rope[5]), rope[5], inverse=True)
+    assert torch.allclose(y, x, atol=1e-5) and torch.equal(V.rope_tail(x, rope[0]), x)
+    yarn = V.rope_table(8, 160000.0, 65536, 16.0)
+    plain = V.rope_table(8, 160000.0)
+    assert torch.allclose(yarn[:, 0], plain[:, 0], atol=1e-6) and not torch.allclose(yarn[:, -1], plain[:, -1])
+
+
+def test_cache_writes_pooling_and_indexer_selection():
+    st = V.DSV4State(1, 1, [(0, 2), (1, 1)], 512, "cpu")
+    rope, kv, ckv, csc, cw, lat = _fill(st, "cpu")
+    # window ring: position p sits at p % RING with the roped value on the grid
+    p = 250
+    row = st.win[0, 0, p]
+    want = V.mxfp8_round(V.rope_tail(kv[p].float(), rope[p]).to(torch.bfloat16).float())
+    assert torch.equal(V.mxfp8_dequant(row[:512], row[512:]), want)
+    # ratio 2: entry j pools positions 2j, 2j+1 with the per-dim softmax of the scores, normalises, ropes at 2j
+    j = 77
+    wgt = torch.softmax(csc[2 * j: 2 * j + 2].float(), dim=0)
+    pooled = (ckv[2 * j: 2 * j + 2].float() * wgt).sum(0).to(torch.bfloat16).float()
+    latent = (pooled * torch.rsqrt(pooled.pow(2).mean() + 1e-6) * cw.float()).to(torch.bfloat16).float()
+    assert torch.equal(lat[0][2 * j + 1].float(), latent) and float(lat[0][2 * j].abs().max()) == 0
+    ent = st.comp[0][0, j]
+    got = V.nvfp4_dequant16(ent[:256], ent[256:])
+    want = V.rope_tail(latent, rope[2 * j]).to(torch.bfloat16).float()
+    assert float((got - want).norm() / want.norm()) < 0.12
+    assert float(st.comp[0][0, 150:].abs().sum()) == 0 and float(st.idxk[0][0, 149].abs().sum()) > 0      # 300 tokens -> 150 entries
+    # ratio 1: every position has an entry
+    assert float(st.idxk[1][0, 299].abs().sum()) > 0 and float(st.idxk[1][0, 300:].abs().sum()) == 0
+    # indexer: few entries -> all of them; many -> the 512 best by the brute-force score, ascending
+    g = torch.Generator().manual_seed(3)
+    st2 = V.DSV4State(1, 1, [(0, 1)], 2048, "cpu")
+    st2.idxk[0][0] = V.mxfp4_round(torch.randn(2048, 128, generator=g)).to(torch.bfloat16)
+    q = (torch.randn(3, 32 * 128, generator=g)).to(torch.bfloat16)
+    w = torch.randn(3, 32, generator=g).abs()
+    slot = torch.zeros(3, dtype=torch.int32)
+    pos = torch.tensor([99, 1499, 2047], dtype=torch.int32)
+    rope2 = V.rope_table(2048, 160000.0)
+    qi = V.index_queries(q, rope2, pos)
+    sel, nsel = V.indexer(st2, 0, qi, w, slot, pos)
+    assert nsel.tolist() == [100, 512, 512] and sel[0, :100].tolist() == list(range(100))
+    sc = V.index_scores_reference(st2, 0, qi, w, slot, pos)[1]
+    best = set(torch.topk(sc, 512).indices.tolist())
+    assert set(sel[1].tolist()) == best and sel[1].tolist() == sorted(sel[1].tolist())
+    # candidate blocks: level one keeps the best blocks (and the newest), level two only picks inside them
+    sel1, _ = V.indexer(st2, 0, qi, w, slot, pos, cand_mode=1, cand_blocks=40, cand_block=8)
+    keep = V.candidate_blocks_reference(sc, 40, 8)
+    assert int(keep.sum()) == 40 and bool(keep[(1500 - 1) // 8])
+    assert all(bool(keep[i // 8]) for i in sel1[1, : int(_[1])].tolist()) and int(_[1]) == 316     # 39 full blocks + the newest, half-filled one
+    sel2, n2 = V.indexer(st2, 0, qi, w * 0 + 1, slot, pos, cand_mode=2, cand_blocks=40, cand_block=8)
+    assert all(bool(keep[i // 8]) for i in sel2[1, : int(n2[1])].tolist())
+
+
+def test_attention_matches_a_direct_softmax_with_sink():
+    st = V.DSV4State(1, 1, [(0, 2)], 512, "cpu")
+    rope, kv, *_ = _fill(st, "cpu", ratio_src=((0, 2),))
+    g = torch.Generator().manual_seed(5)
+    nh = 8
+    q = torch.randn(2, nh * 512, generator=g).to(torch.bfloat16)
+    sink = torch.randn(nh, generator=g)
+    slot = torch.zeros(2, dtype=torch.int32)
+    pos = torch.tensor([60, 299], dtype=torch.int32)
+    st.sel = (torch.tensor([[3, 9] + [0] * 510, [1, 50, 120] + [0] * 509], dtype=torch.int32), torch.tensor([2, 3], dtype=torch.int32))
+    out = V.attend(st, 0, 0, q, sink, rope, slot, pos, nh)
+    assert out.shape == (1, 2, 8 * 512)
+    # direct: row 1 sees positions 172..299 of the ring and entries 1, 50, 120
+    r = 1
+    rows = st.win[0, 0, 172:300]
+    keys = V.mxfp8_dequant(rows[:, :512].contiguous(), rows[:, 512:].contiguous())
+    ent = st.comp[0][0, [1, 50, 120]]
+    keys = torch.cat((keys, V.nvfp4_dequant16(ent[:, :256].contiguous(), ent[:, 256:].contiguous())))
+    qv = V.rope_tail(q[r].float().reshape(nh, 512), rope[299][None]).to(torch.bfloat16).float()
+    logits = torch.cat((qv @ keys.t() / math.sqrt(512), sink[:, None]), 1)
+    pr = torch.softmax(logits, -1)[:, :-1]
+    o = V.rope_tail((pr @ keys).to(torch.bfloat16).float(), rope[299][None], inverse=True).to(torch.bfloat16).float()
+    want = V.mxfp8_round(o).reshape(1, 8 * 512)
+    assert torch.allclose(out[:, r].float(), want, atol=2e-2, rtol=2e-2)
+    # the window floor hides older ring entries; row 0 (61 positions) ignores entries beyond its list
+    out2 = V.attend(st, 0, 0, q, sink, rope, slot, pos, nh, win_floor=290)
+    assert not torch.allclose(out2[:, 1].float(), out[:, 1].float(), atol=1e-3)
+    # sqrt-softplus routing and the engram gate
+    lg = torch.randn(4, 16, generator=g)
+    ids, w = V.route_sqrt_softplus(lg, torch.zeros(16), 3, 1.5)
+    s = torch.nn.functional.softplus(lg).sqrt()
+    assert torch.equal(ids.long().sort(-1).values, s.topk(3).indices.sort(-1).values) and torch.allclose(w.sum(-1), torch.full((4,), 1.5))
+    xs = torch.randn(3, 4, 64, generator=g)
+    kvr = torch.randn(3, 5 * 64, generator=g).to(torch.bfloat16)
+    before = xs.clone()
+    V.engram_gate(xs, kvr, torch.ones(4, 64), skip=torch.tensor([0, 1, 0], dtype=torch.uint8))
+    assert torch.equal(xs[1], before[1]) and not torch.equal(xs[0], before[0])
+    delta = (xs[0] - before[0]) / kvr[0, 256:].float()[None]
+    assert float(delta.std(dim=1).max()) < 1e-3 and 0 < float(delta.min()) and float(delta.max()) < 1      # one gate per stream
+
+
+@pytest.mark.gpu
+def test_dsv4_kernels_match_the_statement():
+    dev = torch.device("cuda:0")
+    srcs = [(0, 2), (1, 1)]
+    a, b = V.DSV4State(1, 1, srcs, 512, "cpu"), V.DSV4State(1, 1, srcs, 512, dev)
+    rope, kv, ckv, csc, cw, lat_c = _fill(a, "cpu")
+    rope_g, *_, lat_g = _fill(b, dev)
+    torch.cuda.synchronize()
+    # window ring: bytes equal
+    assert torch.equal(b.win.cpu()[0, 0, :300], a.win[0, 0, :300])
+    # latents and compressed entries: rsqrt / exp differ in the last ulp, so almost all codes agree
+    for s in (0, 1):
+        lc, lg = lat_c[s].float(), lat_g[s].float().cpu()
+        assert float((lc - lg).abs().max()) <= 0.02 * float(lc.abs().max())
+        n = 300 // a.ratios[s]
+        ca, cb = a.comp[s][0, :n], b.comp[s].cpu()[0, :n]
+        assert float((ca != cb).float().mean()) < 0.01
+        da = V.nvfp4_dequant16(ca[:, :256].contiguous(), ca[:, 256:].contiguous())
+        db = V.nvfp4_dequant16(cb[:, :256].contiguous(), cb[:, 256:].contiguous())
+        assert float((da - db).norm() / da.norm()) < 0.02
+        ka, kb = a.idxk[s][0, :n].float(), b.idxk[s].cpu()[0, :n].float()
+        assert float((ka != kb).float().mean()) < 0.02 and float((ka - kb).norm() / ka.norm()) < 0.05
+    # indexer on identical keys: same queries, same selection
+    g = torch.Generator().manual_seed(3)
+    keys = V.mxfp4_round(torch.randn(2048, 128, generator=g)).to(torch.bfloat16)
+    q = torch.randn(4, 32 * 128, generator=g).to(torch.bfloat16)
+    w = torch.randn(4, 32, generator=g).abs()
+    slot = torch.tensor([0, 0, -1, 0], dtype=torch.int32)
+    pos = torch.tensor([99, 1499, 7, 2047], dtype=torch.int32)
+    ropel = V.rope_table(2048, 160000.0)
+    res = {}
+    for d in ("cpu", dev):
+        st = V.DSV4State(1, 1, [(0, 1)], 2048, d)
+        st.idxk[0][0] = keys.to(d)
+        qi = V.index_queries(q.to(d), ropel.to(d), pos.to(d))
+        plain = V.indexer(st, 0, qi, w.to(d), slot.to(d), pos.to(d))
+        l1 = V.indexer(st, 0, qi, w.to(d), slot.to(d), pos.to(d), cand_mode=1, cand_blocks=40, cand_block=8)
+        l2 = V.indexer(st, 0, qi, (w * 0 + 1).to(d), slot.to(d), pos.to(d), cand_mode=2, cand_blocks=40, cand_block=8)
+        res[d] = (qi.cpu(), [(s.cpu(), n.cpu()) for s, n in (plain, l1, l2)])
+    assert torch.equal(res["cpu"][0], res[dev][0])
+    for (sc, nc), (sg, ng) in zip(res["cpu"][1], res[dev][1]):
+        assert nc.tolist() == ng.tolist()
+        for r in (0, 1, 3):
+            got, want = set(sg[r, : int(ng[r])].tolist()), set(sc[r, : int(nc[r])].tolist())
+            assert len(got ^ want) <= 4 and sg[r, : int(ng[r])].tolist() == sorted(sg[r, : int(ng[r])].tolist())
+    # attention: the scratch-page path against the statement on the same caches
+    nh = 16
+    q = torch.randn(3, nh * 512, generator=g).to(torch.bfloat16)
+    sink = torch.randn(nh, generator=g)
+    slot = torch.tensor([0, -1, 0], dtype=torch.int32)
+    pos = torch.tensor([60, 5, 299], dtype=torch.int32)
+    sel = torch.zeros(3, 512, dtype=torch.int32)
+    sel[0, :2] = torch.tensor([3, 9])
+    sel[2, :140] = torch.arange(140)
+    nsel = torch.tensor([2, 0, 140], dtype=torch.int32)
+    a.sel, b.sel = (sel, nsel), (sel.to(dev), nsel.to(dev))
+    b.comp[0].copy_(a.comp[0])
+    b.win.copy_(a.win)
+    want = V.attend(a, 0, 0, q, sink, rope, slot, pos, nh)
+    got = V.attend(b, 0, 0, q.to(dev), sink.to(dev), rope_g, slot.to(dev), pos.to(dev), nh).cpu()
+    for r in (0, 2):
+        cos = torch.nn.functional.cosine_similarity(got[:, r].float().flatten(), want[:, r].float().flatten(), dim=0)
+        assert float(cos) > 0.999, (r, float(cos))
+        assert float((got[:, r].float() - want[:, r].float()).abs().max()) < 0.05 * float(want[:, r].float().abs().max()) + 1e-3
+    # window-only layer (no compressed entries) and the engram gate
+    want = V.attend(a, 0, -1, q, sink, rope, slot, pos, nh)
+    got = V.attend(b, 0, -1, q.to(dev), sink.to(dev), rope_g, slot.to(dev), pos.to(dev), nh).cpu()
+    assert float(torch.nn.functional.cosine_similarity(got[:, 2].float().flatten(), want[:, 2].float().flatten(), dim=0)) > 0.999
+    xs = torch.randn(5, 4, 256, generator=g)
+    kvr = torch.randn(5, 5 * 256, generator=g).to(torch.bfloat16)
+    wv = torch.randn(4, 256, generator=g)
+    skip = torch.tensor([0, 1, 0, 0, 0], dtype=torch.uint8)
+    want = V.engram_gate(xs.clone(), kvr, wv, skip)
+    got = V.engram_gate(xs.clone().to(dev), kvr.to(dev), wv.to(dev), skip.to(dev)).cpu()
+    assert torch.allclose(got, want, atol=2e-3, rtol=1e-3)

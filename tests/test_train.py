@@ -152,16 +152,17 @@ def test_hessian_accumulator_gpu():
 
 
 @pytest.mark.gpu
-def test_model_hessian_capture_gpu_matches_cpu_capture():
+def test_model_hessian_capture_gpu_matches_cpu_capture(tmp_path):
     """The capture taps of the dense model on the device (tcgen05 x^T x) against the same model's capture on the CPU."""
-    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.models.dense import DenseConfig
+    from volta_engine_b200.models.factory import load_model, save_dense_checkpoint
     from volta_engine_b200.runtime.engine import Engine
     from volta_engine_b200.runtime.kv_cache import PagedKVCache
     cfg = DenseConfig.tiny(n_layers=2)
+    save_dense_checkpoint(tmp_path / "m", cfg, seed=4, fmt="bf16", std=0.05)
     sums = {}
     for dev in ("cpu", "cuda"):
-        m = DenseModel(cfg, dev)
-        m.init_random(seed=4)
+        m, _ = load_model(tmp_path / "m", dev)
         hs = m.enable_hessians()
         kv = PagedKVCache(cfg.n_layers, cfg.n_kv, cfg.head_dim, 8, 1, 256, dev)
         Engine(m, kv, use_graphs=False, prefill_chunk=128).generate(list(range(3, 99)), 2)

@@ -83,7 +83,7 @@ template <int HEADS>
 __global__ void __launch_bounds__(256) dsa_score_kernel(const __nv_bfloat16* __restrict__ q_idx, const float* __restrict__ w,
                                                         const __nv_bfloat16* __restrict__ pool_plane, float* __restrict__ scores,
                                                         long score_stride, const int* __restrict__ slot,
-                                                        const int* __restrict__ pos, long pool_slot_stride) {
+                                                        const int* __restrict__ pos, long pool_slot_stride, int div) {
   constexpr int LDQ = kDsaDim + 8;
   constexpr int MT = (HEADS + 15) / 16, HP = MT * 16;
   __shared__ __align__(16) __nv_bfloat16 sq[HP * LDQ];
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) dsa_score_kernel(const __nv_bfloat16* __r
   const int r = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sl = slot[r];
   if (sl < 0) return;
-  const int bound = (pos[r] + 1) / kDsaPool;
+  const int bound = (pos[r] + 1) / div;   // div: tokens per key entry (4 for the pooled indexers)
   if (blockIdx.x * 64 >= bound) return;
   for (int i = tid; i < HP * kDsaDim; i += 256) {
     const int h = i / kDsaDim;
@@ -359,18 +359,36 @@ int ve_dsa_pool_update(const void* plane, void* pool_plane, const void* ape, con
 }
 
 // heads = 32 with head weights w (pooled-key indexer) or 4 with w == nullptr (block-sparse indexer)
+static int dsa_score_launch(const void* q_idx, const void* w, const void* pool_plane, void* scores, long score_stride,
+                            const void* slot, const void* pos, long pool_slot_stride, int rows, int max_pools, int heads, int div,
+                            cudaStream_t st);
+
 int ve_dsa_score(const void* q_idx, const void* w, const void* pool_plane, void* scores, long score_stride, const void* slot,
                  const void* pos, long pool_slot_stride, int rows, int max_pools, int heads, cudaStream_t st) {
+  return dsa_score_launch(q_idx, w, pool_plane, scores, score_stride, slot, pos, pool_slot_stride, rows, max_pools, heads,
+                          kDsaPool, st);
+}
+
+// The same score with one key entry per `div` tokens (1, 2, ...): entries below (pos + 1) / div are scored.
+int ve_dsa_score_div(const void* q_idx, const void* w, const void* pool_plane, void* scores, long score_stride, const void* slot,
+                     const void* pos, long pool_slot_stride, int rows, int max_pools, int heads, int div, cudaStream_t st) {
+  if (div < 1) return cudaErrorInvalidValue;
+  return dsa_score_launch(q_idx, w, pool_plane, scores, score_stride, slot, pos, pool_slot_stride, rows, max_pools, heads, div, st);
+}
+
+static int dsa_score_launch(const void* q_idx, const void* w, const void* pool_plane, void* scores, long score_stride,
+                            const void* slot, const void* pos, long pool_slot_stride, int rows, int max_pools, int heads, int div,
+                            cudaStream_t st) {
   if (rows <= 0 || max_pools <= 0) return 0;
   const dim3 grid((max_pools + 63) / 64, rows);
   if (heads == kDsaHeads)
     dsa_score_kernel<kDsaHeads><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q_idx, (const float*)w,
                                                       (const __nv_bfloat16*)pool_plane, (float*)scores, score_stride,
-                                                      (const int*)slot, (const int*)pos, pool_slot_stride);
+                                                      (const int*)slot, (const int*)pos, pool_slot_stride, div);
   else if (heads == kQsaHeads)
     dsa_score_kernel<kQsaHeads><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q_idx, (const float*)w,
                                                       (const __nv_bfloat16*)pool_plane, (float*)scores, score_stride,
-                                                      (const int*)slot, (const int*)pos, pool_slot_stride);
+                                                      (const int*)slot, (const int*)pos, pool_slot_stride, div);
   else
     return cudaErrorInvalidValue;
   VE_CHECK_LAUNCH();

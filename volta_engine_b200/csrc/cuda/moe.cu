@@ -4,6 +4,7 @@
 // Router semantics (reference: src/backend/cuda/modules/moe.cu:297-384, inc/engine/modules/moe.h:80-96):
 //   softmax form  top-k of the raw logits, weights = softmax over the chosen logits only;
 //   sigmoid form  s = sigmoid(logit); choose top-k of s + bias; weights = s_k * scale / (sum of chosen s + 1e-9);
+//   sqrt-softplus form (mode 2, inc/engine/modules/dsv4.h: route)  s = sqrt(softplus(logit)), otherwise as the sigmoid form;
 //   ties go to the lowest expert index. Group-limited routing (DeepSeek-V3 style, absent from the reference):
 //   experts are split into n_group groups, a group's score is the sum of its two best biased scores, only the
 //   topk_group best groups stay eligible.
@@ -57,7 +58,8 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
   const float* row = logits + blockIdx.x * stride;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const float l = row[e];
-    const float s = mode == 1 ? 1.f / (1.f + __expf(-l)) : l;
+    // mode 2: sqrt(softplus(l)), softplus written so that large |l| neither overflows nor cancels
+    const float s = mode == 1 ? 1.f / (1.f + __expf(-l)) : mode == 2 ? sqrtf(fmaxf(l, 0.f) + log1pf(__expf(-fabsf(l)))) : l;
     s_raw[e] = s;
     s_sel[e] = s + (bias ? bias[e] : 0.f);
   }

@@ -76,7 +76,7 @@ class ExpertBank:
 def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | None):
     """fp32 statement of the router (see csrc/cuda/moe.cu): -> (ids [rows, k] int32, weights [rows, k] fp32)."""
     lf = logits.float()
-    s = torch.sigmoid(lf) if cfg.router == "sigmoid" else lf
+    s = torch.sigmoid(lf) if cfg.router == "sigmoid" else torch.nn.functional.softplus(lf).sqrt() if cfg.router == "sqrtsoftplus" else lf
     sel = s + (bias.float() if bias is not None else 0.0)
     rows, E = sel.shape
     if cfg.n_group > 1:
@@ -88,7 +88,7 @@ def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | N
         sel = torch.where(keep[:, :, None].expand_as(g), g, torch.full_like(g, float("-inf"))).reshape(rows, E)
     order = torch.sort(sel, dim=-1, descending=True, stable=True).indices[:, : cfg.top_k]
     chosen = s.gather(1, order)
-    if cfg.router == "sigmoid":
+    if cfg.router in ("sigmoid", "sqrtsoftplus"):
         w = chosen * cfg.router_scale / (chosen.sum(-1, keepdim=True) + 1e-9)
     else:
         w = torch.softmax(chosen, dim=-1) * cfg.router_scale
@@ -236,7 +236,7 @@ class MoEModel(DenseModel):
         ids = torch.empty(rows, k, dtype=torch.int32, device=x.device)
         w = torch.empty(rows, k, dtype=torch.float32, device=x.device)
         call("router_select", "pliiiipfiippp", ptr(logits), logits.stride(0), rows, cfg.n_experts, k,
-             1 if cfg.router == "sigmoid" else 0, ptr(L.router_bias), float(cfg.router_scale), cfg.n_group,
+             {"sigmoid": 1, "sqrtsoftplus": 2}.get(cfg.router, 0), ptr(L.router_bias), float(cfg.router_scale), cfg.n_group,
              cfg.topk_group, ptr(ids), ptr(w), self.heat[li].data_ptr() if self.heat is not None else 0)
         routes = rows * k
         rec = getattr(self, "route_recorder", None)
