@@ -295,3 +295,31 @@ def test_dsv4_model_gpu_matches_cpu_and_graph_replay():
     e_eager = Engine(m6, kv6, use_graphs=False, prefill_chunk=64)
     bb, _ = e_eager.generate(toks[:50], 12)
     assert a == bb
+
+
+def test_dsv41_config_parsing_and_synthetic_directory(tmp_path):
+    import json
+    from volta_engine_b200.models.factory import dsv4_config_from_hf, load_model
+    official = {"model_type": "deepseek_v41", "n_layers": 40, "dim": 5120, "n_heads": 64, "n_routed_experts": 384,
+                "n_activated_experts": 6, "moe_inter_dim": 2304, "score_func": "sqrtsoftplus", "route_scale": 1.5, "q_lora_rank": 1280,
+                "o_groups": 8, "o_lora_rank": 1024, "kv_source_layers": [2, 8, 14, 20], "index_source_layers": [2, 8, 14, 20, 24, 28, 32, 36],
+                "candidate_source_layer": 20, "compress_ratios": [0, 0] + [2] * 18 + [1] * 20 + [0, 0, 0], "engram_layer_ids": [1, 14],
+                "norm_eps": 1e-20, "compress_rope_theta": 160000, "original_seq_len": 65536}
+    cfg = dsv4_config_from_hf(official)
+    from volta_engine_b200.models.dsv4 import DSV4Config
+    ref = DSV4Config.baseline_dsv41()
+    for k in ("n_layers", "hidden", "n_q", "n_experts", "top_k", "expert_ffn", "compress_ratios", "kv_sources", "index_sources",
+              "candidate_source", "engram_layers", "router", "rms_eps"):
+        assert getattr(cfg, k) == getattr(ref, k), k
+    tiny = {"model_type": "deepseek_v41", "synthetic_weights": 3, "n_layers": 3, "dim": 256, "n_heads": 16, "n_routed_experts": 4,
+            "n_activated_experts": 2, "moe_inter_dim": 128, "q_lora_rank": 128, "o_groups": 2, "o_lora_rank": 128, "vocab_size": 512,
+            "compress_ratios": [0, 2, 2], "kv_source_layers": [1], "index_source_layers": [1], "norm_eps": 1e-6}
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(tiny))
+    m, hf = load_model(d, "cpu")
+    assert type(m).__name__ == "DSV4Model" and len(m.layers) == 3 and m.layers[2].kv_src == 0
+    del tiny["synthetic_weights"]
+    (d / "config.json").write_text(json.dumps(tiny))
+    with pytest.raises(NotImplementedError):
+        load_model(d, "cpu")

@@ -161,6 +161,8 @@ def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantiz
     if "text_config" in hf and "num_hidden_layers" not in hf:
         hf = dict(hf["text_config"], **{k: v for k, v in hf.items() if k != "text_config"})
     mt = hf.get("model_type", "")
+    if mt == "deepseek_v41":
+        return load_dsv41(hf, d, device, comm), hf
     src = TensorSource(d, prefer)
     if mt in DENSE_TYPES:
         cfg = dense_config_from_hf(hf)
@@ -171,6 +173,43 @@ def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantiz
         from .moe_loader import load_moe_family
         return load_moe_family(hf, src, device, comm, gemm_mode, quantize), hf
     raise NotImplementedError(f"model_type {mt!r} has no pipeline in this build")
+
+
+def dsv4_config_from_hf(c: dict):
+    """DeepSeek-V4.1 ``config.json`` (the official inference configuration's names) -> DSV4Config.
+    Reference: src/models/deepseek_v41.cpp:439-489 (``read_config``: the same keys, the implemented layout checked)."""
+    from .dsv4 import DSV4Config
+    n = int(c.get("n_layers", c.get("num_hidden_layers", 40)))
+    ratios = tuple(c.get("compress_ratios", ()))[:n] or (0,) * n
+    return DSV4Config(
+        n_layers=n, hidden=int(c.get("dim", c.get("hidden_size", 5120))), n_q=int(c.get("n_heads", 64)), n_kv=1,
+        head_dim=int(c.get("head_dim", 512)), ffn=0, vocab=int(c.get("vocab_size", 129280)),
+        n_experts=int(c.get("n_routed_experts", 384)), top_k=int(c.get("n_activated_experts", 6)),
+        expert_ffn=int(c.get("moe_inter_dim", 2304)), shared_ffn=int(c.get("moe_inter_dim", 2304)) * int(c.get("n_shared_experts", 1)),
+        router=c.get("score_func", "sqrtsoftplus"), router_scale=float(c.get("route_scale", 1.5)),
+        act_limit=float(c.get("swiglu_limit", 10.0)), rms_eps=float(c.get("norm_eps", 1e-20)),
+        rope_theta=float(c.get("rope_theta", 10000.0)), hc_sinkhorn=int(c.get("hc_sinkhorn_iters", 20)),
+        hc_eps=float(c.get("hc_eps", 1e-6)), q_lora_rank=int(c.get("q_lora_rank", 1280)), o_groups=int(c.get("o_groups", 8)),
+        o_lora_rank=int(c.get("o_lora_rank", 1024)), compress_ratios=ratios,
+        kv_sources=tuple(c.get("kv_source_layers", ())), index_sources=tuple(c.get("index_source_layers", ())),
+        candidate_source=int(c.get("candidate_source_layer", -1)), candidate_blocks=int(c.get("candidate_topk_blocks", 2048)),
+        candidate_block=int(c.get("candidate_block_size", 8)), compress_rope_theta=float(c.get("compress_rope_theta", 160000.0)),
+        rope_original_len=int(c.get("original_seq_len", 65536)), rope_factor=float(c.get("rope_factor", 16.0)),
+        beta_fast=float(c.get("beta_fast", 32.0)), beta_slow=float(c.get("beta_slow", 1.0)),
+        engram_layers=tuple(c.get("engram_layer_ids", ())), engram_dim=int(c.get("engram_n_heads", 8)) * int(c.get("engram_head_dim", 256)),
+        engram_rows=int(c.get("engram_table_rows", 1 << 16)), engram_ngram=int(c.get("engram_max_ngram_size", 4)))
+
+
+def load_dsv41(hf: dict, model_dir: Path, device, comm):
+    """A DeepSeek-V4.1 directory. Only the synthetic form is built: ``config.json`` with ``"synthetic_weights": <seed>``
+    and no tensor files gives the architecture with random weights (benchmarks, tests); the tensor-name mapping of the
+    published FP8 / FP4 checkpoint is not."""
+    from .dsv4 import DSV4Model
+    cfg = dsv4_config_from_hf(hf)
+    if "synthetic_weights" not in hf:
+        raise NotImplementedError("deepseek_v41: loading checkpoint tensors is not built (config.json with "
+                                  "\"synthetic_weights\": <seed> runs the architecture with random weights)")
+    return DSV4Model(cfg, device, comm).init_random(seed=int(hf["synthetic_weights"]))
 
 
 def save_dense_checkpoint(model_dir, cfg: DenseConfig, seed: int = 0, std: float = 0.02, fmt: str = "bf16",
