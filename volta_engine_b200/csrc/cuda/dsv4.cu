@@ -392,11 +392,15 @@ __global__ void __launch_bounds__(256) dsv4_gather_kernel(const uint8_t* __restr
                                                           const int* __restrict__ sel, const int* __restrict__ nsel,
                                                           const int* __restrict__ slot, const int* __restrict__ pos,
                                                           __nv_bfloat16* __restrict__ pages, int* __restrict__ nkeys,
-                                                          int win_floor) {
+                                                          int* __restrict__ v_pos, int* __restrict__ v_slot, int win_floor) {
   const int r = blockIdx.y, i = blockIdx.x * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63;
   const int sl = slot[r];
   if (sl < 0) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) nkeys[r] = 1;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      nkeys[r] = 1;
+      v_pos[r] = 0;
+      v_slot[r] = -1;
+    }
     return;
   }
   const int p = pos[r];
@@ -404,7 +408,11 @@ __global__ void __launch_bounds__(256) dsv4_gather_kernel(const uint8_t* __restr
   const int nwin = max(0, p + 1 - lo);
   const int ns = (comp && sel) ? nsel[r] : 0;
   const int total = nwin + ns + 1;
-  if (blockIdx.x == 0 && threadIdx.x == 0) nkeys[r] = total;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {   // the row's virtual sequence: slot r of the scratch table, last position total - 1
+    nkeys[r] = total;
+    v_pos[r] = total - 1;
+    v_slot[r] = r;
+  }
   if (i >= total) return;
   __nv_bfloat16* dst = pages + (((long)r * kPagesRow + i / 64) * 64 + i % 64) * kLatRowD;
   const int d = 8 * l;
@@ -497,6 +505,44 @@ __global__ void __launch_bounds__(128) dsv4_attn_out_kernel(const __nv_bfloat16*
 #pragma unroll
   for (int j = 0; j < 4; ++j)
     dst[j] = __float2bfloat16_rn(ldexpf(e4m3_dec(e4m3_enc(fminf(fmaxf(ldexpf(v[j], -e), -448.f), 448.f))), e));
+}
+
+// ------------------------------------------------------------------------------------------------ grouped wo_a
+// out[row][g * O + r] = sum_d o[g][row][d] * w[g][r][d] for decode rows (rows <= 16): one warp per (g, r) reads its weight
+// row once and keeps one accumulator per row. grid (groups * O / 8), block 256. K = 8 heads * 512.
+__global__ void __launch_bounds__(256) dsv4_woa_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ w,
+                                                       __nv_bfloat16* __restrict__ out, int groups, int O, int rows) {
+  constexpr int KD = kGroupHeads * kHD;
+  const int lane = threadIdx.x & 31, gr = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (gr >= groups * O) return;
+  const int g = gr / O;
+  const __nv_bfloat16* wr = w + (long)gr * KD;
+  float acc[16];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) acc[n] = 0.f;
+  for (int d = lane * 8; d < KD; d += 256) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(wr + d);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      if (n < rows) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(o + ((long)g * rows + n) * KD + d);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(w2[j]), b = __bfloat1622float2(x2[j]);
+          acc[n] += a.x * b.x + a.y * b.y;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {
+    if (n < rows) {
+      const float v = warp_sum(acc[n]);
+      if (lane == 0) out[(long)n * groups * O + gr] = __float2bfloat16_rn(v);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ engram gate
@@ -599,13 +645,14 @@ int ve_dsv4_select(const void* scores, long score_stride, const void* cand, long
 }
 
 int ve_dsv4_gather(const void* win, int layer, long win_slot_stride, const void* comp, long comp_slot_stride, const void* sel,
-                   const void* nsel, const void* slot, const void* pos, void* pages, void* nkeys, int win_floor, int rows,
-                   cudaStream_t st) {
+                   const void* nsel, const void* slot, const void* pos, void* pages, void* nkeys, void* v_pos, void* v_slot,
+                   int win_floor, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
   dsv4_gather_kernel<<<dim3((kKeysMax + 3) / 4, rows), 256, 0, st>>>((const uint8_t*)win, layer, win_slot_stride,
                                                                      (const uint8_t*)comp, comp_slot_stride, (const int*)sel,
                                                                      (const int*)nsel, (const int*)slot, (const int*)pos,
-                                                                     (__nv_bfloat16*)pages, (int*)nkeys, win_floor);
+                                                                     (__nv_bfloat16*)pages, (int*)nkeys, (int*)v_pos,
+                                                                     (int*)v_slot, win_floor);
   VE_CHECK_LAUNCH();
 }
 
@@ -622,6 +669,14 @@ int ve_dsv4_attn_out(const void* o_lat, void* out, const void* rope, const void*
   if (rows <= 0) return 0;
   dsv4_attn_out_kernel<<<dim3(rows, heads), 128, 0, st>>>((const __nv_bfloat16*)o_lat, (__nv_bfloat16*)out, (const float*)rope,
                                                           (const int*)pos, (const int*)slot, heads, rows);
+  VE_CHECK_LAUNCH();
+}
+
+int ve_dsv4_woa(const void* o, const void* w, void* out, int groups, int O, int rows, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (rows > 16) return cudaErrorInvalidValue;
+  dsv4_woa_kernel<<<(groups * O + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, groups,
+                                                        O, rows);
   VE_CHECK_LAUNCH();
 }
 

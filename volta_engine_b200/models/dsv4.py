@@ -137,7 +137,7 @@ class DSV4Model(MoEModel):
         L.q_proj = self._make_linear(wqb.contiguous(), search)
         L.sink = (torch.randn(cfg.n_q, generator=torch.Generator().manual_seed(li + 7)) * 0.5)[r * hl:(r + 1) * hl].to(dev).contiguous()
         woa = rnd(cfg.o_groups * cfg.o_lora_rank, V.GROUP_HEADS * V.HD).reshape(cfg.o_groups, cfg.o_lora_rank, -1)
-        L.wo_a = [LinearBF16(woa[r * gl + g].to(bf).contiguous()) for g in range(gl)]
+        L.wo_a = woa[r * gl:(r + 1) * gl].to(bf).contiguous()          # [groups, o_lora, 8 * 512]: block diagonal over the groups
         wob = rnd(H, cfg.o_groups * cfg.o_lora_rank)
         L.wo_b = self._make_linear(wob[:, r * gl * cfg.o_lora_rank:(r + 1) * gl * cfg.o_lora_rank].contiguous(), search)
         L.c_norm = L.idx_wk = L.idx_knorm = None
@@ -152,7 +152,7 @@ class DSV4Model(MoEModel):
                         "index": cfg.engram_layers.index(li)}
 
     def _attn_bytes(self, L) -> int:
-        return L.x_proj.nbytes() + L.q_proj.nbytes() + L.wo_b.nbytes() + sum(w.nbytes() for w in L.wo_a)
+        return L.x_proj.nbytes() + L.q_proj.nbytes() + L.wo_b.nbytes() + L.wo_a.numel() * 2
 
     def init_random(self, seed: int = 5, std: float = 0.02, search: bool = False):
         super().init_random(seed, std, search)
@@ -267,5 +267,4 @@ class DSV4Model(MoEModel):
             V.indexer(st, src, qi, wi, b.slot, b.pos, mode, cfg.candidate_blocks, cfg.candidate_block)
         nsplit = 1 if b.n > 16 else max(1, min(8, b.nsplit))
         o = V.attend(st, li, src, q, L.sink, rope, b.slot, b.pos, self.heads, self.attn_ws2, nsplit=nsplit)
-        low = torch.cat([L.wo_a[g].forward(o[g]) for g in range(self.groups)], 1)
-        return L.wo_b.forward(low, out=pbuf)
+        return L.wo_b.forward(V.grouped_out_proj(o, L.wo_a), out=pbuf)

@@ -339,12 +339,13 @@ def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Ten
             cap = max(16, rows)
             st.scratch = (torch.zeros(cap * PAGES_PER_ROW, 1, 64, LAT_ROW, dtype=torch.bfloat16, device=q.device),
                           torch.arange(cap * PAGES_PER_ROW, dtype=torch.int32, device=q.device).reshape(cap, PAGES_PER_ROW).contiguous(),
-                          torch.arange(cap, dtype=torch.int32, device=q.device),
+                          torch.zeros(cap, dtype=torch.int32, device=q.device),
+                          torch.zeros(cap, dtype=torch.int32, device=q.device),
                           torch.zeros(cap, dtype=torch.int32, device=q.device))
-        pages, table, ar, nkeys = st.scratch
+        pages, table, a_slot, nkeys, a_pos = st.scratch
         comp = st.comp[src] if sel is not None else None
-        call("dsv4_gather", "pilplppppppii", ptr(st.win), layer, st.win.stride(0), ptr(comp), comp.stride(0) if comp is not None else 0,
-             ptr(sel), ptr(nsel), ptr(slot), ptr(pos), ptr(pages), ptr(nkeys), win_floor, rows)
+        call("dsv4_gather", "pilplppppppppii", ptr(st.win), layer, st.win.stride(0), ptr(comp), comp.stride(0) if comp is not None else 0,
+             ptr(sel), ptr(nsel), ptr(slot), ptr(pos), ptr(pages), ptr(nkeys), ptr(a_pos), ptr(a_slot), win_floor, rows)
         q_abs = torch.empty(rows, nh, LAT_ROW, dtype=torch.bfloat16, device=q.device)
         call("dsv4_q_prep", "plppppifi", ptr(q), q.stride(0), ptr(q_abs), ptr(sink), ptr(rope), ptr(pos), nh, float(scale), rows)
         o_lat = torch.empty(rows, nh, HD, dtype=torch.bfloat16, device=q.device)
@@ -353,8 +354,6 @@ def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Ten
             ws = (torch.empty(rows * nh * HD, dtype=torch.float32, device=q.device),
                   torch.empty(rows * nh, dtype=torch.float32, device=q.device))
         from .kernels import status_word
-        a_pos = nkeys[:rows] - 1
-        a_slot = torch.where(slot < 0, slot, ar[:rows])
         call("mla_decode", "pppppppipliiifp", ptr(q_abs), ptr(o_lat), ptr(ws[0]), ptr(ws[1]), ptr(a_pos), ptr(a_slot), ptr(table),
              table.shape[1], ptr(pages), pages.shape[0], rows, nh, nsplit, float(scale), ptr(status_word(q.device)))
         call("dsv4_attn_out", "pppppii", ptr(o_lat), ptr(out), ptr(rope), ptr(pos), ptr(slot), nh, rows)
@@ -375,6 +374,20 @@ def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Ten
         o = mxfp8_round(o).to(torch.bfloat16)
         out[:, r] = o.reshape(groups, GROUP_HEADS * HD)
     return out
+
+
+def grouped_out_proj(o: torch.Tensor, woa: torch.Tensor) -> torch.Tensor:
+    """o [groups, rows, 8 * 512] bf16, woa [groups, O, 8 * 512] bf16 -> [rows, groups * O]: every group's heads through its own
+    low-rank projection (block diagonal). Decode rows run one kernel; larger chunks one batched product."""
+    groups, rows, _ = o.shape
+    O = woa.shape[1]
+    if o.is_cuda and rows <= 16:
+        out = torch.empty(rows, groups * O, dtype=torch.bfloat16, device=o.device)
+        call("dsv4_woa", "pppiii", ptr(o), ptr(woa), ptr(out), groups, O, rows)
+        return out
+    if o.is_cuda:
+        return torch.bmm(o, woa.transpose(1, 2)).permute(1, 0, 2).reshape(rows, groups * O).contiguous()
+    return torch.einsum("grd,god->rgo", o.float(), woa.float()).to(torch.bfloat16).reshape(rows, groups * O)
 
 
 # ------------------------------------------------------------------------------------------------ routing

@@ -28,6 +28,10 @@ TABLE = {
     "mla_expand_out": ("MLALatent", P),
     "dsa_prep": ("DSA", P), "dsa_pool_update": ("DSA", P), "dsa_score": ("DSA / QSA", P), "dsa_select": ("DSA / QSA", P),
     "dsa_gather": ("DSA / QSA", P), "dsa_kpad": ("DSA / QSA", D), "qsa_prep": ("QSA", P), "qsa_pool_update": ("QSA", P),
+    "dsa_score_div": ("DSA / QSA", P),
+    "dsv4_window_store": ("DSV4", P), "dsv4_cring_store": ("DSV4", P), "dsv4_compress": ("DSV4", P),
+    "dsv4_index_key_store": ("DSV4", P), "dsv4_index_q": ("DSV4", P), "dsv4_candidates": ("DSV4", P), "dsv4_select": ("DSV4", P),
+    "dsv4_gather": ("DSV4", D), "dsv4_q_prep": ("DSV4", D), "dsv4_attn_out": ("DSV4", P), "dsv4_woa": ("DSV4", P), "dsv4_engram_gate": ("Engram", P),
     "router_select": ("MoERouter", P), "nvfp4_moe_gemv": ("MoE", P), "moe_combine": ("MoE", P), "moe_sort": ("MoE", P),
     "moe_gather": ("MoE", P), "cpu_post": ("CpuExperts", D), "cpu_wait_add": ("CpuExperts", D),
     "cpu_mailbox_bytes": ("CpuExperts", D),
