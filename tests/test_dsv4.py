@@ -323,3 +323,18 @@ def test_dsv41_config_parsing_and_synthetic_directory(tmp_path):
     (d / "config.json").write_text(json.dumps(tiny))
     with pytest.raises(NotImplementedError):
         load_model(d, "cpu")
+
+
+@pytest.mark.gpu
+def test_engram_ids_kernel_matches_the_statement():
+    g = torch.Generator().manual_seed(4)
+    res = {}
+    for dev in ("cpu", "cuda"):
+        hist = torch.zeros(3, 256, dtype=torch.int32, device=dev)
+        outs = []
+        for ids, slot, pos in ((torch.arange(100, 140), torch.zeros(40), torch.arange(40)),
+                               (torch.tensor([7, 9, 11]), torch.tensor([0, 1, -1]), torch.tensor([40, 0, 5]))):
+            outs.append(V.engram_ids(ids.int().to(dev), slot.int().to(dev), pos.int().to(dev), hist, 2, 512, 4).cpu())
+        res[dev] = (torch.cat(outs), hist.cpu())
+    assert torch.equal(res["cpu"][0], res["cuda"][0]) and torch.equal(res["cpu"][1], res["cuda"][1])
+    assert int(res["cpu"][0].min()) >= 0 and int(res["cpu"][0].max()) < 512 and len(set(res["cpu"][0][:, 0].tolist())) > 30

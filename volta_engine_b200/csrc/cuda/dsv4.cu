@@ -545,6 +545,30 @@ __global__ void __launch_bounds__(256) dsv4_woa_kernel(const __nv_bfloat16* __re
   }
 }
 
+// ------------------------------------------------------------------------------------------------ engram ids
+// One block (rows <= 1024): every row records its token in the per-slot history, then hashes the last `ngram` tokens of its
+// sequence into one table row per engram layer. Positions before the sequence start count as token 2 (the pad id).
+__global__ void __launch_bounds__(1024) dsv4_engram_ids_kernel(const int* __restrict__ ids, const int* __restrict__ slot,
+                                                               const int* __restrict__ pos, int* __restrict__ hist, long hist_stride,
+                                                               int spare_slot, int* __restrict__ out, int tables, int table_rows,
+                                                               int ngram, int rows) {
+  const int r = threadIdx.x;
+  int sl = 0, p = 0;
+  if (r < rows) {
+    sl = slot[r] < 0 ? spare_slot : slot[r];
+    p = pos[r];
+    hist[(long)sl * hist_stride + p] = ids[r];
+  }
+  __syncthreads();
+  if (r >= rows) return;
+  long long h = 0;
+  for (int j = 0; j < ngram; ++j) {
+    const long long t = p - j >= 0 ? (long long)hist[(long)sl * hist_stride + (p - j)] : 2ll;
+    h = (h * 1000003ll + t * (2 * j + 1) + 12345ll) % 2147483647ll;
+  }
+  for (int i = 0; i < tables; ++i) out[(long)r * tables + i] = (int)((h * (2 * i + 3) + i) % table_rows);
+}
+
 // ------------------------------------------------------------------------------------------------ engram gate
 // grid (rows, hc), block 256. kv [rows, (hc + 1) * H] = [key 0..hc-1 | value]; streams fp32 [rows, hc, H] in place.
 __global__ void __launch_bounds__(256) dsv4_engram_gate_kernel(float* __restrict__ streams, const __nv_bfloat16* __restrict__ kv,
@@ -677,6 +701,15 @@ int ve_dsv4_woa(const void* o, const void* w, void* out, int groups, int O, int 
   if (rows > 16) return cudaErrorInvalidValue;
   dsv4_woa_kernel<<<(groups * O + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, groups,
                                                         O, rows);
+  VE_CHECK_LAUNCH();
+}
+
+int ve_dsv4_engram_ids(const void* ids, const void* slot, const void* pos, void* hist, long hist_stride, int spare_slot, void* out,
+                       int tables, int table_rows, int ngram, int rows, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (rows > 1024 || tables < 1 || table_rows < 1) return cudaErrorInvalidValue;
+  dsv4_engram_ids_kernel<<<1, 1024, 0, st>>>((const int*)ids, (const int*)slot, (const int*)pos, (int*)hist, hist_stride, spare_slot,
+                                             (int*)out, tables, table_rows, ngram, rows);
   VE_CHECK_LAUNCH();
 }
 

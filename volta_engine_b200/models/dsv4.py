@@ -181,26 +181,6 @@ class DSV4Model(MoEModel):
     def ensure_workspace(self, max_rows: int, max_splits: int):
         return None
 
-    def engram_ids(self, b: BatchRows) -> torch.Tensor | None:
-        """Hashed n-gram row of every (row, engram layer): a multiplicative hash of the last ``engram_ngram`` token ids of the
-        row's sequence. Tokens before the chunk come from the per-slot history that ``forward`` keeps."""
-        cfg = self.cfg
-        if not cfg.engram_layers:
-            return None
-        n, ng = b.n, cfg.engram_ngram
-        hist = self._history
-        ids = b.ids.long()
-        h = torch.zeros(n, dtype=torch.long, device=ids.device)
-        # the rows of a batch are consecutive positions of one slot (prefill chunk) or one row per slot (decode):
-        # the preceding tokens are read from the history written just before this call
-        pos, slot = b.pos.long(), b.slot.long().clamp_min(0)
-        for j in range(ng):
-            t = hist[slot, (pos - j).clamp_min(0)]
-            t = torch.where(pos - j >= 0, t, torch.full_like(t, 2))
-            h = (h * 1000003 + t * (2 * j + 1) + 12345) % 2147483647
-        out = torch.stack([(h * (2 * i + 3) + i) % cfg.engram_rows for i in range(len(cfg.engram_layers))], 1)
-        return out
-
     # ------------------------------------------------------------------------------------------ forward
     def forward(self, b: BatchRows, kv) -> torch.Tensor | None:
         cfg, comm = self.cfg, self.comm
@@ -209,11 +189,9 @@ class DSV4Model(MoEModel):
         eps = cfg.rms_eps
         if cfg.engram_layers:
             if getattr(self, "_history", None) is None:
-                # one spare row takes the writes of padding rows (slot < 0), so the update needs no data-dependent shape
-                self._history = torch.zeros(kv.max_slots + 1, kv.max_pages * 64, dtype=torch.long, device=self.device)
-            hs = torch.where(b.slot < 0, torch.full_like(b.slot, kv.max_slots), b.slot).long()
-            self._history[hs, b.pos.long()] = b.ids.long()
-            eids = self.engram_ids(b)
+                # token history per slot (one spare row takes the writes of padding rows, slot < 0)
+                self._history = torch.zeros(kv.max_slots + 1, kv.max_pages * 64, dtype=torch.int32, device=self.device)
+            eids = V.engram_ids(b.ids, b.slot, b.pos, self._history, len(cfg.engram_layers), cfg.engram_rows, cfg.engram_ngram).long()
         xs = S.init_streams(K.embed(b.ids, self.embed, scale=cfg.embed_scale), 4)
         pre = torch.zeros(b.n, 4, dtype=torch.float32, device=self.device)
         pre[:, 0] = 1.0

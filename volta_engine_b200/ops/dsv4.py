@@ -277,8 +277,9 @@ def indexer(st: DSV4State, src: int, qi: torch.Tensor, w: torch.Tensor, slot, po
     state); 2: entries outside the stored blocks do not compete. -> (sel [rows, TOPK] int32 ascending, nsel [rows])."""
     rows = qi.shape[0]
     ratio = st.ratios[src]
-    sel = torch.zeros(rows, TOPK, dtype=torch.int32, device=qi.device)
-    nsel = torch.zeros(rows, dtype=torch.int32, device=qi.device)
+    alloc = torch.empty if qi.is_cuda else torch.zeros          # the kernels write every entry that is read afterwards
+    sel = alloc(rows, TOPK, dtype=torch.int32, device=qi.device)
+    nsel = alloc(rows, dtype=torch.int32, device=qi.device)
     cap = st.caps[src]
     nblk = (cap + cand_block - 1) // cand_block
     if qi.is_cuda:
@@ -286,7 +287,7 @@ def indexer(st: DSV4State, src: int, qi: torch.Tensor, w: torch.Tensor, slot, po
         call("dsa_score_div", "pppplppliiii", ptr(qi), ptr(w), ptr(st.idxk[src]), ptr(scores), scores.stride(0), ptr(slot), ptr(pos),
              st.idxk[src].stride(0), rows, cap, IDX_HEADS, ratio)
         if cand_mode == 1:
-            st.cand = torch.zeros(rows, nblk, dtype=torch.uint8, device=qi.device)
+            st.cand = torch.empty(rows, nblk, dtype=torch.uint8, device=qi.device)
             call("dsv4_candidates", "plplppiiii", ptr(scores), scores.stride(0), ptr(st.cand), st.cand.stride(0), ptr(slot), ptr(pos),
                  ratio, cand_blocks, cand_block, rows)
         use_cand = cand_mode in (1, 2) and st.cand is not None and st.cand.shape[0] == rows
@@ -401,6 +402,30 @@ def route_sqrt_softplus(logits: torch.Tensor, bias, top_k: int, scale: float):
 
 
 # ------------------------------------------------------------------------------------------------ engram
+def engram_ids(ids, slot, pos, hist: torch.Tensor, tables: int, table_rows: int, ngram: int) -> torch.Tensor:
+    """Records the rows' tokens in ``hist`` int32 [slots + 1, max_seq] (the last row takes padding rows) and returns the hashed
+    table row of every (row, engram layer) int32 [rows, tables]: h = fold over the last ``ngram`` tokens of the sequence
+    (token 2 before its start) of (h * 1000003 + t * (2 j + 1) + 12345) mod (2^31 - 1); row_i = (h * (2 i + 3) + i) mod rows."""
+    n = ids.shape[0]
+    spare = hist.shape[0] - 1
+    out = torch.empty(n, tables, dtype=torch.int32, device=ids.device)
+    if ids.is_cuda:
+        call("dsv4_engram_ids", "pppplipiiii", ptr(ids), ptr(slot), ptr(pos), ptr(hist), hist.stride(0), spare, ptr(out), tables,
+             table_rows, ngram, n)
+        return out
+    sl = torch.where(slot < 0, torch.full_like(slot, spare), slot).long()
+    p = pos.long()
+    hist[sl, p] = ids.int()
+    h = torch.zeros(n, dtype=torch.long)
+    for j in range(ngram):
+        t = hist[sl, (p - j).clamp_min(0)].long()
+        t = torch.where(p - j >= 0, t, torch.full_like(t, 2))
+        h = (h * 1000003 + t * (2 * j + 1) + 12345) % 2147483647
+    for i in range(tables):
+        out[:, i] = ((h * (2 * i + 3) + i) % table_rows).int()
+    return out
+
+
 def engram_gate(streams: torch.Tensor, kv: torch.Tensor, w: torch.Tensor, skip=None, eps: float = 1e-20) -> torch.Tensor:
     """streams fp32 [rows, 4, H] (in place), kv [rows, 5 * H] = [key 0..3 | value] of the looked-up rows, w [4, H] fp32:
     dot = sum_d s[h][d] w[h][d] key[h][d] * rstd(s[h]) * rstd(key[h]) / sqrt(H); gate = sigmoid(sign(dot) sqrt(max(|dot|, 1e-6)));

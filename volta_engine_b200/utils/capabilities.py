@@ -31,7 +31,7 @@ TABLE = {
     "dsa_score_div": ("DSA / QSA", P),
     "dsv4_window_store": ("DSV4", P), "dsv4_cring_store": ("DSV4", P), "dsv4_compress": ("DSV4", P),
     "dsv4_index_key_store": ("DSV4", P), "dsv4_index_q": ("DSV4", P), "dsv4_candidates": ("DSV4", P), "dsv4_select": ("DSV4", P),
-    "dsv4_gather": ("DSV4", D), "dsv4_q_prep": ("DSV4", D), "dsv4_attn_out": ("DSV4", P), "dsv4_woa": ("DSV4", P), "dsv4_engram_gate": ("Engram", P),
+    "dsv4_gather": ("DSV4", D), "dsv4_q_prep": ("DSV4", D), "dsv4_attn_out": ("DSV4", P), "dsv4_woa": ("DSV4", P), "dsv4_engram_gate": ("Engram", P), "dsv4_engram_ids": ("Engram", P),
     "router_select": ("MoERouter", P), "nvfp4_moe_gemv": ("MoE", P), "moe_combine": ("MoE", P), "moe_sort": ("MoE", P),
     "moe_gather": ("MoE", P), "cpu_post": ("CpuExperts", D), "cpu_wait_add": ("CpuExperts", D),
     "cpu_mailbox_bytes": ("CpuExperts", D),
