@@ -338,3 +338,14 @@ def test_engram_ids_kernel_matches_the_statement():
         res[dev] = (torch.cat(outs), hist.cpu())
     assert torch.equal(res["cpu"][0], res["cuda"][0]) and torch.equal(res["cpu"][1], res["cuda"][1])
     assert int(res["cpu"][0].min()) >= 0 and int(res["cpu"][0].max()) < 512 and len(set(res["cpu"][0][:, 0].tolist())) > 30
+
+
+@pytest.mark.gpu
+def test_grouped_output_projection_kernel():
+    g = torch.Generator().manual_seed(8)
+    woa = (torch.randn(2, 128, 8 * 512, generator=g) * 0.02).to(torch.bfloat16)
+    for rows in (1, 3, 9, 16, 40):
+        o = torch.randn(2, rows, 8 * 512, generator=g).to(torch.bfloat16)
+        want = V.grouped_out_proj(o, woa).float()
+        got = V.grouped_out_proj(o.cuda(), woa.cuda()).float().cpu()
+        assert got.shape == (rows, 256) and torch.allclose(got, want, atol=2e-2, rtol=2e-2), rows

@@ -510,6 +510,7 @@ __global__ void __launch_bounds__(128) dsv4_attn_out_kernel(const __nv_bfloat16*
 // ------------------------------------------------------------------------------------------------ grouped wo_a
 // out[row][g * O + r] = sum_d o[g][row][d] * w[g][r][d] for decode rows (rows <= 16): one warp per (g, r) reads its weight
 // row once and keeps one accumulator per row. grid (groups * O / 8), block 256. K = 8 heads * 512.
+template <int RB>
 __global__ void __launch_bounds__(256) dsv4_woa_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ w,
                                                        __nv_bfloat16* __restrict__ out, int groups, int O, int rows) {
   constexpr int KD = kGroupHeads * kHD;
@@ -517,27 +518,33 @@ __global__ void __launch_bounds__(256) dsv4_woa_kernel(const __nv_bfloat16* __re
   if (gr >= groups * O) return;
   const int g = gr / O;
   const __nv_bfloat16* wr = w + (long)gr * KD;
-  float acc[16];
+  float acc[RB];
 #pragma unroll
-  for (int n = 0; n < 16; ++n) acc[n] = 0.f;
-  for (int d = lane * 8; d < KD; d += 256) {
-    const uint4 wv = *reinterpret_cast<const uint4*>(wr + d);
-    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+  for (int n = 0; n < RB; ++n) acc[n] = 0.f;
+  // four 16-byte weight loads in flight per lane before the first use (the weight stream is the only DRAM traffic)
+  for (int d0 = lane * 8; d0 < KD; d0 += 1024) {
+    uint4 wv[4];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      if (n < rows) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(o + ((long)g * rows + n) * KD + d);
-        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    for (int u = 0; u < 4; ++u) wv[u] = __ldg(reinterpret_cast<const uint4*>(wr + d0 + u * 256));
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 a = __bfloat1622float2(w2[j]), b = __bfloat1622float2(x2[j]);
-          acc[n] += a.x * b.x + a.y * b.y;
+    for (int u = 0; u < 4; ++u) {
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+#pragma unroll
+      for (int n = 0; n < RB; ++n) {
+        if (n < rows) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(o + ((long)g * rows + n) * KD + d0 + u * 256);
+          const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 a = __bfloat1622float2(w2[j]), b = __bfloat1622float2(x2[j]);
+            acc[n] += a.x * b.x + a.y * b.y;
+          }
         }
       }
     }
   }
 #pragma unroll
-  for (int n = 0; n < 16; ++n) {
+  for (int n = 0; n < RB; ++n) {
     if (n < rows) {
       const float v = warp_sum(acc[n]);
       if (lane == 0) out[(long)n * groups * O + gr] = __float2bfloat16_rn(v);
@@ -699,8 +706,11 @@ int ve_dsv4_attn_out(const void* o_lat, void* out, const void* rope, const void*
 int ve_dsv4_woa(const void* o, const void* w, void* out, int groups, int O, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (rows > 16) return cudaErrorInvalidValue;
-  dsv4_woa_kernel<<<(groups * O + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, groups,
-                                                        O, rows);
+  const int grid = (groups * O + 7) / 8;
+  const __nv_bfloat16 *op = (const __nv_bfloat16*)o, *wp = (const __nv_bfloat16*)w;
+  if (rows <= 1) dsv4_woa_kernel<1><<<grid, 256, 0, st>>>(op, wp, (__nv_bfloat16*)out, groups, O, rows);
+  else if (rows <= 4) dsv4_woa_kernel<4><<<grid, 256, 0, st>>>(op, wp, (__nv_bfloat16*)out, groups, O, rows);
+  else dsv4_woa_kernel<16><<<grid, 256, 0, st>>>(op, wp, (__nv_bfloat16*)out, groups, O, rows);
   VE_CHECK_LAUNCH();
 }
 

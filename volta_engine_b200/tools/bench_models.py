@@ -51,6 +51,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--chunk", type=int, default=512)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart / Stop (for a profiler started with capture off)")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("volta_bench_models: needs a GPU", file=sys.stderr)
@@ -76,12 +78,16 @@ def main(argv=None) -> int:
         tok = eng.step([tok], [pos], [0])[0]
         pos += 1
     torch.cuda.synchronize()
+    if a.profiler_range:
+        torch.cuda.profiler.start()
     t0.record()
     for _ in range(a.steps):
         tok = eng.step([tok], [pos], [0])[0]
         pos += 1
     t1.record()
     torch.cuda.synchronize()
+    if a.profiler_range:
+        torch.cuda.profiler.stop()
     ms = t0.elapsed_time(t1) / a.steps
     print(json.dumps({"family": a.family, "layers": a.layers, "experts": a.experts, "prompt": a.prompt, "graphs": not a.no_graphs,
                       "decode_tok_s": round(1e3 / ms, 2), "ms_per_step": round(ms, 4), "ms_per_layer": round(ms / a.layers, 4),
