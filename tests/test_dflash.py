@@ -179,3 +179,89 @@ def test_drafter_rounds_on_gpu_equal_plain_greedy():
     g.drafter = D.DFlashRunner(eng2, dc)
     spec = g.generate(Request(p, max_tokens=16, cache_prefix=False))
     assert spec["tokens"] == plain["tokens"] and g.metrics.spec["rounds"] > 0
+
+
+def test_sparse_head_policy_subset_hysteresis_and_persistence(tmp_path):
+    from volta_engine_b200.runtime.sparse_head_policy import SparseHeadParams, SparseHeadPolicy
+    p = SparseHeadPolicy(1000, SparseHeadParams(capacity=8, interval=16, decay_tokens=64, min_evidence=10.0, min_change=0.25,
+                                                full_probe_rounds=5))
+    assert not p.rebuild_due() and not p.use_sparse()
+    p.observe_prompt([1, 2, 3, 1, 2000, -1])                   # out-of-range ids are ignored, prompt tokens weigh 0.2
+    assert abs(float(p.counts[1]) - 0.4) < 1e-6 and abs(p.evidence - 1.2) < 1e-6
+    for t in [5] * 6 + [6] * 4 + [7] * 3 + list(range(20, 30)):
+        p.observe_generated(t)
+    assert p.rebuild_due()
+    first = p.ranked()
+    assert first[:3] == [5, 6, 7] and len(first) == 8 and first[3:] == [20, 21, 22, 23, 24]     # ties to the lower id
+    p.set_subset(first)
+    assert p.built and p.subset_n == 8
+    # an incumbent keeps its place until a challenger beats its count by the margin
+    p.observe_generated(25)                                     # 25: 2.0, incumbent 24: 1.0 -> replaced (2.0 > 1.25)
+    assert 25 in p.ranked() and 24 not in p.ranked()
+    for t in (26, 24):                                          # 26: 2.0 against incumbents 23 / 24 ...
+        p.observe_generated(t)
+    assert 24 in p.ranked()                                     # 24: 2.0 * 1.25 stays ahead of the challengers at 2.0
+    # miss rate: plain mean at first (3 tokens scored: 25 miss, 26 miss, 24 hit)
+    assert abs(p.miss - 2 / 3) < 1e-9 and p.scored == 3
+    # use: needs timings and MIN_SCORED tokens; below the break-even miss rate the sparse head is on, with hysteresis
+    for _ in range(70):
+        p.observe_generated(5)
+    assert not p.use_sparse()                                   # no full-head timing yet
+    p.draft_step_time(False, 2.0)
+    assert p.use_sparse() and p.on                              # measures the sparse steps once
+    p.draft_step_time(True, 0.5)
+    p.round_time(10.0, 4)
+    assert abs(p.breakeven() - 2 * 1.5 * 4 / 10.0) < 1e-9
+    p.miss = 0.5
+    assert p.use_sparse()
+    p.miss = 1.5                                                # above 1.2 x break-even (1.44): off
+    assert not p.use_sparse() and not p.on
+    p.miss = 1.0                                                # between 0.8x and 1.2x: stays off
+    assert not p.use_sparse()
+    p.miss = 0.9
+    assert p.use_sparse()
+    seen = [p.use_sparse() for _ in range(6)]                   # every fifth sparse round is a full probe, the mode stays on
+    assert seen.count(False) == 1 and p.on
+    # rebuild again only after the interval and when enough of the subset would change
+    p.since_rebuild = 0
+    assert not p.rebuild_due()
+    for t in range(100, 116):
+        for _ in range(4):
+            p.observe_generated(t)
+    assert p.rebuild_due()
+    # decay halves the counts
+    c5 = float(p.counts[5])
+    p.since_decay = p.p.decay_tokens - 1
+    p.observe_generated(999)
+    assert abs(float(p.counts[5]) - c5 / 2) < 1e-4
+    # persistence: counts survive, another vocabulary is refused
+    path = tmp_path / "sparse.bin"
+    assert p.save(path)
+    q = SparseHeadPolicy(1000)
+    assert q.load(path) and abs(q.evidence - p.evidence) < 1e-9 and (q.counts == p.counts).all()
+    assert not SparseHeadPolicy(999).load(path) and not q.load(tmp_path / "absent.bin")
+
+
+def test_candidate_log_and_target_spool_round_trip(tmp_path):
+    from volta_engine_b200.runtime.spec_logs import CandLog, TargetSpool, read_cand_log
+    log = CandLog()
+    log.round(0, 1, 2, 3, [])                                    # closed: nothing happens
+    assert not log.on() and log.open(tmp_path / "cand.bin") and log.on()
+    log.round(1, 40, 7, 7, [(11, 11, [0.5, 0.25], [11, 12]), (13, 14, list(range(20)), list(range(100, 120)))])
+    log.request(1, [1, 2, 3, 11, 14])
+    log.flush()
+    log.close()
+    recs = read_cand_log(tmp_path / "cand.bin")
+    assert [r["kind"] for r in recs] == ["round", "request"] and recs[1]["tokens"] == [1, 2, 3, 11, 14]
+    r0 = recs[0]
+    assert (r0["slot"], r0["pos"], r0["anchor"], r0["active"]) == (1, 40, 7, 7) and len(r0["rows"]) == 2
+    assert r0["rows"][0]["ids"][:3] == [11, 12, -1] and r0["rows"][0]["vals"][1] == 0.25 and r0["rows"][0]["vals"][2] == float("-inf")
+    assert r0["rows"][1]["ids"] == list(range(100, 116)) and (r0["rows"][1]["chosen"], r0["rows"][1]["target"]) == (13, 14)
+    sp = TargetSpool()
+    sp.add(0, 5, [1.0], [3])
+    assert sp.take(0) == []                                       # off by default
+    sp.enable()
+    sp.add(0, 5, [1.0, 0.5], [3, 4])
+    sp.add(1, 9, [2.0], [8])
+    sp.add(0, 6, [0.1], [2])
+    assert [r[0] for r in sp.take(0)] == [5, 6] and sp.take(0) == [] and sp.take(1) == [(9, [2.0], [8])]

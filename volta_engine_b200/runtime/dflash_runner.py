@@ -23,7 +23,7 @@ from .._lib import call, ptr
 from ..models.dense import DenseConfig, DenseModel
 from ..ops import kernels as K
 from ..ops.linear import LinearBF16
-from .batch import BatchRows, LOGITS_ALL
+from .batch import BatchRows, LOGITS_ALL, LOGITS_NONE
 from .kv_cache import PagedKVCache
 
 
@@ -98,6 +98,9 @@ class DFlashRunner:
         self.ctx_len = [0] * engine.kv.max_slots
         self.model.ensure_workspace(max(64, cfg.block_size), 8)
         self.stats = {"rounds": 0, "proposed": 0, "accepted": 0}
+        self.sparse_policy = None            # host policy of the sparse drafter head (enable_sparse_head)
+        self.sparse_head = None
+        self.sparse_state_path = None
 
     # ---- weights of a trained drafter: same tensor names as a dense decoder plus ``fc`` and ``hidden_norm``
     def load(self, src) -> None:
@@ -147,15 +150,56 @@ class DFlashRunner:
         ids = [anchor] + [cfg.mask_token_id] * (B - 1)
         b = BatchRows.make(ids, [pos + i for i in range(B)], [slot] * B, e.device, LOGITS_ALL, 1, nsplit=1)
         b.key_end = torch.full((B,), pos + B - 1, dtype=torch.int32, device=e.device)     # the block sees all of itself
-        logits = m.forward(b, self.kv)
+        import time
+        pol = self.sparse_policy
+        sparse = pol is not None and self.sparse_head is not None and pol.use_sparse()
+        t0 = time.perf_counter()
+        if sparse:                               # the block's hidden rows through the subset of head columns only
+            b.logits = LOGITS_NONE
+            m.forward(b, self.kv)
+            logits = self.sparse_head.logits(m.last_hidden)
+        else:
+            logits = m.forward(b, self.kv)
         if logits.is_cuda:
             idx, _ = K.argmax(logits, id_offset=e.comm.rank * m.vocab_local)
             idx = e.comm.merge_argmax(idx, _) if e.comm.size > 1 else idx
         else:
             idx = logits.float().argmax(-1)
         toks = [int(t) for t in idx.tolist()]
+        if pol is not None:                      # the token read above waited for the device: wall time is the step time
+            pol.draft_step_time(sparse, (time.perf_counter() - t0) * 1e3)
         n = B - 1 if depth is None else max(0, min(B - 1, depth))
         return toks[1:1 + n]
+
+    # ---- sparse drafter head: the policy counts tokens, proposes the column subset and decides per round whether to use it
+    def enable_sparse_head(self, params=None, state_path=None):
+        from .sparse_head_policy import SparseHeadPolicy
+        assert self.e.comm.size == 1, "the sparse drafter head is built for a single rank"
+        self.sparse_policy = SparseHeadPolicy(self.e.model.cfg.vocab, params)
+        self.sparse_state_path = state_path
+        if state_path:
+            self.sparse_policy.load(state_path)
+        return self.sparse_policy
+
+    def observe_prompt(self, tokens) -> None:
+        if self.sparse_policy is not None:
+            self.sparse_policy.observe_prompt(tokens)
+
+    def observe_commit(self, tokens) -> None:
+        """Committed output tokens: evidence for the subset, hits / misses of the current one; rebuilds when due."""
+        pol = self.sparse_policy
+        if pol is None:
+            return
+        for t in tokens:
+            pol.observe_generated(int(t))
+        if pol.rebuild_due():
+            cols = sorted(pol.ranked())
+            m = self.model
+            self.sparse_head = SparseHead.extract(m.lm_head, self.cfg.hidden, m.vocab_local,
+                                                  torch.tensor(cols, dtype=torch.int32, device=self.e.device))
+            pol.set_subset(cols)
+        if self.sparse_state_path and pol.save_due():
+            pol.save(self.sparse_state_path)
 
     def walk_candidates(self, unary, cands, gate, pred_cb, succ_cb, anchor):
         """Version 2 token choice: chained greedy walk over per-row candidate sets (top-k of the head) with the low-rank

@@ -493,6 +493,14 @@ class Generator:
             m["steps"][i]["hits"] += 1 if i < acc else 0
         if s.ctrl:
             s.ctrl.record_round(len(new), len(drafts), acc, ms)
+        if kind == "drafter" and self.drafter is not None and hasattr(self.drafter, "observe_commit"):
+            self.drafter.observe_commit(new)                       # sparse-head evidence, hits and misses
+            if self.drafter.sparse_policy is not None:
+                self.drafter.sparse_policy.round_time(ms, len(drafts))
+        log = getattr(self, "cand_log", None)
+        if log is not None and log.on() and kind == "drafter":
+            log.round(s.idx, s.pos - acc - 1, rows[0], len(drafts),
+                      [(drafts[i], toks[i], [0.0], [drafts[i]]) for i in range(min(acc + 1, len(drafts)))])
         self._emit(s, new)
         return len(new)
 
