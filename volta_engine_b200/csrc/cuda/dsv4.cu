@@ -392,7 +392,8 @@ __global__ void __launch_bounds__(256) dsv4_gather_kernel(const uint8_t* __restr
                                                           const int* __restrict__ sel, const int* __restrict__ nsel,
                                                           const int* __restrict__ slot, const int* __restrict__ pos,
                                                           __nv_bfloat16* __restrict__ pages, int* __restrict__ nkeys,
-                                                          int* __restrict__ v_pos, int* __restrict__ v_slot, int win_floor) {
+                                                          int* __restrict__ v_pos, int* __restrict__ v_slot, int win_floor,
+                                                          const int* __restrict__ key_end, int window) {
   const int r = blockIdx.y, i = blockIdx.x * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63;
   const int sl = slot[r];
   if (sl < 0) {
@@ -403,8 +404,10 @@ __global__ void __launch_bounds__(256) dsv4_gather_kernel(const uint8_t* __restr
     }
     return;
   }
-  const int p = pos[r];
-  const int lo = max(max(0, p - kWindow + 1), win_floor);
+  // the newest ring position the row may read (its own position unless the caller widens it, as a drafter block does
+  // whose rows all see the whole block) and how many positions back from there
+  const int p = key_end ? key_end[r] : pos[r];
+  const int lo = max(max(0, p - window + 1), win_floor);
   const int nwin = max(0, p + 1 - lo);
   const int ns = (comp && sel) ? nsel[r] : 0;
   const int total = nwin + ns + 1;
@@ -677,13 +680,14 @@ int ve_dsv4_select(const void* scores, long score_stride, const void* cand, long
 
 int ve_dsv4_gather(const void* win, int layer, long win_slot_stride, const void* comp, long comp_slot_stride, const void* sel,
                    const void* nsel, const void* slot, const void* pos, void* pages, void* nkeys, void* v_pos, void* v_slot,
-                   int win_floor, int rows, cudaStream_t st) {
+                   int win_floor, int rows, const void* key_end, int window, cudaStream_t st) {
   if (rows <= 0) return 0;
+  if (window < 1 || window + kSelTopk + 1 > kPagesRow * 64 || window > kRing) return cudaErrorInvalidValue;
   dsv4_gather_kernel<<<dim3((kKeysMax + 3) / 4, rows), 256, 0, st>>>((const uint8_t*)win, layer, win_slot_stride,
                                                                      (const uint8_t*)comp, comp_slot_stride, (const int*)sel,
                                                                      (const int*)nsel, (const int*)slot, (const int*)pos,
                                                                      (__nv_bfloat16*)pages, (int*)nkeys, (int*)v_pos,
-                                                                     (int*)v_slot, win_floor);
+                                                                     (int*)v_slot, win_floor, (const int*)key_end, window);
   VE_CHECK_LAUNCH();
 }
 

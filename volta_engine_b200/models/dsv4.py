@@ -98,6 +98,8 @@ class DSV4Model(MoEModel):
         self.rope_plain = self.rope_comp = None
         self.attn_ws2 = None
         self.engram_table = None
+        self.tap_ring = None             # a block drafter reads the stream mean at the entry of its target layers
+        self.block_keys = None           # (key_end [rows], window): a drafter block whose rows all see the whole block
 
     kv_layers = 1
 
@@ -199,6 +201,8 @@ class DSV4Model(MoEModel):
             if L.engram is not None:
                 rows = self.engram_table[L.engram["index"]][eids[:, L.engram["index"]]]
                 V.engram_gate(xs, L.engram["wkv"].forward(rows).contiguous(), L.engram["w"], None, eps)
+            if self.tap_ring is not None and li in self.tap_ring.index:
+                self.tap_ring.publish(li, S.head_mean(xs), b.pos, b.slot, b.n)
             fn, base, scale = L.attn_hc
             mix = S.hc_collapse(xs, fn, base, scale, cfg.hc_sinkhorn, cfg.hc_eps, rms_eps=eps, norm_w=L.attn_norm, norm_eps=eps,
                                 norm_bias=cfg.norm_bias, pre_in=pre)
@@ -213,7 +217,7 @@ class DSV4Model(MoEModel):
         fn, base, scale = self.layers[-1].mlp_hc           # only the collapse with the last pre-mix and the final norm are used
         x = S.hc_collapse(xs, fn, base, scale, 1, cfg.hc_eps, rms_eps=eps, norm_w=self.final_norm, norm_eps=eps,
                           norm_bias=cfg.norm_bias, pre_in=pre).collapsed
-        self.last_hidden, self.last_residual, self.last_streams = x, None, xs
+        self.last_hidden, self.last_residual, self.last_streams, self.last_pre = x, None, xs, pre
         if b.logits == LOGITS_NONE:
             return None
         if b.logits == LOGITS_LAST:
@@ -244,5 +248,6 @@ class DSV4Model(MoEModel):
             mode = 0 if cfg.candidate_source < 0 else 1 if li == cfg.candidate_source else 2 if li > cfg.candidate_source else 0
             V.indexer(st, src, qi, wi, b.slot, b.pos, mode, cfg.candidate_blocks, cfg.candidate_block)
         nsplit = 1 if b.n > 16 else max(1, min(8, b.nsplit))
-        o = V.attend(st, li, src, q, L.sink, rope, b.slot, b.pos, self.heads, self.attn_ws2, nsplit=nsplit)
+        ke, win = self.block_keys if self.block_keys is not None else (None, V.WINDOW)
+        o = V.attend(st, li, src, q, L.sink, rope, b.slot, b.pos, self.heads, self.attn_ws2, nsplit=nsplit, key_end=ke, window=win)
         return L.wo_b.forward(V.grouped_out_proj(o, L.wo_a), out=pbuf)

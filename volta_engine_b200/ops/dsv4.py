@@ -314,8 +314,9 @@ def indexer(st: DSV4State, src: int, qi: torch.Tensor, w: torch.Tensor, slot, po
 
 
 # ------------------------------------------------------------------------------------------------ attention
-def _row_keys_reference(st: DSV4State, layer: int, src: int, s: int, p: int, sel, nsel, r: int, win_floor: int):
-    lo = max(0, p - WINDOW + 1, win_floor)
+def _row_keys_reference(st: DSV4State, layer: int, src: int, s: int, p: int, sel, nsel, r: int, win_floor: int,
+                        window: int = WINDOW):
+    lo = max(0, p - window + 1, win_floor)
     at = [(t % RING) for t in range(lo, p + 1)]
     rows = st.win[s, layer, at]
     keys = mxfp8_dequant(rows[:, :HD].contiguous(), rows[:, HD:].contiguous()) if at else torch.zeros(0, HD)
@@ -326,10 +327,12 @@ def _row_keys_reference(st: DSV4State, layer: int, src: int, s: int, p: int, sel
 
 
 def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Tensor, rope, slot, pos, nh: int, ws=None,
-           win_floor: int = 0, nsplit: int = 1) -> torch.Tensor:
+           win_floor: int = 0, nsplit: int = 1, key_end=None, window: int = WINDOW) -> torch.Tensor:
     """q [rows, nh * 512] bf16 unrotated. Softmax over the window and (``src`` >= 0) the state's selected compressed entries,
     logits scaled by 512^-1/2, exp(sink[h]) added to the denominator; the output is inverse-roped at pos, put on the MXFP8
-    grid and returned group-major: [nh / 8, rows, 8 * 512] bf16."""
+    grid and returned group-major: [nh / 8, rows, 8 * 512] bf16. ``key_end`` [rows] (default: pos) is the newest ring position
+    a row reads and ``window`` how many positions back from there: a drafter block, whose rows all see the whole block on top
+    of the committed window, passes the block's last position and 128 + block size."""
     rows = q.shape[0]
     groups = nh // GROUP_HEADS
     scale = HD ** -0.5
@@ -345,8 +348,9 @@ def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Ten
                           torch.zeros(cap, dtype=torch.int32, device=q.device))
         pages, table, a_slot, nkeys, a_pos = st.scratch
         comp = st.comp[src] if sel is not None else None
-        call("dsv4_gather", "pilplppppppppii", ptr(st.win), layer, st.win.stride(0), ptr(comp), comp.stride(0) if comp is not None else 0,
-             ptr(sel), ptr(nsel), ptr(slot), ptr(pos), ptr(pages), ptr(nkeys), ptr(a_pos), ptr(a_slot), win_floor, rows)
+        call("dsv4_gather", "pilplppppppppiipi", ptr(st.win), layer, st.win.stride(0), ptr(comp), comp.stride(0) if comp is not None else 0,
+             ptr(sel), ptr(nsel), ptr(slot), ptr(pos), ptr(pages), ptr(nkeys), ptr(a_pos), ptr(a_slot), win_floor, rows,
+             ptr(key_end), window)
         q_abs = torch.empty(rows, nh, LAT_ROW, dtype=torch.bfloat16, device=q.device)
         call("dsv4_q_prep", "plppppifi", ptr(q), q.stride(0), ptr(q_abs), ptr(sink), ptr(rope), ptr(pos), nh, float(scale), rows)
         o_lat = torch.empty(rows, nh, HD, dtype=torch.bfloat16, device=q.device)
@@ -364,7 +368,7 @@ def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Ten
         s, p = int(slot[r]), int(pos[r])
         if s < 0:
             continue
-        keys = _row_keys_reference(st, layer, src, s, p, sel, nsel, r, win_floor)
+        keys = _row_keys_reference(st, layer, src, s, p if key_end is None else int(key_end[r]), sel, nsel, r, win_floor, window)
         if keys.shape[0] == 0:                                                  # only the sink: the output is zero
             continue
         sc = qv[r] @ keys.t() * scale                                           # [nh, keys]

@@ -132,6 +132,13 @@ def load_drafter(engine, draft_dir: str):
     from ..runtime.dflash_runner import DFlashConfig, DFlashRunner
     with open(os.path.join(draft_dir, "config.json")) as f:
         hf = json.load(f)
+    if hf.get("model_type") == "deepseek_v41":
+        # the DeepSeek-V4.1 drafter ("DSpark") is described by the trunk's own config keys; like the trunk, only the
+        # synthetic form (random weights) is built
+        from ..runtime.dspark_runner import DSparkConfig, DSparkRunner
+        if "synthetic_weights" not in hf:
+            raise NotImplementedError("deepseek_v41 drafter: loading checkpoint tensors is not built")
+        return DSparkRunner(engine, DSparkConfig.from_hf(hf), seed=int(hf["synthetic_weights"]) + 100)
     d = hf.get("dflash_config", {})
     cfg = DFlashConfig(block_size=int(hf.get("block_size", d.get("block_size", 8))), n_layers=int(hf["num_hidden_layers"]),
                        hidden=int(hf["hidden_size"]), n_q=int(hf["num_attention_heads"]), n_kv=int(hf["num_key_value_heads"]),
