@@ -417,3 +417,31 @@ def test_dspark_round_on_the_device():
     d = run.draft(0, first, 150, depth=3)
     got = eng.step([first] + d, [150 + i for i in range(len(d) + 1)], [0] * (len(d) + 1))
     assert len(got) == len(d) + 1
+
+
+def test_dsv4_two_ranks_match_one_rank(tmp_path):
+    """Heads, output groups, experts and the vocabulary split over two gloo ranks against the single-rank model."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = str(tmp_path / "tp")
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29733")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(here, "dsv4_tp_worker.py"), out], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    for p in procs:
+        text, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, text.decode()[-2000:]
+    parts = [torch.load(f"{out}.{r}", weights_only=True) for r in range(2)]
+    assert [(p["heads"], p["groups"], p["e_local"]) for p in parts] == [(8, 1, 4), (8, 1, 4)]
+    m, kv, _ = _dsv4_engine("cpu")
+    g = torch.Generator().manual_seed(11)
+    toks = torch.randint(0, 1024, (48,), generator=g).tolist()
+    want = _all_logits(m, kv, toks, [40, 8])
+    got = torch.cat([p["logits"] for p in parts], 1)[:, :1024]
+    cos = torch.nn.functional.cosine_similarity(got, want[:, :1024], dim=-1)
+    # (every rank quantises its own weight slices, so their NVFP4 scales differ from the whole matrix's: ~1 % apart)
+    assert float(cos.min()) > 0.97, float(cos.min())
+    assert float((got.argmax(-1) == want[:, :1024].argmax(-1)).float().mean()) > 0.7

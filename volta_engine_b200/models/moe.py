@@ -161,7 +161,7 @@ class MoEModel(DenseModel):
             if cfg.shared_ffn:
                 S = cfg.shared_ffn
                 wg, wu, wd = rnd(S, H), rnd(S, H), rnd(H, S)
-                f = S // tp if S % tp == 0 and (S // tp) % 16 == 0 else S
+                f = S // tp if S % tp == 0 and (S // tp) % 128 == 0 else S      # a slice must keep whole 128-wide scale blocks
                 self._shared_sliced = f != S
                 lo, hi = (r * f, (r + 1) * f) if f != S else (0, S)
                 L.shared_gu = self._make_linear(torch.cat([wg[lo:hi], wu[lo:hi]], 0), search)
