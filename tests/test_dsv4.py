@@ -445,3 +445,41 @@ def test_dsv4_two_ranks_match_one_rank(tmp_path):
     # (every rank quantises its own weight slices, so their NVFP4 scales differ from the whole matrix's: ~1 % apart)
     assert float(cos.min()) > 0.97, float(cos.min())
     assert float((got.argmax(-1) == want[:, :1024].argmax(-1)).float().mean()) > 0.7
+
+
+def test_prefill_truncation_runs_only_the_tail_through_the_late_layers():
+    from volta_engine_b200.runtime.batch import BatchRows, LOGITS_LAST, LOGITS_NONE
+    g = torch.Generator().manual_seed(17)
+    toks = torch.randint(0, 1024, (420,), generator=g).tolist()
+
+    def last_logits(keep):
+        m, kv, _ = _dsv4_engine("cpu")
+        m.set_prefill_truncate(keep)
+        m.set_prefill_end(420)
+        kv.reserve(0, 430)
+        out = None
+        for lo in range(0, 420, 60):
+            b = BatchRows.make(toks[lo:lo + 60], list(range(lo, lo + 60)), [0] * 60, "cpu",
+                               LOGITS_LAST if lo + 60 == 420 else LOGITS_NONE, m.nq, prefill=True)
+            out = m.forward(b, kv)
+        return m, out.float()[0, :1024]
+
+    full_m, full = last_logits(0)
+    assert full_m.trunc_layer == -1
+    ex_m, exact = last_logits(-1)
+    assert (ex_m.trunc_layer, ex_m.trunc_keep) == (3, 255)
+    # exact: the kept tail sees everything it would have seen (bf16 noise of the different row counts aside)
+    assert float(torch.nn.functional.cosine_similarity(exact, full, dim=0)) > 0.995
+    # rows before the tail never ran the layer after the truncation layer: its window ring has no entries for them,
+    # while the truncation layer itself and the source caches have all of them
+    assert float(ex_m.state.win[0, 4, :160].float().abs().sum()) == 0 and float(ex_m.state.win[0, 4, 170:420].float().abs().sum()) > 0
+    assert float(full_m.state.win[0, 4, :160].float().abs().sum()) > 0
+    assert torch.equal(ex_m.state.win[0, 3, :160], full_m.state.win[0, 3, :160])
+    assert float((ex_m.state.comp[1][0, :160] != full_m.state.comp[1][0, :160]).float().mean()) < 1e-3
+    # approximate: a shorter tail still gives a close answer (its early window entries are simply not attended)
+    ap_m, approx = last_logits(128)
+    assert ap_m.trunc_keep == 128 and float(torch.nn.functional.cosine_similarity(approx, full, dim=0)) > 0.9
+    assert float(ap_m.state.win[0, 4, :290].float().abs().sum()) == 0
+    # a layout without a ratio-1 source layer leaves it off
+    m3, _, _ = _dsv4_engine("cpu", compress_ratios=(0, 2, 2, 2, 2), kv_sources=(1,), index_sources=(1,), candidate_source=-1)
+    assert m3.trunc_layer == -1

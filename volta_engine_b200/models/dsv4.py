@@ -27,7 +27,7 @@ from ..ops import dsv4 as V
 from ..ops import kernels as K
 from ..ops import streams as S
 from ..ops.linear import LinearBF16
-from ..runtime.batch import LOGITS_LAST, LOGITS_NONE, BatchRows
+from ..runtime.batch import LOGITS_ALL, LOGITS_LAST, LOGITS_NONE, BatchRows
 from .moe import MoEConfig, MoELayer, MoEModel
 
 
@@ -98,6 +98,9 @@ class DSV4Model(MoEModel):
         self.rope_plain = self.rope_comp = None
         self.attn_ws2 = None
         self.engram_table = None
+        self.prefill_end = -1            # total length of the prompt being prefilled (set_prefill_end), -1 outside a prefill
+        self.trunc_layer, self.trunc_keep = -1, 0
+        self.set_prefill_truncate(-1)
         self.tap_ring = None             # a block drafter reads the stream mean at the entry of its target layers
         self.block_keys = None           # (key_end [rows], window): a drafter block whose rows all see the whole block
 
@@ -183,6 +186,51 @@ class DSV4Model(MoEModel):
     def ensure_workspace(self, max_rows: int, max_splits: int):
         return None
 
+    # ------------------------------------------------------------------------------------------ prefill truncation
+    def set_prefill_truncate(self, keep: int) -> None:
+        """From the first layer that reads a ratio-1 source's compressed KV on, nothing a later row needs comes from an
+        earlier row except that source's KV / index keys and each layer's window. So those layers run only the last ``keep``
+        rows of a prefill (``keep`` < 0: the exact count, one window further back per layer; 0: off); the earlier rows stop
+        at that layer after writing its window entries and source caches. Needs every KV source at or before that layer
+        and every engram layer before it. Reference: src/models/deepseek_v41.cpp:576-594, 2060-2071."""
+        cfg = self.cfg
+        self.trunc_layer, self.trunc_keep = -1, 0
+        if keep == 0:
+            return
+        b = next((l for l, r in enumerate(cfg.compress_ratios) if r == 1), -1)
+        ok = b > 0 and b in cfg.kv_sources and all(s <= b for s in cfg.kv_sources) and all(e < b for e in cfg.engram_layers)
+        if not ok:
+            return
+        exact = (cfg.n_layers - b - 1) * (V.WINDOW - 1) + V.WINDOW
+        self.trunc_layer, self.trunc_keep = b, exact if keep < 0 else max(keep, V.WINDOW)
+
+    def set_prefill_end(self, end: int) -> None:
+        self.prefill_end = end
+
+    def _trunc_rows(self, b: BatchRows) -> int:
+        """How many leading rows of this chunk stop at the truncation layer."""
+        if self.trunc_layer < 0 or self.prefill_end < 0 or b.n <= 16 or b.logits == LOGITS_ALL or not b.host_pos:
+            return 0
+        keep_pos = self.prefill_end - self.trunc_keep
+        k = 0
+        while k < b.n and b.host_pos[k] < keep_pos:
+            k += 1
+        return k
+
+    def _attention_kv(self, li, L, x, b: BatchRows, kv):
+        """What later rows read of this layer from rows that go no further: its window entries and, as a KV source, its
+        compressed KV and index keys."""
+        cfg, st, eps = self.cfg, self._state(kv), self.cfg.rms_eps
+        xp = L.x_proj.forward(x)
+        c = L.cols
+        kv_n = K.rmsnorm(xp[:, c["kv"][0]:c["kv"][1]], L.kv_norm, eps, cfg.norm_bias)
+        rope = self.rope_comp if L.ratio > 0 else self.rope_plain
+        V.window_store(st, li, kv_n, rope, b.slot, b.pos)
+        if L.is_kv_source:
+            csc = xp[:, c["csc"][0]:c["csc"][1]] if L.ratio > 1 else None
+            latent = V.compress(st, L.kv_src, xp[:, c["ckv"][0]:c["ckv"][1]], csc, L.c_norm, rope, b.slot, b.pos, eps)
+            V.index_key_store(st, L.kv_src, L.idx_wk.forward(latent), L.idx_knorm, rope, b.slot, b.pos, eps)
+
     # ------------------------------------------------------------------------------------------ forward
     def forward(self, b: BatchRows, kv) -> torch.Tensor | None:
         cfg, comm = self.cfg, self.comm
@@ -197,10 +245,29 @@ class DSV4Model(MoEModel):
         xs = S.init_streams(K.embed(b.ids, self.embed, scale=cfg.embed_scale), 4)
         pre = torch.zeros(b.n, 4, dtype=torch.float32, device=self.device)
         pre[:, 0] = 1.0
+        k0 = self._trunc_rows(b)
+        self.win_floor = 0
         for li, L in enumerate(self.layers):
+            if li == self.trunc_layer and k0 > 0:
+                # prefill truncation: the rows before the kept tail stop here, after writing what the kept rows read of this layer
+                fn, base, scale = L.attn_hc
+                head = BatchRows(b.ids[:k0], b.pos[:k0], b.slot[:k0], k0, LOGITS_NONE)
+                mixh = S.hc_collapse(xs[:k0].contiguous(), fn, base, scale, 1, cfg.hc_eps, rms_eps=eps, norm_w=L.attn_norm,
+                                     norm_eps=eps, norm_bias=cfg.norm_bias, pre_in=pre[:k0].contiguous())
+                self._attention_kv(li, L, mixh.collapsed, head, kv)
+                if k0 == b.n:
+                    return None                                    # nothing of this chunk runs further (it wants no logits)
+                xs, pre = xs[k0:].contiguous(), pre[k0:].contiguous()
+                b = BatchRows(b.ids[k0:], b.pos[k0:], b.slot[k0:], b.n - k0, b.logits, None, b.nsplit, None,
+                              b.host_slots[k0:], b.host_pos[k0:])
+                if st.sel is not None and st.sel[0].shape[0] > b.n:
+                    st.sel = (st.sel[0][k0:].contiguous(), st.sel[1][k0:].contiguous())
+                st.cand = None if st.cand is None else (st.cand[k0:] if isinstance(st.cand, list) else st.cand[k0:].contiguous())
+                self.win_floor = self.prefill_end - self.trunc_keep
             if L.engram is not None:
                 rows = self.engram_table[L.engram["index"]][eids[:, L.engram["index"]]]
                 V.engram_gate(xs, L.engram["wkv"].forward(rows).contiguous(), L.engram["w"], None, eps)
+            self._cur_floor = self.win_floor if li > self.trunc_layer >= 0 else 0
             if self.tap_ring is not None and li in self.tap_ring.index:
                 self.tap_ring.publish(li, S.head_mean(xs), b.pos, b.slot, b.n)
             fn, base, scale = L.attn_hc
@@ -249,5 +316,6 @@ class DSV4Model(MoEModel):
             V.indexer(st, src, qi, wi, b.slot, b.pos, mode, cfg.candidate_blocks, cfg.candidate_block)
         nsplit = 1 if b.n > 16 else max(1, min(8, b.nsplit))
         ke, win = self.block_keys if self.block_keys is not None else (None, V.WINDOW)
-        o = V.attend(st, li, src, q, L.sink, rope, b.slot, b.pos, self.heads, self.attn_ws2, nsplit=nsplit, key_end=ke, window=win)
+        o = V.attend(st, li, src, q, L.sink, rope, b.slot, b.pos, self.heads, self.attn_ws2, nsplit=nsplit, key_end=ke, window=win,
+                     win_floor=getattr(self, "_cur_floor", 0))
         return L.wo_b.forward(V.grouped_out_proj(o, L.wo_a), out=pbuf)

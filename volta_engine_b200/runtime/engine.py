@@ -104,6 +104,8 @@ class Engine:
         G = self.model.nq // self.model.nkv
         done = 0
         tok = -1
+        if hasattr(self.model, "set_prefill_end"):          # models that run only the tail of a prompt through their late layers
+            self.model.set_prefill_end(start_pos + n)
         while done < n:
             c = min(self.prefill_chunk, n - done)
             last = done + c == n
@@ -122,6 +124,8 @@ class Engine:
                 self._sample_greedy(logits, self.s_tok, self.s_val, rows)
                 tok = int(self.s_tok[rows - 1].item())
             done += c
+        if hasattr(self.model, "set_prefill_end"):
+            self.model.set_prefill_end(-1)
         return tok
 
     # ------------------------------------------------------------------------------------------ decode
