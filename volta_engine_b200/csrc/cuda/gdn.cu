@@ -6,6 +6,9 @@
 //                  in registers:  S *= decay;  delta = (v - S^T k) * beta;  S += k (x) delta;  o = S^T q;
 //                  stores the state, and (head 0) rolls the slot's convolution state forward
 //   gdn_gated_norm y = rmsnorm(o) * w * silu(z)
+// KDA (Kimi delta attention) is the same recurrence with one decay per key channel, S = diag(exp(g)) S, where
+//   g = -5 sigmoid(exp(A_log[h]) (f + dt_bias)) and f is a low-rank projection of the input; its output gate is sigmoid(z)
+//   (reference: src/backend/cpu/gdn_ref.cpp:32-57 kda_head_step, :94-127 project_kda_gates, :59-68 gate_norm_out).
 // A row at position 0 starts its slot from zero state. fp32 state and arithmetic; the fused projection row is
 // [q | k | v | z | b | a] in bf16. Reference: inc/engine/modules/gdn.h (project_gates, causal_conv1d_silu*,
 // l2_norm_heads, recurrent_step[_rows], gated_rmsnorm).
@@ -24,6 +27,7 @@ struct GdnArgs {
   float* gb;                    // [rows][2*nv] decay, beta
   float* o;                     // [rows][nv*dv]
   int rows, nk, nv, dk, dv, kc, slots;
+  const float* kdec;            // KDA: [rows][nv * dk] per-key-channel decay exp(g); null = one decay per head (gb)
 };
 
 VE_DEVINL float siluf(float x) { return x / (1.f + __expf(-x)); }
@@ -84,7 +88,7 @@ __global__ void gdn_prepare_kernel(const GdnArgs a) {
 // grid (nv, slots), block dv threads; thread = one column of the head's state.
 template <int DK>
 __global__ void __launch_bounds__(256) gdn_recurrent_kernel(const GdnArgs a) {
-  __shared__ float ks[DK], qs[DK];
+  __shared__ float ks[DK], qs[DK], ds[DK];
   grid_dep_launch();
   grid_dep_wait();
   const int h = blockIdx.x, s = blockIdx.y, col = threadIdx.x;
@@ -103,13 +107,17 @@ __global__ void __launch_bounds__(256) gdn_recurrent_kernel(const GdnArgs a) {
   for (int r = 0; r < count; ++r) {
     const int i = first + r;
     const float* ui = a.u + (long)i * C;
-    for (int t = col; t < DK; t += blockDim.x) { qs[t] = ui[kh * DK + t]; ks[t] = ui[a.nk * DK + kh * DK + t]; }
-    __syncthreads();
     const float decay = a.gb[(long)i * 2 * a.nv + h], beta = a.gb[(long)i * 2 * a.nv + a.nv + h];
+    for (int t = col; t < DK; t += blockDim.x) {
+      qs[t] = ui[kh * DK + t];
+      ks[t] = ui[a.nk * DK + kh * DK + t];
+      ds[t] = a.kdec ? a.kdec[((long)i * a.nv + h) * DK + t] : decay;
+    }
+    __syncthreads();
     const float v = ui[2 * a.nk * DK + h * a.dv + col];
     float mem = 0.f;
 #pragma unroll
-    for (int k = 0; k < DK; ++k) { S[k] *= decay; mem = fmaf(S[k], ks[k], mem); }
+    for (int k = 0; k < DK; ++k) { S[k] *= ds[k]; mem = fmaf(S[k], ks[k], mem); }
     const float delta = (v - mem) * beta;
     float o = 0.f;
 #pragma unroll
@@ -137,6 +145,7 @@ __global__ void __launch_bounds__(256) gdn_recurrent_kernel(const GdnArgs a) {
 }
 
 // grid (nv, rows), block dv threads.
+template <bool SIGMOID>
 __global__ void gdn_gated_norm_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ proj, long ld,
                                       const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int nv, int dv,
                                       int z_off, float eps) {
@@ -147,7 +156,20 @@ __global__ void gdn_gated_norm_kernel(const float* __restrict__ o, const __nv_bf
   const float x = o[((long)i * nv + h) * dv + col];
   const float ss = block_sum(x * x, red);
   const float z = bf2f(proj[(long)i * ld + z_off + h * dv + col]);
-  out[((long)i * nv + h) * dv + col] = f2bf(x * rsqrtf(ss / dv + eps) * w[col] * siluf(z));
+  const float gate = SIGMOID ? 1.f / (1.f + __expf(-z)) : siluf(z);
+  out[((long)i * nv + h) * dv + col] = f2bf(x * rsqrtf(ss / dv + eps) * w[col] * gate);
+}
+
+// KDA decay per key channel: kdec[row][j] = exp(-5 sigmoid(exp(A_log[j / dk]) (f[row][j] + dt_bias[j]))). grid rows.
+__global__ void kda_decay_kernel(const __nv_bfloat16* __restrict__ f, long ld, const float* __restrict__ A_log,
+                                 const float* __restrict__ dt_bias, float* __restrict__ kdec, int channels, int dk) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int i = blockIdx.x;
+  for (int j = threadIdx.x; j < channels; j += blockDim.x) {
+    const float x = __expf(A_log[j / dk]) * (bf2f(f[(long)i * ld + j]) + dt_bias[j]);
+    kdec[(long)i * channels + j] = __expf(-5.f / (1.f + __expf(-x)));
+  }
 }
 
 }  // namespace ve
@@ -163,7 +185,7 @@ int ve_gdn_prepare(const void* proj, long ld, const void* pos, const void* slot,
   if (kc < 2 || kc > 9 || dk > 256 || dv > 256 || nv % nk || nv > 256) return cudaErrorInvalidValue;
   GdnArgs a{(const __nv_bfloat16*)proj, ld, (const int*)pos, (const int*)slot, (float*)conv_state, nullptr,
             (const float*)conv_w, (const float*)A_log, (const float*)dt_bias, (float*)u, (float*)gb, nullptr,
-            rows, nk, nv, dk, dv, kc, slots};
+            rows, nk, nv, dk, dv, kc, slots, nullptr};
   int threads = dk > dv ? dk : dv;
   if (threads < nv) threads = nv;
   threads = (threads + 31) / 32 * 32;
@@ -177,10 +199,32 @@ int ve_gdn_recurrent(const void* proj, long ld, const void* pos, const void* slo
   if (rows <= 0) return 0;
   if (kc < 2 || kc > 9 || dv > 256 || dv % 32 || nv % nk) return cudaErrorInvalidValue;
   GdnArgs a{(const __nv_bfloat16*)proj, ld, (const int*)pos, (const int*)slot, (float*)conv_state, (float*)rec_state,
-            nullptr, nullptr, nullptr, (float*)u, (float*)gb, (float*)o, rows, nk, nv, dk, dv, kc, slots};
+            nullptr, nullptr, nullptr, (float*)u, (float*)gb, (float*)o, rows, nk, nv, dk, dv, kc, slots, nullptr};
   if (dk == 128) launch_pdl(gdn_recurrent_kernel<128>, dim3(nv, slots), dim3(dv), 0, st, a);
   else if (dk == 64) launch_pdl(gdn_recurrent_kernel<64>, dim3(nv, slots), dim3(dv), 0, st, a);
   else return cudaErrorInvalidValue;
+  VE_CHECK_LAUNCH();
+}
+
+// The recurrence with one decay per key channel (kdec [rows][nv * dk], already exponentiated).
+int ve_kda_recurrent(const void* proj, long ld, const void* pos, const void* slot, void* conv_state, void* rec_state,
+                     const void* u, const void* gb, void* o, const void* kdec, int rows, int nk, int nv, int dk, int dv, int kc,
+                     int slots, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (kc < 2 || kc > 9 || dv > 256 || dv % 32 || nv % nk || !kdec) return cudaErrorInvalidValue;
+  GdnArgs a{(const __nv_bfloat16*)proj, ld, (const int*)pos, (const int*)slot, (float*)conv_state, (float*)rec_state,
+            nullptr, nullptr, nullptr, (float*)u, (float*)gb, (float*)o, rows, nk, nv, dk, dv, kc, slots, (const float*)kdec};
+  if (dk == 128) launch_pdl(gdn_recurrent_kernel<128>, dim3(nv, slots), dim3(dv), 0, st, a);
+  else if (dk == 64) launch_pdl(gdn_recurrent_kernel<64>, dim3(nv, slots), dim3(dv), 0, st, a);
+  else return cudaErrorInvalidValue;
+  VE_CHECK_LAUNCH();
+}
+
+int ve_kda_decay(const void* f, long ld, const void* A_log, const void* dt_bias, void* kdec, int rows, int nv, int dk,
+                 cudaStream_t st) {
+  if (rows <= 0) return 0;
+  launch_pdl(kda_decay_kernel, dim3(rows), dim3(256), 0, st, (const __nv_bfloat16*)f, ld, (const float*)A_log,
+             (const float*)dt_bias, (float*)kdec, nv * dk, dk);
   VE_CHECK_LAUNCH();
 }
 
@@ -188,8 +232,18 @@ int ve_gdn_gated_norm(const void* o, const void* proj, long ld, const void* w, v
                       int conv_dim, int kc, float eps, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (dv > 1024 || dv % 32) return cudaErrorInvalidValue;
-  launch_pdl(gdn_gated_norm_kernel, dim3(nv, rows), dim3(dv), 0, st, (const float*)o, (const __nv_bfloat16*)proj, ld,
+  launch_pdl(gdn_gated_norm_kernel<false>, dim3(nv, rows), dim3(dv), 0, st, (const float*)o, (const __nv_bfloat16*)proj, ld,
              (const float*)w, (__nv_bfloat16*)out, nv, dv, conv_dim, eps);
+  VE_CHECK_LAUNCH();
+}
+
+// y = rmsnorm(o) * w * sigmoid(z); z [rows, nv * dv] bf16 with row stride ld.
+int ve_kda_gated_norm(const void* o, const void* z, long ld, const void* w, void* out, int rows, int nv, int dv, float eps,
+                      cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (dv > 1024 || dv % 32) return cudaErrorInvalidValue;
+  launch_pdl(gdn_gated_norm_kernel<true>, dim3(nv, rows), dim3(dv), 0, st, (const float*)o, (const __nv_bfloat16*)z, ld,
+             (const float*)w, (__nv_bfloat16*)out, nv, dv, 0, eps);
   VE_CHECK_LAUNCH();
 }
 

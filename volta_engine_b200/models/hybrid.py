@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from ..ops import kernels as K
-from ..ops.gdn import GDNDims, GDNState, gdn_forward
+from ..ops.gdn import GDNDims, GDNState, KDAWeights, gdn_forward, kda_forward
 from ..ops.linear import LinearBF16
 from ..runtime.batch import BatchRows
 from .moe import MoEConfig, MoELayer, MoEModel
@@ -28,6 +28,8 @@ class HybridConfig(MoEConfig):
     gdn_dv: int = 128
     gdn_conv: int = 4
     attn_gate: bool = True
+    linear_mixer: str = "gdn"      # gdn (one decay per head) | kda (Kimi delta attention: one decay per key channel, low-rank gates)
+    kda_rank: int = 128            # rank of the KDA decay / output-gate projections
     qsa: bool = False              # block-sparse attention: a 4-head indexer over pooled keys picks a decode row's 2048 tokens
     model_type: str = "hybrid_gdn"
 
@@ -117,6 +119,14 @@ class HybridModel(MoEModel):
              "dt_bias": torch.linspace(-1.0, 1.0, d.n_v, device=dev).float(),
              "norm_w": torch.ones(d.dv, device=dev, dtype=torch.float32),
              "out_proj": self._make_linear(rnd(H, d.n_v * d.dv), search)}
+        if cfg.linear_mixer == "kda":
+            from ..ops.linear import LinearBF16
+            bf, r = torch.bfloat16, cfg.kda_rank
+            assert d.n_k == d.n_v, "KDA has as many key heads as value heads"
+            g["kda"] = KDAWeights(f_a=LinearBF16(rnd(r, H).to(bf)), f_b=LinearBF16((rnd(d.n_v * d.dk, r) * 10).to(bf)),
+                                  g_a=LinearBF16(rnd(r, H).to(bf)), g_b=LinearBF16((rnd(d.n_v * d.dv, r) * 10).to(bf)),
+                                  A_log=torch.log(torch.linspace(0.5, 2.0, d.n_v, device=dev)).float(),
+                                  dt_bias=torch.linspace(-1.0, 1.0, d.n_v * d.dk, device=dev).float(), norm_w=g["norm_w"])
         L.gdn = g
         L.qkv = L.o_proj = None
 
@@ -142,6 +152,9 @@ class HybridModel(MoEModel):
         if L.gdn is not None:
             g = L.gdn
             proj = g["in_proj"].forward(x)
+            if "kda" in g:
+                y = kda_forward(proj, x, g["kda"], b.pos, b.slot, self._states(kv)[li], self.dims, g["conv_w"], cfg.rms_eps)
+                return g["out_proj"].forward(y.to(x.dtype), out=pbuf)
             y = gdn_forward(proj, b.pos, b.slot, self._states(kv)[li], self.dims, g["conv_w"], g["A_log"], g["dt_bias"],
                             g["norm_w"], cfg.rms_eps)
             return g["out_proj"].forward(y.to(x.dtype), out=pbuf)

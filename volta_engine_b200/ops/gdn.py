@@ -119,3 +119,82 @@ def gdn_forward(proj, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log, dt_bia
     call("gdn_gated_norm", "pplpp" + "iiiii" + "f", ptr(o), ptr(proj), proj.stride(0), ptr(norm_w), ptr(out), n, d.n_v, d.dv,
          C, d.conv_k, float(eps))
     return out
+
+
+# ---------------------------------------------------------------------------------------------- KDA
+@dataclass
+class KDAWeights:
+    """Kimi-delta-attention gates of one layer (heads of 128 x 128, as many key heads as value heads).
+    Reference: inc/engine/modules/gdn.h:113-132 (project_kda_gates operands)."""
+    f_a: object               # linear hidden -> rank        (decay, low rank)
+    f_b: object               # linear rank -> heads * dk
+    g_a: object               # linear hidden -> rank        (output gate, low rank)
+    g_b: object               # linear rank -> heads * dv
+    A_log: torch.Tensor       # [heads] fp32
+    dt_bias: torch.Tensor     # [heads * dk] fp32
+    norm_w: torch.Tensor      # [dv] fp32
+
+
+def kda_reference(proj, f, z, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log, dt_bias, norm_w, eps: float) -> torch.Tensor:
+    """fp32 statement. proj [n, >= conv_dim + nv*dv + nv] = [q | k | v | (unused z) | b | ...], f [n, nv*dk] decay
+    pre-activations, z [n, nv*dv] gate pre-activations. Per row: conv + SiLU, L2 norms and the q scale as the gated delta
+    rule; S = diag(exp(g)) S with g = -5 sigmoid(exp(A_log[h]) (f + dt_bias)) per key channel; delta = beta (v - S^T k);
+    S += k delta^T; y = rmsnorm(S^T q) * w * sigmoid(z)."""
+    n = proj.shape[0]
+    C, nv, nk, dk, dv = d.conv_dim, d.n_v, d.n_k, d.dk, d.dv
+    assert nk == nv
+    pf = proj.float()
+    raw = pf[:, :C]
+    b = pf[:, C + nv * dv: C + nv * dv + nv]
+    cw = conv_w.float()
+    y = torch.zeros(n, nv, dv)
+    for i in range(n):
+        s, p = int(slot[i]), int(pos[i])
+        if s < 0:
+            continue
+        if p == 0:
+            st.conv[s].zero_()
+            st.rec[s].zero_()
+        hist = torch.cat([st.conv[s], raw[i:i + 1]], 0)
+        u = F.silu((hist * cw.t()).sum(0))
+        st.conv[s] = hist[1:]
+        q = u[: nk * dk].reshape(nk, dk)
+        k = u[nk * dk: 2 * nk * dk].reshape(nk, dk)
+        v = u[2 * nk * dk:].reshape(nv, dv)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        g = -5.0 * torch.sigmoid(torch.exp(A_log.float())[:, None] * (f[i].float().reshape(nv, dk) + dt_bias.float().reshape(nv, dk)))
+        beta = torch.sigmoid(b[i])
+        S = st.rec[s] * torch.exp(g)[:, :, None]
+        mem = torch.einsum("hkv,hk->hv", S, k)
+        delta = (v - mem) * beta[:, None]
+        S = S + k[:, :, None] * delta[:, None, :]
+        st.rec[s] = S
+        o = torch.einsum("hkv,hk->hv", S, q)
+        o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_w.float()[None, :]
+        y[i] = o * torch.sigmoid(z[i].float().reshape(nv, dv))
+    return y.reshape(n, nv * dv)
+
+
+def kda_forward(proj, x, W: KDAWeights, pos, slot, st: GDNState, d: GDNDims, conv_w, eps: float) -> torch.Tensor:
+    """Kimi delta attention over the rows: ``proj`` is the fused [q | k | v | - | b | -] projection of ``x`` (the layout of
+    the gated delta rule, its z and a columns unused), the decay and the output gate come from the low-rank pairs in ``W``."""
+    f = W.f_b.forward(W.f_a.forward(x))
+    z = W.g_b.forward(W.g_a.forward(x))
+    if not proj.is_cuda:
+        return kda_reference(proj, f, z, pos, slot, st, d, conv_w, W.A_log, W.dt_bias, W.norm_w, eps).to(proj.dtype)
+    n, dev = proj.shape[0], proj.device
+    C, nv = d.conv_dim, d.n_v
+    u = torch.empty(n, C, dtype=torch.float32, device=dev)
+    gb = torch.empty(n, 2 * nv, dtype=torch.float32, device=dev)
+    o = torch.empty(n, nv * d.dv, dtype=torch.float32, device=dev)
+    kdec = torch.empty(n, nv * d.dk, dtype=torch.float32, device=dev)
+    out = torch.empty(n, nv * d.dv, dtype=torch.bfloat16, device=dev)
+    zero = torch.zeros(nv, dtype=torch.float32, device=dev)
+    call("gdn_prepare", "plpppppppp" + "iiiiiii", ptr(proj), proj.stride(0), ptr(pos), ptr(slot), ptr(st.conv), ptr(conv_w),
+         ptr(zero), ptr(zero), ptr(u), ptr(gb), n, d.n_k, d.n_v, d.dk, d.dv, d.conv_k, st.conv.shape[0])
+    call("kda_decay", "plpppiii", ptr(f), f.stride(0), ptr(W.A_log), ptr(W.dt_bias), ptr(kdec), n, nv, d.dk)
+    call("kda_recurrent", "plppppppppiiiiiii", ptr(proj), proj.stride(0), ptr(pos), ptr(slot), ptr(st.conv), ptr(st.rec),
+         ptr(u), ptr(gb), ptr(o), ptr(kdec), n, d.n_k, d.n_v, d.dk, d.dv, d.conv_k, st.conv.shape[0])
+    call("kda_gated_norm", "pplppiiif", ptr(o), ptr(z), z.stride(0), ptr(W.norm_w), ptr(out), n, nv, d.dv, float(eps))
+    return out

@@ -36,6 +36,7 @@ TABLE = {
     "moe_gather": ("MoE", P), "cpu_post": ("CpuExperts", D), "cpu_wait_add": ("CpuExperts", D),
     "cpu_mailbox_bytes": ("CpuExperts", D),
     "gdn_prepare": ("GDN", P), "gdn_recurrent": ("GDN", P), "gdn_gated_norm": ("GDN", P),
+    "kda_recurrent": ("GDN / KDA", P), "kda_decay": ("GDN / KDA", P), "kda_gated_norm": ("GDN / KDA", P),
     "hc_collapse": ("HyperConnection", P), "head_mean": ("HyperHead", P), "init_streams": ("HyperConnection / GatedResidual", P),
     "stream_epilogue": ("Stream epilogues", P), "gr_norm": ("GatedResidual", P), "gr_gate": ("GatedResidual", P),
     "gr_up": ("GatedResidual", P), "gr_up_epilogue": ("GatedResidual", P), "gr_shared_gate": ("GatedResidual", P),
