@@ -152,6 +152,32 @@ def main():
     if rank == 0:
         print(f"tp{size} tokens {t_tp} vs single {t1}", flush=True)
     assert K.check_status(dev) == 0
+
+    # --- DeepSeek-V4.1-style model: heads, output groups and experts split over the ranks, caches replicated; the
+    # stream updates run fused with the all-reduce
+    if size == 2:
+        from volta_engine_b200.models.dsv4 import DSV4Config, DSV4Model
+        from volta_engine_b200.runtime.batch import LOGITS_LAST
+        dcfg = DSV4Config.tiny_dsv4()
+        dprompt = torch.randint(0, dcfg.vocab, (100,), generator=torch.Generator().manual_seed(1)).tolist()
+        d_tp = DSV4Model(dcfg, dev, comm).init_random(seed=5, std=0.05)
+        dkv = PagedKVCache(1, 1, 64, 16, 1, 512, dev)
+        de = Engine(d_tp, dkv, prefill_chunk=64)
+        d_toks = [de.prefill(0, dprompt)]
+        for i in range(6):
+            d_toks.append(de.step([d_toks[-1]], [len(dprompt) + i], [0])[0])
+        same_on_all_ranks(torch.tensor(d_toks, device=dev), "DSV4 TP tokens")
+        dkv.reserve(0, 200)
+        dprobe = BatchRows.make(dprompt[:40], list(range(120, 160)), [0] * 40, dev, LOGITS_LAST, d_tp.nq, prefill=True)
+        lg_tp = d_tp.forward(dprobe, dkv).float().clone()
+        d1 = DSV4Model(DSV4Config.tiny_dsv4(), dev).init_random(seed=5, std=0.05)
+        dkv1 = PagedKVCache(1, 1, 64, 16, 1, 512, dev)
+        de1 = Engine(d1, dkv1, prefill_chunk=64)
+        d1_toks = [de1.prefill(0, dprompt)]
+        if rank == 0:
+            print(f"dsv4 tp2 tokens {d_toks} single first {d1_toks[0]}", flush=True)
+        assert (d_tp.heads, d_tp.groups, d_tp.e_local) == (8, 1, 4)
+        assert K.check_status(dev) == 0
     dist.barrier()
     if rank == 0:
         print("TP_WORKER_OK", flush=True)
