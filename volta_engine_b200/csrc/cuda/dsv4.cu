@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(128) dsv4_window_store_kernel(const __nv_bfloa
                                                                 uint8_t* __restrict__ ring, const float* __restrict__ rope,
                                                                 const int* __restrict__ slot, const int* __restrict__ pos,
                                                                 int layer, long slot_stride) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int r = blockIdx.x, t = threadIdx.x, d = 4 * t;
   const int sl = slot[r];
   if (sl < 0) return;
@@ -101,6 +103,8 @@ __global__ void __launch_bounds__(128) dsv4_cring_store_kernel(const __nv_bfloat
                                                                float* __restrict__ ring_kv, float* __restrict__ ring_sc,
                                                                const int* __restrict__ slot, const int* __restrict__ pos,
                                                                long slot_stride) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int r = blockIdx.x, sl = slot[r];
   if (sl < 0) return;
   const long at = (long)sl * slot_stride + (long)(pos[r] % kRing) * kHD;
@@ -119,6 +123,8 @@ __global__ void __launch_bounds__(128) dsv4_compress_kernel(const __nv_bfloat16*
                                                             const float* __restrict__ rope, const int* __restrict__ slot,
                                                             const int* __restrict__ pos, long ring_slot_stride,
                                                             long comp_slot_stride, int ratio, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float red[33];
   const int r = blockIdx.x, t = threadIdx.x, d = 4 * t;
   const int sl = slot[r];
@@ -203,6 +209,8 @@ __global__ void __launch_bounds__(128) dsv4_index_key_kernel(const __nv_bfloat16
                                                              __nv_bfloat16* __restrict__ idxk, const float* __restrict__ rope,
                                                              const int* __restrict__ slot, const int* __restrict__ pos,
                                                              long slot_stride, int ratio, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float red[33];
   const int r = blockIdx.x, sl = slot[r];
   if (sl < 0) return;
@@ -217,6 +225,8 @@ __global__ void __launch_bounds__(128) dsv4_index_key_kernel(const __nv_bfloat16
 __global__ void __launch_bounds__(128) dsv4_index_q_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
                                                            __nv_bfloat16* __restrict__ out, const float* __restrict__ rope,
                                                            const int* __restrict__ pos) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float red[33];
   const int r = blockIdx.x, h = blockIdx.y;
   const float x = __bfloat162float(q[(long)r * q_stride + h * kIdxDim + threadIdx.x]);
@@ -296,6 +306,8 @@ __global__ void __launch_bounds__(1024) dsv4_candidates_kernel(const float* __re
                                                                uint8_t* __restrict__ cand, long cand_stride,
                                                                const int* __restrict__ slot, const int* __restrict__ pos,
                                                                int ratio, int blocks, int block) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ int hist[256];
   __shared__ int wcnt[32], woff[32];
   __shared__ uint32_t s_prefix;
@@ -338,6 +350,8 @@ __global__ void __launch_bounds__(1024) dsv4_select_kernel(const float* __restri
                                                            const uint8_t* __restrict__ cand, long cand_stride, int cand_block,
                                                            int* __restrict__ sel, int* __restrict__ nsel,
                                                            const int* __restrict__ slot, const int* __restrict__ pos, int ratio) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ int hist[256];
   __shared__ int wcnt[32], woff[32];
   __shared__ uint32_t s_prefix;
@@ -394,6 +408,8 @@ __global__ void __launch_bounds__(256) dsv4_gather_kernel(const uint8_t* __restr
                                                           __nv_bfloat16* __restrict__ pages, int* __restrict__ nkeys,
                                                           int* __restrict__ v_pos, int* __restrict__ v_slot, int win_floor,
                                                           const int* __restrict__ key_end, int window) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int r = blockIdx.y, i = blockIdx.x * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63;
   const int sl = slot[r];
   if (sl < 0) {
@@ -454,6 +470,8 @@ __global__ void __launch_bounds__(64) dsv4_q_prep_kernel(const __nv_bfloat16* __
                                                          __nv_bfloat16* __restrict__ q_abs, const float* __restrict__ sink,
                                                          const float* __restrict__ rope, const int* __restrict__ pos, int heads,
                                                          float scale) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int r = blockIdx.x, h = blockIdx.y, l = threadIdx.x, d = 8 * l;
   const __nv_bfloat16* src = q + (long)r * q_stride + (long)h * kHD + d;
   __nv_bfloat16* dst = q_abs + ((long)r * heads + h) * kLatRowD;
@@ -484,6 +502,8 @@ __global__ void __launch_bounds__(128) dsv4_attn_out_kernel(const __nv_bfloat16*
                                                             __nv_bfloat16* __restrict__ out, const float* __restrict__ rope,
                                                             const int* __restrict__ pos, const int* __restrict__ slot, int heads,
                                                             int rows) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x, d = 4 * t;
   if (slot[r] < 0) return;
   const __nv_bfloat16* src = o_lat + ((long)r * heads + h) * kHD + d;
@@ -516,6 +536,8 @@ __global__ void __launch_bounds__(128) dsv4_attn_out_kernel(const __nv_bfloat16*
 template <int RB>
 __global__ void __launch_bounds__(256) dsv4_woa_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ w,
                                                        __nv_bfloat16* __restrict__ out, int groups, int O, int rows) {
+  grid_dep_launch();
+  grid_dep_wait();
   constexpr int KD = kGroupHeads * kHD;
   const int lane = threadIdx.x & 31, gr = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (gr >= groups * O) return;
@@ -562,6 +584,8 @@ __global__ void __launch_bounds__(1024) dsv4_engram_ids_kernel(const int* __rest
                                                                const int* __restrict__ pos, int* __restrict__ hist, long hist_stride,
                                                                int spare_slot, int* __restrict__ out, int tables, int table_rows,
                                                                int ngram, int rows) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int r = threadIdx.x;
   int sl = 0, p = 0;
   if (r < rows) {
@@ -584,6 +608,8 @@ __global__ void __launch_bounds__(1024) dsv4_engram_ids_kernel(const int* __rest
 __global__ void __launch_bounds__(256) dsv4_engram_gate_kernel(float* __restrict__ streams, const __nv_bfloat16* __restrict__ kv,
                                                                const float* __restrict__ w, const uint8_t* __restrict__ skip,
                                                                int H, int hc, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float red[33];
   const int r = blockIdx.x, h = blockIdx.y;
   if (skip && skip[r]) return;
@@ -616,7 +642,7 @@ extern "C" {
 int ve_dsv4_window_store(const void* kv, long kv_stride, void* ring, const void* rope, const void* slot, const void* pos, int layer,
                          long slot_stride, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
-  dsv4_window_store_kernel<<<rows, 128, 0, st>>>((const __nv_bfloat16*)kv, kv_stride, (uint8_t*)ring, (const float*)rope,
+  launch_pdl(dsv4_window_store_kernel, dim3(rows), dim3(128), 0, st, (const __nv_bfloat16*)kv, kv_stride, (uint8_t*)ring, (const float*)rope,
                                                  (const int*)slot, (const int*)pos, layer, slot_stride);
   VE_CHECK_LAUNCH();
 }
@@ -625,7 +651,7 @@ int ve_dsv4_cring_store(const void* ckv, long ckv_stride, const void* csc, long 
                         const void* slot, const void* pos, long slot_stride, int rows, int unused, cudaStream_t st) {
   (void)unused;
   if (rows <= 0) return 0;
-  dsv4_cring_store_kernel<<<rows, 128, 0, st>>>((const __nv_bfloat16*)ckv, ckv_stride, (const __nv_bfloat16*)csc, csc_stride,
+  launch_pdl(dsv4_cring_store_kernel, dim3(rows), dim3(128), 0, st, (const __nv_bfloat16*)ckv, ckv_stride, (const __nv_bfloat16*)csc, csc_stride,
                                                 (float*)ring_kv, (float*)ring_sc, (const int*)slot, (const int*)pos, slot_stride);
   VE_CHECK_LAUNCH();
 }
@@ -635,7 +661,7 @@ int ve_dsv4_compress(const void* ckv, long ckv_stride, const void* ring_kv, cons
                      long comp_slot_stride, int ratio, float eps, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (ratio < 1 || (ratio > 1 && (!ring_kv || !ring_sc))) return cudaErrorInvalidValue;
-  dsv4_compress_kernel<<<rows, 128, 0, st>>>((const __nv_bfloat16*)ckv, ckv_stride, (const float*)ring_kv, (const float*)ring_sc,
+  launch_pdl(dsv4_compress_kernel, dim3(rows), dim3(128), 0, st, (const __nv_bfloat16*)ckv, ckv_stride, (const float*)ring_kv, (const float*)ring_sc,
                                              (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)latent_out, (uint8_t*)comp,
                                              (const float*)rope, (const int*)slot, (const int*)pos, ring_slot_stride,
                                              comp_slot_stride, ratio, eps);
@@ -647,7 +673,7 @@ int ve_dsv4_index_key_store(const void* kraw, long kraw_stride, const void* norm
                             cudaStream_t st) {
   (void)unused;
   if (rows <= 0) return 0;
-  dsv4_index_key_kernel<<<rows, 128, 0, st>>>((const __nv_bfloat16*)kraw, kraw_stride, (const __nv_bfloat16*)norm_w,
+  launch_pdl(dsv4_index_key_kernel, dim3(rows), dim3(128), 0, st, (const __nv_bfloat16*)kraw, kraw_stride, (const __nv_bfloat16*)norm_w,
                                               (__nv_bfloat16*)idxk, (const float*)rope, (const int*)slot, (const int*)pos,
                                               slot_stride, ratio, eps);
   VE_CHECK_LAUNCH();
@@ -655,7 +681,7 @@ int ve_dsv4_index_key_store(const void* kraw, long kraw_stride, const void* norm
 
 int ve_dsv4_index_q(const void* q, long q_stride, void* out, const void* rope, const void* pos, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
-  dsv4_index_q_kernel<<<dim3(rows, kIdxHeads), 128, 0, st>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
+  launch_pdl(dsv4_index_q_kernel, dim3(rows, kIdxHeads), dim3(128), 0, st, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                                              (const float*)rope, (const int*)pos);
   VE_CHECK_LAUNCH();
 }
@@ -664,7 +690,7 @@ int ve_dsv4_candidates(const void* scores, long score_stride, void* cand, long c
                        int ratio, int blocks, int block, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (blocks < 1 || block < 1) return cudaErrorInvalidValue;
-  dsv4_candidates_kernel<<<rows, 1024, 0, st>>>((const float*)scores, score_stride, (uint8_t*)cand, cand_stride, (const int*)slot,
+  launch_pdl(dsv4_candidates_kernel, dim3(rows), dim3(1024), 0, st, (const float*)scores, score_stride, (uint8_t*)cand, cand_stride, (const int*)slot,
                                                 (const int*)pos, ratio, blocks, block);
   VE_CHECK_LAUNCH();
 }
@@ -673,7 +699,7 @@ int ve_dsv4_select(const void* scores, long score_stride, const void* cand, long
                    const void* slot, const void* pos, int ratio, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cand && cand_block < 1) return cudaErrorInvalidValue;
-  dsv4_select_kernel<<<rows, 1024, 0, st>>>((const float*)scores, score_stride, (const uint8_t*)cand, cand_stride, cand_block,
+  launch_pdl(dsv4_select_kernel, dim3(rows), dim3(1024), 0, st, (const float*)scores, score_stride, (const uint8_t*)cand, cand_stride, cand_block,
                                             (int*)sel, (int*)nsel, (const int*)slot, (const int*)pos, ratio);
   VE_CHECK_LAUNCH();
 }
@@ -683,7 +709,7 @@ int ve_dsv4_gather(const void* win, int layer, long win_slot_stride, const void*
                    int win_floor, int rows, const void* key_end, int window, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (window < 1 || window + kSelTopk + 1 > kPagesRow * 64 || window > kRing) return cudaErrorInvalidValue;
-  dsv4_gather_kernel<<<dim3((kKeysMax + 3) / 4, rows), 256, 0, st>>>((const uint8_t*)win, layer, win_slot_stride,
+  launch_pdl(dsv4_gather_kernel, dim3((kKeysMax + 3) / 4, rows), dim3(256), 0, st, (const uint8_t*)win, layer, win_slot_stride,
                                                                      (const uint8_t*)comp, comp_slot_stride, (const int*)sel,
                                                                      (const int*)nsel, (const int*)slot, (const int*)pos,
                                                                      (__nv_bfloat16*)pages, (int*)nkeys, (int*)v_pos,
@@ -694,7 +720,7 @@ int ve_dsv4_gather(const void* win, int layer, long win_slot_stride, const void*
 int ve_dsv4_q_prep(const void* q, long q_stride, void* q_abs, const void* sink, const void* rope, const void* pos, int heads,
                    float scale, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
-  dsv4_q_prep_kernel<<<dim3(rows, heads), 64, 0, st>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_abs, (const float*)sink,
+  launch_pdl(dsv4_q_prep_kernel, dim3(rows, heads), dim3(64), 0, st, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_abs, (const float*)sink,
                                                        (const float*)rope, (const int*)pos, heads, scale);
   VE_CHECK_LAUNCH();
 }
@@ -702,7 +728,7 @@ int ve_dsv4_q_prep(const void* q, long q_stride, void* q_abs, const void* sink, 
 int ve_dsv4_attn_out(const void* o_lat, void* out, const void* rope, const void* pos, const void* slot, int heads, int rows,
                      cudaStream_t st) {
   if (rows <= 0) return 0;
-  dsv4_attn_out_kernel<<<dim3(rows, heads), 128, 0, st>>>((const __nv_bfloat16*)o_lat, (__nv_bfloat16*)out, (const float*)rope,
+  launch_pdl(dsv4_attn_out_kernel, dim3(rows, heads), dim3(128), 0, st, (const __nv_bfloat16*)o_lat, (__nv_bfloat16*)out, (const float*)rope,
                                                           (const int*)pos, (const int*)slot, heads, rows);
   VE_CHECK_LAUNCH();
 }
@@ -712,9 +738,9 @@ int ve_dsv4_woa(const void* o, const void* w, void* out, int groups, int O, int 
   if (rows > 16) return cudaErrorInvalidValue;
   const int grid = (groups * O + 7) / 8;
   const __nv_bfloat16 *op = (const __nv_bfloat16*)o, *wp = (const __nv_bfloat16*)w;
-  if (rows <= 1) dsv4_woa_kernel<1><<<grid, 256, 0, st>>>(op, wp, (__nv_bfloat16*)out, groups, O, rows);
-  else if (rows <= 4) dsv4_woa_kernel<4><<<grid, 256, 0, st>>>(op, wp, (__nv_bfloat16*)out, groups, O, rows);
-  else dsv4_woa_kernel<16><<<grid, 256, 0, st>>>(op, wp, (__nv_bfloat16*)out, groups, O, rows);
+  if (rows <= 1) launch_pdl(dsv4_woa_kernel<1>, dim3(grid), dim3(256), 0, st, op, wp, (__nv_bfloat16*)out, groups, O, rows);
+  else if (rows <= 4) launch_pdl(dsv4_woa_kernel<4>, dim3(grid), dim3(256), 0, st, op, wp, (__nv_bfloat16*)out, groups, O, rows);
+  else launch_pdl(dsv4_woa_kernel<16>, dim3(grid), dim3(256), 0, st, op, wp, (__nv_bfloat16*)out, groups, O, rows);
   VE_CHECK_LAUNCH();
 }
 
@@ -722,7 +748,7 @@ int ve_dsv4_engram_ids(const void* ids, const void* slot, const void* pos, void*
                        int tables, int table_rows, int ngram, int rows, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (rows > 1024 || tables < 1 || table_rows < 1) return cudaErrorInvalidValue;
-  dsv4_engram_ids_kernel<<<1, 1024, 0, st>>>((const int*)ids, (const int*)slot, (const int*)pos, (int*)hist, hist_stride, spare_slot,
+  launch_pdl(dsv4_engram_ids_kernel, dim3(1), dim3(1024), 0, st, (const int*)ids, (const int*)slot, (const int*)pos, (int*)hist, hist_stride, spare_slot,
                                              (int*)out, tables, table_rows, ngram, rows);
   VE_CHECK_LAUNCH();
 }
@@ -730,7 +756,7 @@ int ve_dsv4_engram_ids(const void* ids, const void* slot, const void* pos, void*
 int ve_dsv4_engram_gate(void* streams, const void* kv, const void* w, const void* skip, int H, int hc, float eps, int rows,
                         cudaStream_t st) {
   if (rows <= 0) return 0;
-  dsv4_engram_gate_kernel<<<dim3(rows, hc), 256, 0, st>>>((float*)streams, (const __nv_bfloat16*)kv, (const float*)w,
+  launch_pdl(dsv4_engram_gate_kernel, dim3(rows, hc), dim3(256), 0, st, (float*)streams, (const __nv_bfloat16*)kv, (const float*)w,
                                                           (const uint8_t*)skip, H, hc, eps);
   VE_CHECK_LAUNCH();
 }
