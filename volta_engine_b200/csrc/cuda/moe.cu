@@ -237,6 +237,131 @@ __global__ void __launch_bounds__(128) nvfp4_moe_gemv_kernel(const uint8_t* __re
   }
 }
 
+// Warp-per-row form (K <= kMoeXMax): the route's activation row is staged once per CTA in shared memory (16-byte pieces
+// stored piece-major so that consecutive lanes read consecutive pieces), every warp owns two weight rows (FUSE: gate row o and
+// up row o + N/2; else rows 2w, 2w + 1 of the CTA's eight) and walks K with all 32 lanes, two 16-byte weight loads per row in
+// flight; no cross-warp reduction. One CTA streams 8 weight rows instead of 2-4, which is what lets the weight stream,
+// and not CTA turnover, set the time. grid (outs / (FUSE ? 4 : 8), routes), 128 threads.
+constexpr int kMoeXMax = 8192;
+
+VE_DEVINL float moe_chunk_dot(const uint4 w, const uint32_t sc, const float* xv) {
+  const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int blk = 0; blk < 2; ++blk) {
+    float s = 0.f;
+#pragma unroll
+    for (int hw = 0; hw < 2; ++hw) {
+      const uint32_t word = words[blk * 2 + hw];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t h2 = m_cvt_e2m1x2((word >> (8 * j)) & 0xffu);
+        const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+        s = fmaf(wf.x, xv[blk * 16 + hw * 8 + 2 * j], s);
+        s = fmaf(wf.y, xv[blk * 16 + hw * 8 + 2 * j + 1], s);
+      }
+    }
+    acc = fmaf(m_e4m3(sc >> (8 * blk)), s, acc);
+  }
+  return acc;
+}
+
+template <int FUSE>
+__global__ void __launch_bounds__(128) nvfp4_moe_gemv_rows_kernel(const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ Ws,
+                                                                  const float* __restrict__ gs, const int* __restrict__ ids,
+                                                                  int e0, int e_local, const __nv_bfloat16* __restrict__ x,
+                                                                  long x_stride, int x_div, __nv_bfloat16* __restrict__ out,
+                                                                  long out_stride, int N, int K, int act, float limit) {
+  __shared__ __align__(16) __nv_bfloat16 xs[kMoeXMax];
+  constexpr int OUTS = FUSE ? 4 : 8;
+  const int route = blockIdx.y;
+  const int e = ids[route] - e0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half_n = N >> 1, n_out = FUSE ? half_n : N;
+  const int o_base = blockIdx.x * OUTS;
+  if (e < 0 || e >= e_local) {
+    if (threadIdx.x < OUTS && o_base + threadIdx.x < n_out) out[(long)route * out_stride + o_base + threadIdx.x] = f2bf(0.f);
+    return;
+  }
+  const uint8_t* wp = Ws ? Wp + (size_t)e * N * (K >> 1) : reinterpret_cast<const uint8_t* const*>(Wp)[2 * e];
+  const uint8_t* ws = Ws ? Ws + (size_t)e * N * (K >> 4) : reinterpret_cast<const uint8_t* const*>(Wp)[2 * e + 1];
+  const __nv_bfloat16* xr = x + (long)(route / x_div) * x_stride;
+  const int kchunks = K >> 5;
+  // piece (j, c) = elements [32 c + 8 j, 32 c + 8 j + 8) of the row, stored at piece index j * kchunks + c
+  for (int pc = threadIdx.x; pc < kchunks * 4; pc += 128) {
+    const int c = pc >> 2, j = pc & 3;
+    *reinterpret_cast<uint4*>(xs + ((long)j * kchunks + c) * 8) = *reinterpret_cast<const uint4*>(xr + (long)c * 32 + j * 8);
+  }
+  __syncthreads();
+  const int r0 = FUSE ? o_base + warp : o_base + 2 * warp;
+  const int r1 = FUSE ? r0 + half_n : r0 + 1;
+  const int n0 = min(r0, N - 1), n1 = min(r1, N - 1);
+  const uint4* w0 = reinterpret_cast<const uint4*>(wp + (size_t)n0 * (K >> 1));
+  const uint4* w1 = reinterpret_cast<const uint4*>(wp + (size_t)n1 * (K >> 1));
+  const unsigned short* s0 = reinterpret_cast<const unsigned short*>(ws + (size_t)n0 * (K >> 4));
+  const unsigned short* s1 = reinterpret_cast<const unsigned short*>(ws + (size_t)n1 * (K >> 4));
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int c = lane; c < kchunks; c += 64) {
+    const int c2 = c + 32;
+    const bool two = c2 < kchunks;
+    // all weight loads of the two chunks first, then the arithmetic
+    const uint4 a0 = __ldcs(w0 + c), a1 = __ldcs(w1 + c);
+    const uint32_t sa0 = __ldcs(s0 + c), sa1 = __ldcs(s1 + c);
+    uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
+    uint32_t sb0 = 0, sb1 = 0;
+    if (two) {
+      b0 = __ldcs(w0 + c2);
+      b1 = __ldcs(w1 + c2);
+      sb0 = __ldcs(s0 + c2);
+      sb1 = __ldcs(s1 + c2);
+    }
+    float xv[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bf16x8 t = *reinterpret_cast<const bf16x8*>(xs + ((long)j * kchunks + c) * 8);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 f = __bfloat1622float2(t.v[u]);
+        xv[j * 8 + 2 * u] = f.x;
+        xv[j * 8 + 2 * u + 1] = f.y;
+      }
+    }
+    acc0 += moe_chunk_dot(a0, sa0, xv);
+    acc1 += moe_chunk_dot(a1, sa1, xv);
+    if (two) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bf16x8 t = *reinterpret_cast<const bf16x8*>(xs + ((long)j * kchunks + c2) * 8);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 f = __bfloat1622float2(t.v[u]);
+          xv[j * 8 + 2 * u] = f.x;
+          xv[j * 8 + 2 * u + 1] = f.y;
+        }
+      }
+      acc0 += moe_chunk_dot(b0, sb0, xv);
+      acc1 += moe_chunk_dot(b1, sb1, xv);
+    }
+  }
+  acc0 = warp_sum(acc0);
+  acc1 = warp_sum(acc1);
+  if (lane != 0) return;
+  const float g = gs[e];
+  if (FUSE) {
+    if (r0 < half_n) {
+      // the unfused pair rounds both projections to bf16 before the activation: keep the same rounding points
+      float gate = bf2f(f2bf(acc0 * g)), up = bf2f(f2bf(acc1 * g));
+      if (limit > 0.f) { gate = fminf(gate, limit); up = fminf(fmaxf(up, -limit), limit); }
+      const float a = act ? 0.5f * gate * (1.f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)))
+                          : gate / (1.f + __expf(-gate));
+      out[(long)route * out_stride + r0] = f2bf(a * up);
+    }
+  } else {
+    if (r0 < N) out[(long)route * out_stride + r0] = f2bf(acc0 * g);
+    if (r1 < N) out[(long)route * out_stride + r1] = f2bf(acc1 * g);
+  }
+}
+
 // y[t, :] = sum_k w[t, k] * d[row(t, k), :] (+ shared[t, :]); row(t,k) = inv ? inv[t*topk+k] : t*topk+k.
 // Routes of non-local experts carry zero rows (decode) or are flagged by ids outside [e0, e0+e_local).
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ d, long d_stride, const float* __restrict__ w,
@@ -376,6 +501,17 @@ int ve_nvfp4_moe_gemv(const void* Wp, const void* Ws, const void* gs, const void
   if (routes <= 0) return 0;
   if (K % 32 || N % 2 || (fuse_act && N % 4)) return cudaErrorInvalidValue;
   const int outs = fuse_act ? N / 2 : N;
+  if (K <= kMoeXMax) {
+    if (fuse_act)
+      nvfp4_moe_gemv_rows_kernel<1><<<dim3((outs + 3) / 4, routes), 128, 0, st>>>(
+          (const uint8_t*)Wp, (const uint8_t*)Ws, (const float*)gs, (const int*)ids, e0, e_local, (const __nv_bfloat16*)x,
+          x_stride, x_div, (__nv_bfloat16*)out, out_stride, N, K, act, limit);
+    else
+      nvfp4_moe_gemv_rows_kernel<0><<<dim3((outs + 7) / 8, routes), 128, 0, st>>>(
+          (const uint8_t*)Wp, (const uint8_t*)Ws, (const float*)gs, (const int*)ids, e0, e_local, (const __nv_bfloat16*)x,
+          x_stride, x_div, (__nv_bfloat16*)out, out_stride, N, K, act, limit);
+    VE_CHECK_LAUNCH();
+  }
   dim3 grid((outs + 1) / 2, routes);
   if (fuse_act)
     nvfp4_moe_gemv_kernel<1><<<grid, 128, 0, st>>>((const uint8_t*)Wp, (const uint8_t*)Ws, (const float*)gs, (const int*)ids,
