@@ -483,3 +483,49 @@ def test_prefill_truncation_runs_only_the_tail_through_the_late_layers():
     # a layout without a ratio-1 source layer leaves it off
     m3, _, _ = _dsv4_engine("cpu", compress_ratios=(0, 2, 2, 2, 2), kv_sources=(1,), index_sources=(1,), candidate_source=-1)
     assert m3.trunc_layer == -1
+
+
+def test_launcher_builds_the_synthetic_model_with_its_drafter_and_serves_a_request(tmp_path):
+    """config.json alone (synthetic weights) -> engine, DSpark drafter chosen by model_type, options applied, one request
+    through the scheduler with drafter rounds, candidate log written."""
+    import json
+    from volta_engine_b200.runtime.generator import Generator, Request
+    from volta_engine_b200.runtime.options import Options
+    from volta_engine_b200.runtime.spec_logs import CandLog, read_cand_log
+    from volta_engine_b200.server import cli
+
+    class ByteTok:
+        eos_ids = [0]
+
+        def decode_bytes(self, ids, skip_special=False):
+            return bytes(i & 0xFF for i in ids)
+
+        def encode(self, text, allow_special=True):
+            return list(text.encode())
+
+    hf = {"model_type": "deepseek_v41", "synthetic_weights": 3, "n_layers": 3, "dim": 256, "n_heads": 16, "n_routed_experts": 4,
+          "n_activated_experts": 2, "moe_inter_dim": 128, "q_lora_rank": 128, "o_groups": 2, "o_lora_rank": 128, "vocab_size": 256,
+          "compress_ratios": [0, 2, 1], "kv_source_layers": [1, 2], "index_source_layers": [1, 2], "norm_eps": 1e-6,
+          "dspark_block_size": 3, "dspark_noise_token_id": 5, "dspark_target_layer_ids": [1, 2], "n_mtp_layers": 1,
+          "dspark_markov_rank": 16, "dspark_n_routed_experts": 4, "dspark_n_activated_experts": 2}
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(hf))
+    lc, _ = cli.resolve_config(["--model-dir", str(d), "--set", "max_seq=512", "--set", "max_slots=2", "--set", "kv_pool=1024",
+                                "--set", "prefill_truncate=128", "--set", "prefill_chunk=64", "--set", "dspark_conf=0.0"], env={})
+    model, _, engine, _ = cli.build_engine(lc, device="cpu")
+    assert type(model).__name__ == "DSV4Model" and (model.trunc_layer, model.trunc_keep) == (2, 128)
+    drafter = cli.load_drafter(engine, str(d))
+    assert type(drafter).__name__ == "DSparkRunner" and drafter.cfg.block_size == 3 and model.tap_ring is drafter.ring
+    o = Options.resolve({"max_slots": 2, "speculator": "draft", "spec_ctrl": False, "prefix_cache_mib": 0}, env={})
+    gen = Generator(engine, ByteTok(), o, eos_ids=[])
+    gen.drafter = drafter
+    drafter.cfg.conf_threshold = 0.0
+    gen.cand_log = CandLog()
+    gen.cand_log.open(tmp_path / "cand.bin")
+    prompt = [(7 * i + 3) % 250 + 1 for i in range(200)]
+    res = gen.generate(Request(prompt, max_tokens=10, cache_prefix=False))
+    assert len(res["tokens"]) == 10 and gen.metrics.spec["rounds"] > 0 and drafter.stats["rounds"] > 0
+    gen.cand_log.close()
+    recs = read_cand_log(tmp_path / "cand.bin")
+    assert recs and recs[0]["kind"] == "round" and recs[0]["slot"] == 0

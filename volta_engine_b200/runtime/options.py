@@ -38,6 +38,11 @@ _TABLE = [
     ("log_level", str, "info", "error | warn | info | debug"),
     ("dump_requests", str, "", "directory that receives one JSON file per request"),
     ("trace_layers", bool, False, "NVTX range per layer"),
+    ("prefill_truncate", int, -1, "rows of a prompt's tail that the layers past a ratio-1 KV source run (-1 exact, 0 off; models that allow it)"),
+    ("dspark_conf", float, 0.5, "confidence below which the DSpark block drafter cuts its drafts"),
+    ("sparse_head", bool, False, "block drafter: draft through a learned subset of the head's columns when it pays"),
+    ("sparse_head_state", str, "", "file that keeps the sparse head's token counts between runs"),
+    ("spec_cand_log", str, "", "file that receives the block drafter's candidates per round (offline re-ranker training)"),
     ("hessian_dir", str, "", "calibration capture: x^T x of every projection input over the prefill rows, written here at shutdown"),
     ("hessian_layers", str, "", "lo-hi: capture these layers only (a slice that fits beside the weights)"),
     ("route_dump", str, "", "file that receives the MoE blocks' routed rows and routing weights at shutdown"),

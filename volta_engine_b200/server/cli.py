@@ -183,6 +183,8 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
                       dtype=o.kv_format)
     engine = Engine(model, kv, use_graphs=not o.no_graphs and torch.device(device).type == "cuda",
                     prefill_chunk=o.prefill_chunk)
+    if hasattr(model, "set_prefill_truncate"):
+        model.set_prefill_truncate(o.prefill_truncate)
     if o.hessian_dir and hasattr(model, "enable_hessians"):
         from ..ops.hessian import parse_layer_range
         model.enable_hessians(parse_layer_range(o.hessian_layers, mcfg.n_layers))
@@ -228,6 +230,14 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
     gen = Generator(engine, tok, o, prefix_cache=cache)
     if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size == 1:
         gen.drafter = load_drafter(engine, cfg.draft_model_dir)
+        if hasattr(gen.drafter.cfg, "conf_threshold"):
+            gen.drafter.cfg.conf_threshold = o.dspark_conf
+        if o.sparse_head and hasattr(gen.drafter, "enable_sparse_head"):
+            gen.drafter.enable_sparse_head(state_path=o.sparse_head_state or None)
+        if o.spec_cand_log:
+            from ..runtime.spec_logs import CandLog
+            gen.cand_log = CandLog()
+            gen.cand_log.open(o.spec_cand_log)
     defaults = {"temperature": cfg.default_temperature, "top_p": cfg.default_top_p, "top_k": cfg.default_top_k,
                 "enable_thinking": cfg.default_enable_thinking}
     gc_path = os.path.join(cfg.model_dir, "generation_config.json")
