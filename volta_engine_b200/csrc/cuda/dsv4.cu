@@ -64,7 +64,9 @@ VE_DEVINL void rope_pair_cs(float& a, float& b, const float* cs, bool inverse) {
 __global__ void __launch_bounds__(128) dsv4_window_store_kernel(const __nv_bfloat16* __restrict__ kv, long kv_stride,
                                                                 uint8_t* __restrict__ ring, const float* __restrict__ rope,
                                                                 const int* __restrict__ slot, const int* __restrict__ pos,
-                                                                int layer, long slot_stride) {
+                                                                int layer, long slot_stride,
+                                                                const __nv_bfloat16* __restrict__ norm_w, float eps, float wbias) {
+  __shared__ float red[33];
   grid_dep_launch();
   grid_dep_wait();
   const int r = blockIdx.x, t = threadIdx.x, d = 4 * t;
@@ -74,6 +76,12 @@ __global__ void __launch_bounds__(128) dsv4_window_store_kernel(const __nv_bfloa
   float v[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(kv[(long)r * kv_stride + d + j]);
+  if (norm_w) {   // the projection's RMSNorm, rounded to bf16 as the separate norm kernel stores it
+    const float ss = block_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3], red);
+    const float inv = rsqrtf(ss / (float)kHD + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = bfr(v[j] * inv * (__bfloat162float(norm_w[d + j]) + wbias));
+  }
   if (d >= kHD - kRopeD) {
     const float* cs = rope + ((long)p * (kRopeD / 2) + (d - (kHD - kRopeD)) / 2) * 2;
     rope_pair_cs(v[0], v[1], cs, false);
@@ -407,9 +415,41 @@ __global__ void __launch_bounds__(256) dsv4_gather_kernel(const uint8_t* __restr
                                                           const int* __restrict__ slot, const int* __restrict__ pos,
                                                           __nv_bfloat16* __restrict__ pages, int* __restrict__ nkeys,
                                                           int* __restrict__ v_pos, int* __restrict__ v_slot, int win_floor,
-                                                          const int* __restrict__ key_end, int window) {
+                                                          const int* __restrict__ key_end, int window,
+                                                          const __nv_bfloat16* __restrict__ q, long q_stride,
+                                                          __nv_bfloat16* __restrict__ q_abs, const float* __restrict__ sink,
+                                                          const float* __restrict__ rope, int heads, float scale) {
   grid_dep_launch();
   grid_dep_wait();
+  constexpr int kKeyBlocks = (kKeysMax + 3) / 4;
+  if (blockIdx.x >= kKeyBlocks) {
+    // the blocks past the keys prepare the row's queries (four heads per block, 64 threads each): rope on the last 64
+    // dims, element 512 = sink / scale, the rest of the tail zero
+    const int r = blockIdx.y, h = (blockIdx.x - kKeyBlocks) * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63, d = 8 * l;
+    if (h >= heads) return;
+    const __nv_bfloat16* src = q + (long)r * q_stride + (long)h * kHD + d;
+    __nv_bfloat16* dst = q_abs + ((long)r * heads + h) * kLatRowD;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(src[j]);
+    if (d >= kHD - kRopeD) {
+      const float* cs = rope + ((long)pos[r] * (kRopeD / 2) + (d - (kHD - kRopeD)) / 2) * 2;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) rope_pair_cs(v[2 * j], v[2 * j + 1], cs + 2 * j, false);
+    }
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(v[j]);
+    *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(o);
+    if (l < 8) {
+      __nv_bfloat16 z[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) z[j] = __float2bfloat16_rn(0.f);
+      if (l == 0) z[0] = __float2bfloat16_rn(sink[h] / scale);
+      *reinterpret_cast<uint4*>(dst + kHD + 8 * l) = *reinterpret_cast<const uint4*>(z);
+    }
+    return;
+  }
   const int r = blockIdx.y, i = blockIdx.x * 4 + (threadIdx.x >> 6), l = threadIdx.x & 63;
   const int sl = slot[r];
   if (sl < 0) {
@@ -640,10 +680,10 @@ using namespace ve;
 extern "C" {
 
 int ve_dsv4_window_store(const void* kv, long kv_stride, void* ring, const void* rope, const void* slot, const void* pos, int layer,
-                         long slot_stride, int rows, cudaStream_t st) {
+                         long slot_stride, int rows, const void* norm_w, float eps, float wbias, cudaStream_t st) {
   if (rows <= 0) return 0;
   launch_pdl(dsv4_window_store_kernel, dim3(rows), dim3(128), 0, st, (const __nv_bfloat16*)kv, kv_stride, (uint8_t*)ring, (const float*)rope,
-                                                 (const int*)slot, (const int*)pos, layer, slot_stride);
+                                                 (const int*)slot, (const int*)pos, layer, slot_stride, (const __nv_bfloat16*)norm_w, eps, wbias);
   VE_CHECK_LAUNCH();
 }
 
@@ -706,14 +746,16 @@ int ve_dsv4_select(const void* scores, long score_stride, const void* cand, long
 
 int ve_dsv4_gather(const void* win, int layer, long win_slot_stride, const void* comp, long comp_slot_stride, const void* sel,
                    const void* nsel, const void* slot, const void* pos, void* pages, void* nkeys, void* v_pos, void* v_slot,
-                   int win_floor, int rows, const void* key_end, int window, cudaStream_t st) {
+                   int win_floor, int rows, const void* key_end, int window, const void* q, long q_stride, void* q_abs,
+                   const void* sink, const void* rope, int heads, float scale, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (window < 1 || window + kSelTopk + 1 > kPagesRow * 64 || window > kRing) return cudaErrorInvalidValue;
-  launch_pdl(dsv4_gather_kernel, dim3((kKeysMax + 3) / 4, rows), dim3(256), 0, st, (const uint8_t*)win, layer, win_slot_stride,
+  launch_pdl(dsv4_gather_kernel, dim3((kKeysMax + 3) / 4 + (q ? (heads + 3) / 4 : 0), rows), dim3(256), 0, st, (const uint8_t*)win, layer, win_slot_stride,
                                                                      (const uint8_t*)comp, comp_slot_stride, (const int*)sel,
                                                                      (const int*)nsel, (const int*)slot, (const int*)pos,
                                                                      (__nv_bfloat16*)pages, (int*)nkeys, (int*)v_pos,
-                                                                     (int*)v_slot, win_floor, (const int*)key_end, window);
+                                                                     (int*)v_slot, win_floor, (const int*)key_end, window, (const __nv_bfloat16*)q, q_stride,
+                                                                     (__nv_bfloat16*)q_abs, (const float*)sink, (const float*)rope, heads, scale);
   VE_CHECK_LAUNCH();
 }
 

@@ -298,11 +298,11 @@ class DSV4Model(MoEModel):
         xp = L.x_proj.forward(x)
         c = L.cols
         qr_n = K.rmsnorm(xp[:, c["q"][0]:c["q"][1]], L.qa_norm, eps, cfg.norm_bias)
-        kv_n = K.rmsnorm(xp[:, c["kv"][0]:c["kv"][1]], L.kv_norm, eps, cfg.norm_bias)
         qq = L.q_proj.forward(qr_n)
         q = qq[:, : self.heads * V.HD]
         rope = self.rope_comp if L.ratio > 0 else self.rope_plain
-        V.window_store(st, li, kv_n, rope, b.slot, b.pos)
+        # the KV projection's norm runs inside the ring write
+        V.window_store(st, li, xp[:, c["kv"][0]:c["kv"][1]], rope, b.slot, b.pos, norm=(L.kv_norm, eps, cfg.norm_bias))
         src = L.kv_src
         if L.is_kv_source:
             ckv = xp[:, c["ckv"][0]:c["ckv"][1]]

@@ -147,13 +147,19 @@ class DSV4State:
 
 
 # ------------------------------------------------------------------------------------------------ cache writes
-def window_store(st: DSV4State, layer: int, kv_n: torch.Tensor, rope: torch.Tensor, slot: torch.Tensor, pos: torch.Tensor):
-    """kv_n [rows, 512] bf16 (normed) -> rope at pos, bf16 rounding, MXFP8 -> win[slot, layer, pos % RING]."""
+def window_store(st: DSV4State, layer: int, kv_n: torch.Tensor, rope: torch.Tensor, slot: torch.Tensor, pos: torch.Tensor,
+                 norm=None):
+    """kv_n [rows, 512] bf16 (normed) -> rope at pos, bf16 rounding, MXFP8 -> win[slot, layer, pos % RING].
+    ``norm`` = (weight, eps, weight bias): the rows are the raw projection and their RMSNorm is applied here first."""
     rows = kv_n.shape[0]
     if kv_n.is_cuda:
-        call("dsv4_window_store", "plppppili", ptr(kv_n), kv_n.stride(0), ptr(st.win), ptr(rope), ptr(slot), ptr(pos), layer,
-             st.win.stride(0), rows)
+        w, eps, wb = norm if norm is not None else (None, 0.0, 0.0)
+        call("dsv4_window_store", "plppppilipff", ptr(kv_n), kv_n.stride(0), ptr(st.win), ptr(rope), ptr(slot), ptr(pos), layer,
+             st.win.stride(0), rows, ptr(w), float(eps), float(wb))
         return
+    if norm is not None:
+        from . import reference as ref
+        kv_n = ref.rmsnorm(kv_n, norm[0], norm[1], norm[2])[0]
     ok = slot >= 0
     v = _bf(rope_tail(kv_n.float(), rope[pos.long()]))
     codes, exps = mxfp8_quant(v)
@@ -348,11 +354,10 @@ def attend(st: DSV4State, layer: int, src: int, q: torch.Tensor, sink: torch.Ten
                           torch.zeros(cap, dtype=torch.int32, device=q.device))
         pages, table, a_slot, nkeys, a_pos = st.scratch
         comp = st.comp[src] if sel is not None else None
-        call("dsv4_gather", "pilplppppppppiipi", ptr(st.win), layer, st.win.stride(0), ptr(comp), comp.stride(0) if comp is not None else 0,
-             ptr(sel), ptr(nsel), ptr(slot), ptr(pos), ptr(pages), ptr(nkeys), ptr(a_pos), ptr(a_slot), win_floor, rows,
-             ptr(key_end), window)
         q_abs = torch.empty(rows, nh, LAT_ROW, dtype=torch.bfloat16, device=q.device)
-        call("dsv4_q_prep", "plppppifi", ptr(q), q.stride(0), ptr(q_abs), ptr(sink), ptr(rope), ptr(pos), nh, float(scale), rows)
+        call("dsv4_gather", "pilplppppppppiipi" + "plpppif", ptr(st.win), layer, st.win.stride(0), ptr(comp), comp.stride(0) if comp is not None else 0,
+             ptr(sel), ptr(nsel), ptr(slot), ptr(pos), ptr(pages), ptr(nkeys), ptr(a_pos), ptr(a_slot), win_floor, rows,
+             ptr(key_end), window, ptr(q), q.stride(0), ptr(q_abs), ptr(sink), ptr(rope), nh, float(scale))
         o_lat = torch.empty(rows, nh, HD, dtype=torch.bfloat16, device=q.device)
         if ws is None or ws[0].numel() < rows * nh * nsplit * HD:
             nsplit = 1
