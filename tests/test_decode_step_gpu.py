@@ -1,0 +1,131 @@
+"""Persistent decode-step kernel (csrc/cuda/decode_step.cu) against the kernel-per-op decode path of the same model:
+same quantised weights, same cache, so logits must agree to rounding and greedy tokens must match."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _cos(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-30))
+
+
+def _setup(cfg_kw, prompt_len=300, seed=0):
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    dev = torch.device("cuda", 0)
+    cfg = DenseConfig(**cfg_kw)
+    model = DenseModel(cfg, dev).init_random(seed=seed)
+    kv = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, 48, 2, 1024, dev)
+    eng = Engine(model, kv, prefill_chunk=128, use_graphs=False)
+    g = torch.Generator().manual_seed(seed)
+    prompt = torch.randint(0, cfg.vocab, (prompt_len,), generator=g).tolist()
+    return dev, cfg, model, kv, eng, prompt
+
+
+def _rows(model, kv, ids, pos, slots, dev):
+    from volta_engine_b200.runtime.batch import BatchRows
+    b = BatchRows.make(ids, pos, slots, dev, nsplit=2)
+    return model.forward(b, kv).clone()
+
+
+BASE = dict(n_layers=3, hidden=1024, n_q=8, n_kv=2, head_dim=128, ffn=2048, vocab=4096)
+
+
+@pytest.mark.parametrize("cfg_kw", [BASE, dict(BASE, hidden=1152, n_q=9, n_kv=3, ffn=1920),
+                                   dict(BASE, act="gelu_tanh", norm_bias=1.0, rot_dim=64)])
+def test_step_matches_kernel_path(cfg_kw):
+    from volta_engine_b200.ops import decode_step as PS
+    from volta_engine_b200.ops import kernels as K
+    dev, cfg, model, kv, eng, prompt = _setup(cfg_kw)
+    PS.ENABLED = False
+    try:
+        tok = eng.prefill(0, prompt)
+    finally:
+        PS.ENABLED = True
+    n = len(prompt)
+    for rows in (1, 3, 4):
+        ids = [tok] + prompt[:rows - 1]
+        pos = list(range(n, n + rows))
+        kv.reserve(0, n + rows + 1)
+        PS.ENABLED = False
+        try:
+            want = _rows(model, kv, ids, pos, [0] * rows, dev)
+            hid_want = model.last_hidden.clone()
+        finally:
+            PS.ENABLED = True
+        got = _rows(model, kv, ids, pos, [0] * rows, dev)
+        assert got.shape == want.shape
+        assert _cos(got, want) > 0.9995, (rows, _cos(got, want))
+        assert _cos(model.last_hidden, hid_want) > 0.9995
+        assert torch.equal(got.argmax(-1), want.argmax(-1)) or _cos(got, want) > 0.9999
+    assert K.check_status(dev) == 0
+
+
+def test_step_two_slots_and_padding_row():
+    from volta_engine_b200.ops import decode_step as PS
+    dev, cfg, model, kv, eng, prompt = _setup(BASE)
+    PS.ENABLED = False
+    try:
+        t0 = eng.prefill(0, prompt)
+        t1 = eng.prefill(1, prompt[:170])
+    finally:
+        PS.ENABLED = True
+    kv.reserve(0, len(prompt) + 2)
+    kv.reserve(1, 172)
+    ids, pos, slots = [t0, t1, 5], [len(prompt), 170, 0], [0, 1, -1]
+    PS.ENABLED = False
+    try:
+        want = _rows(model, kv, ids, pos, slots, dev)
+    finally:
+        PS.ENABLED = True
+    got = _rows(model, kv, ids, pos, slots, dev)
+    assert _cos(got[:2], want[:2]) > 0.9995
+
+
+def test_step_greedy_tokens_and_graph_replay():
+    from volta_engine_b200.ops import decode_step as PS
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    dev, cfg, model, kv, eng, prompt = _setup(BASE, prompt_len=200)
+    outs = {}
+    for mode in ("kernels", "step_eager", "step_graph"):
+        PS.ENABLED = mode != "kernels"
+        try:
+            kv2 = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, 48, 2, 1024, dev)
+            e = Engine(model, kv2, prefill_chunk=128, use_graphs=mode == "step_graph")
+            first = e.prefill(0, prompt)
+            toks = e.decode_chain([first], [len(prompt)], [0], 12)
+            outs[mode] = [first] + toks[:, 0].tolist()
+        finally:
+            PS.ENABLED = True
+    assert outs["step_eager"] == outs["step_graph"], outs
+    same = sum(a == b for a, b in zip(outs["kernels"], outs["step_eager"]))
+    assert same >= len(outs["kernels"]) - 1 or outs["kernels"][:4] == outs["step_eager"][:4], outs
+
+
+def test_step_drains_at_once_when_status_is_set():
+    """A status word left set by an earlier failure makes every wait of the launch give up immediately: the kernel
+    returns in well under the one-second wait budget, leaves the status in place and the context stays usable."""
+    import time
+    from volta_engine_b200.ops import kernels as K
+    dev, cfg, model, kv, eng, prompt = _setup(BASE, prompt_len=80)
+    tok = eng.prefill(0, prompt)
+    kv.reserve(0, len(prompt) + 4)
+    good = _rows(model, kv, [tok], [len(prompt)], [0], dev)
+    st = K.status_word(dev)
+    st.fill_(2)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    _rows(model, kv, [tok], [len(prompt)], [0], dev)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 0.5
+    assert int(st.item()) == 2
+    st.zero_()
+    from volta_engine_b200.ops import decode_step as PS
+    for prog in model._pstep_programs.values():      # counters of an aborted step are reset by the host
+        prog.reset()
+    again = _rows(model, kv, [tok], [len(prompt)], [0], dev)
+    assert _cos(again, good) > 0.9999

@@ -16,6 +16,7 @@ from dataclasses import dataclass, asdict
 import torch
 
 from ..ops import kernels as K
+from ..ops import decode_step as PS
 from ..ops.streams import sandwich_add_norm
 from ..ops.linear import LinearBF16, LinearNVFP4
 from ..parallel.comm import LocalComm
@@ -55,6 +56,7 @@ class DenseConfig:
     logit_softcap: float = 0.0
     quant: str = "nvfp4"          # nvfp4 | bf16
     gemm_mode: str = "w4a16"      # prefill arithmetic for nvfp4 weights
+    lm_head_quant: str = "auto"   # auto: random-init NVFP4 models quantise the head like every other weight; bf16 keeps it dense
     model_type: str = "dense"
 
     @classmethod
@@ -182,7 +184,9 @@ class DenseModel:
         hi = min(cfg.vocab, lo + self.vocab_local)
         if hi > lo:
             head[: hi - lo] = full[lo:hi]
-        self.lm_head = self._make_linear(head.float(), search) if cfg.quant.startswith("gguf_") else LinearBF16(head)
+        quant_head = cfg.quant.startswith("gguf_") or (cfg.quant == "nvfp4" and cfg.lm_head_quant != "bf16"
+                                                          and cfg.hidden % 256 == 0)
+        self.lm_head = self._make_linear(head.float(), search) if quant_head else LinearBF16(head)
         return self
 
     def weight_bytes(self) -> int:
@@ -204,6 +208,10 @@ class DenseModel:
         the rows selected by ``b.logits`` (None for LOGITS_NONE)."""
         cfg = self.cfg
         comm = self.comm
+        if PS.supported(self, b, kv):
+            # decode rows: the whole step is one persistent launch (ops/decode_step.py)
+            logits, self.last_hidden, self.last_residual = PS.program_for(self, kv, b.n).run(b.ids, b.pos, b.slot)
+            return logits if logits is not None else self.lm_head.forward(self.last_hidden, out_f32=True)
         if cfg.residual != "plain":
             return self._forward_streams(b, kv)
         if self._prenorm_ok(b):

@@ -107,17 +107,26 @@ class LinearNVFP4:
         K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, addnorm=(resid, norm_w, normed, eps, wbias))
         return normed
 
-    def forward(self, x, residual=None, out=None, push=None):
+    def forward(self, x, residual=None, out=None, push=None, out_f32=False):
         """``push``: a communicator with ``push_target(rows, N)``; when the decode kernel runs, its epilogue also sends
-        the rows into the peers' all-reduce staging area and ``push.pushed`` is set for the collective behind."""
+        the rows into the peers' all-reduce staging area and ``push.pushed`` is set for the collective behind.
+        ``out_f32``: fp32 result (logits of a quantised LM head)."""
         if push is not None:
             push.pushed = False
         if not x.is_cuda:
             y = x.float() @ qn.dequantize_nvfp4(self.packed, self.scales, self.gscale).t()
             if residual is not None:
                 y = y + residual.float()
-            return y.to(x.dtype)
+            return y if out_f32 else y.to(x.dtype)
         rows = x.shape[0]
+        if out_f32:
+            if rows <= GEMV_MAX_ROWS and self._sf_atoms is not None and self._tc_ok() and GEMV_KERNEL in ("auto", "tc"):
+                return K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, x, out=out, out_f32=True)
+            y = self.forward(x, residual=residual).float()       # many rows: bf16 product widened (perplexity tools)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
         if rows <= GEMV_MAX_ROWS:
             # tcgen05 path: the tensor core decodes the FP4 weights itself; activations ride as 4 residual NVFP4
             # terms per row (error below bf16 rounding), cost independent of the row count
