@@ -29,15 +29,17 @@
 
 namespace ve {
 
-constexpr int DS_NS = 8;                                 // ring stages
-constexpr int DS_A = 16384, DS_B = 2048, DS_SF = 2048;   // weight tile / B operand / one scale block
-constexpr int DS_STAGE = DS_A + DS_B + 2 * DS_SF;        // 22528 B
-constexpr int DS_SCR = 40960;                            // scratch: normalised-input row(s) or attention merge
+constexpr int DS_MAXNS = 10;                             // most ring stages (the count follows from the scratch a launch needs)
+constexpr int DS_A = 16384, DS_SF = 2048;                // weight tile / its four scale atoms
+constexpr int DS_STAGE = DS_A + DS_SF;                   // 18432 B: one unit as it lies in memory (or one K / V page)
+constexpr int DS_SLOTS = 20;                             // operand cache: k-tiles of one op a CTA can hold
+constexpr int DS_SFB = 256;                              // distance of the four scale atoms of a slot (16 rows used of 32)
+constexpr int DS_SLOT = 2048 + 4 * DS_SFB;               // 16 operand rows x 128 B (swizzled) | scale atoms
+constexpr int DS_CACHE = DS_SLOTS * DS_SLOT + 512;       // (the last atom is read 256 B past its slot)
 constexpr int DS_MAXM = 4;
 constexpr int DS_TERMS = 4;
-constexpr int DS_LOOK = 4;                               // epilogues run this many units behind the B-operand fill
-constexpr int DS_TMEM = 128;
-constexpr int DS_SMEM = DS_NS * DS_STAGE + DS_SCR + 1024;
+constexpr int DS_TMEM = 256;                             // 2 issuers x 2 accumulators x 32 columns, scale columns from 128
+constexpr int DS_SMEM = 226 * 1024;
 
 enum : int { OP_LINEAR = 0, OP_QKV_FIN = 1, OP_ATTN = 2, OP_MERGE = 3, OP_NORMOUT = 4 };
 enum : int { IN_X = 0, IN_NORM = 1, IN_GATED = 2, IN_EMBED = 3 };
@@ -56,7 +58,8 @@ struct StepOp {
   int ypar;                    // OUT_TICKET: reduced-output buffer written
   int ar;                      // OUT_TICKET, tensor parallel: index of this all-reduce inside the step
   int flags;                   // 1: write the normalised input rows to xfinal
-  const uint8_t* sfa;          // scale atoms [N/128][ceil(K/256)*4][512]
+  const uint8_t* wt;           // weight units [N/128][ceil(K/256)][18432]: the 128 x 128 B tile of packed codes as it sits
+                               // in swizzled shared memory, followed by its four 512 B scale atoms
   const __nv_bfloat16* norm_w; // IN_NORM / IN_EMBED
 };
 
@@ -83,11 +86,13 @@ struct StepParams {
   __nv_bfloat16* kpool;        // [layers][pages][nkv][64][128]
   __nv_bfloat16* vpool;
   int* status;
+  unsigned long long* prof;    // optional [nops][4] timestamps (ns) of CTA prof_cta: op entered, input ready, units done, op left
+  int* dbg;                    // [0] waits that gave up, then records {site, op, ring index / counter, cta, aux, -} from [8]
   uint8_t* peer[8];
   uint32_t* seq;
   unsigned long long off_ll, ll_row_bytes, budget_ns;
   long ldl, pool_layer_rows;
-  int nops, kmap, vmap, M, H, nq, nkv, S, max_pages, vocab, rot, act, rank, size, n_ar, pad0;
+  int nops, kmap, vmap, M, H, nq, nkv, S, max_pages, vocab, rot, act, rank, size, n_ar, prof_cta, ns, scr;      // ns ring stages, scr scratch bytes
   float eps, wbias, scale_log2, rope_theta, act_limit, embed_scale;
 };
 
@@ -121,22 +126,37 @@ VE_DEVINL void bar_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 struct Ctx {
   const StepParams* p;
-  uint8_t* smem;
+  uint8_t* smem;                 // ring stages
+  uint8_t* cache;                // operand cache slots
   uint8_t* scratch;
-  uint64_t *tfull, *bfull, *empty, *acc_full, *acc_empty;
+  uint64_t *tfull, *cfull, *empty, *acc_full, *acc_empty;
+  int ns;
   volatile int* s_fail;
+  volatile uint32_t* attn_seq;   // attention ops this CTA's compute warps have finished
+  volatile uint32_t* prog;       // [2] units each issuer has passed
   int cta, G;
   VE_DEVINL uint8_t* stage(int s) const { return smem + (size_t)s * DS_STAGE; }
   VE_DEVINL bool failed() const { return *s_fail != 0; }
   VE_DEVINL void fail() const { *s_fail = 1; }
   // bounded waits that give up at once after a failure anywhere in the CTA
-  VE_DEVINL bool wait_bar(uint64_t* bar, uint32_t parity) const {
+  // the first wait of the launch that runs out of time leaves a record of where it was
+  VE_DEVINL void record(int site, int oi, uint32_t r, int aux) const {
+    if (!p->dbg) return;
+    const int i = atomicAdd(p->dbg, 1);
+    if (i < 1000) {
+      int* d = p->dbg + 8 + 6 * i;
+      d[0] = site; d[1] = oi; d[2] = (int)r; d[3] = cta; d[4] = aux;
+    }
+  }
+  VE_DEVINL bool wait_bar(uint64_t* bar, uint32_t parity, int site = 0, int oi = -1, uint32_t r = 0) const {
+    if (mbar_try_wait(bar, parity)) return true;      // the common case costs one instruction
     if (failed()) return false;
     if (mbar_wait(bar, parity)) return true;
+    if ((threadIdx.x & 31) == 0) record(failed() ? site + 100 : site, oi, r, (int)parity);
     fail();
     return false;
   }
-  VE_DEVINL bool wait_cnt(const uint32_t* c, uint32_t target) const {
+  VE_DEVINL bool wait_cnt(const uint32_t* c, uint32_t target, int site = 0, int oi = -1) const {
     if (failed()) return false;
     if ((int)(ld_acquire_gpu(c) - target) >= 0) return true;
     const uint64_t t0 = globaltimer_ns();
@@ -144,7 +164,8 @@ struct Ctx {
 #pragma unroll 1
       for (int i = 0; i < 16; ++i)
         if ((int)(ld_acquire_gpu(c) - target) >= 0) return true;
-      if (globaltimer_ns() - t0 > kWaitNs || failed()) { fail(); return false; }
+      if (failed()) { record(site + 100, oi, ld_acquire_gpu(c), (int)target); return false; }
+      if (globaltimer_ns() - t0 > kWaitNs) { record(site, oi, ld_acquire_gpu(c), (int)target); fail(); return false; }
     }
   }
 };
@@ -155,6 +176,10 @@ VE_DEVINL void ds_run(const StepOp& op, int cta, int& u0, int& u1) {
   u0 = min(U, cta * op.upc);
   u1 = min(U, u0 + op.upc);
 }
+// Operand cache: the first min(KT, run length) units of a run touch distinct k-tiles; k-tile kt sits in slot
+// (kt - first k-tile of the run) mod KT.
+VE_DEVINL int ds_nslots(int KT, int u0, int u1) { return min(KT, u1 - u0); }
+VE_DEVINL int ds_slot(int KT, int u0, int u) { return (u - u0) % KT; }
 // CTAs that share tile t of op: first CTA and count
 VE_DEVINL void ds_splits(const StepOp& op, int t, int& first, int& n) {
   const int KT = ds_kt(op);
@@ -196,16 +221,13 @@ VE_DEVINL void ds_loader(const Ctx& c) {
     if (op.type == OP_LINEAR) {
       int u0, u1;
       ds_run(op, c.cta, u0, u1);
-      const CUtensorMap* map = p.maps + op.map;
-      const int KT = ds_kt(op), nkg = KT * 4;
+      // a CTA's run of units is one contiguous stretch of memory: pure sequential streaming
+      const uint8_t* wt = op.wt;
       for (int u = u0; u < u1; ++u, ++r) {
-        const int s = r % DS_NS;
-        if (!c.wait_bar(&c.empty[s], ((r / DS_NS) & 1) ^ 1)) return;
-        const int tile = u / KT, kt = u % KT;
-        uint8_t* st = c.stage(s);
+        const int s = r % c.ns;
+        if (!c.wait_bar(&c.empty[s], ((r / c.ns) & 1) ^ 1, 1, oi, r)) return;
         mbar_expect_tx(&c.tfull[s], DS_A + DS_SF);
-        tma_load_2d(st, map, &c.tfull[s], kt * 128, tile * 128);
-        bulk_load(st + DS_A + DS_B, op.sfa + ((size_t)tile * nkg + kt * 4) * 512, DS_SF, &c.tfull[s]);
+        bulk_load(c.stage(s), wt + (size_t)u * (DS_A + DS_SF), DS_A + DS_SF, &c.tfull[s]);
       }
     } else if (op.type == OP_ATTN) {
       const int items = p.M * p.nkv * p.S;
@@ -219,15 +241,15 @@ VE_DEVINL void ds_loader(const Ctx& c) {
         for (int kt = a.kt0; kt < a.kt1; ++kt) {
           if (kt >= safe_end && !fresh) {
             // this page receives the step's own keys: wait until the finalise stage has stored them
-            if (!c.wait_cnt(p.cnt + op.src, p.ops[op.src].ncontrib)) return;
+            if (!c.wait_cnt(p.cnt + op.src, p.ops[op.src].ncontrib, 2, oi)) return;
             fence_proxy_async_all();
             fresh = true;
           }
           const int page = p.page_table[(long)a.slot * p.max_pages + kt];
           const int row = (int)(op.layer * p.pool_layer_rows) + (page * p.nkv + a.kvh) * 64;
           for (int kv = 0; kv < 2; ++kv, ++r) {
-            const int s = r % DS_NS;
-            if (!c.wait_bar(&c.empty[s], ((r / DS_NS) & 1) ^ 1)) return;
+            const int s = r % c.ns;
+            if (!c.wait_bar(&c.empty[s], ((r / c.ns) & 1) ^ 1, 3, oi, r)) return;
             uint8_t* st = c.stage(s);
             const CUtensorMap* map = p.maps + (kv ? p.vmap : p.kmap);
             mbar_expect_tx(&c.tfull[s], DS_A);
@@ -240,42 +262,98 @@ VE_DEVINL void ds_loader(const Ctx& c) {
   }
 }
 
-// ------------------------------------------------------------------------------------------------ MMA issuer (warp 1, lane 0)
-VE_DEVINL void ds_mma(const Ctx& c, uint32_t tmem_base) {
+// ------------------------------------------------------------------------------------------------ MMA issuers (warps 1 and 6, lane 0)
+// Two issuer threads share the units of every run by unit parity, each with its own accumulators and scale columns: one
+// thread's issue rate (about 65 cycles per tcgen05 instruction, thirteen of them per 18 KB unit) is half of what the weight
+// stream needs. The epilogue adds the two accumulators in a fixed order, and the parity is that of the unit's index in
+// the op, so the grouping of the sum does not depend on what ran before.
+VE_DEVINL void ds_mma(const Ctx& c, uint32_t tmem_base, int which) {
   const StepParams& p = *c.p;
   constexpr uint32_t idesc = make_idesc_nvf4(128, 16);
-  const uint32_t tmem_sfa = tmem_base + 64, tmem_sfb = tmem_base + 80;
-  uint32_t r = 0, seg = 0;
+  const uint32_t tmem_acc = tmem_base + which * 64;
+  const uint32_t tmem_sfa = tmem_base + 128 + which * 32, tmem_sfb = tmem_sfa + 16;
+  const uint32_t ring_s = smem_u32(c.smem), cache_s = smem_u32(c.cache);
+  uint32_t r = 0, seg = 0, na = 0;
+  uint32_t g = 0;               // units passed so far (same count in both issuers)
+  uint32_t cpar = 0;            // phase parity of every cache slot's barrier (a slot is filled once per op that uses it)
   for (int oi = 0; oi < p.nops && !c.failed(); ++oi) {
     const StepOp& op = p.ops[oi];
-    if (op.type == OP_ATTN) { r += ds_attn_tiles(p, c.cta, c.G); continue; }
+    if (op.type == OP_ATTN) {
+      // The issuers take no part in attention, but they must not run ahead of it: a parity wait cannot tell a stage's
+      // phase from the one two ring passes earlier, so they wait here until the compute warps have used up the op's pages.
+      if (c.cta < p.M * p.nkv * p.S) {
+        ++na;
+        const uint64_t t0 = globaltimer_ns();
+        while ((int)(*c.attn_seq - na) < 0) {
+          if (c.failed()) return;
+          if (globaltimer_ns() - t0 > kWaitNs) { c.record(13, oi, r, (int)na); c.fail(); return; }
+        }
+      }
+      r += ds_attn_tiles(p, c.cta, c.G);
+      continue;
+    }
     if (op.type != OP_LINEAR) continue;
     int u0, u1;
     ds_run(op, c.cta, u0, u1);
+    if (u0 >= u1) continue;
     const int KT = ds_kt(op);
+    const int nslots = ds_nslots(KT, u0, u1);
+    int kt = u0 % KT, slot = 0;
+    const uint32_t g0 = g;
+    bool seg_start = true, issued = false;
     for (int u = u0; u < u1; ++u, ++r) {
-      const int s = r % DS_NS, kt = u % KT;
       const uint32_t buf = seg & 1;
-      const bool first = kt == 0 || u == u0;
-      if (first && !c.wait_bar(&c.acc_empty[buf], ((seg >> 1) & 1) ^ 1)) return;
-      if (!c.wait_bar(&c.tfull[s], (r / DS_NS) & 1)) return;
-      if (!c.wait_bar(&c.bfull[s], (r / DS_NS) & 1)) return;
-      tc_fence_after();
-      uint8_t* st = c.stage(s);
-      const uint32_t sfa_s = smem_u32(st + DS_A + DS_B), sfb_s = sfa_s + DS_SF;
-#pragma unroll
-      for (int kb = 0; kb < 4; ++kb) {
-        tc_cp_sf(tmem_sfa + kb * 4, make_desc_sf(sfa_s + kb * 512));
-        tc_cp_sf(tmem_sfb + kb * 4, make_desc_sf(sfb_s + kb * 512));
+      if (seg_start) {
+        // the epilogue warps have read this accumulator pair out (their tcgen05.ld is ordered before the arrive); an
+        // issuer without a unit in the segment waits too, so that its arrival below cannot land in the phase before
+        if (!c.wait_bar(&c.acc_empty[buf], ((seg >> 1) & 1) ^ 1, 10, oi, seg)) return;
+        tc_fence_after();
+        seg_start = false;
+        issued = false;
       }
-      const uint64_t ad = make_desc_sw128(smem_u32(st)), bd = make_desc_sw128(smem_u32(st + DS_A));
+      if ((u & 1) == which) {
+        // Stay close to the other issuer: it must have passed every unit of the ops before this one, and be within three
+        // units inside it. An issuer without a unit in a stretch of ops would otherwise run ahead, and a parity wait
+        // cannot tell a barrier's phase from the one two completions earlier: it would take a cache slot (or a ring
+        // stage) that still holds the operand of an earlier op for its own.
+        {
+          const uint32_t need = max(g0, g >= 3u ? g - 3u : 0u);
+          if ((int)(c.prog[which ^ 1] - need) < 0) {
+            const uint64_t t0 = globaltimer_ns();
+            while ((int)(c.prog[which ^ 1] - need) < 0) {
+              if (c.failed()) return;
+              if (globaltimer_ns() - t0 > kWaitNs) { c.record(14, oi, r, (int)g); c.fail(); return; }
+            }
+          }
+        }
+        const int s = r % c.ns;
+        if (!c.wait_bar(&c.tfull[s], (r / c.ns) & 1, 11, oi, r)) return;
+        if (!c.wait_bar(&c.cfull[slot], (cpar >> slot) & 1, 12, oi, slot)) return;
+        const uint32_t st = ring_s + (uint32_t)s * DS_STAGE, bs = cache_s + (uint32_t)slot * DS_SLOT;
 #pragma unroll
-      for (int kb = 0; kb < 4; ++kb)
-        tc_mma_nvf4(tmem_base + buf * 32, ad + kb * 2, bd + kb * 2, idesc, (first && kb == 0) ? 0u : 1u,
-                    tmem_sfa + kb * 4, tmem_sfb + kb * 4);
-      tc_commit(&c.empty[s]);
-      if (kt == KT - 1 || u == u1 - 1) { tc_commit(&c.acc_full[buf]); ++seg; }
+        for (int kb = 0; kb < 4; ++kb) {
+          tc_cp_sf(tmem_sfa + kb * 4, make_desc_sf(st + DS_A + kb * 512));
+          tc_cp_sf(tmem_sfb + kb * 4, make_desc_sf(bs + 2048 + kb * DS_SFB));
+        }
+        const uint64_t ad = make_desc_sw128(st), bd = make_desc_sw128(bs);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)
+          tc_mma_nvf4(tmem_acc + buf * 32, ad + kb * 2, bd + kb * 2, idesc, (!issued && kb == 0) ? 0u : 1u,
+                      tmem_sfa + kb * 4, tmem_sfb + kb * 4);
+        tc_commit(&c.empty[s]);
+        issued = true;
+      }
+      c.prog[which] = ++g;
+      if (++slot == KT) slot = 0;
+      if (++kt == KT || u == u1 - 1) {
+        if (issued) tc_commit(&c.acc_full[buf]);
+        else mbar_arrive(&c.acc_full[buf]);
+        ++seg;
+        kt = 0;
+        seg_start = true;
+      }
     }
+    cpar ^= (nslots >= 32 ? 0xffffffffu : ((1u << nslots) - 1u));
   }
 }
 
@@ -303,6 +381,14 @@ VE_DEVINL void ld8_cg(const __nv_bfloat16* src, float* r) {
     r[2 * j] = f.x; r[2 * j + 1] = f.y;
   }
 }
+VE_DEVINL void unpack8(uint4 raw, float* r) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+    r[2 * j] = f.x; r[2 * j + 1] = f.y;
+  }
+}
 VE_DEVINL uint4 pack8(const float* r) {
   return make_uint4(ds_pack(r[0], r[1]), ds_pack(r[2], r[3]), ds_pack(r[4], r[5]), ds_pack(r[6], r[7]));
 }
@@ -313,7 +399,7 @@ VE_DEVINL uint4 pack8(const float* r) {
 VE_DEVINL bool cw_wait_op(const Ctx& c, Cw& w, int oi, uint32_t need) {
   const int slot = w.nwait++ & 1;
   if (w.ctid == 0) {
-    w.s_ok[slot] = c.wait_cnt(c.p->cnt + oi, need) ? 1 : 0;
+    w.s_ok[slot] = c.wait_cnt(c.p->cnt + oi, need, 20, oi) ? 1 : 0;
     __threadfence();
   }
   bar_compute();
@@ -342,26 +428,44 @@ VE_DEVINL void cw_prologue(const Ctx& c, Cw& w, const StepOp& op) {
     float ss = 0.f;
     int id = 0;
     if (op.in_mode == IN_EMBED) { id = p.ids[m]; id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id); }
-    for (int i = w.ctid * 8; i < H; i += 1024) {
-      float v[8];
-      if (op.in_mode == IN_EMBED) {
-        ld8(p.embed + (size_t)id * H + i, v);
-        if (p.embed_scale != 1.f) {
+    // five 1024-element passes at a time, their loads issued together (one L2 round trip instead of five)
+    for (int i0 = w.ctid * 8; i0 < H; i0 += 5 * 1024) {
+      uint4 hv[5], yv[5];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = round_bf16(v[j] * p.embed_scale);
+      for (int q = 0; q < 5; ++q) {
+        const int i = i0 + q * 1024;
+        if (i < H) {
+          if (op.in_mode == IN_EMBED) {
+            hv[q] = *reinterpret_cast<const uint4*>(p.embed + (size_t)id * H + i);
+          } else {
+            hv[q] = __ldcg(reinterpret_cast<const uint4*>(hin + (size_t)m * H + i));
+            yv[q] = __ldcg(reinterpret_cast<const uint4*>(y + (size_t)m * H + i));
+          }
         }
-      } else {
-        float a[8];
-        ld8_cg(hin + (size_t)m * H + i, v);
-        ld8_cg(y + (size_t)m * H + i, a);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = round_bf16(v[j] + a[j]);
       }
-      const uint4 o = pack8(v);
-      *reinterpret_cast<uint4*>(hrow + (size_t)m * H + i) = o;
-      if (c.cta == 0) *reinterpret_cast<uint4*>(hout + (size_t)m * H + i) = o;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+      for (int q = 0; q < 5; ++q) {
+        const int i = i0 + q * 1024;
+        if (i >= H) continue;
+        float v[8];
+        unpack8(hv[q], v);
+        if (op.in_mode == IN_EMBED) {
+          if (p.embed_scale != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = round_bf16(v[j] * p.embed_scale);
+          }
+        } else {
+          float a[8];
+          unpack8(yv[q], a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = round_bf16(v[j] + a[j]);
+        }
+        const uint4 o = pack8(v);
+        *reinterpret_cast<uint4*>(hrow + (size_t)m * H + i) = o;
+        if (c.cta == 0) *reinterpret_cast<uint4*>(hout + (size_t)m * H + i) = o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+      }
     }
     ss = warp_sum(ss);
     if (w.lane == 0) w.s_red[w.cw * DS_MAXM + m] = ss;
@@ -395,63 +499,76 @@ VE_DEVINL float ds_act(float g, float u, int act, float limit) {
   return a * u;
 }
 
-// B operand of unit u (ring index r): warp-wide, lane = (16-element block, half)
-VE_DEVINL void cw_bfill(const Ctx& c, const Cw& w, const StepOp& op, int u, uint32_t r) {
+// Eight consecutive input values of row m at column k of the op (zero beyond K): the fused part of every linear.
+VE_DEVINL void cw_input8(const Ctx& c, const Cw& w, const StepOp& op, int m, int k, float* x) {
   const StepParams& p = *c.p;
-  const int s = r % DS_NS;
-  int ok = 1;
-  if (w.lane == 0) ok = c.wait_bar(&c.empty[s], ((r / DS_NS) & 1) ^ 1) ? 1 : 0;
-  if (!__shfl_sync(0xffffffffu, ok, 0)) return;
-  const int KT = ds_kt(op), kt = u % KT;
+  if (k >= op.K) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = 0.f;
+  } else if (op.in_mode == IN_X) {
+    ld8_cg(p.attn_out + (size_t)m * op.K + k, x);
+  } else if (op.in_mode == IN_GATED) {
+    // act(gate) * up from the split partials of the gate / up tile that holds column k (64 gate rows, then their 64 up rows)
+    const StepOp& so = p.ops[op.src];
+    const int t = k >> 6, f0 = k & 63;
+    int first, n;
+    ds_splits(so, t, first, n);
+    const float* base = p.ws + so.ws_off + ((size_t)(t * so.ms) * DS_MAXM + m) * 128 + f0;
+    const size_t step = (size_t)DS_MAXM * 128;
+    float g[8], up[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = up[j] = 0.f;
+    for (int sp = 0; sp < n; sp += 2) {
+      // two splits per round, all eight loads in flight together
+      const bool two = sp + 1 < n;
+      const float* b0 = base + sp * step;
+      const float* b1 = two ? b0 + step : b0;
+      const float4 a0 = __ldcg(reinterpret_cast<const float4*>(b0)), a1 = __ldcg(reinterpret_cast<const float4*>(b0 + 4));
+      const float4 a2 = __ldcg(reinterpret_cast<const float4*>(b0 + 64)), a3 = __ldcg(reinterpret_cast<const float4*>(b0 + 68));
+      const float4 c0 = __ldcg(reinterpret_cast<const float4*>(b1)), c1 = __ldcg(reinterpret_cast<const float4*>(b1 + 4));
+      const float4 c2 = __ldcg(reinterpret_cast<const float4*>(b1 + 64)), c3 = __ldcg(reinterpret_cast<const float4*>(b1 + 68));
+      g[0] += a0.x; g[1] += a0.y; g[2] += a0.z; g[3] += a0.w; g[4] += a1.x; g[5] += a1.y; g[6] += a1.z; g[7] += a1.w;
+      up[0] += a2.x; up[1] += a2.y; up[2] += a2.z; up[3] += a2.w; up[4] += a3.x; up[5] += a3.y; up[6] += a3.z; up[7] += a3.w;
+      if (two) {
+        g[0] += c0.x; g[1] += c0.y; g[2] += c0.z; g[3] += c0.w; g[4] += c1.x; g[5] += c1.y; g[6] += c1.z; g[7] += c1.w;
+        up[0] += c2.x; up[1] += c2.y; up[2] += c2.z; up[3] += c2.w; up[4] += c3.x; up[5] += c3.y; up[6] += c3.z; up[7] += c3.w;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = round_bf16(ds_act(g[j] * so.alpha, up[j] * so.alpha, p.act, p.act_limit));
+  } else {
+    float g[8];
+    ld8(reinterpret_cast<const __nv_bfloat16*>(c.scratch) + (size_t)m * p.H + k, x);
+    ld8(op.norm_w + k, g);
+    const float rs = w.s_rs[m];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = round_bf16(x[j] * rs * (g[j] + p.wbias));
+  }
+}
+
+// Operand of k-tile kt into cache slot `slot`: warp-wide, lane = (16-element block, half). The four compute warps take
+// the slots of an op in turn; the issuers wait on the slot's barrier the first time a unit needs it.
+VE_DEVINL void cw_fill_slot(const Ctx& c, const Cw& w, const StepOp& op, int kt, int slot) {
+  const StepParams& p = *c.p;
   const int b = w.lane >> 1, hf = w.lane & 1;
   const int k = kt * 256 + b * 16 + hf * 8;
-  uint8_t* bt = c.stage(s) + DS_A;
-  uint8_t* sf = bt + DS_B + DS_SF;
-  const __nv_bfloat16* hrow = reinterpret_cast<const __nv_bfloat16*>(c.scratch);
+  uint8_t* bt = c.cache + (size_t)slot * DS_SLOT;
+  uint8_t* sf = bt + 2048;
   for (int m = 0; m < p.M; ++m) {
     float x[8];
-    if (k >= op.K) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = 0.f;
-    } else if (op.in_mode == IN_X) {
-      ld8_cg(p.attn_out + (size_t)m * op.K + k, x);
-    } else if (op.in_mode == IN_GATED) {
-      const StepOp& so = p.ops[op.src];
-      const int t = k >> 6, f0 = k & 63;
-      int first, n;
-      ds_splits(so, t, first, n);
-      float g[8], up[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] = up[j] = 0.f;
-      for (int sp = 0; sp < n; ++sp) {
-        const float* base = p.ws + so.ws_off + ((size_t)(t * so.ms + sp) * DS_MAXM + m) * 128 + f0;
-        const float4 g0 = __ldcg(reinterpret_cast<const float4*>(base)), g1 = __ldcg(reinterpret_cast<const float4*>(base + 4));
-        const float4 u0 = __ldcg(reinterpret_cast<const float4*>(base + 64)), u1 = __ldcg(reinterpret_cast<const float4*>(base + 68));
-        g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
-        up[0] += u0.x; up[1] += u0.y; up[2] += u0.z; up[3] += u0.w; up[4] += u1.x; up[5] += u1.y; up[6] += u1.z; up[7] += u1.w;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = round_bf16(ds_act(g[j] * so.alpha, up[j] * so.alpha, p.act, p.act_limit));
-    } else {
-      float g[8];
-      ld8(hrow + (size_t)m * p.H + k, x);
-      ld8(op.norm_w + k, g);
-      const float rs = w.s_rs[m];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = round_bf16(x[j] * rs * (g[j] + p.wbias));
-    }
+    cw_input8(c, w, op, m, k, x);
     uint32_t codes[DS_TERMS], sc[DS_TERMS];
     expand_half8<DS_TERMS>(x, codes, sc);
 #pragma unroll
     for (int t = 0; t < DS_TERMS; ++t) {
       const int v = m * DS_TERMS + t;
       *reinterpret_cast<uint32_t*>(bt + v * 128 + (((b >> 1) ^ (v & 7)) << 4) + (b & 1) * 8 + hf * 4) = codes[t];
-      if (hf == 0) sf[(b >> 2) * 512 + (v & 31) * 16 + (v >> 5) * 4 + (b & 3)] = (uint8_t)sc[t];
+      if (hf == 0) sf[(b >> 2) * DS_SFB + v * 16 + (b & 3)] = (uint8_t)sc[t];
     }
   }
   fence_proxy_async_smem();
   __syncwarp();
-  if (w.lane == 0) mbar_arrive(&c.bfull[s]);
+  if (w.lane == 0) mbar_arrive(&c.cfull[slot]);
 }
 
 VE_DEVINL uint4 ds_ld_volatile_v4(const void* ptr) {
@@ -462,24 +579,31 @@ VE_DEVINL uint4 ds_ld_volatile_v4(const void* ptr) {
 }
 
 // Epilogue of the segment that ends at unit j (tile t): TMEM lane = feature, column m * TERMS + term.
-VE_DEVINL void cw_epilogue(const Ctx& c, const Cw& w, const StepOp& op, int oi, int j, uint32_t seg, uint32_t tmem_base) {
+VE_DEVINL void cw_epilogue(const Ctx& c, const Cw& w, const StepOp& op, int oi, int u0, int j, uint32_t seg, uint32_t tmem_base) {
   const StepParams& p = *c.p;
   const int KT = ds_kt(op), t = j / KT;
   const uint32_t buf = seg & 1;
   const int f = w.q * 32 + w.lane, n = t * 128 + f;
-  const bool ok = c.wait_bar(&c.acc_full[buf], (seg >> 1) & 1);
+  const bool ok = c.wait_bar(&c.acc_full[buf], (seg >> 1) & 1, 22, oi, seg);
   tc_fence_after();
   float acc[DS_MAXM] = {0.f, 0.f, 0.f, 0.f};
   if (ok) {
-    uint32_t r[16];
-    tmem_ld16(tmem_base + ((uint32_t)(w.q * 32) << 16) + buf * 32, r);
-    tmem_ld_wait();
+    // units of the segment alternate between the two issuers by unit parity; a one-unit segment has one accumulator
+    const int js = max(u0, t * KT);
+    const bool has0 = j > js || (j & 1) == 0, has1 = j > js || (j & 1) == 1;
 #pragma unroll
-    for (int m = 0; m < DS_MAXM; ++m) {
-      float v = 0.f, s = 1.f;
+    for (int who = 0; who < 2; ++who) {
+      if (!(who ? has1 : has0)) continue;
+      uint32_t r[16];
+      tmem_ld16(tmem_base + ((uint32_t)(w.q * 32) << 16) + who * 64 + buf * 32, r);
+      tmem_ld_wait();
 #pragma unroll
-      for (int tt = 0; tt < DS_TERMS; ++tt) { v = fmaf(__uint_as_float(r[m * DS_TERMS + tt]), s, v); s *= 0.125f; }
-      acc[m] = v;
+      for (int m = 0; m < DS_MAXM; ++m) {
+        float v = 0.f, s = 1.f;
+#pragma unroll
+        for (int tt = 0; tt < DS_TERMS; ++tt) { v = fmaf(__uint_as_float(r[m * DS_TERMS + tt]), s, v); s *= 0.125f; }
+        acc[m] += v;
+      }
     }
   }
   tc_fence_before();
@@ -627,7 +751,7 @@ VE_DEVINL void cw_qkv_fin(const Ctx& c, Cw& w, const StepOp& op, int oi) {
   cw_signal(c, w, oi);
 }
 
-// Split-KV attention of this CTA's (row, kv head, split) items: each warp scores its own 16 keys of every page.
+// Split-KV attention of this CTA's (row, kv head, split) items.
 VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& r) {
   const StepParams& p = *c.p;
   const int items = p.M * p.nkv * p.S;
@@ -637,7 +761,7 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
   const int lane = w.lane, g = lane >> 2, t4 = lane & 3;
   float* ms = reinterpret_cast<float*>(c.scratch);     // [4][16]
   float* ls = ms + 64;                                   // [4][16]
-  float* os = ls + 64;                                   // [4][16][128]
+  float* os = ls + 64;                                   // [4][G][128]
   for (int it = c.cta; it < items; it += c.G) {
     const AttnItem a = ds_item(p, it);
     bool r_ok[2];
@@ -662,38 +786,43 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
 #pragma unroll
     for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.f, 0.f};
-    const int key0 = w.cw * 16;
-    for (int kt = a.kt0; kt < a.kt1; ++kt) {
-      // K page
-      const int sk = r % DS_NS;
-      const bool okk = c.wait_bar(&c.tfull[sk], (r / DS_NS) & 1);
+    // Each warp takes every fourth page of the item whole (16 query rows x 64 keys), so the page loop has no CTA-wide
+    // barrier: four pages are in flight per CTA, one per warp, and a warp frees its two stages itself.
+    const int npg = a.kt1 - a.kt0;
+    for (int i = w.cw; i < npg; i += 4) {
+      const int kt = a.kt0 + i;
+      const uint32_t rk = r + 2 * i, rv = rk + 1;
+      const int sk = rk % c.ns, sv = rv % c.ns;
+      const bool okk = c.wait_bar(&c.tfull[sk], (rk / c.ns) & 1, 23, oi, rk);
       const uint32_t kb = smem_u32(c.stage(sk));
-      float sacc[2][4];
+      float sacc[8][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+      for (int j = 0; j < 8; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
       if (okk) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const int cch = (kk * 16) / 64, ci = ((kk * 16) % 64) / 8;
-          const int mi = lane >> 3, rr = lane & 7;
-          const int key = key0 + (mi >> 1) * 8 + rr;
-          const int ch = ci + (mi & 1);
-          uint32_t b0, b1, b2, b3;
-          ds_ldsm_x4(kb + cch * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
-          ds_mma_bf16(sacc[0], qf[kk], b0, b1);
-          ds_mma_bf16(sacc[1], qf[kk], b2, b3);
+#pragma unroll
+          for (int np = 0; np < 4; ++np) {
+            const int mi = lane >> 3, rr = lane & 7;
+            const int key = np * 16 + (mi >> 1) * 8 + rr;
+            const int ch = ci + (mi & 1);
+            uint32_t b0, b1, b2, b3;
+            ds_ldsm_x4(kb + cch * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+            ds_mma_bf16(sacc[2 * np], qf[kk], b0, b1);
+            ds_mma_bf16(sacc[2 * np + 1], qf[kk], b2, b3);
+          }
         }
       }
-      bar_compute();
-      if (w.ctid == 0) { mbar_arrive(&c.bfull[sk]); mbar_arrive(&c.empty[sk]); }   // (bfull keeps one phase per ring pass)
-      ++r;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.empty[sk]);
       float mx[2] = {-FLT_MAX, -FLT_MAX};
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int h = e >> 1;
-          const int key = kt * 64 + key0 + nt * 8 + 2 * t4 + (e & 1);
+          const int key = kt * 64 + nt * 8 + 2 * t4 + (e & 1);
           const bool allow = r_ok[h] && key <= a.pos;
           const float v = allow ? sacc[nt][e] * p.scale_log2 : -FLT_MAX;
           sacc[nt][e] = v;
@@ -710,9 +839,9 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
         m_run[h] = m_new;
         l_run[h] *= corr[h];
       }
-      uint32_t pf[4];
+      uint32_t pf[4][4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < 8; ++nt) {
         float pv[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -720,32 +849,33 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
           pv[e] = (sacc[nt][e] == -FLT_MAX) ? 0.f : exp2f(sacc[nt][e] - m_run[h]);
           l_run[h] += pv[e];
         }
-        pf[nt * 2 + 0] = ds_pack(pv[0], pv[1]);
-        pf[nt * 2 + 1] = ds_pack(pv[2], pv[3]);
+        pf[nt >> 1][(nt & 1) * 2 + 0] = ds_pack(pv[0], pv[1]);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = ds_pack(pv[2], pv[3]);
       }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
-      // V page
-      const int sv = r % DS_NS;
-      const bool okv = c.wait_bar(&c.tfull[sv], (r / DS_NS) & 1);
+      for (int j = 0; j < 16; ++j) { o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1]; }
+      const bool okv = c.wait_bar(&c.tfull[sv], (rv / c.ns) & 1, 24, oi, rv);
       const uint32_t vb = smem_u32(c.stage(sv));
       if (okv) {
 #pragma unroll
-        for (int dp = 0; dp < 8; ++dp) {
-          const int mi = lane >> 3, rr = lane & 7;
-          const int key = key0 + (mi & 1) * 8 + rr;
-          const int d = dp * 16 + (mi >> 1) * 8;
-          const int cch = d / 64, ch = (d % 64) / 8;
-          uint32_t b0, b1, b2, b3;
-          ds_ldsm_x4_t(vb + cch * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
-          ds_mma_bf16(o[2 * dp], pf, b0, b1);
-          ds_mma_bf16(o[2 * dp + 1], pf, b2, b3);
+        for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+          for (int dp = 0; dp < 8; ++dp) {
+            const int mi = lane >> 3, rr = lane & 7;
+            const int key = ks * 16 + (mi & 1) * 8 + rr;
+            const int d = dp * 16 + (mi >> 1) * 8;
+            const int cch = d / 64, ch = (d % 64) / 8;
+            uint32_t b0, b1, b2, b3;
+            ds_ldsm_x4_t(vb + cch * 8192 + key * 128 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+            ds_mma_bf16(o[2 * dp], pf[ks], b0, b1);
+            ds_mma_bf16(o[2 * dp + 1], pf[ks], b2, b3);
+          }
         }
       }
-      bar_compute();
-      if (w.ctid == 0) { mbar_arrive(&c.bfull[sv]); mbar_arrive(&c.empty[sv]); }
-      ++r;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.empty[sv]);
     }
+    r += 2 * npg;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -759,7 +889,7 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
       if (row < G) {
 #pragma unroll
         for (int nt = 0; nt < 16; ++nt)
-          *reinterpret_cast<float2*>(os + (size_t)(w.cw * 16 + row) * 128 + nt * 8 + 2 * t4) =
+          *reinterpret_cast<float2*>(os + (size_t)(w.cw * G + row) * 128 + nt * 8 + 2 * t4) =
               make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
       }
     }
@@ -775,7 +905,7 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
         const float mw = ms[ww * 16 + row];
         if (mw != -FLT_MAX) {
           const float cc = exp2f(mw - m);
-          acc += os[(size_t)(ww * 16 + row) * 128 + d] * cc;
+          acc += os[(size_t)(ww * G + row) * 128 + d] * cc;
           l += ls[ww * 16 + row] * cc;
         }
       }
@@ -787,6 +917,7 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
     bar_compute();
   }
   cw_signal(c, w, oi);
+  if (w.ctid == 0) { __threadfence_block(); *c.attn_seq = *c.attn_seq + 1; }
 }
 
 // One (row, head) per CTA: merge the split partials in split order.
@@ -823,9 +954,15 @@ VE_DEVINL void ds_compute(const Ctx& c, Cw& w, uint32_t tmem_base) {
     bar_compute();
     if (w.s_ok[2 + (oi & 1)]) break;
     const StepOp& op = p.ops[oi];
-    if (op.type == OP_QKV_FIN) { cw_qkv_fin(c, w, op, oi); continue; }
-    if (op.type == OP_ATTN) { cw_attn(c, w, op, oi, r); continue; }
-    if (op.type == OP_MERGE) { cw_merge(c, w, op, oi); continue; }
+    const bool prof = p.prof && c.cta == p.prof_cta && w.ctid == 0;
+    if (prof) p.prof[oi * 4] = globaltimer_ns();
+    if (op.type != OP_LINEAR && op.type != OP_NORMOUT) {
+      if (op.type == OP_QKV_FIN) cw_qkv_fin(c, w, op, oi);
+      else if (op.type == OP_ATTN) cw_attn(c, w, op, oi, r);
+      else cw_merge(c, w, op, oi);
+      if (prof) p.prof[oi * 4 + 3] = globaltimer_ns();
+      continue;
+    }
     if (op.type == OP_NORMOUT) {               // final residual add + norm when the LM head runs outside this kernel
       if (c.cta == 0) cw_prologue(c, w, op);
       continue;
@@ -834,52 +971,60 @@ VE_DEVINL void ds_compute(const Ctx& c, Cw& w, uint32_t tmem_base) {
     ds_run(op, c.cta, u0, u1);
     if (u0 >= u1) continue;
     cw_prologue(c, w, op);
+    if (prof) p.prof[oi * 4 + 1] = globaltimer_ns();
     const int KT = ds_kt(op);
-    for (int u = u0; u < u1; ++u, ++r) {
-      if ((int)(r & 3) == w.cw) cw_bfill(c, w, op, u, r);
-      const int j = u - DS_LOOK;
-      if (j >= u0 && (j % KT == KT - 1)) cw_epilogue(c, w, op, oi, j, seg++, tmem_base);
-    }
-    for (int j = max(u0, u1 - DS_LOOK); j < u1; ++j)
-      if (j % KT == KT - 1 || j == u1 - 1) cw_epilogue(c, w, op, oi, j, seg++, tmem_base);
+    // the operand of every k-tile of the run, once (the previous op's products have all been read: its last epilogue
+    // waited for them), in the order the units need them
+    const int nslots = ds_nslots(KT, u0, u1);
+    for (int i = w.cw; i < nslots; i += 4) cw_fill_slot(c, w, op, (u0 + i) % KT, i);
+    if (prof) p.prof[oi * 4 + 2] = globaltimer_ns();
+    for (int j = u0; j < u1; ++j)
+      if (j % KT == KT - 1 || j == u1 - 1) cw_epilogue(c, w, op, oi, u0, j, seg++, tmem_base);
+    r += (uint32_t)(u1 - u0);
     if (op.out_mode == OUT_PART) cw_signal(c, w, oi);
+    if (prof) p.prof[oi * 4 + 3] = globaltimer_ns();
   }
 }
 
-__global__ void __launch_bounds__(192, 1) decode_step_kernel(const __grid_constant__ StepParams p) {
+__global__ void __launch_bounds__(224, 1) decode_step_kernel(const __grid_constant__ StepParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t tfull[DS_NS], bfull[DS_NS], empty[DS_NS], acc_full[2], acc_empty[2];
+  __shared__ uint64_t tfull[DS_MAXNS], empty[DS_MAXNS], cfull[DS_SLOTS], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_holder;
   __shared__ int s_fail, s_flag, s_last, s_ok[4];
+  __shared__ uint32_t s_attn_seq, s_prog[2];
   __shared__ float s_rs[DS_MAXM], s_red[4 * DS_MAXM];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < DS_NS; ++s) { mbar_init(&tfull[s], 1); mbar_init(&bfull[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 1); }
+    for (int s = 0; s < DS_MAXNS; ++s) { mbar_init(&tfull[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < DS_SLOTS; ++s) mbar_init(&cfull[s], 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 2); mbar_init(&acc_empty[b], 1); }
     // a status word left set by an earlier failure makes every wait of this launch give up at once
     s_fail = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    s_attn_seq = 0;
+    s_prog[0] = s_prog[1] = 0;
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(&tmem_holder, DS_TMEM); tmem_relinquish(); }
-  if (warp >= 2) {
-    // scale bytes of the B rows that no activation row uses stay zero
-    const int ctid = threadIdx.x - 64;
-    for (int s = 0; s < DS_NS; ++s)
-      *reinterpret_cast<uint4*>(smem + (size_t)s * DS_STAGE + DS_A + DS_B + DS_SF + ctid * 16) = make_uint4(0, 0, 0, 0);
+  {
+    // operand rows and scale bytes that no activation row uses stay zero for the whole launch (a stray scale byte in an
+    // unused column costs the used columns their precision)
+    uint8_t* cache0 = smem + (size_t)p.ns * DS_STAGE;
+    for (int i = threadIdx.x * 16; i < DS_CACHE; i += blockDim.x * 16) *reinterpret_cast<uint4*>(cache0 + i) = make_uint4(0, 0, 0, 0);
     fence_proxy_async_smem();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_holder;
-  Ctx c{&p, smem, smem + (size_t)DS_NS * DS_STAGE, tfull, bfull, empty, acc_full, acc_empty, &s_fail,
-        (int)blockIdx.x, (int)gridDim.x};
+  // shared memory: ring stages | operand cache | scratch (row(s) of the normalised input, attention merge)
+  Ctx c{&p, smem, smem + (size_t)p.ns * DS_STAGE, smem + (size_t)p.ns * DS_STAGE + DS_CACHE, tfull, cfull, empty, acc_full,
+        acc_empty, p.ns, &s_fail, &s_attn_seq, s_prog, (int)blockIdx.x, (int)gridDim.x};
   if (warp == 0) {
     if (lane == 0) ds_loader(c);
-  } else if (warp == 1) {
-    if (lane == 0) ds_mma(c, tmem_base);
+  } else if (warp == 1 || warp == 6) {
+    if (lane == 0) ds_mma(c, tmem_base, warp == 1 ? 0 : 1);
   } else {
     Cw w{(int)threadIdx.x - 64, warp - 2, lane, warp & 3, s_rs, s_red, &s_flag, s_ok, 0};
     ds_compute(c, w, tmem_base);
@@ -888,7 +1033,7 @@ __global__ void __launch_bounds__(192, 1) decode_step_kernel(const __grid_consta
   __syncthreads();
   if (s_fail && threadIdx.x == 0) {
     // after a failed wait copies of the loader may still be in flight: give each stage a short time to land
-    for (int s = 0; s < DS_NS; ++s) {
+    for (int s = 0; s < p.ns; ++s) {
       mbar_wait(&tfull[s], 0, 2000000ull);
       mbar_wait(&tfull[s], 1, 2000000ull);
     }
@@ -937,10 +1082,17 @@ int ve_make_tmap_2d(void* out, const void* base, int dtype, int elem_bytes, long
 
 // params: host copy of StepParams. ctas: one per SM (all must be resident together: cooperative launch).
 int ve_decode_step(const void* params, int ctas, int cooperative, cudaStream_t st) {
-  const StepParams& p = *reinterpret_cast<const StepParams*>(params);
-  if (p.M < 1 || p.M > DS_MAXM || p.H % 8 || (size_t)p.M * p.H * 2 > DS_SCR || p.nq % p.nkv || p.nq / p.nkv > 16 ||
-      p.S < 1 || ctas < 1 || p.size < 1 || p.size > 8)
+  StepParams p = *reinterpret_cast<const StepParams*>(params);
+  if (p.M < 1 || p.M > DS_MAXM || p.H % 8 || p.nkv < 1 || p.nq % p.nkv || p.nq / p.nkv > 16 || p.S < 1 || ctas < 1 ||
+      p.size < 1 || p.size > 8)
     return cudaErrorInvalidValue;
+  // scratch: the normalised-input rows of a linear, or the four warps' attention states; the ring takes what is left
+  const int G = p.nq / p.nkv;
+  const int need = max(p.M * p.H * 2, 512 + 4 * G * 128 * 4);
+  p.scr = (need + 1023) / 1024 * 1024;
+  p.ns = (DS_SMEM - 1024 - DS_CACHE - p.scr) / DS_STAGE;
+  if (p.ns > DS_MAXNS) p.ns = DS_MAXNS;
+  if (p.ns < 3) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DS_SMEM);
@@ -949,7 +1101,7 @@ int ve_decode_step(const void* params, int ctas, int cooperative, cudaStream_t s
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ctas);
-  cfg.blockDim = dim3(192);
+  cfg.blockDim = dim3(224);
   cfg.dynamicSmemBytes = DS_SMEM;
   cfg.stream = st;
   cudaLaunchAttribute at[1];

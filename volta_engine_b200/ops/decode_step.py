@@ -22,6 +22,7 @@ OP_LINEAR, OP_QKV_FIN, OP_ATTN, OP_MERGE, OP_NORMOUT = 0, 1, 2, 3, 4
 IN_X, IN_NORM, IN_GATED, IN_EMBED = 0, 1, 2, 3
 OUT_PART, OUT_LOGITS, OUT_TICKET = 0, 1, 2
 MAXM = 4
+CACHE_SLOTS = 20          # k-tiles of one op a CTA keeps expanded (DS_SLOTS of the kernel)
 
 ENABLED = os.environ.get("VOLTA_PSTEP", "1") != "0"
 COOPERATIVE = os.environ.get("VOLTA_PSTEP_COOP", "1") != "0"
@@ -33,19 +34,19 @@ class StepOp(ctypes.Structure):
                 ("N", ctypes.c_int), ("K", ctypes.c_int), ("upc", ctypes.c_int), ("src", ctypes.c_int),
                 ("alpha", ctypes.c_float), ("ws_off", ctypes.c_int), ("ms", ctypes.c_int), ("tk_off", ctypes.c_int),
                 ("ncontrib", ctypes.c_int), ("layer", ctypes.c_int), ("hpar", ctypes.c_int), ("ypar", ctypes.c_int),
-                ("ar", ctypes.c_int), ("flags", ctypes.c_int), ("sfa", ctypes.c_void_p), ("norm_w", ctypes.c_void_p)]
+                ("ar", ctypes.c_int), ("flags", ctypes.c_int), ("wt", ctypes.c_void_p), ("norm_w", ctypes.c_void_p)]
 
 
 class StepParams(ctypes.Structure):
     """Mirror of ``ve::StepParams``."""
     _fields_ = [(n, ctypes.c_void_p) for n in (
         "ops", "maps", "cnt", "ctrl", "tickets", "ws", "ybuf", "hbuf", "qbuf", "attn_out", "o_part", "lse_part", "xfinal",
-        "logits", "ids", "pos", "slot", "page_table", "embed", "kpool", "vpool", "status")] + [
+        "logits", "ids", "pos", "slot", "page_table", "embed", "kpool", "vpool", "status", "prof", "dbg")] + [
         ("peer", ctypes.c_void_p * 8), ("seq", ctypes.c_void_p),
         ("off_ll", ctypes.c_ulonglong), ("ll_row_bytes", ctypes.c_ulonglong), ("budget_ns", ctypes.c_ulonglong),
         ("ldl", ctypes.c_long), ("pool_layer_rows", ctypes.c_long)] + [(n, ctypes.c_int) for n in (
         "nops", "kmap", "vmap", "M", "H", "nq", "nkv", "S", "max_pages", "vocab", "rot", "act", "rank", "size", "n_ar",
-        "pad0")] + [(n, ctypes.c_float) for n in ("eps", "wbias", "scale_log2", "rope_theta", "act_limit", "embed_scale")]
+        "prof_cta", "ns", "scr")] + [(n, ctypes.c_float) for n in ("eps", "wbias", "scale_log2", "rope_theta", "act_limit", "embed_scale")]
 
 
 _sizes = None
@@ -87,6 +88,26 @@ def padded_atoms(lin) -> torch.Tensor:
     if pad:
         a = torch.cat([a, torch.zeros(N // 128, pad, 512, dtype=a.dtype, device=a.device)], 1).contiguous()
     return a
+
+
+def weight_units(lin) -> torch.Tensor:
+    """The weight of an NVFP4 linear as the step kernel streams it: [N/128][ceil(K/256)][18432] bytes, each unit the
+    128 x 128 B tile of packed codes laid out as the 128-byte swizzle puts it in shared memory (16-byte chunk c of row r
+    at chunk c ^ (r & 7)), followed by the tile's four 512 B scale atoms. Units of one tile row follow each other, so a
+    CTA's run of units is one contiguous read."""
+    N, Kk = lin.out_features, lin.in_features
+    NT, KT = N // 128, (Kk + 255) // 256
+    pk = lin.packed
+    if pk.shape[1] != KT * 128:
+        pk = torch.cat([pk, torch.zeros(N, KT * 128 - pk.shape[1], dtype=pk.dtype, device=pk.device)], 1)
+    src = pk.view(NT, 16, 8, KT, 8, 16)                     # tile, row group, row in group, k-tile, chunk, byte
+    out = torch.empty(NT, KT, 18432, dtype=torch.uint8, device=pk.device)
+    dst = out[:, :, :16384].view(NT, KT, 16, 8, 8, 16)      # tile, k-tile, row group, row in group, chunk, byte
+    ch = torch.arange(8, device=pk.device)
+    for j in range(8):
+        dst[:, :, :, j] = src[:, :, j].index_select(3, ch ^ j).permute(0, 2, 1, 3, 4)
+    out[:, :, 16384:] = padded_atoms(lin).reshape(NT, KT, 2048)
+    return out
 
 
 def _splits(NT: int, KT: int, upc: int) -> int:
@@ -136,11 +157,12 @@ class StepProgram:
                 tk_total += NT
             o.ws_off, o.tk_off = ws_off[kind], tk_off[kind]
             o.ncontrib = NT if out_mode == OUT_TICKET else (U + upc - 1) // upc
-            atoms = padded_atoms(lin)
-            self._keep.append(atoms)
-            o.sfa = atoms.data_ptr()
-            o.map = len(maps)
-            maps.append(_tmap(lin.packed.data_ptr(), 0, 1, N, Kk // 2, Kk // 2, 128, 128))
+            if min(KT, upc) > CACHE_SLOTS:
+                raise ValueError(f"{kind}: {min(KT, upc)} k-tiles per CTA exceed the kernel's operand cache")
+            units = getattr(lin, "_step_units", None)        # built once per weight, shared by the programs of all row counts
+            if units is None:
+                units = lin._step_units = weight_units(lin)
+            o.wt = units.data_ptr()
             if norm_w is not None:
                 o.norm_w = norm_w.data_ptr()
             if in_mode == IN_EMBED:
@@ -218,6 +240,8 @@ class StepProgram:
         p.page_table, p.embed = kv.page_table.data_ptr(), model.embed.data_ptr()
         p.kpool, p.vpool = kv.k.data_ptr(), kv.v.data_ptr()
         p.status = K.status_word(dev).data_ptr()
+        self.dbg = torch.zeros(8 + 6 * 1000, dtype=torch.int32, device=dev)
+        p.dbg = self.dbg.data_ptr()
         p.ldl = model.vocab_local
         p.pool_layer_rows = pages * nkv * 64
         p.nops, p.kmap, p.vmap, p.M, p.H, p.nq, p.nkv, p.S = self.nops, kmap, kmap + 1, M, H, nq, nkv, self.S
@@ -232,6 +256,12 @@ class StepProgram:
                 p.peer[i] = a.peer[i]
             p.seq, p.off_ll, p.ll_row_bytes, p.budget_ns = a.seq, a.off_ll, a.ll_row_bytes, a.budget_ns
         self.params = p
+
+    def enable_profile(self, cta: int = 0):
+        """Per-op device timestamps of one CTA (ns): op entered, input ready, units done, op left."""
+        self.prof = torch.zeros(self.nops, 4, dtype=torch.int64, device=self.dbg.device)
+        self.params.prof, self.params.prof_cta = self.prof.data_ptr(), cta
+        return self.prof
 
     def reset(self):
         """Host-side recovery after a step that gave up on a wait: arrival counters and tickets back to zero."""
@@ -272,6 +302,15 @@ def supported(model, b, kv) -> bool:
                 ok = ok and isinstance(lin, LinearNVFP4) and lin.packed.is_cuda and lin.out_features % 128 == 0 \
                     and lin.in_features % 128 == 0
             ok = ok and getattr(L.gate_up, "gated", False)
+        if ok:
+            G = torch.cuda.get_device_properties(model.device).multi_processor_count
+            lins = [lin for L in model.layers for lin in (L.qkv, L.o_proj, L.gate_up, L.down)]
+            if isinstance(model.lm_head, LinearNVFP4):
+                lins.append(model.lm_head)
+            for lin in lins:
+                NT, KT = lin.out_features // 128, (lin.in_features + 255) // 256
+                upc = KT * ((NT + G - 1) // G) if lin is model.lm_head else (NT * KT + G - 1) // G
+                ok = ok and min(KT, upc) <= CACHE_SLOTS
         model._pstep_static = bool(ok)
     if not ok or kv.fmt != 0 or kv.head_dim != 128 or kv.v_head_dim != 128:
         return False
