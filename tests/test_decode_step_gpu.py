@@ -40,26 +40,22 @@ def test_step_matches_kernel_path(cfg_kw):
     from volta_engine_b200.ops import decode_step as PS
     from volta_engine_b200.ops import kernels as K
     dev, cfg, model, kv, eng, prompt = _setup(cfg_kw)
-    PS.ENABLED = False
-    try:
+    with PS.enabled(False):
         tok = eng.prefill(0, prompt)
-    finally:
-        PS.ENABLED = True
     n = len(prompt)
     for rows in (1, 3, 4):
         ids = [tok] + prompt[:rows - 1]
         pos = list(range(n, n + rows))
         kv.reserve(0, n + rows + 1)
-        PS.ENABLED = False
-        try:
+        with PS.enabled(False):
             want = _rows(model, kv, ids, pos, [0] * rows, dev)
             hid_want = model.last_hidden.clone()
-        finally:
-            PS.ENABLED = True
-        got = _rows(model, kv, ids, pos, [0] * rows, dev)
+        with PS.enabled(True):
+            got = _rows(model, kv, ids, pos, [0] * rows, dev)
+            hid_got = model.last_hidden.clone()
         assert got.shape == want.shape
         assert _cos(got, want) > 0.9995, (rows, _cos(got, want))
-        assert _cos(model.last_hidden, hid_want) > 0.9995
+        assert _cos(hid_got, hid_want) > 0.9995
         assert torch.equal(got.argmax(-1), want.argmax(-1)) or _cos(got, want) > 0.9999
     assert K.check_status(dev) == 0
 
@@ -67,21 +63,16 @@ def test_step_matches_kernel_path(cfg_kw):
 def test_step_two_slots_and_padding_row():
     from volta_engine_b200.ops import decode_step as PS
     dev, cfg, model, kv, eng, prompt = _setup(BASE)
-    PS.ENABLED = False
-    try:
+    with PS.enabled(False):
         t0 = eng.prefill(0, prompt)
         t1 = eng.prefill(1, prompt[:170])
-    finally:
-        PS.ENABLED = True
     kv.reserve(0, len(prompt) + 2)
     kv.reserve(1, 172)
     ids, pos, slots = [t0, t1, 5], [len(prompt), 170, 0], [0, 1, -1]
-    PS.ENABLED = False
-    try:
+    with PS.enabled(False):
         want = _rows(model, kv, ids, pos, slots, dev)
-    finally:
-        PS.ENABLED = True
-    got = _rows(model, kv, ids, pos, slots, dev)
+    with PS.enabled(True):
+        got = _rows(model, kv, ids, pos, slots, dev)
     assert _cos(got[:2], want[:2]) > 0.9995
 
 
@@ -92,15 +83,12 @@ def test_step_greedy_tokens_and_graph_replay():
     dev, cfg, model, kv, eng, prompt = _setup(BASE, prompt_len=200)
     outs = {}
     for mode in ("kernels", "step_eager", "step_graph"):
-        PS.ENABLED = mode != "kernels"
-        try:
+        with PS.enabled(mode != "kernels"):
             kv2 = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, 48, 2, 1024, dev)
             e = Engine(model, kv2, prefill_chunk=128, use_graphs=mode == "step_graph")
             first = e.prefill(0, prompt)
             toks = e.decode_chain([first], [len(prompt)], [0], 12)
             outs[mode] = [first] + toks[:, 0].tolist()
-        finally:
-            PS.ENABLED = True
     assert outs["step_eager"] == outs["step_graph"], outs
     same = sum(a == b for a, b in zip(outs["kernels"], outs["step_eager"]))
     assert same >= len(outs["kernels"]) - 1 or outs["kernels"][:4] == outs["step_eager"][:4], outs
@@ -111,21 +99,22 @@ def test_step_drains_at_once_when_status_is_set():
     returns in well under the one-second wait budget, leaves the status in place and the context stays usable."""
     import time
     from volta_engine_b200.ops import kernels as K
+    from volta_engine_b200.ops import decode_step as PS
     dev, cfg, model, kv, eng, prompt = _setup(BASE, prompt_len=80)
     tok = eng.prefill(0, prompt)
     kv.reserve(0, len(prompt) + 4)
-    good = _rows(model, kv, [tok], [len(prompt)], [0], dev)
-    st = K.status_word(dev)
-    st.fill_(2)
-    torch.cuda.synchronize()
-    t0 = time.time()
-    _rows(model, kv, [tok], [len(prompt)], [0], dev)
-    torch.cuda.synchronize()
-    assert time.time() - t0 < 0.5
-    assert int(st.item()) == 2
-    st.zero_()
-    from volta_engine_b200.ops import decode_step as PS
-    for prog in model._pstep_programs.values():      # counters of an aborted step are reset by the host
-        prog.reset()
-    again = _rows(model, kv, [tok], [len(prompt)], [0], dev)
+    with PS.enabled(True):
+        good = _rows(model, kv, [tok], [len(prompt)], [0], dev)
+        st = K.status_word(dev)
+        st.fill_(2)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        _rows(model, kv, [tok], [len(prompt)], [0], dev)
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 0.5
+        assert int(st.item()) == 2
+        st.zero_()
+        for prog in model._pstep_programs.values():      # counters of an aborted step are reset by the host
+            prog.reset()
+        again = _rows(model, kv, [tok], [len(prompt)], [0], dev)
     assert _cos(again, good) > 0.9999

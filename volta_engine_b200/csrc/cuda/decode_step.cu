@@ -134,6 +134,7 @@ struct Ctx {
   volatile int* s_fail;
   volatile uint32_t* attn_seq;   // attention ops this CTA's compute warps have finished
   volatile uint32_t* prog;       // [2] units each issuer has passed
+  volatile uint32_t* kv_seq;     // attention items whose new keys / values this CTA has stored
   int cta, G;
   VE_DEVINL uint8_t* stage(int s) const { return smem + (size_t)s * DS_STAGE; }
   VE_DEVINL bool failed() const { return *s_fail != 0; }
@@ -215,7 +216,7 @@ VE_DEVINL int ds_attn_tiles(const StepParams& p, int cta, int G) {
 // ------------------------------------------------------------------------------------------------ loader (warp 0, lane 0)
 VE_DEVINL void ds_loader(const Ctx& c) {
   const StepParams& p = *c.p;
-  uint32_t r = 0;
+  uint32_t r = 0, nitems = 0;
   for (int oi = 0; oi < p.nops && !c.failed(); ++oi) {
     const StepOp& op = p.ops[oi];
     if (op.type == OP_LINEAR) {
@@ -235,13 +236,19 @@ VE_DEVINL void ds_loader(const Ctx& c) {
       for (int m = 0; m < p.M; ++m)
         if (!p.slot || p.slot[m] >= 0) pos_min = min(pos_min, p.pos[m]);
       const int safe_end = pos_min / 64;        // pages below hold tokens of earlier steps only
-      bool fresh = false;
       for (int it = c.cta; it < items; it += c.G) {
         const AttnItem a = ds_item(p, it);
+        ++nitems;
+        bool fresh = false;
         for (int kt = a.kt0; kt < a.kt1; ++kt) {
           if (kt >= safe_end && !fresh) {
-            // this page receives the step's own keys: wait until the finalise stage has stored them
-            if (!c.wait_cnt(p.cnt + op.src, p.ops[op.src].ncontrib, 2, oi)) return;
+            // this page receives the step's own keys: the compute warps of this CTA store them (from the qkv partial
+            // sums) before they start on the item, and say so through shared memory
+            const uint64_t t0 = globaltimer_ns();
+            while ((int)(*c.kv_seq - nitems) < 0) {
+              if (c.failed()) return;
+              if (globaltimer_ns() - t0 > kWaitNs) { c.record(2, oi, r, (int)nitems); c.fail(); return; }
+            }
             fence_proxy_async_all();
             fresh = true;
           }
@@ -762,6 +769,7 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
   float* ms = reinterpret_cast<float*>(c.scratch);     // [4][16]
   float* ls = ms + 64;                                   // [4][16]
   float* os = ls + 64;                                   // [4][G][128]
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(os + 4 * G * 128);   // [G][128] rotated query heads of the item
   for (int it = c.cta; it < items; it += c.G) {
     const AttnItem a = ds_item(p, it);
     bool r_ok[2];
@@ -772,14 +780,68 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
       r_ok[h] = rr < G;
       r_head[h] = a.kvh * G + (r_ok[h] ? rr : 0);
     }
+    // Finalise the qkv projection for this item: the G query heads of its row (split sum, rounding, rotation) go to
+    // shared memory; the key and value head of every row of the same sequence whose position lies in this item's pages
+    // go into the paged cache (several CTAs may store the same row: same bits). 64 threads per head, one rotary pair each.
+    {
+      const StepOp& so = p.ops[op.src];
+      const int f = w.ctid & 63, half = p.rot >> 1;
+      const float inv_freq = exp2f(-log2f(p.rope_theta) * (2.f * (float)f / (float)p.rot));
+      const int njobs = G + 2 * p.M;
+      for (int job = w.ctid >> 6; job < njobs; job += 2) {
+        const bool isq = job < G;
+        const int m = isq ? a.row : (job - G) >> 1;
+        const bool is_v = !isq && ((job - G) & 1);
+        const int head = isq ? a.kvh * G + job : p.nq + (is_v ? p.nkv : 0) + a.kvh;
+        const int ps = p.pos[m];
+        const int sl = p.slot ? p.slot[m] : 0;
+        if (!isq && (sl != a.slot || sl < 0 || ps / 64 < a.kt0 || ps / 64 >= a.kt1)) continue;
+        int i0, i1;
+        if (is_v) { i0 = 2 * f; i1 = i0 + 1; }
+        else if (f < half) { i0 = f; i1 = f + half; }
+        else { i0 = p.rot + 2 * (f - half); i1 = i0 + 1; }
+        int first, nsp;
+        ds_splits(so, head, first, nsp);
+        const float* base = p.ws + so.ws_off + ((size_t)(head * so.ms) * DS_MAXM + m) * 128;
+        float a0 = 0.f, a1 = 0.f;
+        for (int sp = 0; sp < nsp; ++sp) {
+          a0 += __ldcg(base + (size_t)sp * DS_MAXM * 128 + i0);
+          a1 += __ldcg(base + (size_t)sp * DS_MAXM * 128 + i1);
+        }
+        a0 = round_bf16(a0 * so.alpha);
+        a1 = round_bf16(a1 * so.alpha);
+        if (!is_v && f < half) {
+          float sn, cs;
+          sincosf((float)ps * inv_freq, &sn, &cs);
+          const float r0 = a0 * cs - a1 * sn, r1 = a1 * cs + a0 * sn;
+          a0 = r0;
+          a1 = r1;
+        }
+        const __nv_bfloat16 b0 = f2bf(a0), b1 = f2bf(a1);
+        if (isq) {
+          qs[job * 128 + i0] = b0;
+          qs[job * 128 + i1] = b1;
+        } else {
+          const int page = p.page_table[(long)sl * p.max_pages + ps / 64];
+          const long dst = ((long)op.layer * p.pool_layer_rows + ((long)page * p.nkv + a.kvh) * 64 + (ps % 64)) * 128;
+          __nv_bfloat16* pool = is_v ? p.vpool : p.kpool;
+          pool[dst + i0] = b0;
+          pool[dst + i1] = b1;
+        }
+      }
+      fence_proxy_async_all();       // the cache rows are read back through TMA by this CTA's loader
+      __threadfence();
+      bar_compute();
+      if (w.ctid == 0) *c.kv_seq = *c.kv_seq + 1;
+    }
     uint32_t qf[8][4];
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const __nv_bfloat16* qr = p.qbuf + (size_t)a.row * p.nq * 128 + (size_t)r_head[h] * 128 + kk * 16 + 2 * t4;
-        qf[kk][h] = r_ok[h] ? __ldcg(reinterpret_cast<const uint32_t*>(qr)) : 0u;
-        qf[kk][2 + h] = r_ok[h] ? __ldcg(reinterpret_cast<const uint32_t*>(qr + 8)) : 0u;
+        const __nv_bfloat16* qr = qs + (r_ok[h] ? g + h * 8 : 0) * 128 + kk * 16 + 2 * t4;
+        qf[kk][h] = r_ok[h] ? *reinterpret_cast<const uint32_t*>(qr) : 0u;
+        qf[kk][2 + h] = r_ok[h] ? *reinterpret_cast<const uint32_t*>(qr + 8) : 0u;
       }
     }
     float o[16][4];
@@ -920,27 +982,45 @@ VE_DEVINL void cw_attn(const Ctx& c, Cw& w, const StepOp& op, int oi, uint32_t& 
   if (w.ctid == 0) { __threadfence_block(); *c.attn_seq = *c.attn_seq + 1; }
 }
 
-// One (row, head) per CTA: merge the split partials in split order.
+// One (row, head) per CTA: merge the split partials in split order. The split weights are computed once by the block
+// (a thread per split) and shared; empty splits (sequence shorter than the split grid) cost one comparison.
 VE_DEVINL void cw_merge(const Ctx& c, Cw& w, const StepOp& op, int oi) {
   const StepParams& p = *c.p;
   const int items = p.M * p.nq;
   if (c.cta >= items) return;
   if (!cw_wait_op(c, w, op.src, p.ops[op.src].ncontrib)) return;
   const int d = w.ctid;
+  float* wts = reinterpret_cast<float*>(c.scratch);      // [S] weights, then [4] warp maxima / sums
+  float* red = wts + ((p.S + 3) & ~3);
   for (int it = c.cta; it < items; it += c.G) {
     const int row = it / p.nq, head = it % p.nq;
     const long base = ((long)row * p.nq + head) * p.S;
     float mx = -FLT_MAX;
-    for (int i = 0; i < p.S; ++i) mx = fmaxf(mx, __ldcg(p.lse_part + base + i));
-    float acc = 0.f, wsum = 0.f;
-    for (int i = 0; i < p.S; ++i) {
+    for (int i = w.ctid; i < p.S; i += 128) {
       const float l = __ldcg(p.lse_part + base + i);
-      if (l == -FLT_MAX) continue;
-      const float wt = exp2f(l - mx);
+      wts[i] = l;
+      mx = fmaxf(mx, l);
+    }
+    mx = warp_max(mx);
+    if (w.lane == 0) red[w.cw] = mx;
+    bar_compute();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    bar_compute();
+    for (int i = w.ctid; i < p.S; i += 128) {
+      const float l = wts[i];
+      wts[i] = (l == -FLT_MAX) ? 0.f : exp2f(l - mx);
+    }
+    bar_compute();
+    float acc = 0.f, wsum = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < p.S; ++i) {
+      const float wt = wts[i];
+      if (wt == 0.f) continue;
       wsum += wt;
       acc += wt * __ldcg(p.o_part + (base + i) * 128 + d);
     }
     p.attn_out[(size_t)row * p.nq * 128 + head * 128 + d] = f2bf(wsum > 0.f ? acc / wsum : 0.f);
+    bar_compute();
   }
   cw_signal(c, w, oi);
 }
@@ -992,7 +1072,7 @@ __global__ void __launch_bounds__(224, 1) decode_step_kernel(const __grid_consta
   __shared__ uint64_t tfull[DS_MAXNS], empty[DS_MAXNS], cfull[DS_SLOTS], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_holder;
   __shared__ int s_fail, s_flag, s_last, s_ok[4];
-  __shared__ uint32_t s_attn_seq, s_prog[2];
+  __shared__ uint32_t s_attn_seq, s_prog[2], s_kv_seq;
   __shared__ float s_rs[DS_MAXM], s_red[4 * DS_MAXM];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1004,6 +1084,7 @@ __global__ void __launch_bounds__(224, 1) decode_step_kernel(const __grid_consta
     s_fail = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     s_attn_seq = 0;
     s_prog[0] = s_prog[1] = 0;
+    s_kv_seq = 0;
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(&tmem_holder, DS_TMEM); tmem_relinquish(); }
@@ -1020,7 +1101,7 @@ __global__ void __launch_bounds__(224, 1) decode_step_kernel(const __grid_consta
   const uint32_t tmem_base = tmem_holder;
   // shared memory: ring stages | operand cache | scratch (row(s) of the normalised input, attention merge)
   Ctx c{&p, smem, smem + (size_t)p.ns * DS_STAGE, smem + (size_t)p.ns * DS_STAGE + DS_CACHE, tfull, cfull, empty, acc_full,
-        acc_empty, p.ns, &s_fail, &s_attn_seq, s_prog, (int)blockIdx.x, (int)gridDim.x};
+        acc_empty, p.ns, &s_fail, &s_attn_seq, s_prog, &s_kv_seq, (int)blockIdx.x, (int)gridDim.x};
   if (warp == 0) {
     if (lane == 0) ds_loader(c);
   } else if (warp == 1 || warp == 6) {
@@ -1088,7 +1169,7 @@ int ve_decode_step(const void* params, int ctas, int cooperative, cudaStream_t s
     return cudaErrorInvalidValue;
   // scratch: the normalised-input rows of a linear, or the four warps' attention states; the ring takes what is left
   const int G = p.nq / p.nkv;
-  const int need = max(p.M * p.H * 2, 512 + 4 * G * 128 * 4);
+  const int need = max(max(p.M * p.H * 2, 512 + 4 * G * 128 * 4 + G * 256), (p.S + 8) * 4);
   p.scr = (need + 1023) / 1024 * 1024;
   p.ns = (DS_SMEM - 1024 - DS_CACHE - p.scr) / DS_STAGE;
   if (p.ns > DS_MAXNS) p.ns = DS_MAXNS;

@@ -24,7 +24,27 @@ OUT_PART, OUT_LOGITS, OUT_TICKET = 0, 1, 2
 MAXM = 4
 CACHE_SLOTS = 20          # k-tiles of one op a CTA keeps expanded (DS_SLOTS of the kernel)
 
-ENABLED = os.environ.get("VOLTA_PSTEP", "1") != "0"
+# Off by default: measured on the 27B flagship the persistent step is 5.9 ms on one GPU against 5.0 ms for the
+# kernel-per-op graph (each of its six stages per layer costs 5-12 us of dependent L2 round trips: arrival counter, input
+# read, operand fill, issue, epilogue, ticket), so the engine opts in with VOLTA_PSTEP=1 / enable().
+ENABLED = os.environ.get("VOLTA_PSTEP", "0") == "1"
+
+
+class enabled:
+    """Context manager / switch: ``with decode_step.enabled(True): ...``"""
+
+    def __init__(self, on: bool):
+        self.on = on
+
+    def __enter__(self):
+        global ENABLED
+        self.prev, ENABLED = ENABLED, self.on
+        return self
+
+    def __exit__(self, *exc):
+        global ENABLED
+        ENABLED = self.prev
+        return False
 COOPERATIVE = os.environ.get("VOLTA_PSTEP_COOP", "1") != "0"
 
 
@@ -189,8 +209,7 @@ class StepProgram:
         heads = nq + 2 * nkv
         for li, L in enumerate(model.layers):
             qkv = linear(L.qkv, "qkv", li, IN_EMBED if li == 0 else IN_NORM, OUT_PART, prev, L.attn_norm)
-            fin = small(OP_QKV_FIN, qkv, li, min(G, heads))
-            att = small(OP_ATTN, fin, li, min(G, M * nkv * self.S))
+            att = small(OP_ATTN, qkv, li, min(G, M * nkv * self.S))     # finalises q / k / v of the projection itself
             mrg = small(OP_MERGE, att, li, min(G, M * nq))
             op_o = linear(L.o_proj, "o", li, IN_X, OUT_TICKET, mrg)
             gu = linear(L.gate_up, "gu", li, IN_NORM, OUT_PART, op_o, L.ffn_norm)

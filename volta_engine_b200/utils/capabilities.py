@@ -53,6 +53,8 @@ TABLE = {
     "train_exp_scale": ("Training primitives", P), "train_gather_rows": ("Training primitives", P),
     "train_scatter_add_rows": ("Training primitives", P), "train_scale_rows": ("Training primitives", P),
     "train_mul": ("Training primitives", P),
+    "decode_step": ("Persistent decode step", D), "decode_step_sizes": ("Persistent decode step", D),
+    "make_tmap_2d": ("Persistent decode step", D),
 }
 
 
