@@ -159,3 +159,63 @@ def test_reasoning_budget_forces_the_closing_sequence(model):
     own = gen.generate(Request(prompt=prompt, max_tokens=12, think_open=True, think_end_id=free[2], think_close=close,
                                thinking_budget=8))["tokens"]
     assert own == free[:12]
+
+
+@pytest.mark.parametrize("family", ["hybrid", "dsv4"])
+def test_models_with_state_outside_the_kv_pool_do_not_resume_from_snapshots(family):
+    """Snapshots hold KV pages only. A model with recurrent / ring / indexer state outside the pool must answer the
+    same prompt identically the second time with the cache passed in (the scheduler drops it), not continue from the state
+    the slot's previous request left behind."""
+    if family == "hybrid":
+        from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+        cfg = HybridConfig.tiny_hybrid()
+        m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+        kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 24, 2, 512, "cpu")
+    else:
+        from volta_engine_b200.models.dsv4 import DSV4Config, DSV4Model
+        cfg = DSV4Config.tiny_dsv4()
+        m = DSV4Model(cfg, "cpu").init_random(seed=5, std=0.05)
+        kv = PagedKVCache(1, 1, 64, 24, 2, 512, "cpu")
+    assert m.prefix_resume is None
+    eng = Engine(m, kv, use_graphs=False, prefill_chunk=32)
+    o = Options.resolve({"max_slots": 1, "prefix_interval": 32}, env={})
+    g = Generator(eng, ByteTok(), o, prefix_cache=PrefixCache(64 << 20), eos_ids=[])
+    assert g.cache is None
+    p = [t % cfg.vocab for t in prompt(70, 3)]
+    cold = g.generate(Request(p, max_tokens=6))
+    again = g.generate(Request(p, max_tokens=6))
+    assert again["tokens"] == cold["tokens"] and again["usage"]["cached_tokens"] == 0
+    turn2 = g.generate(Request(p + cold["tokens"] + p[:9], max_tokens=4))
+    kv2 = type(kv)(kv.n_layers, kv.n_kv, kv.head_dim, 24, 2, 512, "cpu")
+    g2 = Generator(Engine(m, kv2, use_graphs=False, prefill_chunk=32), ByteTok(), o, eos_ids=[])
+    assert g2.generate(Request(p + cold["tokens"] + p[:9], max_tokens=4))["tokens"] == turn2["tokens"]
+
+
+def test_prefix_cache_fingerprint_separates_models(tmp_path):
+    from volta_engine_b200.runtime.prefix_cache import model_fingerprint
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text('{"model_type": "dense", "hidden_size": 64}')
+    (d / "model.safetensors").write_bytes(b"x" * 100)
+    a = model_fingerprint(str(d), kv_format="bf16", tp=1)
+    assert a == model_fingerprint(str(d), kv_format="bf16", tp=1)
+    assert a != model_fingerprint(str(d), kv_format="fp8", tp=1)
+    assert a != model_fingerprint(str(d), kv_format="bf16", tp=2)
+    (d / "model.safetensors").write_bytes(b"y" * 101)
+    assert a != model_fingerprint(str(d), kv_format="bf16", tp=1)
+
+
+def test_prefix_cache_insert_refuses_a_detached_parent():
+    cache = PrefixCache(1 << 20)
+    toks = list(range(1, 40))
+    snap = lambda a, b: {"from": a, "to": b, "p0": 0, "k": torch.zeros(1, 1, 4), "v": torch.zeros(1, 1, 4)}
+    parent = cache.insert(toks, 16, snap)
+    assert parent is not None and cache.entries == 1
+
+    def evicting_snapshot(a, b):
+        # the parent disappears while the snapshot is being taken (outside the lock)
+        cache.root.children[toks[0]].remove(parent)
+        cache.entries -= 1
+        return snap(a, b)
+    assert cache.insert(toks, 32, evicting_snapshot) is None
+    assert cache.entries == 0 and cache.find(toks) == []

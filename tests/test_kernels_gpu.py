@@ -286,6 +286,11 @@ def test_bounded_wait_reports_through_the_status_word():
     call("wait_flag", "pilp", ptr(flag), 1, 50_000_000, ptr(status))          # 50 ms budget
     torch.cuda.synchronize()
     assert int(status.item()) == 2 and time.time() - t0 < 2.0                   # kErrPeerTimeout
+    # the status word is sticky: a second wait on the same dead flag returns at once instead of spending its budget again
+    t1 = time.time()
+    call("wait_flag", "pilp", ptr(flag), 1, 2_000_000_000, ptr(status))        # 2 s budget that must not be used
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2 and time.time() - t1 < 0.5
     status.zero_()
     flag.fill_(1)
     call("wait_flag", "pilp", ptr(flag), 1, 50_000_000, ptr(status))

@@ -33,6 +33,36 @@ def test_router_select(router, n_group, topk_group, E, k):
     assert_close(w.cpu(), rw, rel=1e-4, abs_=1e-5, name="router weights")
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+def test_router_select_keeps_ids_in_range_on_nan_and_inf_rows(mode):
+    """A row of NaN or infinite logits (an overflowed hidden state) must give expert ids inside [0, E) and finite weights:
+    the ids index shared and global memory in the kernels behind the router."""
+    from volta_engine_b200._lib import NativeError
+    E, k = 64, 6
+    logits = torch.randn(4, E, device=DEV)
+    logits[0] = float("nan")
+    logits[1] = float("-inf")
+    logits[2, ::2] = float("inf")
+    ids = torch.full((4, k), -7, dtype=torch.int32, device=DEV)
+    w = torch.empty(4, k, dtype=torch.float32, device=DEV)
+    heat = torch.zeros(E, dtype=torch.float32, device=DEV)
+    call("router_select", "pliiiipfiippp", ptr(logits), logits.stride(0), 4, E, k, mode, 0, 1.0, 1, 1, ptr(ids), ptr(w), ptr(heat))
+    torch.cuda.synchronize()
+    assert int(ids.min()) >= 0 and int(ids.max()) < E
+    for r in range(4):
+        assert len(set(ids[r].tolist())) == k                      # distinct experts
+    assert bool(torch.isfinite(w).all())
+    assert float(heat.sum()) == 4 * k
+    for bad in [dict(topk=E + 1), dict(n_group=8, topk_group=9), dict(n_group=8, topk_group=0), dict(n_group=64, topk_group=1)]:
+        a = dict(topk=k, n_group=1, topk_group=1)
+        a.update(bad)
+        ids2 = torch.empty(4, max(a["topk"], 1), dtype=torch.int32, device=DEV)
+        w2 = torch.empty(4, max(a["topk"], 1), dtype=torch.float32, device=DEV)
+        with pytest.raises(NativeError):
+            call("router_select", "pliiiipfiippp", ptr(logits), logits.stride(0), 4, E, a["topk"], mode, 0, 1.0, a["n_group"],
+                 a["topk_group"], ptr(ids2), ptr(w2), 0)
+
+
 def _models(**kw):
     cfg = MoEConfig.tiny_moe(**kw)
     m_gpu = MoEModel(cfg, DEV).init_random(seed=4)

@@ -49,3 +49,30 @@ def test_static_scratch_matvec_matches_regular_entry_twice():
     assert fn(wg.data_ptr(), sg.data_ptr(), gs, x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), None, 0,
               1, 65536, 64, 8, stream) != 0
     torch.cuda.synchronize()
+
+
+def test_static_scratch_limits_and_reuse():
+    """The corners of the built-in scratch: no split (no counter clearing), a call that fills the scratch exactly
+    (KS * N == 32768, the last slot), and a small call right after a large one (partials of the large call are still in
+    the shared array). Each must agree bit for bit with the entry point that takes caller-owned scratch."""
+    from volta_engine_b200.ops import kernels as K
+    from volta_engine_b200.quant import nvfp4 as qn
+    dev = "cuda"
+    fn = _sym()
+    g = torch.Generator(device=dev).manual_seed(9)
+    stream = torch.cuda.current_stream().cuda_stream
+    for N, Kd, KS, M in ((1024, 512, 1, 2), (8192, 1024, 4, 5), (256, 1024, 4, 1), (8192, 1024, 4, 16), (512, 2048, 2, 3)):
+        w = torch.randn(N, Kd, generator=g, device=dev) * 0.02
+        p, s_, gs = qn.quantize_nvfp4(w, search=False)
+        wg, sg = qn.prepack_gv(p, s_)
+        x = torch.randn(M, Kd, generator=g, device=dev).to(torch.bfloat16)
+        want = K.nvfp4_gemv_mma(wg, sg, gs, x, N, Kd, ks=KS)
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        rc = fn(wg.data_ptr(), sg.data_ptr(), gs, x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), None, 0,
+                M, N, Kd, KS, stream)
+        assert rc == 0, (N, Kd, KS, M, rc)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), (N, Kd, KS, M)
+    # one past the limit is refused
+    assert fn(wg.data_ptr(), sg.data_ptr(), gs, x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), None, 0,
+              1, 8192 + 16, 1024, 4, stream) != 0

@@ -55,13 +55,16 @@ VE_DEVINL uint4 ld_volatile_v4(const void* p) {
   return v;
 }
 
-// Poll one LL line until both tags equal seq. Returns false on timeout.
-VE_DEVINL bool ll_wait(const void* line, uint32_t seq, uint2& data, unsigned long long budget) {
+// Poll one LL line until both tags equal seq. Returns false on timeout, and at once when `gave_up` is already set: after
+// the first wait of a launch (or of an earlier launch: the status word) ran out of time, every later wait is skipped, so a
+// peer that left costs one wait budget, not one per line, source and replayed kernel.
+VE_DEVINL bool ll_wait(const void* line, uint32_t seq, uint2& data, unsigned long long budget, volatile int* gave_up) {
   uint4 v = ld_volatile_v4(line);
   if (v.y == seq && v.w == seq) {
     data = make_uint2(v.x, v.z);
     return true;
   }
+  if (*gave_up) return false;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
@@ -72,7 +75,7 @@ VE_DEVINL bool ll_wait(const void* line, uint32_t seq, uint2& data, unsigned lon
         return true;
       }
     }
-    if (globaltimer_ns() - t0 > budget) return false;
+    if (*gave_up || globaltimer_ns() - t0 > budget) return false;
   }
 }
 
@@ -97,13 +100,17 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
                                                             float eps, float wbias, int pushed, const EpiArgs epi) {
   extern __shared__ float rowbuf[];  // H floats (MODE >= 1)
   __shared__ float red[33];
-  __shared__ int s_timeout;
+  __shared__ volatile int s_timeout;
   const int row = blockIdx.x, tid = threadIdx.x;
+  grid_dep_launch();                 // the kernel behind this one may be scheduled and set up now
+  const int lines = H >> 2;
+  if (tid == 0) s_timeout = (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) ? 1 : 0;
+  __syncthreads();
+  // partial / residual belong to the kernel in front, and the sequence number to the all-reduce before that one: both
+  // are complete once the dependency wait returns (the kernel in front waited for that all-reduce itself)
+  grid_dep_wait();
   const uint32_t seq = a.seq[0];
   const int stage = seq & (kLLStages - 1);
-  const int lines = H >> 2;
-  if (tid == 0) s_timeout = 0;
-  __syncthreads();
   const __nv_bfloat16* prow = partial + (long)row * part_stride;
   const size_t slot_me = a.off_ll + ((size_t)(stage * a.size + a.rank) * kLLMaxRows + row) * a.ll_row_bytes;
   // push (skipped when the kernel that produced ``partial`` already sent the lines from its epilogue)
@@ -127,7 +134,7 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
         d = *reinterpret_cast<const uint2*>(prow + l * 4);
       } else {
         const size_t slot = a.off_ll + ((size_t)(stage * a.size + src) * kLLMaxRows + row) * a.ll_row_bytes;
-        if (!ll_wait(a.peer[a.rank] + slot + (size_t)l * 16, seq, d, a.budget_ns)) {
+        if (!ll_wait(a.peer[a.rank] + slot + (size_t)l * 16, seq, d, a.budget_ns, &s_timeout)) {
           s_timeout = 1;
           d = make_uint2(0u, 0u);
         }
@@ -206,6 +213,9 @@ __global__ void ll_argmax_merge_kernel(const CommArgs a, const int* __restrict__
   const int row = threadIdx.x;
   const uint32_t seq = a.seq[0];
   const int stage = seq & (kLLStages - 1);
+  __shared__ volatile int s_gave_up;
+  if (threadIdx.x == 0) s_gave_up = (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) ? 1 : 0;
+  __syncthreads();
   bool timeout = false;
   if (row < rows) {
     const uint4 pkt = make_uint4(__float_as_uint(val[row]), seq, (uint32_t)idx[row], seq);
@@ -217,8 +227,9 @@ __global__ void ll_argmax_merge_kernel(const CommArgs a, const int* __restrict__
       if (src == a.rank) continue;
       const size_t slot = a.off_ll + ((size_t)(stage * a.size + src) * kLLMaxRows + row) * a.ll_row_bytes;
       uint2 d;
-      if (!ll_wait(a.peer[a.rank] + slot, seq, d, a.budget_ns)) {
+      if (!ll_wait(a.peer[a.rank] + slot, seq, d, a.budget_ns, &s_gave_up)) {
         timeout = true;
+        s_gave_up = 1;
         continue;
       }
       const float v = __uint_as_float(d.x);
@@ -241,12 +252,15 @@ __global__ void ll_argmax_merge_kernel(const CommArgs a, const int* __restrict__
 // ------------------------------------------------------------------------------------------------
 // Cross-rank barrier for CTA `cta` (same grid on every rank). tag must increase monotonically.
 // ------------------------------------------------------------------------------------------------
+// A barrier that ran out of time (in this launch or, through the status word, an earlier one) makes the later ones
+// return at once.
 VE_DEVINL bool rank_barrier(const CommArgs& a, int cta, uint32_t tag) {
   __shared__ int ok_s;
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) ok_s = 1;
+  if (threadIdx.x == 0) ok_s = (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) ? 0 : 1;
   __syncthreads();
+  if (!ok_s) return false;
   if (threadIdx.x < a.size) {
     const int peer = threadIdx.x;
     uint32_t* theirs = reinterpret_cast<uint32_t*>(a.peer[peer] + a.off_flags) + (size_t)cta * kMaxRanks + a.rank;
@@ -362,6 +376,8 @@ __global__ void __launch_bounds__(1024) rs_norm_ag_kernel(const CommArgs a, __nv
       }
     }
   }
+  if (!ok && tid == 0 && a.status) atomicExch(a.status, (int)kErrPeerTimeout);   // before the second barrier: it then returns at once
+  __syncthreads();
   ok = rank_barrier(a, blockIdx.x, 2 * seq + 2) && ok;
   if (tid == 0) {
     if (!ok && a.status) atomicExch(a.status, (int)kErrPeerTimeout);
@@ -378,6 +394,7 @@ __global__ void __launch_bounds__(1024) rs_norm_ag_kernel(const CommArgs a, __nv
 // Test hook for the timeout path: waits (bounded by budget_ns) on a flag that nothing sets, records the
 // status and returns. The context stays usable.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, unsigned long long budget_ns, int* status) {
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;      // an earlier wait already gave up: do not wait again
   const uint64_t t0 = globaltimer_ns();
   while (ld_acquire_sys(flag) != want) {
     if (globaltimer_ns() - t0 > budget_ns) {
@@ -402,13 +419,16 @@ int ve_ll_allreduce(const void* args, int mode, const void* partial, long part_s
   int threads = ((H / 4 + 31) / 32) * 32;
   threads = threads > 1024 ? 1024 : threads;
   const int pushed = (mode >> 1) & 1;      // bit 1: the producer of ``partial`` already sent this rank's lines
+  // programmatic launch: set-up overlaps the linear in front, and the decode linear behind starts streaming its weights
+  // while this kernel still waits for the peers' lines
   if ((mode & 1) == 0)
-    ll_allreduce_kernel<0><<<rows, threads, 0, st>>>(a, (const __nv_bfloat16*)partial, part_stride, nullptr, nullptr,
-                                                     (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed, EpiArgs{});
+    launch_pdl(ll_allreduce_kernel<0>, dim3(rows), dim3(threads), 0, st, a, (const __nv_bfloat16*)partial, part_stride,
+               (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed,
+               EpiArgs{});
   else
-    ll_allreduce_kernel<1><<<rows, threads, H * sizeof(float), st>>>(
-        a, (const __nv_bfloat16*)partial, part_stride, (__nv_bfloat16*)residual, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)out, out_stride, H, eps, wbias, pushed, EpiArgs{});
+    launch_pdl(ll_allreduce_kernel<1>, dim3(rows), dim3(threads), H * sizeof(float), st, a, (const __nv_bfloat16*)partial,
+               part_stride, (__nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, H, eps, wbias,
+               pushed, EpiArgs{});
   VE_CHECK_LAUNCH();
 }
 
@@ -429,9 +449,10 @@ int ve_ll_allreduce_epi(const void* args, int mode, int pushed, const void* part
   int threads = ((H / 4 + 31) / 32) * 32;
   threads = threads > 1024 ? 1024 : threads;
   const size_t smem = (size_t)H * sizeof(float);
-#define VE_LLE(M)                                                                                                    \
-  ll_allreduce_kernel<M><<<rows, threads, smem, st>>>(a, (const __nv_bfloat16*)partial, part_stride, nullptr, nullptr, \
-                                                      nullptr, 0, H, eps, wbias, pushed, e)
+#define VE_LLE(M)                                                                                                     \
+  launch_pdl(ll_allreduce_kernel<M>, dim3(rows), dim3(threads), smem, st, a, (const __nv_bfloat16*)partial, part_stride, \
+             (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)nullptr, (long)0, H, eps, wbias,    \
+             pushed, e)
   switch (mode) {
     case kEpiSandwich:
       if ((!xs && !res16) || !w || !w2 || !out) return cudaErrorInvalidValue;

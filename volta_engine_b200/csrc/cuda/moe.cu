@@ -57,7 +57,10 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
   __shared__ int s_id[32];
   const float* row = logits + blockIdx.x * stride;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    const float l = row[e];
+    // a row of NaN / inf logits (an overflowed hidden state) must still yield in-range expert ids: NaN counts as the
+    // lowest score, infinities are clamped to the largest finite values
+    float l = row[e];
+    l = (l != l) ? -FLT_MAX : fminf(fmaxf(l, -FLT_MAX), FLT_MAX);
     // mode 2: sqrt(softplus(l)), softplus written so that large |l| neither overflows nor cancels
     const float s = mode == 1 ? 1.f / (1.f + __expf(-l)) : mode == 2 ? sqrtf(fmaxf(l, 0.f) + log1pf(__expf(-fabsf(l)))) : l;
     s_raw[e] = s;
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
         int best = -1;
         for (int g = 0; g < n_group; ++g)
           if (!keep[g] && (best < 0 || s_gscore[g] > s_gscore[best])) best = g;
-        keep[best] = true;
+        if (best >= 0) keep[best] = true;
       }
       for (int g = 0; g < n_group; ++g) s_gscore[g] = keep[g] ? 1.f : 0.f;
     }
@@ -96,9 +99,19 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
     for (int e = threadIdx.x; e < E; e += blockDim.x) a = rv_better(a, RV{s_sel[e], e});
     a = block_best(a, red);
     if (threadIdx.x == 0) {
-      s_id[k] = a.i;
-      s_w[k] = s_raw[a.i];
-      s_sel[a.i] = -FLT_MAX;
+      int pick = a.i;
+      if (pick < 0 || pick >= E) {
+        // nothing beat the sentinel (every remaining score is the lowest value): take the first expert not picked yet
+        pick = 0;
+        for (int e = 0; e < E; ++e) {
+          bool used = false;
+          for (int j = 0; j < k; ++j) used = used || s_id[j] == e;
+          if (!used) { pick = e; break; }
+        }
+      }
+      s_id[k] = pick;
+      s_w[k] = s_raw[pick];
+      s_sel[pick] = -FLT_MAX;
     }
     __syncthreads();
   }
@@ -107,7 +120,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
       float m = -FLT_MAX, sum = 0.f;
       for (int k = 0; k < topk; ++k) m = fmaxf(m, s_w[k]);
       for (int k = 0; k < topk; ++k) { s_w[k] = __expf(s_w[k] - m); sum += s_w[k]; }
-      for (int k = 0; k < topk; ++k) s_w[k] = s_w[k] / sum * scale;
+      for (int k = 0; k < topk; ++k) s_w[k] = sum > 0.f ? s_w[k] / sum * scale : scale / (float)topk;
     } else {
       float sum = 0.f;
       for (int k = 0; k < topk; ++k) sum += s_w[k];
@@ -116,7 +129,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
     for (int k = 0; k < topk; ++k) {
       ids[blockIdx.x * topk + k] = s_id[k];
       weights[blockIdx.x * topk + k] = s_w[k];
-      if (heat) atomicAdd(&heat[s_id[k]], 1.f);      // routing histogram: monitor page and expert residency decisions
+      if (heat && s_id[k] >= 0 && s_id[k] < E) atomicAdd(&heat[s_id[k]], 1.f);      // routing histogram: monitor page and expert residency decisions
     }
   }
 }
@@ -489,7 +502,9 @@ extern "C" {
 int ve_router_select(const void* logits, long stride, int rows, int E, int topk, int mode, const void* bias, float scale,
                      int n_group, int topk_group, void* ids, void* weights, void* heat, cudaStream_t st) {
   if (rows <= 0) return 0;
-  if (E > 1024 || topk > 32 || topk < 1 || n_group > 64 || (n_group > 1 && E % n_group)) return cudaErrorInvalidValue;
+  if (E > 1024 || topk > 32 || topk < 1 || topk > E || n_group > 64 || (n_group > 1 && E % n_group)) return cudaErrorInvalidValue;
+  if (n_group > 1 && (topk_group < 1 || topk_group > n_group || E / n_group < 2 || topk > topk_group * (E / n_group)))
+    return cudaErrorInvalidValue;
   router_select_kernel<<<rows, 256, 0, st>>>((const float*)logits, stride, E, topk, mode, (const float*)bias, scale,
                                              n_group, topk_group, (int*)ids, (float*)weights, (float*)heat);
   VE_CHECK_LAUNCH();

@@ -15,7 +15,9 @@
 // counter) sums them in split order, so results are deterministic and a row's value does not depend on how
 // many rows are in the batch. The reference's counterpart is the skinny NVFP4 family
 // (src/kernels/cuda/nvfp4/skinny_kernels.cu:14-310), which software-unpacks to FP16 for mma.m8n8k4.
+#include <atomic>
 #include "common.cuh"
+#include "volta_noalloc.h"
 
 namespace ve {
 
@@ -200,8 +202,12 @@ constexpr int kStaticCounters = 4096;     // limit on N / 16
 static __device__ __align__(256) float g_static_ws[(size_t)kStaticWsRows * 16];
 static __device__ __align__(256) int g_static_counters[kStaticCounters];
 constexpr int kMaxDevices = 64;
-static float* g_ws_addr[kMaxDevices];     // device addresses of the arrays above, resolved per device
-static int* g_cnt_addr[kMaxDevices];
+// device addresses of the arrays above, resolved per device. The pair is published through one atomic pointer so that a
+// host thread that sees the entry sees both addresses (two threads making the first call on a device resolve the same
+// values; whichever publishes last wins, harmlessly)
+struct StaticAddrs { float* ws; int* cnt; };
+static StaticAddrs g_addr_store[kMaxDevices];
+static std::atomic<StaticAddrs*> g_addrs[kMaxDevices];
 }  // namespace ve
 
 extern "C" {
@@ -216,7 +222,8 @@ int ve_nvfp4_gemv_mma_static(const void* Wg, const void* Sg, float gscale, const
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-  if (!g_ws_addr[dev]) {
+  StaticAddrs* addrs = g_addrs[dev].load(std::memory_order_acquire);
+  if (!addrs) {
     // In host code the array names are only handles; the kernel needs the addresses the current device
     // gave them. Resolved on the first call for each device.
     float* ws = nullptr;
@@ -225,17 +232,18 @@ int ve_nvfp4_gemv_mma_static(const void* Wg, const void* Sg, float gscale, const
     if (e != cudaSuccess) return (int)e;
     e = cudaGetSymbolAddress((void**)&cnt, g_static_counters);
     if (e != cudaSuccess) return (int)e;
-    g_cnt_addr[dev] = cnt;
-    g_ws_addr[dev] = ws;
+    g_addr_store[dev] = StaticAddrs{ws, cnt};
+    addrs = &g_addr_store[dev];
+    g_addrs[dev].store(addrs, std::memory_order_release);
   }
   if (KS > 1) {
     // the arrival counters must read zero when the kernel starts; the partial sums need no clearing
     // because every slot that is read has been written by this call
-    e = cudaMemsetAsync(g_cnt_addr[dev], 0, (size_t)(N / 16) * sizeof(int), st);
+    e = cudaMemsetAsync(addrs->cnt, 0, (size_t)(N / 16) * sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
   }
   return ve_nvfp4_gemv_mma(Wg, Sg, gscale, x, x_stride, out, out_stride, residual, res_stride, M, N, K, KS,
-                           g_ws_addr[dev], g_cnt_addr[dev], st);
+                           addrs->ws, addrs->cnt, st);
 }
 
 }  // extern "C"

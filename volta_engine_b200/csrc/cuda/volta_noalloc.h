@@ -26,7 +26,8 @@ extern "C" {
 //
 // The first call on each device looks up the device addresses of the built-in arrays
 // (cudaGetSymbolAddress) with that device current; make that first call before starting any stream
-// capture. Every GPU that loads the library keeps the arrays (2 MiB + 16 KiB) until the process exits.
+// capture. Host threads may make that first call concurrently (they resolve the same addresses and publish them
+// together). Every GPU that loads the library keeps the arrays (2 MiB + 16 KiB) until the process exits.
 //
 // All calls on a device share the one scratch area and it keeps the previous call's contents: two calls
 // that may overlap on the GPU (different streams without an ordering between them) race. Order them on

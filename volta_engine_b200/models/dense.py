@@ -95,6 +95,10 @@ class DenseLayer:
 
 
 class DenseModel:
+    # what a prefix-cache snapshot must hold to resume this model inside a sequence: "kv" = the paged KV rows are the whole
+    # per-slot state; None = there is state outside the pool, so the scheduler must not resume from a snapshot
+    prefix_resume = "kv"
+
     def __init__(self, cfg: DenseConfig, device, comm=None):
         self.cfg = cfg
         self.device = torch.device(device)

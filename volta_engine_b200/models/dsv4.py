@@ -81,6 +81,7 @@ class DSV4Layer(MoELayer):
 
 
 class DSV4Model(MoEModel):
+    prefix_resume = None      # recurrent / ring / indexer state lives outside the paged KV pool
     layer_cls = DSV4Layer
 
     def __init__(self, cfg: DSV4Config, device, comm=None):

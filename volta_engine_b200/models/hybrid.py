@@ -64,6 +64,7 @@ class HybridLayer(MoELayer):
 
 
 class HybridModel(MoEModel):
+    prefix_resume = None      # recurrent / ring / indexer state lives outside the paged KV pool
     layer_cls = HybridLayer
 
     def __init__(self, cfg: HybridConfig, device, comm=None):

@@ -64,6 +64,11 @@ class MLALayer(MoELayer):
 
 
 class MLAModel(MoEModel):
+    @property
+    def prefix_resume(self):
+        """The sparse-attention indexer keeps pooled keys outside the paged pool."""
+        return None if self.cfg.dsa else "kv"
+
     layer_cls = MLALayer
 
     def __init__(self, cfg: MLAConfig, device, comm=None):

@@ -143,6 +143,13 @@ class Metrics:
 class Generator:
     def __init__(self, engine, tokenizer, options=None, prefix_cache=None, eos_ids=None):
         self.engine, self.tok, self.opt, self.cache = engine, tokenizer, options, prefix_cache
+        mdl = getattr(engine, "model", None)
+        if self.cache is not None and mdl is not None and getattr(mdl, "prefix_resume", "kv") != "kv":
+            # snapshots hold KV pages only; this model keeps state elsewhere, and resuming would continue from whatever
+            # the slot's previous request left there
+            from ..utils import log
+            log.warn("prefix cache disabled: %s keeps per-slot state outside the paged KV pool", type(mdl).__name__)
+            self.cache = None
         self.max_slots = min(getattr(options, "max_slots", engine.kv.max_slots), engine.kv.max_slots) if options else engine.kv.max_slots
         self.slots = [SlotState(i) for i in range(self.max_slots)]
         self.eos_ids = set(eos_ids if eos_ids is not None else getattr(tokenizer, "eos_ids", []) or [])

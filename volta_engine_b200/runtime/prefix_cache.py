@@ -97,7 +97,7 @@ class PrefixCache:
         path = os.path.join(self.disk_dir, node.key + ".pt")
         if not os.path.exists(path):
             return None
-        snap = torch.load(path, map_location="cpu")
+        snap = torch.load(path, map_location="cpu", weights_only=True)
         with self.lock:
             self.stats["disk_hits"] += 1
             node.snap = snap["snap"]
@@ -127,6 +127,10 @@ class PrefixCache:
         node = Node(seg, start, snap, parent, pinned=pinned, last_used=time.monotonic(), nbytes=_snap_bytes(snap),
                     key=_digest(tokens[:upto]))
         with self.lock:
+            # the snapshot was taken outside the lock: a parent evicted meanwhile (no disk copy: unlinked from the tree)
+            # must not get a child, or the new node would hang off a detached subtree and still be counted
+            if parent is not self.root and not self._linked_locked(parent):
+                return None
             parent.children.setdefault(seg[0], []).append(node)
             self.bytes += node.nbytes
             self.entries += 1
@@ -135,6 +139,14 @@ class PrefixCache:
         if self._q is not None:
             self._q.put(node)
         return node
+
+    def _linked_locked(self, node) -> bool:
+        while node is not None and node is not self.root:
+            par = node.parent
+            if par is None or node not in par.children.get(node.tokens[0], []):
+                return False
+            node = par
+        return node is self.root
 
     def _evict_locked(self):
         while self.bytes > self.budget:
@@ -189,7 +201,7 @@ class PrefixCache:
         for name in os.listdir(self.disk_dir):
             if name.endswith(".pt"):
                 try:
-                    d = torch.load(os.path.join(self.disk_dir, name), map_location="cpu")
+                    d = torch.load(os.path.join(self.disk_dir, name), map_location="cpu", weights_only=True)
                     metas.append((d["tokens"], d["start"], name[:-3]))
                 except Exception:
                     continue
@@ -220,6 +232,26 @@ class PrefixCache:
         s = dict(self.stats)
         s.update(entries=self.entries, bytes=self.bytes, budget_bytes=self.budget)
         return s
+
+
+def model_fingerprint(model_dir: str, **facts) -> str:
+    """Directory name of the disk tier for one model and option set: hash of ``config.json``, the names, sizes and
+    modification times of the weight files, and the facts the caller passes (KV format, head dims, layer count, TP size,
+    format version). Snapshots of another checkpoint or cache format then never meet this model's pool."""
+    import hashlib
+    import json
+    h = hashlib.sha256(b"volta-prefix-cache-v2")
+    cfg = os.path.join(model_dir or "", "config.json")
+    if os.path.exists(cfg):
+        with open(cfg, "rb") as f:
+            h.update(f.read())
+    if model_dir and os.path.isdir(model_dir):
+        for name in sorted(os.listdir(model_dir)):
+            if name.endswith((".safetensors", ".gguf", ".bin")):
+                st = os.stat(os.path.join(model_dir, name))
+                h.update(f"{name}:{st.st_size}:{int(st.st_mtime)}".encode())
+    h.update(json.dumps(facts, sort_keys=True, default=str).encode())
+    return h.hexdigest()[:24]
 
 
 def _snap_bytes(snap: dict) -> int:

@@ -226,7 +226,15 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         template = ChatTemplate.load(cfg.model_dir)
     except (FileNotFoundError, KeyError):
         template = None
-    cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None) if o.prefix_cache_mib > 0 else None
+    cache = None
+    if o.prefix_cache_mib > 0 and getattr(model, "prefix_resume", None) == "kv":
+        # a snapshot holds KV pages only: families with state outside the pool (recurrent / conv state, window and
+        # compressor rings, indexer keys) run without the cache instead of resuming from a stale state
+        from ..runtime.prefix_cache import model_fingerprint
+        kvc = engine.kv
+        fp = model_fingerprint(cfg.model_dir, kv_format=o.kv_format, tp=cfg.tp_size, layers=kvc.n_layers, kv_heads=kvc.n_kv,
+                               head_dim=kvc.head_dim, v_head_dim=kvc.v_head_dim, model_type=getattr(model.cfg, "model_type", ""))
+        cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None, fingerprint=fp)
     gen = Generator(engine, tok, o, prefix_cache=cache)
     if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size == 1:
         gen.drafter = load_drafter(engine, cfg.draft_model_dir)
