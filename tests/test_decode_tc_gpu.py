@@ -32,6 +32,26 @@ def test_expansion_reaches_bf16_accuracy():
         assert rel < bound, (terms, rel)
 
 
+@pytest.mark.parametrize("Kd", [640, 2176])
+def test_decode_linear_with_a_half_k_tile(Kd):
+    """K that is a multiple of 128 but not of 256 (the row-parallel shards of the 27B model on 8 GPUs: 640 and 2176): the
+    last k-tile is half weights, half zero fill, and the scale atoms are padded to whole tiles."""
+    from volta_engine_b200.ops.linear import LinearNVFP4
+    from volta_engine_b200.quant import nvfp4 as qn
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(Kd)
+    lin = LinearNVFP4.from_dense((torch.randn(512, Kd, generator=g) * 0.05).to(dev), search=False).prepare()
+    assert lin.tc_ready()
+    wd = qn.dequantize_nvfp4(lin.packed, lin.scales, lin.gscale).double().cpu()
+    for M in (1, 4, 16):
+        x = (torch.randn(M, Kd, generator=g) * 2).to(torch.bfloat16)
+        ref = x.double() @ wd.t()
+        y = lin.forward(x.to(dev)).double().cpu()
+        assert float((y - ref).norm() / ref.norm()) < 5e-3, (M, float((y - ref).norm() / ref.norm()))
+        y1 = lin.forward(x[:1].to(dev)).double().cpu()
+        assert torch.equal(y1[0], y[0])                  # row 0 does not depend on how many rows ride along
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 16])
 def test_decode_linear_matches_reference(M):
     from volta_engine_b200.ops import kernels as K

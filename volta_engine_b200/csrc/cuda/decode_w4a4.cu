@@ -122,10 +122,10 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, n0 = tile * 128;
   const int KS = gridDim.y, ks = blockIdx.y;
-  const int nkt_all = p.K >> 8;
+  const int nkt_all = (p.K + 255) >> 8;           // a K that is a multiple of 128 only ends in a half tile (zero filled)
   const int kt0 = (int)((long)ks * nkt_all / KS), kt1 = (int)((long)(ks + 1) * nkt_all / KS);
   const int nkt = kt1 - kt0;
-  const int nkg = p.K >> 6;                       // 64-wide k groups (scale atoms) along K
+  const int nkg = nkt_all * 4;                    // scale atoms along K, padded to whole k-tiles
   const int tpt = p.tpt;
 
   auto stage_ptr = [&](int s) { return smem + (size_t)s * STAGE_BYTES; };   // [A][B][SFA][SFB]
@@ -261,8 +261,11 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
             const float rm = m == 0 ? rs[0] : m == 1 ? rs[1] : m == 2 ? rs[2] : rs[3];
 #pragma unroll
             for (int j = 0; j < 16; ++j) r16[j] = round_bf16(r16[j] * rm * (w16[j] + p.pn_wbias));
-          } else {
+          } else if (k0 < p.K) {
             load16(p.x + (long)m * p.ldx + k0, r16);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r16[j] = 0.f;   // beyond K: the half tile's weights are zero as well
           }
           expand_block16<TERMS>(r16, codes, sc);
 #pragma unroll
@@ -530,7 +533,7 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
   VE_CHECK_LAUNCH();
 }
 
-// Wp [N, K/2] codes, sfa [N/128][K/64][512], X [M, K] bf16 (pitch ldx elements, rows 16-byte aligned).
+// Wp [N, K/2] codes, sfa [N/128][ceil(K/256)*4][512] (k-groups padded with zero scales to whole 256-wide tiles), X [M, K] bf16 (pitch ldx elements, rows 16-byte aligned).
 // ws: fp32 [N/128][ks][16][128]; tickets: int [N/128] zeroed once; ks = K splits (>= 1).
 // pdl != 0 launches with programmatic stream serialization: set-up and the first weight tiles overlap the kernel
 // in front of it in the stream (the kernel waits for that kernel before it touches X, residual or out).
@@ -548,10 +551,10 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
   if (an_out && (act || out_f32 || residual || comm_args || !out || !an_resid || !an_w || !an_ticket || ldo % 8 || N % 8))
     return cudaErrorInvalidValue;
   if (pn_w && (M > 4 || !pn_resid || K % 16 || (pn_delta && pn_resid_out == pn_resid))) return cudaErrorInvalidValue;
-  if (M < 1 || N % 128 || K % 256 || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
+  if (M < 1 || N % 128 || K % 128 || (pn_w && K % 256) || ldx % 8 || (terms != 1 && terms != 2 && terms != 4) || M * terms > 64)
     return cudaErrorInvalidValue;
   if (ks < 1) ks = 1;
-  if (ks > K / 256) ks = K / 256;
+  if (ks > (K + 255) / 256) ks = (K + 255) / 256;
   if (ks > 1 && (!ws || !tickets)) return cudaErrorInvalidValue;
   const int cols = M * terms, bn = cols <= 16 ? 16 : cols <= 32 ? 32 : 64;
   CUtensorMap amap;

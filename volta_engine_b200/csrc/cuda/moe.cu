@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x)
-      if (s_gscore[e / per] == 0.f) s_sel[e] = -FLT_MAX;
+      if (s_gscore[e / per] == 0.f) s_sel[e] = -INFINITY;     // below every sanitised score: never picked
     __syncthreads();
   }
   for (int k = 0; k < topk; ++k) {
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
       }
       s_id[k] = pick;
       s_w[k] = s_raw[pick];
-      s_sel[pick] = -FLT_MAX;
+      s_sel[pick] = -INFINITY;                                  // taken (sanitised scores are >= -FLT_MAX)
     }
     __syncthreads();
   }

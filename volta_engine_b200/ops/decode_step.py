@@ -97,10 +97,8 @@ def _tmap(base: int, dtype: int, elem: int, rows: int, cols: int, pitch: int, bo
 def padded_atoms(lin) -> torch.Tensor:
     """Scale atoms [N/128][ceil(K/256)*4][512] of an NVFP4 linear: k-groups padded with zero scales so that a 256-wide
     k-tile always owns four atoms (K that is a multiple of 128 but not of 256 ends in a half tile)."""
-    a = lin._sf_atoms
-    if a is None:
-        from ..quant import nvfp4 as qn
-        a = qn.scales_atoms_512(lin.scales)
+    from ..quant import nvfp4 as qn
+    a = qn.scales_atoms_512(lin.scales)
     N, Kk = lin.out_features, lin.in_features
     nkg = Kk // 64
     a = a.reshape(N // 128, nkg, 512)

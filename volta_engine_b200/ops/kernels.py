@@ -387,7 +387,7 @@ def dw_scratch(device):
 
 def dw_splits(N: int, K: int) -> int:
     """K splits of the decode linear: about two waves of CTAs, at least two 256-wide k-tiles each."""
-    tiles, nkt = N // 128, K // 256
+    tiles, nkt = N // 128, (K + 255) // 256
     ks = (2 * 148) // tiles                    # all CTAs resident at once (two per SM)
     ks = max(1, min(ks, nkt // 2, 32))
     while ks > 1 and ks * tiles > 1024:

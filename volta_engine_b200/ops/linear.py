@@ -72,14 +72,19 @@ class LinearNVFP4:
         tc = self._tc_ok() and GEMV_KERNEL in ("auto", "tc")
         if (self.gemm_mode == "w4a4" or tc) and self._sf_atoms is None and self.out_features % 128 == 0 \
                 and self.in_features % 64 == 0:
-            self._sf_atoms = qn.scales_atoms_512(self.scales)
+            a = qn.scales_atoms_512(self.scales)
+            nkg = self.in_features // 64
+            if nkg % 4:         # K a multiple of 128 only: pad the k-groups with zero scales to whole 256-wide tiles
+                a = a.reshape(self.out_features // 128, nkg, 512)
+                a = torch.cat([a, torch.zeros(a.shape[0], (-nkg) % 4, 512, dtype=a.dtype, device=a.device)], 1).contiguous()
+            self._sf_atoms = a
         if self._gv is None and self.packed.is_cuda and self.out_features % 16 == 0 and self.in_features % 64 == 0 \
                 and (GEMV_KERNEL == "mma" or (GEMV_KERNEL == "auto" and not tc)):
             self._gv = qn.prepack_gv(self.packed, self.scales)
         return self
 
     def _tc_ok(self) -> bool:
-        return (self.packed.is_cuda and self.out_features % 128 == 0 and self.in_features % 256 == 0
+        return (self.packed.is_cuda and self.out_features % 128 == 0 and self.in_features % 128 == 0
                 and self.in_features <= K.DW_MAX_K)
 
     def dequant(self):
