@@ -124,21 +124,42 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
       st_volatile_v4(a.peer[peer] + slot_me + (size_t)l * 16, pkt);
     }
   }
-  // gather + reduce in rank order
+  // gather + reduce in rank order. The lines of all sources are requested together and only the ones whose tags do not
+  // match yet are asked for again: one round trip to L2 per poll, not one per source.
   float ss = 0.f;
   for (int l = tid; l < lines; l += blockDim.x) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int src = 0; src < a.size; ++src) {
-      uint2 d;
-      if (src == a.rank) {
-        d = *reinterpret_cast<const uint2*>(prow + l * 4);
-      } else {
-        const size_t slot = a.off_ll + ((size_t)(stage * a.size + src) * kLLMaxRows + row) * a.ll_row_bytes;
-        if (!ll_wait(a.peer[a.rank] + slot + (size_t)l * 16, seq, d, a.budget_ns, &s_timeout)) {
-          s_timeout = 1;
-          d = make_uint2(0u, 0u);
+    uint4 v[kMaxRanks];
+    const uint8_t* lp[kMaxRanks];
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src >= a.size || src == a.rank) continue;
+      lp[src] = a.peer[a.rank] + a.off_ll + ((size_t)(stage * a.size + src) * kLLMaxRows + row) * a.ll_row_bytes + (size_t)l * 16;
+      v[src] = ld_volatile_v4(lp[src]);
+    }
+    bool all = false;
+    uint64_t t0 = 0;
+    while (!all) {
+      all = true;
+#pragma unroll
+      for (int src = 0; src < kMaxRanks; ++src) {
+        if (src >= a.size || src == a.rank) continue;
+        if (v[src].y != seq || v[src].w != seq) {
+          v[src] = ld_volatile_v4(lp[src]);
+          all = all && v[src].y == seq && v[src].w == seq;
         }
       }
+      if (all) break;
+      if (s_timeout) break;
+      if (t0 == 0) t0 = globaltimer_ns();
+      else if (globaltimer_ns() - t0 > a.budget_ns) { s_timeout = 1; break; }
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src >= a.size) continue;
+      uint2 d;
+      if (src == a.rank) d = *reinterpret_cast<const uint2*>(prow + l * 4);
+      else d = (v[src].y == seq && v[src].w == seq) ? make_uint2(v[src].x, v[src].z) : make_uint2(0u, 0u);
       acc_bf16x4(acc, d);
     }
     __nv_bfloat162 y01 = __floats2bfloat162_rn(acc[0], acc[1]), y23 = __floats2bfloat162_rn(acc[2], acc[3]);
@@ -197,12 +218,15 @@ __global__ void __launch_bounds__(1024) ll_allreduce_kernel(const CommArgs a, co
   __syncthreads();
   if (tid == 0) {
     if (s_timeout && a.status) atomicExch(a.status, (int)kErrPeerTimeout);
-    __threadfence();
-    const uint32_t done = atomicAdd(&a.seq[1], 1u);
-    if (done == gridDim.x - 1) {
-      a.seq[1] = 0;
-      __threadfence();
-      a.seq[0] = seq + 1;
+    if (gridDim.x == 1) {
+      a.seq[0] = seq + 1;               // one row: nothing to count (the next collective is a later kernel)
+    } else {
+      const uint32_t done = atomicAdd(&a.seq[1], 1u);
+      if (done == gridDim.x - 1) {
+        a.seq[1] = 0;
+        __threadfence();
+        a.seq[0] = seq + 1;
+      }
     }
   }
 }
