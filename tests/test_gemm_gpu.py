@@ -40,6 +40,30 @@ def test_gemm_w4a16(T, N, Kd):
     assert_close(got, x.float() @ wd.t(), name="gemm w4a16")
 
 
+@pytest.mark.parametrize("T,N,Kd", [(129, 256, 128), (300, 512, 640), (1000, 1024, 5120), (2048, 768, 2176)])
+def test_gemm_w4a16_wide_tiles(T, N, Kd):
+    """The 256 x 256-tile prefill kernel (two weight sub-tiles per activation tile): ragged token counts, K that is an odd
+    multiple of 128 (the last 128-wide scale block is half used per stage), residual input, and agreement with the
+    128-feature-tile kernel on the same operands."""
+    w = rnd(N, Kd, std=0.02, seed=14, dtype=torch.float32)
+    p, s, g = qn.quantize_nvfp4(w, search=False)
+    wd = qn.dequantize_nvfp4(p, s, g)
+    x = rnd(T, Kd, seed=15)
+    sf = qn.scales_blocked_k128(s)
+    want = x.float() @ wd.t()
+    got = K.gemm_w4a16(p, sf, g, x)
+    assert K.check_status(DEV) == 0
+    assert_close(got, want, name="gemm w4a16 wide")
+    res = rnd(T, N, seed=16)
+    assert_close(K.gemm_w4a16(p, sf, g, x, residual=res), want + res.float(), name="gemm w4a16 wide + residual")
+    K.GEMM_WIDE = False
+    try:
+        narrow = K.gemm_w4a16(p, sf, g, x)
+    finally:
+        K.GEMM_WIDE = True
+    assert_close(got, narrow.float(), rel=1e-2, name="wide vs 128-feature tiles")
+
+
 @pytest.mark.parametrize("T,N,Kd", [(16, 256, 512), (130, 384, 1024), (600, 1024, 5120)])
 def test_gemm_w4a4(T, N, Kd):
     w = rnd(N, Kd, std=0.02, seed=6, dtype=torch.float32)

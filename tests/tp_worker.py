@@ -20,6 +20,25 @@ def cos(a, b):
     return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-30))
 
 
+def _assert_same_greedy_run(t_tp, t_one, model_one, kv_one, prompt, dev, what, tol=2e-2):
+    """Greedy tokens of the tensor-parallel run against the single-GPU run of the same weights; at the first difference
+    the single-GPU logits of that step must hold the two tokens within ``tol`` of each other (relative to their spread)."""
+    from volta_engine_b200.runtime.batch import BatchRows
+    for i, (a, b) in enumerate(zip(t_tp, t_one)):
+        if a == b:
+            continue
+        assert i > 0, f"{what}: the prefill token differs ({a} vs {b})"
+        # logits of step i on the single-GPU model: token t_one[i-1] at position len(prompt) + i - 1 (cache rows below are
+        # identical in both runs up to here)
+        row = BatchRows.make([t_one[i - 1]], [len(prompt) + i - 1], [0], dev, nsplit=2)
+        lg = model_one.forward(row, kv_one)[0].float()
+        gap = float(lg[b] - lg[a])
+        spread = float(lg.max() - lg.median())
+        assert 0 <= gap <= tol * spread, f"{what}: step {i} picked {a} instead of {b}, logit gap {gap:.4g} of spread {spread:.4g}"
+        return
+    assert len(t_tp) == len(t_one)
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -142,15 +161,27 @@ def main():
         t1.append(e1.step([t1[-1]], [len(prompt) + i], [0])[0])
     kv1.reserve(0, len(prompt) + 32)
     lg_1 = m1.forward(probe, kv1)
-    # the caches differ after the first diverging token, so probe logits are compared only when the
-    # generated prefixes agree; the prefill token (same cache contents) must always agree
-    assert t1[0] == t_tp[0], "TP prefill token differs from the single-GPU model"
+    # The whole greedy run must agree with the single-GPU model. The two sum their partial products in different groupings,
+    # so a step whose two best logits are closer than that rounding may legitimately pick the other one: the run is then
+    # checked up to that step, and the step itself must be such a near tie (the reference's coherence tests allow the same:
+    # an FP16-ulp near tie, docs/TESTS.md:51-75).
+    _assert_same_greedy_run(t_tp, t1, m1, kv1, prompt, dev, "dense")
     if t1 == t_tp:
         lo = rank * m_tp.vocab_local
         c = cos(lg_tp, lg_1[:, lo:lo + m_tp.vocab_local])
         assert c > 0.999, f"TP logits cos={c}"
+    # the persistent decode step (one launch per token, all-reduce inside the linears' epilogues) on the same shards
+    from volta_engine_b200.ops import decode_step as PS
+    with PS.enabled(True):
+        kv_p = PagedKVCache(cfg.n_layers, m_tp.nkv, cfg.head_dim, 16, 1, 512, dev)
+        e_p = Engine(m_tp, kv_p, prefill_chunk=64)
+        t_p = [e_p.prefill(0, prompt)]
+        for i in range(5):
+            t_p.append(e_p.step([t_p[-1]], [len(prompt) + i], [0])[0])
+    same_on_all_ranks(torch.tensor(t_p, device=dev), "persistent-step TP tokens")
+    _assert_same_greedy_run(t_p, t1, m1, kv1, prompt, dev, "dense, persistent step")
     if rank == 0:
-        print(f"tp{size} tokens {t_tp} vs single {t1}", flush=True)
+        print(f"tp{size} tokens {t_tp} / persistent step {t_p} vs single {t1}", flush=True)
     assert K.check_status(dev) == 0
 
     # --- DeepSeek-V4.1-style model: heads, output groups and experts split over the ranks, caches replicated; the
@@ -174,8 +205,14 @@ def main():
         dkv1 = PagedKVCache(1, 1, 64, 16, 1, 512, dev)
         de1 = Engine(d1, dkv1, prefill_chunk=64)
         d1_toks = [de1.prefill(0, dprompt)]
+        for i in range(6):
+            d1_toks.append(de1.step([d1_toks[-1]], [len(dprompt) + i], [0])[0])
         if rank == 0:
-            print(f"dsv4 tp2 tokens {d_toks} single first {d1_toks[0]}", flush=True)
+            print(f"dsv4 tp2 tokens {d_toks} single {d1_toks}", flush=True)
+        same = sum(a == b for a, b in zip(d_toks, d1_toks))
+        assert d_toks[0] == d1_toks[0], "DSV4 TP prefill token differs from the single-GPU model"
+        first_diff = next((i for i, (a, b) in enumerate(zip(d_toks, d1_toks)) if a != b), len(d_toks))
+        assert first_diff >= 3, f"DSV4 TP run leaves the single-GPU run at step {first_diff}: {d_toks} vs {d1_toks}"
         assert (d_tp.heads, d_tp.groups, d_tp.e_local) == (8, 1, 4)
         assert K.check_status(dev) == 0
     dist.barrier()

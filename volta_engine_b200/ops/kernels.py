@@ -471,12 +471,21 @@ def gemm_bf16(W, x, out=None, residual=None, alpha=1.0, out_f32=False):
     return out
 
 
+GEMM_WIDE = os.environ.get("VOLTA_GEMM_WIDE", "1") != "0"
+
+
 def gemm_w4a16(packed, sf_blocked, gscale, x, out=None, residual=None):
     N, K2 = packed.shape
     K = K2 * 2
     T = x.shape[0]
     if out is None:
         out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    if T > 128 and N % 256 == 0 and K % 128 == 0 and GEMM_WIDE and out.dtype == torch.bfloat16:
+        # prefill chunks: 256 x 256 tiles, two weight sub-tiles per activation tile (csrc/cuda/gemm_w4a16_wide.cu)
+        call("gemm_w4a16_wide", "ppplplpliiifp", ptr(packed), ptr(sf_blocked), ptr(x), x.stride(0), ptr(out), out.stride(0),
+             ptr(residual), residual.stride(0) if residual is not None else 0, T, N, K, float(gscale),
+             ptr(status_word(x.device)))
+        return out
     call("gemm_w4a16", "ppplplppliiifp", ptr(packed), ptr(sf_blocked), ptr(x), x.stride(0), ptr(out),
          out.stride(0), 0, ptr(residual), residual.stride(0) if residual is not None else 0, T, N, K,
          float(gscale), ptr(status_word(x.device)))

@@ -16,7 +16,7 @@ TABLE = {
     "embed": ("Embedding", P), "rope_store": ("RoPE + KV store", P), "gated_act": ("SwiGLU / GeGLU", P),
     "kv_quant_store": ("KV formats", P), "attention": ("Attention", P),
     "argmax": ("Sampling", P), "argmax2": ("Sampling", P), "topk": ("Sampling", P),
-    "gemm_bf16": ("Gemm", P), "gemm_w4a16": ("LinearNVFP4", P), "gemm_w4a4": ("LinearNVFP4", P),
+    "gemm_bf16": ("Gemm", P), "gemm_w4a16": ("LinearNVFP4", P), "gemm_w4a16_wide": ("LinearNVFP4", P), "gemm_w4a4": ("LinearNVFP4", P),
     "gemm_grouped_bf16": ("MoE grouped GEMM", P), "gemm_grouped_w4a16": ("MoE grouped GEMM", P),
     "decode_w4a4": ("LinearNVFP4 decode", P), "nvfp4_expand_rows": ("LinearNVFP4 decode", P),
     "nvfp4_gemv": ("LinearNVFP4 decode", P), "nvfp4_gemv_mma": ("LinearNVFP4 decode", P),
