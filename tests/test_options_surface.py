@@ -1,0 +1,97 @@
+"""Launch options: every key of the reference's option table parses; unknown keys are fatal; aliases map; the keys
+that name subsystems this build does not wire say so. Reference: inc/engine/runtime/options.def, docs/CONFIG.md."""
+import os
+
+import pytest
+import torch
+
+from volta_engine_b200.runtime import options as O
+
+KEYS_FILE = os.path.join(os.path.dirname(__file__), "data", "reference_option_keys.txt")
+
+
+def _reference_keys():
+    """Option names of the reference's table (inc/engine/runtime/options.def), one per line."""
+    with open(KEYS_FILE) as f:
+        return [ln.strip() for ln in f if ln.strip()]
+
+
+def test_every_reference_key_is_accepted():
+    keys = _reference_keys()
+    assert len(keys) > 100
+    known = O.known_keys()
+    missing = [k for k in keys if k not in known]
+    assert not missing, missing
+    for k in keys:
+        assert O.disposition(k)
+
+
+def test_unknown_key_is_fatal():
+    with pytest.raises(KeyError):
+        O.Options.resolve({"no_such_option": 1}, env={})
+
+
+def test_aliases_and_wide_values():
+    o = O.Options.resolve({"prefix_cache_gib": 3, "loop_detect": "stop", "speculator": "dflash", "mtp_graph": False,
+                           "expert_shard": 0, "sparse_head_file": "/tmp/x.bin", "spec_suffix": 2, "kv_format": ""}, env={})
+    assert o.prefix_cache_mib == 3072 and o.loop_detect is True and o.speculator == "draft" and o.no_graphs is True
+    assert o.expert_parallel is True and o.sparse_head_state == "/tmp/x.bin" and o.kv_format == "bf16"
+    o = O.Options.resolve({"spec_suffix": 2}, env={})
+    assert o.speculator == "suffix"
+    o = O.Options.resolve({"speculator": "mtp", "mtp_depth": 5}, env={})
+    assert o.spec_depth == 5
+
+
+def test_ignored_lists_the_keys_without_effect():
+    o = O.Options.resolve({"gemv_int8": False, "steer_scale": 2.0, "prefill_cooldown": 2}, env={})
+    names = [k for k, _ in o.ignored()]
+    assert "gemv_int8" in names and "steer_scale" in names and "prefill_cooldown" not in names
+
+
+def test_env_and_docs():
+    o = O.Options.resolve({}, env={"ENGINE_PREFILL_COOLDOWN": "3", "ENGINE_AR_LL": "0"})
+    assert o.prefill_cooldown == 3 and o.ar_ll is False
+    doc = O.config_docs()
+    for k in ("arena_gib", "prefill_cooldown", "gemv_int8", "steer_scale", "trace_layers"):
+        assert f"`{k}`" in doc
+
+
+def test_layer_trace_wraps_sub_layers():
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime.batch import BatchRows
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.utils.trace import enable_layer_trace
+    cfg = DenseConfig(n_layers=2, hidden=256, n_q=2, n_kv=1, head_dim=128, ffn=256, vocab=512)
+    model = DenseModel(cfg, torch.device("cpu")).init_random(seed=0)
+    kv = PagedKVCache(2, model.nkv, 128, 4, 1, 128, torch.device("cpu"))
+    seen, depth = [], [0]
+
+    def push(name):
+        seen.append(name)
+        depth[0] += 1
+
+    def pop():
+        depth[0] -= 1
+
+    assert enable_layer_trace(model, push, pop) == ["attn_block", "ffn_block"]
+    assert enable_layer_trace(model, push, pop) == []            # wrapping twice would nest the ranges
+    kv.reserve(0, 8)
+    model.forward(BatchRows.make([1, 2, 3], [0, 1, 2], [0, 0, 0], torch.device("cpu")), kv)
+    assert seen == ["L0.attn", "L0.ffn", "L1.attn", "L1.ffn"] and depth[0] == 0
+
+
+def test_disk_tier_budget_trims_oldest(tmp_path):
+    from volta_engine_b200.runtime.prefix_cache import PrefixCache
+    pc = PrefixCache(1 << 30, str(tmp_path), fingerprint="m", disk_budget_bytes=200_000)
+
+    def snap(a, b):
+        return {"k": torch.zeros(b - a, 2000, dtype=torch.bfloat16)}
+
+    for i in range(6):
+        toks = [i] * 40
+        pc.insert(toks, 16, snap)
+        pc.flush()
+    files = [f for f in os.listdir(os.path.join(str(tmp_path), "m")) if f.endswith(".pt")]
+    total = sum(os.path.getsize(os.path.join(str(tmp_path), "m", f)) for f in files)
+    assert total <= 200_000 and 1 <= len(files) < 6
+    assert pc.stats["disk_bytes"] == total

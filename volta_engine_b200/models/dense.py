@@ -346,7 +346,12 @@ class DenseModel:
         h = K.embed(b.ids, self.embed, scale=cfg.embed_scale)
         h2 = torch.empty_like(h)
         delta = None
+        mark = getattr(self, "_trace_mark", None)          # (push, pop) of utils.trace.enable_layer_trace
         for li, L in enumerate(self.layers):
+            if mark is not None:
+                if li:
+                    mark[1]()
+                mark[0](f"L{li}")
             kpool, vpool = kv.layer(li)
             qkv = L.qkv.forward_prenorm(h, delta, L.attn_norm, cfg.rms_eps, cfg.norm_bias, h2 if delta is not None else None)
             if delta is not None:
@@ -364,6 +369,8 @@ class DenseModel:
             a = L.gate_up.forward_prenorm(h, o, L.ffn_norm, cfg.rms_eps, cfg.norm_bias, h2, act=act, limit=cfg.act_limit)
             h, h2 = h2, h
             delta = L.down.forward(a)
+        if mark is not None:
+            mark[1]()
         x = K.rmsnorm(delta, self.final_norm, cfg.rms_eps, cfg.norm_bias, residual=h)
         self.last_hidden, self.last_residual = x, h
         if b.logits == LOGITS_NONE:

@@ -10,6 +10,8 @@ projection; prefill chunks sort routes by expert and run the grouped tcgen05 GEM
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass
 
 import torch
@@ -221,10 +223,22 @@ class MoEModel(DenseModel):
             return y
         logits = L.router.forward(x, out_f32=True)
         shared = None
+        side = None
         if L.shared_gu is not None:
-            sgu = L.shared_gu.forward(x)
-            sa = K.gated_act(sgu, sgu.shape[1] // 2, act, cfg.act_limit)
-            shared = L.shared_dn.forward(sa)
+            if getattr(self, "side_streams", False) and x.is_cuda and rows <= 16:
+                # the shared expert does not depend on the routing: it runs on a side stream beside the router and the
+                # routed experts and joins before the combine (inside a graph capture this becomes a forked branch). Decode
+                # rows only: larger chunks are compute-bound and their kernels share workspaces
+                side = getattr(self, "_side", None)
+                if side is None:
+                    side = self._side = torch.cuda.Stream(device=x.device)
+                main = torch.cuda.current_stream(x.device)
+                side.wait_stream(main)
+                x.record_stream(side)
+            with (torch.cuda.stream(side) if side is not None else contextlib.nullcontext()):
+                sgu = L.shared_gu.forward(x)
+                sa = K.gated_act(sgu, sgu.shape[1] // 2, act, cfg.act_limit)
+                shared = L.shared_dn.forward(sa)
             if not getattr(self, "_shared_sliced", False) and self.comm.size > 1 and self.comm.rank != 0:
                 shared = None            # replicated shared expert: only one rank contributes it to the sum
         if not x.is_cuda:
@@ -261,6 +275,10 @@ class MoEModel(DenseModel):
         else:
             d, inv = self._grouped(bank, x, ids, routes, k, act)
         gate = logits[:, cfg.n_experts:] if getattr(L, "shared_gated", False) else None     # extra router column
+        if side is not None:
+            main.wait_stream(side)
+            if shared is not None:
+                shared.record_stream(main)
         call("moe_combine", "plpppiiplplpliii", ptr(d), d.stride(0), ptr(w), ptr(ids), ptr(inv), bank.e0, bank.e_local,
              ptr(shared), shared.stride(0) if shared is not None else 0,
              gate.data_ptr() if gate is not None else 0, logits.stride(0) if gate is not None else 0,

@@ -15,6 +15,25 @@ from . import reference as ref
 PAGE = ref.PAGE
 
 _status = {}
+_scratch_registry = {}
+
+
+def use_scratch(registry, device) -> None:
+    """Kernel workspaces of ``device`` created after this call are carved from ``registry``
+    (``runtime.arena.ScratchRegistry``) instead of the caching allocator: one device allocation per process, stable
+    addresses for graph replay. ``None`` restores the allocator."""
+    if registry is None:
+        _scratch_registry.pop(str(device), None)
+    else:
+        _scratch_registry[str(device)] = registry
+
+
+def _ws(name, shape, dtype, device, zero=False):
+    reg = _scratch_registry.get(str(device))
+    if reg is None:
+        return (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=device)
+    t = reg.typed(name, shape if isinstance(shape, tuple) else (shape,), dtype)
+    return t.zero_() if zero else t
 
 
 def status_word(device) -> torch.Tensor:
@@ -333,8 +352,8 @@ def gv_scratch(device):
     key = str(device)
     t = _gv_scratch.get(key)
     if t is None:
-        t = (torch.empty(GV_WS_ROWS * 16, dtype=torch.float32, device=device),
-             torch.zeros(4096, dtype=torch.int32, device=device))
+        t = (_ws("gemv/partials", GV_WS_ROWS * 16, torch.float32, device),
+             _ws("gemv/counters", 4096, torch.int32, device, zero=True))
         _gv_scratch[key] = t
     return t
 
@@ -377,10 +396,10 @@ def dw_scratch(device):
     key = str(device)
     t = _dw_scratch.get(key)
     if t is None:
-        t = (torch.zeros(64, DW_MAX_K // 2, dtype=torch.uint8, device=device),
-             torch.zeros(DW_MAX_K // 64 * 512, dtype=torch.uint8, device=device),
-             torch.empty(1024 * 16 * 128, dtype=torch.float32, device=device),
-             torch.zeros(1024 + 8, dtype=torch.int32, device=device))      # [1024] = ticket of the fused add + norm
+        t = (_ws("decode_linear/codes", (64, DW_MAX_K // 2), torch.uint8, device, zero=True),
+             _ws("decode_linear/scale_atoms", DW_MAX_K // 64 * 512, torch.uint8, device, zero=True),
+             _ws("decode_linear/partials", 1024 * 16 * 128, torch.float32, device),
+             _ws("decode_linear/tickets", 1024 + 8, torch.int32, device, zero=True))      # [1024] = ticket of the fused add + norm
         _dw_scratch[key] = t
     return t
 

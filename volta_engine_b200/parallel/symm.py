@@ -83,6 +83,9 @@ class SymmComm:
         self._arg_idx = torch.empty(LL_MAX_ROWS, dtype=torch.int32, device=self.device)
         self.pushed = False        # set by a linear whose epilogue already sent its rows (see push_target)
         self.fuse_push = os.environ.get("VOLTA_FUSE_PUSH", "1") != "0"
+        # False (launch option ar_ll = false): decode rows take the two-shot collective too, followed by the add + norm
+        # kernel; an A/B switch for the one-shot low-latency form
+        self.use_ll = True
         dist.barrier(self.group)
         torch.cuda.synchronize(self.device)
 
@@ -112,14 +115,14 @@ class SymmComm:
     def push_target(self, rows: int, H: int) -> int:
         """Address of the argument block for a producer kernel that sends its [rows, H] result into the peers' low-latency
         staging area itself (decode rows only), or 0 when the fused send does not apply."""
-        if not self.fuse_push or rows > LL_MAX_ROWS or H * 4 > self.args.ll_row_bytes or H % 4:
+        if not self.fuse_push or not self.use_ll or rows > LL_MAX_ROWS or H * 4 > self.args.ll_row_bytes or H % 4:
             return 0
         return self._args_ptr
 
     # ---- collectives ---------------------------------------------------------------------------
     def allreduce_(self, x: torch.Tensor) -> torch.Tensor:
         rows, H = x.shape
-        if rows <= LL_MAX_ROWS:
+        if rows <= LL_MAX_ROWS and self.use_ll:
             out = torch.empty_like(x)
             _lib.call("ll_allreduce", "piplpppliiff", self._args_ptr, 0, x.data_ptr(), x.stride(0), 0, 0,
                       out.data_ptr(), out.stride(0), rows, H, 0.0, 0.0)
@@ -144,6 +147,11 @@ class SymmComm:
         Returns the normalised activations [rows, H] (replicated)."""
         rows, H = partial.shape
         pushed, self.pushed = self.pushed, False
+        if rows <= LL_MAX_ROWS and not self.use_ll:
+            part = self.partial_buffer(rows, H)
+            part.copy_(partial)
+            self._two_shot(None, None, rows, H, 0.0, 0.0, 0)
+            return K.rmsnorm(self._xout(rows, H), w, eps, wbias, residual=residual, out=out)
         if rows <= LL_MAX_ROWS:
             if out is None:
                 out = torch.empty_like(partial)

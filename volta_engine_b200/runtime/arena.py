@@ -79,9 +79,12 @@ class Arena:
 
 
 class ScratchRegistry:
-    def __init__(self, arena: Arena | None = None, device="cuda:0"):
+    def __init__(self, arena: Arena | None = None, device="cuda:0", overflow: bool = False):
+        """``overflow``: a workspace that no longer fits the arena is allocated by itself (and counted in
+        ``overflow_bytes``) instead of raising."""
         self.arena, self.device = arena, torch.device(device if arena is None else arena.device)
         self.items: dict[str, torch.Tensor] = {}
+        self.overflow, self.overflow_bytes = overflow, 0
 
     def get(self, name: str, nbytes: int) -> torch.Tensor:
         """uint8 workspace of at least ``nbytes``; the same tensor for the same name on every call."""
@@ -91,7 +94,13 @@ class ScratchRegistry:
         if t is not None and self.arena is not None and self.arena.frozen:
             raise ArenaError(f"scratch '{name}' would grow from {t.numel()} to {nbytes} B after start-up")
         if self.arena is not None:
-            t = self.arena.alloc(nbytes, torch.uint8, f"scratch/{name}")
+            try:
+                t = self.arena.alloc(nbytes, torch.uint8, f"scratch/{name}")
+            except ArenaError:
+                if not self.overflow:
+                    raise
+                self.overflow_bytes += nbytes
+                t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         else:
             t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.items[name] = t

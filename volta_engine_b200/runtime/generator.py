@@ -166,6 +166,10 @@ class Generator:
         self.loop_detect = getattr(options, "loop_detect", True) if options else True
         self.prefix_interval = getattr(options, "prefix_interval", 16384) if options else 16384
         self.budget_ms = getattr(options, "prefill_budget_ms", 50.0) if options else 50.0
+        # extra decode steps that run between two prompt pieces while other slots decode (0 = a piece every step)
+        self.prefill_cooldown = max(0, getattr(options, "prefill_cooldown", 0)) if options else 0
+        self._since_prefill = 1 << 30
+        self.cache_reply = getattr(options, "prefix_cache_reply", True) if options else True
         self.drafter = None                    # block drafter (speculator "dflash"): object with draft(slot, anchor, pos, depth)
         self.mtp = None
         if self.speculator == "mtp":
@@ -321,6 +325,10 @@ class Generator:
             self._finish(s, "cancelled")
             return 0
         decoding = any(x.phase == "decode" for x in self.slots)
+        if decoding and self._since_prefill < self.prefill_cooldown:
+            self._since_prefill += 1
+            return 0
+        self._since_prefill = 0
         chunk = self.engine.prefill_chunk
         done_rows, t0 = 0, time.time()
         prompt = s.req.prompt
@@ -594,7 +602,7 @@ class Generator:
     def _finish(self, s: SlotState, reason: str, error: str | None = None):
         req = s.req
         now = time.time()
-        if self.cache is not None and req.cache_prefix and reason in ("stop", "length", "stop_string") and s.pos > 0:
+        if self.cache is not None and self.cache_reply and req.cache_prefix and reason in ("stop", "length", "stop_string") and s.pos > 0:
             try:                                   # reply snapshot: the next turn resumes after this answer
                 self._store_prefix(s, min(s.pos, len(req.prompt) + len(s.out)))
             except Exception:

@@ -24,7 +24,13 @@ KV_FORMATS = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp8": torch.float
 
 class PagedKVCache:
     def __init__(self, n_layers: int, n_kv: int, head_dim: int, num_pages: int, max_slots: int, max_seq: int,
-                 device, dtype=torch.bfloat16, v_head_dim: int | None = None):
+                 device, dtype=torch.bfloat16, v_head_dim: int | None = None, arena=None):
+        """``arena``: a ``runtime.arena.Arena`` that the page pools are carved from (one device allocation for the
+        serving process); ``None`` allocates each pool by itself."""
+        def pool(name, *shape, dtype):
+            if arena is None:
+                return torch.zeros(*shape, dtype=dtype, device=device)
+            return arena.alloc(shape, dtype, name).zero_()
         if isinstance(dtype, str):
             dtype = KV_FORMATS[dtype]
         self.n_layers, self.n_kv, self.head_dim = n_layers, n_kv, head_dim
@@ -40,19 +46,33 @@ class PagedKVCache:
             self.fmt = C.FORMAT_CODES[dtype]
             kq, vq = C.FORMATS[self.fmt]
             assert head_dim % 64 == 0 and self.v_head_dim % 64 == 0, "scaled KV formats need head dims that are multiples of 64"
-            self.k = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.data_bytes(kq, head_dim), dtype=torch.uint8, device=device)
-            self.v = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.data_bytes(vq, self.v_head_dim), dtype=torch.uint8, device=device)
-            self.ks = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.scale_bytes(kq, head_dim), dtype=torch.uint8, device=device)
-            self.vs = torch.zeros(n_layers, num_pages, n_kv, PAGE, C.scale_bytes(vq, self.v_head_dim), dtype=torch.uint8, device=device)
+            self.k = pool("kv/k", n_layers, num_pages, n_kv, PAGE, C.data_bytes(kq, head_dim), dtype=torch.uint8)
+            self.v = pool("kv/v", n_layers, num_pages, n_kv, PAGE, C.data_bytes(vq, self.v_head_dim), dtype=torch.uint8)
+            self.ks = pool("kv/k_scales", n_layers, num_pages, n_kv, PAGE, C.scale_bytes(kq, head_dim), dtype=torch.uint8)
+            self.vs = pool("kv/v_scales", n_layers, num_pages, n_kv, PAGE, C.scale_bytes(vq, self.v_head_dim), dtype=torch.uint8)
         else:
             self.fmt = 1 if dtype == torch.float8_e5m2 else 0
-            self.k = torch.zeros(n_layers, num_pages, n_kv, PAGE, head_dim, dtype=dtype, device=device)
-            self.v = torch.zeros(n_layers, num_pages, n_kv, PAGE, self.v_head_dim, dtype=dtype, device=device)
+            self.k = pool("kv/k", n_layers, num_pages, n_kv, PAGE, head_dim, dtype=dtype)
+            self.v = pool("kv/v", n_layers, num_pages, n_kv, PAGE, self.v_head_dim, dtype=dtype)
         self.page_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32, device=device)
         self.host_table = torch.zeros(max_slots, self.max_pages, dtype=torch.int32)
         self.free = list(range(num_pages - 1, 0, -1))
         self.slot_pages = [0] * max_slots  # logical pages covered per slot (high-water mark)
         self.slot_first = [0] * max_slots  # first logical page still held (pages below were recycled by release_prefix)
+
+    @staticmethod
+    def pool_bytes(n_layers: int, n_kv: int, head_dim: int, num_pages: int, dtype="bf16", v_head_dim: int | None = None) -> int:
+        """Device bytes of the page pools for these dimensions (alignment slack of the four pools included)."""
+        vd = v_head_dim or head_dim
+        fmt = KV_FORMATS[dtype] if isinstance(dtype, str) else dtype
+        rows = n_layers * num_pages * n_kv * PAGE
+        if isinstance(fmt, str):
+            from ..quant import kv_codec as C
+            kq, vq = C.FORMATS[C.FORMAT_CODES[fmt]]
+            per = C.data_bytes(kq, head_dim) + C.data_bytes(vq, vd) + C.scale_bytes(kq, head_dim) + C.scale_bytes(vq, vd)
+        else:
+            per = (head_dim + vd) * torch.empty((), dtype=fmt).element_size()
+        return rows * per + 4 * 256
 
     @staticmethod
     def pages_for(n_tokens: int) -> int:

@@ -48,15 +48,112 @@ _TABLE = [
     ("route_dump", str, "", "file that receives the MoE blocks' routed rows and routing weights at shutdown"),
 ]
 
+# Keys of the reference's option table (inc/engine/runtime/options.def) that this engine takes under the same name, so a
+# launch file written for the reference loads unchanged. Each entry says what the key does here: "-> name" = an alias of
+# one of the options above (the value is converted), "live" = read by the engine under its own name, anything else = why
+# the key has no effect on this engine (it is still parsed and type-checked; an unknown key stays fatal).
+_NOOP_KERNEL = "no effect: selects between kernel variants of the reference's sm_70 / sm_80 build; here each op has one sm_100a kernel"
+_NOOP_DEBUG = "no effect: debugging aid of a reference code path that has no counterpart here"
+_COMPAT = [
+    # name, type, default, disposition
+    ("arena_gib", int, -1, "live"), ("scratch_mib", int, 256, "live"),
+    ("prefix_cache_gib", int, 16, "-> prefix_cache_mib"), ("prefix_cache_disk_gib", int, 64, "live"),
+    ("prefill_window", int, -1, "no effect: expert weights of a layer stay resident in HBM, so a prompt's chunks need not be "
+                                 "regrouped layer by layer to amortise expert staging"),
+    ("prefill_cooldown", int, 0, "live"), ("prefix_cache_reply", bool, True, "live"),
+    ("nvfp4_experts", str, "", "live"), ("nvfp4_dense", str, "", "live"), ("nvfp4_dense_dir", str, "", "live"),
+    ("nvfp4_dense_src", str, "", "live"), ("nvfp4_expert_layers", str, "", "live"),
+    ("embed_host", bool, True, "no effect: the embedding table stays in HBM (180 GB per GPU); a host copy would add a PCIe "
+                               "read to every step"),
+    ("mtp_nvfp4", bool, False, "live"), ("mtp_head_dir", str, "", "live"), ("dflash_hessian_dir", str, "", "live"),
+    ("sparse_head_interval", int, 2048, "live"), ("sparse_head_file", str, "", "-> sparse_head_state"),
+    ("expert_cache", float, 1.0, "live"), ("expert_stage", int, -1, "live"), ("expert_adapt_every", int, 64, "live"),
+    ("route_resident_bias", float, 0.0, "live"), ("expert_swap_margin", int, 2, "live"),
+    ("expert_history_pct", int, 75, "live"), ("expert_swaps", int, -1, "live"), ("expert_swap_mib", int, 1024, "live"),
+    ("expert_shard", int, -1, "-> expert_parallel"), ("expert_heat_file", str, "", "live"),
+    ("cpu_experts", float, 0.0, "live"), ("cpu_expert_cpus", str, "", "live"), ("cpu_expert_node", int, -1, "live"),
+    ("cpu_expert_spin_us", int, 2000, "live"),
+    ("steer", str, "off", "live"), ("steer_layers", str, "", "live"), ("steer_file", str, "", "live"),
+    ("steer_dir", str, "", "live"), ("probe", str, "", "live"), ("low_priority_models", str, "haiku", "live"),
+    ("steer_scale", float, 1.0, "live"), ("steer_scope", str, "", "live"), ("steer_gate_threshold", str, "auto", "live"),
+    ("steer_edit_strength", str, "auto", "live"), ("steer_hedge_strength", float, -1.0, "live"),
+    ("steer_openings", str, "", "live"), ("steer_directions", int, 1, "live"), ("steer_keep_norm", bool, False, "live"),
+    ("steer_push", float, 0.0, "live"), ("steer_band", str, "", "live"), ("steer_edit_layers", str, "", "live"),
+    ("thinking_soft_close", int, 128, "live"), ("think_penalty", float, 0.0, "live"),
+    ("think_penalty_words", str, "", "live"),
+    ("exl3_gemv_max_m", int, 4, _NOOP_KERNEL), ("exl3_wmma_max_m", int, 64, _NOOP_KERNEL),
+    ("glm_layers", int, 0, _NOOP_DEBUG), ("gemv_max_rows", int, 16, _NOOP_KERNEL), ("gemv_int8", bool, True, _NOOP_KERNEL),
+    ("gguf_mma", bool, True, _NOOP_KERNEL), ("gguf_gemv_warp", int, -1, _NOOP_KERNEL),
+    ("ar_ll", bool, True, "live"), ("dflash_attn_scalar", bool, False, _NOOP_KERNEL), ("spec_profile", bool, False, "live"),
+    ("merge_expert_groups", bool, True, _NOOP_KERNEL), ("fp8_resident", bool, True, _NOOP_KERNEL),
+    ("indexer_tc", bool, True, _NOOP_KERNEL),
+    ("mtp_depth", int, 7, "live"), ("draft_tp", bool, True, "live"), ("dsa", bool, True, "live"),
+    ("vision_cpu", int, 0, "no effect: the vision tower always runs on rank 0's GPU"), ("vision_cpus", str, "", "no effect: see vision_cpu"),
+    ("vision_mmproj", str, "", "live"), ("vision_dir", str, "", "live"), ("max_image_tokens", int, 1024, "live"),
+    ("expert_stats", bool, True, "live"), ("spec_block_cycle", str, "", _NOOP_DEBUG), ("spec_depth_rate", bool, False, "live"),
+    ("spec_suffix", int, 0, "live"),
+    ("moe_coop_mode", int, -1, _NOOP_KERNEL), ("moe_prefill_tile", bool, True, _NOOP_KERNEL), ("gguf_q8r", bool, True, _NOOP_KERNEL),
+    ("gguf_moe_tile", bool, True, _NOOP_KERNEL), ("gguf_moe_tile884", bool, True, _NOOP_KERNEL),
+    ("shared_slice", bool, True, _NOOP_KERNEL), ("moe_gemv", bool, False, _NOOP_KERNEL),
+    ("nvfp4_hipblas", bool, False, "no effect: ROCm build switch"), ("ple_log", bool, False, "live"),
+    ("expert_log", bool, False, "live"), ("glm_logit_rows", int, 0, _NOOP_DEBUG), ("expert_stream", bool, False, _NOOP_KERNEL),
+    ("expert_synth", int, 0, _NOOP_DEBUG), ("dsa_diag", bool, False, _NOOP_DEBUG), ("sparse_head_force", bool, False, "live"),
+    ("train_inputs", str, "", _NOOP_DEBUG), ("route_dump_from", int, 0, "live"), ("route_replay", str, "", _NOOP_DEBUG),
+    ("gr_fuse", bool, True, _NOOP_KERNEL), ("mem_log", bool, False, "live"), ("side_streams", bool, True, "live"),
+    ("kda_rows", bool, True, _NOOP_KERNEL), ("hc_rows", bool, True, _NOOP_KERNEL), ("hc_fuse", bool, True, _NOOP_KERNEL),
+    ("normed_add_fuse", bool, True, _NOOP_KERNEL), ("dflash_graph", bool, True, "no effect: drafter rounds always replay as graphs"),
+    ("mtp_chain", bool, True, "no effect: the draft chain always runs on the device"), ("mtp_graph", bool, True, "-> no_graphs"),
+    ("qsa_off", bool, False, "live"), ("router_fp16", bool, False, _NOOP_KERNEL), ("spec_ctrl_log", bool, False, "live"),
+    ("draft_per_slot", bool, True, "live"), ("spec_agg_dense", int, -1, _NOOP_DEBUG), ("tap_spool", str, "", "live"),
+    ("tap_spool_window", int, 768, "live"), ("spec_joint_max", int, 2, "live"), ("spec_joint", int, -1, "live"),
+    ("spec_interleave", bool, True, "live"), ("dflash_tap_shift", int, 0, _NOOP_DEBUG),
+    ("dflash_embed_scale", bool, True, _NOOP_DEBUG), ("dflash_sliding_causal", bool, True, _NOOP_DEBUG),
+    ("dump_draft_round", int, -1, _NOOP_DEBUG),
+]
+# keys both tables know under the same name but whose reference form is wider than ours: converted when parsed
+_WIDE = {
+    "loop_detect": lambda raw: (str(raw).strip().lower() in ("1", "true", "yes", "on", "stop", "report")) if not isinstance(raw, bool) else raw,
+    "sparse_head": lambda raw: (int(raw) > 0 if str(raw).strip().lstrip("-").isdigit() else str(raw).strip().lower() in ("true", "yes", "on")) if not isinstance(raw, bool) else raw,
+    "trace_layers": lambda raw: (str(raw).strip().lower() not in ("", "0", "false", "no", "off")) if not isinstance(raw, bool) else raw,
+    "kv_format": lambda raw: {"": "bf16", "fp16": "bf16"}.get(str(raw), str(raw)),
+    "tp": lambda raw: 1 if int(raw) < 0 else int(raw),
+    "speculator": lambda raw: {"dflash": "draft", "dflash2": "draft", "dspark": "draft"}.get(str(raw), str(raw)),
+    "spec_depth": lambda raw: max(0, int(float(raw))),
+    "max_seq": lambda raw: int(raw) if int(raw) > 0 else 32768,
+    "max_slots": lambda raw: int(raw) if int(raw) > 0 else 8,
+    "vram_reserve_mib": lambda raw: int(raw) if int(raw) >= 0 else 2048,
+    "moe_heavy_rows": lambda raw: int(raw) if int(raw) > 0 else 64,
+}
+
+_NOT_WIRED = {'nvfp4_experts': 'loader: experts from a second NVFP4 checkpoint', 'nvfp4_dense': 'loader: quantise named dense groups to NVFP4 at load', 'nvfp4_dense_dir': 'loader: calibrated NVFP4 dense tensors', 'nvfp4_dense_src': 'loader: source checkpoint of nvfp4_dense', 'nvfp4_expert_layers': 'loader: layers whose experts come from the NVFP4 checkpoint', 'mtp_nvfp4': 'loader: MTP head from the NVFP4 checkpoint', 'mtp_head_dir': 'loader: MTP head from another checkpoint', 'dflash_hessian_dir': 'calibration capture of the block drafter', 'sparse_head_interval': 'sparse head policy (runtime/sparse_head_policy.py) takes its interval from its constructor', 'expert_cache': 'expert tier (runtime/expert_tier.py) is built by the model code, not from this key', 'expert_stage': 'expert tier: staging a layer ahead is not built', 'expert_adapt_every': 'expert tier rebalance period', 'route_resident_bias': 'router bias towards resident experts', 'expert_swap_margin': 'expert tier swap rule', 'expert_history_pct': 'expert tier swap rule', 'expert_swaps': 'expert tier swap rule', 'expert_swap_mib': 'expert tier swap rule', 'expert_heat_file': 'expert tier heat persistence', 'cpu_experts': 'CPU expert service (runtime/cpu_experts.py) share', 'cpu_expert_cpus': 'CPU expert service thread placement', 'cpu_expert_node': 'CPU expert service NUMA node', 'cpu_expert_spin_us': 'CPU expert service polling time', 'steer': 'steering (runtime/steering.py) is attached through the API, not from launch options', 'steer_layers': 'steering layer range', 'steer_file': 'steering file', 'steer_dir': 'steering directory', 'probe': 'steering probes', 'steer_scale': 'steering scale', 'steer_scope': 'steering scope', 'steer_gate_threshold': 'steering gate', 'steer_edit_strength': 'steering edit strength', 'steer_hedge_strength': 'steering hedge strength', 'steer_openings': 'steering openings', 'steer_directions': 'steering directions', 'steer_keep_norm': 'steering norm keeping', 'steer_push': 'steering push', 'steer_band': 'steering band', 'steer_edit_layers': 'steering edit layers', 'thinking_soft_close': 'length of the forced closing run of the reasoning budget', 'think_penalty': 'reasoning-marker logit penalty', 'think_penalty_words': 'reasoning-marker words', 'spec_profile': 'per-stage timers of a drafter round', 'draft_tp': 'tensor-parallel drafter', 'dsa': 'sparse attention switch (set in the model config here)', 'vision_mmproj': 'GGUF vision projector file', 'vision_dir': 'vision tower directory', 'max_image_tokens': 'image token cap', 'expert_stats': 'routing heat is always collected', 'spec_depth_rate': 'depth chosen by rate', 'ple_log': 'n-gram layer log', 'expert_log': 'expert tier log', 'sparse_head_force': 'sparse head always on', 'route_dump_from': 'first step of the route dump', 'qsa_off': 'block-sparse attention switch (set in the model config here)', 'spec_ctrl_log': 'controller log', 'draft_per_slot': 'drafter state per slot', 'tap_spool': 'tap spool file', 'tap_spool_window': 'tap spool window', 'spec_joint_max': 'slots per joint round', 'spec_joint': 'joint rounds', 'spec_interleave': 'interleaved rounds'}
+_COMPAT_HELP = {'arena_gib': 'size of the per-GPU arena in GiB; <= 0 sizes it from free memory minus vram_reserve_mib', 'scratch_mib': 'arena memory set aside for kernel workspaces before the model loads', 'prefix_cache_gib': 'prefix cache budget in GiB (alias of prefix_cache_mib)', 'prefix_cache_disk_gib': "size limit of the prefix cache's disk tier; the least recently used files go first", 'prefill_cooldown': 'decode steps that run between two prompt pieces while other requests decode', 'prefix_cache_reply': 'snapshot prompt + reply when a request ends', 'ar_ll': 'false: decode rows use the two-shot collective instead of the one-shot LL all-reduce (A/B)', 'mtp_depth': 'draft depth of the MTP speculator (alias of spec_depth when speculator=mtp)', 'spec_suffix': '> 0 turns the suffix drafter on when no speculator is named', 'mem_log': 'log device memory after start-up', 'side_streams': 'independent chains of a layer (shared expert beside the routed experts) run on a side stream', 'low_priority_models': 'comma list of model-name substrings whose requests queue behind the others', 'sparse_head_file': 'alias of sparse_head_state', 'expert_shard': '0 / 1: whole experts per rank / a slice of every expert per rank (alias of expert_parallel)', 'mtp_graph': 'false: alias of no_graphs'}
+_COMPAT = [(n, t, d, ("parsed, not wired in this build: " + _NOT_WIRED[n]) if n in _NOT_WIRED else disp) for n, t, d, disp in _COMPAT]
+
 _TYPES = {n: t for n, t, _, _ in _TABLE}
+_TYPES.update({n: t for n, t, _, _ in _COMPAT})
+_DISPOSITION = {n: d for n, _, _, d in _COMPAT}
+
+
+def known_keys() -> set:
+    """Every option name the launcher accepts."""
+    return set(_TYPES)
+
+
+def disposition(name: str) -> str:
+    """What a reference option key does in this engine (see ``_COMPAT``); "native" for the engine's own options."""
+    return _DISPOSITION.get(name, "native")
 
 
 def _parse(name: str, raw):
+    if name in _WIDE:
+        return _WIDE[name](raw)
     t = _TYPES[name]
     if t is bool:
         if isinstance(raw, bool):
             return raw
         return str(raw).strip().lower() in ("1", "true", "yes", "on")
+    if t is float and isinstance(raw, str) and raw.strip().lower() == "auto":
+        return -1.0                     # "auto" of a numeric option (expert_cache): let the engine size it
     return t(raw)
 
 
@@ -74,14 +171,18 @@ class Options:
     def resolve(cls, json_options: dict | None = None, cli_sets: list[str] | None = None, env=None) -> "Options":
         env = os.environ if env is None else env
         v = {n: d for n, _, d, _ in _TABLE}
-        for n in v:
-            raw = env.get("ENGINE_" + n.upper())
+        v.update({n: d for n, _, d, _ in _COMPAT})
+        given = set()
+        for n in list(v):
+            raw = env.get("ENGINE_" + n.upper(), env.get("ENGINE_DEBUG_" + n.upper()))
             if raw is not None:
                 v[n] = _parse(n, raw)
+                given.add(n)
         for k, raw in (json_options or {}).items():
             if k not in v:
                 raise KeyError(f"unknown option '{k}'")
             v[k] = _parse(k, raw)
+            given.add(k)
         for item in cli_sets or []:
             if "=" not in item:
                 raise ValueError(f"--set expects key=value, got '{item}'")
@@ -89,9 +190,30 @@ class Options:
             if k not in v:
                 raise KeyError(f"unknown option '{k}'")
             v[k] = _parse(k, raw)
+            given.add(k)
+        # aliases of the reference's names
+        if "prefix_cache_gib" in given and "prefix_cache_mib" not in given:
+            v["prefix_cache_mib"] = max(0, int(v["prefix_cache_gib"])) * 1024
+        if "sparse_head_file" in given and "sparse_head_state" not in given:
+            v["sparse_head_state"] = v["sparse_head_file"]
+        if "expert_shard" in given and "expert_parallel" not in given and int(v["expert_shard"]) >= 0:
+            v["expert_parallel"] = int(v["expert_shard"]) == 0
+        if "mtp_graph" in given and "no_graphs" not in given and not v["mtp_graph"]:
+            v["no_graphs"] = True
+        if "mtp_depth" in given and "spec_depth" not in given and v["speculator"] == "mtp":
+            v["spec_depth"] = int(v["mtp_depth"])
+        if v["speculator"] == "none" and int(v["spec_suffix"]) > 0:
+            v["speculator"] = "suffix"
         if v["tp"] not in (1, 2, 4, 8):
             raise ValueError("tp must be 1, 2, 4 or 8")
-        return cls(v)
+        o = cls(v)
+        o.__dict__["given"] = given
+        return o
+
+    def ignored(self) -> list[tuple[str, str]]:
+        """Keys the launch set explicitly that have no effect here, with the reason (the launcher logs them once)."""
+        return [(k, _DISPOSITION[k]) for k in sorted(self.__dict__.get("given", ()))
+                if _DISPOSITION.get(k, "").startswith(("no effect", "parsed, not wired"))]
 
 
 def config_docs() -> str:
@@ -99,4 +221,8 @@ def config_docs() -> str:
     lines = ["| option | type | default | env | meaning |", "|---|---|---|---|---|"]
     for n, t, d, h in _TABLE:
         lines.append(f"| `{n}` | {t.__name__} | `{d}` | `ENGINE_{n.upper()}` | {h} |")
+    lines += ["", "Keys of the reference engine's option table accepted under the same name:", "",
+              "| option | type | default | in this engine |", "|---|---|---|---|"]
+    for n, t, d, disp in _COMPAT:
+        lines.append(f"| `{n}` | {t.__name__} | `{d}` | {_COMPAT_HELP.get(n, disp)} |")
     return "\n".join(lines) + "\n"

@@ -43,7 +43,7 @@ class Node:
 
 
 class PrefixCache:
-    def __init__(self, budget_bytes: int, disk_dir: str = "", fingerprint: str = "default"):
+    def __init__(self, budget_bytes: int, disk_dir: str = "", fingerprint: str = "default", disk_budget_bytes: int = 0):
         self.budget = budget_bytes
         self.root = Node((), 0, None)
         self.bytes = 0
@@ -52,6 +52,7 @@ class PrefixCache:
                       "disk_hits": 0, "disk_entries": 0, "disk_bytes": 0}
         self.lock = threading.Lock()
         self.disk_dir = os.path.join(disk_dir, fingerprint) if disk_dir else ""
+        self.disk_budget = int(disk_budget_bytes)          # 0: the disk tier is not trimmed
         self._q: queue.Queue | None = None
         self._writer = None
         if self.disk_dir:
@@ -98,6 +99,10 @@ class PrefixCache:
         if not os.path.exists(path):
             return None
         snap = torch.load(path, map_location="cpu", weights_only=True)
+        try:
+            os.utime(path)             # the disk tier trims by last use
+        except OSError:
+            pass
         with self.lock:
             self.stats["disk_hits"] += 1
             node.snap = snap["snap"]
@@ -194,6 +199,48 @@ class PrefixCache:
             with self.lock:
                 self.stats["disk_entries"] += 1
                 self.stats["disk_bytes"] += os.path.getsize(path)
+            if self.disk_budget > 0 and self.stats["disk_bytes"] > self.disk_budget:
+                self._trim_disk(keep=path)
+
+    def _trim_disk(self, keep: str = ""):
+        """Remove the least recently used snapshot files until the tier fits its budget. A node whose file went and
+        that holds no resident snapshot is unlinked with its subtree (its descendants resume from it)."""
+        files = []
+        for name in os.listdir(self.disk_dir):
+            if name.endswith(".pt"):
+                fp = os.path.join(self.disk_dir, name)
+                try:
+                    st = os.stat(fp)
+                except OSError:
+                    continue
+                files.append((max(st.st_atime, st.st_mtime), st.st_size, fp, name[:-3]))
+        files.sort()
+        total = sum(f[1] for f in files)
+        gone = set()
+        for _, size, fp, key in files:
+            if total <= self.disk_budget:
+                break
+            if fp == keep:
+                continue
+            try:
+                os.remove(fp)
+            except OSError:
+                continue
+            total -= size
+            gone.add(key)
+        with self.lock:
+            self.stats["disk_bytes"] = total
+            self.stats["disk_entries"] = len(files) - len(gone)
+            for node in list(self._iter(self.root)):
+                if node.key in gone and node.snap is None and node.parent is not None:
+                    sib = node.parent.children.get(node.tokens[0], [])
+                    if node in sib:
+                        sib.remove(node)
+                        self.entries -= sum(1 for _ in self._iter(node)) + 1
+                        for sub in self._iter(node):         # resident descendants can no longer be reached
+                            if sub.snap is not None:
+                                self.bytes -= sub.nbytes
+                                sub.snap, sub.nbytes = None, 0
 
     def _scan_disk(self):
         """Rebuild the tree skeleton from the files of an earlier run (snapshots stay on disk until used)."""

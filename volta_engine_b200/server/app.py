@@ -221,7 +221,11 @@ class VoltaServer:
                 self.http.respond(conn, 200, json.dumps(body, ensure_ascii=False))
 
         sys_end = []
-        r = Request(prompt=ids, mm=mm, cache_key=cache_key, max_tokens=max_new, params=cr.params, stop=cr.stop, priority=cr.priority,
+        prio = cr.priority
+        low = [m.strip().lower() for m in str(getattr(self.gen.opt, "low_priority_models", "") or "").split(",") if m.strip()]
+        if low and any(m in (cr.model or "").lower() for m in low):
+            prio -= 100                 # requests that name one of these models queue behind the others
+        r = Request(prompt=ids, mm=mm, cache_key=cache_key, max_tokens=max_new, params=cr.params, stop=cr.stop, priority=prio,
                     on_text=on_text, on_finish=on_finish, checkpoints=sys_end)
         rid = self.gen.submit(r)
         with self._lock:

@@ -15,10 +15,13 @@ import json
 import os
 import signal
 import sys
+import logging
 import threading
 from dataclasses import asdict, dataclass, field
 
 from ..runtime.options import Options, config_docs
+
+log = logging.getLogger("volta")
 
 _TOP_KEYS = {
     "model_dir": (str, ""), "draft_model_dir": (str, ""), "use_speculation": (bool, False), "tui": (bool, False),
@@ -162,27 +165,54 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     device = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
     model, hf = load_model(cfg.model_dir, device, comm, gemm_mode=o.gemm_mode)
     mcfg = model.cfg
+    model.side_streams = bool(o.side_streams)
+    if o.trace_layers:
+        from ..utils.trace import enable_layer_trace
+        enable_layer_trace(model)
     from ..runtime.kv_cache import KV_FORMATS
     if o.kv_format not in KV_FORMATS:
         raise ValueError(f"kv_format '{o.kv_format}': this build has {sorted(KV_FORMATS)}")
     # bytes per cached element, scales included: bf16 2, E5M2 1, k8v4 (1 + 1/32 + 1/2 + 1/32) / 2, nvfp4 1/2 + 1/16
     kv_bytes = {"fp8": 1.0, "k8v4": 0.78125, "nvfp4": 0.5625}.get(o.kv_format, 2.0)
     bpt = int(getattr(model, "kv_layers", mcfg.n_layers) * model.nkv * 2 * mcfg.head_dim * kv_bytes)
+    on_gpu = torch.device(device).type == "cuda"
+    scratch_bytes = max(0, o.scratch_mib) << 20
+    budget = None
+    if on_gpu:
+        free, _ = torch.cuda.mem_get_info(torch.device(device))
+        # the arena holds the KV pools and the kernels' workspaces: arena_gib fixes its size, otherwise it takes what
+        # is free after the weights minus the reserve (graphs, library workspaces, prefill activations)
+        budget = (o.arena_gib << 30) if o.arena_gib > 0 else int((free - (o.vram_reserve_mib << 20)) * 0.9)
+        budget = min(budget, free - (256 << 20))
     if o.kv_pool:
         pool_tokens = o.kv_pool
-    elif torch.device(device).type == "cuda":
-        free, _ = torch.cuda.mem_get_info(torch.device(device))
-        pool_tokens = max(4096, int((free - (o.vram_reserve_mib << 20)) * 0.9) // bpt)
+    elif on_gpu:
+        pool_tokens = max(4096, (budget - scratch_bytes) // bpt)
     else:
         pool_tokens = min(o.max_seq * 2, 16384)
     pool_tokens = min(pool_tokens, o.max_seq * o.max_slots)
     if agree is not None:
         pool_tokens = agree(pool_tokens)
     kv_layers = getattr(model, "kv_layers", mcfg.n_layers)       # hybrid models keep KV only for their attention layers
-    kv = PagedKVCache(kv_layers, model.nkv, mcfg.head_dim, max(2, pool_tokens // 64), o.max_slots, o.max_seq, device,
-                      dtype=o.kv_format)
+    pages = max(2, pool_tokens // 64)
+    arena = scratch = None
+    if on_gpu:
+        from ..ops import kernels as K
+        from ..runtime.arena import Arena, ScratchRegistry
+        arena = Arena(PagedKVCache.pool_bytes(kv_layers, model.nkv, mcfg.head_dim, pages, o.kv_format) + scratch_bytes
+                      + (1 << 20), device)
+        scratch = ScratchRegistry(arena, overflow=True)
+        K.use_scratch(scratch, device)
+    kv = PagedKVCache(kv_layers, model.nkv, mcfg.head_dim, pages, o.max_slots, o.max_seq, device,
+                      dtype=o.kv_format, arena=arena)
     engine = Engine(model, kv, use_graphs=not o.no_graphs and torch.device(device).type == "cuda",
                     prefill_chunk=o.prefill_chunk)
+    engine.arena, engine.scratch = arena, scratch
+    if o.mem_log and on_gpu:
+        free, total = torch.cuda.mem_get_info(torch.device(device))
+        log.info("memory: device %.1f GiB used of %.1f; arena %.2f GiB (%s); KV pool %d tokens", (total - free) / 2**30,
+                 total / 2**30, arena.capacity / 2**30,
+                 ", ".join(f"{k} {v / 2**20:.0f} MiB" for k, v in arena.report()["by_name"].items()), pool_tokens)
     if hasattr(model, "set_prefill_truncate"):
         model.set_prefill_truncate(o.prefill_truncate)
     if o.hessian_dir and hasattr(model, "enable_hessians"):
@@ -234,7 +264,8 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         kvc = engine.kv
         fp = model_fingerprint(cfg.model_dir, kv_format=o.kv_format, tp=cfg.tp_size, layers=kvc.n_layers, kv_heads=kvc.n_kv,
                                head_dim=kvc.head_dim, v_head_dim=kvc.v_head_dim, model_type=getattr(model.cfg, "model_type", ""))
-        cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None, fingerprint=fp)
+        cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None, fingerprint=fp,
+                            disk_budget_bytes=max(0, o.prefix_cache_disk_gib) << 30)
     gen = Generator(engine, tok, o, prefix_cache=cache)
     if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size == 1:
         gen.drafter = load_drafter(engine, cfg.draft_model_dir)
@@ -279,6 +310,8 @@ def _run_rank(cfg: LaunchConfig) -> int:
     from ..runtime.tp_control import ControlChannel, follower_loop
     if cuda:
         comm = make_comm(cfg.options.comm, device)
+        if hasattr(comm, "use_ll"):
+            comm.use_ll = cfg.options.ar_ll
     else:
         from ..parallel.host import HostComm
         comm = HostComm()

@@ -35,6 +35,12 @@ def stats_payload(srv, brief: bool = False) -> dict:
     out["recent"] = snap["recent"]
     out["history"] = snap["history"]
     out["gpus"] = gpu_stats()
+    arena = getattr(g.engine, "arena", None)
+    if arena is not None and out["gpus"]:
+        idx = arena.device.index or 0
+        for row in out["gpus"]:
+            if row.get("index") == idx:
+                row["arena_bytes"] = arena.capacity
     out["host"] = host_stats()
     return out
 
