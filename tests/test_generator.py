@@ -219,3 +219,37 @@ def test_prefix_cache_insert_refuses_a_detached_parent():
         return snap(a, b)
     assert cache.insert(toks, 32, evicting_snapshot) is None
     assert cache.entries == 0 and cache.find(toks) == []
+
+
+def test_speculative_sampling_step_is_distributed_like_the_target():
+    """Accept the draft with probability p(draft), else draw from the rest renormalised: the token that comes out has the
+    target distribution whatever the draft (inc/engine/runtime/sampling.h:197-223 in the reference)."""
+    from volta_engine_b200.runtime.sampling import Candidates, Xoshiro256pp, distribution, spec_step
+    c = Candidates([7, 3, 9, 1], [2.0, 1.5, 0.2, -1.0], 2.9)
+    p = SamplingParams(temperature=0.8)
+    want = dict(zip(c.ids, distribution(c, p)))
+    for draft in (7, 9, 55):                        # likely draft, unlikely draft, draft outside the candidates
+        rng = Xoshiro256pp(123 + draft)
+        n, seen, hits = 40000, {}, 0
+        for _ in range(n):
+            ok, t = spec_step(c, p, draft, rng)
+            assert ok == (t == draft) or (not ok and t != draft)
+            hits += ok
+            seen[t] = seen.get(t, 0) + 1
+        for tok, q in want.items():
+            assert abs(seen.get(tok, 0) / n - q) < 0.012, (draft, tok, seen.get(tok, 0) / n, q)
+        assert abs(hits / n - want.get(draft, 0.0)) < 0.012
+
+
+def test_sampled_requests_take_speculative_rounds(model):
+    p = (prompt(20, 3) * 6)[:100]
+    spec, _ = make(model, speculator="suffix", spec_ctrl=False, spec_depth=4)
+    sp = SamplingParams(temperature=0.7, top_k=8, seed=11)
+    a = spec.generate(Request(p, max_tokens=24, params=sp))
+    assert spec.metrics.spec["rounds"] > 0 and len(a["tokens"]) == 24
+    b = spec.generate(Request(p, max_tokens=24, params=sp))
+    assert a["tokens"] == b["tokens"]               # seeded: the same draws, round by round
+    # a near-zero temperature makes the sampled rounds agree with greedy decoding
+    cold = spec.generate(Request(p, max_tokens=24, params=SamplingParams(temperature=1e-4, seed=5)))
+    plain, _ = make(model)
+    assert cold["tokens"] == plain.generate(Request(p, max_tokens=24))["tokens"]

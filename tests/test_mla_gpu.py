@@ -64,3 +64,29 @@ def test_mtp_head_matches_reference():
     lg, hg = mg.mtp_forward(nxt.to(DEV), hid.to(DEV), bg, kvg)
     lc, hc = mc.mtp_forward(nxt, hid, bc, kvc)
     assert cos(lg.cpu(), lc) > 0.995 and cos(hg.cpu(), hc) > 0.999
+
+
+def test_mtp_rounds_run_on_the_device_and_reproduce_plain_greedy():
+    """Draft chain + verify step + acceptance count as one graph replay; the host reads one result vector per round."""
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.mtp_runner import MtpRunner
+    cfg = MLAConfig.tiny_mla(vocab=512)
+    m = MLAModel(cfg, DEV).init_random(seed=1)
+    prompt = torch.randint(0, cfg.vocab, (77,), generator=torch.Generator().manual_seed(4)).tolist()
+    plain, _ = Engine(m, _kv(m, DEV), prefill_chunk=64).generate(prompt, 24)
+    eng = Engine(m, _kv(m, DEV), prefill_chunk=64)
+    run = MtpRunner(eng, depth=3)
+    assert run._device_round_ok()
+    eng.kv.reserve(0, len(prompt) + 40)
+    tok = run.prefill_rows(0, prompt, 0, len(prompt), True)
+    out, pos = [tok], len(prompt)
+    while len(out) < 24:
+        new = run.round(0, out[-1], pos)
+        assert 1 <= len(new) <= 4
+        out += new
+        pos += len(new)
+    assert out[:24] == plain[:24], (out, plain)
+    assert run._st["graph"] is not None and run.stats["rounds"] >= 6
+    assert run.stats["proposed"] == 3 * run.stats["rounds"]
+    from volta_engine_b200.ops import kernels as K
+    assert K.check_status(DEV) == 0

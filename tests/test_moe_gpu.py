@@ -104,6 +104,41 @@ def test_moe_ffn_block_matches_reference(rows):
     assert_close(got.cpu(), want, rel=0.02, name=f"moe ffn rows={rows}")
 
 
+def test_shared_expert_on_a_side_stream_gives_the_same_bits_eager_and_in_a_graph():
+    m_gpu, _ = _models()
+    prompt = torch.randint(0, m_gpu.cfg.vocab, (70,), generator=torch.Generator().manual_seed(3)).tolist()
+    runs = []
+    for side, graphs in ((False, True), (True, True), (True, False)):
+        m_gpu.side_streams = side
+        eng = Engine(m_gpu, PagedKVCache(2, m_gpu.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64, use_graphs=graphs)
+        out, _ = eng.generate(prompt, 12)
+        runs.append(out)
+    m_gpu.side_streams = False
+    assert runs[0] == runs[1] == runs[2], runs
+
+
+def test_kv_pools_and_workspaces_carved_from_one_arena():
+    from volta_engine_b200.ops import kernels as K
+    from volta_engine_b200.runtime.arena import Arena, ScratchRegistry
+    m_gpu, _ = _models()
+    pages = 16
+    need = PagedKVCache.pool_bytes(2, m_gpu.nkv, 64, pages, "bf16")
+    arena = Arena(need + (8 << 20), DEV)
+    kv = PagedKVCache(2, m_gpu.nkv, 64, pages, 1, 512, DEV, arena=arena)
+    lo, hi = arena.buf.data_ptr(), arena.buf.data_ptr() + arena.capacity
+    assert lo <= kv.k.data_ptr() < hi and lo <= kv.v.data_ptr() < hi and kv.k.data_ptr() % 256 == 0
+    assert arena.report()["by_name"]["kv"] >= need - 4 * 256
+    reg = ScratchRegistry(arena, overflow=True)
+    a = reg.typed("t/a", (1024,), torch.float32)
+    assert lo <= a.data_ptr() < hi and reg.typed("t/a", (1024,), torch.float32).data_ptr() == a.data_ptr()
+    big = reg.typed("t/big", (16 << 20,), torch.uint8)          # does not fit: allocated by itself, counted
+    assert not (lo <= big.data_ptr() < hi) and reg.overflow_bytes == 16 << 20
+    prompt = torch.randint(0, m_gpu.cfg.vocab, (70,), generator=torch.Generator().manual_seed(3)).tolist()
+    out_a, _ = Engine(m_gpu, kv, prefill_chunk=64).generate(prompt, 8)
+    out_b, _ = Engine(m_gpu, PagedKVCache(2, m_gpu.nkv, 64, pages, 1, 512, DEV), prefill_chunk=64).generate(prompt, 8)
+    assert out_a == out_b
+
+
 def test_moe_model_generates_like_reference_and_zipf_bias():
     m_gpu, m_cpu = _models(router_bias_zipf=1.2)
     prompt = torch.randint(0, m_gpu.cfg.vocab, (90,), generator=torch.Generator().manual_seed(1)).tolist()

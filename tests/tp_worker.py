@@ -20,9 +20,11 @@ def cos(a, b):
     return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-30))
 
 
-def _assert_same_greedy_run(t_tp, t_one, model_one, kv_one, prompt, dev, what, tol=2e-2):
-    """Greedy tokens of the tensor-parallel run against the single-GPU run of the same weights; at the first difference
-    the single-GPU logits of that step must hold the two tokens within ``tol`` of each other (relative to their spread)."""
+def _assert_same_greedy_run(t_tp, t_one, model_one, kv_one, prompt, dev, what, tol=4e-2):
+    """Greedy tokens of the tensor-parallel run against the single-GPU run of the same weights. A first difference is
+    accepted only as a near-tie: the tensor-parallel pick must be among the three best tokens of the single-GPU logits of
+    that step and within ``tol`` of the best, relative to the spread of the row (every rank rounds its partial sums to
+    bf16 before the all-reduce, so logits move by a few bf16 steps against the single-GPU sum)."""
     from volta_engine_b200.runtime.batch import BatchRows
     for i, (a, b) in enumerate(zip(t_tp, t_one)):
         if a == b:
@@ -34,7 +36,9 @@ def _assert_same_greedy_run(t_tp, t_one, model_one, kv_one, prompt, dev, what, t
         lg = model_one.forward(row, kv_one)[0].float()
         gap = float(lg[b] - lg[a])
         spread = float(lg.max() - lg.median())
-        assert 0 <= gap <= tol * spread, f"{what}: step {i} picked {a} instead of {b}, logit gap {gap:.4g} of spread {spread:.4g}"
+        rank_a = int((lg > lg[a]).sum())
+        assert 0 <= gap <= tol * spread and rank_a < 3, \
+            f"{what}: step {i} picked {a} (rank {rank_a}) instead of {b}, logit gap {gap:.4g} of spread {spread:.4g}"
         return
     assert len(t_tp) == len(t_one)
 
@@ -71,6 +75,22 @@ def main():
         unfused = K.rmsnorm(y, w, 1e-6, 1.0, residual=res_u[:rows])
         assert torch.equal(fused, unfused), f"fused != unfused at step {step}"
         assert torch.equal(res_f, res_u)
+    # --- the same decode-row calls with the low-latency form switched off (two-shot collective + add + norm kernel)
+    comm.use_ll = False
+    for rows in (1, 4):
+        x = torch.randn(rows, H, device=dev, generator=g).bfloat16()
+        want = x.float().clone()
+        dist.all_reduce(want)
+        y = comm.allreduce_(x.clone())
+        assert cos(y, want) > 0.9999, "two-shot all-reduce of decode rows"
+        same_on_all_ranks(y, "two-shot all-reduce of decode rows")
+        ra, rb = res_f[:rows].clone(), res_f[:rows].clone()
+        two = comm.allreduce_add_norm(x, ra, w, 1e-6, 1.0).clone()
+        comm.use_ll = True
+        one = comm.allreduce_add_norm(x, rb, w, 1e-6, 1.0)
+        comm.use_ll = False
+        assert cos(two, one) > 0.9999 and cos(ra, rb) > 0.9999, "decode rows: two-shot form vs low-latency form"
+    comm.use_ll = True
     # --- two-shot reduce-scatter + norm + all-gather on a prefill-sized chunk
     for T in (300, 512, 33):
         part = comm.partial_buffer(T, H)

@@ -384,13 +384,13 @@ class Generator:
             return 0
         # speculative round for one slot at a time when it is the only decoder (single-stream latency mode)
         budgeted = any(s.think_open and s.req.thinking_budget > 0 or s.forced for s in act)   # plain steps while a budget runs
-        if not budgeted and self.speculator == "suffix" and len(act) == 1 and act[0].req.params.greedy:
+        if not budgeted and self.speculator == "suffix" and len(act) == 1 and not act[0].req.params.logprobs:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
                 n = self._suffix_round(s)
                 if n:
                     return n
-        if not budgeted and self.drafter is not None and len(act) == 1 and act[0].req.params.greedy:
+        if not budgeted and self.drafter is not None and len(act) == 1 and not act[0].req.params.logprobs:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
                 depth = s.ctrl.depth(self.spec_depth) if s.ctrl else self.spec_depth
@@ -487,12 +487,33 @@ class Generator:
         t0 = time.time()
         rows = [s.next_tok] + drafts
         pos = [s.pos + i for i in range(len(rows))]
-        toks = self.engine.step(rows, pos, [s.idx] * len(rows))
-        # longest accepted prefix: draft i is accepted when the model's token after row i equals it
-        acc = 0
-        while acc < len(drafts) and toks[acc] == drafts[acc]:
-            acc += 1
-        new = drafts[:acc] + [toks[acc]]
+        params = s.req.params
+        if params.greedy:
+            toks = self.engine.step(rows, pos, [s.idx] * len(rows))
+            # longest accepted prefix: draft i is accepted when the model's token after row i equals it
+            acc = 0
+            while acc < len(drafts) and toks[acc] == drafts[acc]:
+                acc += 1
+            new = drafts[:acc] + [toks[acc]]
+        else:
+            # sampled requests: exact speculative sampling against the point-mass proposal of each draft. Row i is
+            # judged with the penalties of everything committed before it (the drafts accepted so far included), so the
+            # tokens are distributed exactly as one-row sampling steps would give them.
+            cands = self.engine.step_candidates(rows, pos, [s.idx] * len(rows))
+            counts = dict(s.counts.counts)
+            new, acc = [], 0
+            for i in range(len(rows)):
+                c = penalize(cands[i], params, counts)
+                if i == len(drafts):
+                    new.append(sample_token(c, params, s.rng))
+                    break
+                ok, t = spec_step(c, params, drafts[i], s.rng)
+                new.append(t)
+                counts[t] = counts.get(t, 0) + 1
+                if not ok:
+                    break
+                acc += 1
+            toks = new + [new[-1]] * (len(rows) - len(new))
         ms = (time.time() - t0) * 1e3
         s.pos += acc + 1
         s.next_tok = new[-1]
