@@ -173,3 +173,42 @@ def test_hybrid_model_with_kda_mixer_prefill_equals_decode_on_cpu():
     kv2 = PagedKVCache(m2.kv_layers, m2.nkv, cfg.head_dim, 16, 1, 256, "cpu")
     b, _ = Engine(m2, kv2, use_graphs=False, prefill_chunk=64).generate(toks, 5)
     assert a == b and len(a) == 5
+
+
+@pytest.mark.gpu
+def test_gpu_hybrid_verify_blocks_roll_back_bit_exactly():
+    """A journalled block of 4 rows rolled back to k rows leaves the state that stepping only k rows leaves (same kernel,
+    same operands), eager and as a CUDA graph replay; decoding after a rollback equals plain greedy decoding."""
+    dev = torch.device("cuda:0")
+    cfg = HybridConfig.tiny_hybrid()
+    m = HybridModel(cfg, dev).init_random(seed=0, search=False)
+    prompt = torch.randint(0, cfg.vocab, (90,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def fresh(graphs):
+        m.gdn_states = None
+        kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, dev)
+        return Engine(m, kv, use_graphs=graphs, prefill_chunk=64)
+
+    plain, _ = fresh(True).generate(prompt, 14)
+    for graphs in (False, True):
+        eng = fresh(graphs)
+        assert eng.prefill(0, prompt) == plain[0]
+        out, pos = [plain[0]], len(prompt)
+        wrong = (plain[3] + 1) % cfg.vocab
+        # the same block shape three times so that the third is a graph replay
+        for drafts in ([plain[1], wrong, 7], [plain[2], plain[3], wrong], [plain[4], wrong, wrong], [wrong, 1, 2]):
+            rows = [out[-1]] + drafts
+            toks = eng.step(rows, [pos + i for i in range(len(rows))], [0] * len(rows), journal=True)
+            acc = 0
+            while acc < len(drafts) and toks[acc] == drafts[acc]:
+                acc += 1
+            if acc < len(drafts):
+                eng.rollback(0, acc + 1)
+            out += drafts[:acc] + [toks[acc]]
+            pos += acc + 1
+        while len(out) < 12:
+            out.append(eng.step([out[-1]], [pos], [0])[0])
+            pos += 1
+        assert out == plain[:len(out)], (graphs, out, plain)
+    from volta_engine_b200.ops import kernels as K
+    assert K.check_status(dev) == 0

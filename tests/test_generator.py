@@ -168,7 +168,7 @@ def test_models_with_state_outside_the_kv_pool_do_not_resume_from_snapshots(fami
     the slot's previous request left behind."""
     if family == "hybrid":
         from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
-        cfg = HybridConfig.tiny_hybrid()
+        cfg = HybridConfig.tiny_hybrid(vocab=256, qsa=True)          # indexer keys live outside the pool
         m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
         kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 24, 2, 512, "cpu")
     else:
@@ -253,3 +253,77 @@ def test_sampled_requests_take_speculative_rounds(model):
     cold = spec.generate(Request(p, max_tokens=24, params=SamplingParams(temperature=1e-4, seed=5)))
     plain, _ = make(model)
     assert cold["tokens"] == plain.generate(Request(p, max_tokens=24))["tokens"]
+
+
+def _hybrid():
+    from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+    cfg = HybridConfig.tiny_hybrid(vocab=256)
+    m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+
+    def gen(cache=None, **opt):
+        kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 24, 2, 512, "cpu")
+        eng = Engine(m, kv, use_graphs=False, prefill_chunk=32)
+        o = Options.resolve(dict({"max_slots": 1, "prefix_interval": 32}, **opt), env={})
+        return Generator(eng, ByteTok(), o, prefix_cache=cache, eos_ids=[])
+    return m, gen
+
+
+def test_hybrid_model_resumes_from_snapshots_that_carry_its_recurrent_state():
+    """KV pages + the convolution and recurrent state at the snapshot's last position: the second request continues from
+    the cached prefix and produces what a cold run produces; another request in between leaves its own state in the slot."""
+    m, gen = _hybrid()
+    assert m.prefix_resume == "kv+state"
+    g = gen(cache=PrefixCache(256 << 20))
+    assert g.cache is not None
+    p = prompt(70, 3)
+    cold = g.generate(Request(p, max_tokens=6))
+    g.generate(Request(prompt(50, 9), max_tokens=3))             # overwrites the slot's state
+    again = g.generate(Request(p, max_tokens=6))
+    assert again["usage"]["cached_tokens"] >= 64 and again["tokens"] == cold["tokens"]
+    turn2 = p + cold["tokens"] + p[:9]
+    warm = g.generate(Request(turn2, max_tokens=5))
+    assert warm["usage"]["cached_tokens"] >= 70                  # the reply snapshot
+    assert warm["tokens"] == gen().generate(Request(turn2, max_tokens=5))["tokens"]
+
+
+def test_hybrid_model_takes_rejected_draft_rows_back():
+    """Suffix speculation on the model with recurrent state: a verify block runs journalled, rejected rows are rolled
+    back, and the tokens equal plain greedy decoding."""
+    m, gen = _hybrid()
+    p = prompt(60, 3)
+    kv0 = PagedKVCache(m.kv_layers, m.nkv, m.cfg.head_dim, 24, 2, 512, "cpu")
+    plain, _ = Engine(m, kv0, use_graphs=False, prefill_chunk=32).generate(p, 12)
+    m.gdn_states = None
+    kv1 = PagedKVCache(m.kv_layers, m.nkv, m.cfg.head_dim, 24, 2, 512, "cpu")
+    eng = Engine(m, kv1, use_graphs=False, prefill_chunk=32)
+    assert eng.supports_journal
+    assert eng.prefill(0, p) == plain[0]
+    out, pos = [plain[0]], len(p)
+    wrong = (plain[3] + 1) % 256
+    for drafts in ([plain[1], plain[2], wrong, 7], [wrong], [plain[5], plain[6]], [plain[8], wrong, wrong]):
+        rows = [out[-1]] + drafts
+        toks = eng.step(rows, [pos + i for i in range(len(rows))], [0] * len(rows), journal=True)
+        acc = 0
+        while acc < len(drafts) and toks[acc] == drafts[acc]:
+            acc += 1
+        if acc < len(drafts):
+            eng.rollback(0, acc + 1)
+        out += drafts[:acc] + [toks[acc]]
+        pos += acc + 1
+    assert out == plain[:len(out)] and len(out) >= 9, (out, plain)
+    m.gdn_states = None
+    # the journal's replay equals stepping: state after a block of 4 rows rolled back to 2 == state after 2 rows
+    from volta_engine_b200.runtime.batch import BatchRows
+    kv = PagedKVCache(m.kv_layers, m.nkv, m.cfg.head_dim, 24, 2, 512, "cpu")
+    kv.reserve(0, 64)
+    m.gdn_states = None
+    rows = BatchRows.make([5, 6, 7, 8], [0, 1, 2, 3], [0] * 4, "cpu")
+    m.begin_journal(True, 4)
+    m.forward(rows, kv)
+    m.rollback_state(0, 2)
+    got = [(s.conv[0].clone(), s.rec[0].clone()) for s in m.gdn_states if s is not None]
+    m.gdn_states = None
+    m.begin_journal(False)
+    m.forward(BatchRows.make([5, 6], [0, 1], [0] * 2, "cpu"), kv)
+    want = [(s.conv[0], s.rec[0]) for s in m.gdn_states if s is not None]
+    assert all(torch.equal(a, c) and torch.equal(b, d) for (a, b), (c, d) in zip(got, want))

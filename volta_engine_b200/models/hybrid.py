@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from ..ops import kernels as K
-from ..ops.gdn import GDNDims, GDNState, KDAWeights, gdn_forward, kda_forward
+from ..ops.gdn import GDNJournal, GDNDims, GDNState, KDAWeights, gdn_forward, kda_forward
 from ..ops.linear import LinearBF16
 from ..runtime.batch import BatchRows
 from .moe import MoEConfig, MoELayer, MoEModel
@@ -64,7 +64,13 @@ class HybridLayer(MoELayer):
 
 
 class HybridModel(MoEModel):
-    prefix_resume = None      # recurrent / ring / indexer state lives outside the paged KV pool
+    @property
+    def prefix_resume(self):
+        """"kv+state": a sequence snapshot is the KV pages plus the recurrent and convolution state of the slot at the
+        snapshot's last position (``snapshot_state`` / ``restore_state``). Models whose attention layers keep indexer
+        keys outside the pool have no resumable snapshot."""
+        return None if getattr(self.cfg, "qsa", False) else "kv+state"
+
     layer_cls = HybridLayer
 
     def __init__(self, cfg: HybridConfig, device, comm=None):
@@ -153,11 +159,25 @@ class HybridModel(MoEModel):
         if L.gdn is not None:
             g = L.gdn
             proj = g["in_proj"].forward(x)
+            st = self._states(kv)[li]
+            jn = None
+            if self.journal_on and b.tiles is None:
+                # rows of a speculative verify block (one slot): keep what is needed to take rejected rows back
+                js = self._jcur
+                jn = js["layers"].get(li)
+                if jn is None:
+                    sh = self._shadows.get(li)
+                    if sh is None:
+                        sh = self._shadows[li] = (torch.zeros_like(st.conv[:1]), torch.zeros_like(st.rec[:1]))
+                    jn = js["layers"][li] = GDNJournal(st, sh)
+                if js["rows"] is None:
+                    js["rows"] = (b.pos.clone(), b.slot.clone())      # the engine advances its row descriptor after the step
+            jpos, jslot = self._jcur["rows"] if jn is not None else (b.pos, b.slot)
             if "kda" in g:
-                y = kda_forward(proj, x, g["kda"], b.pos, b.slot, self._states(kv)[li], self.dims, g["conv_w"], cfg.rms_eps)
+                y = kda_forward(proj, x, g["kda"], jpos, jslot, st, self.dims, g["conv_w"], cfg.rms_eps, journal=jn)
                 return g["out_proj"].forward(y.to(x.dtype), out=pbuf)
-            y = gdn_forward(proj, b.pos, b.slot, self._states(kv)[li], self.dims, g["conv_w"], g["A_log"], g["dt_bias"],
-                            g["norm_w"], cfg.rms_eps)
+            y = gdn_forward(proj, jpos, jslot, st, self.dims, g["conv_w"], g["A_log"], g["dt_bias"],
+                            g["norm_w"], cfg.rms_eps, journal=jn)
             return g["out_proj"].forward(y.to(x.dtype), out=pbuf)
         kpool, vpool = kv.layer(L.kv_index)
         qkv = L.qkv.forward(x)
@@ -209,6 +229,29 @@ class HybridModel(MoEModel):
                             torch.arange(cap, dtype=torch.int32, device=kpool.device))
         return self.qsa_scr
 
+    # ---- speculative verify blocks: journal and rollback of the recurrent state
+    journal_on = False            # set by the engine for a verify step (rows of one slot that may be rejected)
+
+    def begin_journal(self, on: bool, tag=0) -> None:
+        """Called before a forward. ``tag`` names the set of operands this forward records into (the engine passes the
+        row count: a CUDA graph of that row count keeps writing the tensors its capture pass recorded)."""
+        self.journal_on = bool(on)
+        if not hasattr(self, "_jsets"):
+            self._jsets, self._shadows = {}, {}
+        if on:
+            self._jcur = self._jsets.setdefault(tag, {"rows": None, "layers": {}})
+            self._jcur["rows"] = None
+            self._jlast = tag
+
+    def rollback_state(self, slot: int, keep: int) -> None:
+        """After a journalled block: leave the slot's recurrent and convolution state as if only the block's first
+        ``keep`` rows had run (the KV pool needs nothing: rejected rows are overwritten by the next step)."""
+        js = getattr(self, "_jsets", {}).get(getattr(self, "_jlast", None))
+        if js is None:
+            raise RuntimeError("rollback without a journalled step")
+        for li, jn in js["layers"].items():
+            jn.replay(self.gdn_states[li], slot, keep)
+
     # recurrent state travels with sequence snapshots
     def snapshot_state(self, slot: int) -> list:
         return [s.snapshot(slot) if s is not None else None for s in (self.gdn_states or [])]
@@ -217,3 +260,16 @@ class HybridModel(MoEModel):
         for s, snap in zip(self.gdn_states or [], snaps):
             if s is not None and snap is not None:
                 s.restore(slot, snap)
+
+    def pack_state(self, slot: int) -> dict:
+        """The slot's state of every linear-attention layer as two stacked host tensors (what a prefix snapshot stores)."""
+        sts = [s for s in (self.gdn_states or []) if s is not None]
+        if not sts:
+            return {}
+        return {"gdn_conv": torch.stack([s.conv[slot] for s in sts]).cpu(), "gdn_rec": torch.stack([s.rec[slot] for s in sts]).cpu()}
+
+    def unpack_state(self, slot: int, snap: dict, kv) -> None:
+        sts = [s for s in self._states(kv) if s is not None]
+        for i, s in enumerate(sts):
+            s.conv[slot].copy_(snap["gdn_conv"][i])
+            s.rec[slot].copy_(snap["gdn_rec"][i])

@@ -100,9 +100,45 @@ def gdn_reference(proj, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log, dt_b
     return y.reshape(n, nv * dv)
 
 
-def gdn_forward(proj, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log, dt_bias, norm_w, eps: float, scratch=None):
-    """GPU path: prepare (conv + norms + gates, parallel over rows), recurrence (sequential per slot), gated norm."""
+class GDNJournal:
+    """What a block of rows did to one layer's state, kept so that a speculative verify step can be taken back: the
+    state of the block's slot before the block (``shadow``) and the per-row operands of the recurrence (on the GPU the
+    outputs of the prepare kernel: post-convolution q | k | v, decay and beta; on the CPU the projection rows).
+    ``replay(keep)`` restores the shadow and applies the first ``keep`` rows again with the same kernel and the same
+    operands, so the state equals, bit for bit, the one that stepping only those rows would have left.
+    Reference: inc/engine/modules/gdn.h:157-161 (journal + kda_replay). A slot's state of one layer is 2 MB here, so
+    the shadow is a device copy inside the verify step's graph rather than a 36 MiB snapshot per row."""
+
+    def __init__(self, st: GDNState, shadow: tuple | None = None):
+        """``shadow``: (conv [1, ...], rec [1, ...]) buffers shared by the journals of one layer (one per row count of the
+        verify step: each CUDA graph keeps its own operands, and only the last step's shadow is ever needed)."""
+        self.shadow_conv, self.shadow_rec = shadow if shadow is not None else (torch.zeros_like(st.conv[:1]),
+                                                                               torch.zeros_like(st.rec[:1]))
+        self.rows = None          # operands of the last journalled block
+        self.fn = None            # callable(keep): applies rows [0, keep) to the state
+
+    def begin(self, st: GDNState, slot: torch.Tensor):
+        idx = slot[:1].clamp(min=0).long()
+        torch.index_select(st.conv, 0, idx, out=self.shadow_conv)
+        torch.index_select(st.rec, 0, idx, out=self.shadow_rec)
+
+    def replay(self, st: GDNState, slot: int, keep: int):
+        st.conv[slot].copy_(self.shadow_conv[0])
+        st.rec[slot].copy_(self.shadow_rec[0])
+        if keep > 0 and self.fn is not None:
+            self.fn(keep)
+
+
+def gdn_forward(proj, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log, dt_bias, norm_w, eps: float, scratch=None,
+                journal: GDNJournal | None = None):
+    """GPU path: prepare (conv + norms + gates, parallel over rows), recurrence (sequential per slot), gated norm.
+    ``journal``: the block's slot state is copied aside first and the operands are kept for ``journal.replay``."""
+    if journal is not None:
+        journal.begin(st, slot)
     if not proj.is_cuda:
+        if journal is not None:
+            journal.fn = lambda keep: gdn_reference(proj[:keep], pos[:keep], slot[:keep], st, d, conv_w, A_log, dt_bias,
+                                                    norm_w, eps)
         return gdn_reference(proj, pos, slot, st, d, conv_w, A_log, dt_bias, norm_w, eps).to(proj.dtype)
     n = proj.shape[0]
     dev = proj.device
@@ -118,6 +154,13 @@ def gdn_forward(proj, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log, dt_bia
          ptr(u), ptr(gb), ptr(o), n, d.n_k, d.n_v, d.dk, d.dv, d.conv_k, st.conv.shape[0])
     call("gdn_gated_norm", "pplpp" + "iiiii" + "f", ptr(o), ptr(proj), proj.stride(0), ptr(norm_w), ptr(out), n, d.n_v, d.dv,
          C, d.conv_k, float(eps))
+    if journal is not None:
+        o2 = torch.empty_like(o)
+
+        def again(keep, proj=proj, pos=pos, slot=slot, u=u, gb=gb):
+            call("gdn_recurrent", "plpppppppiiiiiii", ptr(proj), proj.stride(0), ptr(pos), ptr(slot), ptr(st.conv), ptr(st.rec),
+                 ptr(u), ptr(gb), ptr(o2), keep, d.n_k, d.n_v, d.dk, d.dv, d.conv_k, st.conv.shape[0])
+        journal.fn = again
     return out
 
 
@@ -176,12 +219,18 @@ def kda_reference(proj, f, z, pos, slot, st: GDNState, d: GDNDims, conv_w, A_log
     return y.reshape(n, nv * dv)
 
 
-def kda_forward(proj, x, W: KDAWeights, pos, slot, st: GDNState, d: GDNDims, conv_w, eps: float) -> torch.Tensor:
+def kda_forward(proj, x, W: KDAWeights, pos, slot, st: GDNState, d: GDNDims, conv_w, eps: float,
+                journal: GDNJournal | None = None) -> torch.Tensor:
     """Kimi delta attention over the rows: ``proj`` is the fused [q | k | v | - | b | -] projection of ``x`` (the layout of
     the gated delta rule, its z and a columns unused), the decay and the output gate come from the low-rank pairs in ``W``."""
     f = W.f_b.forward(W.f_a.forward(x))
     z = W.g_b.forward(W.g_a.forward(x))
+    if journal is not None:
+        journal.begin(st, slot)
     if not proj.is_cuda:
+        if journal is not None:
+            journal.fn = lambda keep: kda_reference(proj[:keep], f[:keep], z[:keep], pos[:keep], slot[:keep], st, d, conv_w,
+                                                    W.A_log, W.dt_bias, W.norm_w, eps)
         return kda_reference(proj, f, z, pos, slot, st, d, conv_w, W.A_log, W.dt_bias, W.norm_w, eps).to(proj.dtype)
     n, dev = proj.shape[0], proj.device
     C, nv = d.conv_dim, d.n_v
@@ -197,4 +246,11 @@ def kda_forward(proj, x, W: KDAWeights, pos, slot, st: GDNState, d: GDNDims, con
     call("kda_recurrent", "plppppppppiiiiiii", ptr(proj), proj.stride(0), ptr(pos), ptr(slot), ptr(st.conv), ptr(st.rec),
          ptr(u), ptr(gb), ptr(o), ptr(kdec), n, d.n_k, d.n_v, d.dk, d.dv, d.conv_k, st.conv.shape[0])
     call("kda_gated_norm", "pplppiiif", ptr(o), ptr(z), z.stride(0), ptr(W.norm_w), ptr(out), n, nv, d.dv, float(eps))
+    if journal is not None:
+        o2 = torch.empty_like(o)
+
+        def again(keep, proj=proj, pos=pos, slot=slot, u=u, gb=gb, kdec=kdec):
+            call("kda_recurrent", "plppppppppiiiiiii", ptr(proj), proj.stride(0), ptr(pos), ptr(slot), ptr(st.conv), ptr(st.rec),
+                 ptr(u), ptr(gb), ptr(o2), ptr(kdec), keep, d.n_k, d.n_v, d.dk, d.dv, d.conv_k, st.conv.shape[0])
+        journal.fn = again
     return out

@@ -151,9 +151,12 @@ class Engine:
             self.s_pos[:rows].add_(1)
         return logits
 
-    def _run_rows(self, rows: int, topk: bool = False):
+    def _run_rows(self, rows: int, topk: bool = False, journal: bool = False):
         nsplit = self._nsplit(rows)
-        key = (rows, nsplit, self.feedback, topk)
+        journal = journal and self.supports_journal
+        if self.supports_journal:
+            self.model.begin_journal(journal, rows)
+        key = (rows, nsplit, self.feedback, topk, journal)
         if not self.use_graphs or rows > MAX_GRAPH_ROWS:
             self._forward_static(rows, nsplit, topk)
             return
@@ -183,19 +186,31 @@ class Engine:
         self.s_pos[:n].copy_(self.h_in[1, :n], non_blocking=True)
         self.s_slot[:n].copy_(self.h_in[2, :n], non_blocking=True)
 
-    def step(self, ids: list[int], pos: list[int], slots: list[int]) -> list[int]:
-        """One batched decode / verify step with host round trip: H2D rows, forward, D2H tokens."""
+    @property
+    def supports_journal(self) -> bool:
+        """Models with recurrent state record verify blocks so that rejected rows can be taken back (``rollback``)."""
+        return hasattr(self.model, "rollback_state")
+
+    def rollback(self, slot: int, keep_rows: int) -> None:
+        """After ``step(..., journal=True)`` over rows of ``slot``: keep the effect of the first ``keep_rows`` rows on the
+        model's per-slot state (no-op for models whose only state is the KV pool)."""
+        if self.supports_journal:
+            self.model.rollback_state(slot, keep_rows)
+
+    def step(self, ids: list[int], pos: list[int], slots: list[int], journal: bool = False) -> list[int]:
+        """One batched decode / verify step with host round trip: H2D rows, forward, D2H tokens. ``journal``: the rows
+        are a speculative block of one slot, part of which may be taken back with :meth:`rollback`."""
         n = len(ids)
         for s, p in zip(slots, pos):
             self.kv.reserve(s, p + 2)
         self.set_rows(ids, pos, slots)
-        self._run_rows(n)
+        self._run_rows(n, journal=journal)
         self.h_tok[:n].copy_(self.s_tok[:n], non_blocking=True)
         if self.cuda:
             torch.cuda.current_stream().synchronize()
         return self.h_tok[:n].tolist()
 
-    def step_candidates(self, ids: list[int], pos: list[int], slots: list[int]):
+    def step_candidates(self, ids: list[int], pos: list[int], slots: list[int], journal: bool = False):
         """Like :meth:`step` but returns, per row, the merged top-16 candidates (ids, logits, lse) for the
         host sampler instead of the greedy token."""
         from .sampling import Candidates, merge_shards
@@ -203,7 +218,7 @@ class Engine:
         for s, p in zip(slots, pos):
             self.kv.reserve(s, p + 2)
         self.set_rows(ids, pos, slots)
-        self._run_rows(n, topk=True)
+        self._run_rows(n, topk=True, journal=journal)
         cid, cval, clse = self.s_cand_ids[:n], self.s_cand_vals[:n], self.s_cand_lse[:n]
         if self.comm.size > 1:
             cid, cval, clse = (self.comm.all_gather_rows(t) for t in (cid, cval, clse))

@@ -144,7 +144,8 @@ class Generator:
     def __init__(self, engine, tokenizer, options=None, prefix_cache=None, eos_ids=None):
         self.engine, self.tok, self.opt, self.cache = engine, tokenizer, options, prefix_cache
         mdl = getattr(engine, "model", None)
-        if self.cache is not None and mdl is not None and getattr(mdl, "prefix_resume", "kv") != "kv":
+        self._state_snaps = mdl is not None and getattr(mdl, "prefix_resume", "kv") == "kv+state"
+        if self.cache is not None and mdl is not None and getattr(mdl, "prefix_resume", "kv") not in ("kv", "kv+state"):
             # snapshots hold KV pages only; this model keeps state elsewhere, and resuming would continue from whatever
             # the slot's previous request left there
             from ..utils import log
@@ -296,12 +297,21 @@ class Generator:
         if self.cache is not None and req.cache_prefix:
             t0 = time.time()
             chain = self.cache.find(req.cache_key if req.cache_key is not None else req.prompt)
+            snaps = []
             for node in chain:
                 snap = self.cache.load(node)
                 if snap is None:
                     break
+                snaps.append((node, snap))
+            if self._state_snaps:
+                # the recurrent state is that of the last node of the chain: resume at the deepest node that holds one
+                while snaps and "gdn_rec" not in snaps[-1][1]:
+                    snaps.pop()
+            for node, snap in snaps:
                 self.engine.kv.load_rows(s.idx, snap)
                 s.pos = s.cursor = node.end
+            if self._state_snaps and snaps:
+                self.engine.model.unpack_state(s.idx, snaps[-1][1], self.engine.kv)
             s.cached_tokens = s.pos
             s.t_restore_ms = (time.time() - t0) * 1e3
         if s.suffix is not None:
@@ -370,7 +380,15 @@ class Generator:
     def _store_prefix(self, s: SlotState, upto: int, pinned: bool = False):
         t0 = time.time()
         toks = ((s.req.cache_key if s.req.cache_key is not None else s.req.prompt) + s.out)[:upto]
-        self.cache.insert(toks, upto, lambda a, b: self.engine.kv.save_rows(s.idx, a, b), pinned=pinned)
+        if self._state_snaps and upto != s.pos:
+            return                 # the recurrent state belongs to position s.pos: no snapshot of an earlier point exists
+
+        def snap(a, b):
+            d = self.engine.kv.save_rows(s.idx, a, b)
+            if self._state_snaps:
+                d.update(self.engine.model.pack_state(s.idx))
+            return d
+        self.cache.insert(toks, upto, snap, pinned=pinned)
         s.t_store_ms += (time.time() - t0) * 1e3
 
     # ------------------------------------------------------------------------------------------ decode
@@ -488,8 +506,9 @@ class Generator:
         rows = [s.next_tok] + drafts
         pos = [s.pos + i for i in range(len(rows))]
         params = s.req.params
+        jn = {"journal": True} if getattr(self.engine, "supports_journal", False) else {}
         if params.greedy:
-            toks = self.engine.step(rows, pos, [s.idx] * len(rows))
+            toks = self.engine.step(rows, pos, [s.idx] * len(rows), **jn)
             # longest accepted prefix: draft i is accepted when the model's token after row i equals it
             acc = 0
             while acc < len(drafts) and toks[acc] == drafts[acc]:
@@ -499,7 +518,7 @@ class Generator:
             # sampled requests: exact speculative sampling against the point-mass proposal of each draft. Row i is
             # judged with the penalties of everything committed before it (the drafts accepted so far included), so the
             # tokens are distributed exactly as one-row sampling steps would give them.
-            cands = self.engine.step_candidates(rows, pos, [s.idx] * len(rows))
+            cands = self.engine.step_candidates(rows, pos, [s.idx] * len(rows), **jn)
             counts = dict(s.counts.counts)
             new, acc = [], 0
             for i in range(len(rows)):
@@ -514,6 +533,8 @@ class Generator:
                     break
                 acc += 1
             toks = new + [new[-1]] * (len(rows) - len(new))
+        if jn and acc < len(drafts):
+            self.engine.rollback(s.idx, acc + 1)          # recurrent state: as if only the accepted rows had run
         ms = (time.time() - t0) * 1e3
         s.pos += acc + 1
         s.next_tok = new[-1]

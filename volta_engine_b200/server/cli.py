@@ -257,7 +257,7 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
     except (FileNotFoundError, KeyError):
         template = None
     cache = None
-    if o.prefix_cache_mib > 0 and getattr(model, "prefix_resume", None) == "kv":
+    if o.prefix_cache_mib > 0 and getattr(model, "prefix_resume", None) in ("kv", "kv+state"):
         # a snapshot holds KV pages only: families with state outside the pool (recurrent / conv state, window and
         # compressor rings, indexer keys) run without the cache instead of resuming from a stale state
         from ..runtime.prefix_cache import model_fingerprint
