@@ -96,7 +96,7 @@ def test_sandwich_norm_windowed_model_prefill_equals_decode():
 
 def test_gguf_block_decoders_match_ggml_goldens():
     """(sum, one element, max |x|) of the decoded synthetic blocks; the numbers were produced by the ggml C row
-    dequantisers on the same bytes (bit-equal to this decoder for all twelve formats when they were taken)."""
+    dequantisers on the same bytes (bit-equal to this decoder for every format when they were taken)."""
     from volta_engine_b200.quant import gguf as G
     golden = {
         3: (5.891298294067383, -0.13057708740234375, 0.30628204345703125),
@@ -107,6 +107,14 @@ def test_gguf_block_decoders_match_ggml_goldens():
         13: (-4511.329105377197, 0.2799797058105469, 24.929656982421875),
         20: (17.381572723388672, -0.029878616333007812, 2.507598876953125),
         23: (1052.876178741455, -0.05899810791015625, 44.815093994140625),
+        # the codebook formats: IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M
+        16: (-3.6108641624450684, -0.38962554931640625, 2.257613182067871),
+        17: (-5.912283897399902, 0.3155059814453125, 3.1120147705078125),
+        18: (34.321876525878906, 0.09368896484375, 7.841766357421875),
+        19: (-0.5756797790527344, -0.14499664306640625, 0.30487060546875),
+        21: (0.289398193359375, 0.39859771728515625, 4.753875732421875),
+        22: (1.9254817962646484, 0.18060302734375, 3.0135135650634766),
+        29: (-2.6709327697753906, 0.05484151840209961, 0.32469749450683594),
     }
     for t, (s, e, m) in golden.items():
         y = G.dequantize(G.random_blocks(t, 2, 512, seed=100 + t), t, 512).double()

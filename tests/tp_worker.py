@@ -214,25 +214,39 @@ def main():
         d_tp = DSV4Model(dcfg, dev, comm).init_random(seed=5, std=0.05)
         dkv = PagedKVCache(1, 1, 64, 16, 1, 512, dev)
         de = Engine(d_tp, dkv, prefill_chunk=64)
-        d_toks = [de.prefill(0, dprompt)]
-        for i in range(6):
-            d_toks.append(de.step([d_toks[-1]], [len(dprompt) + i], [0])[0])
-        same_on_all_ranks(torch.tensor(d_toks, device=dev), "DSV4 TP tokens")
-        dkv.reserve(0, 200)
-        dprobe = BatchRows.make(dprompt[:40], list(range(120, 160)), [0] * 40, dev, LOGITS_LAST, d_tp.nq, prefill=True)
-        lg_tp = d_tp.forward(dprobe, dkv).float().clone()
         d1 = DSV4Model(DSV4Config.tiny_dsv4(), dev).init_random(seed=5, std=0.05)
         dkv1 = PagedKVCache(1, 1, 64, 16, 1, 512, dev)
         de1 = Engine(d1, dkv1, prefill_chunk=64)
-        d1_toks = [de1.prefill(0, dprompt)]
-        for i in range(6):
-            d1_toks.append(de1.step([d1_toks[-1]], [len(dprompt) + i], [0])[0])
-        if rank == 0:
-            print(f"dsv4 tp2 tokens {d_toks} single {d1_toks}", flush=True)
-        same = sum(a == b for a, b in zip(d_toks, d1_toks))
+        d_toks, d1_toks = [de.prefill(0, dprompt)], [de1.prefill(0, dprompt)]
         assert d_toks[0] == d1_toks[0], "DSV4 TP prefill token differs from the single-GPU model"
-        first_diff = next((i for i, (a, b) in enumerate(zip(d_toks, d1_toks)) if a != b), len(d_toks))
-        assert first_diff >= 3, f"DSV4 TP run leaves the single-GPU run at step {first_diff}: {d_toks} vs {d1_toks}"
+        # the single-GPU run leads and the TP model is fed the same tokens: at every step its pick must be the single-GPU
+        # pick, or one of its three best within 4 % of the row's top-16 range (bf16 partial sums per rank move the logits
+        # by a few bf16 steps); most steps must agree exactly
+        agree = 0
+        for i in range(6):
+            cand = de1.step_candidates([d1_toks[-1]], [len(dprompt) + i], [0])[0]
+            t_tp = de.step([d1_toks[-1]], [len(dprompt) + i], [0])[0]
+            d_toks.append(t_tp)
+            d1_toks.append(cand.ids[0])
+            if t_tp == cand.ids[0]:
+                agree += 1
+                continue
+            assert t_tp in cand.ids[:3], f"DSV4 TP step {i}: picked {t_tp}, single-GPU candidates {cand.ids[:4]}"
+            gap = cand.logits[0] - cand.logits[cand.ids.index(t_tp)]
+            assert gap <= 0.04 * (cand.logits[0] - cand.logits[-1]), \
+                f"DSV4 TP step {i}: picked {t_tp} at logit gap {gap:.4g}, top-16 range {cand.logits[0] - cand.logits[-1]:.4g}"
+        same_on_all_ranks(torch.tensor(d_toks, device=dev), "DSV4 TP tokens")
+        if rank == 0:
+            print(f"dsv4 tp2 tokens {d_toks} single {d1_toks} ({agree} of 6 steps identical)", flush=True)
+        assert agree >= 4, f"DSV4 TP run agrees with the single-GPU run on {agree} of 6 steps only"
+        dkv.reserve(0, 200)
+        dkv1.reserve(0, 200)
+        probe = lambda m: BatchRows.make(dprompt[:40], list(range(120, 160)), [0] * 40, dev, LOGITS_LAST, m.nq, prefill=True)
+        lg_tp = d_tp.forward(probe(d_tp), dkv).float()
+        lg_1 = d1.forward(probe(d1), dkv1).float()
+        if comm.size > 1 and lg_tp.shape[-1] != lg_1.shape[-1]:
+            lg_tp = comm.all_gather_rows(lg_tp.t().contiguous()).t()       # vocabulary shards -> whole rows
+        assert cos(lg_tp, lg_1) > 0.99, f"DSV4 TP prefill logits against the single-GPU model: cos {cos(lg_tp, lg_1)}"
         assert (d_tp.heads, d_tp.groups, d_tp.e_local) == (8, 1, 4)
         assert K.check_status(dev) == 0
     dist.barrier()

@@ -37,6 +37,9 @@ class MoEConfig(DenseConfig):
     first_dense_layers: int = 0    # leading layers with a dense FFN of width cfg.ffn
     router_bias_zipf: float = 0.0  # synthetic skew: expert bias ~ Zipf(s)
     shared_gate: bool = False      # shared expert output scaled by sigmoid(x . w): one more row of the router weight
+    # storage of the routed experts: "nvfp4", or GGUF blocks "gguf_<type>" / "gguf_<gate-up type>+<down type>"
+    # (e.g. "gguf_iq2_xxs+q4_k"); a random-init GGUF bank is random block bytes drawn on the device
+    expert_quant: str = "nvfp4"
     model_type: str = "moe"
 
     @classmethod
@@ -148,17 +151,23 @@ class MoEModel(DenseModel):
                 ranks = torch.arange(1, cfg.n_experts + 1, device=dev, dtype=torch.float32)
                 perm = torch.randperm(cfg.n_experts, generator=gen, device=dev)
                 L.router_bias = (torch.log(ranks.pow(-cfg.router_bias_zipf)))[perm].contiguous()
-            gp, gs, gg, dp, ds, dg = [], [], [], [], [], []
-            for e in range(cfg.n_experts):       # every rank draws all experts so shards agree; keeps its own
-                wgu, wdn = rnd(2 * I, H), rnd(H, I)
-                if self.e0 <= e < self.e0 + self.e_local:
-                    p, s, g = qn.quantize_nvfp4(wgu, search=search)
-                    gp.append(p), gs.append(s), gg.append(g)
-                    p, s, g = qn.quantize_nvfp4(wdn, search=search)
-                    dp.append(p), ds.append(s), dg.append(g)
-            L.bank = ExpertBank(torch.stack(gp), torch.stack(gs), torch.tensor(gg, device=dev, dtype=torch.float32),
-                                torch.stack(dp), torch.stack(ds), torch.tensor(dg, device=dev, dtype=torch.float32),
-                                self.e0, I, H)
+            if cfg.expert_quant.startswith("gguf_"):
+                from ..ops.moe_gguf import GGUFExpertBank, parse_expert_quant
+                gt, dt = parse_expert_quant(cfg.expert_quant)
+                L.bank = GGUFExpertBank.random(self.e_local, I, H, gt, dt, self.e0, seed=seed * 100003 + li * 4099 + self.e0,
+                                               device=dev, amp=std)
+            else:
+                gp, gs, gg, dp, ds, dg = [], [], [], [], [], []
+                for e in range(cfg.n_experts):       # every rank draws all experts so shards agree; keeps its own
+                    wgu, wdn = rnd(2 * I, H), rnd(H, I)
+                    if self.e0 <= e < self.e0 + self.e_local:
+                        p, s, g = qn.quantize_nvfp4(wgu, search=search)
+                        gp.append(p), gs.append(s), gg.append(g)
+                        p, s, g = qn.quantize_nvfp4(wdn, search=search)
+                        dp.append(p), ds.append(s), dg.append(g)
+                L.bank = ExpertBank(torch.stack(gp), torch.stack(gs), torch.tensor(gg, device=dev, dtype=torch.float32),
+                                    torch.stack(dp), torch.stack(ds), torch.tensor(dg, device=dev, dtype=torch.float32),
+                                    self.e0, I, H)
             L.shared_gu = L.shared_dn = None
             if cfg.shared_ffn:
                 S = cfg.shared_ffn
@@ -261,7 +270,10 @@ class MoEModel(DenseModel):
         y = pbuf if pbuf is not None else torch.empty(rows, H, dtype=x.dtype, device=x.device)
         I = bank.inter
         tier = getattr(L, "tier", None)
-        if tier is not None or rows <= 16 or bank.gu_sf is None:
+        if hasattr(bank, "routes"):
+            # experts held as GGUF blocks: fused dequant mat-vec per route, or per-slab dequantise + grouped GEMM
+            d, inv = bank.routes(x, ids, act, cfg.act_limit), None
+        elif tier is not None or rows <= 16 or bank.gu_sf is None:
             # tiered residency: per-expert base pointers (device slot or pinned host memory) instead of the stacked bank
             gu = (tier.tab_gu.data_ptr(), 0) if tier is not None else (ptr(bank.gu_p), ptr(bank.gu_s))
             dn = (tier.tab_dn.data_ptr(), 0) if tier is not None else (ptr(bank.dn_p), ptr(bank.dn_s))

@@ -1,4 +1,5 @@
-"""Linear layer over GGUF block-quantised weights (Q8_0, Q4_0/1, Q5_0/1, Q2_K..Q6_K, IQ4_NL/XS; F16/BF16 pass through).
+"""Linear layer over GGUF block-quantised weights (Q8_0, Q4_0/1, Q5_0/1, Q2_K..Q6_K, IQ4_NL/XS, IQ1_S/M, IQ2_XXS/XS/S,
+IQ3_XXS/S; F16/BF16 pass through).
 
 GPU: rows <= 16 use the fused dequant mat-vec (csrc/cuda/gguf_gemv.cu); larger row counts dequantise to bf16
 and run the tcgen05 GEMM. CPU: fp32 oracle, optionally with the CPU backend's Q8_0 activation semantics
@@ -6,15 +7,35 @@ and run the tcgen05 GEMM. CPU: fp32 oracle, optionally with the CPU backend's Q8
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
+from .. import _lib
 from .._lib import call, ptr
 from ..quant import gguf as gq
 from . import kernels as K
 
 
 FUSED_TYPES = frozenset((gq.GGML_Q8_0, gq.GGML_Q4_0, gq.GGML_Q4_K, gq.GGML_Q6_K, gq.GGML_Q4_1, gq.GGML_Q5_0, gq.GGML_Q5_1,
-                         gq.GGML_Q2_K, gq.GGML_Q3_K, gq.GGML_Q5_K, gq.GGML_IQ4_NL, gq.GGML_IQ4_XS))
+                         gq.GGML_Q2_K, gq.GGML_Q3_K, gq.GGML_Q5_K, gq.GGML_IQ4_NL, gq.GGML_IQ4_XS)) | gq.IQ_TYPES
+
+_iq_tables: dict = {}
+
+
+def ensure_iq_grids(device) -> None:
+    """The codebook formats read their grids from one table in device memory: upload it once per device."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key in _iq_tables:
+        return
+    from ..quant import gguf_iq
+    t = torch.frombuffer(bytearray(gguf_iq.grid_blob()), dtype=torch.uint8).to(device)
+    with torch.cuda.device(device):
+        rc = _lib.kernels().ve_gguf_set_iq_grids(ctypes.c_void_p(t.data_ptr()))
+    if rc != 0:
+        raise RuntimeError(f"ve_gguf_set_iq_grids failed with CUDA error {rc}")
+    _iq_tables[key] = t
 
 
 class LinearGGUF:
@@ -24,12 +45,16 @@ class LinearGGUF:
         self.row_bytes = self.raw.shape[1]
         assert self.row_bytes == gq.row_bytes(ggml_type, in_features)
         self.act_q8 = act_q8
+        if self.raw.is_cuda and ggml_type in gq.IQ_TYPES:
+            ensure_iq_grids(self.raw.device)
 
     @classmethod
     def from_dense(cls, w: torch.Tensor, ggml_type: int, act_q8: bool = False):
         return cls(gq.quantize(w, ggml_type), ggml_type, w.shape[0], w.shape[1], act_q8)
 
     def dequant(self) -> torch.Tensor:
+        if self.raw.is_cuda and self.ggml_type in gq.IQ_TYPES:
+            ensure_iq_grids(self.raw.device)
         if self.raw.is_cuda and self.ggml_type in FUSED_TYPES:
             out = torch.empty(self.out_features, self.in_features, dtype=torch.bfloat16, device=self.raw.device)
             call("gguf_dequant", "pilpli", ptr(self.raw), self.ggml_type, self.row_bytes, ptr(out), self.out_features,
@@ -47,6 +72,8 @@ class LinearGGUF:
                 y = y + residual.float()
             return y if out_f32 else y.to(x.dtype)
         rows = x.shape[0]
+        if self.ggml_type in gq.IQ_TYPES:
+            ensure_iq_grids(x.device)
         quant = self.ggml_type in FUSED_TYPES
         if rows <= 16 and quant and residual is None:
             if out is None:

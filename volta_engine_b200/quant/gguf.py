@@ -11,6 +11,7 @@ src/kernels/cpu/gguf/ggml): little-endian, fp16 scales.
   Q2_K (16 x {4-bit scale, 4-bit min}, 64 bytes of 2-bit values, d, dmin), Q3_K (32 bytes of high bits, 64 bytes of
   2-bit values, 16 packed 6-bit scales, d), Q5_K (Q4_K plus 32 bytes of high bits)
   IQ4_NL (Q4_0 container over 16 non-uniform levels), IQ4_XS (256 values, 8 six-bit sub-block scales over the levels)
+  IQ1_S, IQ1_M, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S: codebook formats, see quant/gguf_iq.py
 Read-only formats (no quantiser): a synthetic block is random bytes with finite fp16 fields (`random_blocks`).
 CPU linear semantics (src/backend/cpu/linear_gguf.cpp:65-113): the activation row is quantised to Q8_0,
 each block contributes an integer dot product scaled by both block scales, accumulated in fp32.
@@ -352,14 +353,17 @@ def dequantize_iq4_xs(raw, K):
     return (q * (d[..., None] * (ls - 32).float())[..., None]).reshape(rows, K)
 
 
-def random_blocks(ggml_type: int, rows: int, K: int, seed: int = 0, amp: float = 0.02) -> torch.Tensor:
-    """Synthetic packed rows: uniformly random payload bytes, fp16 fields set to small finite values."""
+def random_blocks(ggml_type: int, rows: int, K: int, seed: int = 0, amp: float = 0.02, device="cpu") -> torch.Tensor:
+    """Synthetic packed rows: uniformly random payload bytes, fp16 fields set to small finite values. ``device``: where
+    the bytes are drawn (a CUDA device draws a large bank in place; the values then differ from the CPU stream)."""
+    if ggml_type in IQ_TYPES:
+        return _iq.random_iq_blocks(ggml_type, rows, K, seed, amp, device)
     n, bs = BLOCK[ggml_type]
-    g = torch.Generator().manual_seed(seed)
-    raw = torch.randint(0, 256, (rows, K // n, bs), dtype=torch.uint8, generator=g)
+    g = torch.Generator(device=device).manual_seed(seed)
+    raw = torch.randint(0, 256, (rows, K // n, bs), dtype=torch.uint8, generator=g, device=device)
     for off in F16_FIELDS[ggml_type]:
-        v = (torch.rand(rows, K // n, generator=g) * 0.9 + 0.1) * amp
-        v = v * (torch.randint(0, 2, (rows, K // n), generator=g) * 2 - 1)
+        v = (torch.rand(rows, K // n, generator=g, device=device) * 0.9 + 0.1) * amp
+        v = v * (torch.randint(0, 2, (rows, K // n), generator=g, device=device) * 2 - 1)
         raw[..., off:off + 2] = _f16_bytes(v)
     return raw.reshape(rows, -1)
 
@@ -407,6 +411,15 @@ def dequantize(raw: torch.Tensor, ggml_type: int, K: int) -> torch.Tensor:
         return raw.contiguous().view(torch.float32).reshape(rows, K)
     raise ValueError(f"unsupported ggml type {ggml_type}")
 
+
+from . import gguf_iq as _iq          # noqa: E402  (the codebook formats live in their own module)
+
+GGML_IQ2_XXS, GGML_IQ2_XS, GGML_IQ3_XXS, GGML_IQ1_S, GGML_IQ3_S, GGML_IQ2_S, GGML_IQ1_M = (
+    _iq.GGML_IQ2_XXS, _iq.GGML_IQ2_XS, _iq.GGML_IQ3_XXS, _iq.GGML_IQ1_S, _iq.GGML_IQ3_S, _iq.GGML_IQ2_S, _iq.GGML_IQ1_M)
+IQ_TYPES = frozenset(_iq.IQ_BLOCK)
+BLOCK.update(_iq.IQ_BLOCK)
+NAMES.update(_iq.IQ_NAMES)
+_DEQUANT.update(_iq.IQ_DEQUANT)
 
 _QUANT.update({GGML_Q4_1: quantize_q4_1, GGML_Q5_0: quantize_q5_0, GGML_Q5_1: quantize_q5_1,
                GGML_IQ4_NL: quantize_iq4_nl})

@@ -23,7 +23,8 @@ TABLE = {
     "nvfp4_gemv_mma_static": ("LinearNVFP4 decode", D), "nvfp4_quant_rows": ("NVFP4 quantise", P),
     "nvfp4_dequant": ("NVFP4 quantise", P), "bf16_gemv_f32": ("LinearPlainGEMV", P),
     "exl3_gemv": ("LinearTrellis", P), "exl3_reconstruct": ("LinearTrellis", P), "had128": ("LinearTrellis", P),
-    "gguf_gemv": ("LinearGguf", P), "gguf_dequant": ("LinearGguf", P),
+    "gguf_gemv": ("LinearGguf", P), "gguf_dequant": ("LinearGguf", P), "gguf_set_iq_grids": ("LinearGguf", P),
+    "gguf_moe_gemv": ("MoEGguf", P),
     "mla_rope_store": ("MLALatent", P), "mla_absorb_q": ("MLALatent", P), "mla_decode": ("MLALatent", P),
     "mla_expand_out": ("MLALatent", P),
     "dsa_prep": ("DSA", P), "dsa_pool_update": ("DSA", P), "dsa_score": ("DSA / QSA", P), "dsa_select": ("DSA / QSA", P),
