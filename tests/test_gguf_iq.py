@@ -104,6 +104,7 @@ def test_gpu_moe_model_with_gguf_experts_matches_the_cpu_statement():
     cfg = MoEConfig.tiny_moe(expert_quant="gguf_iq3_xxs+q4_k", hidden=256, expert_ffn=256)
     mc = MoEModel(cfg, "cpu").init_random(seed=3)
     mg = to_device(mc, "cuda")
+    mg.ensure_workspace(16, 8)
     prompt = torch.randint(0, cfg.vocab, (90,), generator=torch.Generator().manual_seed(1)).tolist()
     kvg, kvc = PagedKVCache(2, mg.nkv, 64, 16, 1, 512, "cuda"), PagedKVCache(2, mc.nkv, 64, 16, 1, 512, "cpu")
     kvg.reserve(0, 128)

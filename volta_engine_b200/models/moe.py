@@ -73,6 +73,22 @@ class ExpertBank:
     def nbytes(self):
         return sum(t.numel() * t.element_size() for t in (self.gu_p, self.gu_s, self.dn_p, self.dn_s))
 
+    @classmethod
+    def random(cls, E: int, inter: int, hidden: int, e0: int, seed: int, device, std: float = 0.02):
+        """Synthetic bank drawn directly in the storage format (uniform E2M1 codes, E4M3 block scales in [0.5, 1.875],
+        one tensor scale that puts the weights at about ``std``): a benchmark-sized model initialises in seconds instead
+        of quantising tens of thousands of dense matrices."""
+        g = torch.Generator(device=device).manual_seed(seed)
+
+        def part(n, k):
+            p = torch.randint(0, 256, (E, n, k // 2), dtype=torch.uint8, generator=g, device=device)
+            s = torch.randint(0x30, 0x40, (E, n, k // 16), dtype=torch.uint8, generator=g, device=device)
+            return p, s
+        gp, gs = part(2 * inter, hidden)
+        dp, ds = part(hidden, inter)
+        scale = torch.full((E,), std / 3.0, dtype=torch.float32, device=device)     # E2M1 codes have an rms of about 3
+        return cls(gp, gs, scale, dp, ds, scale.clone(), e0, inter, hidden)
+
     def dequant(self, which: str, e: int) -> torch.Tensor:
         p, s, g = (self.gu_p, self.gu_s, self.gu_g) if which == "gu" else (self.dn_p, self.dn_s, self.dn_g)
         return qn.dequantize_nvfp4(p[e], s[e], float(g[e]))
@@ -156,6 +172,8 @@ class MoEModel(DenseModel):
                 gt, dt = parse_expert_quant(cfg.expert_quant)
                 L.bank = GGUFExpertBank.random(self.e_local, I, H, gt, dt, self.e0, seed=seed * 100003 + li * 4099 + self.e0,
                                                device=dev, amp=std)
+            elif cfg.expert_quant == "nvfp4_random":
+                L.bank = ExpertBank.random(self.e_local, I, H, self.e0, seed * 100003 + li * 4099 + self.e0, dev, std)
             else:
                 gp, gs, gg, dp, ds, dg = [], [], [], [], [], []
                 for e in range(cfg.n_experts):       # every rank draws all experts so shards agree; keeps its own
