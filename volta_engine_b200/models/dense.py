@@ -121,9 +121,17 @@ class DenseModel:
         self.attn_ws = None
 
     # ------------------------------------------------------------------------------------- weights
-    def _make_linear(self, w: torch.Tensor, search: bool):
+    def _make_linear(self, w: torch.Tensor, search: bool, whole=None):
+        """``whole``: the full matrices this rank's shard ``w`` was cut from (a tensor or several). The NVFP4 tensor
+        scale then comes from them, so every rank's shard carries exactly the values of the single-GPU quantisation and
+        tensor-parallel results differ from single-GPU ones by summation order only."""
         if self.cfg.quant == "nvfp4":
-            return LinearNVFP4.from_dense(w, self.cfg.gemm_mode, search=search).prepare()
+            gs = None
+            if whole is not None and self.comm.size > 1:
+                parts = whole if isinstance(whole, (list, tuple)) else [whole]
+                gmax = max(float(t.abs().max()) for t in parts)
+                gs = gmax / (6.0 * 448.0) if gmax > 0 else 1.0
+            return LinearNVFP4.from_dense(w, self.cfg.gemm_mode, search=search, global_scale=gs).prepare()
         if self.cfg.quant.startswith("gguf_"):
             from ..ops.linear_gguf import LinearGGUF
             from ..quant import gguf as gq
@@ -155,19 +163,19 @@ class DenseModel:
             kv0 = (r // self.kv_rep) * self.nkv if cfg.n_kv < tp else r * self.nkv
             wqkv = torch.cat([wq[r * self.nq * hd:(r + 1) * self.nq * hd],
                               wk[kv0 * hd:(kv0 + self.nkv) * hd], wv[kv0 * hd:(kv0 + self.nkv) * hd]], 0)
-            L.qkv = self._make_linear(wqkv, search)
+            L.qkv = self._make_linear(wqkv, search, whole=(wq, wk, wv))
             del wq, wk, wv, wqkv
             wo = rnd(H, cfg.n_q * hd)
-            L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search)
+            L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search, whole=wo)
             del wo
             wg, wu = rnd(cfg.ffn, H), rnd(cfg.ffn, H)
             L.gate_up = self._make_linear(torch.cat([wg[r * self.ffn:(r + 1) * self.ffn],
-                                                     wu[r * self.ffn:(r + 1) * self.ffn]], 0), search)
+                                                     wu[r * self.ffn:(r + 1) * self.ffn]], 0), search, whole=(wg, wu))
             if isinstance(L.gate_up, LinearNVFP4) and FUSE_GATED_ACT:
                 L.gate_up.interleave_gated()
             del wg, wu
             wd = rnd(H, cfg.ffn)
-            L.down = self._make_linear(wd[:, r * self.ffn:(r + 1) * self.ffn].contiguous(), search)
+            L.down = self._make_linear(wd[:, r * self.ffn:(r + 1) * self.ffn].contiguous(), search, whole=wd)
             del wd
             L.attn_norm, L.ffn_norm = nw.clone(), nw.clone()
             L.post_attn_norm = L.post_ffn_norm = None
@@ -190,7 +198,7 @@ class DenseModel:
             head[: hi - lo] = full[lo:hi]
         quant_head = cfg.quant.startswith("gguf_") or (cfg.quant == "nvfp4" and cfg.lm_head_quant != "bf16"
                                                           and cfg.hidden % 256 == 0)
-        self.lm_head = self._make_linear(head.float(), search) if quant_head else LinearBF16(head)
+        self.lm_head = self._make_linear(head.float(), search, whole=full) if quant_head else LinearBF16(head)
         return self
 
     def weight_bytes(self) -> int:

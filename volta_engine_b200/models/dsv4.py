@@ -136,16 +136,18 @@ class DSV4Model(MoEModel):
         ones = torch.ones
         L.qa_norm = ones(ql, device=dev, dtype=bf)
         L.kv_norm = ones(V.HD, device=dev, dtype=bf)
-        wqb = rnd(cfg.n_q * V.HD, ql)[r * hl * V.HD:(r + 1) * hl * V.HD]
+        wqb_all = [rnd(cfg.n_q * V.HD, ql)]
+        wqb = wqb_all[0][r * hl * V.HD:(r + 1) * hl * V.HD]
         if L.is_index_source:                                        # the indexer's queries ride on the same launch
             L.cols["qi"] = (hl * V.HD, hl * V.HD + V.IDX_HEADS * V.IDX_DIM)
-            wqb = torch.cat([wqb, rnd(V.IDX_HEADS * V.IDX_DIM, ql) * 4], 0)
-        L.q_proj = self._make_linear(wqb.contiguous(), search)
+            wqb_all.append(rnd(V.IDX_HEADS * V.IDX_DIM, ql) * 4)
+            wqb = torch.cat([wqb, wqb_all[1]], 0)
+        L.q_proj = self._make_linear(wqb.contiguous(), search, whole=wqb_all)
         L.sink = (torch.randn(cfg.n_q, generator=torch.Generator().manual_seed(li + 7)) * 0.5)[r * hl:(r + 1) * hl].to(dev).contiguous()
         woa = rnd(cfg.o_groups * cfg.o_lora_rank, V.GROUP_HEADS * V.HD).reshape(cfg.o_groups, cfg.o_lora_rank, -1)
         L.wo_a = woa[r * gl:(r + 1) * gl].to(bf).contiguous()          # [groups, o_lora, 8 * 512]: block diagonal over the groups
         wob = rnd(H, cfg.o_groups * cfg.o_lora_rank)
-        L.wo_b = self._make_linear(wob[:, r * gl * cfg.o_lora_rank:(r + 1) * gl * cfg.o_lora_rank].contiguous(), search)
+        L.wo_b = self._make_linear(wob[:, r * gl * cfg.o_lora_rank:(r + 1) * gl * cfg.o_lora_rank].contiguous(), search, whole=wob)
         L.c_norm = L.idx_wk = L.idx_knorm = None
         if L.is_kv_source:
             L.c_norm = ones(V.HD, device=dev, dtype=bf)

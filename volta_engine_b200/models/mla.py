@@ -95,7 +95,7 @@ class MLAModel(MoEModel):
         L.q_a_norm = ones(cfg.q_lora_rank, device=self.device, dtype=torch.bfloat16)
         L.kv_a_norm = ones(LAT, device=self.device, dtype=torch.bfloat16)
         wqb = rnd(cfg.n_q * self.qd, cfg.q_lora_rank)
-        L.q_b = self._make_linear(wqb[r * hl * self.qd:(r + 1) * hl * self.qd].contiguous(), search)
+        L.q_b = self._make_linear(wqb[r * hl * self.qd:(r + 1) * hl * self.qd].contiguous(), search, whole=wqb)
         wkvb = rnd(cfg.n_q * (cfg.qk_nope + cfg.v_head_dim), LAT).reshape(cfg.n_q, cfg.qk_nope + cfg.v_head_dim, LAT)
         mine = wkvb[r * hl:(r + 1) * hl]
         # W_uk as [head, nope, 512] for q absorption; W_uv [head, v, 512]; stacked [head*(nope+v), 512] for prefill
@@ -103,7 +103,7 @@ class MLAModel(MoEModel):
         L.w_uv = mine[:, cfg.qk_nope:].contiguous().to(torch.bfloat16)
         L.w_ukv = LinearBF16(mine.reshape(hl * (cfg.qk_nope + cfg.v_head_dim), LAT).to(torch.bfloat16))
         wo = rnd(H, cfg.n_q * cfg.v_head_dim)
-        L.o_proj = self._make_linear(wo[:, r * hl * cfg.v_head_dim:(r + 1) * hl * cfg.v_head_dim].contiguous(), search)
+        L.o_proj = self._make_linear(wo[:, r * hl * cfg.v_head_dim:(r + 1) * hl * cfg.v_head_dim].contiguous(), search, whole=wo)
         L.qkv = None
         L.dsa = None
         if cfg.dsa:                                  # indexer weights (replicated on every rank: the list must agree)

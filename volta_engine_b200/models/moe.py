@@ -156,8 +156,8 @@ class MoEModel(DenseModel):
             if L.dense_ffn:
                 wg, wu, wd = rnd(cfg.ffn, H), rnd(cfg.ffn, H), rnd(H, cfg.ffn)
                 f = cfg.ffn // tp
-                L.gate_up = self._make_linear(torch.cat([wg[r * f:(r + 1) * f], wu[r * f:(r + 1) * f]], 0), search)
-                L.down = self._make_linear(wd[:, r * f:(r + 1) * f].contiguous(), search)
+                L.gate_up = self._make_linear(torch.cat([wg[r * f:(r + 1) * f], wu[r * f:(r + 1) * f]], 0), search, whole=(wg, wu))
+                L.down = self._make_linear(wd[:, r * f:(r + 1) * f].contiguous(), search, whole=wd)
                 self.layers.append(L)
                 continue
             L.shared_gated = bool(cfg.shared_gate and cfg.shared_ffn)
@@ -193,8 +193,8 @@ class MoEModel(DenseModel):
                 f = S // tp if S % tp == 0 and (S // tp) % 128 == 0 else S      # a slice must keep whole 128-wide scale blocks
                 self._shared_sliced = f != S
                 lo, hi = (r * f, (r + 1) * f) if f != S else (0, S)
-                L.shared_gu = self._make_linear(torch.cat([wg[lo:hi], wu[lo:hi]], 0), search)
-                L.shared_dn = self._make_linear(wd[:, lo:hi].contiguous(), search)
+                L.shared_gu = self._make_linear(torch.cat([wg[lo:hi], wu[lo:hi]], 0), search, whole=(wg, wu))
+                L.shared_dn = self._make_linear(wd[:, lo:hi].contiguous(), search, whole=wd)
             self.layers.append(L)
         self.final_norm = nw.clone()
         full = self.embed if cfg.tie_embeddings else rnd(cfg.vocab, H).to(torch.bfloat16)
@@ -214,9 +214,9 @@ class MoEModel(DenseModel):
         kv0 = (r // self.kv_rep) * self.nkv if cfg.n_kv < tp else r * self.nkv
         L.qkv = self._make_linear(torch.cat([wq[r * self.nq * hd:(r + 1) * self.nq * hd],
                                              wk[kv0 * hd:(kv0 + self.nkv) * hd],
-                                             wv[kv0 * hd:(kv0 + self.nkv) * hd]], 0), search)
+                                             wv[kv0 * hd:(kv0 + self.nkv) * hd]], 0), search, whole=(wq, wk, wv))
         wo = rnd(H, cfg.n_q * hd)
-        L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search)
+        L.o_proj = self._make_linear(wo[:, r * self.nq * hd:(r + 1) * self.nq * hd].contiguous(), search, whole=wo)
 
     def _attn_bytes(self, L) -> int:
         return L.qkv.nbytes() + L.o_proj.nbytes()

@@ -61,8 +61,10 @@ class LinearNVFP4:
         self._gv = None
 
     @classmethod
-    def from_dense(cls, w: torch.Tensor, gemm_mode="w4a16", search=True):
-        p, s, g = qn.quantize_nvfp4(w, search=search)
+    def from_dense(cls, w: torch.Tensor, gemm_mode="w4a16", search=True, global_scale: float | None = None):
+        """``global_scale``: the tensor scale to quantise against (default: from this matrix's largest magnitude). A
+        shard quantised against the scale of the whole matrix equals the slice of the quantised whole matrix."""
+        p, s, g = qn.quantize_nvfp4(w, search=search, global_scale=global_scale)
         return cls(p, s, g, gemm_mode)
 
     def prepare(self):
