@@ -24,7 +24,7 @@ VE_DEVINL uint32_t exl3_decode2(uint32_t w0, uint32_t w1) {
   if (CB == 2) {
     const uint32_t h0 = __dp4a(w0 * 0x83DCD12Du, 0x01010101u, 0x6400u);   // fp16 bits of 1024 + s
     const uint32_t h1 = __dp4a(w1 * 0x83DCD12Du, 0x01010101u, 0x6400u);
-    const uint32_t pk = h0 | (h1 << 16);
+    const uint32_t pk = __byte_perm(h0, h1, 0x5410);                       // low halves of h0, h1 (their high halves are 0)
     const __half2 a = __half2half2(__ushort_as_half((unsigned short)0x1eee));
     const __half2 b = __half2half2(__ushort_as_half((unsigned short)0xc931));
     const __half2 v = __hfma2(*reinterpret_cast<const __half2*>(&pk), a, b);
@@ -63,9 +63,12 @@ template <int BITS> struct Exl3Lane {
     uint32_t win[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const int t = i * BITS, j = t >> 5, sh = t & 31;
-      const uint32_t top = sh == 0 ? q[j] : __funnelshift_l(q[j + 1 > 2 ? 2 : j + 1], q[j], sh);
-      win[i] = top >> 16;
+      const int t = i * BITS, j = t >> 5, sh = t & 31;          // window i = bits [sh, sh + 16) below the top of q[j] : q[j + 1]
+      if (sh <= 16) {
+        win[i] = (q[j] >> (16 - sh)) & 0xffffu;                 // inside one word: a single bit-field extract
+      } else {
+        win[i] = __funnelshift_r(q[j + 1 > 2 ? 2 : j + 1], q[j], 48 - sh) & 0xffffu;
+      }
     }
 #pragma unroll
     for (int p = 0; p < 4; ++p) frag[p] = exl3_decode2<CB>(win[2 * p], win[2 * p + 1]);
@@ -82,28 +85,20 @@ constexpr int kExl3Warps = 8;
 
 // x: fp16 [groups][M][K] rotated activations (read through L1: at most 16 x K halves, re-used by every warp);
 // y: fp32 [groups][M][N]; group = blockIdx.y, its weights start at codes + expert[group] * expert_stride
-// (expert == nullptr: one shared matrix). A warp walks its share of K and, per k-tile, NTW adjacent column tiles
-// (NTW * 32 * BITS contiguous bytes per request); the CTA owns 16 * NTW output columns.
+// (expert == nullptr: one shared matrix). The column tiles of a group are split evenly over gridDim.x CTAs (the host
+// sizes the grid to the number of CTAs that are resident at once, so every CTA gets the same work to within one tile
+// and there is no partial last wave); a CTA walks its range in units of 4, 2 or 1 adjacent column tiles. In a unit every
+// warp walks its share of K and reads NTW * 32 * BITS contiguous bytes per k-tile.
 template <int BITS, int CB, int MH, int NTW>   // MH: 8 or 16 activation rows held by the A fragment
-__global__ void __launch_bounds__(kExl3Warps * 32)
-exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ x, float* __restrict__ y,
-                 int M, int K, int N, const int* __restrict__ expert, long expert_stride) {
-  __shared__ float red[kExl3Warps * 256 * NTW];                     // [warps][16 rows][16 * NTW cols]
-  const int grp = blockIdx.y;
-  if (expert) { const int e = expert[grp]; if (e < 0) return; codes += (size_t)e * expert_stride; }
-  x += (size_t)grp * M * K; y += (size_t)grp * M * N;
+VE_DEVINL void exl3_gemv_unit(const uint32_t* __restrict__ base, size_t tstride, const __half* __restrict__ xlo,
+                              const __half* __restrict__ xhi, bool row_lo, bool row_hi, float* __restrict__ y, float* red,
+                              int M, int KT, int N, int nt0) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const bool row_lo = g < M, row_hi = MH == 16 && g + 8 < M;
-  const __half* xlo = x + (size_t)(row_lo ? g : 0) * K + 2 * t;
-  const __half* xhi = x + (size_t)(row_hi ? g + 8 : 0) * K + 2 * t;
-
-  const int KT = K >> 4, NT = N >> 4, nt0 = blockIdx.x * NTW;
   const int per = (KT + kExl3Warps - 1) / kExl3Warps;
   const int kt0 = warp * per, kt1 = min(KT, kt0 + per);
   const Exl3Lane<BITS> L(lane);
   constexpr int NW = Exl3Lane<BITS>::NW;
-  const uint32_t* base = reinterpret_cast<const uint32_t*>(codes) + (size_t)nt0 * (8 * BITS);
-  const size_t tstride = (size_t)NT * (8 * BITS);
+  base += (size_t)nt0 * (8 * BITS);
   float acc[NTW][2][4];
 #pragma unroll
   for (int j = 0; j < NTW; ++j)
@@ -141,6 +136,7 @@ exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ 
   }
   // C fragment: c[0],c[1] -> row g, cols 2t,2t+1; c[2],c[3] -> row g+8.
   constexpr int W = 16 * NTW;
+  __syncthreads();                                                  // the previous unit's sums have been read
   float* r = red + warp * 16 * W;
 #pragma unroll
   for (int j = 0; j < NTW; ++j)
@@ -157,6 +153,31 @@ exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ 
 #pragma unroll
     for (int wv = 0; wv < kExl3Warps; ++wv) s += red[wv * 16 * W + m * W + n];
     y[(size_t)m * N + nt0 * 16 + n] = s;
+  }
+}
+
+template <int BITS, int CB, int MH>
+__global__ void __launch_bounds__(kExl3Warps * 32)
+exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ x, float* __restrict__ y,
+                 int M, int K, int N, const int* __restrict__ expert, long expert_stride) {
+  __shared__ float red[kExl3Warps * 256 * 4];                       // [warps][16 rows][16 * NTW cols], NTW <= 4
+  const int grp = blockIdx.y;
+  if (expert) { const int e = expert[grp]; if (e < 0) return; codes += (size_t)e * expert_stride; }
+  x += (size_t)grp * M * K; y += (size_t)grp * M * N;
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const bool row_lo = g < M, row_hi = MH == 16 && g + 8 < M;
+  const __half* xlo = x + (size_t)(row_lo ? g : 0) * K + 2 * t;
+  const __half* xhi = x + (size_t)(row_hi ? g + 8 : 0) * K + 2 * t;
+  const int KT = K >> 4, NT = N >> 4;
+  const uint32_t* base = reinterpret_cast<const uint32_t*>(codes);
+  const size_t tstride = (size_t)NT * (8 * BITS);
+  int nt = (int)((long)NT * blockIdx.x / gridDim.x);
+  const int nt_end = (int)((long)NT * (blockIdx.x + 1) / gridDim.x);
+  while (nt < nt_end) {
+    const int left = nt_end - nt;
+    if (left >= 4) { exl3_gemv_unit<BITS, CB, MH, 4>(base, tstride, xlo, xhi, row_lo, row_hi, y, red, M, KT, N, nt); nt += 4; }
+    else if (left >= 2) { exl3_gemv_unit<BITS, CB, MH, 2>(base, tstride, xlo, xhi, row_lo, row_hi, y, red, M, KT, N, nt); nt += 2; }
+    else { exl3_gemv_unit<BITS, CB, MH, 1>(base, tstride, xlo, xhi, row_lo, row_hi, y, red, M, KT, N, nt); nt += 1; }
   }
 }
 
@@ -287,26 +308,36 @@ __global__ void __launch_bounds__(256) exl3_reconstruct_kernel(const uint16_t* _
 
 using namespace ve;
 
-template <int BITS, int CB, int NTW>
-static void exl3_gemv_launch_n(const void* codes, const void* x, void* y, int M, int K, int N, const int* expert,
-                               long stride, int groups, cudaStream_t st) {
-  const dim3 grid(N / (16 * NTW), groups);
-  if (M <= 8)
-    exl3_gemv_kernel<BITS, CB, 8, NTW><<<grid, kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x,
-                                                                         (float*)y, M, K, N, expert, stride);
-  else
-    exl3_gemv_kernel<BITS, CB, 16, NTW><<<grid, kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x,
-                                                                          (float*)y, M, K, N, expert, stride);
+// Grid: as many CTAs as are resident at once (occupancy x SMs), shared between the groups; never more than the column
+// tiles of a group.
+template <int BITS, int CB, int MH>
+static int exl3_gemv_grid() {
+  static int ctas = 0;
+  if (!ctas) {
+    int per_sm = 0, dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, exl3_gemv_kernel<BITS, CB, MH>, kExl3Warps * 32, 0) != cudaSuccess ||
+        per_sm < 1)
+      per_sm = 1;
+    ctas = per_sm * sms;
+  }
+  return ctas;
 }
 
-// Column tiles per warp: as wide as the request can be (up to 512 B) while the grid still fills the GPU.
 template <int BITS, int CB>
 static int exl3_gemv_launch(const void* codes, const void* x, void* y, int M, int K, int N, const int* expert,
                             long stride, int groups, cudaStream_t st) {
-  const long ctas1 = (long)(N / 16) * groups;
-  if (N % 64 == 0 && ctas1 / 4 >= 2 * 148) exl3_gemv_launch_n<BITS, CB, 4>(codes, x, y, M, K, N, expert, stride, groups, st);
-  else if (N % 32 == 0 && ctas1 / 2 >= 2 * 148) exl3_gemv_launch_n<BITS, CB, 2>(codes, x, y, M, K, N, expert, stride, groups, st);
-  else exl3_gemv_launch_n<BITS, CB, 1>(codes, x, y, M, K, N, expert, stride, groups, st);
+  const int NT = N / 16;
+  if (M <= 8) {
+    const int gx = max(1, min(NT, exl3_gemv_grid<BITS, CB, 8>() / groups));
+    exl3_gemv_kernel<BITS, CB, 8><<<dim3(gx, groups), kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x,
+                                                                                 (float*)y, M, K, N, expert, stride);
+  } else {
+    const int gx = max(1, min(NT, exl3_gemv_grid<BITS, CB, 16>() / groups));
+    exl3_gemv_kernel<BITS, CB, 16><<<dim3(gx, groups), kExl3Warps * 32, 0, st>>>((const uint16_t*)codes, (const __half*)x,
+                                                                                  (float*)y, M, K, N, expert, stride);
+  }
   VE_CHECK_LAUNCH();
 }
 
