@@ -106,30 +106,45 @@ VE_DEVINL void exl3_gemv_unit(const uint32_t* __restrict__ base, size_t tstride,
     for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[j][h][i] = 0.f;
-  constexpr int UK = (NW == 2 ? 8 : 4) / NTW > 0 ? (NW == 2 ? 8 : 4) / NTW : 1;   // k-tiles in flight per warp
-  for (int kt = kt0; kt < kt1; kt += UK) {
-    uint32_t w[UK][NTW][NW];
+  constexpr int UK = (NW == 2 ? 4 : 2) / NTW > 0 ? (NW == 2 ? 4 : 2) / NTW : 1;   // k-tiles per step of a warp
+  // Two register buffers: the words of step i + 1 are requested before step i is decoded, so a warp's memory latency
+  // overlaps its own arithmetic (the warps of a CTA run in lock-step and would otherwise all wait at the same time).
+  uint32_t wn[UK][NTW][NW], an[UK][4];
+  auto fetch = [&](int kt) {
 #pragma unroll
     for (int u = 0; u < UK; ++u) {
-      const int k = min(kt + u, kt1 - 1);                           // tail: re-read the last tile, skip its math
+      const int k = min(kt + u, kt1 - 1);                           // tail: re-read the last tile, its math is skipped
 #pragma unroll
-      for (int j = 0; j < NTW; ++j) L.load(base + (size_t)k * tstride + j * (8 * BITS), w[u][j]);
+      for (int j = 0; j < NTW; ++j) L.load(base + (size_t)k * tstride + j * (8 * BITS), wn[u][j]);
+      const int ko = k * 16;                                        // the A fragment of the same k-tile (L1 resident)
+      an[u][0] = row_lo ? __ldg(reinterpret_cast<const uint32_t*>(xlo + ko)) : 0u;
+      an[u][2] = row_lo ? __ldg(reinterpret_cast<const uint32_t*>(xlo + ko + 8)) : 0u;
+      an[u][1] = row_hi ? __ldg(reinterpret_cast<const uint32_t*>(xhi + ko)) : 0u;
+      an[u][3] = row_hi ? __ldg(reinterpret_cast<const uint32_t*>(xhi + ko + 8)) : 0u;
     }
+  };
+  if (kt0 < kt1) fetch(kt0);
+  for (int kt = kt0; kt < kt1; kt += UK) {
+    uint32_t w[UK][NTW][NW], a[UK][4];
+#pragma unroll
+    for (int u = 0; u < UK; ++u) {
+#pragma unroll
+      for (int j = 0; j < NTW; ++j)
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[u][j][i] = wn[u][j][i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[u][i] = an[u][i];
+    }
+    if (kt + UK < kt1) fetch(kt + UK);
 #pragma unroll
     for (int u = 0; u < UK; ++u) {
       if (kt + u < kt1) {
-        uint32_t a[4];
-        const int ko = (kt + u) * 16;
-        a[0] = row_lo ? __ldg(reinterpret_cast<const uint32_t*>(xlo + ko)) : 0u;
-        a[2] = row_lo ? __ldg(reinterpret_cast<const uint32_t*>(xlo + ko + 8)) : 0u;
-        a[1] = row_hi ? __ldg(reinterpret_cast<const uint32_t*>(xhi + ko)) : 0u;
-        a[3] = row_hi ? __ldg(reinterpret_cast<const uint32_t*>(xhi + ko + 8)) : 0u;
 #pragma unroll
         for (int j = 0; j < NTW; ++j) {
           uint32_t f[4];
           L.template decode<CB>(w[u][j], f);
-          mma_f16(acc[j][0], a, f[0], f[1]);
-          mma_f16(acc[j][1], a, f[2], f[3]);
+          mma_f16(acc[j][0], a[u], f[0], f[1]);
+          mma_f16(acc[j][1], a[u], f[2], f[3]);
         }
       }
     }
@@ -157,7 +172,7 @@ VE_DEVINL void exl3_gemv_unit(const uint32_t* __restrict__ base, size_t tstride,
 }
 
 template <int BITS, int CB, int MH>
-__global__ void __launch_bounds__(kExl3Warps * 32)
+__global__ void __launch_bounds__(kExl3Warps * 32, 2)
 exl3_gemv_kernel(const uint16_t* __restrict__ codes, const __half* __restrict__ x, float* __restrict__ y,
                  int M, int K, int N, const int* __restrict__ expert, long expert_stride) {
   __shared__ float red[kExl3Warps * 256 * 4];                       // [warps][16 rows][16 * NTW cols], NTW <= 4
