@@ -214,3 +214,41 @@ def test_cpu_expert_service_answers_through_the_mailbox_and_a_stopped_service_ti
     assert K.check_status(x.device) == 2
     K.status_word(x.device).zero_()
     assert float((x.float() + 1).sum()) != 0
+
+
+def test_expert_tier_from_launch_options_rebalances_while_decoding(tmp_path):
+    """expert_cache = 0.5: half of every layer's experts resident, the rest read in place from pinned memory; the tokens
+    equal the untiered model's; the generator rebalances every expert_adapt_every steps; the heat file round-trips."""
+    from volta_engine_b200.runtime.generator import Generator, Request
+    from volta_engine_b200.runtime.options import Options
+    from volta_engine_b200.server.cli import configure_expert_tier, dump_calibration
+
+    class Tok:
+        eos_ids = [0]
+
+        def decode_bytes(self, ids, skip_special=False):
+            return bytes(i & 0xFF for i in ids)
+
+        def encode(self, text, allow_special=True):
+            return list(text.encode())
+
+    prompt = torch.randint(1, 1000, (60,), generator=torch.Generator().manual_seed(5)).tolist()
+    m_ref, _ = _models(router_bias_zipf=1.2)
+    want, _ = Engine(m_ref, PagedKVCache(2, m_ref.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64).generate(prompt, 20)
+    heat_file = str(tmp_path / "heat.pt")
+    o = Options.resolve({"expert_cache": 0.5, "expert_adapt_every": 4, "expert_swaps": 2, "expert_heat_file": heat_file,
+                         "max_slots": 1, "prefix_cache_mib": 0}, env={})
+    m, _ = _models(router_bias_zipf=1.2)
+    configure_expert_tier(m, o)
+    assert m.expert_adapt_every == 4 and m.expert_max_swaps == 2 and len(m.tiers) == 2
+    assert all(len(t.resident()) == m.e_local // 2 for _, t in m.tiers)
+    eng = Engine(m, PagedKVCache(2, m.nkv, 64, 16, 1, 512, DEV), prefill_chunk=64)
+    gen = Generator(eng, Tok(), o, eos_ids=[])
+    out = gen.generate(Request(prompt, max_tokens=20, cache_prefix=False))["tokens"]
+    assert out == want
+    assert sum(t.swaps for _, t in m.tiers) > 0, "the skewed router should have moved experts"
+    assert heat_file in dump_calibration(m, o)
+    m2, _ = _models(router_bias_zipf=1.2)
+    configure_expert_tier(m2, o)                       # starts from the saved counts: the hottest experts are resident
+    hot = torch.load(heat_file)[0].topk(m2.e_local // 2).indices.tolist()
+    assert len(set(hot) & set(m2.tiers[0][1].resident())) >= m2.e_local // 2 - 1

@@ -43,16 +43,16 @@ def test_aliases_and_wide_values():
 
 
 def test_ignored_lists_the_keys_without_effect():
-    o = O.Options.resolve({"gemv_int8": False, "steer_scale": 2.0, "prefill_cooldown": 2}, env={})
+    o = O.Options.resolve({"gemv_int8": False, "steer_push": 2.0, "prefill_cooldown": 2}, env={})
     names = [k for k, _ in o.ignored()]
-    assert "gemv_int8" in names and "steer_scale" in names and "prefill_cooldown" not in names
+    assert "gemv_int8" in names and "steer_push" in names and "prefill_cooldown" not in names
 
 
 def test_env_and_docs():
     o = O.Options.resolve({}, env={"ENGINE_PREFILL_COOLDOWN": "3", "ENGINE_AR_LL": "0"})
     assert o.prefill_cooldown == 3 and o.ar_ll is False
     doc = O.config_docs()
-    for k in ("arena_gib", "prefill_cooldown", "gemv_int8", "steer_scale", "trace_layers"):
+    for k in ("arena_gib", "prefill_cooldown", "gemv_int8", "steer_push", "trace_layers"):
         assert f"`{k}`" in doc
 
 
@@ -95,3 +95,57 @@ def test_disk_tier_budget_trims_oldest(tmp_path):
     total = sum(os.path.getsize(os.path.join(str(tmp_path), "m", f)) for f in files)
     assert total <= 200_000 and 1 <= len(files) < 6
     assert pc.stats["disk_bytes"] == total
+
+
+def test_steering_from_launch_options_and_request_fields(tmp_path):
+    """steer = file applies the file to every request; a request may switch it off, name another file of steer_dir,
+    rescale it; the reasoning-marker penalty lowers the first tokens of the marker words inside the reasoning block."""
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.generator import Generator, Request
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.runtime.steering import SteerConfig, SteerEntry, SteerFile, STEER_ADD, save_steer_file
+    from volta_engine_b200.server.protocol import ProtocolError, steer_fields
+
+    class Tok:
+        eos_ids = [0]
+
+        def decode_bytes(self, ids, skip_special=False):
+            return bytes(i & 0xFF for i in ids)
+
+        def encode(self, text, allow_special=True):
+            return list(text.encode())
+
+    cfg = DenseConfig.tiny(vocab=256)
+    model = DenseModel(cfg, "cpu").init_random(seed=0, search=False)
+    g = torch.Generator().manual_seed(1)
+    sf = SteerFile(hidden=cfg.hidden, layers=cfg.n_layers, entries=[
+        SteerEntry(layer=li, kind=STEER_ADD, par=4.0, vec=torch.randn(cfg.hidden, generator=g)) for li in range(cfg.n_layers)])
+    save_steer_file(str(tmp_path / "push.steer"), sf)
+    o = O.Options.resolve({"steer": "file", "steer_file": str(tmp_path / "push.steer"), "steer_dir": str(tmp_path),
+                           "steer_layers": f"0-{cfg.n_layers - 1}", "think_penalty": 0.0, "max_slots": 1}, env={})
+    sc = SteerConfig(o, cfg.n_layers, Tok())
+    assert sc.enabled and sc.default is not None and sc.penalty_ids
+
+    def run(fields):
+        kv = PagedKVCache(cfg.n_layers, model.nkv, cfg.head_dim, 24, 1, 512, "cpu")
+        eng = Engine(model, kv, use_graphs=False, prefill_chunk=32)
+        gen = Generator(eng, Tok(), o, eos_ids=[])
+        gen.steer_cfg = sc
+        model.steer = sc.tables(cfg.hidden, 1, "cpu")
+        prompt = [(7 * i + 3) % 250 + 1 for i in range(40)]
+        out = gen.generate(Request(prompt, max_tokens=8, cache_prefix=False, **sc.for_request(fields)))["tokens"]
+        model.steer = None
+        return out
+
+    steered, plain = run({}), run({"steer_vector": "off"})
+    assert steered != plain                                   # the file edits every request unless it says otherwise
+    assert run({"steer_vector": "push"}) == steered           # the same file by name from steer_dir
+    assert run({"steer_scale": 0.0}) == plain                 # scale 0 leaves the residual alone
+    with pytest.raises(ValueError):
+        sc.for_request({"steer_vector": "../etc/passwd"})
+    assert steer_fields({"steer_scale": "2", "think_penalty": 1}) == {"steer_scale": 2.0, "think_penalty": 1.0}
+    with pytest.raises(ProtocolError):
+        steer_fields({"steer_scale": "x"})
+    off = SteerConfig(O.Options.resolve({}, env={}), cfg.n_layers, Tok())
+    assert not off.enabled and off.for_request({"steer_vector": "push"})["steer"] is None

@@ -267,6 +267,12 @@ class DenseModel:
                 call("softcap", "plf", ptr(logits), logits.numel(), float(cfg.logit_softcap))
             else:
                 logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
+        steer = getattr(self, "steer", None)
+        if steer is not None:
+            # reasoning-marker penalty of steered slots (a no-op for slots whose control word holds no penalty ids)
+            last = b.logits == LOGITS_LAST
+            steer.penalize(logits, b.pos[b.n - 1: b.n] if last else b.pos, b.slot[b.n - 1: b.n] if last else b.slot,
+                           self.comm.rank * self.vocab_local)
         return logits
 
     # ------------------------------------------------------------------------------------- multi-stream residuals

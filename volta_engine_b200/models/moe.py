@@ -364,14 +364,14 @@ class MoEModel(DenseModel):
             y += shared.float()
         return y.to(x.dtype)
 
-    def enable_expert_tier(self, hot_slots: int, decay: float = 0.9):
+    def enable_expert_tier(self, hot_slots: int, decay: float = 0.9, margin: float = 1.25, margin_add: float = 0.0):
         """Keep only ``hot_slots`` experts of every MoE layer in device memory; the rest stay in pinned host memory and are
         read in place by the mat-vec kernel. Returns the tiers (``ExpertTier.rebalance`` moves experts between the two)."""
         from ..runtime.expert_tier import ExpertTier
         tiers = []
         for li, L in enumerate(self.layers):
             if getattr(L, "bank", None) is not None and not L.dense_ffn:
-                L.tier = ExpertTier(L.bank, hot_slots, decay)
+                L.tier = ExpertTier(L.bank, hot_slots, decay, margin, margin_add)
                 tiers.append((li, L.tier))
         self.tiers = tiers
         return tiers

@@ -17,11 +17,11 @@ import torch
 class ExpertTier:
     NAMES = ("gu_p", "gu_s", "dn_p", "dn_s")
 
-    def __init__(self, bank, hot_slots: int, decay: float = 0.9, margin: float = 1.25):
+    def __init__(self, bank, hot_slots: int, decay: float = 0.9, margin: float = 1.25, margin_add: float = 0.0):
         E = bank.e_local
         self.bank, self.E = bank, E
         self.hot_slots = max(0, min(hot_slots, E))
-        self.decay, self.margin = decay, margin
+        self.decay, self.margin, self.margin_add = decay, margin, margin_add      # swap when up > margin * down + margin_add
         dev = bank.gu_p.device
         self.device = dev
         pin = dev.type == "cuda"
@@ -82,7 +82,7 @@ class ExpertTier:
             hot = [e for e in range(self.E) if self.slot_of[e] >= 0]
             up = max(cold, key=lambda e: (float(self.heat[e]), -e))
             down = min(hot, key=lambda e: (float(self.heat[e]), e))
-            if float(self.heat[up]) <= float(self.heat[down]) * self.margin or float(self.heat[up]) <= 0:
+            if float(self.heat[up]) <= float(self.heat[down]) * self.margin + self.margin_add or float(self.heat[up]) <= 0:
                 break
             self._load(up, self.slot_of[down])
             n += 1

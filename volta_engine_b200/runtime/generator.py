@@ -46,6 +46,7 @@ class Request:
     steer: object = None          # runtime.steering.SteerFile applied to this request's slot
     steer_scale: float = 1.0
     steer_scope: int | None = None
+    think_penalty: float = 0.0    # logit taken from the first tokens of reflection markers inside the reasoning block
     id: int = 0
     cancelled: bool = False
     t_submit: float = 0.0
@@ -286,8 +287,10 @@ class Generator:
         s.think_open, s.think_count, s.forced = req.think_open, 0, []
         steer = getattr(getattr(self.engine, "model", None), "steer", None)
         if steer is not None:
-            if req.steer is not None:
-                steer.set_slot(s.idx, req.steer, prompt_len=len(req.prompt), scale=req.steer_scale, scope=req.steer_scope)
+            pen_ids = getattr(getattr(self, "steer_cfg", None), "penalty_ids", [])
+            if req.steer is not None or (req.think_penalty > 0 and pen_ids):
+                steer.set_slot(s.idx, req.steer, prompt_len=len(req.prompt), scale=req.steer_scale, scope=req.steer_scope,
+                               penalty_ids=pen_ids if req.think_penalty > 0 else (), penalty=req.think_penalty)
             else:
                 steer.clear_slot(s.idx)
         if len(req.prompt) == 0:
@@ -440,6 +443,11 @@ class Generator:
             else:
                 for s in act:            # batched plain steps do not maintain the head: drop its state
                     self.mtp.release(s.idx)
+        self._decode_steps = getattr(self, "_decode_steps", 0) + 1
+        mdl = getattr(self.engine, "model", None)
+        every = getattr(mdl, "expert_adapt_every", 0) if mdl is not None else 0
+        if every and self._decode_steps % every == 0:
+            mdl.rebalance_experts(getattr(mdl, "expert_max_swaps", 2))      # expert residency follows the routing heat
         for s, t, c in zip(act, toks, cands):
             t = self._think_gate(s, t)
             s.pos += 1

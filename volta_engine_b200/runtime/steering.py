@@ -264,3 +264,76 @@ def probe_fraction(axis: ProbeAxis, state: torch.Tensor) -> float:
     gap = axis.pb - axis.pa
     gap = gap if abs(gap) > 1e-6 else (1e-6 if gap >= 0 else -1e-6)
     return (float(state.float() @ axis.dir) - axis.pa) / gap
+
+
+# ---------------------------------------------------------------------------------------------- launch configuration
+class SteerConfig:
+    """What the launch options say about steering, resolved once: mode (off | on | file), the default control-vector
+    file, the directory requests may name files in, scale / scope defaults and the reasoning-marker penalty.
+    ``for_request`` turns a request's steering fields into the arguments of ``SteerTables.set_slot``.
+    Reference: docs/CONFIG.md (``steer``, ``steer_layers``, ``steer_file``, ``steer_dir``, ``steer_scale``,
+    ``steer_scope``, ``think_penalty``, ``think_penalty_words``)."""
+
+    DEFAULT_WORDS = ("Wait", " Wait", "Hmm", " Hmm", "Alternatively", " Alternatively", "But wait", " But wait")
+
+    def __init__(self, options, n_layers: int, tokenizer=None):
+        self.mode = str(getattr(options, "steer", "off") or "off").lower()
+        if self.mode not in ("off", "on", "file"):
+            raise ValueError(f"steer = '{self.mode}': off, on or file")
+        self.first, self.last = parse_steer_layers(getattr(options, "steer_layers", "") or "1/3-2/3", n_layers)
+        self.dir = getattr(options, "steer_dir", "") or ""
+        self.scale = float(getattr(options, "steer_scale", 1.0))
+        sc = getattr(options, "steer_scope", "") or ""
+        self.scope = parse_steer_scope(sc) if sc else None
+        self.default = None
+        path = getattr(options, "steer_file", "") or ""
+        if self.mode == "file":
+            if not path:
+                raise ValueError("steer = file needs steer_file")
+            self.default = load_steer_file(path)
+        elif path and self.mode == "on":
+            self.default_path = path
+        self.penalty = float(getattr(options, "think_penalty", 0.0) or 0.0)
+        words = getattr(options, "think_penalty_words", "") or ""
+        words = [w for w in words.split("|") if w] if words else list(self.DEFAULT_WORDS)
+        self.penalty_ids = []
+        if tokenizer is not None:
+            for w in words:
+                ids = tokenizer.encode(w, allow_special=False) if hasattr(tokenizer, "encode") else []
+                if ids and ids[0] not in self.penalty_ids:
+                    self.penalty_ids.append(ids[0])              # the first token of a marker is what gets the penalty
+        self._files: dict = {}
+
+    @property
+    def enabled(self) -> bool:
+        return self.mode != "off"
+
+    def tables(self, hidden: int, slots: int, device) -> "SteerTables":
+        return SteerTables(hidden, self.first, self.last, slots, device)
+
+    def _named(self, name: str) -> SteerFile:
+        if not self.dir:
+            raise ValueError("the server has no steer_dir: requests cannot name control-vector files")
+        if "/" in name or "\\" in name or name.startswith("."):
+            raise ValueError("steer_vector is a file name inside steer_dir, not a path")
+        sf = self._files.get(name)
+        if sf is None:
+            import os
+            sf = self._files[name] = load_steer_file(os.path.join(self.dir, name if name.endswith(".steer") else name + ".steer"))
+        return sf
+
+    def for_request(self, fields: dict) -> dict:
+        """-> keyword arguments for the request: steer (SteerFile or None), steer_scale, steer_scope, think_penalty."""
+        out = {"steer": self.default, "steer_scale": self.scale, "steer_scope": self.scope, "think_penalty": self.penalty}
+        if not self.enabled:
+            return dict(out, steer=None, think_penalty=0.0)
+        name = fields.get("steer_vector")
+        if name is not None:
+            out["steer"] = None if name.lower() in ("off", "none", "") else self._named(name)
+        if "steer_scale" in fields:
+            out["steer_scale"] = float(fields["steer_scale"])
+        if "steer_scope" in fields:
+            out["steer_scope"] = parse_steer_scope(fields["steer_scope"])
+        if "think_penalty" in fields:
+            out["think_penalty"] = float(fields["think_penalty"])
+        return out

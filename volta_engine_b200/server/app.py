@@ -225,7 +225,17 @@ class VoltaServer:
         low = [m.strip().lower() for m in str(getattr(self.gen.opt, "low_priority_models", "") or "").split(",") if m.strip()]
         if low and any(m in (cr.model or "").lower() for m in low):
             prio -= 100                 # requests that name one of these models queue behind the others
+        steer_kw = {}
+        scfg = getattr(self.gen, "steer_cfg", None)
+        if scfg is not None and scfg.enabled:
+            try:
+                steer_kw = scfg.for_request(cr.steer)
+            except (ValueError, OSError) as ex:
+                return self.http.respond(conn, 400, error_body(proto, f"steering: {ex}"))
+        elif cr.steer:
+            return self.http.respond(conn, 400, error_body(proto, "steering is off on this server (launch option steer)"))
         r = Request(prompt=ids, mm=mm, cache_key=cache_key, max_tokens=max_new, params=cr.params, stop=cr.stop, priority=prio,
+                    **steer_kw,
                     on_text=on_text, on_finish=on_finish, checkpoints=sys_end)
         rid = self.gen.submit(r)
         with self._lock:

@@ -169,6 +169,7 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     if o.trace_layers:
         from ..utils.trace import enable_layer_trace
         enable_layer_trace(model)
+    configure_expert_tier(model, o, getattr(comm, "rank", 0) if comm is not None else 0)
     from ..runtime.kv_cache import KV_FORMATS
     if o.kv_format not in KV_FORMATS:
         raise ValueError(f"kv_format '{o.kv_format}': this build has {sorted(KV_FORMATS)}")
@@ -224,12 +225,48 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     return model, hf, engine, pool_tokens
 
 
+def configure_expert_tier(model, o, rank: int = 0) -> None:
+    """``expert_cache`` below 1 keeps that fraction of every layer's routed experts in device memory and the rest in pinned
+    host memory (read in place); ``expert_adapt_every`` decode steps apart the residency follows the routing heat
+    (``expert_swaps`` per layer, or as many as ``expert_swap_mib`` pays for; a cold expert replaces a resident one when
+    its heat exceeds 1.5 x the resident one's plus ``expert_swap_margin``). ``expert_heat_file``: counts of an earlier
+    run choose the first resident set and are saved again at shutdown."""
+    model.expert_adapt_every = 0
+    frac = float(o.expert_cache)
+    if not (0.0 < frac < 1.0) or not hasattr(model, "enable_expert_tier") or getattr(model, "e_local", 0) < 2:
+        return
+    bank = next((L.bank for L in model.layers if getattr(L, "bank", None) is not None and hasattr(L.bank, "gu_p")), None)
+    if bank is None:
+        raise ValueError("expert_cache < 1 needs routed experts in the NVFP4 bank form")
+    hot = max(1, int(model.e_local * frac))
+    per_expert = bank.nbytes() // max(1, bank.e_local)
+    tiers = model.enable_expert_tier(hot, margin=1.5, margin_add=float(o.expert_swap_margin))
+    swaps = int(o.expert_swaps)
+    if swaps < 0:
+        swaps = max(1, (int(o.expert_swap_mib) << 20) // max(1, 2 * per_expert * max(1, len(tiers))))
+    model.expert_adapt_every, model.expert_max_swaps = max(0, int(o.expert_adapt_every)), swaps
+    path = (o.expert_heat_file + (f".r{rank}" if rank else "")) if o.expert_heat_file else ""
+    if path and os.path.exists(path):
+        import torch
+        heat = torch.load(path, map_location="cpu", weights_only=True)
+        if tuple(heat.shape) == tuple(model.heat.shape):
+            model.heat.copy_(heat)
+            model.rebalance_experts(max_swaps=hot)            # start with the hottest experts resident
+    log.info("expert tier: %d of %d experts per layer resident (%d layers, %.1f MiB per expert), rebalance every %d steps, "
+             "%d swaps per layer", hot, model.e_local, len(tiers), per_expert / 2**20, model.expert_adapt_every, swaps)
+
+
 def dump_calibration(model, options, rank: int = 0) -> list[str]:
     """Writes what the capture options collected (Hessian files per site, the route dump); called at shutdown."""
     out = []
     hs = getattr(model, "hess", None)
     if hs is not None and options.hessian_dir:
         out += hs.dump(options.hessian_dir, rank)
+    if getattr(options, "expert_heat_file", "") and getattr(model, "tiers", None) and getattr(model, "heat", None) is not None:
+        import torch
+        path = options.expert_heat_file + (f".r{rank}" if rank else "")
+        torch.save(model.heat.detach().cpu(), path)
+        out.append(path)
     rec = getattr(model, "route_recorder", None)
     if rec is not None and options.route_dump:
         path = options.route_dump if rank == 0 else f"{options.route_dump}.r{rank}"
@@ -267,6 +304,12 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None, fingerprint=fp,
                             disk_budget_bytes=max(0, o.prefix_cache_disk_gib) << 30)
     gen = Generator(engine, tok, o, prefix_cache=cache)
+    if o.steer != "off":
+        from ..runtime.steering import SteerConfig
+        if getattr(model.cfg, "residual", "plain") != "plain":
+            raise ValueError("steer: the residual edit is built for the plain-residual decoder families")
+        gen.steer_cfg = SteerConfig(o, model.cfg.n_layers, tok)
+        model.steer = gen.steer_cfg.tables(model.cfg.hidden, o.max_slots, engine.device)
     if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size == 1:
         gen.drafter = load_drafter(engine, cfg.draft_model_dir)
         if hasattr(gen.drafter.cfg, "conf_threshold"):

@@ -38,11 +38,25 @@ class ChatRequest:
     priority: int = 0
     n_images: int = 0
     images: list = field(default_factory=list)      # raw bytes of every image part, in prompt order
+    steer: dict = field(default_factory=dict)       # request steering fields: steer_vector, steer_scale, steer_scope, think_penalty
 
 
 # what an image part becomes in the rendered text: the tokenizer turns the middle piece into ONE placeholder token, which
 # the multimodal front end expands to the image's token count
 IMAGE_MARK = "<|vision_start|><|image_pad|><|vision_end|>"
+
+
+def steer_fields(body: dict) -> dict:
+    """The steering fields a request may carry (both protocols): ``steer_vector`` (a file name inside the server's
+    steer_dir, or ``"off"``), ``steer_scale``, ``steer_scope``, ``think_penalty``."""
+    out = {}
+    for k, conv in (("steer_vector", str), ("steer_scale", float), ("steer_scope", str), ("think_penalty", float)):
+        if body.get(k) is not None:
+            try:
+                out[k] = conv(body[k])
+            except (TypeError, ValueError) as e:
+                raise ProtocolError(f"{k}: {e}") from e
+    return out
 
 
 def _image_bytes(part: dict) -> bytes:
@@ -147,7 +161,8 @@ def parse_openai(body: dict, defaults: dict) -> ChatRequest:
     so = body.get("stream_options") or {}
     return ChatRequest("openai", out, tools, bool(body.get("stream")), int(mt), _sampling(body, defaults), list(stop),
                        think, int(body.get("thinking_budget", 0) or 0), body.get("model", ""),
-                       bool(so.get("include_usage", True)), int(body.get("priority", 0) or 0), n_img, images)
+                       bool(so.get("include_usage", True)), int(body.get("priority", 0) or 0), n_img, images,
+                       steer_fields(body))
 
 
 def parse_anthropic(body: dict, defaults: dict) -> ChatRequest:
@@ -206,7 +221,8 @@ def parse_anthropic(body: dict, defaults: dict) -> ChatRequest:
         think = False
     return ChatRequest("anthropic", out, tools, bool(body.get("stream")), int(body["max_tokens"]),
                        _sampling(body, defaults), list(body.get("stop_sequences") or []), think,
-                       int(th.get("budget_tokens", 0) or 0), body.get("model", ""), True, 0, n_img, images)
+                       int(th.get("budget_tokens", 0) or 0), body.get("model", ""), True, 0, n_img, images,
+                       steer_fields(body))
 
 
 # ------------------------------------------------------------------------------------------------ responders
