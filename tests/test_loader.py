@@ -1,6 +1,7 @@
 """Checkpoint containers and the model factory: safetensors (sharded, sliced, quantised dialects), GGUF files,
 and a model directory round trip through ``load_model``."""
 import json
+import re
 
 import pytest
 import torch
@@ -277,3 +278,71 @@ def test_ngram_table_hashing_and_the_three_row_formats(tmp_path):
     gt = NgramTable.open_gguf(GGUFFile(tmp_path / "t.gguf"), "per_layer_token_embd.weight")
     assert gt.row_ids(toks).tolist() == want
     assert np.allclose(gt.decode_row(9, 0), gq.dequantize(raw[9:10], gq.GGML_IQ4_NL, ROW_DIM)[0].numpy())
+
+
+@pytest.mark.parametrize("mla", [False, True])
+def test_moe_gguf_file_with_stacked_experts_keeps_the_blocks_and_matches_its_safetensors_twin(tmp_path, mla):
+    """The MoE / MLA test model as a GGUF file in llama.cpp's layout (experts of a layer stacked in ffn_*_exps, Q8_0 blocks;
+    dense tensors F32): the routed experts stay GGUF blocks in memory (GGUFExpertBank) and the model gives the
+    safetensors twin's first token."""
+    from volta_engine_b200.ops.moe_gguf import GGUFExpertBank
+    st_dir, gg_dir = tmp_path / "st", tmp_path / "gg"
+    st_dir.mkdir()
+    gg_dir.mkdir()
+    hf = _moe_dir(st_dir, mla)
+    (gg_dir / "config.json").write_text((st_dir / "config.json").read_text())
+    repo = SafeTensorsRepo(st_dir)
+    inv = {"input_layernorm": "attn_norm", "post_attention_layernorm": "ffn_norm", "self_attn.q_proj": "attn_q",
+           "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v", "self_attn.o_proj": "attn_output",
+           "self_attn.q_norm": "attn_q_norm", "self_attn.k_norm": "attn_k_norm", "mlp.gate_proj": "ffn_gate",
+           "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down", "mlp.gate": "ffn_gate_inp",
+           "mlp.gate.e_score_correction_bias": "exp_probs_b", "self_attn.q_a_proj": "attn_q_a", "self_attn.q_b_proj": "attn_q_b",
+           "self_attn.q_a_layernorm": "attn_q_a_norm", "self_attn.kv_a_proj_with_mqa": "attn_kv_a_mqa",
+           "self_attn.kv_b_proj": "attn_kv_b", "self_attn.kv_a_layernorm": "attn_kv_a_norm",
+           "mlp.shared_experts.gate_proj": "ffn_gate_shexp", "mlp.shared_experts.up_proj": "ffn_up_shexp",
+           "mlp.shared_experts.down_proj": "ffn_down_shexp"}
+    tensors, stacks = {}, {}
+    for name in repo.names():
+        t = repo.load(name).float()
+        if name.startswith("model.layers."):
+            _, _, li, rest = name.split(".", 3)
+            m = re.match(r"mlp\.experts\.(\d+)\.(gate|up|down)_proj\.weight$", rest)
+            if m:
+                stacks.setdefault((li, m.group(2)), {})[int(m.group(1))] = t
+                continue
+            if rest == "mlp.gate.e_score_correction_bias":
+                tensors[f"blk.{li}.exp_probs_b.bias"] = (t.contiguous(), 0, tuple(t.shape))
+                continue
+            inner, kind = rest.rsplit(".", 1)
+            tensors[f"blk.{li}.{inv[inner]}.{kind}"] = (t.contiguous(), 0, tuple(t.shape))
+        else:
+            gname = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+                     "lm_head.weight": "output.weight"}[name]
+            tensors[gname] = (t.contiguous(), 0, tuple(t.shape))
+    for (li, which), per in stacks.items():
+        full = torch.stack([per[e] for e in range(len(per))])                       # [E, rows, cols]
+        raw = gq.quantize(full.reshape(-1, full.shape[-1]), gq.GGML_Q8_0)
+        tensors[f"blk.{li}.ffn_{which}_exps.weight"] = (raw, gq.GGML_Q8_0, tuple(full.shape))
+    arch = "deepseek2" if mla else "qwen3moe"
+    write_gguf(gg_dir / "model.gguf", {"general.architecture": arch, f"{arch}.block_count": 2}, tensors)
+    mg, _ = load_model(gg_dir, "cpu")
+    ms, _ = load_model(st_dir, "cpu")
+    moe_layer = mg.layers[1]
+    assert isinstance(moe_layer.bank, GGUFExpertBank) and moe_layer.bank.gu_type == gq.GGML_Q8_0
+    assert moe_layer.bank.gu_raw.shape[:2] == (4, 2 * mg.cfg.expert_ffn)
+    from volta_engine_b200.runtime.batch import BatchRows
+    rows = []
+    for m in (mg, ms):
+        kv = PagedKVCache(m.cfg.n_layers, m.nkv, m.cfg.head_dim, 8, 2, 256, "cpu", **({"v_head_dim": 0} if mla else {}))
+        kv.reserve(0, 32)
+        b = BatchRows.make(list(range(20)), list(range(20)), [0] * 20, "cpu", "last", max(1, m.nq // m.nkv), prefill=True)
+        rows.append(m.forward(b, kv).float().flatten())
+    # the twin holds every linear as NVFP4 (4-bit) and this file F32 / Q8_0: the logits agree to that quantisation noise
+    c = float(torch.dot(rows[0], rows[1]) / (rows[0].norm() * rows[1].norm()))
+    assert c > 0.93, c
+    # and the bank holds exactly the file's blocks: expert 2 of layer 1 decodes to the Q8_0 rounding of the source tensors
+    src = {w: stacks[("1", w)][2] for w in ("gate", "up", "down")}
+    want_gu = gq.dequantize(gq.quantize(torch.cat([src["gate"], src["up"]], 0), gq.GGML_Q8_0), gq.GGML_Q8_0, src["gate"].shape[1])
+    assert torch.equal(moe_layer.bank.dequant("gu", 2), want_gu)
+    want_dn = gq.dequantize(gq.quantize(src["down"], gq.GGML_Q8_0), gq.GGML_Q8_0, src["down"].shape[1])
+    assert torch.equal(moe_layer.bank.dequant("dn", 2), want_dn)

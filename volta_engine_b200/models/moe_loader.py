@@ -47,7 +47,36 @@ def _nvfp4_of(src: TensorSource, base: str):
     return qn.quantize_nvfp4(w, search=True)
 
 
+def _load_bank_gguf(src: TensorSource, prefix: str, cfg, e0: int, e_local: int, dev):
+    """GGUF files stack the experts of a layer in three tensors ([experts, rows, cols]: ``ffn_gate_exps``, ``ffn_up_exps``,
+    ``ffn_down_exps``). When gate and up share a block type the blocks are kept as they are (``GGUFExpertBank``: fused
+    dequant mat-vec, slab dequantise + grouped GEMM); ``None`` when the file has no stacked experts or mixes types that
+    cannot be stacked (the caller then goes through the per-expert path).
+    Reference: src/loader/gguf_arch.h:21-66 (expert tensors of the GGUF adapters), src/kernels/cuda/gguf/gguf_moe.cu."""
+    g = src.gguf
+    if g is None:
+        return None
+    names = {k: src.names.get(f"{prefix}experts.{k}_proj.weight") for k in ("gate", "up", "down")}
+    if not all(names.values()):
+        return None
+    from ..loader.gguf_file import _PLAIN
+    from ..ops.linear_gguf import FUSED_TYPES
+    from ..ops.moe_gguf import GGUFExpertBank
+    info = {k: g.tensors[n] for k, n in names.items()}
+    gt, dt = info["gate"].ggml_type, info["down"].ggml_type
+    if gt != info["up"].ggml_type or gt in _PLAIN or dt in _PLAIN or gt not in FUSED_TYPES or dt not in FUSED_TYPES:
+        return None
+    E, I, H = cfg.n_experts, cfg.expert_ffn, cfg.hidden
+    gate = g.load(names["gate"]).reshape(E, I, -1)[e0:e0 + e_local]
+    up = g.load(names["up"]).reshape(E, I, -1)[e0:e0 + e_local]
+    down = g.load(names["down"]).reshape(E, H, -1)[e0:e0 + e_local]
+    return GGUFExpertBank(torch.cat([gate, up], 1).to(dev), gt, down.contiguous().to(dev), dt, e0, I, H)
+
+
 def _load_bank(src: TensorSource, prefix: str, cfg, e0: int, e_local: int, dev) -> ExpertBank:
+    bank = _load_bank_gguf(src, prefix, cfg, e0, e_local, dev)
+    if bank is not None:
+        return bank
     gp, gs, gg, dp, ds, dg = [], [], [], [], [], []
     for e in range(e0, e0 + e_local):
         p = f"{prefix}experts.{e}."
