@@ -212,3 +212,47 @@ def test_gpu_hybrid_verify_blocks_roll_back_bit_exactly():
         assert out == plain[:len(out)], (graphs, out, plain)
     from volta_engine_b200.ops import kernels as K
     assert K.check_status(dev) == 0
+
+
+@pytest.mark.parametrize("mixer", ["gdn", "kda"])
+def test_hybrid_model_tensor_parallel_matches_one_rank(tmp_path, mixer):
+    """Linear-attention heads split over two CPU ranks (gloo): the gathered logits equal the single-rank model's to
+    rounding (the shards are quantised against the whole matrices' tensor scales)."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    from volta_engine_b200.runtime.batch import BatchRows, LOGITS_ALL
+    here = os.path.dirname(os.path.abspath(__file__))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    out = str(tmp_path / "tp")
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(here, "hybrid_tp_worker.py"), out, mixer], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    for p in procs:
+        text, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, text.decode()[-3000:]
+    parts = [torch.load(f"{out}.{r}", weights_only=True) for r in range(2)]
+    kw = {"linear_mixer": "kda", "gdn_k_heads": 4} if mixer == "kda" else {}
+    cfg = HybridConfig.tiny_hybrid(vocab=256, **kw)
+    m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+    assert parts[0]["heads"] == (m.dims.n_k // 2, m.dims.n_v // 2)
+    kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    toks = torch.randint(0, 256, (40,), generator=torch.Generator().manual_seed(11)).tolist()
+    kv.reserve(0, 64)
+    outs = []
+    for lo, hi in ((0, 30), (30, 34), (34, 35), (35, 40)):
+        b = BatchRows.make(toks[lo:hi], list(range(lo, hi)), [0] * (hi - lo), "cpu", LOGITS_ALL, m.nq // m.nkv, prefill=hi - lo > 16)
+        outs.append(m.forward(b, kv).float())
+    want = torch.cat(outs)
+    got = torch.cat([p["logits"] for p in parts], 1)[:, :256]
+    cos = torch.nn.functional.cosine_similarity(got, want[:, :256], dim=-1)
+    # (a row whose router scores nearly tie may pick another expert under the other summation order: most rows agree
+    # to rounding, none is far off)
+    assert float(cos.median()) > 0.9995 and float((cos > 0.999).float().mean()) > 0.8 and float(cos.min()) > 0.95, cos
+    assert float((got.argmax(-1) == want[:, :256].argmax(-1)).float().mean()) > 0.9

@@ -75,8 +75,14 @@ class HybridModel(MoEModel):
 
     def __init__(self, cfg: HybridConfig, device, comm=None):
         super().__init__(cfg, device, comm)
-        assert self.comm.size == 1, "the hybrid model runs on one GPU in this build"
-        self.dims = GDNDims(cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, cfg.gdn_conv)
+        tp = self.comm.size
+        # tensor parallel: the key and value heads of the linear-attention mixers are split over the ranks (a value head
+        # reads key head h // (n_v / n_k), so contiguous slices stay together); the fused input projection is column
+        # parallel per section, the output projection row parallel into the layer's all-reduce, the state is per rank
+        assert cfg.gdn_k_heads % tp == 0 and cfg.gdn_v_heads % tp == 0, "linear-attention heads must divide by the rank count"
+        assert tp == 1 or not cfg.qsa, "the block-sparse indexer runs on one GPU in this build"
+        self.dims_full = GDNDims(cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, cfg.gdn_conv)
+        self.dims = GDNDims(cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp, cfg.gdn_dk, cfg.gdn_dv, cfg.gdn_conv)
         self.n_full = sum(1 for li in range(cfg.n_layers) if cfg.is_full(li))
         self.gdn_states: list[GDNState] | None = None
         self._li = 0
@@ -108,7 +114,9 @@ class HybridModel(MoEModel):
             super()._init_attention(L, rnd, search)
             L.kv_index = sum(1 for j in range(li) if cfg.is_full(j))
             if cfg.attn_gate:
-                L.gate_proj = self._make_linear(rnd(cfg.n_q * cfg.head_dim, cfg.hidden), search)
+                wg = rnd(cfg.n_q * cfg.head_dim, cfg.hidden)
+                q0, q1 = self.comm.rank * self.nq * cfg.head_dim, (self.comm.rank + 1) * self.nq * cfg.head_dim
+                L.gate_proj = self._make_linear(wg[q0:q1].contiguous(), search, whole=wg)
             if cfg.qsa:
                 from ..ops import dsa as D
                 from ..ops.linear import LinearBF16
@@ -117,23 +125,38 @@ class HybridModel(MoEModel):
                                      q_norm=z.clone(), k_norm=z.clone(), rot=min(64, D.DIM), theta=cfg.rope_theta, eps=cfg.rms_eps)
             return
         H = cfg.hidden
+        r, tp, df = self.comm.rank, self.comm.size, self.dims_full
+        real = df.conv_dim + df.n_v * df.dv + 2 * df.n_v
+        w_full = rnd(real, H)                                   # [q | k | v | z | b | a] of all heads
+
+        def sections(nk, nv):
+            return [nk * d.dk, nk * d.dk, nv * d.dv, nv * d.dv, nv, nv]
+        rows, at = [], 0
+        for full_n, mine_n in zip(sections(df.n_k, df.n_v), sections(d.n_k, d.n_v)):
+            rows.append(torch.arange(at + r * mine_n, at + (r + 1) * mine_n, device=dev))     # this rank's slice of the section
+            at += full_n
+        rows = torch.cat(rows)
         w_in = torch.zeros(d.proj_out, H, device=dev)
-        real = d.conv_dim + d.n_v * d.dv + 2 * d.n_v
-        w_in[:real] = rnd(real, H)
-        g = {"in_proj": self._make_linear(w_in, search),
-             "conv_w": (rnd(d.conv_dim, d.conv_k) * (0.5 / 0.02)).float().contiguous(),
-             "A_log": torch.log(torch.linspace(1.0, 8.0, d.n_v, device=dev)).float(),
-             "dt_bias": torch.linspace(-1.0, 1.0, d.n_v, device=dev).float(),
+        w_in[:rows.numel()] = w_full[rows]
+        conv_full = (rnd(df.conv_dim, d.conv_k) * (0.5 / 0.02)).float()
+        v0, v1 = r * d.n_v, (r + 1) * d.n_v
+        w_out = rnd(H, df.n_v * d.dv)
+        g = {"in_proj": self._make_linear(w_in, search, whole=w_full),
+             "conv_w": conv_full[rows[: d.conv_dim]].contiguous(),
+             "A_log": torch.log(torch.linspace(1.0, 8.0, df.n_v, device=dev)).float()[v0:v1].contiguous(),
+             "dt_bias": torch.linspace(-1.0, 1.0, df.n_v, device=dev).float()[v0:v1].contiguous(),
              "norm_w": torch.ones(d.dv, device=dev, dtype=torch.float32),
-             "out_proj": self._make_linear(rnd(H, d.n_v * d.dv), search)}
+             "out_proj": self._make_linear(w_out[:, v0 * d.dv:v1 * d.dv].contiguous(), search, whole=w_out)}
         if cfg.linear_mixer == "kda":
             from ..ops.linear import LinearBF16
-            bf, r = torch.bfloat16, cfg.kda_rank
+            bf, kr = torch.bfloat16, cfg.kda_rank
             assert d.n_k == d.n_v, "KDA has as many key heads as value heads"
-            g["kda"] = KDAWeights(f_a=LinearBF16(rnd(r, H).to(bf)), f_b=LinearBF16((rnd(d.n_v * d.dk, r) * 10).to(bf)),
-                                  g_a=LinearBF16(rnd(r, H).to(bf)), g_b=LinearBF16((rnd(d.n_v * d.dv, r) * 10).to(bf)),
-                                  A_log=torch.log(torch.linspace(0.5, 2.0, d.n_v, device=dev)).float(),
-                                  dt_bias=torch.linspace(-1.0, 1.0, d.n_v * d.dk, device=dev).float(), norm_w=g["norm_w"])
+            f_b, g_b = (rnd(df.n_v * d.dk, kr) * 10).to(bf), (rnd(df.n_v * d.dv, kr) * 10).to(bf)
+            g["kda"] = KDAWeights(f_a=LinearBF16(rnd(kr, H).to(bf)), f_b=LinearBF16(f_b[v0 * d.dk:v1 * d.dk].contiguous()),
+                                  g_a=LinearBF16(rnd(kr, H).to(bf)), g_b=LinearBF16(g_b[v0 * d.dv:v1 * d.dv].contiguous()),
+                                  A_log=torch.log(torch.linspace(0.5, 2.0, df.n_v, device=dev)).float()[v0:v1].contiguous(),
+                                  dt_bias=torch.linspace(-1.0, 1.0, df.n_v * d.dk, device=dev).float()[v0 * d.dk:v1 * d.dk].contiguous(),
+                                  norm_w=g["norm_w"])
         L.gdn = g
         L.qkv = L.o_proj = None
 
