@@ -86,7 +86,30 @@ def test_mtp_rounds_run_on_the_device_and_reproduce_plain_greedy():
         out += new
         pos += len(new)
     assert out[:24] == plain[:24], (out, plain)
-    assert run._st["graph"] is not None and run.stats["rounds"] >= 6
+    assert run._sts[(1, 3)]["graph"] is not None and run.stats["rounds"] >= 6
     assert run.stats["proposed"] == 3 * run.stats["rounds"]
+    # two slots in one joint round: one draft chain and one verify block of 8 rows; each slot continues its own greedy run
+    other = torch.randint(0, cfg.vocab, (50,), generator=torch.Generator().manual_seed(9)).tolist()
+    plain2, _ = Engine(m, _kv(m, DEV), prefill_chunk=64).generate(other, 16)
+    eng2 = Engine(m, _kv(m, DEV), prefill_chunk=64)
+    run2 = MtpRunner(eng2, depth=3)
+    eng2.kv.reserve(0, len(prompt) + 40)
+    eng2.kv.reserve(1, len(other) + 40)
+    outs = [[run2.prefill_rows(0, prompt, 0, len(prompt), True)], [run2.prefill_rows(1, other, 0, len(other), True)]]
+    poss = [len(prompt), len(other)]
+    for _ in range(6):
+        news = run2.round_joint([0, 1], [outs[0][-1], outs[1][-1]], poss)
+        for j in range(2):
+            outs[j] += news[j]
+            poss[j] += len(news[j])
+    n0, n1 = min(len(outs[0]), len(plain)), min(len(outs[1]), len(plain2))
+    assert outs[0][:n0] == plain[:n0] and outs[1][:n1] == plain2[:n1] and n0 >= 7 and n1 >= 7, (outs, plain, plain2)
+    assert run2._sts[(2, 3)]["graph"] is not None
+    # the survival estimate shortens rounds whose later drafts are never accepted
+    run2.adaptive = True
+    run2.cond = [0.2, 0.2, 0.2]
+    assert run2.round_depth() == 1
+    run2.cond = [0.9, 0.9, 0.9]
+    assert run2.round_depth() == 3
     from volta_engine_b200.ops import kernels as K
     assert K.check_status(DEV) == 0

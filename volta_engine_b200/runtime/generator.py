@@ -177,6 +177,10 @@ class Generator:
         if self.speculator == "mtp":
             from .mtp_runner import MtpRunner
             self.mtp = MtpRunner(engine, self.spec_depth)
+            self.mtp.adaptive = self.use_ctrl               # the depth of a round follows the survival estimate
+            # several decoding slots: one joint round (one draft chain, one verify block) for up to spec_joint_max of them
+            self.mtp_joint = int(getattr(options, "spec_joint", -1)) == 1 if options else False
+            self.mtp_joint_max = max(2, int(getattr(options, "spec_joint_max", 2))) if options else 2
 
     # ------------------------------------------------------------------------------------------ API
     def submit(self, req: Request) -> int:
@@ -422,6 +426,9 @@ class Generator:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
                 return self._mtp_round(s)
+        if (not budgeted and self.mtp is not None and getattr(self, "mtp_joint", False) and 2 <= len(act) <= self.mtp_joint_max
+                and all(s.req.params.greedy and s.idx in self.mtp.hidden for s in act) and self.mtp._device_round_ok(len(act))):
+            return self._mtp_round_joint(act)
         t0 = time.time()
         ids = [s.next_tok for s in act]
         pos = [s.pos for s in act]
@@ -484,21 +491,30 @@ class Generator:
     def _mtp_round(self, s: SlotState) -> int:
         t0 = time.time()
         new = self.mtp.round(s.idx, s.next_tok, s.pos)
+        return self._mtp_account(s, new, (time.time() - t0) * 1e3)
+
+    def _mtp_round_joint(self, act: list) -> int:
+        t0 = time.time()
+        news = self.mtp.round_joint([s.idx for s in act], [s.next_tok for s in act], [s.pos for s in act])
         ms = (time.time() - t0) * 1e3
+        return sum(self._mtp_account(s, new, ms / len(act)) for s, new in zip(act, news))
+
+    def _mtp_account(self, s: SlotState, new: list[int], ms: float) -> int:
+        depth = self.mtp.last_depth
         acc = len(new) - 1
         s.pos += acc + 1
         s.next_tok = new[-1]
         m = self.metrics.spec
         m["rounds"] += 1
-        m["proposed"] += self.mtp.depth
+        m["proposed"] += depth
         m["accepted"] += acc
-        while len(m["steps"]) < self.mtp.depth:
+        while len(m["steps"]) < depth:
             m["steps"].append({"attempts": 0, "hits": 0})
-        for i in range(self.mtp.depth):
+        for i in range(depth):
             m["steps"][i]["attempts"] += 1
             m["steps"][i]["hits"] += 1 if i < acc else 0
         if s.ctrl:
-            s.ctrl.record_round(len(new), self.mtp.depth, acc, ms)
+            s.ctrl.record_round(len(new), depth, acc, ms)
         self._emit(s, new)
         return len(new)
 
