@@ -36,3 +36,21 @@ def test_sequence_parallel_gradients_and_context_parallel_attention(world):
             o, _ = p.communicate()
         logs.append(o.decode(errors="replace"))
     assert all(p.returncode == 0 for p in procs) and "SP_WORKER_OK" in logs[0], "\n---\n".join(l[-3000:] for l in logs)
+
+
+def test_e2e_tuning_in_the_sequence_parallel_form_matches_one_rank():
+    port = _free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "e2e_sp_worker.py")], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT))
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        logs.append(o.decode(errors="replace"))
+    assert all(p.returncode == 0 for p in procs) and "E2E_SP_OK" in logs[0], "\n---\n".join(l[-3000:] for l in logs)

@@ -112,6 +112,128 @@ class E2EOptions:
     devices: list = field(default_factory=lambda: ["cpu"])
 
 
+# ---------------------------------------------------------------------------------------------- tensor parallel form
+class ShardedTunedLinear(torch.nn.Module):
+    """A ``TunedLinear`` cut for one rank. ``split = "col"``: this rank's output features (``cols``), the input scale
+    deltas replicated (their gradient is summed over the ranks); ``split = "row"``: this rank's input features, the output
+    scale deltas replicated and applied by the caller after the partial sums are reduced (``finish``)."""
+
+    def __init__(self, full: TunedLinear, split: str, idx: torch.Tensor):
+        super().__init__()
+        self.split = split
+        if split == "col":
+            self.register_buffer("core", full.core[:, idx].contiguous())
+            self.register_buffer("su", full.su.clone())
+            self.register_buffer("sv", full.sv[idx].clone())
+        else:
+            self.register_buffer("core", full.core[idx].contiguous())
+            self.register_buffer("su", full.su[idx].clone())
+            self.register_buffer("sv", full.sv.clone())
+        self.a_u = torch.nn.Parameter(torch.zeros_like(self.su))
+        self.a_v = torch.nn.Parameter(torch.zeros_like(self.sv))
+
+    def forward(self, x):
+        y = (x * (self.su * torch.exp(self.a_u))) @ self.core
+        return y * (self.sv * torch.exp(self.a_v)) if self.split == "col" else y
+
+    def finish(self, y):
+        """Row-parallel: the output scales, on the reduced rows."""
+        return y * (self.sv * torch.exp(self.a_v))
+
+    def replicated(self):
+        return [self.a_u] if self.split == "col" else [self.a_v]
+
+
+class TunedLayerSP(torch.nn.Module):
+    """``TunedLayer`` in the sequence-parallel form: every rank owns ``T / ranks`` rows of the fp32 stream and the heads /
+    hidden units ``rank :: ranks`` of the sub-layers. A sub-layer normalises its rows, all-gathers them, runs its
+    column-parallel and row-parallel linears on its slice and reduce-scatters the partial sums back to rows
+    (``parallel.sequence_parallel``; the collectives are each other's gradient).
+    Reference: inc/engine/train/qwen4_exp.h:15-20, src/train/qwen4_exp.cpp:229-259."""
+
+    def __init__(self, layer: "TunedLayer", rank: int, world: int, group=None):
+        super().__init__()
+        c = layer.cfg
+        self.cfg, self.rank, self.world, self.group = c, rank, world, group
+        hd, nq, nkv = c.head_dim, c.n_q, c.n_kv
+        assert nq % world == 0 and nkv % world == 0, "heads must divide by the rank count"
+        self.nq, self.nkv = nq // world, nkv // world
+        ar = torch.arange
+        q = ar(rank * self.nq * hd, (rank + 1) * self.nq * hd)
+        k = nq * hd + ar(rank * self.nkv * hd, (rank + 1) * self.nkv * hd)
+        v = (nq + nkv) * hd + ar(rank * self.nkv * hd, (rank + 1) * self.nkv * hd)
+        self.qkv = ShardedTunedLinear(layer.qkv, "col", torch.cat([q, k, v]))
+        self.o = ShardedTunedLinear(layer.o, "row", q)
+        inter = layer.gu.core.shape[1] // 2
+        assert inter % world == 0
+        f = inter // world
+        gcols = ar(rank * f, (rank + 1) * f)
+        self.gu = ShardedTunedLinear(layer.gu, "col", torch.cat([gcols, inter + gcols]))
+        self.dn = ShardedTunedLinear(layer.dn, "row", gcols)
+        self.n1, self.n2 = layer.n1, layer.n2
+
+    def replicated(self):
+        return self.qkv.replicated() + self.o.replicated() + self.gu.replicated() + self.dn.replicated() + [self.n1.delta, self.n2.delta]
+
+    def forward(self, h):
+        from ..parallel.sequence_parallel import gather_rows, reduce_scatter_rows
+        c = self.cfg
+        hd, nq, nkv = c.head_dim, self.nq, self.nkv
+        x = gather_rows(self.n1(h), self.group)                         # [T, H]
+        T = x.shape[0]
+        qkv = self.qkv(x)
+        pos = torch.arange(T, device=h.device)
+        rot = c.rot_dim or hd
+        q = _rope(qkv[:, : nq * hd].reshape(T, nq, hd), pos, c.rope_theta, rot)
+        k = _rope(qkv[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd), pos, c.rope_theta, rot)
+        v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+        g = nq // nkv
+        att = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.repeat_interleave(g, 1).transpose(0, 1)[None],
+                                             v.repeat_interleave(g, 1).transpose(0, 1)[None], is_causal=True,
+                                             scale=c.attn_scale or 1.0 / math.sqrt(hd))[0].transpose(0, 1).reshape(T, nq * hd)
+        h = h + self.o.finish(reduce_scatter_rows(self.o(att), self.group))
+        gu = self.gu(gather_rows(self.n2(h), self.group))
+        inter = gu.shape[-1] // 2
+        act = F.silu(gu[:, :inter]) if c.act == "silu" else F.gelu(gu[:, :inter], approximate="tanh")
+        return h + self.dn.finish(reduce_scatter_rows(self.dn(act * gu[:, inter:]), self.group))
+
+
+class TunedModelSP(torch.nn.Module):
+    """``TunedModel`` over a process group: rows sharded from the embedding to the logits (every rank scores its own
+    rows against the teacher; the loss is the sum over ranks). ``sync_grads`` sums the gradients of the parameters every
+    rank holds in full; sharded parameters keep their local gradients."""
+
+    def __init__(self, full: "TunedModel", rank: int, world: int, device="cpu", group=None):
+        super().__init__()
+        self.cfg, self.rank, self.world, self.group = full.cfg, rank, world, group
+        self.layers = torch.nn.ModuleList([TunedLayerSP(L, rank, world, group) for L in full.layers])
+        self.final_norm = full.final_norm
+        self.register_buffer("embed", full.embed.clone())
+        self.register_buffer("head", full.head.clone())
+        self.devices = [device]
+        self.to(device)
+
+    def rows(self, T: int) -> slice:
+        per = T // self.world
+        assert per * self.world == T, "sequence length must be a multiple of the rank count"
+        return slice(self.rank * per, (self.rank + 1) * per)
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        """-> logits of this rank's rows [T / ranks, vocab]."""
+        mine = ids[self.rows(ids.shape[0])]
+        h = self.embed[mine.to(self.embed.device).long()] * self.cfg.embed_scale
+        for L in self.layers:
+            h = checkpoint(L, h, use_reentrant=False) if self.training else L(h)
+        return self.final_norm(h) @ self.head.t()
+
+    def sync_grads(self) -> None:
+        from ..parallel.sequence_parallel import sum_replicated_grads
+        reps = [self.final_norm.delta]
+        for L in self.layers:
+            reps += L.replicated()
+        sum_replicated_grads(reps, self.group)
+
+
 class TunedModel(torch.nn.Module):
     """fp32 training form of a dense decoder whose linears are ``TunedLinear`` (stacked qkv / gate_up like the engine)."""
 
@@ -190,15 +312,34 @@ def tune(model: TunedModel, sequences: list, teachers: list, o: E2EOptions, held
     train = list(range(len(sequences) - held_out))
     hist = {"eval": [], "train": []}
 
+    sp = isinstance(model, TunedModelSP)
+
+    def teacher_of(i, T):
+        t = _to(teachers[i], model.devices[-1])
+        if not sp:
+            return t
+        r = model.rows(T)                                   # this rank scores its own rows
+        return tuple(x[r] for x in t) if isinstance(t, (tuple, list)) else t[r]
+
+    def over_ranks(x: float) -> float:
+        if not sp or model.world == 1:
+            return x
+        import torch.distributed as dist
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, group=model.group)
+        return float(t) / model.world
+
     def evaluate(step):
         model.eval()
         with torch.no_grad():
-            kl = sum(float(kl_teacher(model(sequences[i]), _to(teachers[i], model.devices[-1])))
+            kl = sum(float(kl_teacher(model(sequences[i]), teacher_of(i, sequences[i].shape[0])))
                      for i in range(len(sequences) - held_out, len(sequences))) / max(1, held_out)
+        kl = over_ranks(kl)
         hist["eval"].append((step, kl))
         log(f"step {step}: held-out KL {kl:.6f}")
         return kl
     evaluate(0)
+    scale = o.batch * (model.world if sp else 1)
     for step in range(o.steps):
         model.train()
         for g in opt.param_groups:
@@ -207,14 +348,65 @@ def tune(model: TunedModel, sequences: list, teachers: list, o: E2EOptions, held
         total = 0.0
         for b in range(o.batch):
             i = train[(step * o.batch + b) % len(train)]
-            loss = kl_teacher(model(sequences[i]), _to(teachers[i], model.devices[-1])) / o.batch
+            loss = kl_teacher(model(sequences[i]), teacher_of(i, sequences[i].shape[0])) / scale
             loss.backward()
             total += float(loss.detach())
+        if sp:
+            model.sync_grads()                              # parameters every rank holds in full: sum over the ranks
+            total = over_ranks(total) * model.world
         opt.step()
         hist["train"].append(total)
         if (step + 1) % o.eval_every == 0 or step + 1 == o.steps:
             evaluate(step + 1)
     return hist
+
+
+def gather_tuned_model(sp: "TunedModelSP"):
+    """The tuned scales of every rank put back into whole vectors (what the tool writes): an object with the attributes
+    ``main`` reads (``layers[i].qkv / o / gu / dn`` with ``tuned_scales()``, ``n1`` / ``n2``)."""
+    import torch.distributed as dist
+
+    class _Lin:
+        def __init__(self, su, sv):
+            self.su, self.sv = su, sv
+
+        def tuned_scales(self):
+            return self.su, self.sv
+
+    def whole(lin: ShardedTunedLinear):
+        su = (lin.su * torch.exp(lin.a_u)).detach().cpu()
+        sv = (lin.sv * torch.exp(lin.a_v)).detach().cpu()
+        part = sv if lin.split == "col" else su
+        parts = [torch.empty_like(part) for _ in range(sp.world)]
+        dist.all_gather(parts, part.contiguous(), group=sp.group)
+        return parts, (su if lin.split == "col" else sv)
+
+    class _Layer:
+        pass
+    layers = []
+    for L in sp.layers:
+        out = _Layer()
+        c = sp.cfg
+        hd = c.head_dim
+        parts, su = whole(L.qkv)                                        # per rank [q | k | v] slices -> [Q | K | V]
+        nq, nkv = L.nq * hd, L.nkv * hd
+        sv = torch.cat([p[:nq] for p in parts] + [p[nq:nq + nkv] for p in parts] + [p[nq + nkv:] for p in parts])
+        out.qkv = _Lin(su, sv)
+        parts, sv = whole(L.o)
+        out.o = _Lin(torch.cat(parts), sv)
+        parts, su = whole(L.gu)
+        f = parts[0].shape[0] // 2
+        out.gu = _Lin(su, torch.cat([p[:f] for p in parts] + [p[f:] for p in parts]))
+        parts, sv = whole(L.dn)
+        out.dn = _Lin(torch.cat(parts), sv)
+        out.n1, out.n2 = L.n1, L.n2
+        layers.append(out)
+
+    class _Model:
+        pass
+    m = _Model()
+    m.layers = layers
+    return m
 
 
 def main(argv=None) -> int:
@@ -231,6 +423,10 @@ def main(argv=None) -> int:
     ap.add_argument("--lr-min", type=float, default=0.1)
     ap.add_argument("--eval-every", type=int, default=16)
     ap.add_argument("--norms", type=int, default=1)
+    ap.add_argument("--tp", type=int, default=0,
+                    help="N > 0: sequence-parallel tensor parallelism over the N ranks this process was started with "
+                         "(python -m torch.distributed.run --nproc-per-node N -m volta_engine_b200.tools.e2e ...); "
+                         "0: the layers are split over --devices as sequential stages")
     a = ap.parse_args(argv)
     from pathlib import Path
     from ..loader.safetensors import write_safetensors
@@ -249,7 +445,26 @@ def main(argv=None) -> int:
         if isinstance(teachers, dict):                   # the top-K teacher of volta_ppl
             teachers = list(zip(teachers["ids"], teachers["logp"], teachers["tail"]))
     o = E2EOptions(a.steps, a.batch, a.lr, a.warmup, a.lr_min, a.eval_every, bool(a.norms), devices)
-    hist = tune(tm, seqs, teachers, o)
+    rank = 0
+    if a.tp > 0:
+        import os
+        import torch.distributed as dist
+        cuda = devices[0].startswith("cuda")
+        dist.init_process_group("nccl" if cuda else "gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        if world != a.tp:
+            raise SystemExit(f"--tp {a.tp} but the process group has {world} ranks")
+        dev = f"cuda:{int(os.environ.get('LOCAL_RANK', rank))}" if cuda else "cpu"
+        tm = TunedModelSP(tm, rank, world, dev)
+        # sequences are cut to a multiple of the rank count (rows are sharded evenly)
+        seqs = [sq[: sq.shape[0] // world * world] for sq in seqs]
+        teachers = [tuple(x[: sq.shape[0]] for x in t) if isinstance(t, (tuple, list)) else t[: sq.shape[0]]
+                    for t, sq in zip(teachers, seqs)]
+    hist = tune(tm, seqs, teachers, o, log=print if rank == 0 else (lambda *_: None))
+    if a.tp > 0:
+        tm = gather_tuned_model(tm)
+        if rank != 0:
+            return 0
     out = Path(a.out) / ".partial"
     out.mkdir(parents=True, exist_ok=True)
     tensors = {}
