@@ -103,3 +103,55 @@ def test_gpu_had128_and_linear_paths():
     # decode rows are batch-invariant: row 0 alone equals row 0 inside a 3-row batch
     a = lin.forward(x[:1].to(dev)); b = lin.forward(x[:3].to(dev))[:1]
     assert torch.equal(a, b)
+
+
+def test_moe_model_with_exl3_experts_runs_on_cpu_and_its_bank_matches_dense_weights():
+    from volta_engine_b200.models.moe import MoEConfig, MoEModel
+    from volta_engine_b200.ops.moe_exl3 import EXL3ExpertBank
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    bank = EXL3ExpertBank.random(3, 128, 256, 3, e0=2, seed=1, std=0.05)
+    x = (torch.randn(2, 256, generator=torch.Generator().manual_seed(0)) * 0.5).to(torch.bfloat16)
+    ids = torch.tensor([[2, 9], [4, 3]], dtype=torch.int32)                  # expert 9 lives on another rank
+    d = bank.routes(x, ids, 0, 0.0).float()
+    assert float(d[1].abs().max()) == 0.0 and float(d[0].abs().max()) > 0
+    # the statement through dense effective weights
+    for r, (t, e) in enumerate(((0, 0), (0, None), (1, 2), (1, 1))):
+        if e is None:
+            continue
+        gu, dn = bank.dequant("gu", e), bank.dequant("dn", e)
+        h = x[t].float() @ gu.t()
+        a = torch.nn.functional.silu(h[:128]) * h[128:]
+        want = a @ dn.t()
+        assert torch.allclose(d[r], want, atol=3e-2 * float(want.abs().max()) + 1e-5), (r, float((d[r] - want).abs().max()))
+    cfg = MoEConfig.tiny_moe(expert_quant="exl3_4", hidden=256, expert_ffn=128)
+    m = MoEModel(cfg, "cpu").init_random(seed=3)
+    assert isinstance(m.layers[0].bank, EXL3ExpertBank) and m.layers[0].bank.bits == 4
+    kv = PagedKVCache(2, m.nkv, 64, 16, 1, 512, "cpu")
+    out, _ = Engine(m, kv, use_graphs=False, prefill_chunk=16).generate(list(range(1, 25)), 4)
+    assert len(out) == 4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 4, 5])
+def test_gpu_routed_experts_in_exl3(bits):
+    from volta_engine_b200.ops.moe_exl3 import EXL3ExpertBank
+    from volta_engine_b200.ops import kernels as K
+    dev = "cuda"
+    E, I, H, k = 8, 256, 512, 2
+    bank_c = EXL3ExpertBank.random(E, I, H, bits, e0=4, seed=9, std=0.05)
+    bank_g = bank_c.to(dev)
+    g = torch.Generator().manual_seed(2)
+    for rows in (1, 7, 16, 150):
+        x = (torch.randn(rows, H, generator=g) * 0.5).to(torch.bfloat16)
+        ids = torch.randint(0, 16, (rows, k), generator=g, dtype=torch.int32)
+        if rows == 150:
+            ids[:, 0] = 5                                  # one crowded expert: several tiles of the grouped GEMM
+        want = bank_c.routes(x[:24], ids[:24], 0, 0.0).float()       # (the CPU statement is slow: the first 24 rows)
+        got = bank_g.routes(x.to(dev), ids.to(dev), 0, 0.0).float().cpu()
+        scale = float(want.abs().max()) + 1e-6
+        n = want.shape[0]
+        assert float((got[:n] - want).abs().max()) < 4e-2 * scale, (bits, rows, float((got[:n] - want).abs().max()), scale)
+        away = ((ids < 4) | (ids >= 12)).reshape(-1)
+        assert float(got[away].abs().max()) == 0.0 if away.any() else True
+    assert K.check_status(dev) == 0

@@ -297,24 +297,26 @@ __global__ void __launch_bounds__(256) had128_kernel(HadArgs a) {
 
 // ------------------------------------------------------------------------------------------------ reconstruct
 // codes -> bf16 [N][K] (output features major, K contiguous): the A operand layout of the tcgen05 GEMM.
+// batch > 1: `batch` matrices back to back (the experts of a bank) -> [batch * N][K].
 template <int BITS, int CB>
 __global__ void __launch_bounds__(256) exl3_reconstruct_kernel(const uint16_t* __restrict__ codes,
-                                                               __nv_bfloat16* __restrict__ out, int K, int N) {
+                                                               __nv_bfloat16* __restrict__ out, int K, int N, int batch) {
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int KT = K >> 4, NT = N >> 4;
   const Exl3Lane<BITS> L(lane);
-  const long total = (long)KT * NT;
+  const long per = (long)KT * NT, total = per * batch;
   // consecutive warps walk kt for a fixed nt so that a CTA writes runs of 128 contiguous k per output row
-  for (long id = (long)blockIdx.x * 8 + (threadIdx.x >> 5); id < total; id += (long)gridDim.x * 8) {
+  for (long gid = (long)blockIdx.x * 8 + (threadIdx.x >> 5); gid < total; gid += (long)gridDim.x * 8) {
+    const long b = gid / per, id = gid % per;
     const int nt = (int)(id / KT), kt = (int)(id % KT);
     uint32_t w[3], f[4];
-    L.load(reinterpret_cast<const uint32_t*>(codes) + ((size_t)kt * NT + nt) * (8 * BITS), w);
+    L.load(reinterpret_cast<const uint32_t*>(codes) + ((size_t)b * per + (size_t)kt * NT + nt) * (8 * BITS), w);
     L.template decode<CB>(w, f);
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&f[p]));
       const int n = nt * 16 + g + 8 * (p >> 1), k = kt * 16 + 2 * t + 8 * (p & 1);
-      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)n * K + k) = __floats2bfloat162_rn(v.x, v.y);
+      *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)b * N + n) * K + k) = __floats2bfloat162_rn(v.x, v.y);
     }
   }
 }
@@ -373,15 +375,29 @@ int ve_exl3_gemv(const void* codes, const void* x, void* y, int M, int K, int N,
 #undef VE_EX
 }
 
+static int exl3_reconstruct_n(const void* codes, void* out, int K, int N, int bits, int cb, int batch, cudaStream_t st);
+
 int ve_exl3_reconstruct(const void* codes, void* out, int K, int N, int bits, int cb, cudaStream_t st) {
-  if (K % 16 || N % 16 || cb < 0 || cb > 2) return cudaErrorInvalidValue;
-  const long tiles = (long)(K / 16) * (N / 16);
+  return exl3_reconstruct_n(codes, out, K, N, bits, cb, 1, st);
+}
+
+// `batch` matrices back to back ([batch][K/16][N/16][16 * bits]) -> bf16 [batch * N][K]: the stacked A operand of the
+// grouped GEMM for a slab of routed experts.
+int ve_exl3_reconstruct_batch(const void* codes, void* out, int K, int N, int bits, int cb, int batch, cudaStream_t st) {
+  return exl3_reconstruct_n(codes, out, K, N, bits, cb, batch, st);
+}
+
+}  // extern "C"
+
+static int exl3_reconstruct_n(const void* codes, void* out, int K, int N, int bits, int cb, int batch, cudaStream_t st) {
+  if (K % 16 || N % 16 || cb < 0 || cb > 2 || batch < 1) return cudaErrorInvalidValue;
+  const long tiles = (long)(K / 16) * (N / 16) * batch;
   const int blocks = (int)((tiles + 7) / 8 < 148 * 8 ? (tiles + 7) / 8 : 148 * 8);
 #define VE_RC(B)                                                                                                           \
   case B:                                                                                                                  \
-    if (cb == 2) exl3_reconstruct_kernel<B, 2><<<blocks, 256, 0, st>>>((const uint16_t*)codes, (__nv_bfloat16*)out, K, N); \
-    else if (cb == 1) exl3_reconstruct_kernel<B, 1><<<blocks, 256, 0, st>>>((const uint16_t*)codes, (__nv_bfloat16*)out, K, N); \
-    else exl3_reconstruct_kernel<B, 0><<<blocks, 256, 0, st>>>((const uint16_t*)codes, (__nv_bfloat16*)out, K, N);         \
+    if (cb == 2) exl3_reconstruct_kernel<B, 2><<<blocks, 256, 0, st>>>((const uint16_t*)codes, (__nv_bfloat16*)out, K, N, batch); \
+    else if (cb == 1) exl3_reconstruct_kernel<B, 1><<<blocks, 256, 0, st>>>((const uint16_t*)codes, (__nv_bfloat16*)out, K, N, batch); \
+    else exl3_reconstruct_kernel<B, 0><<<blocks, 256, 0, st>>>((const uint16_t*)codes, (__nv_bfloat16*)out, K, N, batch);         \
     break;
   switch (bits) {
     VE_RC(1) VE_RC(2) VE_RC(3) VE_RC(4) VE_RC(5) VE_RC(6) VE_RC(7) VE_RC(8)
@@ -390,6 +406,8 @@ int ve_exl3_reconstruct(const void* codes, void* out, int K, int N, int bits, in
 #undef VE_RC
   VE_CHECK_LAUNCH();
 }
+
+extern "C" {
 
 // dt codes: 0 bf16, 1 fp32, 2 fp16. Supported (in -> out): bf16->fp16, fp32->bf16, fp32->fp16, fp16->fp16, bf16->bf16.
 int ve_had128(const void* in, const void* in2, void* out, const void* scale, const void* scale2, const void* expert,

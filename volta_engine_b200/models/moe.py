@@ -37,8 +37,9 @@ class MoEConfig(DenseConfig):
     first_dense_layers: int = 0    # leading layers with a dense FFN of width cfg.ffn
     router_bias_zipf: float = 0.0  # synthetic skew: expert bias ~ Zipf(s)
     shared_gate: bool = False      # shared expert output scaled by sigmoid(x . w): one more row of the router weight
-    # storage of the routed experts: "nvfp4", or GGUF blocks "gguf_<type>" / "gguf_<gate-up type>+<down type>"
-    # (e.g. "gguf_iq2_xxs+q4_k"); a random-init GGUF bank is random block bytes drawn on the device
+    # storage of the routed experts: "nvfp4" (quantised from random dense weights), "nvfp4_random" (codes drawn directly),
+    # "exl3_<bits>" (trellis codes drawn directly), or GGUF blocks "gguf_<type>" / "gguf_<gate-up type>+<down type>"
+    # (e.g. "gguf_iq2_xxs+q4_k": random block bytes drawn on the device)
     expert_quant: str = "nvfp4"
     model_type: str = "moe"
 
@@ -172,6 +173,10 @@ class MoEModel(DenseModel):
                 gt, dt = parse_expert_quant(cfg.expert_quant)
                 L.bank = GGUFExpertBank.random(self.e_local, I, H, gt, dt, self.e0, seed=seed * 100003 + li * 4099 + self.e0,
                                                device=dev, amp=std)
+            elif cfg.expert_quant.startswith("exl3_"):
+                from ..ops.moe_exl3 import EXL3ExpertBank
+                L.bank = EXL3ExpertBank.random(self.e_local, I, H, int(cfg.expert_quant[5:]), self.e0,
+                                               seed=seed * 100003 + li * 4099 + self.e0, device=dev, std=std)
             elif cfg.expert_quant == "nvfp4_random":
                 L.bank = ExpertBank.random(self.e_local, I, H, self.e0, seed * 100003 + li * 4099 + self.e0, dev, std)
             else:

@@ -4,6 +4,7 @@ directly in their storage format (so a 77 B-parameter model initialises in secon
   moe80b     48 layers, hidden 2048, 512 routed experts top-10 + shared expert, GQA attention; experts sharded over the
              ranks (expert parallel) with tensor-parallel attention. The reference's row runs EXL3 4.0 bpw experts; the
              routed experts here are NVFP4 (4.5 bpw): the EXL3 routed-expert kernels are not built.
+  moe80b_exl3  the same model with the routed experts as EXL3 4.0 bpw trellis codes (the reference row's format).
   mla_mtp    46 layers MLA attention + 128 experts top-8 + shared, one MTP layer drafting 3 tokens per round. NVFP4.
   dsv3_gguf  DeepSeek-V3 shape (61 layers, 3 dense, 256 experts sigmoid top-8 in 8 groups / top-4), dense linears Q4_K,
              routed experts IQ2_XXS (gate / up) + Q4_K (down) as GGUF blocks. Needs the memory of 4 or more GPUs.
@@ -23,7 +24,7 @@ import time
 
 import torch
 
-CONFIGS = ("moe80b", "mla_mtp", "dsv3_gguf")
+CONFIGS = ("moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf")
 
 
 def build(name: str, dev, comm, layers: int):
@@ -32,6 +33,11 @@ def build(name: str, dev, comm, layers: int):
         cfg = MoEConfig.baseline_moe()
         cfg.expert_quant = "nvfp4_random"
         klass, note = MoEModel, "routed experts NVFP4 4.5 bpw (reference row: EXL3 4.0 bpw; EXL3 expert kernels not built)"
+    elif name == "moe80b_exl3":
+        from ..models.moe import MoEConfig, MoEModel
+        cfg = MoEConfig.baseline_moe()
+        cfg.expert_quant = "exl3_4"
+        klass, note = MoEModel, "routed experts EXL3 4.0 bpw (trellis codes drawn at random), dense linears NVFP4"
     elif name == "mla_mtp":
         from ..models.mla import MLAConfig, MLAModel
         cfg = MLAConfig.baseline_mla_mtp()
