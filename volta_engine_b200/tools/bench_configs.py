@@ -2,8 +2,8 @@
 directly in their storage format (so a 77 B-parameter model initialises in seconds), synthetic token ids.
 
   moe80b     48 layers, hidden 2048, 512 routed experts top-10 + shared expert, GQA attention; experts sharded over the
-             ranks (expert parallel) with tensor-parallel attention. The reference's row runs EXL3 4.0 bpw experts; the
-             routed experts here are NVFP4 (4.5 bpw): the EXL3 routed-expert kernels are not built.
+             ranks (expert parallel) with tensor-parallel attention. The routed experts are NVFP4 (4.5 bpw), this engine's
+             native format; the reference's row runs EXL3 4.0 bpw experts (next entry).
   moe80b_exl3  the same model with the routed experts as EXL3 4.0 bpw trellis codes (the reference row's format).
   mla_mtp    46 layers MLA attention + 128 experts top-8 + shared, one MTP layer drafting 3 tokens per round. NVFP4.
   dsv3_gguf  DeepSeek-V3 shape (61 layers, 3 dense, 256 experts sigmoid top-8 in 8 groups / top-4), dense linears Q4_K,
@@ -32,7 +32,7 @@ def build(name: str, dev, comm, layers: int):
         from ..models.moe import MoEConfig, MoEModel
         cfg = MoEConfig.baseline_moe()
         cfg.expert_quant = "nvfp4_random"
-        klass, note = MoEModel, "routed experts NVFP4 4.5 bpw (reference row: EXL3 4.0 bpw; EXL3 expert kernels not built)"
+        klass, note = MoEModel, "routed experts NVFP4 4.5 bpw (reference row: EXL3 4.0 bpw, see moe80b_exl3)"
     elif name == "moe80b_exl3":
         from ..models.moe import MoEConfig, MoEModel
         cfg = MoEConfig.baseline_moe()
