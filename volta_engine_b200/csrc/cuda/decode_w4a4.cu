@@ -92,6 +92,13 @@ struct DecodeParams {
   void* rp_vpool;
   int rp_nq, rp_nkv, rp_rot, rp_fp8;
   float rp_theta;
+  // Optional L2 prefetch for the kernel behind: while this kernel streams its own weights (marked evict-first), every CTA
+  // asks for its share of [pf_ptr, pf_ptr + pf_bytes), the weights the next linear of the step will read, so that
+  // kernel finds them in L2 instead of paying HBM latency at its start. pf_ptr null: off.
+  const uint8_t* pf_ptr;
+  size_t pf_bytes;
+  const uint8_t* pf_ptr2;             // second range (the scale atoms)
+  size_t pf_bytes2;
   int* an_ticket;
   __nv_bfloat16* an_resid;            // [M, N], pitch N
   const __nv_bfloat16* an_w;          // [N]
@@ -108,7 +115,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, SF_BYTES = 2048;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
   constexpr int ACC_COLS = BN < 32 ? 32 : BN;
-  constexpr int TMEM_COLS = ACC_COLS + 32 <= 64 ? 64 : 128;
+  constexpr int TMEM_COLS = ACC_COLS + 64 <= 64 ? 64 : 128;      // accumulator + two sets of scale columns
   constexpr int MROWS = BN / TERMS;
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024 B alignment");
 
@@ -152,6 +159,7 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
   if (warp == 0) {
     if (elect_one()) {
       prefetch_tmap(&amap);
+      const uint64_t pol = l2_policy_evict_first();
       // weights do not depend on the kernel in front: with a programmatic dependent launch they start streaming
       // while that kernel is still running
       for (int i = 0; i < nkt; ++i) {
@@ -159,17 +167,37 @@ decode_w4a4_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ama
         if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) { atomicExch(&s_fail, 1); break; }
         uint8_t* st = stage_ptr(s);
         mbar_expect_tx(&full[s], A_BYTES + SF_BYTES);
-        tma_load_2d(st, &amap, &full[s], kt * 128, n0);
+        tma_load_2d_hint(st, &amap, &full[s], kt * 128, n0, pol);
+        if (p.pf_ptr && i == (nkt > STAGES ? STAGES : nkt - 1)) {
+          // own pipeline is full: now ask for this CTA's share of the next kernel's weights (chunks of <= 64 KB)
+          const size_t ctas = (size_t)gridDim.x * gridDim.y, me = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+          for (int r = 0; r < 2; ++r) {
+            const uint8_t* base = r ? p.pf_ptr2 : p.pf_ptr;
+            const size_t total = r ? p.pf_bytes2 : p.pf_bytes;
+            if (!base || !total) continue;
+            const size_t per = ((total + ctas - 1) / ctas + 15) & ~(size_t)15;
+            size_t lo = me * per;
+            const size_t hi = lo + per < total ? lo + per : total;
+            while (lo < hi) {
+              const size_t n = hi - lo < 65536 ? (hi - lo) & ~(size_t)15 : 65536;
+              if (!n) break;
+              l2_prefetch(base + lo, (uint32_t)n);
+              lo += n;
+            }
+          }
+        }
         bulk_load(st + A_BYTES + B_BYTES, p.sfa + ((size_t)tile * nkg + kt * 4) * 512, SF_BYTES, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_nvf4(128, BN);
-      const uint32_t tmem_sfa = tmem_base + ACC_COLS, tmem_sfb = tmem_base + ACC_COLS + 16;
       bool ok = true;
       for (int i = 0; i < nkt && ok; ++i) {
         const int s = i % STAGES;
+        // the scale columns alternate between two sets: the copies of k-tile i + 1 then do not have to wait until the
+        // MMAs of k-tile i have read theirs (a write-after-read chain through TMEM otherwise serialises the tiles)
+        const uint32_t tmem_sfa = tmem_base + ACC_COLS + (i & 1) * 32, tmem_sfb = tmem_sfa + 16;
         ok = mbar_wait(&full[s], (i / STAGES) & 1);
         if (!ok) break;
         tc_fence_after();
@@ -537,6 +565,20 @@ int ve_nvfp4_expand_rows(const void* X, long ldx, void* Xp, void* Xs, int M, int
 // ws: fp32 [N/128][ks][16][128]; tickets: int [N/128] zeroed once; ks = K splits (>= 1).
 // pdl != 0 launches with programmatic stream serialization: set-up and the first weight tiles overlap the kernel
 // in front of it in the stream (the kernel waits for that kernel before it touches X, residual or out).
+// The ranges the next ve_decode_w4a4 launch of this host thread asks the memory system to bring into L2 (consumed by that
+// launch). Both pointers 16 B aligned; sizes are rounded down to multiples of 16 B.
+static thread_local const void* g_pf_ptr = nullptr;
+static thread_local size_t g_pf_bytes = 0;
+static thread_local const void* g_pf_ptr2 = nullptr;
+static thread_local size_t g_pf_bytes2 = 0;
+
+int ve_decode_set_prefetch(const void* w, size_t bytes, const void* sf, size_t sf_bytes) {
+  if (((uintptr_t)w & 15) || ((uintptr_t)sf & 15)) return cudaErrorMisalignedAddress;
+  g_pf_ptr = w; g_pf_bytes = bytes & ~(size_t)15;
+  g_pf_ptr2 = sf; g_pf_bytes2 = sf_bytes & ~(size_t)15;
+  return 0;
+}
+
 int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, void* out, long ldo, void* out_f32,
                    const void* residual, long ldr, int M, int N, int K, float alpha, int terms, int ks, int pdl, int act,
                    float act_limit, const void* pn_w, const void* pn_resid, const void* pn_delta, void* pn_resid_out,
@@ -573,6 +615,8 @@ int ve_decode_w4a4(const void* Wp, const void* sfa, const void* X, long ldx, voi
   p.rp_rot = rp_rot; p.rp_fp8 = rp_fp8; p.rp_theta = rp_theta;
   p.an_ticket = (int*)an_ticket; p.an_resid = (__nv_bfloat16*)an_resid; p.an_w = (const __nv_bfloat16*)an_w;
   p.an_out = (__nv_bfloat16*)an_out; p.an_eps = an_eps; p.an_wbias = an_wbias;
+  p.pf_ptr = (const uint8_t*)g_pf_ptr; p.pf_bytes = g_pf_bytes; p.pf_ptr2 = (const uint8_t*)g_pf_ptr2; p.pf_bytes2 = g_pf_bytes2;
+  g_pf_ptr = g_pf_ptr2 = nullptr; g_pf_bytes = g_pf_bytes2 = 0;
   if (comm_args) {
     // leading fields of ve::CommArgs (csrc/cuda/comm.cu): peer[8], mc, rank, size, seq, status, budget, off_ll, ll_row_bytes
     struct Lead { uint8_t* peer[8]; uint8_t* mc; int rank, size; uint32_t* seq; int* status; unsigned long long budget;

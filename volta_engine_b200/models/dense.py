@@ -201,6 +201,17 @@ class DenseModel:
         self.lm_head = self._make_linear(head.float(), search, whole=full) if quant_head else LinearBF16(head)
         return self
 
+    def link_prefetch(self) -> None:
+        """Tell every decode linear which weights the step reads next (ops.kernels.link_prefetch): qkv -> o_proj ->
+        gate / up -> down -> the next layer's qkv, the last down -> the LM head."""
+        chain = []
+        for L in self.layers:
+            chain += [getattr(L, "qkv", None), getattr(L, "o_proj", None), getattr(L, "gate_up", None), getattr(L, "down", None)]
+        chain.append(self.lm_head)
+        chain = [c for c in chain if c is not None]
+        for a, b in zip(chain, chain[1:]):
+            K.link_prefetch(a, b)
+
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes()
         for L in self.layers:

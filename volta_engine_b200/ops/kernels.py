@@ -4,6 +4,7 @@ a GPU machine: a missing library raises); CPU tensors run the fp32 PyTorch oracl
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -15,6 +16,10 @@ from . import reference as ref
 PAGE = ref.PAGE
 
 _status = {}
+
+
+def _lib_kernels():
+    return _lib.kernels()
 _scratch_registry = {}
 
 
@@ -427,6 +432,23 @@ def nvfp4_expand_rows(x, terms=DW_TERMS):
 DW_PDL = os.environ.get("VOLTA_PDL", "1") != "0"
 
 
+# L2 prefetch chain of the decode linears: weights of the linear that runs next in a decode step are requested into L2 by
+# the CTAs of the current one (which streams its own weights evict-first), so the next kernel starts on L2 hits instead
+# of HBM latency. VOLTA_L2_PREFETCH_MB: most bytes requested per launch (0 = off).
+L2_PREFETCH_BYTES = int(float(os.environ.get("VOLTA_L2_PREFETCH_MB", "0")) * (1 << 20))
+_prefetch_next: dict = {}
+
+
+def link_prefetch(lin, nxt) -> None:
+    """After the decode linear over ``lin``'s weights the step runs ``nxt``: remember what to request."""
+    if lin is None or nxt is None or getattr(lin, "packed", None) is None or getattr(nxt, "packed", None) is None:
+        return
+    if not lin.packed.is_cuda or getattr(nxt, "_sf_atoms", None) is None:
+        return
+    w, sf = nxt.packed, nxt._sf_atoms
+    _prefetch_next[lin.packed.data_ptr()] = (w.data_ptr(), w.numel() * w.element_size(), sf.data_ptr(), sf.numel() * sf.element_size())
+
+
 def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=False, terms=DW_TERMS, ks=None, pdl=None,
                 act=0, act_limit=0.0, prenorm=None, push_args=0, addnorm=None, rope=None):
     """Decode / verify linear (M <= 16 rows) on the block-scaled FP4 tensor-core path; the kernel expands each bf16
@@ -456,6 +478,11 @@ def decode_w4a4(packed, sf_atoms, gscale, x, out=None, residual=None, out_f32=Fa
     # 128 rotates its q / k heads and writes k / v into the paged cache from its own epilogue
     rp = rope if rope is not None else (None, None, None, None, None, 0, 0, 0, 0.0)
     rp_table = rp[2]
+    nxt = _prefetch_next.get(packed.data_ptr()) if L2_PREFETCH_BYTES > 0 else None
+    if nxt is not None:
+        wb = min(nxt[1], L2_PREFETCH_BYTES)
+        sb = min(nxt[3], max(0, L2_PREFETCH_BYTES - wb))
+        _lib_kernels().ve_decode_set_prefetch(ctypes.c_void_p(nxt[0]), ctypes.c_size_t(wb), ctypes.c_void_p(nxt[2]), ctypes.c_size_t(sb))
     call("decode_w4a4", "pppl" + "plppl" + "iiifiiiif" + "ppppff" + "ppppffp" + "pppippiiifi" + "ppp", ptr(packed), ptr(sf_atoms), ptr(x), x.stride(0),
          0 if f32 else ptr(out), out.stride(0), ptr(out) if f32 else 0, ptr(residual),
          residual.stride(0) if residual is not None else 0, M, N, K, float(gscale), terms, ks, 1 if pdl else 0,

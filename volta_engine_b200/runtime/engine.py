@@ -56,6 +56,8 @@ class Engine:
         self.prefill_chunk = prefill_chunk
         self.feedback = feedback
         self.comm = model.comm
+        if self.cuda and hasattr(model, "link_prefetch"):
+            model.link_prefetch()
         dev = self.device
         R = MAX_GRAPH_ROWS
         # static step descriptor (device) + pinned host staging

@@ -18,7 +18,7 @@ TABLE = {
     "argmax": ("Sampling", P), "argmax2": ("Sampling", P), "topk": ("Sampling", P),
     "gemm_bf16": ("Gemm", P), "gemm_w4a16": ("LinearNVFP4", P), "gemm_w4a16_wide": ("LinearNVFP4", P), "gemm_w4a4": ("LinearNVFP4", P),
     "gemm_grouped_bf16": ("MoE grouped GEMM", P), "gemm_grouped_w4a16": ("MoE grouped GEMM", P),
-    "decode_w4a4": ("LinearNVFP4 decode", P), "nvfp4_expand_rows": ("LinearNVFP4 decode", P),
+    "decode_w4a4": ("LinearNVFP4 decode", P), "decode_set_prefetch": ("LinearNVFP4 decode", P), "nvfp4_expand_rows": ("LinearNVFP4 decode", P),
     "nvfp4_gemv": ("LinearNVFP4 decode", P), "nvfp4_gemv_mma": ("LinearNVFP4 decode", P),
     "nvfp4_gemv_mma_static": ("LinearNVFP4 decode", D), "nvfp4_quant_rows": ("NVFP4 quantise", P),
     "nvfp4_dequant": ("NVFP4 quantise", P), "bf16_gemv_f32": ("LinearPlainGEMV", P),
