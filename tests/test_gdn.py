@@ -256,3 +256,28 @@ def test_hybrid_model_tensor_parallel_matches_one_rank(tmp_path, mixer):
     # to rounding, none is far off)
     assert float(cos.median()) > 0.9995 and float((cos > 0.999).float().mean()) > 0.8 and float(cos.min()) > 0.95, cos
     assert float((got.argmax(-1) == want[:, :256].argmax(-1)).float().mean()) > 0.9
+
+
+@pytest.mark.gpu
+def test_gpu_hybrid_mtp_rounds_on_the_device_roll_back_and_match_plain_greedy():
+    from volta_engine_b200.runtime.mtp_runner import MtpRunner
+    dev = torch.device("cuda:0")
+    cfg = HybridConfig.tiny_hybrid(mtp_layers=1)
+    m = HybridModel(cfg, dev).init_random(seed=0, search=False)
+    prompt = torch.randint(0, cfg.vocab, (77,), generator=torch.Generator().manual_seed(4)).tolist()
+
+    def fresh():
+        m.gdn_states = None
+        return Engine(m, PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, dev), prefill_chunk=64)
+    plain, _ = fresh().generate(prompt, 20)
+    eng = fresh()
+    run = MtpRunner(eng, depth=3)
+    assert run._device_round_ok() and not run._device_round_ok(2)
+    eng.kv.reserve(0, len(prompt) + 40)
+    out, pos = [run.prefill_rows(0, prompt, 0, len(prompt), True)], len(prompt)
+    while len(out) < 20:
+        new = run.round(0, out[-1], pos)
+        out += new
+        pos += len(new)
+    assert out[:20] == plain[:20], (out, plain)
+    assert run._sts[(1, 3)]["graph"] is not None and run.stats["accepted"] < run.stats["proposed"]

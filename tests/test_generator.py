@@ -327,3 +327,26 @@ def test_hybrid_model_takes_rejected_draft_rows_back():
     m.forward(BatchRows.make([5, 6], [0, 1], [0] * 2, "cpu"), kv)
     want = [(s.conv[0], s.rec[0]) for s in m.gdn_states if s is not None]
     assert all(torch.equal(a, c) and torch.equal(b, d) for (a, b), (c, d) in zip(got, want))
+
+
+def test_hybrid_model_with_its_own_mtp_head_speculates_like_plain_greedy():
+    """The hybrid (GDN + gated attention) family with a checkpoint-style MTP head: the head's block is one more
+    full-attention layer with its own cache layer; rounds run journalled and rejected drafts are rolled back."""
+    from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+    cfg = HybridConfig.tiny_hybrid(vocab=256, mtp_layers=1)
+    m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+    assert m.mtp is not None and m.kv_layers == m.n_full + 1 and len(m.layers) == cfg.n_layers
+    assert m.mtp["layer"].gdn is None and m.mtp["layer"].kv_index == m.n_full
+
+    def gen(**opt):
+        kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 24, 2, 512, "cpu")
+        m.gdn_states = None
+        eng = Engine(m, kv, use_graphs=False, prefill_chunk=32)
+        o = Options.resolve(dict({"max_slots": 2, "prefix_interval": 0}, **opt), env={})
+        return Generator(eng, ByteTok(), o, eos_ids=[])
+    p = prompt(45, 12)
+    plain = gen().generate(Request(p, max_tokens=14, cache_prefix=False))
+    g = gen(speculator="mtp", spec_ctrl=False, spec_depth=3)
+    spec = g.generate(Request(p, max_tokens=14, cache_prefix=False))
+    assert spec["tokens"] == plain["tokens"]
+    assert g.metrics.spec["rounds"] > 0 and g.metrics.spec["accepted"] < g.metrics.spec["proposed"]

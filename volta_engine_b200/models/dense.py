@@ -201,6 +201,49 @@ class DenseModel:
         self.lm_head = self._make_linear(head.float(), search, whole=full) if quant_head else LinearBF16(head)
         return self
 
+    # ------------------------------------------------------------------------------------------ MTP head
+    mtp = None
+
+    def _init_random_with_mtp(self, base_init, seed: int, std: float, search: bool):
+        """Random weights plus the checkpoint-style MTP head when ``cfg.mtp_layers``: the head's block is built like one
+        more decoder layer (it gets cache layer ``n_layers``), plus the projection of [norm(embedding) | norm(hidden)]
+        and three norms. ``base_init`` is the family's own ``init_random``."""
+        cfg = self.cfg
+        n_main = cfg.n_layers
+        extra = int(getattr(cfg, "mtp_layers", 0) or 0)
+        cfg.n_layers = n_main + extra
+        try:
+            base_init(seed, std, search)
+        finally:
+            cfg.n_layers = n_main
+        if extra:
+            gen = torch.Generator(device=self.device)
+            gen.manual_seed(seed + 1000)
+            H = cfg.hidden
+            block = self.layers.pop()
+            fc = torch.randn(H, 2 * H, generator=gen, device=self.device) * std
+            ones = torch.ones(H, device=self.device, dtype=torch.bfloat16)
+            self.mtp = {"layer": block, "fc": self._make_linear(fc, search), "norm_e": ones.clone(),
+                        "norm_h": ones.clone(), "norm_out": ones.clone(), "cache_layer": n_main}
+        return self
+
+    def mtp_forward(self, next_ids: torch.Tensor, hidden: torch.Tensor, b: BatchRows, kv):
+        """One MTP step for the rows of ``b``: ``next_ids[r]`` is the token that follows row r, ``hidden[r]`` the
+        residual-stream state of row r. Returns (logits of this rank's vocabulary shard, MTP hidden [n, H])."""
+        cfg, m = self.cfg, self.mtp
+        e = K.embed(next_ids, self.embed, scale=cfg.embed_scale)
+        en = K.rmsnorm(e, m["norm_e"], cfg.rms_eps, cfg.norm_bias)
+        hn = K.rmsnorm(hidden, m["norm_h"], cfg.rms_eps, cfg.norm_bias)
+        h = m["fc"].forward(torch.cat([en, hn], dim=1).contiguous())
+        L = m["layer"]
+        comm = self.comm
+        x = K.rmsnorm(h, L.attn_norm, cfg.rms_eps, cfg.norm_bias)
+        o = self.attn_block(m["cache_layer"], L, x, b, kv, None)
+        x = comm.allreduce_add_norm(o, h, L.ffn_norm, cfg.rms_eps, cfg.norm_bias)
+        d = self.ffn_block(m["cache_layer"], L, x, b, None)
+        x = comm.allreduce_add_norm(d, h, m["norm_out"], cfg.rms_eps, cfg.norm_bias)
+        return self.lm_head.forward(x, out_f32=True), h
+
     def link_prefetch(self) -> None:
         """Tell every decode linear which weights the step reads next (ops.kernels.link_prefetch): qkv -> o_proj ->
         gate / up -> down -> the next layer's qkv, the last down -> the LM head."""

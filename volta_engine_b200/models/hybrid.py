@@ -56,7 +56,13 @@ class HybridConfig(MoEConfig):
         return c
 
     def is_full(self, li: int) -> bool:
+        if li >= self.n_layers_main:
+            return True                 # the MTP head's block is a full-attention layer
         return (li + 1) % self.full_interval == 0
+
+    @property
+    def n_layers_main(self) -> int:
+        return getattr(self, "_n_main", None) or self.n_layers
 
 
 class HybridLayer(MoELayer):
@@ -90,13 +96,19 @@ class HybridModel(MoEModel):
 
     @property
     def kv_layers(self) -> int:
-        """KV-cache layers this model needs (only the full-attention layers hold keys and values)."""
-        return self.n_full
+        """KV-cache layers this model needs (only the full-attention layers hold keys and values; one more for the MTP
+        head's block)."""
+        return self.n_full + int(getattr(self.cfg, "mtp_layers", 0) or 0)
 
     def init_random(self, seed: int = 4, std: float = 0.02, search: bool = False):
         self._li = 0
-        super().init_random(seed, std, search)
         cfg = self.cfg
+        cfg._n_main = cfg.n_layers
+        self._init_random_with_mtp(super().init_random, seed, std, search)
+        if self.mtp is not None and cfg.qk_norm:
+            L = self.mtp["layer"]
+            L.q_norm = torch.ones(cfg.head_dim, device=self.device, dtype=torch.bfloat16) * (1.0 - cfg.norm_bias)
+            L.k_norm = L.q_norm.clone()
         if cfg.qk_norm:
             for L in self.layers:
                 if L.gdn is None:

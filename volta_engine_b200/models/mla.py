@@ -117,21 +117,7 @@ class MLAModel(MoEModel):
         return L.qkv_a.nbytes() + L.q_b.nbytes() + L.o_proj.nbytes() + (L.w_uk.numel() + L.w_uv.numel()) * 2
 
     def init_random(self, seed: int = 3, std: float = 0.02, search: bool = False):
-        cfg = self.cfg
-        n_main = cfg.n_layers
-        cfg.n_layers = n_main + cfg.mtp_layers           # the MTP block is built like one more decoder layer
-        super().init_random(seed, std, search)
-        cfg.n_layers = n_main
-        if cfg.mtp_layers:
-            gen = torch.Generator(device=self.device)
-            gen.manual_seed(seed + 1000)
-            H = cfg.hidden
-            block = self.layers.pop()
-            fc = torch.randn(H, 2 * H, generator=gen, device=self.device) * std
-            ones = torch.ones(H, device=self.device, dtype=torch.bfloat16)
-            self.mtp = {"layer": block, "fc": self._make_linear(fc, search), "norm_e": ones.clone(),
-                        "norm_h": ones.clone(), "norm_out": ones.clone(), "cache_layer": n_main}
-        return self
+        return self._init_random_with_mtp(super().init_random, seed, std, search)
 
     def ensure_workspace(self, max_rows: int, max_splits: int):
         if self.device.type == "cuda" and self.mla_ws is None:
@@ -263,20 +249,3 @@ class MLAModel(MoEModel):
             out[r] = torch.einsum("hc,hvc->hv", o_lat, wuv).reshape(-1).to(q.dtype)
         return out
 
-    # ------------------------------------------------------------------------------------------ MTP head
-    def mtp_forward(self, next_ids: torch.Tensor, hidden: torch.Tensor, b: BatchRows, kv):
-        """One MTP step for the rows of ``b``: ``next_ids[r]`` is the token that follows row r, ``hidden[r]`` the
-        residual-stream state of row r. Returns (logits of this rank's vocabulary shard, MTP hidden [n, H])."""
-        cfg, m = self.cfg, self.mtp
-        e = K.embed(next_ids, self.embed, scale=cfg.embed_scale)
-        en = K.rmsnorm(e, m["norm_e"], cfg.rms_eps, cfg.norm_bias)
-        hn = K.rmsnorm(hidden, m["norm_h"], cfg.rms_eps, cfg.norm_bias)
-        h = m["fc"].forward(torch.cat([en, hn], dim=1).contiguous())
-        L = m["layer"]
-        comm = self.comm
-        x = K.rmsnorm(h, L.attn_norm, cfg.rms_eps, cfg.norm_bias)
-        o = self.attn_block(m["cache_layer"], L, x, b, kv, None)
-        x = comm.allreduce_add_norm(o, h, L.ffn_norm, cfg.rms_eps, cfg.norm_bias)
-        d = self.ffn_block(m["cache_layer"], L, x, b, None)
-        x = comm.allreduce_add_norm(d, h, m["norm_out"], cfg.rms_eps, cfg.norm_bias)
-        return self.lm_head.forward(x, out_f32=True), h

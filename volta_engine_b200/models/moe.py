@@ -37,6 +37,7 @@ class MoEConfig(DenseConfig):
     first_dense_layers: int = 0    # leading layers with a dense FFN of width cfg.ffn
     router_bias_zipf: float = 0.0  # synthetic skew: expert bias ~ Zipf(s)
     shared_gate: bool = False      # shared expert output scaled by sigmoid(x . w): one more row of the router weight
+    mtp_layers: int = 0            # 1: the checkpoint's own multi-token-prediction head (one more decoder block)
     # storage of the routed experts: "nvfp4" (quantised from random dense weights), "nvfp4_random" (codes drawn directly),
     # "exl3_<bits>" (trellis codes drawn directly), or GGUF blocks "gguf_<type>" / "gguf_<gate-up type>+<down type>"
     # (e.g. "gguf_iq2_xxs+q4_k": random block bytes drawn on the device)

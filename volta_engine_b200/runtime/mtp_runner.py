@@ -109,6 +109,9 @@ class MtpRunner:
         st["rows"][:, 0].copy_(st["anchor"])
         hid, nxt = st["hid"], st["anchor"]
         nsk = e._nsplit(k)
+        journal = hasattr(m, "rollback_state")             # recurrent state: the verify block runs journalled
+        if journal:
+            m.begin_journal(False)
         for i in range(d):                                # head position pos-1+i consumes (hidden, next token)
             b = BatchRows(st["anchor"], st["head_pos"][i], st["slot"], k, LOGITS_ALL, None, nsk)
             logits, hid = m.mtp_forward(nxt, hid, b, e.kv)
@@ -117,7 +120,11 @@ class MtpRunner:
             st["rows"][:, i + 1].copy_(nxt)
         n = k * (d + 1)
         b = BatchRows(st["rows"].view(n), st["rows_pos"].view(n), st["slots"].view(n), n, LOGITS_ALL, None, e._nsplit(n))
+        if journal:
+            m.begin_journal(True, ("mtp", k, d))
         logits = m.forward(b, e.kv)
+        if journal:
+            m.journal_on = False
         e._sample_greedy(logits, st["target"], st["val"], n)
         tgt = st["target"].view(k, d + 1)
         ok = (tgt[:, :d] == st["rows"][:, 1:]).to(torch.int32)
@@ -127,6 +134,8 @@ class MtpRunner:
 
     def _device_round_ok(self, k: int = 1) -> bool:
         e = self.e
+        if k > 1 and hasattr(self.model, "rollback_state"):
+            return False                                   # a journalled verify block holds the rows of one slot
         return (e.cuda and hasattr(e, "_nsplit") and not getattr(e, "mrope", False)
                 and k * (self.depth + 1) <= MAX_GRAPH_ROWS)
 
@@ -175,6 +184,9 @@ class MtpRunner:
             rows = [anchor] + drafts
             new = drafts[:acc] + [toks[acc]]
             base = j * (d + 1)
+            if acc < d and hasattr(m, "rollback_state"):
+                m._jlast = ("mtp", k, d)
+                m.rollback_state(slot, acc + 1)           # as if only the accepted rows had run
             if acc > 0:                                    # catch-up with the true hidden states of accepted rows
                 b = self._rows(rows[:acc], [pos + i for i in range(acc)], slot, False)
                 nx = torch.tensor(new[:acc], dtype=torch.int32).to(e.device)
@@ -204,10 +216,13 @@ class MtpRunner:
             e._sample_greedy(logits, nxt, val_buf, 1)
         drafts = dev_drafts.tolist()
         rows = [anchor] + drafts
-        toks = e.step(rows, [pos + i for i in range(len(rows))], [slot] * len(rows))
+        jn = {"journal": True} if getattr(e, "supports_journal", False) else {}
+        toks = e.step(rows, [pos + i for i in range(len(rows))], [slot] * len(rows), **jn)
         acc = 0
         while acc < len(drafts) and toks[acc] == drafts[acc]:
             acc += 1
+        if jn and acc < len(drafts):
+            e.rollback(slot, acc + 1)
         new = drafts[:acc] + [toks[acc]]
         h = m.last_residual
         if acc > 0:                                        # catch-up with the true hidden states of accepted rows
