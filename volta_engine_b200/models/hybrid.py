@@ -48,6 +48,23 @@ class HybridConfig(MoEConfig):
                    norm_bias=1.0, rope_theta=1e7)
 
     @classmethod
+    def flash_next(cls):
+        """The Flash-Next assembly (reference: src/models/qwen4_exp.cpp, docs/FLASH_NEXT.md:8-45): 48 layers of hidden
+        2560, gated delta-net mixers with block-sparse (QSA) full-attention layers of 24 query / 2 KV heads of 256, 512
+        routed experts top-10 (softmax) beside a sigmoid-gated shared expert, four gated fp32 residual streams, the
+        checkpoint's own MTP head. (The n-gram embedding layer needs its table files and is left to the loader.)"""
+        return cls(n_layers=48, hidden=2560, n_q=24, n_kv=2, head_dim=256, ffn=0, vocab=151936, n_experts=512, top_k=10,
+                   expert_ffn=512, shared_ffn=512, shared_gate=True, router="softmax", rot_dim=64, qk_norm=True, norm_bias=1.0,
+                   rope_theta=1e7, qsa=True, attn_gate=True, residual="gated", mtp_layers=1, gdn_k_heads=16, gdn_v_heads=32)
+
+    @classmethod
+    def qwen3_5_27b(cls):
+        """The 27B hybrid assembly (reference: src/models/qwen3_5.cpp): ``dense_27b`` plus the checkpoint's MTP head."""
+        c = cls.dense_27b()
+        c.mtp_layers = 1
+        return c
+
+    @classmethod
     def tiny_hybrid(cls, **kw):
         c = cls(n_layers=4, hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, vocab=1024, n_experts=8, top_k=2, expert_ffn=128,
                 shared_ffn=128, full_interval=2, gdn_k_heads=2, gdn_v_heads=4, gdn_dk=64, gdn_dv=64, rot_dim=32, qk_norm=True)

@@ -6,6 +6,8 @@ directly in their storage format (so a 77 B-parameter model initialises in secon
              native format; the reference's row runs EXL3 4.0 bpw experts (next entry).
   moe80b_exl3  the same model with the routed experts as EXL3 4.0 bpw trellis codes (the reference row's format).
   mla_mtp    46 layers MLA attention + 128 experts top-8 + shared, one MTP layer drafting 3 tokens per round. NVFP4.
+  flash_next the Flash-Next assembly (48 layers, GDN + block-sparse attention, 512 experts, gated residual streams, MTP).
+  qwen3_5    the 27B hybrid assembly (48 GDN + 16 gated attention layers, dense FFN, MTP head).
   dsv3_gguf  DeepSeek-V3 shape (61 layers, 3 dense, 256 experts sigmoid top-8 in 8 groups / top-4), dense linears Q4_K,
              routed experts IQ2_XXS (gate / up) + Q4_K (down) as GGUF blocks. Needs the memory of 4 or more GPUs.
 
@@ -24,7 +26,7 @@ import time
 
 import torch
 
-CONFIGS = ("moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf")
+CONFIGS = ("moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf", "flash_next", "qwen3_5")
 
 
 def build(name: str, dev, comm, layers: int):
@@ -43,6 +45,13 @@ def build(name: str, dev, comm, layers: int):
         cfg = MLAConfig.baseline_mla_mtp()
         cfg.expert_quant = "nvfp4_random"
         klass, note = MLAModel, "NVFP4 weights (reference row: EXL3 3.05 bpw)"
+    elif name in ("flash_next", "qwen3_5"):
+        from ..models.hybrid import HybridConfig, HybridModel
+        cfg = HybridConfig.flash_next() if name == "flash_next" else HybridConfig.qwen3_5_27b()
+        cfg.expert_quant = "nvfp4_random"
+        klass = HybridModel
+        note = ("GDN + QSA attention, 512 NVFP4 experts + gated shared expert, gated residual streams, MTP head" if name == "flash_next"
+                else "48 GDN + 16 gated attention layers, dense FFN, NVFP4, MTP head")
     elif name == "dsv3_gguf":
         from ..models.mla import MLAConfig, MLAModel
         cfg = MLAConfig.baseline_dsv3()
@@ -54,7 +63,10 @@ def build(name: str, dev, comm, layers: int):
     if layers:
         cfg.n_layers = layers
         cfg.first_dense_layers = min(cfg.first_dense_layers, max(0, layers - 1))
-    return klass(cfg, dev, comm).init_random(seed=1), cfg, note
+    model = klass(cfg, dev, comm).init_random(seed=1)
+    if getattr(cfg, "residual", "plain") != "plain":
+        model.init_stream_weights()
+    return model, cfg, note
 
 
 def run(args, ClockSampler) -> int:
@@ -96,7 +108,8 @@ def run(args, ClockSampler) -> int:
     streams = 16
     max_seq = plen + 4 * (steps + warm) + 256
     mla = hasattr(cfg, "q_lora_rank")
-    n_cache = cfg.n_layers + getattr(cfg, "mtp_layers", 0)
+    n_cache = model.kv_layers if hasattr(type(model), "kv_layers") and isinstance(getattr(type(model), "kv_layers"), property) \
+        else cfg.n_layers + getattr(cfg, "mtp_layers", 0)
     pages = streams * ((max_seq + 63) // 64 + 2)
     if mla:
         kv = PagedKVCache(n_cache, 1, 576, pages, streams, max_seq, dev, v_head_dim=8)
