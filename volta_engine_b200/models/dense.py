@@ -376,6 +376,7 @@ class DenseModel:
                 normed = S.gated_stream_update(d, xs, post, nxt.norm, eps, comm=comm)
             hid, _ = S.gr_mix_prenormed(normed, self.final_hc)
             x = K.rmsnorm(hid, self.final_norm, eps, cfg.norm_bias)
+            pre = hid
         else:
             for li, L in enumerate(self.layers):
                 fn, base, scale = L.attn_hc
@@ -386,8 +387,10 @@ class DenseModel:
                 mix = S.hc_collapse(xs, fn, base, scale, cfg.hc_sinkhorn, norm_w=L.ffn_norm, norm_eps=eps, norm_bias=cfg.norm_bias)
                 d = self.ffn_block(li, L, mix.collapsed, b, None)
                 S.hc_update(d, xs, mix.post, mix.comb, comm=comm)
-            x = K.rmsnorm(S.head_mean(xs), self.final_norm, eps, cfg.norm_bias)
-        self.last_hidden, self.last_residual, self.last_streams = x, None, xs
+            pre = S.head_mean(xs)
+            x = K.rmsnorm(pre, self.final_norm, eps, cfg.norm_bias)
+        # (last_residual: the state in front of the final norm, what an MTP head reads; the streams themselves stay fp32)
+        self.last_hidden, self.last_residual, self.last_streams = x, pre.to(x.dtype), xs
         if b.logits == LOGITS_NONE:
             return None
         if b.logits == LOGITS_LAST:
