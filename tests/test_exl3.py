@@ -155,3 +155,31 @@ def test_gpu_routed_experts_in_exl3(bits):
         away = ((ids < 4) | (ids >= 12)).reshape(-1)
         assert float(got[away].abs().max()) == 0.0 if away.any() else True
     assert K.check_status(dev) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,cb", [(2, ex.CB_MUL1), (3, ex.CB_MUL1), (4, ex.CB_MUL1), (4, ex.CB_3INST), (6, ex.CB_MCG)])
+def test_gpu_viterbi_encoder_matches_the_host_statement(bits, cb):
+    """The device encoder runs the same search as quant.exl3.viterbi_encode_tile: the same code words (or, where two
+    paths tie to the last bit, the same squared error), and its streams are tail-biting (they decode to 256 windows)."""
+    from volta_engine_b200.ops.linear_exl3 import exl3_viterbi
+    g = torch.Generator().manual_seed(bits * 10 + cb)
+    targets = torch.randn(3, 256, generator=g)
+    got = exl3_viterbi(targets.cuda(), bits, cb).cpu()
+    for i in range(3 if bits >= 4 else 1):                       # (the host search is slow at low rates: 2^(16 + bits) per step)
+        want = ex.viterbi_encode_tile(targets[i], bits, cb)
+        vg = ex.decode_windows(ex.tile_windows(got[i], bits), cb)
+        vw = ex.decode_windows(ex.tile_windows(want, bits), cb)
+        eg, ew = float(((vg - targets[i]) ** 2).sum()), float(((vw - targets[i]) ** 2).sum())
+        assert torch.equal(got[i], want) or abs(eg - ew) < 1e-4 * max(1.0, ew), (bits, cb, i, eg, ew)
+        assert eg < 256 * (4.0 ** -bits) * 6 + 1e-3, (bits, eg)         # the rate-distortion ballpark of a trellis code
+
+
+@pytest.mark.gpu
+def test_gpu_quantize_whole_matrix_with_the_device_encoder():
+    W = torch.randn(256, 384, generator=torch.Generator().manual_seed(1)) * 0.03
+    codes, suh, svh = ex.quantize(W.cuda(), 4)
+    assert codes.shape == (16, 24, 64) and codes.is_cuda
+    eff = ex.effective_weight(codes.cpu(), 4, suh.cpu(), svh.cpu())
+    rel = float((eff - W).norm() / W.norm())
+    assert rel < 0.12, rel                                         # 4 bits per weight: about 7-9 % relative error

@@ -44,6 +44,20 @@ def exl3_reconstruct(codes, K_, N, bits, cb, out=None):
     return out
 
 
+def exl3_viterbi(targets: torch.Tensor, bits: int, cb: int = ex.CB_MUL1, ctas: int | None = None) -> torch.Tensor:
+    """Trellis-encode tiles on the GPU: ``targets`` fp32 [tiles, 256] (stream-position order, codebook units) -> codes
+    int16 [tiles, 16 * bits]; the exact Viterbi search of ``quant.exl3.viterbi_encode_tile`` (bits 2..8)."""
+    assert targets.is_cuda and targets.dtype == torch.float32 and targets.shape[-1] == 256 and 2 <= bits <= 8
+    targets = targets.contiguous()
+    tiles = targets.shape[0]
+    ctas = ctas or min(tiles, 148)
+    per = 255 * (1 << (16 - bits))
+    back = torch.empty(ctas * per, dtype=torch.uint8, device=targets.device)
+    codes = torch.empty(tiles, 16 * bits, dtype=torch.int16, device=targets.device)
+    call("exl3_viterbi", "pppiiii", ptr(targets), ptr(codes), ptr(back), tiles, bits, cb, ctas)
+    return codes
+
+
 class LinearEXL3:
     """codes int16 [K/16, N/16, 16*bits]; suh fp16 [K]; svh fp16 [N]; optional bias."""
 

@@ -190,6 +190,12 @@ def quantize(W: torch.Tensor, bits: int, cb: int = CB_MUL1, seed: int = 0):
     scale = Wr.std().clamp(min=1e-12)          # codebook values have ~unit variance
     Wn = Wr / scale
     row, col = _tile_positions()
+    if W.is_cuda and 2 <= bits <= 8:
+        # every tile at once on the device (csrc/cuda/exl3_quant.cu): [K/16, N/16, 256] targets in stream-position order
+        from ..ops.linear_exl3 import exl3_viterbi
+        tiles = Wn.reshape(K // 16, 16, N // 16, 16).permute(0, 2, 1, 3)[:, :, row.to(W.device), col.to(W.device)]
+        codes = exl3_viterbi(tiles.reshape(-1, 256).float().contiguous(), bits, cb).reshape(K // 16, N // 16, 16 * bits)
+        return codes, su.to(torch.float16), (sv * scale).to(torch.float16)
     codes = torch.zeros(K // 16, N // 16, 16 * bits, dtype=torch.int16)
     for kt in range(K // 16):
         for nt in range(N // 16):

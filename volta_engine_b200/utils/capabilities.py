@@ -22,7 +22,7 @@ TABLE = {
     "nvfp4_gemv": ("LinearNVFP4 decode", P), "nvfp4_gemv_mma": ("LinearNVFP4 decode", P),
     "nvfp4_gemv_mma_static": ("LinearNVFP4 decode", D), "nvfp4_quant_rows": ("NVFP4 quantise", P),
     "nvfp4_dequant": ("NVFP4 quantise", P), "bf16_gemv_f32": ("LinearPlainGEMV", P),
-    "exl3_gemv": ("LinearTrellis", P), "exl3_reconstruct": ("LinearTrellis", P), "exl3_reconstruct_batch": ("MoE (EXL3 experts)", P), "had128": ("LinearTrellis", P),
+    "exl3_gemv": ("LinearTrellis", P), "exl3_reconstruct": ("LinearTrellis", P), "exl3_reconstruct_batch": ("MoE (EXL3 experts)", P), "exl3_viterbi": ("EXL3 quantiser", P), "exl3_viterbi_scratch": ("EXL3 quantiser", P), "had128": ("LinearTrellis", P),
     "gguf_gemv": ("LinearGguf", P), "gguf_dequant": ("LinearGguf", P), "gguf_set_iq_grids": ("LinearGguf", P),
     "gguf_moe_gemv": ("MoEGguf", P),
     "mla_rope_store": ("MLALatent", P), "mla_absorb_q": ("MLALatent", P), "mla_decode": ("MLALatent", P),
