@@ -91,7 +91,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
     ap.add_argument("--gemm-mode", default=os.environ.get("VOLTA_GEMM_MODE", "w4a16"))
-    ap.add_argument("--prefill-chunk", type=int, default=4096)
+    ap.add_argument("--prefill-chunk", type=int, default=8192)
     ap.add_argument("--comm", default=os.environ.get("VOLTA_COMM", "symm"))
     ap.add_argument("--kv-format", default="bf16", help="bf16 (the configuration of record) | fp8 | k8v4 | nvfp4 (quantised caches, A/B)")
     ap.add_argument("--config", default="dense27b", choices=["dense27b", "moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf", "flash_next", "qwen3_5"],
