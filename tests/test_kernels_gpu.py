@@ -131,6 +131,53 @@ def test_attention_prefill(hd, nq, nkv, n):
     assert_close(got.cpu(), want, rel=0.01, name="attn prefill")  # P is rounded to bf16 for the PV MMA
 
 
+@pytest.mark.parametrize("nq,nkv,start,n,window,gated", [(40, 8, 0, 40, 0, False), (40, 8, 1000, 700, 0, False),
+                                                         (16, 16, 300, 300, 0, False), (32, 4, 500, 260, 192, True)])
+def test_attention_prefill_tcgen05(nq, nkv, start, n, window, gated):
+    """The tcgen05 prefill kernel (128-row tiles, two softmax streams, lazy rescale) against the fp32 oracle and the
+    mma.sync kernel: one-page tiles, many pages, G = 1 and G = 8, sliding window with a sigmoid gate, two sequences."""
+    hd = 128
+    kpool, vpool, table = _kv_setup(nkv, hd, 2, 2048, 70)
+    _fill_cache(kpool, vpool, 21)
+    half = n // 2
+    slots = [1] * half + [0] * (n - half)                     # two sequences in one launch
+    pos = torch.tensor([start + i for i in range(half)] + [start // 2 + i for i in range(n - half)], dtype=torch.int32, device=DEV)
+    slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    q = rnd(n, (nq + 2 * nkv) * hd, seed=22)
+    gate = rnd(n, nq * hd, seed=23) if gated else None
+    tiles = K.make_prefill_tiles(slots, nq // nkv, DEV)
+    assert len(tiles) == 4 and tiles[3][2] <= tiles[2]
+    got = K.attention(q, pos, slot, table, kpool, vpool, nq, nkv, hd, 1 / math.sqrt(hd), tiles=tiles, window=window, gate=gate)
+    old = K.ATTN_PREFILL_TC
+    K.ATTN_PREFILL_TC = False
+    try:
+        mma = K.attention(q, pos, slot, table, kpool, vpool, nq, nkv, hd, 1 / math.sqrt(hd), tiles=tiles, window=window, gate=gate)
+    finally:
+        K.ATTN_PREFILL_TC = old
+    want = ref.attention(q.cpu(), pos.cpu(), slot.cpu(), table.cpu(), kpool.cpu(), vpool.cpu(), nq, nkv, hd,
+                         1 / math.sqrt(hd), window, None, gate.cpu() if gated else None)
+    assert K.check_status(torch.device(DEV)) == 0
+    assert_close(got.cpu(), want, rel=0.01, name="attn prefill tcgen05")
+    assert_close(mma.cpu(), want, rel=0.01, name="attn prefill mma.sync")
+
+
+def test_attention_prefill_tcgen05_key_end():
+    """Bidirectional rows (key_end past the row's own position) on the tcgen05 kernel."""
+    hd, nq, nkv, n, start = 128, 8, 2, 90, 100
+    kpool, vpool, table = _kv_setup(nkv, hd, 2, 512, 20)
+    _fill_cache(kpool, vpool, 31)
+    pos = torch.arange(start, start + n, dtype=torch.int32, device=DEV)
+    slot = torch.ones(n, dtype=torch.int32, device=DEV)
+    key_end = pos.clone()
+    key_end[20:60] = start + 59                                # an image span: every row sees the whole span
+    q = rnd(n, (nq + 2 * nkv) * hd, seed=32)
+    tiles = K.make_prefill_tiles([1] * n, nq // nkv, DEV)
+    got = K.attention(q, pos, slot, table, kpool, vpool, nq, nkv, hd, 1 / math.sqrt(hd), tiles=tiles, key_end=key_end)
+    want = ref.attention(q.cpu(), pos.cpu(), slot.cpu(), table.cpu(), kpool.cpu(), vpool.cpu(), nq, nkv, hd,
+                         1 / math.sqrt(hd), 0, key_end.cpu())
+    assert_close(got.cpu(), want, rel=0.01, name="attn prefill tcgen05 key_end")
+
+
 def test_argmax_topk():
     logits = rnd(5, 151936 // 8, seed=14, dtype=torch.float32)
     logits[2, 100] = logits[2, 7] = 50.0  # tie -> lowest id

@@ -545,6 +545,10 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
   out[(long)row * out_stride + (long)head * HD + d] = f2bf(v);
 }
 
+}  // namespace ve
+#include "attention_tc.cuh"
+namespace ve {
+
 template <int HD, int NW, bool KS, int FMT>
 static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
                        cudaStream_t st) {
@@ -571,7 +575,8 @@ using namespace ve;
 extern "C" {
 
 // warps: 1 (decode / verify: <= 16 packed rows per tile, one warp), 104 (same tiles, four warps that split the
-// keys of every page) or 4 (prefill: <= 64 packed rows, 16 per warp).
+// keys of every page), 4 (prefill: <= 64 packed rows, 16 per warp) or 8 (prefill on tcgen05: <= 128 packed rows per tile,
+// bf16 cache, head_dim 128, one split).
 int ve_attention(const void* q, long q_stride, void* out, long out_stride, const void* gate, long gate_stride,
                  void* o_part, void* lse_part, const void* pos, const void* slot, const void* key_end,
                  const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
@@ -616,6 +621,9 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
     if (!stages) { const char* e = getenv("VOLTA_ATTN_STAGES"); stages = (e && e[0] == '2') ? 2 : 3; }   // 3: -8 % at 16K keys
     p.nst = (warps == 104 && hd <= 128) ? stages : 2;
   }
+  if (warps == 8 && (hd != 128 || kv_fp8 != 0 || nsplit != 1 || ((uintptr_t)q & 15) || (q_stride & 7) ||
+                     ((uintptr_t)out & 15) || (out_stride & 7) || ((uintptr_t)gate & 15) || (gate_stride & 7)))
+    return cudaErrorInvalidValue;
   CUtensorMap kmap, vmap;
   const uint64_t total_rows = (uint64_t)pool_pages * nkv * kPageTok;
   int rc;
@@ -645,7 +653,8 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   if (hd == HD_) {                                                               \
     if (kv_fp8 == 1) { VE_ATTN2(HD_, 1) } else if (kv_fp8 == 0) { VE_ATTN2(HD_, 0) }            \
   } else
-  if (kv_fp8 == 2 && hd == 128) { VE_ATTNQ(128, 2) }
+  if (warps == 8) { rc = launch_attn_tc<128>(p, kmap, vmap, ntiles, st); }
+  else if (kv_fp8 == 2 && hd == 128) { VE_ATTNQ(128, 2) }
   else if (kv_fp8 == 2 && hd == 256) { VE_ATTNQ(256, 2) }
   else if (kv_fp8 == 3 && hd == 128) { VE_ATTNQ(128, 3) }
   else if (kv_fp8 == 3 && hd == 256) { VE_ATTNQ(256, 3) }

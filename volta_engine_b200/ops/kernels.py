@@ -197,6 +197,8 @@ ATTN_DECODE_WARPS = 1 if os.environ.get("VOLTA_ATTN_DECODE", "ksplit") == "1warp
 # "fused": the split CTA that finishes last merges the partials itself. Measured slower than the parallel merge kernel
 # (one CTA walks 32 splits x 5 heads serially: 166 vs 192 tok/s on the 27B decode), so the kernel form is the default.
 ATTN_FUSED_MERGE = os.environ.get("VOLTA_ATTN_MERGE", "kernel") == "fused"
+# prefill tiles on the tcgen05 kernel where it applies (bf16 cache, head_dim 128); "mma" keeps the mma.sync kernel
+ATTN_PREFILL_TC = os.environ.get("VOLTA_ATTN_PREFILL", "tc") != "mma"
 
 
 class AttnWorkspace:
@@ -213,8 +215,10 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
               gate=None, tiles=None, nsplit=1, ws: AttnWorkspace | None = None):
     """Paged GQA attention. ``q`` is the (rotated) fused qkv buffer [rows, >= nq*hd].
 
-    ``tiles`` = (tile_first, tile_count, ntiles) int32 device tensors grouping consecutive rows of one
-    sequence for prefill (<= 64 // G tokens per tile); None = one row per tile (decode / verify).
+    ``tiles`` = (tile_first, tile_count, ntiles[, wide]) int32 device tensors grouping consecutive rows of one
+    sequence for prefill (<= 64 // G tokens per tile); None = one row per tile (decode / verify). ``wide`` is the same
+    grouping at <= 128 // G tokens per tile: with a bf16 cache and head_dim 128 the prefill runs on the tcgen05 kernel
+    (128 query rows per CTA, accumulators in TMEM), otherwise on the mma.sync kernel over the 64-row tiles.
     """
     rows = q.shape[0]
     fmt = kv_format_of(kpool)
@@ -232,8 +236,13 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
         tf = tc = None
         ntiles, warps = rows, ATTN_DECODE_WARPS
     else:
-        tf, tc, ntiles = tiles
+        tf, tc, ntiles = tiles[:3]
         warps = 4
+        if (ATTN_PREFILL_TC and len(tiles) > 3 and tiles[3] is not None and hd == 128 and fmt == 0 and nsplit == 1
+                and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0
+                and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0))):
+            tf, tc, ntiles = tiles[3]
+            warps = 8
     if fmt >= 2 and warps == 1:
         warps = 104                      # the scaled formats are built for the four-warp kernels
     if nsplit > 1 and ws is None:
@@ -248,8 +257,11 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
     return out
 
 
-def make_prefill_tiles(slots, G, device, max_rows_per_tile=64):
-    """Host helper: group consecutive rows with the same slot into tiles of <= 64 // G tokens."""
+def make_prefill_tiles(slots, G, device, max_rows_per_tile=64, wide=True):
+    """Host helper: group consecutive rows with the same slot into tiles of <= 64 // G tokens; ``wide`` appends the
+    grouping at <= 128 // G tokens (what the tcgen05 prefill kernel takes) as a fourth element."""
+    if wide and max_rows_per_tile == 64 and G <= 128:
+        return make_prefill_tiles(slots, G, device, 64, False) + (make_prefill_tiles(slots, G, device, 128, False),)
     per = max(1, max_rows_per_tile // G)
     first, count = [], []
     i, n = 0, len(slots)
