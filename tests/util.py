@@ -2,7 +2,7 @@ import torch
 
 
 def cos(a, b):
-    a, b = a.float().flatten(), b.float().flatten()
+    a, b = a.double().flatten(), b.double().flatten()      # fp32 sums over millions of elements lose ~1e-4
     return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-30))
 
 
