@@ -521,24 +521,45 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   }
 }
 
-// Merge split partials in split order. grid (rows * nq), block HD threads.
+// Merge split partials. grid (rows * nq), block (HD, kReduceGroups): the splits are dealt to kReduceGroups thread groups so
+// that every load of a partial is in flight at once (one round trip for the log-sum-exps, one for the partial outputs)
+// instead of one thread walking all splits; the groups' sums are combined through shared memory in group order, so the
+// result does not depend on timing.
+constexpr int kReduceGroups = 4;
+constexpr int kReduceMaxSplit = 128;
 __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part,
                                    __nv_bfloat16* __restrict__ out, long out_stride,
                                    const __nv_bfloat16* __restrict__ gate, long gate_stride, const int* __restrict__ slot,
                                    int nq, int nsplit, int HD) {
   grid_dep_launch();
   grid_dep_wait();
-  const int row = blockIdx.x / nq, head = blockIdx.x % nq, d = threadIdx.x;
+  __shared__ float s_l[kReduceMaxSplit];
+  __shared__ float s_acc[kReduceGroups][256];
+  __shared__ float s_ws[kReduceGroups];
+  const int row = blockIdx.x / nq, head = blockIdx.x % nq, d = threadIdx.x, sg = threadIdx.y;
   if (slot && slot[row] < 0) return;
   const long base = ((long)row * nq + head) * nsplit;
+  const int tid = sg * HD + d;
+  if (tid < nsplit) s_l[tid] = lse_part[base + tid];
+  __syncthreads();
   float mx = -FLT_MAX;
-  for (int i = 0; i < nsplit; ++i) mx = fmaxf(mx, lse_part[base + i]);
+  for (int i = 0; i < nsplit; ++i) mx = fmaxf(mx, s_l[i]);
   float acc = 0.f, wsum = 0.f;
-  for (int i = 0; i < nsplit; ++i) {
-    const float l = lse_part[base + i];
+#pragma unroll 8
+  for (int i = sg; i < nsplit; i += kReduceGroups) {
+    const float l = s_l[i];
     const float w = (l == -FLT_MAX) ? 0.f : exp2f(l - mx);
     wsum += w;
     acc += w * o_part[(base + i) * HD + d];
+  }
+  s_acc[sg][d] = acc;
+  if (d == 0) s_ws[sg] = wsum;
+  __syncthreads();
+  if (sg != 0) return;
+#pragma unroll
+  for (int g = 1; g < kReduceGroups; ++g) {
+    acc += s_acc[g][d];
+    wsum += s_ws[g];
   }
   float v = wsum > 0.f ? acc / wsum : 0.f;
   if (gate) v *= 1.f / (1.f + __expf(-bf2f(gate[(long)row * gate_stride + (long)head * HD + d])));
@@ -584,7 +605,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
                  float scale, int window, int warps, int kv_fp8, const void* kscale, const void* vscale, void* tickets,
                  void* status, cudaStream_t st) {
   if (ntiles <= 0) return 0;
-  if (nq % nkv || nsplit < 1 || kv_fp8 < 0 || kv_fp8 > 3) return cudaErrorInvalidValue;
+  if (nq % nkv || nsplit < 1 || nsplit > kReduceMaxSplit || kv_fp8 < 0 || kv_fp8 > 3) return cudaErrorInvalidValue;
   if (kv_fp8 >= 2 && ((hd != 128 && hd != 256) || warps == 1 || !kscale || !vscale)) return cudaErrorInvalidValue;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q;
@@ -665,7 +686,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
 #undef VE_ATTN
   if (rc) return rc;
   if (nsplit > 1 && !p.tickets) {
-  launch_pdl(attn_reduce_kernel, dim3(rows * nq), dim3(hd), 0, st, (const float*)o_part, (const float*)lse_part,
+  launch_pdl(attn_reduce_kernel, dim3(rows * nq), dim3(hd, kReduceGroups), 0, st, (const float*)o_part, (const float*)lse_part,
                (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, (const int*)slot, nq, nsplit, hd);
     rc = (int)cudaGetLastError();
   }
