@@ -94,7 +94,7 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=8192)
     ap.add_argument("--comm", default=os.environ.get("VOLTA_COMM", "symm"))
     ap.add_argument("--kv-format", default="bf16", help="bf16 (the configuration of record) | fp8 | k8v4 | nvfp4 (quantised caches, A/B)")
-    ap.add_argument("--config", default="dense27b", choices=["dense27b", "moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf", "flash_next", "qwen3_5"],
+    ap.add_argument("--config", default="dense27b", choices=["dense27b", "moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf", "flash_next", "qwen3_5", "glm5_next"],
                     help="dense27b: the configuration of record (default); the others are the reference's further headline "
                          "models (volta_engine_b200/tools/bench_configs.py)")
     args = ap.parse_args()

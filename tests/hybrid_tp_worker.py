@@ -20,10 +20,16 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]), world, rank == 0, timeout=datetime.timedelta(seconds=60))
     dist.init_process_group("gloo", store=store, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
-    kw = {"linear_mixer": "kda", "gdn_k_heads": 4} if mixer == "kda" else {}
-    cfg = HybridConfig.tiny_hybrid(vocab=256, **kw)
-    m = HybridModel(cfg, "cpu", HostComm()).init_random(seed=0, search=False)
-    kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
+    if mixer == "glm5":             # KDA mixers + latent attention: the GLM-5-Next-style assembly
+        from volta_engine_b200.models.glm5 import Glm5NextConfig, Glm5NextModel
+        cfg = Glm5NextConfig.tiny_glm5(vocab=256, gdn_k_heads=4, gdn_v_heads=4)
+        m = Glm5NextModel(cfg, "cpu", HostComm()).init_random(seed=0, search=False)
+        kv = m.make_cache(16, 2, 512)
+    else:
+        kw = {"linear_mixer": "kda", "gdn_k_heads": 4} if mixer == "kda" else {}
+        cfg = HybridConfig.tiny_hybrid(vocab=256, **kw)
+        m = HybridModel(cfg, "cpu", HostComm()).init_random(seed=0, search=False)
+        kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
     toks = torch.randint(0, 256, (40,), generator=torch.Generator().manual_seed(11)).tolist()
     kv.reserve(0, 64)
     outs = []

@@ -214,7 +214,7 @@ def test_gpu_hybrid_verify_blocks_roll_back_bit_exactly():
     assert K.check_status(dev) == 0
 
 
-@pytest.mark.parametrize("mixer", ["gdn", "kda"])
+@pytest.mark.parametrize("mixer", ["gdn", "kda", "glm5"])
 def test_hybrid_model_tensor_parallel_matches_one_rank(tmp_path, mixer):
     """Linear-attention heads split over two CPU ranks (gloo): the gathered logits equal the single-rank model's to
     rounding (the shards are quantised against the whole matrices' tensor scales)."""
@@ -238,11 +238,17 @@ def test_hybrid_model_tensor_parallel_matches_one_rank(tmp_path, mixer):
         text, _ = p.communicate(timeout=300)
         assert p.returncode == 0, text.decode()[-3000:]
     parts = [torch.load(f"{out}.{r}", weights_only=True) for r in range(2)]
-    kw = {"linear_mixer": "kda", "gdn_k_heads": 4} if mixer == "kda" else {}
-    cfg = HybridConfig.tiny_hybrid(vocab=256, **kw)
-    m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+    if mixer == "glm5":
+        from volta_engine_b200.models.glm5 import Glm5NextConfig, Glm5NextModel
+        cfg = Glm5NextConfig.tiny_glm5(vocab=256, gdn_k_heads=4, gdn_v_heads=4)
+        m = Glm5NextModel(cfg, "cpu").init_random(seed=0, search=False)
+        kv = m.make_cache(16, 2, 512)
+    else:
+        kw = {"linear_mixer": "kda", "gdn_k_heads": 4} if mixer == "kda" else {}
+        cfg = HybridConfig.tiny_hybrid(vocab=256, **kw)
+        m = HybridModel(cfg, "cpu").init_random(seed=0, search=False)
+        kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
     assert parts[0]["heads"] == (m.dims.n_k // 2, m.dims.n_v // 2)
-    kv = PagedKVCache(m.kv_layers, m.nkv, cfg.head_dim, 16, 2, 512, "cpu")
     toks = torch.randint(0, 256, (40,), generator=torch.Generator().manual_seed(11)).tolist()
     kv.reserve(0, 64)
     outs = []

@@ -1,0 +1,95 @@
+"""The GLM-5-Next-style assembly (KDA mixers + latent attention with the indexer + experts + hyper-connection streams +
+MTP head): chunked prefill and decode agree with a whole prefill on the CPU statement, the CUDA path agrees with the CPU
+statement, the MTP rounds on the device reproduce plain greedy decoding, and the launch configuration maps."""
+import json
+
+import pytest
+import torch
+
+from volta_engine_b200.models.glm5 import Glm5NextConfig, Glm5NextModel
+from volta_engine_b200.runtime.engine import Engine
+
+
+def _model(dev, **kw):
+    cfg = Glm5NextConfig.tiny_glm5(**kw)
+    m = Glm5NextModel(cfg, dev).init_random(seed=3)
+    if cfg.residual != "plain":
+        m.init_stream_weights()
+    return cfg, m
+
+
+@pytest.mark.parametrize("kw", [{}, {"residual": "hc"}, {"dsa": True}, {"mtp_layers": 1}])
+def test_glm5_prefill_equals_decode_on_cpu(kw):
+    cfg, m = _model("cpu", **kw)
+    assert ["kda" if L.gdn is not None else "mla" for L in m.layers] == ["kda", "mla", "kda", "mla"]
+    assert m.kv_layers == 2 + cfg.mtp_layers
+    assert m.prefix_resume == (None if cfg.dsa else "kv+state")
+    prompt = list(range(5, 45))
+    out, _ = Engine(m, m.make_cache(16, 2, 512), use_graphs=False, prefill_chunk=16).generate(prompt, 5)
+    m.gdn_states = None
+    nxt = Engine(m, m.make_cache(16, 2, 512), use_graphs=False, prefill_chunk=1000).prefill(0, prompt + out[:3])
+    assert nxt == out[3]
+
+
+def test_glm5_config_from_launch_directory(tmp_path):
+    from volta_engine_b200.models.factory import glm5_config_from_hf, load_model
+    c = glm5_config_from_hf({})
+    assert (c.n_layers, c.hidden, c.n_experts, c.top_k, c.expert_ffn, c.ffn, c.vocab) == (45, 4096, 288, 8, 2048, 12288, 154880)
+    assert sum(1 for li in range(c.n_layers) if c.is_full(li)) == 11 and c.linear_mixer == "kda" and c.residual == "hc"
+    hf = {"model_type": "glm5_next", "num_hidden_layers": 4, "num_mla_layers": 2, "hidden_size": 256, "num_attention_heads": 4,
+          "dense_intermediate_size": 512, "moe_intermediate_size": 128, "n_routed_experts": 8, "num_experts_per_tok": 2,
+          "first_k_dense_replace": 1, "vocab_size": 1024, "q_lora_rank": 128, "kda_heads": 2, "kda_head_dim": 64, "kda_rank": 32,
+          "num_nextn_predict_layers": 0, "dsa": False, "synthetic_weights": 5, "expert_quant": "nvfp4"}
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    m, _ = load_model(tmp_path, device="cpu")
+    assert isinstance(m, Glm5NextModel) and len(m.layers) == 4 and m.kv_layers == 2
+    out, _ = Engine(m, m.make_cache(16, 1, 256), use_graphs=False, prefill_chunk=16).generate(list(range(3, 30)), 3)
+    assert len(out) == 3
+    (tmp_path / "config.json").write_text(json.dumps({k: v for k, v in hf.items() if k != "synthetic_weights"}))
+    with pytest.raises(NotImplementedError):
+        load_model(tmp_path, device="cpu")
+
+
+@pytest.mark.gpu
+def test_gpu_glm5_matches_cpu_statement_and_whole_prefill():
+    dev = torch.device("cuda:0")
+    cfg, m = _model(dev, residual="hc", dsa=True)
+    prompt = torch.randint(0, cfg.vocab, (150,), generator=torch.Generator().manual_seed(0)).tolist()
+    eng = Engine(m, m.make_cache(16, 2, 512), use_graphs=True, prefill_chunk=64)
+    t1 = eng.prefill(0, prompt)
+    h1 = m.last_hidden[-1].float().cpu()
+    out, _ = eng.generate(prompt, 8, slot=1)
+    assert len(out) == 8 and out[0] == t1
+    m.gdn_states = None
+    m.dsa_states = {}
+    Engine(m, m.make_cache(16, 2, 512), use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
+    h2 = m.last_hidden[-1].float().cpu()
+    assert torch.nn.functional.cosine_similarity(h1, h2, dim=0) > 0.995
+    from volta_engine_b200.models.util import to_device
+    mc = to_device(m, "cpu")
+    mc.gdn_states = None
+    mc.dsa_states = {}
+    Engine(mc, mc.make_cache(16, 2, 512), use_graphs=False, prefill_chunk=1000).prefill(0, prompt)
+    assert torch.nn.functional.cosine_similarity(mc.last_hidden[-1].float(), h2, dim=0) > 0.98
+
+
+@pytest.mark.gpu
+def test_gpu_glm5_mtp_rounds_match_plain_greedy():
+    from volta_engine_b200.runtime.mtp_runner import MtpRunner
+    dev = torch.device("cuda:0")
+    cfg, m = _model(dev, mtp_layers=1)
+    prompt = torch.randint(0, cfg.vocab, (77,), generator=torch.Generator().manual_seed(4)).tolist()
+
+    def fresh():
+        m.gdn_states = None
+        return Engine(m, m.make_cache(16, 2, 512), prefill_chunk=64)
+    plain, _ = fresh().generate(prompt, 20)
+    eng = fresh()
+    run = MtpRunner(eng, depth=3)
+    eng.kv.reserve(0, len(prompt) + 40)
+    out, pos = [run.prefill_rows(0, prompt, 0, len(prompt), True)], len(prompt)
+    while len(out) < 20:
+        new = run.round(0, out[-1], pos)
+        out += new
+        pos += len(new)
+    assert out[:20] == plain[:20], (out, plain)

@@ -209,13 +209,17 @@ class DenseModel:
         more decoder layer (it gets cache layer ``n_layers``), plus the projection of [norm(embedding) | norm(hidden)]
         and three norms. ``base_init`` is the family's own ``init_random``."""
         cfg = self.cfg
+        if getattr(self, "_mtp_init_active", False):       # a family composed of two others: the outer call adds the head
+            return base_init(seed, std, search)
         n_main = cfg.n_layers
         extra = int(getattr(cfg, "mtp_layers", 0) or 0)
         cfg.n_layers = n_main + extra
+        self._mtp_init_active = True
         try:
             base_init(seed, std, search)
         finally:
             cfg.n_layers = n_main
+            self._mtp_init_active = False
         if extra:
             gen = torch.Generator(device=self.device)
             gen.manual_seed(seed + 1000)

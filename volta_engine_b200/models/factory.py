@@ -163,6 +163,8 @@ def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantiz
     mt = hf.get("model_type", "")
     if mt == "deepseek_v41":
         return load_dsv41(hf, d, device, comm), hf
+    if mt in ("glm5_next", "glm5-next"):
+        return load_glm5(hf, d, device, comm), hf
     src = TensorSource(d, prefer)
     if mt in DENSE_TYPES:
         cfg = dense_config_from_hf(hf)
@@ -198,6 +200,52 @@ def dsv4_config_from_hf(c: dict):
         beta_fast=float(c.get("beta_fast", 32.0)), beta_slow=float(c.get("beta_slow", 1.0)),
         engram_layers=tuple(c.get("engram_layer_ids", ())), engram_dim=int(c.get("engram_n_heads", 8)) * int(c.get("engram_head_dim", 256)),
         engram_rows=int(c.get("engram_table_rows", 1 << 16)), engram_ngram=int(c.get("engram_max_ngram_size", 4)))
+
+
+def glm5_config_from_hf(c: dict):
+    """GLM-5-Next ``config.json`` -> Glm5NextConfig. Keys as the reference reads them (src/models/glm5_next.cpp:499-552;
+    defaults are the published shape, inc/engine/models/glm5_next.h:33-52)."""
+    from .glm5 import Glm5NextConfig
+    base = Glm5NextConfig.glm5_next()
+    n = int(c.get("num_hidden_layers", base.n_layers))
+    n_mla = int(c.get("num_mla_layers", 0)) or sum(1 for li in range(n) if (li + 1) % base.full_interval == 0)
+    base.n_layers, base.hidden = n, int(c.get("hidden_size", base.hidden))
+    base.full_interval = max(1, n // max(1, n_mla))
+    base.n_q = int(c.get("num_attention_heads", base.n_q))
+    base.ffn = int(c.get("dense_intermediate_size", c.get("intermediate_size_dense", base.ffn)))
+    base.expert_ffn = int(c.get("moe_intermediate_size", c.get("intermediate_size", base.expert_ffn)))
+    base.shared_ffn = base.expert_ffn * int(c.get("n_shared_experts", 1))
+    base.n_experts, base.top_k = int(c.get("n_routed_experts", c.get("num_experts", base.n_experts))), int(c.get("num_experts_per_tok", base.top_k))
+    base.first_dense_layers = int(c.get("first_k_dense_replace", base.first_dense_layers))
+    base.router_scale = float(c.get("routed_scaling_factor", base.router_scale))
+    base.vocab = int(c.get("vocab_size", base.vocab))
+    base.q_lora_rank = int(c.get("q_lora_rank", base.q_lora_rank))
+    base.qk_nope, base.v_head_dim = int(c.get("qk_nope_head_dim", base.qk_nope)), int(c.get("v_head_dim", base.v_head_dim))
+    base.gdn_k_heads = base.gdn_v_heads = int(c.get("kda_heads", c.get("linear_num_heads", base.gdn_k_heads)))
+    base.gdn_dk = base.gdn_dv = int(c.get("kda_head_dim", c.get("linear_head_dim", base.gdn_dk)))
+    base.kda_rank = int(c.get("kda_rank", base.kda_rank))
+    base.rms_eps = float(c.get("rms_norm_eps", base.rms_eps))
+    base.rope_theta = float(c.get("rope_theta", base.rope_theta))
+    base.mtp_layers = int(c.get("num_nextn_predict_layers", base.mtp_layers))
+    base.dsa = bool(c.get("dsa", c.get("index_topk", 1)))
+    base.residual = "hc" if int(c.get("hc_mult", 4)) > 1 else "plain"
+    return base
+
+
+def load_glm5(hf: dict, model_dir: Path, device, comm):
+    """A GLM-5-Next directory. The synthetic form is built: ``config.json`` with ``"synthetic_weights": <seed>`` and no
+    tensor files runs the architecture (KDA mixers, latent attention with the indexer, experts, hyper-connection streams,
+    MTP head) with random weights; the tensor-name mapping of the published checkpoint is not."""
+    from .glm5 import Glm5NextModel
+    cfg = glm5_config_from_hf(hf)
+    if "synthetic_weights" not in hf:
+        raise NotImplementedError("glm5_next: loading checkpoint tensors is not built (config.json with "
+                                  "\"synthetic_weights\": <seed> runs the architecture with random weights)")
+    cfg.expert_quant = hf.get("expert_quant", "nvfp4_random")
+    model = Glm5NextModel(cfg, device, comm).init_random(seed=int(hf["synthetic_weights"]))
+    if cfg.residual != "plain":
+        model.init_stream_weights()
+    return model
 
 
 def load_dsv41(hf: dict, model_dir: Path, device, comm):

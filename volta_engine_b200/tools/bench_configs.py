@@ -8,6 +8,8 @@ directly in their storage format (so a 77 B-parameter model initialises in secon
   mla_mtp    46 layers MLA attention + 128 experts top-8 + shared, one MTP layer drafting 3 tokens per round. NVFP4.
   flash_next the Flash-Next assembly (48 layers, GDN + block-sparse attention, 512 experts, gated residual streams, MTP).
   qwen3_5    the 27B hybrid assembly (48 GDN + 16 gated attention layers, dense FFN, MTP head).
+  glm5_next  the GLM-5-Next assembly (45 layers: 34 KDA mixers + 11 latent-attention layers with the sparse indexer, 288
+             experts top-8 + shared, hyper-connection streams, MTP head).
   dsv3_gguf  DeepSeek-V3 shape (61 layers, 3 dense, 256 experts sigmoid top-8 in 8 groups / top-4), dense linears Q4_K,
              routed experts IQ2_XXS (gate / up) + Q4_K (down) as GGUF blocks. Needs the memory of 4 or more GPUs.
 
@@ -26,7 +28,7 @@ import time
 
 import torch
 
-CONFIGS = ("moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf", "flash_next", "qwen3_5")
+CONFIGS = ("moe80b", "moe80b_exl3", "mla_mtp", "dsv3_gguf", "flash_next", "qwen3_5", "glm5_next")
 
 
 def build(name: str, dev, comm, layers: int):
@@ -52,6 +54,11 @@ def build(name: str, dev, comm, layers: int):
         klass = HybridModel
         note = ("GDN + QSA attention, 512 NVFP4 experts + gated shared expert, gated residual streams, MTP head" if name == "flash_next"
                 else "48 GDN + 16 gated attention layers, dense FFN, NVFP4, MTP head")
+    elif name == "glm5_next":
+        from ..models.glm5 import Glm5NextConfig, Glm5NextModel
+        cfg = Glm5NextConfig.glm5_next()
+        cfg.expert_quant = "nvfp4_random"
+        klass, note = Glm5NextModel, "KDA mixers + latent attention with the sparse indexer, 288 NVFP4 experts + shared, hyper-connection streams, MTP head"
     elif name == "dsv3_gguf":
         from ..models.mla import MLAConfig, MLAModel
         cfg = MLAConfig.baseline_dsv3()
