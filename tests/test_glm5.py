@@ -75,6 +75,10 @@ def test_gpu_glm5_matches_cpu_statement_and_whole_prefill():
 
 @pytest.mark.gpu
 def test_gpu_glm5_mtp_rounds_match_plain_greedy():
+    """MTP rounds (draft chain through the head's latent-attention block, journalled verify block, rollback of the KDA
+    state) emit what plain greedy decoding emits. A verify block of four rows and a single decode row take different
+    kernels, so where the plain model's two best logits are closer than 0.02 the two may legitimately part ways: the
+    sequences must agree up to the first such near tie."""
     from volta_engine_b200.runtime.mtp_runner import MtpRunner
     dev = torch.device("cuda:0")
     cfg, m = _model(dev, mtp_layers=1)
@@ -83,13 +87,24 @@ def test_gpu_glm5_mtp_rounds_match_plain_greedy():
     def fresh():
         m.gdn_states = None
         return Engine(m, m.make_cache(16, 2, 512), prefill_chunk=64)
-    plain, _ = fresh().generate(prompt, 20)
+    e = fresh()
+    plain, gaps, pos = [e.prefill(0, prompt)], [], len(prompt)
+    for _ in range(20):
+        c = e.step_candidates([plain[-1]], [pos], [0])[0]
+        v = sorted(c.logits, reverse=True)
+        plain.append(c.ids[max(range(len(c.ids)), key=lambda i: c.logits[i])])
+        gaps.append(v[0] - v[1])
+        pos += 1
     eng = fresh()
     run = MtpRunner(eng, depth=3)
+    assert run._device_round_ok()
     eng.kv.reserve(0, len(prompt) + 40)
     out, pos = [run.prefill_rows(0, prompt, 0, len(prompt), True)], len(prompt)
     while len(out) < 20:
         new = run.round(0, out[-1], pos)
         out += new
         pos += len(new)
-    assert out[:20] == plain[:20], (out, plain)
+    div = next((i for i in range(20) if out[i] != plain[i]), None)
+    assert div is None or (div > 0 and gaps[div - 1] < 0.02), (div, out, plain, gaps)
+    assert div is None or div >= 4
+    assert run.stats["rounds"] > 0 and run._sts[(1, 3)]["graph"] is not None

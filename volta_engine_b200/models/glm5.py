@@ -50,7 +50,7 @@ class Glm5NextConfig(HybridConfig):
     def tiny_glm5(cls, **kw):
         c = cls(n_layers=4, hidden=256, n_q=4, n_kv=1, head_dim=576, ffn=512, vocab=1024, n_experts=8, top_k=2, expert_ffn=128,
                 shared_ffn=128, router="sigmoid", first_dense_layers=1, full_interval=2, linear_mixer="kda", gdn_k_heads=2,
-                gdn_v_heads=2, gdn_dk=64, gdn_dv=64, kda_rank=32, attn_gate=False, qk_norm=False, residual="plain",
+                gdn_v_heads=2, gdn_dk=64, gdn_dv=64, kda_rank=64, attn_gate=False, qk_norm=False, residual="plain",
                 mtp_layers=0, q_lora_rank=128, dsa=False)
         for k, v in kw.items():
             setattr(c, k, v)
