@@ -74,6 +74,54 @@ def test_ingest_window_and_release():
     assert r.ctx_len[0] == 0 and r.kv.slot_pages[0] == 0
 
 
+def _v2_config(dc):
+    import dataclasses
+    return dataclasses.replace(dc, version=2, conv_group_size=16, selector_rank=32, selector_top_k=8)
+
+
+def test_version2_drafter_rounds_leave_greedy_output_unchanged():
+    """The version-2 drafter (dynamic convolutions around every sub-layer, candidate walk) proposes other tokens than
+    version 1 but the verified output is the target's greedy output all the same."""
+    cfg, m, eng, dc = _setup()
+    p = _prompt(45, 5)
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0}, env={})
+    plain = Generator(eng, ByteTok(), o, eos_ids=[]).generate(Request(p, max_tokens=12, cache_prefix=False))
+    cfg2, m2, eng2, _ = _setup()
+    o2 = Options.resolve({"max_slots": 2, "prefix_interval": 0, "speculator": "draft", "spec_ctrl": False, "spec_depth": 3}, env={})
+    g = Generator(eng2, ByteTok(), o2, eos_ids=[])
+    g.drafter = D.DFlashRunner(eng2, _v2_config(dc))
+    spec = g.generate(Request(p, max_tokens=12, cache_prefix=False))
+    assert spec["tokens"] == plain["tokens"] and g.metrics.spec["rounds"] > 0
+    assert g.drafter.last_conf is not None and g.drafter.last_conf.numel() == dc.block_size - 1
+
+
+def test_version2_with_identity_convolutions_and_no_pairwise_term_is_version1():
+    """Static kernels = identity on tap 0, dynamic coefficients zero, pairwise codebooks zero: the version-2 stream is the
+    version-1 stream (up to the fp32 residual) and the walk picks every row's best candidate, the version-1 argmax."""
+    cfg, m, eng, dc = _setup()
+    p = _prompt(60, 7)
+    r1 = D.DFlashRunner(eng, dc, seed=11)
+    eng.prefill(0, p)                                      # the runner's ring is attached: the prompt's taps land in it
+    assert float(r1.ring.rows(0, 0, len(p)).abs().sum()) > 0
+    want = r1.draft(0, 9, len(p))
+    cfg_b, m_b, eng_b, _ = _setup()                        # the same target again (same seed) for the second drafter
+    r2 = D.DFlashRunner(eng_b, _v2_config(dc), seed=11)
+    eng_b.prefill(0, p)
+    r2.model.layers = r1.model.layers
+    r2.model.final_norm, r2.fc, r2.hidden_norm = r1.model.final_norm, r1.fc, r1.hidden_norm
+    taps = dc.conv_kernel_size
+    for V in r2.v2["layers"]:
+        for k in ("attn", "mlp"):
+            V[k + "_proj"].weight.zero_()
+            V[k + "_base"].zero_()
+            V[k + "_base"][0] = 1.0
+            V[k + "_base"][taps] = 1.0
+    r2.v2["pred"].zero_()
+    got = r2.draft(0, 9, len(p))
+    assert got == want, (got, want)
+    assert float(r2.last_conf.min()) > 0 and float(r2.last_conf.max()) <= 1
+
+
 def _walk_inputs(dev="cpu"):
     g = torch.Generator().manual_seed(3)
     bsz, rows, k, rank, vocab = 2, 5, 6, 32, 100
@@ -181,6 +229,49 @@ def test_drafter_rounds_on_gpu_equal_plain_greedy():
     assert spec["tokens"] == plain["tokens"] and g.metrics.spec["rounds"] > 0
 
 
+@pytest.mark.gpu
+def test_version2_drafter_on_gpu_matches_cpu_statement_and_plain_greedy():
+    dev = torch.device("cuda:0")
+    p = _prompt(45, 5)
+    cfg, m, eng, dc = _setup(dev)
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0}, env={})
+    plain = Generator(eng, ByteTok(), o, eos_ids=[]).generate(Request(p, max_tokens=16, cache_prefix=False))
+    cfg2, m2, eng2, _ = _setup(dev)
+    o2 = Options.resolve({"max_slots": 2, "prefix_interval": 0, "speculator": "draft", "spec_ctrl": False, "spec_depth": 3}, env={})
+    g = Generator(eng2, ByteTok(), o2, eos_ids=[])
+    g.drafter = D.DFlashRunner(eng2, _v2_config(dc))
+    spec = g.generate(Request(p, max_tokens=16, cache_prefix=False))
+    assert spec["tokens"] == plain["tokens"] and g.metrics.spec["rounds"] > 0
+    # the block's hidden rows on the device against the CPU statement of the same weights
+    from volta_engine_b200.models.util import to_device
+    from volta_engine_b200.runtime.batch import BatchRows, LOGITS_ALL
+    cfg3, m3, eng3, _ = _setup(dev)
+    r = D.DFlashRunner(eng3, _v2_config(dc))
+    eng3.prefill(0, p)
+    r.ingest(0, len(p))
+    r._reserve(0, len(p) + dc.block_size + 1)
+    B = dc.block_size
+    b = BatchRows.make([9] + [dc.mask_token_id] * (B - 1), [len(p) + i for i in range(B)], [0] * B, dev, LOGITS_ALL, 1, nsplit=1)
+    b.key_end = torch.full((B,), len(p) + B - 1, dtype=torch.int32, device=dev)
+    h_gpu = r._forward_v2(b).float().cpu()
+    mc = to_device(m3, "cpu")                         # the same target weights on the CPU
+    engc = Engine(mc, PagedKVCache(cfg3.n_layers, mc.nkv, cfg3.head_dim, 40, 2, 512, "cpu"), use_graphs=False, prefill_chunk=32)
+    rc = D.DFlashRunner(engc, _v2_config(dc))
+    engc.prefill(0, p)
+    rc.model.layers = to_device(r.model, "cpu").layers
+    rc.fc = LinearBF16(r.fc.weight.cpu())
+    rc.hidden_norm, rc.model.final_norm = r.hidden_norm.cpu(), r.model.final_norm.cpu()
+    rc.v2 = {"layers": [{k: (LinearBF16(v.weight.cpu()) if isinstance(v, LinearBF16) else v.cpu()) for k, v in V.items()} for V in r.v2["layers"]],
+             "gate": LinearBF16(r.v2["gate"].weight.cpu()), "pred": r.v2["pred"].cpu(), "succ": r.v2["succ"].cpu()}
+    rc.ingest(0, len(p))
+    rc._reserve(0, len(p) + B + 1)
+    bc = BatchRows.make([9] + [dc.mask_token_id] * (B - 1), [len(p) + i for i in range(B)], [0] * B, "cpu", LOGITS_ALL, 1, nsplit=1)
+    bc.key_end = torch.full((B,), len(p) + B - 1, dtype=torch.int32)
+    h_cpu = rc._forward_v2(bc).float()
+    cos = torch.nn.functional.cosine_similarity(h_gpu.flatten(), h_cpu.flatten(), dim=0)
+    assert cos > 0.995, float(cos)
+
+
 def test_sparse_head_policy_subset_hysteresis_and_persistence(tmp_path):
     from volta_engine_b200.runtime.sparse_head_policy import SparseHeadParams, SparseHeadPolicy
     p = SparseHeadPolicy(1000, SparseHeadParams(capacity=8, interval=16, decay_tokens=64, min_evidence=10.0, min_change=0.25,
@@ -265,3 +356,42 @@ def test_candidate_log_and_target_spool_round_trip(tmp_path):
     sp.add(1, 9, [2.0], [8])
     sp.add(0, 6, [0.1], [2])
     assert [r[0] for r in sp.take(0)] == [5, 6] and sp.take(0) == [] and sp.take(1) == [(9, [2.0], [8])]
+
+
+def test_version2_drafter_loads_from_a_checkpoint_directory(tmp_path):
+    """A drafter directory whose config says version 2 brings the convolution pairs and the selector in under the
+    reference's tensor names; the loaded runner drafts what a runner holding the same tensors drafts."""
+    import json
+    from volta_engine_b200.loader.safetensors import write_safetensors
+    from volta_engine_b200.models.factory import save_dense_checkpoint
+    from volta_engine_b200.server.cli import load_drafter
+    cfg, m, eng, dc = _setup()
+    dcfg = DenseConfig(n_layers=dc.n_layers, hidden=dc.hidden, n_q=dc.n_q, n_kv=dc.n_kv, head_dim=dc.head_dim, ffn=dc.ffn,
+                       vocab=cfg.vocab, rope_theta=dc.rope_theta, rms_eps=dc.rms_eps, qk_norm=True)
+    save_dense_checkpoint(tmp_path, dcfg, seed=3, fmt="bf16", shards=1)
+    hf = json.loads((tmp_path / "config.json").read_text())
+    hf.update(sliding_window=64, dflash_config={"block_size": 4, "target_layer_ids": [0, cfg.n_layers - 1], "mask_token_id": 255,
+                                                "version": 2, "conv_group_size": 16, "selector_rank": 32, "selector_top_k": 8})
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    g = torch.Generator().manual_seed(9)
+    bf, H, taps, G = torch.bfloat16, dc.hidden, 2, dc.hidden // 16
+    extra = {"fc.weight": (torch.randn(H, 2 * H, generator=g) * 0.02).to(bf), "hidden_norm.weight": torch.ones(H, dtype=bf),
+             "candidate_selector.hidden_projection.weight": (torch.randn(32, H, generator=g) * 0.05).to(bf),
+             "candidate_selector.predecessor_codebook": (torch.randn(cfg.vocab, 32, generator=g) * 0.3).to(bf),
+             "candidate_selector.successor_codebook": (torch.randn(cfg.vocab, 32, generator=g) * 0.3).to(bf)}
+    for i in range(dc.n_layers):
+        for name in ("attention_conv", "mlp_conv"):
+            base = (torch.randn(2 * taps, H, generator=g) * 0.02)
+            base[0] += 1
+            base[taps] += 1
+            extra[f"layers.{i}.{name}.base_kernel"] = base.to(bf)
+            extra[f"layers.{i}.{name}.kernel_projection.weight"] = (torch.randn(2 * taps * G, H, generator=g) * 0.02).to(bf)
+    write_safetensors(tmp_path / "drafter_extra.safetensors", extra)
+    r = load_drafter(eng, str(tmp_path))
+    assert r.cfg.version == 2 and r.v2 is not None and r.cfg.selector_rank == 32
+    assert torch.equal(r.v2["pred"], extra["candidate_selector.predecessor_codebook"])
+    assert torch.equal(r.v2["layers"][1]["mlp_proj"].weight, extra["layers.1.mlp_conv.kernel_projection.weight"])
+    p = _prompt(50, 2)
+    eng.prefill(0, p)
+    d = r.draft(0, 9, len(p))
+    assert len(d) == 3 and all(0 <= t < cfg.vocab for t in d)

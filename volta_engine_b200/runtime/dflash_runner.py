@@ -8,8 +8,11 @@ Round (reference: inc/engine/runtime/dflash2_runner.h:26-60, inc/engine/spec/dfl
     stores that context's keys and values, layer by layer, in its own paged cache;
   * a block of ``block_size`` rows (the anchor token followed by mask tokens) runs through the drafter with attention over
     the context and, bidirectionally, over the block itself; row i of the block proposes the token at position pos + i
-    (version 1: the head's argmax per row; version 2 adds the dynamic convolutions' kernels and the candidate walk,
-    csrc/cuda/spec.cu, which ``walk_candidates`` exposes);
+    (version 1: the head's argmax per row; version 2: every sub-layer of the drafter is wrapped in a pair of grouped
+    dynamic convolutions over the block's rows whose per-row kernels are a projection of the normed input, the residual
+    stream is fp32, and the tokens are chosen by a chained walk over the top-16 candidates of every row with a low-rank
+    pairwise term between the previous choice and each candidate; ``_forward_v2`` / ``walk_candidates``,
+    reference: src/spec/dflash_backbone.cu:186-350, inc/engine/spec/dflash.h:96-140);
   * the target verifies ``[anchor, drafts...]`` in ONE forward and keeps the longest agreeing prefix (generator).
 The drafter shares the target's embedding and LM head. Drafter context belongs to a slot; every slot has its own ring.
 """
@@ -44,6 +47,10 @@ class DFlashConfig:
     tap_cap: int = 2048
     version: int = 1
     quant: str = "bf16"
+    conv_kernel_size: int = 2      # version 2: taps of the dynamic convolutions
+    conv_group_size: int = 16      # channels that share one dynamic coefficient
+    selector_rank: int = 256       # width of the pairwise term of the candidate walk
+    selector_top_k: int = 16       # candidates per block row
 
 
 class TapRing:
@@ -98,6 +105,10 @@ class DFlashRunner:
         self.ctx_len = [0] * engine.kv.max_slots
         self.model.ensure_workspace(max(64, cfg.block_size), 8)
         self.stats = {"rounds": 0, "proposed": 0, "accepted": 0}
+        self.v2 = None
+        if cfg.version == 2:
+            self._init_v2(g, tc.vocab)
+        self.last_conf = None
         self.sparse_policy = None            # host policy of the sparse drafter head (enable_sparse_head)
         self.sparse_head = None
         self.sparse_state_path = None
@@ -110,10 +121,103 @@ class DFlashRunner:
         self.model.embed, self.model.lm_head = keep
         self.fc = LinearBF16(src.tensor("fc.weight", self.e.device, torch.bfloat16))
         self.hidden_norm = src.tensor("hidden_norm.weight", self.e.device, torch.bfloat16)
+        if self.v2 is not None:
+            # version-2 tensors (names of the reference's loader, src/spec/dflash_speculator.cu:363-454): per layer the two
+            # convolution pairs' static kernels and coefficient projections, then the candidate selector
+            dev, bf = self.e.device, torch.bfloat16
+
+            def get(name):
+                return src.tensor(name if src.has(name) else name + ".weight", dev, bf)
+            for i, V in enumerate(self.v2["layers"]):
+                for ours, theirs in (("attn", "attention_conv"), ("mlp", "mlp_conv")):
+                    V[ours + "_base"] = get(f"layers.{i}.{theirs}.base_kernel").reshape(2 * self.cfg.conv_kernel_size, self.cfg.hidden).contiguous()
+                    V[ours + "_proj"] = LinearBF16(get(f"layers.{i}.{theirs}.kernel_projection"))
+            self.v2["gate"] = LinearBF16(get("candidate_selector.hidden_projection"))
+            self.v2["pred"] = get("candidate_selector.predecessor_codebook")
+            self.v2["succ"] = get("candidate_selector.successor_codebook")
 
     def release(self, slot: int) -> None:
         self.ctx_len[slot] = 0
         self.kv.release(slot)
+
+    # ---- version 2: dynamic convolutions around every sub-layer, candidate selector
+    def _init_v2(self, g, vocab: int) -> None:
+        """Random weights of the version-2 parts. Per layer and sub-layer (attention, MLP): ``proj`` [2 * taps * groups,
+        H] emits the coefficients of both convolutions of the pair (side 0: in front of the sub-layer, side 1: behind
+        it; within a side [tap][group]) and ``base`` [2 * taps, H] holds the static kernels of the two sides. Selector:
+        ``gate`` [rank, H] projects a block row's hidden state, ``pred`` / ``succ`` [vocab, rank] are the codebooks of
+        the previous token and of a candidate."""
+        cfg, dev, bf = self.cfg, self.e.device, torch.bfloat16
+        H, taps, G = cfg.hidden, cfg.conv_kernel_size, cfg.hidden // cfg.conv_group_size
+        assert H % cfg.conv_group_size == 0
+
+        def rnd(*shape, std):
+            return (torch.randn(*shape, generator=g, device=dev) * std).to(bf)
+
+        def base():
+            b = rnd(2 * taps, H, std=0.02)
+            b[0] += 1.0                          # tap 0 of both sides starts as the identity: a fresh drafter is a v1 drafter
+            b[taps] += 1.0
+            return b.contiguous()
+        self.v2 = {"layers": [{"attn_proj": LinearBF16(rnd(2 * taps * G, H, std=0.02)), "attn_base": base(),
+                               "mlp_proj": LinearBF16(rnd(2 * taps * G, H, std=0.02)), "mlp_base": base()}
+                              for _ in range(cfg.n_layers)],
+                   "gate": LinearBF16(rnd(cfg.selector_rank, H, std=0.05)),
+                   "pred": rnd(vocab, cfg.selector_rank, std=0.3), "succ": rnd(vocab, cfg.selector_rank, std=0.3)}
+
+    @staticmethod
+    def _norm_f32(res: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+        """RMSNorm of the fp32 residual stream, rounded to bf16 for the projections that follow."""
+        y = res * torch.rsqrt((res * res).mean(-1, keepdim=True) + eps) * w.float()
+        return y.to(torch.bfloat16)
+
+    def _forward_v2(self, b: BatchRows) -> torch.Tensor:
+        """The version-2 drafter over one block: returns the final-normed hidden rows [block, H] (bf16). Per layer:
+        residual split + norm -> conv (side 0) -> attention -> conv (side 1) -> residual split + norm -> conv (side 0) ->
+        gated MLP -> conv (side 1); the stream ends in norm(last output + residual)."""
+        cfg, m = self.cfg, self.model
+        taps, gs = cfg.conv_kernel_size, cfg.conv_group_size
+        G = cfg.hidden // gs
+        n = b.n
+        x = K.embed(b.ids, m.embed, scale=m.cfg.embed_scale).float()
+        res = torch.zeros_like(x)
+        for li, L in enumerate(m.layers):
+            V = self.v2["layers"][li]
+            res = res + x
+            normed = self._norm_f32(res, L.attn_norm, cfg.rms_eps)
+            dyn = V["attn_proj"].forward(normed).reshape(n, 2, taps, G)
+            stage = dynconv(normed.float(), dyn[:, 0].contiguous(), V["attn_base"][:taps], gs).to(torch.bfloat16)
+            o = m.attn_block(li, L, stage, b, self.kv, None)
+            x = dynconv(o.float(), dyn[:, 1].contiguous(), V["attn_base"][taps:], gs)
+            res = res + x
+            normed = self._norm_f32(res, L.ffn_norm, cfg.rms_eps)
+            dyn = V["mlp_proj"].forward(normed).reshape(n, 2, taps, G)
+            stage = dynconv(normed.float(), dyn[:, 0].contiguous(), V["mlp_base"][:taps], gs).to(torch.bfloat16)
+            d = m.ffn_block(li, L, stage, b, None)
+            x = dynconv(d.float(), dyn[:, 1].contiguous(), V["mlp_base"][taps:], gs)
+        return self._norm_f32(res + x, m.final_norm, cfg.rms_eps)
+
+    def _select_v2(self, hidden: torch.Tensor, anchor: int) -> list[int]:
+        """Candidates of block rows 1.. through the (sharded) target head, then the chained walk."""
+        cfg, m, e = self.cfg, self.model, self.e
+        rows = hidden[1:].contiguous()
+        logits = m.lm_head.forward(rows, out_f32=True)
+        ids, vals, lse = K.topk(logits, cfg.selector_top_k, e.comm.rank * m.vocab_local)
+        vals = vals - lse[:, None]
+        if e.comm.size > 1:                      # every rank's shard candidates, merged to the best k of the union
+            ids_all, vals_all, lse_all = (e.comm.all_gather_rows(t) for t in (ids, vals + lse[:, None], lse))
+            r = rows.shape[0]
+            ids_all = ids_all.reshape(e.comm.size, r, -1).permute(1, 0, 2).reshape(r, -1)
+            vals_all = vals_all.reshape(e.comm.size, r, -1).permute(1, 0, 2).reshape(r, -1)
+            total = torch.logsumexp(lse_all.reshape(e.comm.size, r), dim=0)
+            top = torch.topk(vals_all, cfg.selector_top_k, dim=1)
+            ids, vals = torch.gather(ids_all, 1, top.indices).int().contiguous(), (top.values - total[:, None]).contiguous()
+        gate = self.v2["gate"].forward(rows)
+        anc = torch.tensor([anchor], dtype=torch.int32, device=rows.device)
+        out, conf = self.walk_candidates(vals.unsqueeze(0).contiguous(), ids.unsqueeze(0).contiguous(),
+                                         gate.unsqueeze(0).contiguous(), self.v2["pred"], self.v2["succ"], anc)
+        self.last_conf = conf[0, 1:]
+        return [int(t) for t in out[0].tolist()]
 
     # ---- context: keys and values of every layer from the projected taps of positions [ctx_len, upto)
     def ingest(self, slot: int, upto: int) -> int:
@@ -154,6 +258,12 @@ class DFlashRunner:
         pol = self.sparse_policy
         sparse = pol is not None and self.sparse_head is not None and pol.use_sparse()
         t0 = time.perf_counter()
+        if self.v2 is not None:
+            toks = self._select_v2(self._forward_v2(b), anchor)      # [anchor, d1 .. d_{B-1}]
+            if pol is not None:
+                pol.draft_step_time(False, (time.perf_counter() - t0) * 1e3)
+            nd = B - 1 if depth is None else max(0, min(B - 1, depth))
+            return toks[1:1 + nd]
         if sparse:                               # the block's hidden rows through the subset of head columns only
             b.logits = LOGITS_NONE
             m.forward(b, self.kv)

@@ -148,7 +148,10 @@ def load_drafter(engine, draft_dir: str):
                        head_dim=int(hf.get("head_dim", hf["hidden_size"] // hf["num_attention_heads"])),
                        ffn=int(hf["intermediate_size"]), target_layer_ids=tuple(d.get("target_layer_ids", hf.get("target_layer_ids", ()))),
                        sliding_window=int(hf.get("sliding_window") or 2048), rope_theta=float(hf.get("rope_theta", 1e7)),
-                       rms_eps=float(hf.get("rms_norm_eps", 1e-6)), mask_token_id=int(d.get("mask_token_id", hf.get("mask_token_id", 0))))
+                       rms_eps=float(hf.get("rms_norm_eps", 1e-6)), mask_token_id=int(d.get("mask_token_id", hf.get("mask_token_id", 0))),
+                       version=int(d.get("version", hf.get("dflash_version", 1))),
+                       conv_kernel_size=int(d.get("conv_kernel_size", 2)), conv_group_size=int(d.get("conv_group_size", 16)),
+                       selector_rank=int(d.get("selector_rank", 256)), selector_top_k=int(d.get("selector_top_k", 16)))
     runner = DFlashRunner(engine, cfg)
     runner.load(TensorSource(draft_dir))
     return runner
