@@ -395,3 +395,15 @@ def test_version2_drafter_loads_from_a_checkpoint_directory(tmp_path):
     eng.prefill(0, p)
     d = r.draft(0, 9, len(p))
     assert len(d) == 3 and all(0 <= t < cfg.vocab for t in d)
+
+
+def test_drafter_round_profile_reports_stage_times():
+    cfg, m, eng, dc = _setup()
+    r = D.DFlashRunner(eng, _v2_config(dc))
+    r.enable_profile()
+    p = _prompt(40, 1)
+    eng.prefill(0, p)
+    r.draft(0, 5, len(p))
+    r.draft(0, 6, len(p))
+    rep = r.profile_report()
+    assert rep["rounds"] == 2 and rep["backbone_ms"] > 0 and rep["select_ms"] > 0 and rep["ingest_ms"] >= 0

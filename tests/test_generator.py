@@ -145,7 +145,7 @@ def test_mtp_speculation_equals_plain_greedy():
 
 
 def test_reasoning_budget_forces_the_closing_sequence(model):
-    gen, _ = make(model)
+    gen, _ = make(model, thinking_soft_close=0)
     prompt = [(11 * i + 5) % 250 for i in range(30)]
     free = gen.generate(Request(prompt=prompt, max_tokens=24))["tokens"]
     close = [201, 202, 203]
@@ -159,6 +159,31 @@ def test_reasoning_budget_forces_the_closing_sequence(model):
     own = gen.generate(Request(prompt=prompt, max_tokens=12, think_open=True, think_end_id=free[2], think_close=close,
                                thinking_budget=8))["tokens"]
     assert own == free[:12]
+
+
+def test_reasoning_budget_soft_close_waits_for_a_sentence_end(model):
+    """thinking_soft_close = n: once the budget is spent the block stays open until a token ends a sentence or a line,
+    at most n tokens; the byte tokenizer of the test makes token 46 a full stop and 10 a newline."""
+    gen0, _ = make(model, thinking_soft_close=0)
+    prompt = [(11 * i + 5) % 250 for i in range(30)]
+    free = gen0.generate(Request(prompt=prompt, max_tokens=24))["tokens"]
+    close = [201, 202, 203]
+    # no sentence end among the free tokens: the close lands exactly soft tokens after the budget ran out
+    assert not any(t in (10, 33, 46, 63) for t in free[:12])
+    gen, _ = make(model, thinking_soft_close=4)
+    out = gen.generate(Request(prompt=prompt, max_tokens=24, think_open=True, think_end_id=202, think_close=close,
+                               thinking_budget=5))["tokens"]
+    exact = gen0.generate(Request(prompt=prompt, max_tokens=24, think_open=True, think_end_id=202, think_close=close,
+                                  thinking_budget=5))["tokens"].index(close[0])
+    k = out.index(close[0])
+    assert out[:k] == free[:k] and k == exact + 4 and out[k:k + 3] == close
+    # the sentence rule itself
+    class S:
+        last_char = ""
+    g = gen
+    assert g._ends_sentence(S(), 46) and g._ends_sentence(S(), 10) and g._ends_sentence(S(), 33) and not g._ends_sentence(S(), 65)
+    S.last_char = "3"
+    assert not g._ends_sentence(S(), 46)          # "3." is a number, not the end of a sentence
 
 
 @pytest.mark.parametrize("family", ["hybrid", "dsv4"])

@@ -149,3 +149,50 @@ def test_steering_from_launch_options_and_request_fields(tmp_path):
         steer_fields({"steer_scale": "x"})
     off = SteerConfig(O.Options.resolve({}, env={}), cfg.n_layers, Tok())
     assert not off.enabled and off.for_request({"steer_vector": "push"})["steer"] is None
+
+
+def test_model_switches_drop_indexers_and_the_routing_histogram():
+    from volta_engine_b200.models.mla import MLAConfig, MLAModel
+    from volta_engine_b200.runtime.options import Options
+    from volta_engine_b200.server.cli import apply_model_switches
+    m = MLAModel(MLAConfig.tiny_mla(dsa=True, mtp_layers=0), "cpu").init_random(seed=1)
+    assert all(L.dsa is not None for L in m.layers) and m.prefix_resume is None and m.heat is not None
+    apply_model_switches(m, Options.resolve({}, env={}))
+    assert all(L.dsa is not None for L in m.layers) and m.heat is not None          # defaults change nothing
+    apply_model_switches(m, Options.resolve({"dsa": False, "expert_stats": False}, env={}))
+    assert all(L.dsa is None for L in m.layers) and m.cfg.dsa is False and m.prefix_resume == "kv" and m.heat is None
+
+
+def test_small_runtime_switches():
+    import logging
+    from volta_engine_b200.runtime.route_dump import RouteRecorder
+    from volta_engine_b200.runtime.sparse_head_policy import SparseHeadParams, SparseHeadPolicy
+    from volta_engine_b200.runtime.spec_controller import SpecController
+    import torch
+    p = SparseHeadPolicy(100, SparseHeadParams(capacity=4, interval=7))
+    assert p.p.interval == 7 and not p.use_sparse()
+    p.set_subset([1, 2, 3])
+    p.force = True
+    assert p.use_sparse()                      # forced: whatever the measured miss rate
+    rec = RouteRecorder(layers=range(3, 5), min_rows=1)
+    x, ids, w = torch.zeros(2, 8), torch.tensor([[0, 1], [1, 2]]), torch.ones(2, 2)
+    rec.record(1, x, ids, w)
+    rec.record(4, x, ids, w)
+    assert list(rec.data) == [4]
+    c = SpecController()
+    c.log_decisions = True
+    records = []
+    h = logging.Handler()
+    h.emit = lambda r: records.append(r.getMessage())
+    lg = logging.getLogger("volta.spec")
+    lg.addHandler(h)
+    lg.setLevel(logging.INFO)
+    try:
+        c.use_speculation()
+        c.record_round(3, 3, 2, 1.0)
+        c.record_plain(1.0)
+        for _ in range(40):
+            c.use_speculation()
+    finally:
+        lg.removeHandler(h)
+    assert any("probe" in r for r in records) and any("speculative round" in r for r in records)

@@ -140,6 +140,24 @@ class DFlashRunner:
         self.ctx_len[slot] = 0
         self.kv.release(slot)
 
+    # ---- launch option spec_profile: wall time of a round's stages, the device drained at every stage boundary
+    def enable_profile(self) -> None:
+        self.profile = {"rounds": 0, "ingest_ms": 0.0, "backbone_ms": 0.0, "select_ms": 0.0}
+
+    def _mark(self, key: str, t0: float) -> float:
+        import time
+        if self.e.cuda:
+            torch.cuda.synchronize(self.e.device)
+        t1 = time.perf_counter()
+        self.profile[key] += (t1 - t0) * 1e3
+        return t1
+
+    def profile_report(self) -> dict:
+        pr = getattr(self, "profile", None)
+        if not pr or not pr["rounds"]:
+            return {}
+        return {k: (round(v / pr["rounds"], 4) if k != "rounds" else v) for k, v in pr.items()}
+
     # ---- version 2: dynamic convolutions around every sub-layer, candidate selector
     def _init_v2(self, g, vocab: int) -> None:
         """Random weights of the version-2 parts. Per layer and sub-layer (attention, MLP): ``proj`` [2 * taps * groups,
@@ -249,7 +267,14 @@ class DFlashRunner:
     def draft(self, slot: int, anchor: int, pos: int, depth: int | None = None) -> list[int]:
         cfg, m, e = self.cfg, self.model, self.e
         B = cfg.block_size
+        prof = getattr(self, "profile", None)
+        if prof is not None:
+            import time as _t
+            tp = _t.perf_counter()
         self.ingest(slot, pos)
+        if prof is not None:
+            prof["rounds"] += 1
+            tp = self._mark("ingest_ms", tp)
         self._reserve(slot, pos + B + 1)
         ids = [anchor] + [cfg.mask_token_id] * (B - 1)
         b = BatchRows.make(ids, [pos + i for i in range(B)], [slot] * B, e.device, LOGITS_ALL, 1, nsplit=1)
@@ -259,7 +284,12 @@ class DFlashRunner:
         sparse = pol is not None and self.sparse_head is not None and pol.use_sparse()
         t0 = time.perf_counter()
         if self.v2 is not None:
-            toks = self._select_v2(self._forward_v2(b), anchor)      # [anchor, d1 .. d_{B-1}]
+            hid = self._forward_v2(b)
+            if prof is not None:
+                tp = self._mark("backbone_ms", tp)
+            toks = self._select_v2(hid, anchor)                      # [anchor, d1 .. d_{B-1}]
+            if prof is not None:
+                self._mark("select_ms", tp)
             if pol is not None:
                 pol.draft_step_time(False, (time.perf_counter() - t0) * 1e3)
             nd = B - 1 if depth is None else max(0, min(B - 1, depth))
@@ -270,12 +300,16 @@ class DFlashRunner:
             logits = self.sparse_head.logits(m.last_hidden)
         else:
             logits = m.forward(b, self.kv)
+        if prof is not None:
+            tp = self._mark("backbone_ms", tp)
         if logits.is_cuda:
             idx, _ = K.argmax(logits, id_offset=e.comm.rank * m.vocab_local)
             idx = e.comm.merge_argmax(idx, _) if e.comm.size > 1 else idx
         else:
             idx = logits.float().argmax(-1)
         toks = [int(t) for t in idx.tolist()]
+        if prof is not None:
+            self._mark("select_ms", tp)
         if pol is not None:                      # the token read above waited for the device: wall time is the step time
             pol.draft_step_time(sparse, (time.perf_counter() - t0) * 1e3)
         n = B - 1 if depth is None else max(0, min(B - 1, depth))

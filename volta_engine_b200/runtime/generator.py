@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import heapq
 import itertools
+import logging
 import threading
 import time
 from collections import deque
@@ -20,6 +21,8 @@ from .sampling import SamplingParams, TokenCounts, Xoshiro256pp, logprob_of, pen
 from .spec_controller import SpecController
 from .suffix_index import SuffixIndex
 
+
+log = logging.getLogger("volta.generator")
 
 @dataclass
 class Request:
@@ -77,6 +80,7 @@ class SlotState:
     last_emit: float = 0.0
     think_open: bool = False      # currently inside the reasoning block
     think_count: int = 0          # reasoning tokens produced so far
+    last_char: str = ""           # last character of the previous reasoning token (soft close: "3." is not a sentence end)
     forced: list = field(default_factory=list)   # tokens that replace the next sampled ones
 
 
@@ -285,6 +289,8 @@ class Generator:
         s.loop = LoopDetector() if self.loop_detect else None
         s.suffix = SuffixIndex(min_k=getattr(self.opt, "spec_suffix_min", 2) if self.opt else 2) if self.speculator == "suffix" else None
         s.ctrl = SpecController() if (self.speculator != "none" and self.use_ctrl) else None
+        if s.ctrl is not None and self.opt is not None and getattr(self.opt, "spec_ctrl_log", False):
+            s.ctrl.log_decisions = True
         s.pending_bytes, s.held = b"", ""
         s.t_start, s.t_first, s.t_prefill_ms, s.t_restore_ms, s.t_store_ms = time.time(), 0.0, 0.0, 0.0, 0.0
         s.cached_tokens = 0
@@ -454,7 +460,9 @@ class Generator:
         mdl = getattr(self.engine, "model", None)
         every = getattr(mdl, "expert_adapt_every", 0) if mdl is not None else 0
         if every and self._decode_steps % every == 0:
-            mdl.rebalance_experts(getattr(mdl, "expert_max_swaps", 2))      # expert residency follows the routing heat
+            swaps = mdl.rebalance_experts(getattr(mdl, "expert_max_swaps", 2))      # expert residency follows the routing heat
+            if self.opt is not None and getattr(self.opt, "expert_log", False):
+                log.info("expert tier: step %d, %s swaps this rebalance", self._decode_steps, swaps)
         for s, t, c in zip(act, toks, cands):
             t = self._think_gate(s, t)
             s.pos += 1
@@ -476,8 +484,17 @@ class Generator:
             t = s.forced.pop(0)
         elif s.think_open and req.thinking_budget > 0 and req.think_close:
             if t != req.think_end_id and s.think_count + 1 >= req.thinking_budget:
-                s.forced = list(req.think_close)
-                t = s.forced.pop(0)
+                # The budget is spent. Soft close (reference: docs/CONFIG.md:122, thinking_soft_close): the block closes
+                # after the next token that ends a sentence (. ! ?, not a "." behind a digit) or a line, at most
+                # ``soft_close`` tokens later; 0 closes right here.
+                over = s.think_count + 1 - req.thinking_budget
+                soft = int(getattr(self.opt, "thinking_soft_close", 0) or 0) if self.opt is not None else 0
+                if over >= soft or self._ends_sentence(s, t):
+                    if over >= soft:
+                        s.forced = list(req.think_close)
+                        t = s.forced.pop(0)
+                    else:
+                        s.forced = list(req.think_close)      # this token ends the sentence: it stays, the close follows
         if s.think_open:
             if t == req.think_end_id:
                 s.think_open = False
@@ -486,7 +503,29 @@ class Generator:
                     steer.set_think_end(s.idx, s.pos + 1)
             else:
                 s.think_count += 1
+                if req.thinking_budget > 0 and s.think_count + 2 >= req.thinking_budget:
+                    try:                      # only near and past the budget: the soft close looks one character back
+                        piece = self.tok.decode_bytes([t]).decode("utf-8", "ignore")
+                        s.last_char = piece[-1:] if piece else s.last_char
+                    except Exception:
+                        pass
         return t
+
+    def _ends_sentence(self, s: SlotState, t: int) -> bool:
+        try:
+            piece = self.tok.decode_bytes([t]).decode("utf-8", "ignore").rstrip(" ")
+        except Exception:
+            return False
+        if not piece:
+            return False
+        if piece.endswith("\n"):
+            return True
+        if piece[-1] in "!?":
+            return True
+        if piece[-1] == ".":
+            before = piece[-2] if len(piece) > 1 else s.last_char
+            return not before.isdigit()
+        return False
 
     def _mtp_round(self, s: SlotState) -> int:
         t0 = time.time()

@@ -123,8 +123,13 @@ class SparseHeadPolicy:
         saving = max(0.0, self.t_full - self.t_sparse) * max(self.steps, 1.0)
         return 2.0 * saving / self.t_round if self.t_round > 0 else 0.0
 
+    force = False          # draft through the subset whenever one exists, whatever the miss rate (A/B measurement)
+
     def use_sparse(self) -> bool:
         """Whether the next round drafts through the subset."""
+        if self.force and self.built:
+            self.on = True
+            return True
         if not self.built or self.t_full <= 0 or self.scored < MIN_SCORED:
             self.on = False
             return False

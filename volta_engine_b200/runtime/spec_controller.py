@@ -3,6 +3,10 @@
 millisecond for both modes, periodic probing of the losing mode, back-off after poor rounds."""
 from __future__ import annotations
 
+import logging
+
+log = logging.getLogger("volta.spec")
+
 
 class SpecController:
     def __init__(self, alpha: float = 0.1, probe_every: int = 32, min_accept: float = 0.3):
@@ -12,6 +16,16 @@ class SpecController:
         self.accept_ema = None
         self.since_probe = 0
         self.rounds = self.proposed = self.accepted = 0
+        self.log_decisions = False       # launch option spec_ctrl_log: log every change of mode and every probe
+        self._last = None
+
+    def _decide(self, spec: bool, why: str) -> bool:
+        if self.log_decisions and (spec != self._last or why == "probe"):
+            log.info("spec controller: %s (%s; rounds %.3f tok/ms, plain %.3f tok/ms, acceptance %.2f)",
+                     "speculative round" if spec else "plain step", why, self.spec_rate or 0.0, self.plain_rate or 0.0,
+                     self.accept_ema or 0.0)
+        self._last = spec
+        return spec
 
     def _ema(self, old, x):
         return x if old is None else old + self.alpha * (x - old)
@@ -32,12 +46,12 @@ class SpecController:
     def use_speculation(self) -> bool:
         self.since_probe += 1
         if self.spec_rate is None or self.plain_rate is None:
-            return self.spec_rate is None or self.since_probe % 2 == 0   # measure both modes first
+            return self._decide(self.spec_rate is None or self.since_probe % 2 == 0, "measuring")   # measure both modes first
         better_spec = self.spec_rate >= self.plain_rate
         if self.since_probe >= self.probe_every:
             self.since_probe = 0
-            return not better_spec                                      # probe the losing mode once
-        return better_spec
+            return self._decide(not better_spec, "probe")                # probe the losing mode once
+        return self._decide(better_spec, "rate")
 
     def depth(self, max_depth: int) -> int:
         """Draft depth cut by the acceptance estimate (survival below min_accept is not worth a row)."""

@@ -224,8 +224,30 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
         model.enable_hessians(parse_layer_range(o.hessian_layers, mcfg.n_layers))
     if o.route_dump and hasattr(model, "heat"):
         from ..runtime.route_dump import RouteRecorder
-        model.route_recorder = RouteRecorder()
+        n_all = mcfg.n_layers + int(getattr(mcfg, "mtp_layers", 0) or 0)
+        # route_dump_from: only the layers from this index on (n_layers = the MTP head's block only)
+        model.route_recorder = RouteRecorder(layers=range(o.route_dump_from, n_all) if o.route_dump_from > 0 else None)
+    apply_model_switches(model, o)
     return model, hf, engine, pool_tokens
+
+
+def apply_model_switches(model, o) -> None:
+    """Launch options that turn parts of a loaded model off: ``expert_stats`` (routing histogram for the monitor),
+    ``dsa`` / ``qsa_off`` (the sparse-attention indexers: without them every row attends densely)."""
+    mcfg = model.cfg
+    if not o.expert_stats and getattr(model, "heat", None) is not None and not getattr(model, "tiers", None):
+        model.heat = None                 # (the expert tier needs the histogram and keeps it)
+    if (not o.dsa or o.qsa_off) and hasattr(model, "layers"):
+        blocks = list(model.layers) + ([model.mtp["layer"]] if getattr(model, "mtp", None) else [])
+        for L in blocks:
+            if not o.dsa and getattr(L, "dsa", None) is not None:
+                L.dsa = None
+            if o.qsa_off and getattr(L, "qsa", None) is not None:
+                L.qsa = None
+        if not o.dsa and hasattr(mcfg, "dsa"):
+            mcfg.dsa = False
+        if o.qsa_off and hasattr(mcfg, "qsa"):
+            mcfg.qsa = False
 
 
 def configure_expert_tier(model, o, rank: int = 0) -> None:
@@ -263,6 +285,9 @@ def dump_calibration(model, options, rank: int = 0) -> list[str]:
     """Writes what the capture options collected (Hessian files per site, the route dump); called at shutdown."""
     out = []
     hs = getattr(model, "hess", None)
+    drafter = getattr(model, "_drafter_for_report", None)
+    if drafter is not None and hasattr(drafter, "profile_report") and drafter.profile_report():
+        log.info("drafter rounds: %s", drafter.profile_report())
     if hs is not None and options.hessian_dir:
         out += hs.dump(options.hessian_dir, rank)
     if getattr(options, "expert_heat_file", "") and getattr(model, "tiers", None) and getattr(model, "heat", None) is not None:
@@ -318,7 +343,13 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         if hasattr(gen.drafter.cfg, "conf_threshold"):
             gen.drafter.cfg.conf_threshold = o.dspark_conf
         if o.sparse_head and hasattr(gen.drafter, "enable_sparse_head"):
-            gen.drafter.enable_sparse_head(state_path=o.sparse_head_state or None)
+            from ..runtime.sparse_head_policy import SparseHeadParams
+            pol = gen.drafter.enable_sparse_head(params=SparseHeadParams(interval=max(1, o.sparse_head_interval)),
+                                                 state_path=o.sparse_head_state or None)
+            pol.force = bool(o.sparse_head_force)
+        if o.spec_profile and hasattr(gen.drafter, "enable_profile"):
+            gen.drafter.enable_profile()
+            model._drafter_for_report = gen.drafter            # dump_calibration logs the per-round averages at shutdown
         if o.spec_cand_log:
             from ..runtime.spec_logs import CandLog
             gen.cand_log = CandLog()
