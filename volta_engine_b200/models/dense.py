@@ -79,10 +79,11 @@ class DenseConfig:
 # decode: act(gate) * up inside the gate/up linear's epilogue (VOLTA_FUSE_ACT=0 keeps the separate activation kernel)
 FUSE_ROPE = os.environ.get("VOLTA_FUSE_ROPE", "1") != "0"   # rotary embedding + KV store in the qkv decode linear's epilogue
 FUSE_GATED_ACT = os.environ.get("VOLTA_FUSE_ACT", "1") != "0"
-# decode: RMSNorm fused into the linear that consumes it (VOLTA_FUSE_NORM=1). Measured neutral on the 27B decode
-# (194.0 vs 192.5 tok/s: every CTA recomputes the row statistics, which costs what the removed kernels saved), so the
-# norm kernels stay the default.
-FUSE_PRENORM = os.environ.get("VOLTA_FUSE_NORM", "0") == "1"
+# decode: RMSNorm fused into the linear that consumes it (VOLTA_FUSE_NORM=0 turns it off). By itself it measured neutral on
+# the 27B decode (every CTA recomputes the row statistics, which costs what the removed norm kernels saved); together
+# with the rotary / cache-write epilogue in the same qkv launch a layer is five launches and the step went from 4.79 to
+# 4.69 ms (208.9 -> 213.3 tok/s), so it is the default for decode rows of the plain dense model on one GPU.
+FUSE_PRENORM = os.environ.get("VOLTA_FUSE_NORM", "1") != "0"
 
 
 def _pad_to(n: int, m: int) -> int:
@@ -428,15 +429,21 @@ class DenseModel:
                     mark[1]()
                 mark[0](f"L{li}")
             kpool, vpool = kv.layer(li)
-            qkv = L.qkv.forward_prenorm(h, delta, L.attn_norm, cfg.rms_eps, cfg.norm_bias, h2 if delta is not None else None)
+            # norm in front and rotation + cache write behind, all inside the projection's launch where the layer allows
+            fuse_rope = (FUSE_ROPE and not cfg.qk_norm and not cfg.rope_interleaved and b.pos3 is None
+                         and L.qkv.rope_ready(b.n, self.hd) and K.kv_format_of(kpool) < 2)
+            rope = (b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.rot, self.layer_theta(li)) if fuse_rope else None
+            qkv = L.qkv.forward_prenorm(h, delta, L.attn_norm, cfg.rms_eps, cfg.norm_bias, h2 if delta is not None else None,
+                                        rope=rope)
             if delta is not None:
                 h, h2 = h2, h
-            if cfg.qk_norm:
-                stride = qkv.stride(0)
-                K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
-                K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias, self.nq * self.hd)
-            K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
-                         self.layer_theta(li), cfg.rope_interleaved)
+            if not fuse_rope:
+                if cfg.qk_norm:
+                    stride = qkv.stride(0)
+                    K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
+                    K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias, self.nq * self.hd)
+                K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
+                             self.layer_theta(li), cfg.rope_interleaved)
             att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.scale,
                               window=self.layer_window(li), key_end=b.key_end, tiles=b.tiles,
                               nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)

@@ -182,11 +182,12 @@ class LinearNVFP4:
         """True when decode rows of this layer run on the tcgen05 decode linear."""
         return GEMV_KERNEL in ("auto", "tc") and self._sf_atoms is not None and self._tc_ok()
 
-    def forward_prenorm(self, resid, delta, norm_w, eps, wbias, resid_out, act=None, limit: float = 0.0):
+    def forward_prenorm(self, resid, delta, norm_w, eps, wbias, resid_out, act=None, limit: float = 0.0, rope=None):
         """Decode rows (<= 4) with the RMSNorm in front fused into the kernel: input RMSNorm(resid + delta) * (w + wbias),
-        resid + delta written to ``resid_out``; ``act`` (0 SiLU / 1 GELU) additionally applies the gated activation."""
+        resid + delta written to ``resid_out``; ``act`` (0 SiLU / 1 GELU) additionally applies the gated activation;
+        ``rope`` (the tuple of :meth:`forward_rope`) additionally rotates q / k and stores k / v from the epilogue."""
         return K.decode_w4a4(self.packed, self._sf_atoms, self.gscale, None, act=0 if act is None else 1 + act,
-                             act_limit=limit, prenorm=(norm_w, resid, delta, resid_out, eps, wbias))
+                             act_limit=limit, prenorm=(norm_w, resid, delta, resid_out, eps, wbias), rope=rope)
 
     def forward_gated(self, x, act: int = 0, limit: float = 0.0):
         """act(gate) * up of a ``interleave_gated`` projection: [rows, N/2]."""
