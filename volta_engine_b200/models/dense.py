@@ -410,7 +410,7 @@ class DenseModel:
         ok = getattr(self, "_prenorm_cached", None)
         if ok is None:
             cfg = self.cfg
-            ok = not cfg.sandwich_norm and all(
+            ok = not cfg.sandwich_norm and cfg.hidden % 256 == 0 and all(      # (the norm prologue reads K in 256-wide steps)
                 isinstance(L.qkv, LinearNVFP4) and L.qkv.tc_ready() and isinstance(L.gate_up, LinearNVFP4)
                 and L.gate_up.tc_ready() and getattr(L.gate_up, "gated", False) for L in self.layers)
             self._prenorm_cached = ok
