@@ -125,7 +125,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
         from volta_engine_b200.parallel import make_comm
-        comm = make_comm(args.comm, dev)
+        comm = make_comm(args.comm, dev, chunk_rows=max(4096, args.prefill_chunk))    # the two-shot buffers hold one prefill chunk
 
     cfg = DenseConfig.baseline_27b()
     cfg.gemm_mode = args.gemm_mode

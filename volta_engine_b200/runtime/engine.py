@@ -54,6 +54,9 @@ class Engine:
         self.cuda = self.device.type == "cuda"
         self.use_graphs = use_graphs and self.cuda
         self.prefill_chunk = prefill_chunk
+        cap = getattr(getattr(model, "comm", None), "chunk_rows", None)
+        if cap:                                    # the communicator's reduce-scatter buffers hold one chunk
+            self.prefill_chunk = min(self.prefill_chunk, int(cap))
         self.feedback = feedback
         self.comm = model.comm
         if self.cuda and hasattr(model, "link_prefetch"):

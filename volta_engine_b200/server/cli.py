@@ -386,7 +386,7 @@ def _run_rank(cfg: LaunchConfig) -> int:
     ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=3600))
     from ..runtime.tp_control import ControlChannel, follower_loop
     if cuda:
-        comm = make_comm(cfg.options.comm, device)
+        comm = make_comm(cfg.options.comm, device, chunk_rows=max(4096, int(cfg.options.prefill_chunk)))
         if hasattr(comm, "use_ll"):
             comm.use_ll = cfg.options.ar_ll
     else:
