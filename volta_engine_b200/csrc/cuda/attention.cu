@@ -47,6 +47,11 @@ struct AttnParams {
   const uint8_t* vscale;
   int* tickets;     // optional [tiles * nkv], zero between launches: the CTA that finishes a (tile, kv head) last merges
                     // the split partials itself (key-split kernel only), so no separate merge launch is needed
+  // Tree verification (optional, per row): keys at cache positions >= tree_base[row] belong to the verify block, and
+  // the row sees block key tree_base + j only when bit j of tree_mask[row] is set (its ancestors and itself); keys in
+  // front of the block are seen as usual. Blocks hold at most 64 rows.
+  const int* tree_base;
+  const unsigned long long* tree_mask;
 };
 
 VE_DEVINL void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -146,8 +151,10 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   const int kt_end = min(kt_end_all, kt_begin + tps);
 
   // this thread's two rows
-  int r_tok[2], r_head[2], r_pos[2], r_lim[2];
+  int r_tok[2], r_head[2], r_pos[2], r_lim[2], r_tb[2];
+  unsigned long long r_tm[2];
   bool r_ok[2];
+  const bool tree = p.tree_base != nullptr;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = (KS ? 0 : warp * 16) + g + h * 8;
@@ -157,6 +164,8 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
     r_head[h] = kvh * G + rr % G;
     r_pos[h] = p.pos[r_tok[h]];
     r_lim[h] = p.key_end ? p.key_end[r_tok[h]] : r_pos[h];
+    r_tb[h] = tree ? p.tree_base[r_tok[h]] : 0x7fffffff;
+    r_tm[h] = tree ? p.tree_mask[r_tok[h]] : ~0ull;
   }
 
   if (tid == 0) {
@@ -354,7 +363,8 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
         const int key = kt * kPageTok + key0 + nt * 8 + 2 * t + (e & 1);
-        const bool allow = r_ok[h] && key <= r_lim[h] && (p.window <= 0 || key > r_pos[h] - p.window);
+        bool allow = r_ok[h] && key <= r_lim[h] && (p.window <= 0 || key > r_pos[h] - p.window);
+        if (tree && key >= r_tb[h]) allow = allow && ((r_tm[h] >> ((key - r_tb[h]) & 63)) & 1ull) != 0ull;
         const float v = allow ? sacc[nt][e] * p.scale_log2 : -FLT_MAX;
         sacc[nt][e] = v;
         mx[h] = fmaxf(mx[h], v);
@@ -603,7 +613,7 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
                  const void* tile_first, const void* tile_count, int ntiles, int rows, const void* page_table,
                  int max_pages, void* kpool, void* vpool, long pool_pages, int nq, int nkv, int hd, int nsplit,
                  float scale, int window, int warps, int kv_fp8, const void* kscale, const void* vscale, void* tickets,
-                 void* status, cudaStream_t st) {
+                 const void* tree_base, const void* tree_mask, void* status, cudaStream_t st) {
   if (ntiles <= 0) return 0;
   if (nq % nkv || nsplit < 1 || nsplit > kReduceMaxSplit || kv_fp8 < 0 || kv_fp8 > 3) return cudaErrorInvalidValue;
   if (kv_fp8 >= 2 && ((hd != 128 && hd != 256) || warps == 1 || !kscale || !vscale)) return cudaErrorInvalidValue;
@@ -637,6 +647,9 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   }
   p.kscale = (const uint8_t*)kscale;
   p.vscale = (const uint8_t*)vscale;
+  p.tree_base = (const int*)tree_base;
+  p.tree_mask = (const unsigned long long*)tree_mask;
+  if ((tree_base != nullptr) != (tree_mask != nullptr) || (tree_base && warps == 8)) return cudaErrorInvalidValue;
   {
     static int stages = 0;      // VOLTA_ATTN_STAGES: page-load pipeline depth of the key-split decode kernel
     if (!stages) { const char* e = getenv("VOLTA_ATTN_STAGES"); stages = (e && e[0] == '2') ? 2 : 3; }   // 3: -8 % at 16K keys

@@ -407,6 +407,8 @@ class DenseModel:
         linears that consume them (no norm kernels on the critical path)."""
         if b.n > 4 or not FUSE_PRENORM or type(self) is not DenseModel or self.comm.size != 1 or not self.embed.is_cuda:
             return False
+        if getattr(b, "pos3", None) is not None or getattr(b, "tree", None) is not None or getattr(b, "embeds", None) is not None:
+            return False                  # rows with their own rotary positions / a tree mask / injected embeddings
         ok = getattr(self, "_prenorm_cached", None)
         if ok is None:
             cfg = self.cfg
@@ -491,7 +493,7 @@ class DenseModel:
         hs = getattr(self, "hess", None)
         if hs is not None and b.n >= hs.min_rows:      # calibration capture: the unfused path below, with its taps
             return self._attn_block_capture(li, L, x, b, kv, pbuf, hs)
-        if (FUSE_ROPE and x.is_cuda and not cfg.qk_norm and not cfg.rope_interleaved and b.pos3 is None
+        if (FUSE_ROPE and x.is_cuda and not cfg.qk_norm and not cfg.rope_interleaved and b.pos3 is None and b.tree is None
                 and isinstance(L.qkv, LinearNVFP4) and L.qkv.rope_ready(b.n, self.hd) and K.kv_format_of(kpool) < 2):
             # decode rows: rotation and cache write happen in the projection's epilogue (one launch less per layer)
             qkv = L.qkv.forward_rope(x, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.rot,
@@ -506,12 +508,16 @@ class DenseModel:
             K.rmsnorm_heads_(qkv, L.q_norm, b.n, self.nq, self.hd, stride, cfg.rms_eps, cfg.norm_bias, 0)
             K.rmsnorm_heads_(qkv, L.k_norm, b.n, self.nkv, self.hd, stride, cfg.rms_eps, cfg.norm_bias,
                              self.nq * self.hd)
-        mrope = (b.pos3, tuple(cfg.mrope_sections)) if b.pos3 is not None and cfg.mrope_sections else None
+        # rows with rotary positions of their own (b.pos stays the cache position): the multimodal sections of the model,
+        # or, for a model without them (tree verification: position = depth), one section that covers every pair
+        mrope = None
+        if b.pos3 is not None:
+            mrope = (b.pos3, tuple(cfg.mrope_sections) if cfg.mrope_sections else (self.rot // 2, 0))
         K.rope_store(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd, self.rot,
                      self.layer_theta(li), cfg.rope_interleaved, mrope=mrope)
         att = K.attention(qkv, b.pos, b.slot, kv.page_table, kpool, vpool, self.nq, self.nkv, self.hd,
                           self.scale, window=self.layer_window(li), key_end=b.key_end, tiles=b.tiles,
-                          nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws)
+                          nsplit=1 if b.tiles is not None else b.nsplit, ws=self.attn_ws, tree=b.tree)
         return self._row_parallel(L.o_proj, att, pbuf)
 
     def _attn_block_capture(self, li, L, x, b, kv, pbuf, hs):

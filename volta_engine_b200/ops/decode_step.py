@@ -305,7 +305,7 @@ def supported(model, b, kv) -> bool:
     cfg = model.cfg
     if b.n > MAXM or b.n * cfg.hidden * 2 > 40960 or b.logits != LOGITS_ALL or b.tiles is not None or b.key_end is not None:
         return False
-    if b.pos3 is not None or b.embeds is not None or b.slot is None:
+    if b.pos3 is not None or b.embeds is not None or b.slot is None or getattr(b, "tree", None) is not None:
         return False
     ok = getattr(model, "_pstep_static", None)
     if ok is None:

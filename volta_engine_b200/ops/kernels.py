@@ -212,20 +212,22 @@ class AttnWorkspace:
 
 
 def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out=None, window=0, key_end=None,
-              gate=None, tiles=None, nsplit=1, ws: AttnWorkspace | None = None):
+              gate=None, tiles=None, nsplit=1, ws: AttnWorkspace | None = None, tree=None):
     """Paged GQA attention. ``q`` is the (rotated) fused qkv buffer [rows, >= nq*hd].
 
     ``tiles`` = (tile_first, tile_count, ntiles[, wide]) int32 device tensors grouping consecutive rows of one
     sequence for prefill (<= 64 // G tokens per tile); None = one row per tile (decode / verify). ``wide`` is the same
     grouping at <= 128 // G tokens per tile: with a bf16 cache and head_dim 128 the prefill runs on the tcgen05 kernel
     (128 query rows per CTA, accumulators in TMEM), otherwise on the mma.sync kernel over the 64-row tiles.
+    ``tree`` = (base int32 [rows], mask int64 [rows]): rows of a verification tree. Keys at cache positions >= base[r]
+    are the tree's own nodes and row r sees node j only if bit j of mask[r] is set (its ancestors and itself).
     """
     rows = q.shape[0]
     fmt = kv_format_of(kpool)
     if not q.is_cuda:
         if fmt >= 2:
             kpool, vpool = _dequant_pools(kpool, vpool, hd)
-        o = ref.attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window, key_end, gate)
+        o = ref.attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window, key_end, gate, tree)
         if out is not None:
             out.copy_(o)
             return out
@@ -247,13 +249,15 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, *, out
         warps = 104                      # the scaled formats are built for the four-warp kernels
     if nsplit > 1 and ws is None:
         raise ValueError("split-KV attention needs a workspace")
-    call("attention", "plplplpppppppiipippliiiifiiipppp",
+    assert tree is None or tiles is None, "tree rows are decode / verify rows"
+    call("attention", "plplplpppppppiipippliiiifiiipppppp",
          ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(gate), gate.stride(0) if gate is not None else 0,
          ptr(ws.o_part) if ws else 0, ptr(ws.lse_part) if ws else 0, ptr(pos), ptr(slot), ptr(key_end),
          ptr(tf), ptr(tc), ntiles, rows, ptr(page_table), page_table.shape[1], ptr(kpool), ptr(vpool),
          kpool.shape[0], nq, nkv, hd, nsplit, float(scale), window, warps,
          fmt, ptr(kpool.kv_scale) if fmt >= 2 else 0, ptr(vpool.kv_scale) if fmt >= 2 else 0,
-         ptr(ws.tickets) if (ws is not None and ATTN_FUSED_MERGE) else 0, ptr(status_word(q.device)))
+         ptr(ws.tickets) if (ws is not None and ATTN_FUSED_MERGE) else 0,
+         ptr(tree[0]) if tree is not None else 0, ptr(tree[1]) if tree is not None else 0, ptr(status_word(q.device)))
     return out
 
 

@@ -98,8 +98,9 @@ def gated_act(gu, I, act=0, limit=0.0):
     return (a * u).to(gu.dtype)
 
 
-def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window=0, key_end=None, gate=None):
-    """q [rows, >= nq*hd] (already rotated). Returns [rows, nq*hd]."""
+def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window=0, key_end=None, gate=None, tree=None):
+    """q [rows, >= nq*hd] (already rotated). Returns [rows, nq*hd]. ``tree`` = (base [rows], mask [rows] int64): keys at
+    cache positions >= base[r] are visible to row r only where bit (position - base[r]) of mask[r] is set."""
     rows = q.shape[0]
     G = nq // nkv
     out = torch.zeros(rows, nq * hd, dtype=q.dtype, device=q.device)
@@ -116,6 +117,11 @@ def attention(q, pos, slot, page_table, kpool, vpool, nq, nkv, hd, scale, window
         V = vpool[pages].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, lo:n].float()
         qr = q[r, : nq * hd].reshape(nkv, G, hd).float()
         sc = torch.einsum("hgd,hkd->hgk", qr, K) * scale
+        if tree is not None:
+            tb, tm = int(tree[0][r]), int(tree[1][r])
+            keys = torch.arange(lo, n)
+            hide = (keys >= tb) & (((tm >> (keys - tb).clamp(min=0)) & 1) == 0)
+            sc = sc.masked_fill(hide[None, None, :], float("-inf"))
         pr = torch.softmax(sc, dim=-1)
         o = torch.einsum("hgk,hkd->hgd", pr, V).reshape(nq * hd)
         if gate is not None:

@@ -33,6 +33,7 @@ class BatchRows:
     pos3: torch.Tensor | None = None        # [3, n] int32 rotary positions (time, height, width) of multimodal prompts
     embeds: torch.Tensor | None = None      # [n, H] rows that replace the token embedding where embed_mask is set
     embed_mask: torch.Tensor | None = None  # [n] bool
+    tree: tuple | None = None               # (base int32 [n], mask int64 [n]): rows of a verification tree (ops.kernels.attention)
 
     @classmethod
     def make(cls, ids, pos, slots, device, logits=LOGITS_ALL, G=1, prefill=False, nsplit=1):

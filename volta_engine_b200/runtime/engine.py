@@ -215,6 +215,43 @@ class Engine:
             torch.cuda.current_stream().synchronize()
         return self.h_tok[:n].tolist()
 
+    # ------------------------------------------------------------------------------------------ tree verification
+    @property
+    def supports_tree(self) -> bool:
+        """Tree rows need a model whose only per-sequence state is the paged cache and whose attention takes the tree
+        mask: the dense GQA family with plain residuals on one rank's rows (every rank runs the same rows under TP)."""
+        m = self.model
+        return (type(m).__name__ == "DenseModel" and getattr(m.cfg, "residual", "plain") == "plain"
+                and not getattr(m.cfg, "mrope_sections", ()) and not getattr(m.cfg, "sliding_window", 0)
+                and not getattr(m.cfg, "sandwich_norm", False))
+
+    @property
+    def max_tree_nodes(self) -> int:
+        return min(64, int(self.s_tok.numel()))
+
+    def step_tree(self, slot: int, pos0: int, tree) -> list[int]:
+        """One forward over all nodes of ``tree`` (runtime.spec_tree.TokenTree) hanging off position ``pos0`` of
+        ``slot``; returns the target's greedy token after every node. ``commit_tree`` keeps one branch afterwards."""
+        n = len(tree)
+        dev = self.device
+        assert n <= self.max_tree_nodes, "the tree is larger than the engine's row buffers"
+        self.kv.reserve(slot, pos0 + n + 1)
+        b = BatchRows.make(tree.tokens, [pos0 + i for i in range(n)], [slot] * n, dev, LOGITS_ALL, 1, nsplit=self._nsplit(n))
+        rope = torch.tensor([pos0 + d for d in tree.depths], dtype=torch.int32)
+        b.pos3 = rope.unsqueeze(0).expand(3, n).contiguous().to(dev)
+        masks = [m - (1 << 64) if m >= (1 << 63) else m for m in tree.masks]          # two's complement for int64
+        b.tree = (torch.full((n,), pos0, dtype=torch.int32).to(dev), torch.tensor(masks, dtype=torch.int64).to(dev))
+        logits = self.model.forward(b, self.kv)
+        self._sample_greedy(logits, self.s_tok, self.s_val, n)
+        self.h_tok[:n].copy_(self.s_tok[:n], non_blocking=True)
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()
+        return self.h_tok[:n].tolist()
+
+    def commit_tree(self, slot: int, pos0: int, path: list[int]) -> None:
+        """Keep the accepted branch: node path[d] (stored at pos0 + path[d]) becomes position pos0 + d."""
+        self.kv.move_rows(slot, [pos0 + i for i in path], [pos0 + d for d in range(len(path))])
+
     def step_candidates(self, ids: list[int], pos: list[int], slots: list[int], journal: bool = False):
         """Like :meth:`step` but returns, per row, the merged top-16 candidates (ids, logits, lse) for the
         host sampler instead of the greedy token."""

@@ -559,7 +559,39 @@ class Generator:
 
     def _suffix_round(self, s: SlotState) -> int:
         depth = s.ctrl.depth(self.spec_depth) if s.ctrl else self.spec_depth
+        width = int(getattr(self.opt, "spec_tree", 0) or 0) if self.opt is not None else 0
+        if width > 1 and s.req.params.greedy and getattr(self.engine, "supports_tree", False):
+            # several earlier occurrences of the suffix continue differently: verify them as one tree
+            from .spec_tree import TokenTree
+            paths = s.suffix.draft_paths(depth, width)
+            if len(paths) > 1:
+                return self._tree_round(s, TokenTree.from_paths(s.next_tok, paths, self.engine.max_tree_nodes), "suffix")
+            return self._verify_round(s, paths[0] if paths else [], "suffix")
         return self._verify_round(s, s.suffix.draft(depth), "suffix")
+
+    def _tree_round(self, s: SlotState, tree, kind: str) -> int:
+        """One target forward over every node of the tree; the branch the target agrees with is kept (its cache rows
+        moved to consecutive positions), the target's token after its last node is the bonus token."""
+        t0 = time.time()
+        targets = self.engine.step_tree(s.idx, s.pos, tree)
+        path, new = tree.accept(targets)
+        self.engine.commit_tree(s.idx, s.pos, path)
+        acc = len(path) - 1
+        ms = (time.time() - t0) * 1e3
+        s.pos += acc + 1
+        s.next_tok = new[-1]
+        m = self.metrics.spec
+        m["rounds"] += 1
+        m["tree_rounds"] = m.get("tree_rounds", 0) + 1
+        m["tree_nodes"] = m.get("tree_nodes", 0) + len(tree) - 1
+        m["suffix_rounds"] += 1 if kind == "suffix" else 0
+        deepest = max(tree.depths)
+        m["proposed"] += deepest
+        m["accepted"] += acc
+        if s.ctrl:
+            s.ctrl.record_round(len(new), deepest, acc, ms)
+        self._emit(s, new)
+        return len(new)
 
     def _verify_round(self, s: SlotState, drafts: list[int], kind: str) -> int:
         """One target forward over [next token, drafts...]; keeps the longest prefix the target agrees with."""

@@ -129,6 +129,24 @@ class PagedKVCache:
         self.slot_first[slot] = upto
         return n
 
+    def move_rows(self, slot: int, src_pos: list[int], dst_pos: list[int]) -> None:
+        """Copy the cache rows of ``slot`` at positions ``src_pos`` to ``dst_pos`` in every layer (keys, values and
+        their scales): what keeps the accepted branch of a verification tree and drops the rest. All sources are read
+        before any destination is written."""
+        pairs = [(s, d) for s, d in zip(src_pos, dst_pos) if s != d]
+        if not pairs:
+            return
+        dev = self.k.device
+        sp = torch.tensor([p for p, _ in pairs], dtype=torch.long)
+        dp = torch.tensor([p for _, p in pairs], dtype=torch.long)
+        tab = self.host_table[slot].long()
+        s_page, s_off = tab[sp // PAGE].to(dev), (sp % PAGE).to(dev)
+        d_page, d_off = tab[dp // PAGE].to(dev), (dp % PAGE).to(dev)
+        for pool in (self.k, self.v, self.ks, self.vs):
+            if pool is not None:
+                rows = pool[:, s_page, :, s_off]              # gathered first: [pairs, layers, kv heads, width]
+                pool[:, d_page, :, d_off] = rows
+
     def layer(self, i: int):
         k, v = self.k[i], self.v[i]
         if self.fmt >= 2:      # the ops read the format and the scale pools off the pool tensors

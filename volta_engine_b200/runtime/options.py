@@ -19,6 +19,8 @@ _TABLE = [
     ("kv_format", str, "bf16", "KV cache element format: bf16 | fp8 | k8v4 | nvfp4"),
     ("vram_reserve_mib", int, 2048, "device memory left unallocated"),
     ("prefill_chunk", int, 2048, "rows per prefill forward"),
+    ("spec_tree", int, 0, "suffix speculator: > 1 verifies up to this many different continuations of the current suffix "
+                          "as one token tree (tree attention mask, one forward; greedy requests on the dense GQA family)"),
     ("prefill_budget_ms", float, 50.0, "prefill time slice between decode steps when sequences are decoding"),
     ("prefix_cache_mib", int, 4096, "host memory for sequence snapshots (0 disables the prefix cache)"),
     ("prefix_cache_dir", str, "", "directory of the disk tier of the prefix cache"),
