@@ -426,6 +426,62 @@ def _serve_forever(cfg: LaunchConfig, srv, engine) -> int:
     return 0
 
 
+def is_video_model_dir(model_dir: str) -> bool:
+    """A directory whose ``model_index.json`` names the MiniMaxH3Pipeline class selects the video service: no language-model
+    runtime, a job queue with one worker that owns the GPU (reference: docs/video.md:88-92)."""
+    path = os.path.join(model_dir, "model_index.json")
+    if not os.path.exists(path):
+        return False
+    with open(path) as f:
+        return json.load(f).get("_class_name") == "MiniMaxH3Pipeline"
+
+
+def build_video_service(model_dir: str, out_dir: str | None = None, device=None, max_rows: int = 0):
+    """The video pipeline of a MiniMax-H3 directory. Built: the synthetic form (``"synthetic_weights": <seed>`` in
+    ``model_index.json``, optional ``"shape": "tiny"``): every component with random weights at the published or the tiny
+    shape; the tensor mapping of the published checkpoints is not."""
+    import torch
+    from ..video import dit as D
+    from ..video.audio import AudioConfig
+    from ..video.pipeline import H3Pipeline
+    from ..video.service import VideoService
+    from ..video.text import H3TextTower
+    from ..video.vae import VaeConfig
+    with open(os.path.join(model_dir, "model_index.json")) as f:
+        idx = json.load(f)
+    if "synthetic_weights" not in idx:
+        raise NotImplementedError("minimax_h3: loading checkpoint tensors is not built (model_index.json with "
+                                  "\"synthetic_weights\": <seed> runs the pipeline with random weights)")
+    seed = int(idx["synthetic_weights"])
+    dev = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
+    if idx.get("shape", "full") == "tiny":
+        pipe = H3Pipeline.tiny(dev, seed)
+    else:
+        vae, aud, cfg = VaeConfig(), AudioConfig(), D.H3Config()
+        tok = lambda s: [1 + (b % 150000) for b in s.encode()][:512] or [1]
+        pipe = H3Pipeline(D.H3DiT(cfg, dev).init_random(seed), H3TextTower.qwen3_vl_32b(dev).init_random(seed + 7), vae, aud, tok, dev, seed)
+    return VideoService(pipe, out_dir or os.path.join(model_dir, "out"), max_rows=max_rows)
+
+
+def _serve_video(cfg) -> int:
+    import time
+    from ..video.service import serve
+    vopt = getattr(cfg, "video", None) or {}
+    svc = build_video_service(cfg.model_dir, vopt.get("out_dir"), max_rows=int(vopt.get("max_rows", 0)))
+    stop = []
+    srv = serve(svc, cfg.host, cfg.port, stop=lambda: bool(stop))
+    log.info("video service on http://%s:%d (jobs under %s)", cfg.host, srv.port, svc.out_dir)
+    try:
+        while True:
+            time.sleep(1.0)
+    except KeyboardInterrupt:
+        pass
+    stop.append(1)
+    srv.stop()
+    svc.stop()
+    return 0
+
+
 def main(argv: list[str] | None = None) -> int:
     argv = sys.argv[1:] if argv is None else argv
     cfg, args = resolve_config(argv)
@@ -438,6 +494,8 @@ def main(argv: list[str] | None = None) -> int:
     if not cfg.model_dir:
         print("volta_server: model_dir is required (flag --model-dir or key model_dir)", file=sys.stderr)
         return 2
+    if is_video_model_dir(cfg.model_dir):
+        return _serve_video(cfg)
     if cfg.tp_size > 1:
         if "RANK" not in os.environ:
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={cfg.tp_size}",

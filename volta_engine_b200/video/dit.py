@@ -197,6 +197,10 @@ class H3Block:
         q, k = rope3d(q, pos, cfg.rope_freqs), rope3d(k, pos, cfg.rope_freqs)
         if self.sp_group is not None:
             att = context_parallel_attention(q, k, v, hd ** -0.5, causal=False, group=self.sp_group[0])
+        elif x.is_cuda and hd in (64, 128):
+            # one GPU: the engine's paged attention kernel over the packed rows (head_dim 128: the tcgen05 prefill kernel)
+            from .common import full_attention
+            att = full_attention(q.reshape(rows, nh * hd), k.reshape(rows, nh * hd), v.reshape(rows, nh * hd), nh, hd).float()
         else:
             att = attention_finish(attention_partial(q, k, v, None, hd ** -0.5))
         x = x + g1 * self._sum(self.out.forward(att.reshape(rows, nh * hd)))
@@ -336,7 +340,7 @@ def denoise(model: H3DiT, prompt: torch.Tensor, grid: tuple, audio_rows: int, st
 
 
 def frames_rgb8(latents: torch.Tensor, grid: tuple, proj: torch.Tensor | None = None) -> torch.Tensor:
-    """Headless stand-in for the VAE decoder (not built): unpatchify the [frames * h * w, 24 x 2 x 2] latents to
+    """A quick look at latents without the VAE decoder (``video.vae.VideoDecoder`` is the real one): unpatchify the [frames * h * w, 24 x 2 x 2] latents to
     [frames, 2 h, 2 w, 24] and project 24 channels to RGB with ``proj`` [3, 24] (default: the first three channels);
     returns uint8 [frames, 2 h, 2 w, 3]."""
     F_, Hh, Ww = grid
