@@ -28,7 +28,7 @@ class H3TextTower:
 
     @classmethod
     def tiny(cls, device="cpu", hidden: int = 64, layers: int = 2):
-        cfg = DenseConfig(n_layers=layers, hidden=hidden, n_q=2, n_kv=1, head_dim=32, ffn=128, vocab=512, qk_norm=True, quant="bf16")
+        cfg = DenseConfig(n_layers=layers, hidden=hidden, n_q=2, n_kv=1, head_dim=64, ffn=128, vocab=512, qk_norm=True, quant="bf16")
         return cls(cfg, device)
 
     def init_random(self, seed: int = 0):
