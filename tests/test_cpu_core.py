@@ -216,3 +216,79 @@ def test_cpu_expert_service_handles_a_mailbox_request():
     want0 = 0.25 * e5.forward(xf[0:1])[0]
     want1 = 0.5 * e7.forward(xf[1:2])[0] + 0.125 * e5.forward(xf[1:2])[0]
     assert np.allclose(mb.out[0], want0.numpy(), atol=1e-6) and np.allclose(mb.out[1], want1.numpy(), atol=1e-6)
+
+
+def test_native_host_nvfp4_kernels_match_the_torch_statement():
+    """csrc/host/cpu_experts.cpp: the packed NVFP4 mat-vec against the dequantised matrix, one expert against the fp32
+    host expert (same rounding points), with and without the pinned worker pool."""
+    import ctypes
+    from volta_engine_b200._lib import hcall
+    from volta_engine_b200.quant import nvfp4 as qn
+    from volta_engine_b200.runtime.cpu_experts import HostExpert, HostExpertNVFP4, numa_node_cpus, parse_cpu_list
+    g = torch.Generator().manual_seed(2)
+    H, I = 256, 128
+    wgu, wdn = torch.randn(2 * I, H, generator=g) * 0.05, torch.randn(H, I, generator=g) * 0.05
+    (gp, gs, gg), (dp, ds, dg) = qn.quantize_nvfp4(wgu, search=False), qn.quantize_nvfp4(wdn, search=False)
+    x = torch.randn(3, H, generator=g)
+    want = x @ qn.dequantize_nvfp4(gp, gs, gg).t()
+    y = torch.empty(2 * I)
+    for pool_threads in (0, 3):
+        pool = hcall("cpu_pool_create", "ipii", pool_threads, 0, 0, 50, restype=ctypes.c_void_p) if pool_threads else None
+        try:
+            for r in range(3):
+                assert hcall("cpu_nvfp4_gemv", "pppfppii", pool, gp.data_ptr(), gs.data_ptr(), float(gg), x[r].contiguous().data_ptr(),
+                             y.data_ptr(), 2 * I, H) == 0
+                assert torch.allclose(y, want[r], atol=1e-4, rtol=1e-4), pool_threads
+            ref_e = HostExpert(qn.dequantize_nvfp4(gp, gs, gg), qn.dequantize_nvfp4(dp, ds, dg), 0, 0.0)
+            nat = HostExpertNVFP4(gp, gs, gg, dp, ds, dg, 0, 0.0)
+            out = torch.zeros(3, H)
+            for r in range(3):
+                nat.add_to(pool, x[r].contiguous(), out[r], 0.5)
+            exp = 0.5 * ref_e.forward(x)
+            # (an fp32 sum in another order can move a value across a bf16 rounding boundary: one bf16 step of slack)
+            assert torch.allclose(out, exp, atol=2e-3, rtol=2e-2) and float((out - exp).abs().mean()) < 2e-4
+        finally:
+            if pool:
+                hcall("cpu_pool_destroy", "p", pool, restype=None)
+    assert hcall("cpu_nvfp4_gemv", "pppfppii", None, gp.data_ptr(), gs.data_ptr(), 1.0, x.data_ptr(), y.data_ptr(), 4, 24) == 1
+    assert parse_cpu_list("0-3,8,10-11") == [0, 1, 2, 3, 8, 10, 11] and parse_cpu_list("") == [] and numa_node_cpus(9999) == []
+    assert hcall("cpu_has_avx2", "") in (0, 1)
+
+
+def test_cpu_expert_service_serves_native_experts_through_the_mailbox():
+    import numpy as np
+    from volta_engine_b200.quant import nvfp4 as qn
+    from volta_engine_b200.runtime.cpu_experts import CpuExpertService, HostExpert, HostExpertNVFP4
+    g = torch.Generator().manual_seed(4)
+    H, I = 128, 64
+    svc = CpuExpertService(threads=2, spin_us=50, cpus=[0])
+    refs = {}
+    for e in range(3):
+        (gp, gs, gg), (dp, ds, dg) = (qn.quantize_nvfp4(torch.randn(2 * I, H, generator=g) * 0.05, search=False),
+                                      qn.quantize_nvfp4(torch.randn(H, I, generator=g) * 0.05, search=False))
+        svc.add_expert(0, e, HostExpertNVFP4(gp, gs, gg, dp, ds, dg))
+        refs[e] = HostExpert(qn.dequantize_nvfp4(gp, gs, gg), qn.dequantize_nvfp4(dp, ds, dg))
+    mb = svc.mailbox(H, "cpu")
+    svc.start()
+    try:
+        assert svc.pool is not None
+        x = torch.randn(2, H, generator=g).to(torch.bfloat16)
+        mb.x[:2] = x
+        routes = [(0, 1, 0.7), (0, 2, 0.3), (1, 0, 1.0)]
+        for i, (row, e, w) in enumerate(routes):
+            mb.routes[i, 0], mb.routes[i, 1] = row, e
+            mb.route_w[i, 2] = w
+        mb.hdr[2:6] = [0, 2, len(routes), H]
+        mb.hdr[0] = 1
+        import time
+        t0 = time.time()
+        while int(mb.hdr[1]) != 1 and time.time() - t0 < 20:
+            time.sleep(0.005)
+        assert int(mb.hdr[1]) == 1
+        want = np.zeros((2, H), dtype=np.float32)
+        for row, e, w in routes:
+            want[row] += w * refs[e].forward(x[row:row + 1].float())[0].numpy()
+        assert np.allclose(mb.out[:2], want, atol=2e-3, rtol=2e-2)
+    finally:
+        svc.stop()
+    assert svc.pool is None

@@ -17,7 +17,9 @@ import time
 import numpy as np
 import torch
 
-from .._lib import call, ptr
+import ctypes
+
+from .._lib import call, hcall, ptr
 from ..quant import nvfp4 as qn
 
 MB_ROWS, MAX_ROUTES, OFF_ROUTES = 16, 512, 64
@@ -57,12 +59,59 @@ class HostExpert:
         return ((a * u).to(torch.bfloat16).float() @ self.dn.t()).to(torch.bfloat16).float()
 
 
+class HostExpertNVFP4:
+    """One expert kept in its packed NVFP4 form in host memory (4.5 bits per weight) and evaluated by the native host
+    kernels (csrc/host/cpu_experts.cpp: byte-shuffle decode, AVX2 + FMA dot products, rows split over the pool's pinned
+    workers). Same rounding points as :class:`HostExpert`."""
+
+    def __init__(self, gu_p, gu_s, gu_g: float, dn_p, dn_s, dn_g: float, act: int = 0, limit: float = 0.0):
+        self.gu_p, self.gu_s, self.dn_p, self.dn_s = (t.contiguous().cpu() for t in (gu_p, gu_s, dn_p, dn_s))
+        self.gu_g, self.dn_g, self.act, self.limit = float(gu_g), float(dn_g), act, limit
+        self.inter, self.hidden = self.gu_p.shape[0] // 2, self.dn_p.shape[0]
+        self.scratch = torch.empty(3 * self.inter, dtype=torch.float32)
+
+    def add_to(self, pool, x: torch.Tensor, out: torch.Tensor, weight: float) -> None:
+        """out [hidden] fp32 += weight * expert(x [hidden] fp32)."""
+        rc = hcall("cpu_nvfp4_expert", "pppfppfppiiiffp", pool, self.gu_p.data_ptr(), self.gu_s.data_ptr(), self.gu_g,
+                   self.dn_p.data_ptr(), self.dn_s.data_ptr(), self.dn_g, x.data_ptr(), out.data_ptr(), self.hidden, self.inter,
+                   self.act, float(self.limit), float(weight), self.scratch.data_ptr())
+        if rc:
+            raise ValueError("cpu_nvfp4_expert: dimensions must be multiples of 16")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.zeros(x.shape[0], self.hidden, dtype=torch.float32)
+        xf = x.float().contiguous()
+        for r in range(x.shape[0]):
+            self.add_to(None, xf[r], out[r], 1.0)
+        return out
+
+
+def numa_node_cpus(node: int) -> list[int]:
+    """CPU ids of a NUMA node from sysfs (empty when the node or the file does not exist)."""
+    try:
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            return parse_cpu_list(f.read().strip())
+    except OSError:
+        return []
+
+
+def parse_cpu_list(text: str) -> list[int]:
+    """"0-3,8,10-11" -> [0, 1, 2, 3, 8, 10, 11]."""
+    out = []
+    for part in (p.strip() for p in text.split(",") if p.strip()):
+        a, _, b = part.partition("-")
+        out += list(range(int(a), int(b or a) + 1))
+    return out
+
+
 class CpuExpertService:
-    def __init__(self, threads: int = 4, spin_us: int = 200):
-        self.experts: dict = {}          # (layer, expert id) -> HostExpert
+    def __init__(self, threads: int = 4, spin_us: int = 200, cpus: list[int] | None = None):
+        self.experts: dict = {}          # (layer, expert id) -> HostExpert | HostExpertNVFP4
         self.mailboxes: list = []
         self.seen: list = []
         self.threads, self.spin_us = threads, spin_us
+        self.cpus = list(cpus or [])
+        self.pool = None                 # native worker pool (created by start(), workers pinned to ``cpus`` round robin)
         self._stop = threading.Event()
         self._th = None
         self.served = 0
@@ -80,6 +129,10 @@ class CpuExpertService:
     def start(self) -> "CpuExpertService":
         if self._th is None:
             torch.set_num_threads(max(torch.get_num_threads(), self.threads))
+            if self.pool is None and any(isinstance(e, HostExpertNVFP4) for e in self.experts.values()):
+                arr = (ctypes.c_int * max(1, len(self.cpus)))(*self.cpus) if self.cpus else None
+                self.pool = hcall("cpu_pool_create", "ipii", self.threads, ctypes.addressof(arr) if arr is not None else 0,
+                                  len(self.cpus), int(self.spin_us), restype=ctypes.c_void_p)
             self._stop.clear()
             self._th = threading.Thread(target=self._loop, name="cpu-experts", daemon=True)
             self._th.start()
@@ -91,6 +144,9 @@ class CpuExpertService:
         if self._th is not None:
             self._th.join(timeout=5)
             self._th = None
+        if self.pool is not None:
+            hcall("cpu_pool_destroy", "p", self.pool, restype=None)
+            self.pool = None
 
     def _loop(self):
         while not self._stop.is_set():
@@ -112,13 +168,19 @@ class CpuExpertService:
         layer, rows, n, hidden = (int(v) for v in mb.hdr[2:6])
         out = np.zeros((rows, hidden), dtype=np.float32)
         x = mb.x[:rows].float()
+        xt = ot = None
         for r in range(n):                              # route order: deterministic sums
             row, e = int(mb.routes[r, 0]), int(mb.routes[r, 1])
             he = self.experts.get((layer, e))
             if he is None:
                 mb.hdr[6] = 1
                 continue
-            out[row] += float(mb.route_w[r, 2]) * he.forward(x[row:row + 1])[0].numpy()
+            if isinstance(he, HostExpertNVFP4):
+                if xt is None:
+                    xt, ot = x.contiguous(), torch.from_numpy(out)
+                he.add_to(self.pool, xt[row], ot[row], float(mb.route_w[r, 2]))
+            else:
+                out[row] += float(mb.route_w[r, 2]) * he.forward(x[row:row + 1])[0].numpy()
         mb.out[:rows] = out
 
 
@@ -140,9 +202,11 @@ class CpuExpertLayer:
              self.budget_ns, ptr(status_word(y.device)))
 
 
-def attach_cpu_experts(model, host_fraction: float, service: CpuExpertService | None = None, budget_ms: float = 2000.0):
+def attach_cpu_experts(model, host_fraction: float, service: CpuExpertService | None = None, budget_ms: float = 2000.0,
+                       native: bool = True):
     """Move the last ``host_fraction`` of every MoE layer's experts to the host service (their device weights are zeroed,
-    which makes an unnoticed route to them visible). Returns the service (started)."""
+    which makes an unnoticed route to them visible). ``native``: the experts stay packed and run on the native host
+    kernels; otherwise fp32 copies evaluated with torch. Returns the service (started)."""
     service = service or CpuExpertService()
     cfg = model.cfg
     mb = service.mailbox(cfg.hidden, model.device)
@@ -155,9 +219,15 @@ def attach_cpu_experts(model, host_fraction: float, service: CpuExpertService | 
         owner = torch.zeros(E, dtype=torch.uint8)
         for e in range(E - n_host, E):
             owner[e] = 1
-            gu = qn.dequantize_nvfp4(bank.gu_p[e].cpu(), bank.gu_s[e].cpu(), float(bank.gu_g[e]))
-            dn = qn.dequantize_nvfp4(bank.dn_p[e].cpu(), bank.dn_s[e].cpu(), float(bank.dn_g[e]))
-            service.add_expert(li, bank.e0 + e, HostExpert(gu, dn, 0 if cfg.act == "silu" else 1, cfg.act_limit))
+            act = 0 if cfg.act == "silu" else 1
+            if native and bank.gu_p[e].shape[1] % 8 == 0 and bank.dn_p[e].shape[1] % 8 == 0:
+                he = HostExpertNVFP4(bank.gu_p[e].cpu().clone(), bank.gu_s[e].cpu().clone(), float(bank.gu_g[e]),
+                                     bank.dn_p[e].cpu().clone(), bank.dn_s[e].cpu().clone(), float(bank.dn_g[e]), act, cfg.act_limit)
+            else:
+                gu = qn.dequantize_nvfp4(bank.gu_p[e].cpu(), bank.gu_s[e].cpu(), float(bank.gu_g[e]))
+                dn = qn.dequantize_nvfp4(bank.dn_p[e].cpu(), bank.dn_s[e].cpu(), float(bank.dn_g[e]))
+                he = HostExpert(gu, dn, act, cfg.act_limit)
+            service.add_expert(li, bank.e0 + e, he)
             bank.gu_p[e].zero_()
             bank.dn_p[e].zero_()
         L.cpu = CpuExpertLayer(service, mb, li, owner.to(model.device), budget_ms)

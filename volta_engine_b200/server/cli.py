@@ -173,6 +173,7 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
         from ..utils.trace import enable_layer_trace
         enable_layer_trace(model)
     configure_expert_tier(model, o, getattr(comm, "rank", 0) if comm is not None else 0)
+    configure_cpu_experts(model, o)
     from ..runtime.kv_cache import KV_FORMATS
     if o.kv_format not in KV_FORMATS:
         raise ValueError(f"kv_format '{o.kv_format}': this build has {sorted(KV_FORMATS)}")
@@ -248,6 +249,27 @@ def apply_model_switches(model, o) -> None:
             mcfg.dsa = False
         if o.qsa_off and hasattr(mcfg, "qsa"):
             mcfg.qsa = False
+
+
+def configure_cpu_experts(model, o):
+    """``cpu_experts`` = f in (0, 1): that share of every layer's routed experts lives in host memory in its packed form
+    and is computed by the host pool while the GPU runs the rest of the layer. ``cpu_expert_cpus`` ("0-7,16") pins the
+    pool's workers, ``cpu_expert_node`` takes the CPU list of a NUMA node instead, ``cpu_expert_spin_us`` is how long an
+    idle worker spins before it sleeps. Returns the service (None when off)."""
+    share = float(getattr(o, "cpu_experts", 0.0) or 0.0)
+    if share <= 0 or not hasattr(model, "layers") or not any(getattr(L, "bank", None) is not None for L in model.layers):
+        return None
+    if getattr(model, "tiers", None):
+        raise ValueError("cpu_experts and expert_cache (the host-resident tier) cannot both own the same experts")
+    from ..runtime.cpu_experts import CpuExpertService, attach_cpu_experts, numa_node_cpus, parse_cpu_list
+    cpus = parse_cpu_list(o.cpu_expert_cpus) if o.cpu_expert_cpus else (numa_node_cpus(o.cpu_expert_node) if o.cpu_expert_node >= 0 else [])
+    threads = len(cpus) if cpus else max(1, min(16, (os.cpu_count() or 2) // 2))
+    svc = CpuExpertService(threads=threads, spin_us=int(o.cpu_expert_spin_us), cpus=cpus)
+    attach_cpu_experts(model, min(share, 0.95), service=svc)
+    model.cpu_expert_service = svc
+    log.info("cpu experts: %.0f %% of every layer's experts on the host, %d worker threads%s", 100 * min(share, 0.95), threads,
+             f" pinned to {cpus}" if cpus else "")
+    return svc
 
 
 def configure_expert_tier(model, o, rank: int = 0) -> None:
