@@ -292,3 +292,37 @@ def test_cpu_expert_service_serves_native_experts_through_the_mailbox():
     finally:
         svc.stop()
     assert svc.pool is None
+
+
+def test_expert_tier_history_share_and_resident_route_bias():
+    from volta_engine_b200.models.moe import MoEConfig, MoEModel
+    cfg = MoEConfig.tiny() if hasattr(MoEConfig, "tiny") else None
+    if cfg is None:
+        pytest.skip("no tiny MoE configuration")
+    m = MoEModel(cfg, "cpu").init_random(seed=1)
+    tiers = m.enable_expert_tier(2, decay=0.5, margin=1.0, margin_add=0.0, history_pct=75, resident_bias=0.25)
+    li, tier = tiers[0]
+    L = m.layers[li]
+    E = tier.E
+    assert tier.resident() == [0, 1] and tier.history_pct == 75
+    # the router's selection bias carries the value on the resident experts only, and follows a swap
+    assert L.router_bias[m.e0:m.e0 + E].tolist() == [0.25, 0.25] + [0.0] * (E - 2)
+    counts = torch.zeros(E)
+    counts[E - 1] = 50.0                                   # one window in which the last expert is hot
+    assert tier.rebalance(counts, max_swaps=1) == 1 and (E - 1) in tier.resident()
+    bias = L.router_bias[m.e0:m.e0 + E].tolist()
+    assert bias[E - 1] == 0.25 and sum(1 for b in bias if b == 0.25) == 2
+    # long-run counts pull the decision: expert 2 has a long history, the last window favours expert 3 only slightly
+    def scenario(pct):
+        m2 = MoEModel(cfg, "cpu").init_random(seed=1)
+        t = m2.enable_expert_tier(1, decay=0.0, margin=1.0, history_pct=pct)[0][1]
+        hist = torch.zeros(t.E)
+        hist[2] = 10000.0
+        t.rebalance(hist.clone(), max_swaps=0)             # what earlier runs left (a heat file)
+        win = hist.clone()
+        win[3] += 30.0
+        win[2] += 20.0
+        t.rebalance(win, max_swaps=1)
+        return t.resident()
+    assert scenario(0) == [3]                              # windows only: the window's leader comes in
+    assert scenario(75) == [2]                             # with the long-run share the expert with the history wins

@@ -370,14 +370,22 @@ class MoEModel(DenseModel):
             y += shared.float()
         return y.to(x.dtype)
 
-    def enable_expert_tier(self, hot_slots: int, decay: float = 0.9, margin: float = 1.25, margin_add: float = 0.0):
+    def enable_expert_tier(self, hot_slots: int, decay: float = 0.9, margin: float = 1.25, margin_add: float = 0.0,
+                           history_pct: int = 0, resident_bias: float = 0.0):
         """Keep only ``hot_slots`` experts of every MoE layer in device memory; the rest stay in pinned host memory and are
-        read in place by the mat-vec kernel. Returns the tiers (``ExpertTier.rebalance`` moves experts between the two)."""
+        read in place by the mat-vec kernel. Returns the tiers (``ExpertTier.rebalance`` moves experts between the two).
+        ``history_pct``: largest share of a swap decision taken from the long-run counts; ``resident_bias``: added to the
+        router's selection score of resident experts (near ties then avoid host-memory experts)."""
         from ..runtime.expert_tier import ExpertTier
         tiers = []
         for li, L in enumerate(self.layers):
             if getattr(L, "bank", None) is not None and not L.dense_ffn:
                 L.tier = ExpertTier(L.bank, hot_slots, decay, margin, margin_add)
+                L.tier.history_pct = int(history_pct)
+                if resident_bias:
+                    if getattr(L, "router_bias", None) is None:
+                        L.router_bias = torch.zeros(self.cfg.n_experts, dtype=torch.float32, device=self.device)
+                    L.tier.set_route_bias(L.router_bias, self.e0, resident_bias)
                 tiers.append((li, L.tier))
         self.tiers = tiers
         return tiers

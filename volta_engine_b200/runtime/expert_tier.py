@@ -38,6 +38,8 @@ class ExpertTier:
         self.heat = torch.zeros(E, dtype=torch.float32)
         self._seen = torch.zeros(E, dtype=torch.float32)
         self.swaps = 0
+        self.history_pct = 0               # largest share of a swap decision taken from the long-run counts (expert_history_pct)
+        self.route_bias = None             # (device tensor [n_experts] the router adds to its selection scores, e0, value)
         for e in range(E):
             self._point_cold(e)
         for s in range(self.hot_slots):
@@ -73,21 +75,47 @@ class ExpertTier:
         """``counts``: the router's cumulative histogram over this rank's experts. Returns the number of swaps made."""
         c = counts.detach().float().cpu()
         self.heat = self.heat * self.decay + (c - self._seen)
+        window = float((c - self._seen).sum())
         self._seen = c.clone()
         if self.hot_slots == 0 or self.hot_slots == self.E:
             return 0
+        # the score a swap is decided on: the decayed windows, blended with the long-run counts (which include what a heat
+        # file of earlier runs brought in). The long-run share grows with the amount of history relative to a window and is
+        # capped at history_pct, so a cold start follows its first windows.
+        score = self.heat
+        total = float(c.sum())
+        if self.history_pct > 0 and total > 0 and float(self.heat.sum()) > 0:
+            a = (self.history_pct / 100.0) * total / (total + 16.0 * max(window, 1.0))
+            score = (1 - a) * self.heat / float(self.heat.sum()) + a * c / total
+            score = score * float(self.heat.sum())              # back in route units: margin_add keeps its meaning
         n = 0
         for _ in range(max_swaps):
             cold = [e for e in range(self.E) if self.slot_of[e] < 0]
             hot = [e for e in range(self.E) if self.slot_of[e] >= 0]
-            up = max(cold, key=lambda e: (float(self.heat[e]), -e))
-            down = min(hot, key=lambda e: (float(self.heat[e]), e))
-            if float(self.heat[up]) <= float(self.heat[down]) * self.margin + self.margin_add or float(self.heat[up]) <= 0:
+            up = max(cold, key=lambda e: (float(score[e]), -e))
+            down = min(hot, key=lambda e: (float(score[e]), e))
+            if float(score[up]) <= float(score[down]) * self.margin + self.margin_add or float(score[up]) <= 0:
                 break
             self._load(up, self.slot_of[down])
             n += 1
         self.swaps += n
+        if n:
+            self.sync_route_bias()
         return n
+
+    def set_route_bias(self, bias: torch.Tensor, e0: int, value: float) -> None:
+        """``bias`` [n_experts] fp32 on the device is what the router adds to its selection scores (the weights stay the
+        raw scores): resident experts of this rank's slice [e0, e0 + E) get ``value`` on top of ``base``, so near ties go
+        to experts that are in device memory. Follows the residency after every rebalance."""
+        self.route_bias = (bias, e0, float(value), bias[e0:e0 + self.E].clone())
+        self.sync_route_bias()
+
+    def sync_route_bias(self) -> None:
+        if self.route_bias is None:
+            return
+        bias, e0, value, base = self.route_bias
+        mask = torch.tensor([1.0 if s >= 0 else 0.0 for s in self.slot_of], dtype=torch.float32)
+        bias[e0:e0 + self.E].copy_(base + value * mask.to(bias.device))
 
     def resident(self) -> list[int]:
         return sorted(e for e in range(self.E) if self.slot_of[e] >= 0)

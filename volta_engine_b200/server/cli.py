@@ -287,7 +287,8 @@ def configure_expert_tier(model, o, rank: int = 0) -> None:
         raise ValueError("expert_cache < 1 needs routed experts in the NVFP4 bank form")
     hot = max(1, int(model.e_local * frac))
     per_expert = bank.nbytes() // max(1, bank.e_local)
-    tiers = model.enable_expert_tier(hot, margin=1.5, margin_add=float(o.expert_swap_margin))
+    tiers = model.enable_expert_tier(hot, margin=1.5, margin_add=float(o.expert_swap_margin),
+                                     history_pct=int(o.expert_history_pct), resident_bias=float(o.route_resident_bias))
     swaps = int(o.expert_swaps)
     if swaps < 0:
         swaps = max(1, (int(o.expert_swap_mib) << 20) // max(1, 2 * per_expert * max(1, len(tiers))))
