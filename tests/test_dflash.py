@@ -407,3 +407,29 @@ def test_drafter_round_profile_reports_stage_times():
     r.draft(0, 6, len(p))
     rep = r.profile_report()
     assert rep["rounds"] == 2 and rep["backbone_ms"] > 0 and rep["select_ms"] > 0 and rep["ingest_ms"] >= 0
+
+
+def test_tap_spool_records_tokens_taps_and_target_candidates(tmp_path):
+    from volta_engine_b200.runtime.spec_logs import TapSpool, TargetSpool, read_tap_spool
+    cfg, m, eng, dc = _setup()
+    p = _prompt(45, 5)
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0, "speculator": "draft", "spec_ctrl": False, "spec_depth": 3}, env={})
+    g = Generator(eng, ByteTok(), o, eos_ids=[])
+    g.drafter = D.DFlashRunner(eng, dc)
+    g.tap_spool = TapSpool(str(tmp_path / "taps.bin"), window=32)
+    g.target_spool = TargetSpool()
+    g.target_spool.enable()
+    out = g.generate(Request(p, max_tokens=10, cache_prefix=False))
+    recs = read_tap_spool(str(tmp_path / "taps.bin"))
+    assert len(recs) == 1 and recs[0]["tokens"] == p + out["tokens"]
+    r = recs[0]
+    n_all = len(p) + len(out["tokens"])
+    assert r["taps"].shape == (32, 2 * cfg.hidden) and r["first_pos"] + 32 <= n_all
+    assert float(abs(r["taps"]).sum()) > 0
+    # every recorded target row predicts the token the request really produced at that position
+    assert r["targets"] and all(t["ids"][max(range(16), key=lambda i: t["vals"][i])] == (p + out["tokens"])[t["pos"]] for t in r["targets"])
+    # and the spooling step decodes the same tokens as the plain one
+    cfg2, m2, eng2, _ = _setup()
+    plain = Generator(eng2, ByteTok(), Options.resolve({"max_slots": 2, "prefix_interval": 0}, env={}), eos_ids=[]).generate(
+        Request(p, max_tokens=10, cache_prefix=False))
+    assert plain["tokens"] == out["tokens"]

@@ -602,7 +602,18 @@ class Generator:
         pos = [s.pos + i for i in range(len(rows))]
         params = s.req.params
         jn = {"journal": True} if getattr(self.engine, "supports_journal", False) else {}
-        if params.greedy:
+        spool = getattr(self, "target_spool", None)
+        if params.greedy and spool is not None and spool.on() and kind == "drafter":
+            # the tap spool wants the target's candidates at the emitted positions: the same step with its top-16 read back
+            cands = self.engine.step_candidates(rows, pos, [s.idx] * len(rows), **jn)
+            toks = [c.ids[max(range(len(c.ids)), key=lambda i: (c.logits[i], -c.ids[i]))] for c in cands]
+            acc = 0
+            while acc < len(drafts) and toks[acc] == drafts[acc]:
+                acc += 1
+            new = drafts[:acc] + [toks[acc]]
+            for i in range(acc + 1):
+                spool.add(s.idx, pos[i] + 1, cands[i].logits, cands[i].ids)
+        elif params.greedy:
             toks = self.engine.step(rows, pos, [s.idx] * len(rows), **jn)
             # longest accepted prefix: draft i is accepted when the model's token after row i equals it
             acc = 0
@@ -758,6 +769,15 @@ class Generator:
         usage = self._usage(req, len(s.out), s.cached_tokens)
         if error:
             usage["error"] = error
+        tap_file = getattr(self, "tap_spool", None)
+        if tap_file is not None and self.drafter is not None and getattr(self.drafter, "ring", None) is not None:
+            try:                                   # offline drafter training: tokens, last taps, the target's candidates
+                end = min(s.pos, len(req.prompt) + len(s.out))
+                lo = max(0, end - min(tap_file.window, self.drafter.ring.cap))
+                tgt = self.target_spool.take(s.idx) if getattr(self, "target_spool", None) is not None else []
+                tap_file.write(list(req.prompt) + list(s.out), self.drafter.ring.rows(s.idx, lo, end) if end > lo else None, lo, tgt)
+            except Exception as e:
+                log.warning("tap spool: %s", e)
         self.engine.kv.release(s.idx)
         if self.mtp is not None:
             self.mtp.release(s.idx)

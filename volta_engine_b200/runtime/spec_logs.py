@@ -8,14 +8,19 @@ so a candidate re-ranker can be trained and tested offline. Little endian:
 ``TargetSpool``: the target's top-k candidates at the positions a round emitted, kept per slot and taken (with the request's
 taps) when the request finishes, so a drafter can be trained against the target's distribution and not its tokens alone.
 
-Reference: inc/engine/runtime/cand_log.h:10-40, inc/engine/runtime/target_spool.h:11-40.
+``TapSpool``: the file those two feed. One record per finished request, little endian:
+    int32 0xC0DE0003, n_tokens, first_pos, n_pos, width, n_targets; n_tokens int32 (prompt and output);
+    n_pos x width fp16 (the drafter taps of positions first_pos .. first_pos + n_pos - 1, width = taps x hidden);
+    n_targets x (int32 pos, 16 float32 values, 16 int32 ids)
+
+Reference: inc/engine/runtime/cand_log.h:10-40, inc/engine/runtime/target_spool.h:11-40; docs/CONFIG.md:192-193 (tap_spool).
 """
 from __future__ import annotations
 
 import struct
 import threading
 
-ROUND_MAGIC, REQUEST_MAGIC = 0xC0DE0001, 0xC0DE0002
+ROUND_MAGIC, REQUEST_MAGIC, TAPS_MAGIC = 0xC0DE0001, 0xC0DE0002, 0xC0DE0003
 CANDS = 16
 
 
@@ -116,3 +121,53 @@ class TargetSpool:
     def take(self, slot: int) -> list:
         with self._lock:
             return self._rows.pop(slot, [])
+
+
+class TapSpool:
+    """Appends a record per finished request: its tokens, the drafter taps of its last ``window`` positions and the target's
+    candidates at the positions speculation emitted."""
+
+    def __init__(self, path, window: int = 768):
+        self.path, self.window = path, max(1, int(window))
+        self._lock = threading.Lock()
+        self.records = 0
+
+    def write(self, tokens, taps, first_pos: int, targets) -> None:
+        """taps: tensor [n_pos, width] (any float type) or None; targets: [(pos, vals, ids)] from ``TargetSpool.take``."""
+        import torch
+        n_pos, width = (int(taps.shape[0]), int(taps.shape[1])) if taps is not None else (0, 0)
+        blob = [struct.pack("<Iiiiii", TAPS_MAGIC, len(tokens), int(first_pos), n_pos, width, len(targets)),
+                struct.pack(f"<{len(tokens)}i", *[int(t) for t in tokens])]
+        if n_pos:
+            blob.append(taps.detach().to("cpu", torch.float16).contiguous().numpy().tobytes())
+        for pos, vals, ids in targets:
+            v = (list(vals) + [0.0] * CANDS)[:CANDS]
+            i = (list(ids) + [-1] * CANDS)[:CANDS]
+            blob.append(struct.pack("<i16f16i", int(pos), *[float(x) for x in v], *[int(x) for x in i]))
+        with self._lock:
+            with open(self.path, "ab") as f:
+                f.write(b"".join(blob))
+            self.records += 1
+
+
+def read_tap_spool(path) -> list[dict]:
+    import numpy as np
+    out, at = [], 0
+    with open(path, "rb") as f:
+        data = f.read()
+    while at + 24 <= len(data):
+        magic, n_tok, first, n_pos, width, n_tgt = struct.unpack_from("<Iiiiii", data, at)
+        if magic != TAPS_MAGIC:
+            raise ValueError(f"tap spool: unknown record 0x{magic:08x} at byte {at}")
+        at += 24
+        toks = list(struct.unpack_from(f"<{n_tok}i", data, at))
+        at += 4 * n_tok
+        taps = np.frombuffer(data, dtype=np.float16, count=n_pos * width, offset=at).reshape(n_pos, width).copy()
+        at += 2 * n_pos * width
+        tg = []
+        for _ in range(n_tgt):
+            v = struct.unpack_from("<i16f16i", data, at)
+            tg.append({"pos": v[0], "vals": list(v[1:17]), "ids": list(v[17:33])})
+            at += 4 + 64 + 64
+        out.append({"tokens": toks, "first_pos": first, "taps": taps, "targets": tg})
+    return out

@@ -373,6 +373,11 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         if o.spec_profile and hasattr(gen.drafter, "enable_profile"):
             gen.drafter.enable_profile()
             model._drafter_for_report = gen.drafter            # dump_calibration logs the per-round averages at shutdown
+        if o.tap_spool and hasattr(gen.drafter, "ring"):
+            from ..runtime.spec_logs import TapSpool, TargetSpool
+            gen.tap_spool = TapSpool(o.tap_spool, o.tap_spool_window)
+            gen.target_spool = TargetSpool()
+            gen.target_spool.enable()
         if o.spec_cand_log:
             from ..runtime.spec_logs import CandLog
             gen.cand_log = CandLog()
