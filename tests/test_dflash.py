@@ -433,3 +433,17 @@ def test_tap_spool_records_tokens_taps_and_target_candidates(tmp_path):
     plain = Generator(eng2, ByteTok(), Options.resolve({"max_slots": 2, "prefix_interval": 0}, env={}), eos_ids=[]).generate(
         Request(p, max_tokens=10, cache_prefix=False))
     assert plain["tokens"] == out["tokens"]
+
+
+def test_drafter_hessian_capture_accumulates_block_rows(tmp_path):
+    cfg, m, eng, dc = _setup()
+    r = D.DFlashRunner(eng, dc)
+    hs = r.model.enable_hessians(None, min_rows=1)
+    p = _prompt(40, 1)
+    eng.prefill(0, p)
+    r.draft(0, 5, len(p))
+    files = hs.dump(str(tmp_path), 0)
+    assert files and all(f.endswith(".f32") for f in files)
+    import numpy as np
+    h = np.fromfile(str(tmp_path / files[0]), dtype=np.float32)
+    assert h.size > 0 and float(np.abs(h).sum()) > 0

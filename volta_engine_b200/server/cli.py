@@ -313,6 +313,9 @@ def dump_calibration(model, options, rank: int = 0) -> list[str]:
         log.info("drafter rounds: %s", drafter.profile_report())
     if hs is not None and options.hessian_dir:
         out += hs.dump(options.hessian_dir, rank)
+    dh = getattr(model, "_drafter_hessians", None)
+    if dh is not None:
+        out += dh[0].dump(dh[1], rank)
     if getattr(options, "expert_heat_file", "") and getattr(model, "tiers", None) and getattr(model, "heat", None) is not None:
         import torch
         path = options.expert_heat_file + (f".r{rank}" if rank else "")
@@ -373,6 +376,10 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         if o.spec_profile and hasattr(gen.drafter, "enable_profile"):
             gen.drafter.enable_profile()
             model._drafter_for_report = gen.drafter            # dump_calibration logs the per-round averages at shutdown
+        if o.dflash_hessian_dir and hasattr(gen.drafter, "model") and hasattr(gen.drafter.model, "enable_hessians"):
+            # calibration capture of the drafter's own projections (every block counts: its rows are few)
+            gen.drafter.model.enable_hessians(None, min_rows=1)
+            model._drafter_hessians = (gen.drafter.model.hess, o.dflash_hessian_dir)
         if o.tap_spool and hasattr(gen.drafter, "ring"):
             from ..runtime.spec_logs import TapSpool, TargetSpool
             gen.tap_spool = TapSpool(o.tap_spool, o.tap_spool_window)
