@@ -196,3 +196,22 @@ def test_small_runtime_switches():
     finally:
         lg.removeHandler(h)
     assert any("probe" in r for r in records) and any("speculative round" in r for r in records)
+
+
+def test_depth_by_rate_prefers_the_depth_with_the_best_expected_rate():
+    from volta_engine_b200.runtime.spec_controller import DepthByRate
+    d = DepthByRate(4)
+    assert d.choose(3) in (2, 3) and d.time_model() is None
+    # rounds cost 2 ms + 1 ms per row; the first draft is nearly always right, the later ones nearly never
+    for i in range(60):
+        drafted = 2 + (i % 3)
+        d.record(drafted, 1, 2.0 + 1.0 * (drafted + 1))
+    a, b = d.time_model()
+    assert abs(a - 2.0) < 1e-6 and abs(b - 1.0) < 1e-6 and d.p[0] > 0.9 and d.p[1] < 0.1
+    assert d.choose(4) == 1
+    # every draft right and rows nearly free: go deep
+    e = DepthByRate(4)
+    for i in range(60):
+        drafted = 3 + (i % 2)
+        e.record(drafted, drafted, 5.0 + 0.01 * (drafted + 1))
+    assert e.choose(3) == 4

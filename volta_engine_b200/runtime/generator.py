@@ -81,6 +81,7 @@ class SlotState:
     think_open: bool = False      # currently inside the reasoning block
     think_count: int = 0          # reasoning tokens produced so far
     last_char: str = ""           # last character of the previous reasoning token (soft close: "3." is not a sentence end)
+    depth_rate: object = None     # DepthByRate of the slot's request (spec_depth_rate)
     forced: list = field(default_factory=list)   # tokens that replace the next sampled ones
 
 
@@ -295,6 +296,7 @@ class Generator:
         s.t_start, s.t_first, s.t_prefill_ms, s.t_restore_ms, s.t_store_ms = time.time(), 0.0, 0.0, 0.0, 0.0
         s.cached_tokens = 0
         s.think_open, s.think_count, s.forced = req.think_open, 0, []
+        s.depth_rate = None
         steer = getattr(getattr(self.engine, "model", None), "steer", None)
         if steer is not None:
             pen_ids = getattr(getattr(self, "steer_cfg", None), "penalty_ids", [])
@@ -425,6 +427,11 @@ class Generator:
             s = act[0]
             if s.ctrl is None or s.ctrl.use_speculation():
                 depth = s.ctrl.depth(self.spec_depth) if s.ctrl else self.spec_depth
+                if self.opt is not None and getattr(self.opt, "spec_depth_rate", False):
+                    from .spec_controller import DepthByRate
+                    if getattr(s, "depth_rate", None) is None:
+                        s.depth_rate = DepthByRate(self.spec_depth)
+                    depth = s.depth_rate.choose(self.spec_depth)
                 n = self._verify_round(s, self.drafter.draft(s.idx, s.next_tok, s.pos, depth), "drafter")
                 if n:
                     return n
@@ -656,6 +663,8 @@ class Generator:
             m["steps"][i]["hits"] += 1 if i < acc else 0
         if s.ctrl:
             s.ctrl.record_round(len(new), len(drafts), acc, ms)
+        if kind == "drafter" and getattr(s, "depth_rate", None) is not None:
+            s.depth_rate.record(len(drafts), acc, ms)
         if kind == "drafter" and self.drafter is not None and hasattr(self.drafter, "observe_commit"):
             self.drafter.observe_commit(new)                       # sparse-head evidence, hits and misses
             if self.drafter.sparse_policy is not None:

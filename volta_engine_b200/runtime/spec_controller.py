@@ -66,3 +66,49 @@ class SpecController:
     @property
     def accept_rate(self) -> float:
         return self.accepted / self.proposed if self.proposed else 0.0
+
+
+class DepthByRate:
+    """Draft depth chosen for the most expected tokens per millisecond (launch option spec_depth_rate). The drafter's
+    recent per-position accuracy (p[k]: how often draft k was accepted when every earlier one was) gives the expected
+    tokens of a depth, E(d) = 1 + sum_{k <= d} prod_{j <= k} p[j]; the measured round times, fitted as a fixed and a
+    per-row cost, give its time. Until both have data the configured depth is used.
+    Reference: docs/CONFIG.md:136 (spec_depth_rate)."""
+
+    def __init__(self, max_depth: int, alpha: float = 0.1):
+        self.max_depth, self.alpha = max_depth, alpha
+        self.p = [0.5] * max_depth
+        self.seen = [0] * max_depth
+        self.n = self.sx = self.sy = self.sxx = self.sxy = 0.0
+
+    def record(self, drafted: int, accepted: int, ms: float) -> None:
+        for k in range(min(drafted, accepted + 1, self.max_depth)):
+            hit = 1.0 if k < accepted else 0.0
+            self.p[k] += self.alpha * (hit - self.p[k])
+            self.seen[k] += 1
+        x = drafted + 1.0                                  # verify rows of the round
+        self.n, self.sx, self.sy, self.sxx, self.sxy = self.n + 1, self.sx + x, self.sy + ms, self.sxx + x * x, self.sxy + x * ms
+
+    def time_model(self):
+        """(fixed ms, ms per row) by least squares; None until rounds of two different sizes were seen."""
+        den = self.n * self.sxx - self.sx * self.sx
+        if self.n < 4 or den <= 1e-9:
+            return None
+        b = (self.n * self.sxy - self.sx * self.sy) / den
+        a = (self.sy - b * self.sx) / self.n
+        return max(a, 0.0), max(b, 0.0)
+
+    def choose(self, default: int) -> int:
+        tm = self.time_model()
+        if tm is None or self.seen[0] < 4:
+            # no fit yet: alternate depths so that the fit gets two sizes
+            return default if int(self.n) % 2 == 0 else max(1, default - 1)
+        a, b = tm
+        best, best_rate, exp, alive = 1, -1.0, 1.0, 1.0
+        for d in range(1, self.max_depth + 1):
+            alive *= self.p[d - 1]
+            exp += alive
+            rate = exp / max(1e-6, a + b * (d + 1))
+            if rate > best_rate:
+                best, best_rate = d, rate
+        return best
