@@ -104,7 +104,7 @@ VE_DEVINL void put16(uint8_t* tile, int key, int j, const float* f) {
 // and 4-bit Hadamard-rotated values with one fp16 scale per 64 elements), 3 nvfp4 (E2M1 with one E4M3 scale per 16):
 // pages and their scales land in a staging buffer and the CTA expands them to bf16 tiles in the same layout, so the
 // arithmetic is that of a bf16 cache whatever the storage (values of the rotated format are rotated back on the way).
-template <int HD, int NW, bool KS, int FMT>
+template <int HD, int NW, bool KS, int FMT, bool TREE = false>
 __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                                                        const __grid_constant__ CUtensorMap vmap) {
   // Everything up to grid_dep_wait() reads only what earlier steps left behind (row descriptors, page table, cache pages
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(NW * 32) attn_kernel(const AttnParams p, const
   int r_tok[2], r_head[2], r_pos[2], r_lim[2], r_tb[2];
   unsigned long long r_tm[2];
   bool r_ok[2];
-  const bool tree = p.tree_base != nullptr;
+  constexpr bool tree = TREE;        // (a template parameter: the plain kernels keep their register count)
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = (KS ? 0 : warp * 16) + g + h * 8;
@@ -580,7 +580,7 @@ __global__ void attn_reduce_kernel(const float* __restrict__ o_part, const float
 #include "attention_tc.cuh"
 namespace ve {
 
-template <int HD, int NW, bool KS, int FMT>
+template <int HD, int NW, bool KS, int FMT, bool TREE = false>
 static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, int ntiles,
                        cudaStream_t st) {
   constexpr int TILE = kPageTok * HD * 2;
@@ -590,12 +590,12 @@ static int launch_attn(const AttnParams& p, const CUtensorMap& kmap, const CUten
   if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
   static int attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<HD, NW, KS, FMT, TREE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
   }
   dim3 grid(ntiles, p.nkv, p.nsplit);
-  launch_pdl(attn_kernel<HD, NW, KS, FMT>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
+  launch_pdl(attn_kernel<HD, NW, KS, FMT, TREE>, grid, dim3(NW * 32), smem, st, p, kmap, vmap);
   return (int)cudaGetLastError();
 }
 
@@ -649,7 +649,9 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   p.vscale = (const uint8_t*)vscale;
   p.tree_base = (const int*)tree_base;
   p.tree_mask = (const unsigned long long*)tree_mask;
-  if ((tree_base != nullptr) != (tree_mask != nullptr) || (tree_base && warps == 8)) return cudaErrorInvalidValue;
+  // tree rows: decode / verify tiles on a bf16 cache
+  if ((tree_base != nullptr) != (tree_mask != nullptr) || (tree_base && (warps == 8 || warps == 4 || kv_fp8 != 0)))
+    return cudaErrorInvalidValue;
   {
     static int stages = 0;      // VOLTA_ATTN_STAGES: page-load pipeline depth of the key-split decode kernel
     if (!stages) { const char* e = getenv("VOLTA_ATTN_STAGES"); stages = (e && e[0] == '2') ? 2 : 3; }   // 3: -8 % at 16K keys
@@ -687,7 +689,15 @@ int ve_attention(const void* q, long q_stride, void* out, long out_stride, const
   if (hd == HD_) {                                                               \
     if (kv_fp8 == 1) { VE_ATTN2(HD_, 1) } else if (kv_fp8 == 0) { VE_ATTN2(HD_, 0) }            \
   } else
-  if (warps == 8) { rc = launch_attn_tc<128>(p, kmap, vmap, ntiles, st); }
+#define VE_ATTN_TREE(HD_)                                                                       \
+    rc = warps == 1 ? launch_attn<HD_, 1, false, 0, true>(p, kmap, vmap, ntiles, st)            \
+                    : launch_attn<HD_, 4, true, 0, true>(p, kmap, vmap, ntiles, st);
+  if (tree_base) {
+    if (hd == 64) { VE_ATTN_TREE(64) } else if (hd == 128) { VE_ATTN_TREE(128) } else if (hd == 256) { VE_ATTN_TREE(256) }
+    else return cudaErrorInvalidValue;
+  }
+#undef VE_ATTN_TREE
+  else if (warps == 8) { rc = launch_attn_tc<128>(p, kmap, vmap, ntiles, st); }
   else if (kv_fp8 == 2 && hd == 128) { VE_ATTNQ(128, 2) }
   else if (kv_fp8 == 2 && hd == 256) { VE_ATTNQ(256, 2) }
   else if (kv_fp8 == 3 && hd == 128) { VE_ATTNQ(128, 3) }
