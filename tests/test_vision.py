@@ -65,3 +65,34 @@ def test_gpu_tower_matches_cpu():
     got = tg.forward(pre.patches, pre.grid_h, pre.grid_w).float().cpu()
     cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
     assert cos > 0.998, float(cos)
+
+
+def test_vision_tower_loads_from_a_checkpoint_directory_and_the_launcher_builds_the_frontend(tmp_path):
+    """The tower's tensors under their checkpoint names round-trip through a safetensors directory; the launcher's
+    frontend caps the image size by max_image_tokens and switches image input off at 0."""
+    import json
+    from types import SimpleNamespace
+    from volta_engine_b200.loader.safetensors import write_safetensors
+    from volta_engine_b200.models.factory import TensorSource
+    from volta_engine_b200.models.vision import VisionConfig, VisionTower
+    from volta_engine_b200.server.cli import load_vision_frontend
+    vc = {"depth": 2, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "patch_size": 16, "temporal_patch_size": 2,
+          "spatial_merge_size": 2, "out_hidden_size": 96}
+    cfg = VisionConfig.from_hf(vc)
+    assert (cfg.depth, cfg.hidden, cfg.heads, cfg.mlp, cfg.out_hidden) == (2, 64, 2, 128, 96)
+    t = VisionTower(cfg, "cpu").init_random(seed=3)
+    write_safetensors(tmp_path / "vision.safetensors", t.state_tensors())
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "qwen3_vl", "vision_config": vc, "image_token_id": 77}))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps({"patch_size": 16, "merge_size": 2, "min_pixels": 4096, "max_pixels": 1 << 20}))
+    t2 = VisionTower(cfg, "cpu").load(TensorSource(tmp_path))
+    patches = torch.randn(4 * 6, cfg.patch_dim, generator=torch.Generator().manual_seed(1))
+    assert torch.equal(t.forward(patches, 4, 6), t2.forward(patches, 4, 6))
+    hf = json.loads((tmp_path / "config.json").read_text())
+    o = SimpleNamespace(vision_dir="", max_image_tokens=16)
+    front = load_vision_frontend(str(tmp_path), hf, o, "cpu")
+    assert front is not None and front.image_token_id == 77 and front.params.max_pixels == 16 * 32 * 32
+    assert load_vision_frontend(str(tmp_path), hf, SimpleNamespace(vision_dir="", max_image_tokens=0), "cpu") is None
+    other = tmp_path / "elsewhere"
+    other.mkdir()
+    (other / "config.json").write_text(json.dumps({"model_type": "x"}))
+    assert load_vision_frontend(str(other), {"model_type": "x"}, SimpleNamespace(vision_dir=str(tmp_path), max_image_tokens=64), "cpu") is not None

@@ -32,6 +32,14 @@ class VisionConfig:
     rope_theta: float = 10000.0
     eps: float = 1e-6
 
+    @classmethod
+    def from_hf(cls, v: dict) -> "VisionConfig":
+        """``vision_config`` of a Qwen3-VL-style ``config.json``."""
+        return cls(depth=int(v.get("depth", 27)), hidden=int(v.get("hidden_size", 1152)), heads=int(v.get("num_heads", 16)),
+                   mlp=int(v.get("intermediate_size", 4304)), patch=int(v.get("patch_size", 16)),
+                   temporal=int(v.get("temporal_patch_size", 2)), merge=int(v.get("spatial_merge_size", 2)),
+                   out_hidden=int(v.get("out_hidden_size", v.get("hidden_size", 1152))), eps=float(v.get("layer_norm_eps", 1e-6)))
+
     @property
     def patch_dim(self) -> int:
         return 3 * self.temporal * self.patch * self.patch
@@ -99,6 +107,57 @@ class VisionTower:
         self.merger = {"ln_w": vec(c.hidden, 1.0), "ln_b": vec(c.hidden), "fc1": rnd(c.hidden * m, c.hidden * m),
                        "fc1_b": vec(c.hidden * m), "fc2": rnd(c.out_hidden, c.hidden * m), "fc2_b": vec(c.out_hidden)}
         return self
+
+    # ---- checkpoint tensors ("model.visual.*" of the Qwen3-VL layout; the merger's Qwen2-VL names are read too)
+    def load(self, src, prefix: str = "model.visual.") -> "VisionTower":
+        """``src``: a tensor source with ``has(name)`` / ``tensor(name, device, dtype)`` (models.factory.TensorSource).
+        Reference: src/models/qwen3_vision.cpp (tensor names), inc/engine/modules/vision.h."""
+        c, dev, bf, f32 = self.cfg, self.device, torch.bfloat16, torch.float32
+
+        def name(*cands):
+            for n in cands:
+                if src.has(prefix + n):
+                    return prefix + n
+            raise KeyError(f"vision tower: none of {[prefix + n for n in cands]} in the checkpoint")
+
+        def lin(*cands):
+            return LinearBF16(src.tensor(name(*(n + ".weight" for n in cands)), dev, bf).reshape(-1, src.tensor(
+                name(*(n + ".weight" for n in cands)), dev, bf).shape[-1]).contiguous())
+
+        def vec(*cands):
+            return src.tensor(name(*cands), dev, f32).contiguous()
+        pe = src.tensor(name("patch_embed.proj.weight"), dev, bf)               # conv [hidden, 3, t, p, p] = a linear over the patch
+        self.patch_embed = LinearBF16(pe.reshape(c.hidden, -1).contiguous())
+        self.patch_bias = vec("patch_embed.proj.bias") if src.has(prefix + "patch_embed.proj.bias") else torch.zeros(c.hidden, device=dev)
+        self.blocks = []
+        for i in range(c.depth):
+            b = f"blocks.{i}."
+            self.blocks.append({"ln1_w": vec(b + "norm1.weight"), "ln1_b": vec(b + "norm1.bias"), "qkv": lin(b + "attn.qkv"),
+                                "qkv_b": vec(b + "attn.qkv.bias"), "proj": lin(b + "attn.proj"), "proj_b": vec(b + "attn.proj.bias"),
+                                "ln2_w": vec(b + "norm2.weight"), "ln2_b": vec(b + "norm2.bias"),
+                                "fc1": lin(b + "mlp.linear_fc1", b + "mlp.fc1"), "fc1_b": vec(b + "mlp.linear_fc1.bias", b + "mlp.fc1.bias"),
+                                "fc2": lin(b + "mlp.linear_fc2", b + "mlp.fc2"), "fc2_b": vec(b + "mlp.linear_fc2.bias", b + "mlp.fc2.bias")})
+        self.merger = {"ln_w": vec("merger.norm.weight", "merger.ln_q.weight"), "ln_b": vec("merger.norm.bias", "merger.ln_q.bias"),
+                       "fc1": lin("merger.linear_fc1", "merger.mlp.0"), "fc1_b": vec("merger.linear_fc1.bias", "merger.mlp.0.bias"),
+                       "fc2": lin("merger.linear_fc2", "merger.mlp.2"), "fc2_b": vec("merger.linear_fc2.bias", "merger.mlp.2.bias")}
+        return self
+
+    def state_tensors(self, prefix: str = "model.visual.") -> dict:
+        """The tower's tensors under their checkpoint names (what ``load`` reads back)."""
+        c = self.cfg
+        out = {prefix + "patch_embed.proj.weight": self.patch_embed.weight.reshape(c.hidden, 3, c.temporal, c.patch, c.patch).cpu(),
+               prefix + "patch_embed.proj.bias": self.patch_bias.cpu()}
+        for i, b in enumerate(self.blocks):
+            q = f"{prefix}blocks.{i}."
+            for ours, theirs in (("ln1", "norm1"), ("ln2", "norm2")):
+                out[q + theirs + ".weight"], out[q + theirs + ".bias"] = b[ours + "_w"].cpu(), b[ours + "_b"].cpu()
+            for ours, theirs in (("qkv", "attn.qkv"), ("proj", "attn.proj"), ("fc1", "mlp.linear_fc1"), ("fc2", "mlp.linear_fc2")):
+                out[q + theirs + ".weight"], out[q + theirs + ".bias"] = b[ours].weight.cpu(), b[ours + "_b"].cpu()
+        m = self.merger
+        out[prefix + "merger.norm.weight"], out[prefix + "merger.norm.bias"] = m["ln_w"].cpu(), m["ln_b"].cpu()
+        for ours, theirs in (("fc1", "merger.linear_fc1"), ("fc2", "merger.linear_fc2")):
+            out[prefix + theirs + ".weight"], out[prefix + theirs + ".bias"] = m[ours].weight.cpu(), m[ours + "_b"].cpu()
+        return out
 
     def patch_positions(self, grid_h: int, grid_w: int):
         """(row, col) of every patch in merge-block order (the order ``prepare_image`` emits)."""

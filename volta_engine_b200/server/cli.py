@@ -232,6 +232,44 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     return model, hf, engine, pool_tokens
 
 
+def load_vision_frontend(model_dir: str, hf: dict, o, device):
+    """The vision tower of a multimodal checkpoint -> ``MultimodalFrontend`` (or None for a text-only model or with
+    ``max_image_tokens`` = 0). ``vision_dir`` names the directory that holds the tower (its ``config.json`` with
+    ``vision_config``, ``preprocessor_config.json`` and ``model.visual.*`` tensors) when it is not the model directory;
+    ``max_image_tokens`` caps an image's size in language-model tokens (it bounds the resize)."""
+    vdir = o.vision_dir or model_dir
+    vcfg = hf.get("vision_config")
+    if o.vision_dir:
+        with open(os.path.join(vdir, "config.json")) as f:
+            vcfg = json.load(f).get("vision_config", vcfg)
+    if not vcfg or int(o.max_image_tokens) <= 0:
+        return None
+    from ..loader.image import VisionParams
+    from ..models.factory import TensorSource
+    from ..models.vision import VisionConfig, VisionTower
+    from ..runtime.multimodal import MultimodalFrontend
+    cfg = VisionConfig.from_hf(vcfg)
+    src = TensorSource(vdir)
+    if not src.has("model.visual.patch_embed.proj.weight"):
+        log.warning("vision: %s has a vision_config but no model.visual.* tensors; image input stays off", vdir)
+        return None
+    tower = VisionTower(cfg, device).load(src)
+    pre = {}
+    for fn in ("preprocessor_config.json", "processor_config.json"):
+        if os.path.exists(os.path.join(vdir, fn)):
+            with open(os.path.join(vdir, fn)) as f:
+                pre = json.load(f)
+            pre = pre.get("image_processor", pre)
+            break
+    params = VisionParams.from_config(pre, vcfg)
+    per_token = (params.patch_size * params.merge_size) ** 2           # pixels behind one language-model token
+    params.max_pixels = min(params.max_pixels, int(o.max_image_tokens) * per_token)
+    params.min_pixels = min(params.min_pixels, params.max_pixels)
+    image_token = int(hf.get("image_token_id", hf.get("image_token_index", 151655)))
+    log.info("vision tower: %d blocks of %d, images up to %d tokens", cfg.depth, cfg.hidden, o.max_image_tokens)
+    return MultimodalFrontend(tower, params, image_token)
+
+
 def apply_model_switches(model, o) -> None:
     """Launch options that turn parts of a loaded model off: ``expert_stats`` (routing histogram for the monitor),
     ``dsa`` / ``qsa_off`` (the sparse-attention indexers: without them every row attends densely)."""
@@ -358,6 +396,10 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         cache = PrefixCache(o.prefix_cache_mib << 20, o.prefix_cache_dir or None, fingerprint=fp,
                             disk_budget_bytes=max(0, o.prefix_cache_disk_gib) << 30)
     gen = Generator(engine, tok, o, prefix_cache=cache)
+    if getattr(model.cfg, "mrope_sections", ()) or hf.get("vision_config") or o.vision_dir:
+        front = load_vision_frontend(cfg.model_dir, hf, o, engine.device)
+        if front is not None:
+            gen.mm_frontend = front              # the server accepts image parts from here on
     if o.steer != "off":
         from ..runtime.steering import SteerConfig
         if getattr(model.cfg, "residual", "plain") != "plain":
