@@ -63,6 +63,19 @@ def test_leader_and_follower_serve_requests_together(tmp_path):
     assert r0["tokens"][0] == ref[0]
 
 
+def test_tensor_parallel_block_drafter_is_mirrored_on_the_follower(tmp_path):
+    r0, r1 = _run("drafter", tmp_path)
+    assert r0["drafter_tp"] == 2 and r1["drafter_tp"] == 2
+    assert len(r0["tokens"]) == 10 and r0["rounds"] > 0 and r0["proposed"] == 3 * r0["rounds"]
+    assert r1["drafter_calls"] >= r0["rounds"]                 # every draft (and the release) ran on the follower too
+    # the verified output is the sharded target's greedy output: the same request without the drafter
+    cfg = DenseConfig.tiny(vocab=256)
+    m = DenseModel(cfg, "cpu").init_random(seed=0, search=False)
+    kv = PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 40, 2, 512, "cpu")
+    ref, _ = Engine(m, kv, use_graphs=False, prefill_chunk=32).generate([(7 * i + 3) % 255 + 1 for i in range(45)], 10)
+    assert r0["tokens"][0] == ref[0]
+
+
 def test_follower_leaving_is_detected_before_the_next_launch(tmp_path):
     r0, r1 = _run("follower_dies", tmp_path)
     assert r1["left"] is True

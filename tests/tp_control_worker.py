@@ -57,6 +57,29 @@ def main():
             lead.shutdown()
         else:
             result["commands"] = follower_loop(eng, chan)
+    elif mode == "drafter":
+        # tensor-parallel block drafter: the leader's generator drafts through LeaderDrafter, the follower mirrors it
+        from volta_engine_b200.runtime import dflash_runner as DF
+        from volta_engine_b200.runtime.tp_control import LeaderDrafter
+        dc = DF.DFlashConfig(block_size=4, n_layers=2, hidden=cfg.hidden, n_q=cfg.n_q, n_kv=cfg.n_kv, head_dim=cfg.head_dim,
+                             ffn=cfg.ffn, target_layer_ids=(0, cfg.n_layers - 1), sliding_window=64, rope_theta=1e4,
+                             mask_token_id=255, tap_cap=64, quant="bf16")
+        runner = DF.DFlashRunner(eng, dc)
+        eng.drafter = runner
+        result["drafter_tp"] = runner.model.comm.size
+        if rank == 0:
+            lead = LeaderEngine(eng, chan)
+            o = Options.resolve({"max_slots": 2, "prefix_interval": 0, "speculator": "draft", "spec_ctrl": False, "spec_depth": 3}, env={})
+            gen = Generator(lead, ByteTok(), o, eos_ids=[])
+            gen.drafter = LeaderDrafter(runner, lead)
+            prompt = [(7 * i + 3) % 255 + 1 for i in range(45)]
+            a = gen.generate(Request(prompt=prompt, max_tokens=10, cache_prefix=False))
+            result.update(tokens=a["tokens"], rounds=gen.metrics.spec["rounds"], proposed=gen.metrics.spec["proposed"])
+            lead.shutdown()
+        else:
+            seen = []
+            result["commands"] = follower_loop(eng, chan, on_command=lambda n, a, k: seen.append(n))
+            result["drafter_calls"] = sum(1 for n in seen if n.startswith("drafter."))
     elif mode == "follower_dies":
         # the follower leaves between steps (no kernel or collective in flight); the leader must notice on the host
         if rank == 0:

@@ -92,7 +92,9 @@ class DFlashRunner:
         dcfg = DenseConfig(n_layers=cfg.n_layers, hidden=cfg.hidden, n_q=cfg.n_q, n_kv=cfg.n_kv, head_dim=cfg.head_dim, ffn=cfg.ffn,
                            vocab=tc.vocab, rope_theta=cfg.rope_theta, rms_eps=cfg.rms_eps, qk_norm=True,
                            sliding_window=cfg.sliding_window, quant=cfg.quant)
-        self.model = DenseModel(dcfg, dev).init_random(seed=seed)
+        # tensor parallel like the target: heads and MLP columns split over the ranks, every rank runs the same calls
+        comm = getattr(tgt, "comm", None)
+        self.model = DenseModel(dcfg, dev, comm if (comm is not None and getattr(comm, "size", 1) > 1) else None).init_random(seed=seed)
         self.model.embed, self.model.lm_head = tgt.embed, tgt.lm_head            # shared with the target
         self.model.vocab_local = tgt.vocab_local
         g = torch.Generator(device=dev).manual_seed(seed + 1)

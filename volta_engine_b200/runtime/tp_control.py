@@ -172,6 +172,27 @@ class LeaderEngine:
         self._publish(("stop", (), {}))
 
 
+_DRAFTER_CALLS = ("draft", "release", "ingest", "observe_prompt", "observe_commit")
+
+
+class LeaderDrafter:
+    """A tensor-parallel block drafter on rank 0: every call that runs the drafter's model (or changes its per-slot state)
+    is published first, so the follower ranks make the same call on their shard (``follower_loop`` routes names that
+    start with ``drafter.`` to ``engine.drafter``)."""
+
+    def __init__(self, drafter, leader: LeaderEngine):
+        self._d, self._lead = drafter, leader
+
+    def __getattr__(self, name):
+        attr = getattr(self._d, name)
+        if name in _DRAFTER_CALLS:
+            def call(*a, **k):
+                self._lead._publish(("drafter." + name, a, k))
+                return attr(*a, **k)
+            return call
+        return attr
+
+
 def follower_loop(engine, chan: ControlChannel, on_command=None) -> int:
     """Mirror the leader's calls until it says stop. Returns the number of commands executed."""
     snaps: dict[int, dict] = {}
@@ -190,6 +211,8 @@ def follower_loop(engine, chan: ControlChannel, on_command=None) -> int:
             engine.kv.load_rows(a[0], snaps[k["hid"]])
         elif name.startswith("kv."):
             getattr(engine.kv, name[3:])(*a, **k)
+        elif name.startswith("drafter."):
+            getattr(engine.drafter, name[8:])(*a, **k)
         else:
             getattr(engine, name)(*a, **k)
         n += 1

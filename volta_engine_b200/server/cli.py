@@ -406,8 +406,16 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
             raise ValueError("steer: the residual edit is built for the plain-residual decoder families")
         gen.steer_cfg = SteerConfig(o, model.cfg.n_layers, tok)
         model.steer = gen.steer_cfg.tables(model.cfg.hidden, o.max_slots, engine.device)
-    if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size == 1:
-        gen.drafter = load_drafter(engine, cfg.draft_model_dir)
+    if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size > 1 and not o.draft_tp:
+        log.warning("draft_tp = false: the vocabulary-sharded head needs every rank in a draft step, so the drafter stays off")
+    if o.speculator == "draft" and cfg.draft_model_dir and (cfg.tp_size == 1 or o.draft_tp):
+        if chan is not None:                       # tensor parallel: the followers hold their shard (see _run_rank)
+            from ..runtime.tp_control import LeaderDrafter
+            raw = load_drafter(engine._e, cfg.draft_model_dir)
+            engine._e.drafter = raw
+            gen.drafter = LeaderDrafter(raw, engine)
+        else:
+            gen.drafter = load_drafter(engine, cfg.draft_model_dir)
         if hasattr(gen.drafter.cfg, "conf_threshold"):
             gen.drafter.cfg.conf_threshold = o.dspark_conf
         if o.sparse_head and hasattr(gen.drafter, "enable_sparse_head"):
@@ -479,6 +487,9 @@ def _run_rank(cfg: LaunchConfig) -> int:
         srv, gen, engine = build_server(cfg, device, comm, chan, agree)
         return _serve_forever(cfg, srv, engine)
     _, _, engine, _ = build_engine(cfg, device, comm, agree)
+    o = cfg.options
+    if o.speculator == "draft" and cfg.draft_model_dir and o.draft_tp:
+        engine.drafter = load_drafter(engine, cfg.draft_model_dir)      # this rank's shard of the block drafter
     follower_loop(engine, chan)
     return 0
 
