@@ -346,3 +346,37 @@ def test_moe_gguf_file_with_stacked_experts_keeps_the_blocks_and_matches_its_saf
     assert torch.equal(moe_layer.bank.dequant("gu", 2), want_gu)
     want_dn = gq.dequantize(gq.quantize(src["down"], gq.GGML_Q8_0), gq.GGML_Q8_0, src["down"].shape[1])
     assert torch.equal(moe_layer.bank.dequant("dn", 2), want_dn)
+
+
+def test_loader_options_take_experts_and_dense_tensors_from_other_directories(tmp_path):
+    """nvfp4_experts / nvfp4_expert_layers / nvfp4_dense_dir: an overlay of checkpoints. The experts of layer 1 come from a
+    second directory (other weights), a dense tensor from a third; the model then differs from the plain load exactly
+    there. nvfp4_dense = head quantises the head."""
+    from volta_engine_b200.loader.safetensors import SafeTensorsRepo
+    from volta_engine_b200.models.factory import OverlaySource, TensorSource, parse_layer_set
+    from volta_engine_b200.ops.linear import LinearBF16
+    base, other, dense = tmp_path / "base", tmp_path / "experts", tmp_path / "dense"
+    for d in (base, other, dense):
+        d.mkdir()
+    _moe_dir(base, mla=False)
+    repo = SafeTensorsRepo(base)
+    g = torch.Generator().manual_seed(99)
+    swapped = {n: (torch.randn(repo.load(n).shape, generator=g) * 0.05).to(torch.bfloat16) for n in repo.names() if ".mlp.experts." in n}
+    write_safetensors(other / "model.safetensors", swapped)
+    o_new = (torch.randn(256, 256, generator=g) * 0.05).to(torch.bfloat16)
+    write_safetensors(dense / "model.safetensors", {"model.layers.0.self_attn.o_proj.weight": o_new})
+    plain, _ = load_model(base, "cpu")
+    mixed, _ = load_model(base, "cpu", overlay={"nvfp4_experts": str(other), "nvfp4_expert_layers": "1", "nvfp4_dense_dir": str(dense)},
+                          nvfp4_dense="head")
+    assert torch.equal(plain.layers[0].bank.gu_p, mixed.layers[0].bank.gu_p)              # layer 0 experts untouched
+    assert not torch.equal(plain.layers[1].bank.gu_p, mixed.layers[1].bank.gu_p)          # layer 1 experts from the other directory
+    assert not torch.equal(plain.layers[0].o_proj.packed, mixed.layers[0].o_proj.packed)  # the calibrated dense tensor
+    assert torch.equal(plain.layers[1].o_proj.packed, mixed.layers[1].o_proj.packed)
+    assert isinstance(plain.lm_head, LinearBF16) and not isinstance(mixed.lm_head, LinearBF16)
+    assert mixed.lm_head.nbytes() < plain.lm_head.weight.numel() * 2 / 3
+    assert parse_layer_set("3-5,9", 12) == {3, 4, 5, 9} and 7 in parse_layer_set("", 12)
+    kv = PagedKVCache(mixed.cfg.n_layers, mixed.nkv, mixed.cfg.head_dim, 8, 2, 256, "cpu")
+    out, _ = Engine(mixed, kv, use_graphs=False, prefill_chunk=16).generate(list(range(20)), 3)
+    assert len(out) == 3
+    src = OverlaySource(TensorSource(base), [])
+    assert src.has("model.norm.weight") and src.repo is not None

@@ -103,6 +103,73 @@ class TensorSource:
         return LinearGGUF(raw, info.ggml_type, n1 - n0, k1 - k0)
 
 
+class OverlaySource:
+    """A tensor source assembled from several checkpoints: names that match a rule come from that rule's source, every
+    other name from the primary one. Rules are (predicate(name) -> bool, TensorSource), first match wins. This is how
+    the launch options that take parts of a model from other directories work (``nvfp4_experts``: routed experts from an
+    NVFP4 checkpoint; ``mtp_head_dir``: the MTP head from another checkpoint; ``nvfp4_dense_dir``: calibrated dense
+    tensors). Reference: docs/CONFIG.md:72-80 (the reference's loader options of the same names)."""
+
+    def __init__(self, primary: TensorSource, rules: list):
+        self.primary, self.rules = primary, list(rules)
+
+    def source_for(self, name: str) -> TensorSource:
+        for pred, src in self.rules:
+            if pred(name) and (src.has(name) or src.has(name + ".weight") or src.has(name + ".weight_packed")
+                               or any(src.has(name + s) for s in ("gate_proj.weight", "gate_proj.weight_packed", "0.gate_proj.weight",
+                                                                  "0.gate_proj.weight_packed"))):
+                return src
+        return self.primary
+
+    def has(self, name: str) -> bool:
+        return self.source_for(name).has(name)
+
+    def tensor(self, name: str, device=None, dtype=None):
+        return self.source_for(name).tensor(name, device, dtype)
+
+    def linear(self, base: str, *a, **k):
+        return self.source_for(base).linear(base, *a, **k)
+
+    def __getattr__(self, name):                   # gguf / repo / names / arch of the primary checkpoint
+        return getattr(self.primary, name)
+
+
+def parse_layer_set(text: str, n_layers: int) -> set:
+    """"3-10,12" -> {3..10, 12}; empty -> every layer."""
+    if not text:
+        return set(range(n_layers + 8))
+    out = set()
+    for part in (p.strip() for p in text.split(",") if p.strip()):
+        a, _, b = part.partition("-")
+        out |= set(range(int(a), int(b or a) + 1))
+    return out
+
+
+def overlay_from_options(primary: TensorSource, hf: dict, nvfp4_experts: str = "", nvfp4_expert_layers: str = "",
+                         mtp_head_dir: str = "", mtp_nvfp4: bool = False, nvfp4_dense_dir: str = ""):
+    """The tensor source the loader options describe (the primary source itself when none of them is set)."""
+    import re as _re
+    n_layers = int(hf.get("num_hidden_layers", 0))
+    layer_of = _re.compile(r"model\.layers\.(\d+)\.")
+    rules = []
+
+    def layer(name):
+        m = layer_of.match(name)
+        return int(m.group(1)) if m else -1
+    if mtp_head_dir:
+        mtp_src = TensorSource(mtp_head_dir)
+        rules.append((lambda n: layer(n) >= n_layers, mtp_src))
+    if nvfp4_experts:
+        ex_src = TensorSource(nvfp4_experts)
+        layers = parse_layer_set(nvfp4_expert_layers, n_layers)
+        rules.append((lambda n: ".mlp.experts." in n and layer(n) in layers and layer(n) < n_layers, ex_src))
+        if mtp_nvfp4 and not mtp_head_dir:
+            rules.append((lambda n: layer(n) >= n_layers, ex_src))
+    if nvfp4_dense_dir:
+        rules.append((lambda n: ".mlp.experts." not in n, TensorSource(nvfp4_dense_dir)))
+    return OverlaySource(primary, rules) if rules else primary
+
+
 def load_dense_weights(model: DenseModel, src: TensorSource, gemm_mode="w4a16", quantize=None) -> DenseModel:
     """Fill a DenseModel from a checkpoint with the usual decoder names (``model.layers.N.self_attn.q_proj`` ...);
     this rank keeps its tensor-parallel shard (q/k/v/gate/up column-split, o/down row-split, vocabulary rows)."""
@@ -154,8 +221,11 @@ def load_dense_weights(model: DenseModel, src: TensorSource, gemm_mode="w4a16", 
     return model
 
 
-def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantize=None, prefer=None):
-    """-> (model, hf_config dict). Raises for model types this build has no pipeline for."""
+def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantize=None, prefer=None, overlay: dict | None = None,
+               nvfp4_dense: str = ""):
+    """-> (model, hf_config dict). Raises for model types this build has no pipeline for. ``overlay``: keyword arguments of
+    :func:`overlay_from_options` (parts of the model taken from other directories); ``nvfp4_dense``: comma list of dense
+    groups quantised to NVFP4 at load beyond the default (``head``, or ``all``)."""
     d = Path(model_dir)
     hf = json.loads((d / "config.json").read_text())
     if "text_config" in hf and "num_hidden_layers" not in hf:
@@ -173,7 +243,10 @@ def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantiz
         return load_dense_weights(model, src, gemm_mode, quantize), hf
     if mt in MOE_TYPES or mt in MLA_TYPES:
         from .moe_loader import load_moe_family
-        return load_moe_family(hf, src, device, comm, gemm_mode, quantize), hf
+        if overlay:
+            src = overlay_from_options(src, hf, **overlay)
+        groups = {g.strip() for g in nvfp4_dense.split(",") if g.strip()}
+        return load_moe_family(hf, src, device, comm, gemm_mode, quantize, nvfp4_head=bool(groups & {"head", "all"})), hf
     raise NotImplementedError(f"model_type {mt!r} has no pipeline in this build")
 
 

@@ -74,6 +74,8 @@ def _load_bank_gguf(src: TensorSource, prefix: str, cfg, e0: int, e_local: int, 
 
 
 def _load_bank(src: TensorSource, prefix: str, cfg, e0: int, e_local: int, dev) -> ExpertBank:
+    if hasattr(src, "source_for"):                 # an overlay: this layer's experts may live in another checkpoint
+        src = src.source_for(prefix + "experts.")
     bank = _load_bank_gguf(src, prefix, cfg, e0, e_local, dev)
     if bank is not None:
         return bank
@@ -164,7 +166,7 @@ def _load_mla(model, src, L, p, kw):
     L.q_norm = L.k_norm = None
 
 
-def load_moe_family(hf: dict, src: TensorSource, device, comm, gemm_mode="w4a16", quantize=None):
+def load_moe_family(hf: dict, src: TensorSource, device, comm, gemm_mode="w4a16", quantize=None, nvfp4_head: bool = False):
     cfg = moe_config_from_hf(hf)
     cfg.gemm_mode = gemm_mode
     mla = isinstance(cfg, MLAConfig)
@@ -194,7 +196,12 @@ def load_moe_family(hf: dict, src: TensorSource, device, comm, gemm_mode="w4a16"
     hi = min(cfg.vocab, lo + model.vocab_local)
     if hi > lo:
         head[: hi - lo] = full[lo:hi]
-    model.lm_head = LinearBF16(head.to(dev))
+    # nvfp4_dense = head: the head as NVFP4 (a quarter of the bytes a decode step streams for it)
+    if nvfp4_head and cfg.hidden % 128 == 0 and model.vocab_local % 128 == 0:
+        from ..ops.linear import LinearNVFP4
+        model.lm_head = LinearNVFP4.from_dense(head.float().to(dev), gemm_mode, search=True).prepare()
+    else:
+        model.lm_head = LinearBF16(head.to(dev))
     if mla and cfg.mtp_layers and src.has(f"model.layers.{cfg.n_layers}.eh_proj.weight"):
         p = f"model.layers.{cfg.n_layers}."
         block = load_layer(cfg.n_layers)
