@@ -117,3 +117,70 @@ def test_gpu_kernels_match_cpu_semantics():
     lw = tc.penalize(torch.zeros(6, 100), pos, slot, id0=5)
     lg = tg.penalize(torch.zeros(6, 100, device=dev), pos.to(dev), slot.to(dev), id0=5).cpu()
     assert torch.equal(lg, lw)
+
+
+def test_request_time_probe_builds_directions_gates_and_steers(tmp_path):
+    """runtime.steer_probe on a tiny dense model: states are read at the band layers for every opening, the gate places
+    the prompt between the two groups, a fired gate installs clamps (count per layer = directions, hedge adds one, push adds
+    one), a shut gate installs nothing; through the scheduler a probed request reports its scores and still decodes."""
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime import steer_probe as sp
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.generator import Generator, Request
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.runtime.options import Options
+
+    class Tok:
+        eos_ids = [0]
+
+        def decode_bytes(self, ids, skip_special=False):
+            return bytes(i & 0xFF for i in ids)
+
+        def encode(self, text, allow_special=True):
+            return [1 + (b % 250) for b in text.encode()]
+    cfg = DenseConfig.tiny(vocab=256)
+    m = DenseModel(cfg, "cpu").init_random(seed=0)
+    eng = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 40, 2, 512, "cpu"), use_graphs=False, prefill_chunk=32)
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0, "steer": "on", "steer_layers": "0-last", "steer_band": "0-last",
+                         "steer_directions": 2, "steer_hedge_strength": 0.5, "steer_gate_threshold": "-100"}, env={})
+    scfg = st.SteerConfig(o, cfg.n_layers, Tok())
+    m.steer = scfg.tables(cfg.hidden, 2, "cpu")
+    ps = sp.ProbeSettings.from_options(o, cfg.n_layers, scfg.first, scfg.last)
+    assert ps.directions == 2 and ps.band == (0, cfg.n_layers - 1) and ps.gate_threshold == -100.0 and ps.edit_strength == sp.AUTO_STRENGTH
+    prompt = [5 + (3 * i) % 200 for i in range(30)]
+    eng.prefill(0, prompt)
+    states = sp.collect_states(eng, m.steer, 0, len(prompt), prompt[-1], ps.openings, Tok(), ps.band)
+    assert set(states) == {"prompt", "accept", "decline", "plain", "hedged"}
+    assert set(states["accept"]) == set(range(cfg.n_layers)) and states["accept"][0].shape == (4, cfg.hidden)
+    edits, scores = sp.build_edits(states, ps, cfg.hidden, cfg.n_layers)
+    assert scores["fired"] and edits is not None
+    per = {}
+    for e in edits.entries:
+        per[e.layer] = per.get(e.layer, 0) + 1
+        assert abs(float(e.vec.norm()) - 1.0) < 1e-4 and e.kind in (st.STEER_CLAMP, st.STEER_CLAMP_KEEP)
+    assert all(v == 3 for v in per.values())                    # first direction + one extra + the hedge clamp
+    ps.gate_threshold = 100.0
+    assert sp.build_edits(states, ps, cfg.hidden, cfg.n_layers)[0] is None
+    ps.push = -0.5                                              # a push does not wait for the gate
+    pushed, _ = sp.build_edits(states, ps, cfg.hidden, cfg.n_layers)
+    assert pushed is not None and all(e.kind == st.STEER_ADD and e.par < 0 for e in pushed.entries)
+    # the extra directions are orthogonal to the first one
+    ex = sp.extra_directions(states["accept"][1], states["decline"][1], st.probe_axis(states["accept"][1], states["decline"][1]).dir, 2)
+    assert ex and all(abs(float(d @ st.probe_axis(states["accept"][1], states["decline"][1]).dir)) < 1e-4 for d in ex)
+    # openings file
+    f = tmp_path / "open.txt"
+    f.write_text("accept: Absolutely\naccept: Gladly\ndecline: No.\nnoise line\n")
+    op = sp.load_openings(str(f))
+    assert op["accept"] == ["Absolutely", "Gladly"] and op["decline"] == ["No."] and op["plain"] == sp.DEFAULT_OPENINGS["plain"]
+    # through the scheduler
+    eng2 = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 40, 2, 512, "cpu"), use_graphs=False, prefill_chunk=32)
+    g = Generator(eng2, Tok(), o, eos_ids=[])
+    g.steer_cfg = scfg
+    g.probe_cfg = sp.ProbeSettings.from_options(o, cfg.n_layers, scfg.first, scfg.last)
+    plain = g.generate(Request(prompt, max_tokens=6, cache_prefix=False))
+    assert "steer_probe" not in plain["usage"]
+    probed = g.generate(Request(prompt, max_tokens=6, cache_prefix=False, **scfg.for_request({"steer_probe": True})))
+    sc = probed["usage"]["steer_probe"]
+    assert sc["fired"] and sc["edits"] > 0 and len(probed["tokens"]) == 6
+    again = g.generate(Request(prompt, max_tokens=6, cache_prefix=False))
+    assert again["tokens"] == plain["tokens"]                   # the slot's edits are gone with the request

@@ -49,6 +49,7 @@ class Request:
     steer: object = None          # runtime.steering.SteerFile applied to this request's slot
     steer_scale: float = 1.0
     steer_scope: int | None = None
+    steer_probe: bool = False     # probe this prompt with the forced openings and clamp the declining direction (runtime.steer_probe)
     think_penalty: float = 0.0    # logit taken from the first tokens of reflection markers inside the reasoning block
     id: int = 0
     cancelled: bool = False
@@ -82,6 +83,7 @@ class SlotState:
     think_count: int = 0          # reasoning tokens produced so far
     last_char: str = ""           # last character of the previous reasoning token (soft close: "3." is not a sentence end)
     depth_rate: object = None     # DepthByRate of the slot's request (spec_depth_rate)
+    probe_scores: dict | None = None   # what the request-time probe measured (reported in the usage)
     forced: list = field(default_factory=list)   # tokens that replace the next sampled ones
 
 
@@ -373,6 +375,8 @@ class Generator:
             if self.cache is not None and s.req.cache_prefix and (end in self._snapshot_points(s)):
                 self._store_prefix(s, end)
             if last:
+                if s.req.steer_probe and getattr(self, "probe_cfg", None) is not None:
+                    tok = self._probe_steer(s, tok)
                 s.next_tok = tok
                 s.phase = "decode"
                 s.t_prefill_ms += (time.time() - t0) * 1e3
@@ -517,6 +521,34 @@ class Generator:
                     except Exception:
                         pass
         return t
+
+    def _probe_steer(self, s: SlotState, tok: int) -> int:
+        """Request-time probe (runtime.steer_probe): the forced openings run behind the prompt, the clamps they call for are
+        installed beside the request's control vectors, and the prompt's last row runs again so that the first token
+        already comes from the edited stream. Returns that token."""
+        from .steer_probe import probe_request
+        from .steering import SteerFile
+        tables = getattr(getattr(self.engine, "model", None), "steer", None)
+        req = s.req
+        if tables is None or len(req.prompt) < 1:
+            return tok
+        edits, scores = probe_request(self.engine, tables, self.tok, s.idx, req.prompt, self.probe_cfg)
+        s.probe_scores = scores
+        if edits is None:
+            return tok
+        base = req.steer
+        merged = SteerFile(hidden=edits.hidden, layers=edits.layers, scope=edits.scope, scale=base.scale if base is not None else 1.0,
+                           entries=(list(base.entries) if base is not None else []) + list(edits.entries))
+        pen_ids = getattr(getattr(self, "steer_cfg", None), "penalty_ids", [])
+        try:
+            tables.set_slot(s.idx, merged, prompt_len=len(req.prompt), scale=req.steer_scale, scope=edits.scope,
+                            penalty_ids=pen_ids if req.think_penalty > 0 else (), penalty=req.think_penalty)
+        except ValueError:                         # more than four edits on a layer: the probe's edits give way
+            scores["edits"] = 0
+            return tok
+        if req.steer is None:
+            req.steer = merged                     # the slot is steered from here on (think-end tracking, clear at finish)
+        return self.engine.step([req.prompt[-1]], [len(req.prompt) - 1], [s.idx])[0]
 
     def _ends_sentence(self, s: SlotState, t: int) -> bool:
         try:
@@ -776,6 +808,9 @@ class Generator:
         if reason in self.metrics.finished:
             self.metrics.finished[reason] += 1
         usage = self._usage(req, len(s.out), s.cached_tokens)
+        if getattr(s, "probe_scores", None):
+            usage["steer_probe"] = s.probe_scores
+            s.probe_scores = None
         if error:
             usage["error"] = error
         tap_file = getattr(self, "tap_spool", None)

@@ -336,4 +336,6 @@ class SteerConfig:
             out["steer_scope"] = parse_steer_scope(fields["steer_scope"])
         if "think_penalty" in fields:
             out["think_penalty"] = float(fields["think_penalty"])
+        if fields.get("steer_probe"):
+            out["steer_probe"] = True
         return out

@@ -48,9 +48,10 @@ IMAGE_MARK = "<|vision_start|><|image_pad|><|vision_end|>"
 
 def steer_fields(body: dict) -> dict:
     """The steering fields a request may carry (both protocols): ``steer_vector`` (a file name inside the server's
-    steer_dir, or ``"off"``), ``steer_scale``, ``steer_scope``, ``think_penalty``."""
+    steer_dir, or ``"off"``), ``steer_scale``, ``steer_scope``, ``think_penalty``, ``steer_probe`` (probe this prompt and
+    clamp the declining direction when it leans that way)."""
     out = {}
-    for k, conv in (("steer_vector", str), ("steer_scale", float), ("steer_scope", str), ("think_penalty", float)):
+    for k, conv in (("steer_vector", str), ("steer_scale", float), ("steer_scope", str), ("think_penalty", float), ("steer_probe", bool)):
         if body.get(k) is not None:
             try:
                 out[k] = conv(body[k])
