@@ -379,3 +379,22 @@ def test_ppl_tool_scores_calibrates_and_measures_kl(tmp_path, capsys):
               "--kl-teacher", str(teacher)])
     quant = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert 1e-5 < quant["kl"] < 0.2
+
+
+def test_tui_views_experts_speculation_memory():
+    ex = {"ranks": 2, "layers": 2, "experts": 4, "total": [10, 30, 0, 60, 0, 0, 0, 0], "recent": []}
+    f = tui.render_experts(ex, width=100)
+    assert "2 layers x 4 experts" in f and " 3:60%" in f and " 1:30%" in f and f.count("\n") == 4     # layer 1 saw no routes
+    assert "no routing histogram" in tui.render_experts({}, 80)
+    stats = dict(STATS)
+    stats["server"] = dict(stats.get("server", {}), speculation=True, speculator="draft")
+    stats["speculation"] = {"rounds": 10, "proposed": 30, "accepted": 12, "accept_rate": 0.4, "tokens_per_round": 2.2,
+                            "steps": [{"attempts": 10, "hits": 8}, {"attempts": 8, "hits": 3}, {"attempts": 3, "hits": 1}], "tree_rounds": 2, "tree_nodes": 9}
+    f = tui.render_speculation(stats, 100)
+    assert "accept 40.0%" in f and "80.0%" in f and "tree rounds 2 (9 nodes)" in f
+    assert "off" in tui.render_speculation({"server": {}}, 80)
+    f = tui.render_memory(stats, 100)
+    assert f.startswith("memory") and "kv pool" in f
+    assert tui.render_view("overview", stats, None, 100) == tui.render_frame(stats, 100)
+    assert tui.render_view("experts", stats, ex, 100) == tui.render_experts(ex, 100)
+    assert tui.VIEWS == ("overview", "experts", "speculation", "memory")
