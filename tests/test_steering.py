@@ -184,3 +184,53 @@ def test_request_time_probe_builds_directions_gates_and_steers(tmp_path):
     assert sc["fired"] and sc["edits"] > 0 and len(probed["tokens"]) == 6
     again = g.generate(Request(prompt, max_tokens=6, cache_prefix=False))
     assert again["tokens"] == plain["tokens"]                   # the slot's edits are gone with the request
+
+
+def test_probe_files_are_scored_at_the_last_prompt_token(tmp_path):
+    from volta_engine_b200.models.dense import DenseConfig, DenseModel
+    from volta_engine_b200.runtime import steer_probe as sp
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.generator import Generator, Request
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from volta_engine_b200.runtime.options import Options
+
+    class Tok:
+        eos_ids = [0]
+
+        def decode_bytes(self, ids, skip_special=False):
+            return bytes(i & 0xFF for i in ids)
+
+        def encode(self, text, allow_special=True):
+            return [1 + (b % 250) for b in text.encode()]
+    cfg = DenseConfig.tiny(vocab=256)
+    m = DenseModel(cfg, "cpu").init_random(seed=0)
+    g = torch.Generator().manual_seed(5)
+    v = torch.randn(cfg.hidden, generator=g)
+    v = v / v.norm()
+    st.save_steer_file(tmp_path / "mood.steer", st.SteerFile(cfg.hidden, cfg.n_layers, st.SCOPE_ALL, 1.0,
+                                                             [st.SteerEntry(1, st.STEER_PROBE, 0.25, v)]))
+    st.save_steer_file(tmp_path / "empty.steer", st.SteerFile(cfg.hidden, cfg.n_layers, st.SCOPE_ALL, 1.0,
+                                                              [st.SteerEntry(1, st.STEER_ADD, 0.25, v)]))
+    probes = sp.load_probe_files("mood", str(tmp_path))
+    assert list(probes) == ["mood"] and len(probes["mood"]) == 1
+    with pytest.raises(ValueError):
+        sp.load_probe_files("empty", str(tmp_path))
+    with pytest.raises(ValueError):
+        sp.load_probe_files("../mood", str(tmp_path))
+    o = Options.resolve({"max_slots": 2, "prefix_interval": 0, "steer": "on", "steer_layers": "0-last"}, env={})
+    scfg = st.SteerConfig(o, cfg.n_layers, Tok())
+    m.steer = scfg.tables(cfg.hidden, 2, "cpu")
+    eng = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 40, 2, 512, "cpu"), use_graphs=False, prefill_chunk=32)
+    gen = Generator(eng, Tok(), o, eos_ids=[])
+    gen.steer_cfg, gen.probe_files = scfg, probes
+    prompt = [5 + (3 * i) % 200 for i in range(30)]
+    out = gen.generate(Request(prompt, max_tokens=4, cache_prefix=False))
+    score = out["usage"]["probes"]["mood"]
+    # the same number from a capture by hand
+    eng2 = Engine(m, PagedKVCache(cfg.n_layers, m.nkv, cfg.head_dim, 40, 2, 512, "cpu"), use_graphs=False, prefill_chunk=32)
+    eng2.prefill(0, prompt)
+    with sp.StateCapture(m.steer, (1, 1)) as cap:
+        cap.row = 0
+        sp._run_rows(eng2, 0, [prompt[-1]], len(prompt) - 1)
+    assert abs(score - (float(cap.states[1] @ v) - 0.25)) < 1e-3
+    m.steer = None

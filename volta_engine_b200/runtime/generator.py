@@ -84,6 +84,7 @@ class SlotState:
     last_char: str = ""           # last character of the previous reasoning token (soft close: "3." is not a sentence end)
     depth_rate: object = None     # DepthByRate of the slot's request (spec_depth_rate)
     probe_scores: dict | None = None   # what the request-time probe measured (reported in the usage)
+    probe_file_scores: dict | None = None   # scores of the launch option's probe files at the prompt's last token
     forced: list = field(default_factory=list)   # tokens that replace the next sampled ones
 
 
@@ -375,6 +376,11 @@ class Generator:
             if self.cache is not None and s.req.cache_prefix and (end in self._snapshot_points(s)):
                 self._store_prefix(s, end)
             if last:
+                if getattr(self, "probe_files", None):
+                    tables = getattr(getattr(self.engine, "model", None), "steer", None)
+                    if tables is not None:
+                        from .steer_probe import score_probe_files
+                        s.probe_file_scores = score_probe_files(self.engine, tables, s.idx, prompt, self.probe_files)
                 if s.req.steer_probe and getattr(self, "probe_cfg", None) is not None:
                     tok = self._probe_steer(s, tok)
                 s.next_tok = tok
@@ -811,6 +817,9 @@ class Generator:
         if getattr(s, "probe_scores", None):
             usage["steer_probe"] = s.probe_scores
             s.probe_scores = None
+        if getattr(s, "probe_file_scores", None):
+            usage["probes"] = s.probe_file_scores
+            s.probe_file_scores = None
         if error:
             usage["error"] = error
         tap_file = getattr(self, "tap_spool", None)

@@ -200,3 +200,39 @@ def probe_request(engine, tables, tokenizer, slot: int, prompt: list[int], cfg: 
     m = engine.model
     states = collect_states(engine, tables, slot, len(prompt), prompt[-1], cfg.openings, tokenizer, cfg.band)
     return build_edits(states, cfg, m.cfg.hidden, m.cfg.n_layers)
+
+
+# ---------------------------------------------------------------------------------------------- probe files
+def load_probe_files(names: str, steer_dir: str) -> dict:
+    """Launch option ``probe``: comma list of probe files inside ``steer_dir`` (at most 4). A probe file is a control-vector
+    file whose probe entries (kind 8) name a layer, a unit direction and an offset; its score for a state is the
+    projection on the direction minus the offset, averaged over its entries."""
+    import os
+    from .steering import STEER_PROBE, load_steer_file
+    out = {}
+    for name in [n.strip() for n in names.split(",") if n.strip()][:4]:
+        if "/" in name or name.startswith("."):
+            raise ValueError("probe names files inside steer_dir, not paths")
+        path = os.path.join(steer_dir, name if name.endswith(".steer") else name + ".steer")
+        entries = [e for e in load_steer_file(path).entries if e.kind == STEER_PROBE and e.vec is not None]
+        if not entries:
+            raise ValueError(f"{path} holds no probe entries")
+        out[name] = entries
+    return out
+
+
+def score_probe_files(engine, tables, slot: int, prompt: list[int], probes: dict) -> dict:
+    """-> {file: score at the prompt's last token}: the last prompt row runs once more with the capture hook on."""
+    layers = sorted({e.layer for es in probes.values() for e in es})
+    if not layers:
+        return {}
+    with StateCapture(tables, (layers[0], layers[-1])) as cap:
+        cap.row = 0
+        _run_rows(engine, slot, [prompt[-1]], len(prompt) - 1)
+        st = dict(cap.states)
+    out = {}
+    for name, es in probes.items():
+        vals = [float(st[e.layer] @ e.vec.float()) - e.par for e in es if e.layer in st]
+        if vals:
+            out[name] = round(sum(vals) / len(vals), 4)
+    return out

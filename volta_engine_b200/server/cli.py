@@ -410,6 +410,9 @@ def build_server(cfg: LaunchConfig, device=None, comm=None, chan=None, agree=Non
         model.steer = gen.steer_cfg.tables(model.cfg.hidden, o.max_slots, engine.device)
         from ..runtime.steer_probe import ProbeSettings
         gen.probe_cfg = ProbeSettings.from_options(o, model.cfg.n_layers, gen.steer_cfg.first, gen.steer_cfg.last)
+        if o.probe:
+            from ..runtime.steer_probe import load_probe_files
+            gen.probe_files = load_probe_files(o.probe, o.steer_dir)
     if o.speculator == "draft" and cfg.draft_model_dir and cfg.tp_size > 1 and not o.draft_tp:
         log.warning("draft_tp = false: the vocabulary-sharded head needs every rank in a draft step, so the drafter stays off")
     if o.speculator == "draft" and cfg.draft_model_dir and (cfg.tp_size == 1 or o.draft_tp):
