@@ -96,3 +96,46 @@ def test_vision_tower_loads_from_a_checkpoint_directory_and_the_launcher_builds_
     other.mkdir()
     (other / "config.json").write_text(json.dumps({"model_type": "x"}))
     assert load_vision_frontend(str(other), {"model_type": "x"}, SimpleNamespace(vision_dir=str(tmp_path), max_image_tokens=64), "cpu") is not None
+
+
+def test_vision_tower_loads_from_a_llama_cpp_projector_file(tmp_path):
+    """vision_mmproj: the tower's weights under llama.cpp's clip tensor names (split temporal patch kernel, merged or
+    separate q / k / v) give the same image tokens as the tower they were written from."""
+    import json
+    from types import SimpleNamespace
+    from volta_engine_b200.loader.gguf_file import GGUFFile, write_gguf
+    from volta_engine_b200.models.vision import VisionConfig, VisionTower
+    from volta_engine_b200.quant import gguf as gq
+    from volta_engine_b200.server.cli import load_vision_frontend
+    vc = {"depth": 2, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "patch_size": 16, "temporal_patch_size": 2,
+          "spatial_merge_size": 2, "out_hidden_size": 96}
+    cfg = VisionConfig.from_hf(vc)
+    t = VisionTower(cfg, "cpu").init_random(seed=5)
+    bf = lambda x: (x.to(torch.bfloat16), gq.GGML_BF16, tuple(x.shape))
+    f32 = lambda x: (x.float(), gq.GGML_F32, tuple(x.shape))
+    pe = t.patch_embed.weight.reshape(cfg.hidden, 3, cfg.temporal, cfg.patch, cfg.patch)
+    tensors = {"v.patch_embd.weight": bf(pe[:, :, 0].contiguous()), "v.patch_embd.weight.1": bf(pe[:, :, 1].contiguous()),
+               "v.patch_embd.bias": f32(t.patch_bias)}
+    for i, b in enumerate(t.blocks):
+        q = f"v.blk.{i}."
+        tensors.update({q + "ln1.weight": f32(b["ln1_w"]), q + "ln1.bias": f32(b["ln1_b"]), q + "ln2.weight": f32(b["ln2_w"]),
+                        q + "ln2.bias": f32(b["ln2_b"]), q + "attn_out.weight": bf(b["proj"].weight), q + "attn_out.bias": f32(b["proj_b"]),
+                        q + "ffn_up.weight": bf(b["fc1"].weight), q + "ffn_up.bias": f32(b["fc1_b"]),
+                        q + "ffn_down.weight": bf(b["fc2"].weight), q + "ffn_down.bias": f32(b["fc2_b"])})
+        if i == 0:                                     # one block merged, one with separate q / k / v
+            tensors.update({q + "attn_qkv.weight": bf(b["qkv"].weight), q + "attn_qkv.bias": f32(b["qkv_b"])})
+        else:
+            for j, n in enumerate("qkv"):
+                tensors[q + f"attn_{n}.weight"] = bf(b["qkv"].weight[j * cfg.hidden:(j + 1) * cfg.hidden].contiguous())
+                tensors[q + f"attn_{n}.bias"] = f32(b["qkv_b"][j * cfg.hidden:(j + 1) * cfg.hidden].contiguous())
+    m = t.merger
+    tensors.update({"v.post_ln.weight": f32(m["ln_w"]), "v.post_ln.bias": f32(m["ln_b"]), "mm.0.weight": bf(m["fc1"].weight),
+                    "mm.0.bias": f32(m["fc1_b"]), "mm.2.weight": bf(m["fc2"].weight), "mm.2.bias": f32(m["fc2_b"])})
+    write_gguf(tmp_path / "model-mmproj-bf16.gguf", {"general.architecture": "clip"}, tensors)
+    t2 = VisionTower(cfg, "cpu").load_mmproj(GGUFFile(tmp_path / "model-mmproj-bf16.gguf"))
+    patches = torch.randn(4 * 6, cfg.patch_dim, generator=torch.Generator().manual_seed(1))
+    assert torch.equal(t.forward(patches, 4, 6), t2.forward(patches, 4, 6))
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "qwen3_vl", "vision_config": vc}))
+    front = load_vision_frontend(str(tmp_path), {"vision_config": vc}, SimpleNamespace(vision_dir="", max_image_tokens=64,
+                                                                                       vision_mmproj=str(tmp_path)), "cpu")
+    assert front is not None and torch.equal(front.tower.forward(patches, 4, 6), t.forward(patches, 4, 6))

@@ -142,6 +142,48 @@ class VisionTower:
                        "fc2": lin("merger.linear_fc2", "merger.mlp.2"), "fc2_b": vec("merger.linear_fc2.bias", "merger.mlp.2.bias")}
         return self
 
+    def load_mmproj(self, gguf) -> "VisionTower":
+        """The tower from a llama.cpp vision projector file (``*mmproj*.gguf``, architecture ``clip``): ``v.patch_embd.weight``
+        (+ ``.weight.1``: the second temporal slice), ``v.blk.N.{ln1,ln2}``, ``attn_qkv`` (or ``attn_q / attn_k / attn_v``),
+        ``attn_out``, ``ffn_up`` / ``ffn_down``, ``v.post_ln`` (the merger's norm) and ``mm.0`` / ``mm.2`` (the merger's two
+        linears). ``gguf``: a loader.gguf_file.GGUFFile."""
+        c, dev, bf, f32 = self.cfg, self.device, torch.bfloat16, torch.float32
+        names = set(gguf.tensors)
+
+        def t(name, dt):
+            return gguf.dequantize(name).to(dt).to(dev).contiguous()
+
+        def lin(name):
+            w = t(name + ".weight", bf)
+            return LinearBF16(w.reshape(w.shape[0], -1).contiguous())
+
+        def vec(name, n):
+            return t(name, f32) if name in names else torch.zeros(n, dtype=f32, device=dev)
+        pe = t("v.patch_embd.weight", bf).reshape(c.hidden, 3, 1, c.patch, c.patch)
+        if "v.patch_embd.weight.1" in names:                       # the converter splits the temporal axis of the conv kernel
+            pe = torch.cat([pe, t("v.patch_embd.weight.1", bf).reshape(c.hidden, 3, 1, c.patch, c.patch)], 2)
+        else:
+            pe = pe.expand(-1, -1, c.temporal, -1, -1) / c.temporal
+        self.patch_embed = LinearBF16(pe.reshape(c.hidden, -1).contiguous())
+        self.patch_bias = vec("v.patch_embd.bias", c.hidden)
+        self.blocks = []
+        for i in range(c.depth):
+            b = f"v.blk.{i}."
+            if b + "attn_qkv.weight" in names:
+                qkv, qkv_b = lin(b + "attn_qkv"), vec(b + "attn_qkv.bias", 3 * c.hidden)
+            else:
+                qkv = LinearBF16(torch.cat([t(b + f"attn_{n}.weight", bf) for n in "qkv"], 0).contiguous())
+                qkv_b = torch.cat([vec(b + f"attn_{n}.bias", c.hidden) for n in "qkv"], 0).contiguous()
+            self.blocks.append({"ln1_w": vec(b + "ln1.weight", c.hidden), "ln1_b": vec(b + "ln1.bias", c.hidden), "qkv": qkv, "qkv_b": qkv_b,
+                                "proj": lin(b + "attn_out"), "proj_b": vec(b + "attn_out.bias", c.hidden),
+                                "ln2_w": vec(b + "ln2.weight", c.hidden), "ln2_b": vec(b + "ln2.bias", c.hidden),
+                                "fc1": lin(b + "ffn_up"), "fc1_b": vec(b + "ffn_up.bias", c.mlp),
+                                "fc2": lin(b + "ffn_down"), "fc2_b": vec(b + "ffn_down.bias", c.hidden)})
+        m = c.merge * c.merge
+        self.merger = {"ln_w": vec("v.post_ln.weight", c.hidden), "ln_b": vec("v.post_ln.bias", c.hidden),
+                       "fc1": lin("mm.0"), "fc1_b": vec("mm.0.bias", c.hidden * m), "fc2": lin("mm.2"), "fc2_b": vec("mm.2.bias", c.out_hidden)}
+        return self
+
     def state_tensors(self, prefix: str = "model.visual.") -> dict:
         """The tower's tensors under their checkpoint names (what ``load`` reads back)."""
         c = self.cfg

@@ -251,11 +251,21 @@ def load_vision_frontend(model_dir: str, hf: dict, o, device):
     from ..models.vision import VisionConfig, VisionTower
     from ..runtime.multimodal import MultimodalFrontend
     cfg = VisionConfig.from_hf(vcfg)
-    src = TensorSource(vdir)
-    if not src.has("model.visual.patch_embed.proj.weight"):
-        log.warning("vision: %s has a vision_config but no model.visual.* tensors; image input stays off", vdir)
-        return None
-    tower = VisionTower(cfg, device).load(src)
+    mm = getattr(o, "vision_mmproj", "") or ""
+    if mm:
+        # vision_mmproj: a directory holding a llama.cpp projector file (*mmproj*.gguf) to take the tower's weights from
+        import glob
+        from ..loader.gguf_file import GGUFFile
+        files = sorted(glob.glob(os.path.join(mm, "*mmproj*.gguf"))) if os.path.isdir(mm) else [mm]
+        if not files:
+            raise FileNotFoundError(f"vision_mmproj: no *mmproj*.gguf in {mm}")
+        tower = VisionTower(cfg, device).load_mmproj(GGUFFile(files[0]))
+    else:
+        src = TensorSource(vdir)
+        if not src.has("model.visual.patch_embed.proj.weight"):
+            log.warning("vision: %s has a vision_config but no model.visual.* tensors; image input stays off", vdir)
+            return None
+        tower = VisionTower(cfg, device).load(src)
     pre = {}
     for fn in ("preprocessor_config.json", "processor_config.json"):
         if os.path.exists(os.path.join(vdir, fn)):
