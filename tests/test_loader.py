@@ -378,5 +378,7 @@ def test_loader_options_take_experts_and_dense_tensors_from_other_directories(tm
     kv = PagedKVCache(mixed.cfg.n_layers, mixed.nkv, mixed.cfg.head_dim, 8, 2, 256, "cpu")
     out, _ = Engine(mixed, kv, use_graphs=False, prefill_chunk=16).generate(list(range(20)), 3)
     assert len(out) == 3
+    via_src, _ = load_model(base, "cpu", overlay={"nvfp4_dense_src": str(dense)})
+    assert torch.equal(via_src.layers[0].o_proj.packed, mixed.layers[0].o_proj.packed)    # the same tensor by the other option
     src = OverlaySource(TensorSource(base), [])
     assert src.has("model.norm.weight") and src.repo is not None

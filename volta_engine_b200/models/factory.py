@@ -146,7 +146,7 @@ def parse_layer_set(text: str, n_layers: int) -> set:
 
 
 def overlay_from_options(primary: TensorSource, hf: dict, nvfp4_experts: str = "", nvfp4_expert_layers: str = "",
-                         mtp_head_dir: str = "", mtp_nvfp4: bool = False, nvfp4_dense_dir: str = ""):
+                         mtp_head_dir: str = "", mtp_nvfp4: bool = False, nvfp4_dense_dir: str = "", nvfp4_dense_src: str = ""):
     """The tensor source the loader options describe (the primary source itself when none of them is set)."""
     import re as _re
     n_layers = int(hf.get("num_hidden_layers", 0))
@@ -167,6 +167,8 @@ def overlay_from_options(primary: TensorSource, hf: dict, nvfp4_experts: str = "
             rules.append((lambda n: layer(n) >= n_layers, ex_src))
     if nvfp4_dense_dir:
         rules.append((lambda n: ".mlp.experts." not in n, TensorSource(nvfp4_dense_dir)))
+    if nvfp4_dense_src:                            # bf16 dense tensors of another checkpoint, quantised at load like the model's own
+        rules.append((lambda n: ".mlp.experts." not in n and "embed_tokens" not in n, TensorSource(nvfp4_dense_src)))
     return OverlaySource(primary, rules) if rules else primary
 
 

@@ -166,7 +166,7 @@ def build_engine(cfg: LaunchConfig, device=None, comm=None, agree=None):
     from ..runtime.kv_cache import PagedKVCache
     o = cfg.options
     device = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
-    overlay = {k: getattr(o, k) for k in ("nvfp4_experts", "nvfp4_expert_layers", "mtp_head_dir", "mtp_nvfp4", "nvfp4_dense_dir")
+    overlay = {k: getattr(o, k) for k in ("nvfp4_experts", "nvfp4_expert_layers", "mtp_head_dir", "mtp_nvfp4", "nvfp4_dense_dir", "nvfp4_dense_src")
                if getattr(o, k)}
     model, hf = load_model(cfg.model_dir, device, comm, gemm_mode=o.gemm_mode, overlay=overlay or None, nvfp4_dense=o.nvfp4_dense)
     mcfg = model.cfg
