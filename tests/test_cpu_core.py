@@ -158,6 +158,46 @@ def test_expert_tier_policy_swaps_the_hottest_cold_expert_in():
     assert t.rebalance(counts2, max_swaps=4) == 1 and 2 in t.resident() and t.swaps == 2
 
 
+def test_expert_stager_copies_cold_experts_into_alternating_scratch_buffers():
+    """Staging a layer ahead: the scratch holds the layer's cold experts in ascending order, the staged tables point hot
+    experts at their slots and cold ones into the scratch, consecutive layers alternate buffers, a changed residency is
+    staged again."""
+    from types import SimpleNamespace
+    from volta_engine_b200.runtime.expert_tier import ExpertStager, ExpertTier
+    E = 6
+
+    def tier(seed):
+        g = torch.Generator().manual_seed(seed)
+        r = lambda *s: torch.randint(0, 255, s, generator=g, dtype=torch.uint8)
+        bank = SimpleNamespace(e_local=E, gu_p=r(E, 4, 2), gu_s=r(E, 4, 1), dn_p=r(E, 2, 4), dn_s=r(E, 2, 1), gu_sf=None, dn_sf=None)
+        return ExpertTier(bank, 2, decay=0.5, margin=1.0)
+    tiers = [(3, tier(1)), (4, tier(2)), (7, tier(3))]
+    st = ExpertStager(tiers)
+    assert st.n_cold == 4 and ExpertStager.scratch_bytes(tiers) == 2 * 4 * (8 + 4 + 8 + 2)
+    assert st.wants(tiers[0][1], 17) and not st.wants(tiers[0][1], 16)
+    t0, t1, t2 = (t for _, t in tiers)
+    gu, dn = st.acquire(t0)
+    assert st.staged == [(0, 0), (1, 0)] and st.copies == 2              # this layer and the next one
+    for j, e in enumerate([2, 3, 4, 5]):
+        assert torch.equal(st.buf[0]["gu_p"][j], t0.cold["gu_p"][e]) and torch.equal(st.buf[1]["dn_s"][j], t1.cold["dn_s"][e])
+        assert int(gu[2 * e]) == st.buf[0]["gu_p"][j].data_ptr() and int(dn[2 * e + 1]) == st.buf[0]["dn_s"][j].data_ptr()
+    assert int(gu[0]) == t0.slots["gu_p"][0].data_ptr() and int(gu[3]) == t0.slots["gu_s"][1].data_ptr()
+    st.release(t0)
+    st.acquire(t1)
+    assert st.staged == [(2, 0), (1, 0)] and st.copies == 3              # layer 2 went into the buffer layer 0 released
+    st.release(t1)
+    st.acquire(t2)
+    st.release(t2)
+    assert st.copies == 3
+    # residency of layer 0 changes: expert 4 in, expert 1 out -> cold set 1 2 3 5, staged again with new tables
+    assert t0.rebalance(torch.tensor([5.0, 0.0, 0.0, 0.0, 9.0, 0.0]), max_swaps=1) == 1 and t0.resident() == [0, 4]
+    gu2, _ = st.acquire(t0)
+    assert st.copies == 4 and st.staged[0] == (0, 1)                     # layer 1 was still staged
+    for j, e in enumerate([1, 2, 3, 5]):
+        assert torch.equal(st.buf[0]["gu_p"][j], t0.cold["gu_p"][e]) and int(gu2[2 * e]) == st.buf[0]["gu_p"][j].data_ptr()
+    assert int(gu2[2 * 4]) == t0.slots["gu_p"][t0.slot_of[4]].data_ptr()
+
+
 def test_sentencepiece_style_tokenizer(tmp_path):
     import json
     from volta_engine_b200.loader.tokenizer import Tokenizer

@@ -216,6 +216,35 @@ def test_cpu_expert_service_answers_through_the_mailbox_and_a_stopped_service_ti
     assert float((x.float() + 1).sum()) != 0
 
 
+def test_expert_staging_gives_the_in_place_bits_and_copies_a_layer_once_while_it_stays_staged():
+    """Prefill rows of a tiered model with the cold experts staged a layer ahead: the same bits as reading them in place
+    from pinned host memory; a layer's cold set is copied once for as long as its buffer keeps it; rows at or below 16 do
+    not stage; a rebalance makes the next chunk copy the new cold set."""
+    m, _ = _models()
+    tiers = m.enable_expert_tier(2)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    xs = {rows: torch.randn(rows, m.cfg.hidden, generator=g, device=DEV).to(torch.bfloat16) for rows in (6, 40, 200)}
+    idx = [li for li, _ in tiers]
+    want = {rows: [m.ffn_block(li, m.layers[li], x, None, None).clone() for li in idx] for rows, x in xs.items()}
+    st = m.enable_expert_staging()
+    assert st is not None and st.n_cold == m.e_local - 2
+    for rep in range(2):
+        for rows, x in xs.items():
+            got = [m.ffn_block(li, m.layers[li], x, None, None) for li in idx]
+            for a, b in zip(got, want[rows]):
+                assert torch.equal(a, b), f"staged != in place at rows={rows}"
+    torch.cuda.synchronize()
+    # with at most two tiered layers nothing overwrites a buffer, so the first copy serves every later chunk; with more,
+    # every chunk (two staged row counts, two repetitions) copies every layer once
+    assert st.copies == (len(idx) if len(idx) <= 2 else 4 * len(idx)), (st.copies, len(idx))
+    swaps = m.rebalance_experts(max_swaps=2)                     # residency moves: the next chunk stages the new cold set
+    assert swaps >= 1
+    m_ref, _ = _models()
+    m_ref.layers[idx[0]].bank.gu_sf = None
+    x = xs[40]
+    assert torch.equal(m.ffn_block(idx[0], m.layers[idx[0]], x, None, None), m_ref.ffn_block(idx[0], m_ref.layers[idx[0]], x, None, None))
+
+
 def test_expert_tier_from_launch_options_rebalances_while_decoding(tmp_path):
     """expert_cache = 0.5: half of every layer's experts resident, the rest read in place from pinned memory; the tokens
     equal the untiered model's; the generator rebalances every expert_adapt_every steps; the heat file round-trips."""

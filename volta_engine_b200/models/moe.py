@@ -299,14 +299,21 @@ class MoEModel(DenseModel):
             d, inv = bank.routes(x, ids, act, cfg.act_limit), None
         elif tier is not None or rows <= 16 or bank.gu_sf is None:
             # tiered residency: per-expert base pointers (device slot or pinned host memory) instead of the stacked bank
-            gu = (tier.tab_gu.data_ptr(), 0) if tier is not None else (ptr(bank.gu_p), ptr(bank.gu_s))
-            dn = (tier.tab_dn.data_ptr(), 0) if tier is not None else (ptr(bank.dn_p), ptr(bank.dn_s))
+            stager = getattr(self, "expert_stager", None)
+            staged = None
+            if tier is not None and stager is not None and stager.wants(tier, rows) and not torch.cuda.is_current_stream_capturing():
+                staged = stager.acquire(tier)                   # cold experts of this layer are in device scratch by now
+            tabs = staged if staged is not None else ((tier.tab_gu, tier.tab_dn) if tier is not None else None)
+            gu = (tabs[0].data_ptr(), 0) if tier is not None else (ptr(bank.gu_p), ptr(bank.gu_s))
+            dn = (tabs[1].data_ptr(), 0) if tier is not None else (ptr(bank.dn_p), ptr(bank.dn_s))
             a = torch.empty(routes, I, dtype=x.dtype, device=x.device)
             call("nvfp4_moe_gemv", "ppppiiplipliiiiif", gu[0], gu[1], ptr(bank.gu_g), ptr(ids), bank.e0,
                  bank.e_local, ptr(x), x.stride(0), k, ptr(a), a.stride(0), routes, 2 * I, H, 1, act, float(cfg.act_limit))
             d = torch.empty(routes, H, dtype=x.dtype, device=x.device)
             call("nvfp4_moe_gemv", "ppppiiplipliiiiif", dn[0], dn[1], ptr(bank.dn_g), ptr(ids), bank.e0,
                  bank.e_local, ptr(a), a.stride(0), 1, ptr(d), d.stride(0), routes, H, I, 0, act, 0.0)
+            if staged is not None:
+                stager.release(tier)
             inv = None
         else:
             d, inv = self._grouped(bank, x, ids, routes, k, act)
@@ -388,7 +395,23 @@ class MoEModel(DenseModel):
                     L.tier.set_route_bias(L.router_bias, self.e0, resident_bias)
                 tiers.append((li, L.tier))
         self.tiers = tiers
+        self.expert_stager = None
         return tiers
+
+    def enable_expert_staging(self, min_rows: int = 17):
+        """Prefill chunks of at least ``min_rows`` rows read a tiered layer's cold experts from device scratch that a copy
+        stream fills a layer ahead (two buffers of one layer's cold experts). Returns the stager, or None when the scratch
+        does not fit in free device memory."""
+        from ..runtime.expert_tier import ExpertStager
+        tiers = getattr(self, "tiers", None)
+        if not tiers or all(t.hot_slots >= t.E for _, t in tiers):
+            return None
+        if self.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.device)
+            if ExpertStager.scratch_bytes(tiers) + (256 << 20) > free:
+                return None
+        self.expert_stager = ExpertStager(tiers, min_rows)
+        return self.expert_stager
 
     def rebalance_experts(self, max_swaps: int = 2) -> int:
         """Fold the routing histogram of every tiered layer into its decayed heat and swap experts whose heat says so."""

@@ -7,7 +7,8 @@ working. ``rebalance`` folds the router's histogram into a decayed heat and swap
 coldest hot ones when the heat ratio exceeds a margin.
 
 Reference: inc/engine/modules/expert_tier.h:14-112 (hot slots, mapped cold experts, decayed heat, online rebalancing);
-the prefill path of a tiered layer runs the same route-indexed kernel (no staging a layer ahead).
+the prefill path of a tiered layer runs the same route-indexed kernel, on cold experts that ``ExpertStager`` copied into
+device scratch a layer ahead (src/backend/cuda/modules/expert_tier.cu:126).
 """
 from __future__ import annotations
 
@@ -125,3 +126,114 @@ class ExpertTier:
 
     def host_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.cold.values())
+
+
+class ExpertStager:
+    """Prefill staging of cold experts: a chunk of many rows would read a cold expert over PCIe once per route, so the
+    cold experts of a layer are copied once into device scratch instead, a layer ahead of the compute, and the route
+    kernel reads that copy through a second pointer table.
+
+    Two scratch buffers alternate between consecutive tiered layers. ``acquire(tier)`` makes the launching stream wait
+    for the layer's copy (starting it first when nothing staged it), starts the next layer's copy into the other buffer on
+    the copy stream, and returns the (gate|up, down) pointer tables to launch with; ``release(tier)`` marks the buffer
+    free for the copy two layers on. The tables of a (tier, buffer) pair depend only on the residency, so they are built
+    once per residency version and no host memory is rewritten while a copy reads it.
+    Reference: src/backend/cuda/modules/expert_tier.cu:126 (stage ahead, two buffers, auto off for trellis experts),
+    docs/CONFIG.md:91 (expert_stage).
+    """
+
+    def __init__(self, tiers: list, min_rows: int = 17):
+        self.tiers = [t for _, t in tiers] if tiers and isinstance(tiers[0], tuple) else list(tiers)
+        assert self.tiers, "no tiered layers to stage"
+        t0 = self.tiers[0]
+        self.device = t0.device
+        self.min_rows = min_rows
+        self.n_cold = max(t.E - t.hot_slots for t in self.tiers)
+        self.order = {id(t): i for i, t in enumerate(self.tiers)}
+        self.buf = [{n: torch.empty((self.n_cold,) + tuple(t0.cold[n].shape[1:]), dtype=t0.cold[n].dtype, device=self.device)
+                     for n in ExpertTier.NAMES} for _ in range(2)]
+        cuda = self.device.type == "cuda"
+        self.copy_stream = torch.cuda.Stream(self.device) if cuda else None
+        self.ready = [torch.cuda.Event() for _ in range(2)] if cuda else None
+        self.free = [torch.cuda.Event() for _ in range(2)] if cuda else None
+        self.staged = [None, None]                     # per buffer: (tier index, residency version) of its content
+        self.used = [False, False]                     # a release was recorded on the buffer's free event
+        self._tabs = {}                                # (tier index, buffer) -> (version, tab_gu, tab_dn)
+        self.copies = 0                                # cold-expert copies started (bytes: see ``bytes_staged``)
+        self.bytes_staged = 0
+
+    @classmethod
+    def scratch_bytes(cls, tiers: list) -> int:
+        ts = [t for _, t in tiers] if tiers and isinstance(tiers[0], tuple) else list(tiers)
+        per = sum(t.cold[n][0].numel() * t.cold[n].element_size() for t in ts[:1] for n in ExpertTier.NAMES)
+        return 2 * per * max((t.E - t.hot_slots for t in ts), default=0)
+
+    def wants(self, tier, rows: int) -> bool:
+        return rows >= self.min_rows and id(tier) in self.order and tier.hot_slots < tier.E
+
+    def _tables(self, i: int, b: int):
+        """Pointer tables of tier ``i`` whose cold entries point into buffer ``b`` (cold experts in ascending order)."""
+        t = self.tiers[i]
+        hit = self._tabs.get((i, b))
+        if hit is not None and hit[0] == t.swaps:
+            return hit[1], hit[2]
+        gu, dn = t.tab_gu.clone(), t.tab_dn.clone()
+        cold = [e for e in range(t.E) if t.slot_of[e] < 0]
+        s = self.buf[b]
+        idx = torch.tensor([2 * e + j for e in cold for j in (0, 1)], dtype=torch.int64)
+        pg = torch.tensor([p for j in range(len(cold)) for p in (s["gu_p"][j].data_ptr(), s["gu_s"][j].data_ptr())], dtype=torch.int64)
+        pd = torch.tensor([p for j in range(len(cold)) for p in (s["dn_p"][j].data_ptr(), s["dn_s"][j].data_ptr())], dtype=torch.int64)
+        gu[idx.to(self.device)] = pg.to(self.device)
+        dn[idx.to(self.device)] = pd.to(self.device)
+        self._tabs[(i, b)] = (t.swaps, gu, dn)
+        return gu, dn
+
+    def _stage(self, i: int, b: int) -> None:
+        """Start the copy of tier ``i``'s cold experts into buffer ``b`` (runs of consecutive experts as one copy each)."""
+        t = self.tiers[i]
+        cold = [e for e in range(t.E) if t.slot_of[e] < 0]
+        runs, j = [], 0
+        while j < len(cold):
+            k = j
+            while k + 1 < len(cold) and cold[k + 1] == cold[k] + 1:
+                k += 1
+            runs.append((j, cold[j], k - j + 1))
+            j = k + 1
+
+        def copy():
+            for pos, e, n in runs:
+                for name in ExpertTier.NAMES:
+                    src = t.cold[name][e:e + n]
+                    self.buf[b][name][pos:pos + n].copy_(src, non_blocking=True)
+                    self.bytes_staged += src.numel() * src.element_size()
+        if self.copy_stream is None:
+            copy()
+        else:
+            with torch.cuda.stream(self.copy_stream):
+                if self.used[b]:
+                    self.copy_stream.wait_event(self.free[b])       # the layer that last read this buffer has finished
+                copy()
+                self.ready[b].record(self.copy_stream)
+        self.staged[b] = (i, t.swaps)
+        self.copies += 1
+
+    def acquire(self, tier):
+        i = self.order[id(tier)]
+        b = i & 1
+        self._tables(i, b)                                  # built on the launching stream before any copy is queued
+        if self.staged[b] != (i, tier.swaps):
+            self._stage(i, b)
+        if self.copy_stream is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.ready[b])
+        if i + 1 < len(self.tiers):
+            nxt = self.tiers[i + 1]
+            if nxt.hot_slots < nxt.E and self.staged[b ^ 1] != (i + 1, nxt.swaps):
+                self._tables(i + 1, b ^ 1)
+                self._stage(i + 1, b ^ 1)
+        return self._tables(i, b)
+
+    def release(self, tier) -> None:
+        b = self.order[id(tier)] & 1
+        if self.free is not None:
+            self.free[b].record(torch.cuda.current_stream(self.device))
+        self.used[b] = True

@@ -127,8 +127,8 @@ _WIDE = {
     "moe_heavy_rows": lambda raw: int(raw) if int(raw) > 0 else 64,
 }
 
-_NOT_WIRED = {'expert_stage': 'expert tier: staging a layer ahead is not built', 'spec_interleave': 'interleaved rounds'}
-_COMPAT_HELP = {'nvfp4_dense_src': 'directory of another checkpoint of the model whose bf16 dense tensors (everything but the routed experts and the embedding) replace the model directory\u2019s and are quantised at load', 'vision_mmproj': 'a llama.cpp vision projector file (or a directory holding a *mmproj*.gguf) the tower takes its weights from instead of the model.visual.* tensors (config.json and preprocessor_config.json still come from vision_dir or model_dir)', 'probe': 'with steer: comma list of probe files in steer_dir (at most 4) scored on every request; the usage reports each file\u2019s score at the last prompt token', 'spec_interleave': 'no effect: several decoding slots take joint MTP rounds (spec_joint: every slot in one verify forward) or plain batched steps; one-slot-per-step interleaving is not offered', 'ple_log': 'no effect: the n-gram embedding lookup of this build runs on the device inside the forward; there is no host lookup to time', 'steer_gate_threshold': 'requests with steer_probe: the look-ahead score (0 = like the accepting openings, 1 = like the declining ones) above which the clamps are installed; auto = 0.5', 'steer_edit_strength': 'requests with steer_probe: the reference level of a clamp sits this many standard deviations (of the projections of the accepting openings) below their mean projection; auto = 1', 'steer_hedge_strength': 'requests with steer_probe: a second clamp on the plain -> hedged axis at this fraction of the gap above the plain mean; < 0 = off', 'steer_openings': 'requests with steer_probe: file that replaces the built-in forced openings (lines accept: / decline: / plain: / hedged: TEXT)', 'steer_directions': 'requests with steer_probe: directions clamped per edit layer (1 to 4: the mean difference of the openings, then the strongest remaining variations of the declining openings)', 'steer_keep_norm': 'requests with steer_probe: a row a clamp edited is rescaled to the norm it had before', 'steer_push': 'requests with steer_probe: add the declining direction to the edit layers, this many times the gap between the accepting and the declining openings, whether or not the gate fires; negative pushes towards accepting', 'steer_band': 'requests with steer_probe: layers the probe reads (first-last as steer_layers); empty = 1/3-2/3', 'steer_edit_layers': 'requests with steer_probe: layers the clamps edit inside the band; empty = the band', 'nvfp4_experts': 'directory of an NVFP4 checkpoint of the same model whose routed experts replace those of model_dir (MoE / MLA families)', 'nvfp4_expert_layers': 'layers ("3-10,12") whose experts come from nvfp4_experts; empty = all', 'mtp_head_dir': 'directory of a checkpoint the MTP head (the block past the last layer and its connectors) is taken from', 'mtp_nvfp4': 'take the MTP head from the nvfp4_experts checkpoint', 'nvfp4_dense_dir': 'directory of calibrated NVFP4 dense tensors used instead of the model directory\'s for the names it holds', 'nvfp4_dense': 'dense groups quantised to NVFP4 at load beyond the default (the MoE / MLA loaders quantise every dense projection already): head, or all', 'draft_tp': 'true: the block drafter runs tensor parallel on every rank (its calls are mirrored to the followers); false with tp > 1: the drafter stays off (the sharded head needs every rank)', 'vision_dir': 'directory that holds the vision tower (config.json with vision_config, preprocessor_config.json, model.visual.* tensors) when it is not model_dir', 'max_image_tokens': 'largest image the vision tower accepts, in language-model tokens (caps the resize); 0 = image input off', 'spec_depth_rate': 'block drafter: choose each round\'s draft depth for the most expected tokens per millisecond (per-position accuracy against a fitted fixed + per-row round time); replaces spec_depth while on', 'dflash_hessian_dir': 'directory that receives, at shutdown, the input Hessians of the block drafter\'s projections (the same per-site files as hessian_dir)', 'tap_spool': 'with a block drafter: file that receives, when a request finishes, its tokens, the drafter taps of its last tap_spool_window positions and the target\'s top-16 candidates at the positions speculation emitted (record layout in runtime/spec_logs.py)', 'tap_spool_window': 'positions of a finished request whose taps are written to tap_spool', 'draft_per_slot': 'true is how this engine always runs: every slot keeps its own drafter context and tap ring; false (one shared context) is not offered', 'route_resident_bias': 'with expert_cache < 1: added to the router\'s selection score of experts resident in device memory (the weights stay the raw scores); follows the residency after every rebalance', 'expert_history_pct': 'largest share (percent) of an expert swap decision taken from the long-run route counts (kept between runs with expert_heat_file) instead of the recent windows; grows with the amount of history', 'cpu_experts': 'share (0..1) of every layer\'s routed experts kept packed in host memory and computed by the host pool (native NVFP4 kernels) beside the GPU', 'cpu_expert_cpus': 'CPU list ("0-7,16") the host pool\'s workers are pinned to', 'cpu_expert_node': 'NUMA node whose CPUs the host pool takes when cpu_expert_cpus is empty', 'cpu_expert_spin_us': 'how long an idle host worker spins on the work counter before it sleeps', 'sparse_head_interval': 'generated tokens between rebuilds of the sparse drafter head', 'sparse_head_force': 'draft through the subset whenever one exists, whatever the miss rate (A/B)', 'route_dump_from': 'route_dump records only the layers from this index on (n_layers = the MTP block only)', 'dsa': 'false: the latent-attention layers drop their indexer and attend densely', 'qsa_off': 'true: the hybrid attention layers drop their block-sparse indexer and attend densely', 'expert_stats': 'false: no routing histogram is kept for the monitor (a model with an expert tier keeps it)', 'spec_profile': 'time the stages of every drafter round (ingest, backbone, head and walk) and log the averages at shutdown', 'thinking_soft_close': 'once a reasoning budget runs out the block closes after the next token that ends a sentence or a line, at most this many tokens later; 0 closes at the budget', 'expert_log': 'log the swaps of every expert rebalance', 'spec_ctrl_log': 'log the speculation controller\'s mode changes', 'arena_gib': 'size of the per-GPU arena in GiB; <= 0 sizes it from free memory minus vram_reserve_mib', 'scratch_mib': 'arena memory set aside for kernel workspaces before the model loads', 'prefix_cache_gib': 'prefix cache budget in GiB (alias of prefix_cache_mib)', 'prefix_cache_disk_gib': "size limit of the prefix cache's disk tier; the least recently used files go first", 'prefill_cooldown': 'decode steps that run between two prompt pieces while other requests decode', 'prefix_cache_reply': 'snapshot prompt + reply when a request ends', 'ar_ll': 'false: decode rows use the two-shot collective instead of the one-shot LL all-reduce (A/B)', 'mtp_depth': 'draft depth of the MTP speculator (alias of spec_depth when speculator=mtp)', 'spec_suffix': '> 0 turns the suffix drafter on when no speculator is named', 'mem_log': 'log device memory after start-up', 'side_streams': 'independent chains of a layer (shared expert beside the routed experts) run on a side stream', 'low_priority_models': 'comma list of model-name substrings whose requests queue behind the others', 'sparse_head_file': 'alias of sparse_head_state', 'expert_shard': '0 / 1: whole experts per rank / a slice of every expert per rank (alias of expert_parallel)', 'mtp_graph': 'false: alias of no_graphs'}
+_NOT_WIRED = {}
+_COMPAT_HELP = {'expert_stage': 'with expert_cache < 1, prompt pieces above 16 rows: copy a layer\'s cold experts once into device scratch, a layer ahead of the compute, instead of reading them over PCIe for every route (two buffers of one layer\'s cold experts; off when they do not fit). -1 and 1: on; 0: off', 'nvfp4_dense_src': 'directory of another checkpoint of the model whose bf16 dense tensors (everything but the routed experts and the embedding) replace the model directory\u2019s and are quantised at load', 'vision_mmproj': 'a llama.cpp vision projector file (or a directory holding a *mmproj*.gguf) the tower takes its weights from instead of the model.visual.* tensors (config.json and preprocessor_config.json still come from vision_dir or model_dir)', 'probe': 'with steer: comma list of probe files in steer_dir (at most 4) scored on every request; the usage reports each file\u2019s score at the last prompt token', 'spec_interleave': 'no effect: several decoding slots take joint MTP rounds (spec_joint: every slot in one verify forward) or plain batched steps; one-slot-per-step interleaving is not offered', 'ple_log': 'no effect: the n-gram embedding lookup of this build runs on the device inside the forward; there is no host lookup to time', 'steer_gate_threshold': 'requests with steer_probe: the look-ahead score (0 = like the accepting openings, 1 = like the declining ones) above which the clamps are installed; auto = 0.5', 'steer_edit_strength': 'requests with steer_probe: the reference level of a clamp sits this many standard deviations (of the projections of the accepting openings) below their mean projection; auto = 1', 'steer_hedge_strength': 'requests with steer_probe: a second clamp on the plain -> hedged axis at this fraction of the gap above the plain mean; < 0 = off', 'steer_openings': 'requests with steer_probe: file that replaces the built-in forced openings (lines accept: / decline: / plain: / hedged: TEXT)', 'steer_directions': 'requests with steer_probe: directions clamped per edit layer (1 to 4: the mean difference of the openings, then the strongest remaining variations of the declining openings)', 'steer_keep_norm': 'requests with steer_probe: a row a clamp edited is rescaled to the norm it had before', 'steer_push': 'requests with steer_probe: add the declining direction to the edit layers, this many times the gap between the accepting and the declining openings, whether or not the gate fires; negative pushes towards accepting', 'steer_band': 'requests with steer_probe: layers the probe reads (first-last as steer_layers); empty = 1/3-2/3', 'steer_edit_layers': 'requests with steer_probe: layers the clamps edit inside the band; empty = the band', 'nvfp4_experts': 'directory of an NVFP4 checkpoint of the same model whose routed experts replace those of model_dir (MoE / MLA families)', 'nvfp4_expert_layers': 'layers ("3-10,12") whose experts come from nvfp4_experts; empty = all', 'mtp_head_dir': 'directory of a checkpoint the MTP head (the block past the last layer and its connectors) is taken from', 'mtp_nvfp4': 'take the MTP head from the nvfp4_experts checkpoint', 'nvfp4_dense_dir': 'directory of calibrated NVFP4 dense tensors used instead of the model directory\'s for the names it holds', 'nvfp4_dense': 'dense groups quantised to NVFP4 at load beyond the default (the MoE / MLA loaders quantise every dense projection already): head, or all', 'draft_tp': 'true: the block drafter runs tensor parallel on every rank (its calls are mirrored to the followers); false with tp > 1: the drafter stays off (the sharded head needs every rank)', 'vision_dir': 'directory that holds the vision tower (config.json with vision_config, preprocessor_config.json, model.visual.* tensors) when it is not model_dir', 'max_image_tokens': 'largest image the vision tower accepts, in language-model tokens (caps the resize); 0 = image input off', 'spec_depth_rate': 'block drafter: choose each round\'s draft depth for the most expected tokens per millisecond (per-position accuracy against a fitted fixed + per-row round time); replaces spec_depth while on', 'dflash_hessian_dir': 'directory that receives, at shutdown, the input Hessians of the block drafter\'s projections (the same per-site files as hessian_dir)', 'tap_spool': 'with a block drafter: file that receives, when a request finishes, its tokens, the drafter taps of its last tap_spool_window positions and the target\'s top-16 candidates at the positions speculation emitted (record layout in runtime/spec_logs.py)', 'tap_spool_window': 'positions of a finished request whose taps are written to tap_spool', 'draft_per_slot': 'true is how this engine always runs: every slot keeps its own drafter context and tap ring; false (one shared context) is not offered', 'route_resident_bias': 'with expert_cache < 1: added to the router\'s selection score of experts resident in device memory (the weights stay the raw scores); follows the residency after every rebalance', 'expert_history_pct': 'largest share (percent) of an expert swap decision taken from the long-run route counts (kept between runs with expert_heat_file) instead of the recent windows; grows with the amount of history', 'cpu_experts': 'share (0..1) of every layer\'s routed experts kept packed in host memory and computed by the host pool (native NVFP4 kernels) beside the GPU', 'cpu_expert_cpus': 'CPU list ("0-7,16") the host pool\'s workers are pinned to', 'cpu_expert_node': 'NUMA node whose CPUs the host pool takes when cpu_expert_cpus is empty', 'cpu_expert_spin_us': 'how long an idle host worker spins on the work counter before it sleeps', 'sparse_head_interval': 'generated tokens between rebuilds of the sparse drafter head', 'sparse_head_force': 'draft through the subset whenever one exists, whatever the miss rate (A/B)', 'route_dump_from': 'route_dump records only the layers from this index on (n_layers = the MTP block only)', 'dsa': 'false: the latent-attention layers drop their indexer and attend densely', 'qsa_off': 'true: the hybrid attention layers drop their block-sparse indexer and attend densely', 'expert_stats': 'false: no routing histogram is kept for the monitor (a model with an expert tier keeps it)', 'spec_profile': 'time the stages of every drafter round (ingest, backbone, head and walk) and log the averages at shutdown', 'thinking_soft_close': 'once a reasoning budget runs out the block closes after the next token that ends a sentence or a line, at most this many tokens later; 0 closes at the budget', 'expert_log': 'log the swaps of every expert rebalance', 'spec_ctrl_log': 'log the speculation controller\'s mode changes', 'arena_gib': 'size of the per-GPU arena in GiB; <= 0 sizes it from free memory minus vram_reserve_mib', 'scratch_mib': 'arena memory set aside for kernel workspaces before the model loads', 'prefix_cache_gib': 'prefix cache budget in GiB (alias of prefix_cache_mib)', 'prefix_cache_disk_gib': "size limit of the prefix cache's disk tier; the least recently used files go first", 'prefill_cooldown': 'decode steps that run between two prompt pieces while other requests decode', 'prefix_cache_reply': 'snapshot prompt + reply when a request ends', 'ar_ll': 'false: decode rows use the two-shot collective instead of the one-shot LL all-reduce (A/B)', 'mtp_depth': 'draft depth of the MTP speculator (alias of spec_depth when speculator=mtp)', 'spec_suffix': '> 0 turns the suffix drafter on when no speculator is named', 'mem_log': 'log device memory after start-up', 'side_streams': 'independent chains of a layer (shared expert beside the routed experts) run on a side stream', 'low_priority_models': 'comma list of model-name substrings whose requests queue behind the others', 'sparse_head_file': 'alias of sparse_head_state', 'expert_shard': '0 / 1: whole experts per rank / a slice of every expert per rank (alias of expert_parallel)', 'mtp_graph': 'false: alias of no_graphs'}
 _COMPAT = [(n, t, d, ("parsed, not wired in this build: " + _NOT_WIRED[n]) if n in _NOT_WIRED else disp) for n, t, d, disp in _COMPAT]
 
 _TYPES = {n: t for n, t, _, _ in _TABLE}

@@ -350,6 +350,11 @@ def configure_expert_tier(model, o, rank: int = 0) -> None:
         if tuple(heat.shape) == tuple(model.heat.shape):
             model.heat.copy_(heat)
             model.rebalance_experts(max_swaps=hot)            # start with the hottest experts resident
+    stage = "off"
+    if int(o.expert_stage) != 0:                                # -1 (auto) and 1: on when the scratch fits
+        st = model.enable_expert_staging()
+        stage = "off (scratch does not fit)" if st is None else f"{st.n_cold} cold experts x 2 buffers"
+    log.info("expert tier: prefill staging %s", stage)
     log.info("expert tier: %d of %d experts per layer resident (%d layers, %.1f MiB per expert), rebalance every %d steps, "
              "%d swaps per layer", hot, model.e_local, len(tiers), per_expert / 2**20, model.expert_adapt_every, swaps)
 
