@@ -127,11 +127,12 @@ __global__ void __launch_bounds__(256) gdn_recurrent_kernel(const GdnArgs a) {
   }
 #pragma unroll
   for (int k = 0; k < DK; ++k) st[(long)k * a.dv] = S[k];
-  if (h == 0) {
-    // roll the convolution state: the newest kc-1 inputs of the slot, oldest first
+  {
+    // roll the convolution state: the newest kc-1 inputs of the slot, oldest first. The channels are dealt to the head
+    // blocks of the slot (every channel is independent), so no block walks all of them alone.
     const int n1 = a.kc - 1;
     float* cs = a.conv_state + (long)s * n1 * C;
-    for (int c = col; c < C; c += blockDim.x) {
+    for (int c = h * blockDim.x + col; c < C; c += gridDim.x * blockDim.x) {
       float old[8], nw[8];
       for (int t = 0; t < n1; ++t) old[t] = fresh ? 0.f : cs[(long)t * C + c];
       for (int t = 0; t < n1; ++t) {
@@ -160,13 +161,13 @@ __global__ void gdn_gated_norm_kernel(const float* __restrict__ o, const __nv_bf
   out[((long)i * nv + h) * dv + col] = f2bf(x * rsqrtf(ss / dv + eps) * w[col] * gate);
 }
 
-// KDA decay per key channel: kdec[row][j] = exp(-5 sigmoid(exp(A_log[j / dk]) (f[row][j] + dt_bias[j]))). grid rows.
+// KDA decay per key channel: kdec[row][j] = exp(-5 sigmoid(exp(A_log[j / dk]) (f[row][j] + dt_bias[j]))). grid (rows, channel chunks).
 __global__ void kda_decay_kernel(const __nv_bfloat16* __restrict__ f, long ld, const float* __restrict__ A_log,
                                  const float* __restrict__ dt_bias, float* __restrict__ kdec, int channels, int dk) {
   grid_dep_launch();
   grid_dep_wait();
   const int i = blockIdx.x;
-  for (int j = threadIdx.x; j < channels; j += blockDim.x) {
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < channels; j += gridDim.y * blockDim.x) {
     const float x = __expf(A_log[j / dk]) * (bf2f(f[(long)i * ld + j]) + dt_bias[j]);
     kdec[(long)i * channels + j] = __expf(-5.f / (1.f + __expf(-x)));
   }
@@ -223,7 +224,8 @@ int ve_kda_recurrent(const void* proj, long ld, const void* pos, const void* slo
 int ve_kda_decay(const void* f, long ld, const void* A_log, const void* dt_bias, void* kdec, int rows, int nv, int dk,
                  cudaStream_t st) {
   if (rows <= 0) return 0;
-  launch_pdl(kda_decay_kernel, dim3(rows), dim3(256), 0, st, (const __nv_bfloat16*)f, ld, (const float*)A_log,
+  const int chunks = (nv * dk + 1023) / 1024;          // 256 threads take four channels each
+  launch_pdl(kda_decay_kernel, dim3(rows, chunks), dim3(256), 0, st, (const __nv_bfloat16*)f, ld, (const float*)A_log,
              (const float*)dt_bias, (float*)kdec, nv * dk, dk);
   VE_CHECK_LAUNCH();
 }

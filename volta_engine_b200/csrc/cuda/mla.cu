@@ -66,6 +66,7 @@ __global__ void mla_absorb_q_kernel(const __nv_bfloat16* __restrict__ q, long q_
   const __nv_bfloat16* w = w_uk + (long)h * nope * kLat;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const int c0 = threadIdx.x * 4;
+#pragma unroll 8                                   // eight independent row loads in flight (the loop is latency-bound)
   for (int d = 0; d < nope; ++d) {
     const uint2 t = *reinterpret_cast<const uint2*>(w + (long)d * kLat + c0);
     const float qd = qs[d];
@@ -92,6 +93,7 @@ __global__ void mla_expand_out_kernel(const __nv_bfloat16* __restrict__ o_lat, c
   if (v >= vdim) return;
   const __nv_bfloat16* w = w_uv + ((long)h * vdim + v) * kLat;
   float acc = 0.f;
+#pragma unroll 8
   for (int c = 0; c < kLat; c += 8) {
     const bf16x8 t = *reinterpret_cast<const bf16x8*>(w + c);
 #pragma unroll

@@ -236,7 +236,8 @@ def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantiz
     if mt == "deepseek_v41":
         return load_dsv41(hf, d, device, comm), hf
     if mt in ("glm5_next", "glm5-next"):
-        return load_glm5(hf, d, device, comm), hf
+        groups = {g.strip() for g in nvfp4_dense.split(",") if g.strip()}
+        return load_glm5(hf, d, device, comm, gemm_mode, quantize, nvfp4_head=bool(groups & {"head", "all"})), hf
     src = TensorSource(d, prefer)
     if mt in DENSE_TYPES:
         cfg = dense_config_from_hf(hf)
@@ -307,15 +308,15 @@ def glm5_config_from_hf(c: dict):
     return base
 
 
-def load_glm5(hf: dict, model_dir: Path, device, comm):
-    """A GLM-5-Next directory. The synthetic form is built: ``config.json`` with ``"synthetic_weights": <seed>`` and no
-    tensor files runs the architecture (KDA mixers, latent attention with the indexer, experts, hyper-connection streams,
-    MTP head) with random weights; the tensor-name mapping of the published checkpoint is not."""
+def load_glm5(hf: dict, model_dir: Path, device, comm, gemm_mode="w4a16", quantize=None, nvfp4_head: bool = False):
+    """A GLM-5-Next directory: the published checkpoint's tensors (:mod:`.glm5_loader`), or, with ``"synthetic_weights":
+    <seed>`` in ``config.json`` and no tensor files, the architecture (KDA mixers, latent attention with the indexer,
+    experts, hyper-connection streams, MTP head) with random weights."""
     from .glm5 import Glm5NextModel
-    cfg = glm5_config_from_hf(hf)
     if "synthetic_weights" not in hf:
-        raise NotImplementedError("glm5_next: loading checkpoint tensors is not built (config.json with "
-                                  "\"synthetic_weights\": <seed> runs the architecture with random weights)")
+        from .glm5_loader import load_glm5_checkpoint
+        return load_glm5_checkpoint(hf, TensorSource(model_dir), device, comm, gemm_mode, quantize, nvfp4_head)
+    cfg = glm5_config_from_hf(hf)
     cfg.expert_quant = hf.get("expert_quant", "nvfp4_random")
     model = Glm5NextModel(cfg, device, comm).init_random(seed=int(hf["synthetic_weights"]))
     if cfg.residual != "plain":

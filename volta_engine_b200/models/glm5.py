@@ -16,7 +16,8 @@ state, except with the indexer on (its pooled keys live outside the pool), where
 
 Reference: src/models/glm5_next.cpp:499-552 (layer kinds), :1612-1764 (linear / latent attention blocks), :1766-2308
 (forward with streams, experts, MTP); inc/engine/models/glm5_next.h:33-52 (shape: 45 layers of hidden 4096, 11 latent
-attention layers, 16 KDA heads of 128, 288 experts top-8 of width 2048, dense width 12288, vocabulary 154880).
+attention layers, 288 experts top-8 of width 2048, dense width 12288, vocabulary 154880); src/models/glm5_next.cpp:107
+(64 heads in all, divided over the ranks).
 """
 from __future__ import annotations
 
@@ -39,12 +40,16 @@ class Glm5NextConfig(HybridConfig):
 
     @classmethod
     def glm5_next(cls):
-        """The published shape: 45 layers (34 KDA + 11 latent attention), hidden 4096, 32 attention heads, 288 experts
-        top-8 (sigmoid, scaled 2.5) of width 2048 + shared expert, 3 leading dense layers of width 12288, MTP head."""
-        return cls(n_layers=45, hidden=4096, n_q=32, n_kv=1, head_dim=576, ffn=12288, vocab=154880, n_experts=288, top_k=8,
+        """The published shape: 45 layers (34 KDA + 11 latent attention), hidden 4096, 64 KDA heads of 128 x 128 (q, k and
+        v projections of 8192 rows each), 64 latent-attention heads (192 + 64 query dims, 256 value dims, query rank 1536),
+        288 experts top-8 (sigmoid, scaled 2.5) of width 2048 + shared expert, 3 leading dense layers of width 12288, MTP
+        head. (The reference's ``kda_heads = 16`` is the per-rank count of its four-GPU layout: 64 / tp,
+        src/models/glm5_next.cpp:107.)"""
+        return cls(n_layers=45, hidden=4096, n_q=64, n_kv=1, head_dim=576, ffn=12288, vocab=154880, n_experts=288, top_k=8,
                    expert_ffn=2048, shared_ffn=2048, router="sigmoid", router_scale=2.5, first_dense_layers=3,
-                   full_interval=4, linear_mixer="kda", gdn_k_heads=16, gdn_v_heads=16, gdn_dk=128, gdn_dv=128, kda_rank=128,
-                   attn_gate=False, qk_norm=False, norm_bias=1.0, residual="hc", mtp_layers=1, q_lora_rank=1536, dsa=True)
+                   full_interval=4, linear_mixer="kda", gdn_k_heads=64, gdn_v_heads=64, gdn_dk=128, gdn_dv=128, kda_rank=128,
+                   attn_gate=False, qk_norm=False, norm_bias=1.0, residual="hc", mtp_layers=1, q_lora_rank=1536, dsa=True,
+                   qk_nope=192, v_head_dim=256)
 
     @classmethod
     def tiny_glm5(cls, **kw):

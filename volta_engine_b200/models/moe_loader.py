@@ -166,6 +166,24 @@ def _load_mla(model, src, L, p, kw):
     L.q_norm = L.k_norm = None
 
 
+def load_head(model, src, embed_name: str, nvfp4_head: bool = False, gemm_mode: str | None = None) -> None:
+    """This rank's vocabulary shard of the output head (``lm_head.weight``, or the embedding when they are tied), padded
+    with zero rows to the shard size; NVFP4 when asked for and the shapes allow it (a quarter of the bytes a decode step
+    streams for it)."""
+    cfg, dev, bf = model.cfg, model.device, torch.bfloat16
+    head_name = "lm_head.weight" if src.has("lm_head.weight") and not cfg.tie_embeddings else embed_name
+    full = src.tensor(head_name, None, bf)
+    head = torch.zeros(model.vocab_local, cfg.hidden, dtype=bf)
+    lo = model.comm.rank * model.vocab_local
+    hi = min(cfg.vocab, lo + model.vocab_local)
+    if hi > lo:
+        head[: hi - lo] = full[lo:hi]
+    if nvfp4_head and cfg.hidden % 128 == 0 and model.vocab_local % 128 == 0:
+        model.lm_head = LinearNVFP4.from_dense(head.float().to(dev), gemm_mode or cfg.gemm_mode, search=True).prepare()
+    else:
+        model.lm_head = LinearBF16(head.to(dev))
+
+
 def load_moe_family(hf: dict, src: TensorSource, device, comm, gemm_mode="w4a16", quantize=None, nvfp4_head: bool = False):
     cfg = moe_config_from_hf(hf)
     cfg.gemm_mode = gemm_mode
@@ -189,19 +207,7 @@ def load_moe_family(hf: dict, src: TensorSource, device, comm, gemm_mode="w4a16"
     for li in range(cfg.n_layers):
         model.layers.append(load_layer(li))
     model.final_norm = src.tensor("model.norm.weight", dev, bf)
-    head_name = "lm_head.weight" if src.has("lm_head.weight") and not cfg.tie_embeddings else "model.embed_tokens.weight"
-    full = src.tensor(head_name, None, bf)
-    head = torch.zeros(model.vocab_local, cfg.hidden, dtype=bf)
-    lo = model.comm.rank * model.vocab_local
-    hi = min(cfg.vocab, lo + model.vocab_local)
-    if hi > lo:
-        head[: hi - lo] = full[lo:hi]
-    # nvfp4_dense = head: the head as NVFP4 (a quarter of the bytes a decode step streams for it)
-    if nvfp4_head and cfg.hidden % 128 == 0 and model.vocab_local % 128 == 0:
-        from ..ops.linear import LinearNVFP4
-        model.lm_head = LinearNVFP4.from_dense(head.float().to(dev), gemm_mode, search=True).prepare()
-    else:
-        model.lm_head = LinearBF16(head.to(dev))
+    load_head(model, src, "model.embed_tokens.weight", nvfp4_head, gemm_mode)
     if mla and cfg.mtp_layers and src.has(f"model.layers.{cfg.n_layers}.eh_proj.weight"):
         p = f"model.layers.{cfg.n_layers}."
         block = load_layer(cfg.n_layers)
