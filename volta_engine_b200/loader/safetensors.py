@@ -39,7 +39,7 @@ def write_safetensors(path, tensors: dict, metadata: dict | None = None, unsigne
     blobs = []
     for name in sorted(tensors):
         t = tensors[name].detach().cpu().contiguous()
-        raw = t.view(torch.uint8).reshape(-1) if t.numel() else torch.empty(0, dtype=torch.uint8)
+        raw = t.reshape(-1).view(torch.uint8) if t.numel() else torch.empty(0, dtype=torch.uint8)      # (0-dim scalars too)
         n = raw.numel()
         dt = "U16" if name in unsigned16 else _NAMES[t.dtype]
         header[name] = {"dtype": dt, "shape": list(t.shape), "data_offsets": [off, off + n]}

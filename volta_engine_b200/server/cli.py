@@ -546,7 +546,7 @@ def is_video_model_dir(model_dir: str) -> bool:
         return json.load(f).get("_class_name") == "MiniMaxH3Pipeline"
 
 
-def build_video_service(model_dir: str, out_dir: str | None = None, device=None, max_rows: int = 0):
+def build_video_service(model_dir: str, out_dir: str | None = None, device=None, max_rows: int = 0, lora_dirs=()):
     """The video pipeline of a MiniMax-H3 directory. Built: the synthetic form (``"synthetic_weights": <seed>`` in
     ``model_index.json``, optional ``"shape": "tiny"``): every component with random weights at the published or the tiny
     shape; the tensor mapping of the published checkpoints is not."""
@@ -570,6 +570,10 @@ def build_video_service(model_dir: str, out_dir: str | None = None, device=None,
         vae, aud, cfg = VaeConfig(), AudioConfig(), D.H3Config()
         tok = lambda s: [1 + (b % 150000) for b in s.encode()][:512] or [1]
         pipe = H3Pipeline(D.H3DiT(cfg, dev).init_random(seed), H3TextTower.qwen3_vl_32b(dev).init_random(seed + 7), vae, aud, tok, dev, seed)
+    if lora_dirs:
+        from ..video.lora import AdapterCatalog
+        pipe.catalog = AdapterCatalog().scan(list(lora_dirs))
+        log.info("video: %d adapter files in %s", len(pipe.catalog.all()), ", ".join(lora_dirs))
     return VideoService(pipe, out_dir or os.path.join(model_dir, "out"), max_rows=max_rows)
 
 
@@ -577,7 +581,8 @@ def _serve_video(cfg) -> int:
     import time
     from ..video.service import serve
     vopt = getattr(cfg, "video", None) or {}
-    svc = build_video_service(cfg.model_dir, vopt.get("out_dir"), max_rows=int(vopt.get("max_rows", 0)))
+    svc = build_video_service(cfg.model_dir, vopt.get("out_dir"), max_rows=int(vopt.get("max_rows", 0)),
+                              lora_dirs=tuple(vopt.get("lora_dirs", ()) or ()))
     stop = []
     srv = serve(svc, cfg.host, cfg.port, stop=lambda: bool(stop))
     log.info("video service on http://%s:%d (jobs under %s)", cfg.host, srv.port, svc.out_dir)

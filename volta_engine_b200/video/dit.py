@@ -18,8 +18,8 @@ What is here (reference: inc/engine/video/h3_dit.h, src/video/h3_dit.cu, h3_dit_
     fp32 all-reduces of the two partial projections per block.
   * ``denoise``: flow-matching Euler steps over a shifted sigma schedule (``sigma' = s sigma / (1 + (s - 1) sigma)``).
 
-Not here: the text tower (it is the dense GQA decoder family of ``models.dense`` with M-RoPE), the video / audio VAEs,
-LoRA adapters, the job service and the MP4 mux. The bf16 GEMM removes the reference's power-of-two row scaling of the
+Not here: the text tower, the video / audio VAEs, the job service and the mux (the other files of this package); LoRA
+adapters are ``video/lora.py`` (``add_lora`` / ``set_lora_scale`` / ``clear_loras`` below). The bf16 GEMM removes the reference's power-of-two row scaling of the
 gated activation (an fp16 range device).
 """
 from __future__ import annotations
@@ -169,6 +169,13 @@ class H3Block:
         self.aw, self.ab = w["adaln_w"], w["adaln_b"]                 # [6 * MODALITIES * H, adaln_dim], [6 * MODALITIES * H]
         self.n1, self.n2, self.qn, self.kn = w["norm1"], w["norm2"], w["q_norm"], w["k_norm"]
         self.sp_group = None
+        self.layer, self.adapters = 0, None          # block index and the model's list of active LoRA adapters
+
+    def _lora(self, slot: int, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        if self.adapters:
+            from .lora import apply_lora
+            apply_lora(self.adapters, self.layer, slot, x, y)
+        return y
 
     def _mod(self, temb_rows: torch.Tensor, tags: torch.Tensor):
         """Per row (shift1, scale1, gate1, shift2, scale2, gate2), each [rows, H], from its timestep and modality."""
@@ -189,7 +196,7 @@ class H3Block:
         hd, nh = cfg.head_dim, self.heads
         sh1, sc1, g1, sh2, sc2, g2 = self._mod(temb_rows, tags)
         h = rms(x, self.n1, cfg.eps) * (1 + sc1) + sh1
-        qkv = self.qkv.forward(h).float()
+        qkv = self._lora(0, h, self.qkv.forward(h).float())
         rows = x.shape[0]
         q = rms(qkv[:, : nh * hd].reshape(rows, nh, hd), self.qn, cfg.qk_eps)
         k = rms(qkv[:, nh * hd:2 * nh * hd].reshape(rows, nh, hd), self.kn, cfg.qk_eps)
@@ -203,11 +210,13 @@ class H3Block:
             att = full_attention(q.reshape(rows, nh * hd), k.reshape(rows, nh * hd), v.reshape(rows, nh * hd), nh, hd).float()
         else:
             att = attention_finish(attention_partial(q, k, v, None, hd ** -0.5))
-        x = x + g1 * self._sum(self.out.forward(att.reshape(rows, nh * hd)))
+        att = att.reshape(rows, nh * hd)
+        x = x + g1 * self._sum(self._lora(1, att, self.out.forward(att)))      # (a tensor-parallel delta is partial like the base product)
         h = rms(x, self.n2, cfg.eps) * (1 + sc2) + sh2
-        a = self.fc1.forward(h).float()
+        a = self._lora(2, h, self.fc1.forward(h).float())
         f = a.shape[1] // 2
-        return x + g2 * self._sum(self.fc2.forward(torch.nn.functional.silu(a[:, :f]) * a[:, f:]))
+        z = torch.nn.functional.silu(a[:, :f]) * a[:, f:]
+        return x + g2 * self._sum(self._lora(3, z, self.fc2.forward(z)))
 
 
 class H3DiT:
@@ -216,6 +225,7 @@ class H3DiT:
         self.tp_rank, self.tp_ranks, self.tp_group = tp_rank, tp_ranks, tp_group
         self.blocks: list[H3Block] = []
         self.sp = None
+        self.adapters: list = []                     # active LoRA adapters (video/lora.py), shared with the blocks
 
     def init_random(self, seed: int = 0, std: float = 0.02):
         """Random weights of the full architecture; a tensor-parallel instance keeps its shard (every rank draws the same
@@ -249,9 +259,23 @@ class H3DiT:
                  "q_norm": torch.ones(hd, device=dev), "k_norm": torch.ones(hd, device=dev)}
             w["adaln_b"].view(MODALITIES, 6, H)[:, (2, 5)] = 1.0          # gates start open
             self.blocks.append(H3Block(cfg, w, r, n, self.tp_group))
+            self.blocks[-1].layer, self.blocks[-1].adapters = len(self.blocks) - 1, self.adapters
         self.final_w, self.final_b = rnd(2 * H, cfg.adaln_dim, sc=0.1).to(dev), torch.zeros(2 * H, device=dev)
         self.head_v, self.head_a = rnd(cfg.latents, H).to(dev), rnd(cfg.audio_latents, H).to(dev)
         return self
+
+    def add_lora(self, path, scale: float = 1.0) -> int:
+        """Stage an adapter file beside the base weights (this rank's shard of it); returns its id."""
+        from .lora import load_adapter
+        self.adapters.append(load_adapter(path, self.cfg, scale, self.tp_rank, self.tp_ranks, self.device))
+        return len(self.adapters) - 1
+
+    def set_lora_scale(self, idx: int, scale: float) -> None:
+        if 0 <= idx < len(self.adapters):
+            self.adapters[idx].scale = float(scale)
+
+    def clear_loras(self) -> None:
+        del self.adapters[:]                          # in place: the blocks hold the same list
 
     def set_sp(self, group, rank: int, ranks: int):
         """Sequence parallelism: this instance owns a contiguous 1 / ranks of the rows of every packed sequence."""

@@ -2,6 +2,7 @@
 
     h3_generate --root <MiniMax-H3 directory> --prompt "..." [--size 1280x736] [--frames 121] [--steps 4] [--seed 0]
                 [--image first.rgb [--image last.rgb]] [--video-shift S] [--audio-shift S] [--out DIR] [--repeat N]
+                [--lora FILE[:scale]]...
 
 ``--root`` is a directory with a ``model_index.json`` of class MiniMaxH3Pipeline (the synthetic form: see
 ``server.cli.build_video_service``). Keyframes are raw RGB8 files of the job's size. Prints one JSON line per job.
@@ -33,6 +34,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default="h3_out")
     ap.add_argument("--repeat", type=int, default=1)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--lora", action="append", default=[], help="adapter file, optionally FILE:scale; repeatable")
     a = ap.parse_args(argv)
     w, h = (int(v) for v in a.size.lower().split("x"))
     svc = build_video_service(a.root, a.out, device=a.device)
@@ -44,9 +46,16 @@ def main(argv=None) -> int:
                 print(f"h3_generate: {path} is not raw RGB8 of {w}x{h}", file=sys.stderr)
                 return 2
             imgs.append((torch.frombuffer(bytearray(raw), dtype=torch.uint8).reshape(h, w, 3), 0 if i == 0 else a.frames - 1))
+        loras = []
+        for spec in a.lora:
+            path, _, sc = spec.rpartition(":")
+            if path and sc.replace(".", "", 1).replace("-", "", 1).isdigit():
+                loras.append((path, float(sc)))
+            else:
+                loras.append((spec, 1.0))
         for r in range(a.repeat):
             job = H3Job(prompt=a.prompt, width=w, height=h, frames=a.frames, steps=a.steps, seed=a.seed + r,
-                        video_shift=a.video_shift, audio_shift=a.audio_shift, images=imgs)
+                        video_shift=a.video_shift, audio_shift=a.audio_shift, images=imgs, loras=loras)
             out = svc.p.run(job, os.path.join(a.out, f"job{r}"), progress=lambda s, d, t: None)
             print(json.dumps(out))
     except ValueError as e:

@@ -97,6 +97,8 @@ class H3Pipeline:
         self.encoder = VideoEncoder(vae_cfg, device).init_random(seed + 2)
         self.audio = AudioDecoder(audio_cfg, device).init_random(seed + 3)
         self.ffmpeg = shutil.which("ffmpeg")
+        self.catalog = None                          # video.lora.AdapterCatalog of the configured directories, when there are any
+        self._staged: list = []                      # paths of the adapters the denoiser currently holds
 
     @classmethod
     def tiny(cls, device="cpu", seed: int = 0):
@@ -108,6 +110,26 @@ class H3Pipeline:
         return cls(dit, text, vae, aud, lambda s: [1 + (b % 500) for b in s.encode()][:256] or [1], device, seed)
 
     # ---- stages --------------------------------------------------------------------------------------------------
+    def stage_adapters(self, job: H3Job) -> None:
+        """The job's LoRA adapters, resolved through the catalogue (a bare file name) or as paths. The set staged by the
+        previous job is kept when it names the same files (only the scales are updated); otherwise it is replaced."""
+        want = []
+        for file, scale in job.loras:
+            info = self.catalog.find(file) if self.catalog is not None else None
+            path = info.path if info is not None else file
+            if not os.path.isfile(path):
+                raise ValueError(f"adapter {file!r} is not in the configured directories")
+            want.append((path, float(scale)))
+        if [p for p, _ in want] == self._staged:
+            for i, (_, sc) in enumerate(want):
+                self.dit.set_lora_scale(i, sc)
+            return
+        self.dit.clear_loras()
+        self._staged = []
+        for path, sc in want:
+            self.dit.add_lora(path, sc)
+            self._staged.append(path)
+
     def encode_references(self, job: H3Job, grid: tuple) -> dict:
         """{latent frame index: rows of that frame} for the keyframes of the job."""
         per = grid[1] * grid[2]
@@ -197,6 +219,7 @@ class H3Pipeline:
             if progress is not None:
                 progress(stage, d, t)
         prog("plan", 1, 1)
+        self.stage_adapters(job)
         cond = self.encode_references(job, grid)
         prog("references", 1, 1)
         prompt = self.encode_prompt(job)

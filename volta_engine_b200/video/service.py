@@ -119,7 +119,9 @@ class VideoService:
         c = self.p.dit.cfg
         return {"model": "minimax_h3", "hidden": c.hidden, "layers": c.layers, "heads": c.heads, "max_rows": self.max_rows,
                 "queued": sum(1 for j in self.jobs.values() if j["status"] == "queued"),
-                "running": sum(1 for j in self.jobs.values() if j["status"] == "running"), "ffmpeg": bool(self.p.ffmpeg)}
+                "running": sum(1 for j in self.jobs.values() if j["status"] == "running"), "ffmpeg": bool(self.p.ffmpeg),
+                "adapters": [{"file": a.file, "label": a.label, "format": a.format, "task": a.task, "turbo": a.turbo, "mb": a.mb}
+                             for a in (self.p.catalog.all() if self.p.catalog is not None else [])]}
 
     def handle(self, method: str, path: str, body: bytes = b"", headers: dict | None = None):
         def js(status, obj):
