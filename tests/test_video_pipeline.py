@@ -209,3 +209,59 @@ def test_gpu_video_job_runs(tmp_path):
     p = H3Pipeline.tiny("cuda")
     out = p.run(H3Job(prompt="tide pools", width=32, height=16, frames=5, steps=2, seed=1), str(tmp_path / "j"))
     assert out["frames"] == 5 and os.path.getsize(out["raw"]) == 5 * 16 * 32 * 3
+
+
+def test_captions_through_the_text_tower_and_the_service(tmp_path):
+    """A tower built with its last layers and head writes text: the condition rows stay those of the shorter tower, greedy
+    decoding continues the same whether the first half of an answer was decoded or prefilled, sampling is seeded, a picture
+    changes the answer; the service runs caption requests on its worker."""
+    import base64
+    import io
+    import json
+    from PIL import Image
+    from volta_engine_b200.loader.image import VisionParams
+    from volta_engine_b200.models.vision import VisionConfig, VisionTower
+    from volta_engine_b200.runtime.multimodal import MultimodalFrontend
+    from volta_engine_b200.video.service import VideoService
+    from volta_engine_b200.video.text import H3Captioner, H3TextTower
+    t, short = H3TextTower.tiny(captioner=True).init_random(1), H3TextTower.tiny().init_random(1)
+    assert t.can_generate and not short.can_generate and t.cfg.n_layers == short.cfg.n_layers + 1
+    ids = [5, 6, 7, 8, 9, 10]
+    assert torch.equal(t.encode(ids), short.encode(ids))
+    prompt = list(range(10, 40))
+    a = t.generate(prompt, 12)
+    assert len(a) == 12 and t.generate(prompt + a[:6], 6) == a[6:]
+    assert t.generate(prompt, 12, forced=a[:5]) == a
+    assert t.generate(prompt, 12, eos_ids=(a[3],)) == a[:4]
+    s1, s2 = t.generate(prompt, 12, temperature=0.7, seed=1), t.generate(prompt, 12, temperature=0.7, seed=1)
+    assert s1 == s2 and t.generate(prompt, 12, temperature=5.0, seed=2) != s1
+    assert "user's idea" in H3Captioner.instruction("a  kite\n") and "a kite" in H3Captioner.instruction("a  kite\n")
+    p = H3Pipeline.tiny(captioner=True)
+    vt = VisionTower(VisionConfig(out_hidden=64), "cpu").init_random(2)
+    fe = MultimodalFrontend(vt, VisionParams(min_pixels=32 * 32, max_pixels=64 * 64), image_token_id=400)
+    cap = p.attach_captioner(lambda ids: bytes(32 + (i % 90) for i in ids).decode(), fe, 400, eos_ids=(0,), max_new=10)
+    buf = io.BytesIO()
+    Image.fromarray(torch.randint(0, 255, (48, 64, 3), dtype=torch.uint8).numpy()).save(buf, format="PNG")
+    with_pic, without = cap.caption(buf.getvalue(), "", greedy=True), cap.caption(None, "", greedy=True)
+    assert with_pic and without and with_pic != without and cap.caption(buf.getvalue(), "", greedy=True) == with_pic
+    svc = VideoService(p, str(tmp_path / "out"))
+    try:
+        st, _, body, _ = svc.handle("POST", "/api/caption", json.dumps({"image": base64.b64encode(buf.getvalue()).decode(), "greedy": True}).encode())
+        cid = json.loads(body)["id"]
+        assert st == 200
+        for _ in range(500):
+            rec = json.loads(svc.handle("GET", f"/api/caption/{cid}")[2])
+            if rec["status"] in ("done", "failed"):
+                break
+            import time
+            time.sleep(0.02)
+        assert rec["status"] == "done" and rec["text"] == with_pic and "_image" not in rec
+        assert svc.handle("POST", "/api/caption", b"{}")[0] == 400 and svc.handle("GET", "/api/caption/nope")[0] == 404
+        assert json.loads(svc.handle("GET", "/api/info")[2])["captioner"] is True
+    finally:
+        svc.stop()
+    plain = VideoService(H3Pipeline.tiny(), str(tmp_path / "out2"))
+    try:
+        assert plain.handle("POST", "/api/caption", json.dumps({"prompt": "x"}).encode())[0] == 400
+    finally:
+        plain.stop()

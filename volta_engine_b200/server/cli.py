@@ -546,7 +546,8 @@ def is_video_model_dir(model_dir: str) -> bool:
         return json.load(f).get("_class_name") == "MiniMaxH3Pipeline"
 
 
-def build_video_service(model_dir: str, out_dir: str | None = None, device=None, max_rows: int = 0, lora_dirs=()):
+def build_video_service(model_dir: str, out_dir: str | None = None, device=None, max_rows: int = 0, lora_dirs=(),
+                        captioner: bool = False):
     """The video pipeline of a MiniMax-H3 directory. Built: the synthetic form (``"synthetic_weights": <seed>`` in
     ``model_index.json``, optional ``"shape": "tiny"``): every component with random weights at the published or the tiny
     shape; the tensor mapping of the published checkpoints is not."""
@@ -565,11 +566,14 @@ def build_video_service(model_dir: str, out_dir: str | None = None, device=None,
     seed = int(idx["synthetic_weights"])
     dev = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
     if idx.get("shape", "full") == "tiny":
-        pipe = H3Pipeline.tiny(dev, seed)
+        pipe = H3Pipeline.tiny(dev, seed, captioner=captioner)
     else:
         vae, aud, cfg = VaeConfig(), AudioConfig(), D.H3Config()
         tok = lambda s: [1 + (b % 150000) for b in s.encode()][:512] or [1]
-        pipe = H3Pipeline(D.H3DiT(cfg, dev).init_random(seed), H3TextTower.qwen3_vl_32b(dev).init_random(seed + 7), vae, aud, tok, dev, seed)
+        text = H3TextTower.qwen3_vl_32b(dev, captioner=captioner).init_random(seed + 7)
+        pipe = H3Pipeline(D.H3DiT(cfg, dev).init_random(seed), text, vae, aud, tok, dev, seed)
+        if captioner:
+            pipe.attach_captioner(lambda ids: bytes(32 + (i % 90) for i in ids).decode(), eos_ids=(151645,))
     if lora_dirs:
         from ..video.lora import AdapterCatalog
         pipe.catalog = AdapterCatalog().scan(list(lora_dirs))
@@ -582,7 +586,7 @@ def _serve_video(cfg) -> int:
     from ..video.service import serve
     vopt = getattr(cfg, "video", None) or {}
     svc = build_video_service(cfg.model_dir, vopt.get("out_dir"), max_rows=int(vopt.get("max_rows", 0)),
-                              lora_dirs=tuple(vopt.get("lora_dirs", ()) or ()))
+                              lora_dirs=tuple(vopt.get("lora_dirs", ()) or ()), captioner=bool(vopt.get("captioner", False)))
     stop = []
     srv = serve(svc, cfg.host, cfg.port, stop=lambda: bool(stop))
     log.info("video service on http://%s:%d (jobs under %s)", cfg.host, srv.port, svc.out_dir)

@@ -3,6 +3,7 @@
     h3_generate --root <MiniMax-H3 directory> --prompt "..." [--size 1280x736] [--frames 121] [--steps 4] [--seed 0]
                 [--image first.rgb [--image last.rgb]] [--video-shift S] [--audio-shift S] [--out DIR] [--repeat N]
                 [--lora FILE[:scale]]...
+    h3_generate --root <directory> --caption IMAGE [--prompt GUIDANCE]      a detailed video prompt for a picture
 
 ``--root`` is a directory with a ``model_index.json`` of class MiniMaxH3Pipeline (the synthetic form: see
 ``server.cli.build_video_service``). Keyframes are raw RGB8 files of the job's size. Prints one JSON line per job.
@@ -34,11 +35,15 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default="h3_out")
     ap.add_argument("--repeat", type=int, default=1)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--caption", default="", help="picture file (PNG / JPEG): write a video prompt for it instead of a video")
     ap.add_argument("--lora", action="append", default=[], help="adapter file, optionally FILE:scale; repeatable")
     a = ap.parse_args(argv)
     w, h = (int(v) for v in a.size.lower().split("x"))
-    svc = build_video_service(a.root, a.out, device=a.device)
+    svc = build_video_service(a.root, a.out, device=a.device, captioner=bool(a.caption))
     try:
+        if a.caption:
+            print(json.dumps({"caption": svc.p.captioner.caption(open(a.caption, "rb").read(), a.prompt, seed=a.seed)}))
+            return 0
         imgs = []
         for i, path in enumerate(a.image[:2]):
             raw = open(path, "rb").read()

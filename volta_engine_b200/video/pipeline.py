@@ -98,16 +98,35 @@ class H3Pipeline:
         self.audio = AudioDecoder(audio_cfg, device).init_random(seed + 3)
         self.ffmpeg = shutil.which("ffmpeg")
         self.catalog = None                          # video.lora.AdapterCatalog of the configured directories, when there are any
+        self.captioner = None                        # video.text.H3Captioner when the text tower was built with all its layers
         self._staged: list = []                      # paths of the adapters the denoiser currently holds
 
     @classmethod
-    def tiny(cls, device="cpu", seed: int = 0):
+    def tiny(cls, device="cpu", seed: int = 0, captioner: bool = False):
         from .text import H3TextTower
         vae, aud = VaeConfig.tiny(), AudioConfig.tiny()
         cfg = D.H3Config.tiny(latents=vae.latent * 4, audio_latents=aud.latent, text_dim=64)
         dit = D.H3DiT(cfg, device).init_random(seed)
-        text = H3TextTower.tiny(device, hidden=64).init_random(seed + 7)
-        return cls(dit, text, vae, aud, lambda s: [1 + (b % 500) for b in s.encode()][:256] or [1], device, seed)
+        text = H3TextTower.tiny(device, hidden=64, captioner=captioner).init_random(seed + 7)
+        tok = lambda s: [1 + (b % 500) for b in s.encode()][:256] or [1]
+        p = cls(dit, text, vae, aud, tok, device, seed)
+        if captioner:
+            p.attach_captioner(lambda ids: bytes(32 + (i % 90) for i in ids).decode(), eos_ids=(0,), max_new=24)
+        return p
+
+    def attach_captioner(self, detokenize, frontend=None, image_token_id=None, eos_ids=(), max_new: int = 400):
+        """Captions through the text tower (it must have been built with all its layers); ``frontend`` turns picture bytes
+        into embedding rows (without one a caption is written from the prompt box alone)."""
+        from .text import H3Captioner
+        tok = self.tokenize
+        if frontend is not None and image_token_id is not None:
+            def tok(s, base=self.tokenize, pad=image_token_id):        # the placeholder becomes the image token id
+                out = []
+                for i, part in enumerate(s.split("<|image_pad|>")):
+                    out += ([pad] if i else []) + (base(part) if part else [])
+                return out
+        self.captioner = H3Captioner(self.text, tok, detokenize, frontend, image_token_id, eos_ids, max_new)
+        return self.captioner
 
     # ---- stages --------------------------------------------------------------------------------------------------
     def stage_adapters(self, job: H3Job) -> None:

@@ -8,6 +8,8 @@ Routes (reference: docs/video.md:93-104, src/server/video/*):
   POST /api/jobs/<id>/cancel
   GET  /api/jobs/<id>/video              the MP4 when ffmpeg muxed one, else the raw RGB8 frames (Range supported)
   GET  /api/jobs/<id>/thumb
+  POST /api/caption     GET /api/caption/<id>   with a captioner: {image: base64 PNG / JPEG, prompt} -> a detailed video
+                                         prompt; runs between jobs, ahead of the queued ones
   GET  /health
 ``handle(method, path, body, headers)`` returns (status, content type, bytes, extra headers) so any HTTP front end can
 mount it; ``serve`` runs it on the engine's epoll server.
@@ -33,6 +35,8 @@ class VideoService:
         os.makedirs(out_dir, exist_ok=True)
         self.jobs: dict[str, dict] = {}
         self.q: queue.Queue = queue.Queue()
+        self.captions: dict[str, dict] = {}           # caption requests: they run between jobs, ahead of the queued ones
+        self.cq: queue.Queue = queue.Queue()
         self.lock = threading.Lock()
         self.stop_flag = False
         self.worker = threading.Thread(target=self._work, name="video-worker", daemon=True)
@@ -82,10 +86,42 @@ class VideoService:
             if j is not None and j["status"] != "running":
                 del self.jobs[jid]
 
+    def submit_caption(self, body: dict) -> dict:
+        """{image: base64 of an encoded picture (PNG / JPEG), prompt: optional text of the prompt box} -> the request's
+        record; the text arrives in it once the worker has run it."""
+        cap = getattr(self.p, "captioner", None)
+        if cap is None:
+            raise ValueError("the captioner is not configured (video.captioner)")
+        img = base64.b64decode(body["image"]) if body.get("image") else None
+        if img is None and not str(body.get("prompt", "")).strip():
+            raise ValueError("a caption needs a picture or a prompt")
+        cid = uuid.uuid4().hex[:12]
+        self.captions[cid] = {"id": cid, "status": "queued", "text": None, "error": None, "submitted": time.time(),
+                              "_image": img, "_idea": str(body.get("prompt", "")), "_greedy": bool(body.get("greedy", False)),
+                              "_seed": int(body.get("seed", 0))}
+        self.cq.put(cid)
+        return {k: v for k, v in self.captions[cid].items() if not k.startswith("_")}
+
+    def _caption(self, cid: str) -> None:
+        c = self.captions[cid]
+        c["status"] = "running"
+        try:
+            c["text"] = self.p.captioner.caption(c["_image"], c["_idea"], greedy=c["_greedy"], seed=c["_seed"])
+            c["status"] = "done"
+        except Exception as e:                      # a failed caption must not take the worker down
+            c["status"], c["error"] = "failed", f"{type(e).__name__}: {e}"
+        c["_image"] = None
+        c["finished"] = time.time()
+
     def _work(self):
         while not self.stop_flag:
             try:
-                jid = self.q.get(timeout=0.2)
+                self._caption(self.cq.get_nowait())
+                continue
+            except queue.Empty:
+                pass
+            try:
+                jid = self.q.get(timeout=0.05)
             except queue.Empty:
                 continue
             j = self.jobs.get(jid)
@@ -120,7 +156,7 @@ class VideoService:
         return {"model": "minimax_h3", "hidden": c.hidden, "layers": c.layers, "heads": c.heads, "max_rows": self.max_rows,
                 "queued": sum(1 for j in self.jobs.values() if j["status"] == "queued"),
                 "running": sum(1 for j in self.jobs.values() if j["status"] == "running"), "ffmpeg": bool(self.p.ffmpeg),
-                "adapters": [{"file": a.file, "label": a.label, "format": a.format, "task": a.task, "turbo": a.turbo, "mb": a.mb}
+                "captioner": getattr(self.p, "captioner", None) is not None, "adapters": [{"file": a.file, "label": a.label, "format": a.format, "task": a.task, "turbo": a.turbo, "mb": a.mb}
                              for a in (self.p.catalog.all() if self.p.catalog is not None else [])]}
 
     def handle(self, method: str, path: str, body: bytes = b"", headers: dict | None = None):
@@ -137,6 +173,12 @@ class VideoService:
                 return js(200, {"jobs": [self.public(i) for i in sorted(self.jobs, key=lambda i: self.jobs[i]["submitted"])]})
             if path == "/api/jobs" and method == "POST":
                 return js(200, self.submit(json.loads(body or b"{}")))
+            if path == "/api/caption" and method == "POST":
+                return js(200, self.submit_caption(json.loads(body or b"{}")))
+            if len(parts) == 3 and parts[:2] == ["api", "caption"] and method == "GET":
+                if parts[2] not in self.captions:
+                    return js(404, {"error": "no such caption"})
+                return js(200, {k: v for k, v in self.captions[parts[2]].items() if not k.startswith("_")})
             if len(parts) >= 3 and parts[:2] == ["api", "jobs"]:
                 jid = parts[2]
                 if jid not in self.jobs:
