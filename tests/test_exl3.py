@@ -33,6 +33,45 @@ def test_window_extraction_matches_a_bit_by_bit_reader():
             assert int(win[p]) == v
 
 
+def test_half_integer_rate_windows_follow_the_funnel_shift_reader(tmp_path):
+    """Rates K + 0.5 (16 K + 8 code words per tile): the windows advance by K and K + 1 bits alternately. The vectorised
+    reader is checked against a literal 64-bit funnel-shift reader of the same stream (two 32-bit words merged high word
+    first, shifted so that the window's end bit lands at bit 0), then through a linear loaded from a checkpoint."""
+    g = torch.Generator().manual_seed(4)
+    for K in (1, 2, 3, 4):
+        codes = ex.random_codes(16, 16, K + 0.5, g)[0, 0]
+        assert codes.numel() == 16 * K + 8 and ex.is_half_rate(codes)
+        nwords = 4 * (2 * K + 1)
+        words = [(int(codes[2 * i]) & 0xFFFF) | ((int(codes[2 * i + 1]) & 0xFFFF) << 16) for i in range(nwords)]
+        win = ex.tile_windows(codes[None], K)[0]
+        bits2 = 2 * K + 1
+        for p in (0, 1, 2, 3, 6, 7, 100, 101, 254, 255):
+            end = (p // 2 + 1) * bits2 - (0 if p % 2 else K + 1) + 128 * bits2          # one tile ahead: the stream wraps
+            hi, lo = (end - 1) // 32, (end - 16) // 32
+            merged = (words[lo % nwords] << 32) | words[hi % nwords] if hi != lo else (words[lo % nwords] << 32) | words[lo % nwords]
+            shift = (hi + 1) * 32 - end
+            if hi == lo:
+                v = (words[lo % nwords] >> shift) & 0xFFFF
+            else:
+                v = (merged >> shift) & 0xFFFF
+            assert int(win[p]) == v, (K, p)
+    # a 2.5 bit linear: the map is that of its decoded tiles, and a checkpoint with such a tensor loads
+    from volta_engine_b200.loader.safetensors import SafeTensorsRepo, write_safetensors
+    from volta_engine_b200.ops.linear_exl3 import LinearEXL3
+    codes = ex.random_codes(128, 256, 2.5, g)
+    suh = (torch.randint(0, 2, (128,), generator=g).float() * 2 - 1).half()
+    svh = ((torch.randint(0, 2, (256,), generator=g).float() * 2 - 1) * 0.05).half()
+    write_safetensors(tmp_path / "m.safetensors", {"l.trellis": codes, "l.suh": suh, "l.svh": svh, "l.mul1": torch.zeros(1, dtype=torch.int32)},
+                      unsigned16=("l.trellis",))
+    lin = SafeTensorsRepo(tmp_path).load_linear("l")
+    assert isinstance(lin, LinearEXL3) and lin.bits == 2 and lin.half and lin.cb == ex.CB_MUL1
+    W = ex.reconstruct(codes, 2, ex.CB_MUL1)
+    assert W.shape == (128, 256) and 0.8 < float(W.std()) < 1.2           # random windows decode to a near-unit Gaussian
+    x = torch.randn(3, 128, generator=g)
+    want = ex.had128(ex.had128(x * suh.float()) @ W) * svh.float()
+    assert torch.allclose(lin.forward(x, out_f32=True), want, atol=1e-5)
+
+
 def test_codebooks_are_near_unit_gaussians():
     w = torch.arange(65536)
     for cb, lo, hi in ((ex.CB_MUL1, 0.95, 1.05), (ex.CB_3INST, 1.1, 1.4), (ex.CB_MCG, 1.1, 1.4)):

@@ -191,8 +191,8 @@ class SafeTensorsRepo:
         codes = self.load(base + ".trellis")
         suh, svh = self.load(base + ".suh"), self.load(base + ".svh")
         bits = codes.shape[-1] // 16
-        if codes.shape[-1] % 16:
-            raise NotImplementedError(f"{base}: half-integer EXL3 rates are not supported")
+        if codes.shape[-1] % 16 not in (0, 8):
+            raise ValueError(f"{base}: {codes.shape[-1]} code words per tile is neither an integer nor a half-integer rate")
         if self.has(base + ".tstart") or self.has(base + ".tgain"):
             raise NotImplementedError(f"{base}: per-tile start / gain side tensors are not supported")
         cb = ex.CB_MUL1 if self.has(base + ".mul1") else ex.CB_MCG if self.has(base + ".mcg") else ex.CB_3INST

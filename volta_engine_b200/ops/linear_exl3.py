@@ -59,14 +59,17 @@ def exl3_viterbi(targets: torch.Tensor, bits: int, cb: int = ex.CB_MUL1, ctas: i
 
 
 class LinearEXL3:
-    """codes int16 [K/16, N/16, 16*bits]; suh fp16 [K]; svh fp16 [N]; optional bias."""
+    """codes int16 [K/16, N/16, 16*bits] (16*bits + 8 for the half-integer rate bits + 0.5); suh fp16 [K]; svh fp16 [N];
+    optional bias."""
 
     def __init__(self, codes, suh, svh, bits: int | None = None, cb: int = ex.CB_MUL1, bias=None,
                  layout: str = "stock"):
         self.codes = codes.contiguous()
         self.layout = layout          # "volta": tiles in the reference engine's lane order
         self._dense = None            # bf16 expansion used on the GPU for the non-stock order
-        self.bits = bits if bits is not None else codes.shape[-1] // 16
+        self.bits = int(bits) if bits is not None else codes.shape[-1] // 16
+        self.half = ex.is_half_rate(codes)       # rate bits + 0.5 (16 * bits + 8 code words per tile): no device decoder,
+                                                 # expanded to bf16 when it moves to a GPU
         self.cb = cb
         self.in_features, self.out_features = codes.shape[0] * 16, codes.shape[1] * 16
         self.suh, self.svh = suh.to(torch.float16).contiguous(), svh.to(torch.float16).contiguous()
@@ -82,7 +85,7 @@ class LinearEXL3:
         return cls(*ex.quantize(w.t().contiguous().float(), bits), bits=bits)
 
     def to(self, device):
-        if self.layout != "stock" and torch.device(device).type == "cuda" and self._dense is None:
+        if (self.layout != "stock" or self.half) and torch.device(device).type == "cuda" and self._dense is None:
             w = ex.reconstruct(self.codes.cpu(), self.bits, self.cb, self.layout)
             self._dense = w.t().contiguous().to(torch.bfloat16).to(device)
         self.codes, self.suh, self.svh = self.codes.to(device), self.suh.to(device), self.svh.to(device)

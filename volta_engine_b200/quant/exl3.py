@@ -55,17 +55,29 @@ def _tile_positions(layout: str = "stock"):
     return row, col
 
 
+def is_half_rate(codes: torch.Tensor) -> bool:
+    """A tile of 16 K + 8 code words holds the half-integer rate K + 0.5."""
+    return codes.shape[-1] % 16 == 8
+
+
 def tile_windows(codes: torch.Tensor, bits: int) -> torch.Tensor:
-    """codes uint16/int [..., 16*bits] -> windows int64 [..., 256] in position order."""
+    """codes uint16/int [..., 16*bits] -> windows int64 [..., 256] in position order.
+
+    Half-integer rates (last dim 16 * bits + 8, the rate bits + 0.5): the windows of a tile advance by ``bits`` and
+    ``bits + 1`` bits alternately, so position 2 j ends at bit j (2 bits + 1) + bits and position 2 j + 1 at
+    (j + 1) (2 bits + 1); the stream is cyclic over the tile like the integer rates'."""
     c = codes.to(torch.int64) & 0xFFFF
-    nw = 8 * bits                                               # 32-bit words per tile
+    half = c.shape[-1] == 16 * bits + 8
+    assert half or c.shape[-1] == 16 * bits, f"{c.shape[-1]} code words per tile do not hold {bits} (or {bits}.5) bits per weight"
+    nw = c.shape[-1] // 2                                       # 32-bit words per tile
     words = c[..., 0::2] | (c[..., 1::2] << 16)                 # little-endian pairs
-    total = 256 * bits
+    total = nw * 32
     # expand the stream to bits (MSB first inside a word), cyclic
     shifts = torch.arange(31, -1, -1, device=c.device)
-    stream = ((words[..., :, None] >> shifts) & 1).reshape(*c.shape[:-1], nw * 32)
+    stream = ((words[..., :, None] >> shifts) & 1).reshape(*c.shape[:-1], total)
     p = torch.arange(256, device=c.device)
-    start = (p * bits + bits - 16) % total
+    end = ((p // 2) * (2 * bits + 1) + torch.where(p % 2 == 0, bits, 2 * bits + 1)) if half else (p + 1) * bits
+    start = (end - 16) % total
     idx = (start[:, None] + torch.arange(16, device=c.device)[None, :]) % total          # [256, 16]
     win_bits = stream[..., idx]                                                           # [..., 256, 16]
     weights = (1 << torch.arange(15, -1, -1, device=c.device)).to(torch.int64)
@@ -73,7 +85,8 @@ def tile_windows(codes: torch.Tensor, bits: int) -> torch.Tensor:
 
 
 def reconstruct(codes: torch.Tensor, bits: int, cb: int = CB_MUL1, layout: str = "stock") -> torch.Tensor:
-    """codes [K/16, N/16, 16*bits] -> W fp32 [K, N] in the rotated basis (no suh / svh)."""
+    """codes [K/16, N/16, 16*bits] (or 16*bits + 8: the rate bits + 0.5) -> W fp32 [K, N] in the rotated basis (no suh /
+    svh)."""
     KT, NT = codes.shape[0], codes.shape[1]
     vals = decode_windows(tile_windows(codes, bits), cb)        # [KT, NT, 256]
     row, col = _tile_positions(layout)
@@ -113,7 +126,8 @@ def effective_weight(codes, bits, suh, svh, cb=CB_MUL1, layout="stock") -> torch
 def random_codes(K: int, N: int, bits: int, gen: torch.Generator | None = None, device="cpu") -> torch.Tensor:
     """Uniform random bit streams. Random windows decode to a near-Gaussian unit-variance codebook value, which is
     what a trellis encoding of random N(0, sigma) weights looks like once sigma sits in the suh / svh scales."""
-    return torch.randint(0, 65536, (K // 16, N // 16, 16 * bits), generator=gen, device=device, dtype=torch.int32).to(torch.int16)
+    words = int(16 * bits)                                    # bits may be K + 0.5: 16 K + 8 code words per tile
+    return torch.randint(0, 65536, (K // 16, N // 16, words), generator=gen, device=device, dtype=torch.int32).to(torch.int16)
 
 
 def synth_linear(K: int, N: int, bits: int, std: float = 0.02, gen=None, device="cpu"):
