@@ -72,6 +72,52 @@ def test_half_integer_rate_windows_follow_the_funnel_shift_reader(tmp_path):
     assert torch.allclose(lin.forward(x, out_f32=True), want, atol=1e-5)
 
 
+def test_extended_trellis_start_states_and_tile_gains(tmp_path):
+    """Open-trellis tiles: the windows are those of the plain (not cyclic) bit string "16 bits of start state + the tile's
+    stream"; a gain code c scales a tile by (896 + c) / 1024; a checkpoint with the two side tensors loads and slices."""
+    from volta_engine_b200.loader.safetensors import SafeTensorsRepo, write_safetensors
+    g = torch.Generator().manual_seed(6)
+    for bits in (2, 3, 4, 5, 8):
+        codes = ex.random_codes(16, 16, bits, g)[0, 0]
+        start = int(torch.randint(0, 65536, (1,), generator=g))
+        words = [(int(codes[2 * i]) & 0xFFFF) | ((int(codes[2 * i + 1]) & 0xFFFF) << 16) for i in range(8 * bits)]
+        string = [(start >> (15 - b)) & 1 for b in range(16)] + [(w >> (31 - b)) & 1 for w in words for b in range(32)]
+        win = ex.tile_windows(codes[None], bits, torch.tensor([start]))[0]
+        ring = ex.tile_windows(codes[None], bits)[0]
+        for p in range(256):
+            v = 0
+            for bit in string[(p + 1) * bits:(p + 1) * bits + 16]:
+                v = (v << 1) | bit
+            assert int(win[p]) == v, (bits, p)
+            if (p + 1) * bits >= 16:
+                assert int(ring[p]) == v                     # past the first 16 bits the two readers agree
+    K, N, bits = 128, 256, 3
+    codes, suh, svh = ex.synth_linear(K, N, bits, 0.05, g)
+    tstart = torch.randint(0, 65536, (K // 16, N // 16), generator=g, dtype=torch.int32).to(torch.int16)
+    tgain = torch.randint(0, 256, (K // 16, N // 16), generator=g, dtype=torch.int32).to(torch.uint8)
+    plain, ext = ex.reconstruct(codes, bits), ex.reconstruct(codes, bits, tstart=tstart, tgain=tgain)
+    gains = ex.tile_gain(tgain)
+    assert float(gains.min()) >= 0.875 and float(gains.max()) <= 1151 / 1024
+    t_plain = plain.reshape(K // 16, 16, N // 16, 16).permute(0, 2, 1, 3)
+    t_ext = ex.reconstruct(codes, bits, tstart=tstart).reshape(K // 16, 16, N // 16, 16).permute(0, 2, 1, 3)
+    changed = (t_plain != t_ext).reshape(K // 16, N // 16, -1).sum(-1)
+    assert int(changed.max()) <= 5 and int(changed.sum()) > 0          # only a tile's first windows (16 / bits of them) see the start state
+    want = (t_ext * gains[..., None, None]).to(torch.float16).float().permute(0, 2, 1, 3).reshape(K, N)
+    assert torch.equal(ext, want)
+    write_safetensors(tmp_path / "m.safetensors", {"l.trellis": codes, "l.suh": suh, "l.svh": svh, "l.tstart": tstart.reshape(-1),
+                                                  "l.tgain": tgain.reshape(-1), "l.mul1": torch.zeros(1, dtype=torch.int32)},
+                      unsigned16=("l.trellis", "l.tstart"))
+    repo = SafeTensorsRepo(tmp_path)
+    lin = repo.load_linear("l")
+    x = torch.randn(2, K, generator=g)
+    full = lin.forward(x, out_f32=True)
+    assert torch.allclose(full, ex.had128(ex.had128(x * suh.float()) @ ext) * svh.float(), atol=1e-5)
+    assert not torch.allclose(full, ex.had128(ex.had128(x * suh.float()) @ plain) * svh.float(), atol=1e-4)
+    cols = torch.cat([repo.load_linear("l", "col", r, 2).forward(x, out_f32=True) for r in range(2)], -1)
+    assert torch.allclose(cols, full, atol=1e-4)
+    assert torch.allclose(lin.dequant().t(), ex.effective_weight(codes, bits, suh, svh, tstart=tstart, tgain=tgain), atol=1e-6)
+
+
 def test_codebooks_are_near_unit_gaussians():
     w = torch.arange(65536)
     for cb, lo, hi in ((ex.CB_MUL1, 0.95, 1.05), (ex.CB_3INST, 1.1, 1.4), (ex.CB_MCG, 1.1, 1.4)):

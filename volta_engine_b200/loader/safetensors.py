@@ -193,15 +193,18 @@ class SafeTensorsRepo:
         bits = codes.shape[-1] // 16
         if codes.shape[-1] % 16 not in (0, 8):
             raise ValueError(f"{base}: {codes.shape[-1]} code words per tile is neither an integer nor a half-integer rate")
-        if self.has(base + ".tstart") or self.has(base + ".tgain"):
-            raise NotImplementedError(f"{base}: per-tile start / gain side tensors are not supported")
+        tstart = self.load(base + ".tstart") if self.has(base + ".tstart") else None      # extended trellis: per-tile
+        tgain = self.load(base + ".tgain") if self.has(base + ".tgain") else None          # start states / gain codes
+        if (tstart is not None or tgain is not None) and codes.shape[-1] % 16:
+            raise ValueError(f"{base}: the extended trellis is defined for integer rates")
         cb = ex.CB_MUL1 if self.has(base + ".mul1") else ex.CB_MCG if self.has(base + ".mcg") else ex.CB_3INST
         layout = "volta" if self.tile_layout == "volta" and base not in self.tile_layout_stock else "stock"
         K, N = codes.shape[0] * 16, codes.shape[1] * 16
         k0, k1 = self._range(K, "row" if split == "row" else None, rank, world, 128)
         n0, n1 = self._range(N, "col" if split == "col" else None, rank, world, 128)
+        tiles = lambda t: None if t is None else t.reshape(K // 16, N // 16)[k0 // 16:k1 // 16, n0 // 16:n1 // 16].contiguous()
         lin = LinearEXL3(codes[k0 // 16:k1 // 16, n0 // 16:n1 // 16].contiguous(), suh[k0:k1].contiguous(),
-                         svh[n0:n1].contiguous(), bits=bits, cb=cb, layout=layout)
+                         svh[n0:n1].contiguous(), bits=bits, cb=cb, layout=layout, tstart=tiles(tstart), tgain=tiles(tgain))
         if self.has(base + ".bias"):
             b = self.load(base + ".bias")
             lin.bias = b[n0:n1].contiguous() if (split != "row" or rank == 0) else None

@@ -63,13 +63,14 @@ class LinearEXL3:
     optional bias."""
 
     def __init__(self, codes, suh, svh, bits: int | None = None, cb: int = ex.CB_MUL1, bias=None,
-                 layout: str = "stock"):
+                 layout: str = "stock", tstart=None, tgain=None):
         self.codes = codes.contiguous()
         self.layout = layout          # "volta": tiles in the reference engine's lane order
         self._dense = None            # bf16 expansion used on the GPU for the non-stock order
         self.bits = int(bits) if bits is not None else codes.shape[-1] // 16
+        self.tstart, self.tgain = tstart, tgain  # extended trellis: per-tile start states / gain codes [K/16, N/16] or None
         self.half = ex.is_half_rate(codes)       # rate bits + 0.5 (16 * bits + 8 code words per tile): no device decoder,
-                                                 # expanded to bf16 when it moves to a GPU
+                                                 # expanded to bf16 when it moves to a GPU (so is an extended trellis)
         self.cb = cb
         self.in_features, self.out_features = codes.shape[0] * 16, codes.shape[1] * 16
         self.suh, self.svh = suh.to(torch.float16).contiguous(), svh.to(torch.float16).contiguous()
@@ -85,8 +86,10 @@ class LinearEXL3:
         return cls(*ex.quantize(w.t().contiguous().float(), bits), bits=bits)
 
     def to(self, device):
-        if (self.layout != "stock" or self.half) and torch.device(device).type == "cuda" and self._dense is None:
-            w = ex.reconstruct(self.codes.cpu(), self.bits, self.cb, self.layout)
+        ext = self.tstart is not None or self.tgain is not None
+        if (self.layout != "stock" or self.half or ext) and torch.device(device).type == "cuda" and self._dense is None:
+            w = ex.reconstruct(self.codes.cpu(), self.bits, self.cb, self.layout,
+                               None if self.tstart is None else self.tstart.cpu(), None if self.tgain is None else self.tgain.cpu())
             self._dense = w.t().contiguous().to(torch.bfloat16).to(device)
         self.codes, self.suh, self.svh = self.codes.to(device), self.suh.to(device), self.svh.to(device)
         if self.bias is not None:
@@ -95,13 +98,14 @@ class LinearEXL3:
 
     def dequant(self) -> torch.Tensor:
         """Effective dense weight [out, in] (fp32), rotations and scales included."""
-        return ex.effective_weight(self.codes.cpu(), self.bits, self.suh.cpu(), self.svh.cpu(), self.cb,
-                                   self.layout).t().contiguous()
+        return ex.effective_weight(self.codes.cpu(), self.bits, self.suh.cpu(), self.svh.cpu(), self.cb, self.layout,
+                                   None if self.tstart is None else self.tstart.cpu(),
+                                   None if self.tgain is None else self.tgain.cpu()).t().contiguous()
 
     def forward(self, x, residual=None, out=None, out_f32=False):
         Kf, N = self.in_features, self.out_features
         if not x.is_cuda:
-            y = ex.linear_reference(x.float(), self.codes, self.bits, self.suh, self.svh, self.cb, self.layout)
+            y = ex.linear_reference(x.float(), self.codes, self.bits, self.suh, self.svh, self.cb, self.layout, self.tstart, self.tgain)
             if self.bias is not None:
                 y = y + self.bias.float()
             if residual is not None:

@@ -60,8 +60,12 @@ def is_half_rate(codes: torch.Tensor) -> bool:
     return codes.shape[-1] % 16 == 8
 
 
-def tile_windows(codes: torch.Tensor, bits: int) -> torch.Tensor:
+def tile_windows(codes: torch.Tensor, bits: int, tstart: torch.Tensor | None = None) -> torch.Tensor:
     """codes uint16/int [..., 16*bits] -> windows int64 [..., 256] in position order.
+
+    ``tstart`` [...] (uint16 per tile, the extended trellis): the tile was encoded without the tail-biting ring, and the
+    bits in front of its stream are the low bits of its start state instead of the tile's last bits; a window that ends
+    before bit 16 takes its leading bits from there (the state's bit 0 sits directly in front of the stream).
 
     Half-integer rates (last dim 16 * bits + 8, the rate bits + 0.5): the windows of a tile advance by ``bits`` and
     ``bits + 1`` bits alternately, so position 2 j ends at bit j (2 bits + 1) + bits and position 2 j + 1 at
@@ -81,14 +85,32 @@ def tile_windows(codes: torch.Tensor, bits: int) -> torch.Tensor:
     idx = (start[:, None] + torch.arange(16, device=c.device)[None, :]) % total          # [256, 16]
     win_bits = stream[..., idx]                                                           # [..., 256, 16]
     weights = (1 << torch.arange(15, -1, -1, device=c.device)).to(torch.int64)
-    return (win_bits * weights).sum(-1)
+    win = (win_bits * weights).sum(-1)
+    if tstart is not None:
+        assert not half, "the extended trellis is defined for integer rates"
+        st = tstart.to(torch.int64) & 0xFFFF
+        for pos in range(256):
+            e = int(end[pos])
+            if e >= 16:
+                break
+            head = (words[..., 0] >> (32 - e)) & ((1 << e) - 1)                          # the stream's first e bits
+            win[..., pos] = ((st & ((1 << (16 - e)) - 1)) << e) | head
+    return win
 
 
-def reconstruct(codes: torch.Tensor, bits: int, cb: int = CB_MUL1, layout: str = "stock") -> torch.Tensor:
+def tile_gain(code: torch.Tensor) -> torch.Tensor:
+    """Gain of a tile from its 8-bit code: (896 + c) / 1024, i.e. 0.875 .. 1.124."""
+    return (896.0 + (code.to(torch.int64) & 0xFF).float()) / 1024.0
+
+
+def reconstruct(codes: torch.Tensor, bits: int, cb: int = CB_MUL1, layout: str = "stock", tstart: torch.Tensor | None = None,
+                tgain: torch.Tensor | None = None) -> torch.Tensor:
     """codes [K/16, N/16, 16*bits] (or 16*bits + 8: the rate bits + 0.5) -> W fp32 [K, N] in the rotated basis (no suh /
-    svh)."""
+    svh). ``tstart`` / ``tgain`` [K/16, N/16]: the extended trellis' per-tile start states and gain codes."""
     KT, NT = codes.shape[0], codes.shape[1]
-    vals = decode_windows(tile_windows(codes, bits), cb)        # [KT, NT, 256]
+    vals = decode_windows(tile_windows(codes, bits, tstart), cb)        # [KT, NT, 256]
+    if tgain is not None:                                       # per-tile gain, the product rounded to fp16 like the values
+        vals = (vals * tile_gain(tgain)[..., None]).to(torch.float16).float()
     row, col = _tile_positions(layout)
     tile = torch.zeros(KT, NT, 16, 16, dtype=torch.float32, device=codes.device)
     tile[:, :, row.to(codes.device), col.to(codes.device)] = vals
@@ -109,17 +131,17 @@ def had128(x: torch.Tensor) -> torch.Tensor:
 
 
 def linear_reference(x: torch.Tensor, codes: torch.Tensor, bits: int, suh: torch.Tensor, svh: torch.Tensor,
-                     cb: int = CB_MUL1, layout: str = "stock") -> torch.Tensor:
+                     cb: int = CB_MUL1, layout: str = "stock", tstart=None, tgain=None) -> torch.Tensor:
     """fp32 statement of the EXL3 linear: x [M, K] -> [M, N]."""
-    W = reconstruct(codes, bits, cb, layout)
+    W = reconstruct(codes, bits, cb, layout, tstart, tgain)
     t = had128(x.float() * suh.float())
     return had128(t @ W) * svh.float()
 
 
-def effective_weight(codes, bits, suh, svh, cb=CB_MUL1, layout="stock") -> torch.Tensor:
+def effective_weight(codes, bits, suh, svh, cb=CB_MUL1, layout="stock", tstart=None, tgain=None) -> torch.Tensor:
     """Dense [K, N] matrix equal to the whole linear map (for tests): row k = Linear(e_k)."""
     K = codes.shape[0] * 16
-    return linear_reference(torch.eye(K, device=codes.device), codes, bits, suh, svh, cb, layout)
+    return linear_reference(torch.eye(K, device=codes.device), codes, bits, suh, svh, cb, layout, tstart, tgain)
 
 
 # ------------------------------------------------------------------------------------------------ synthesis

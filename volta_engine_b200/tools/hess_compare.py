@@ -111,8 +111,9 @@ def load_quantized(ckpt, base: str, device="cpu") -> torch.Tensor | None:
         bits = codes.shape[-1] // 16
         cb = ex.CB_MUL1 if repo.has(base + ".mul1") else ex.CB_MCG if repo.has(base + ".mcg") else ex.CB_3INST
         layout = "volta" if repo.tile_layout == "volta" and base not in repo.tile_layout_stock else "stock"
+        side = lambda n: repo.load(base + n, device=device).reshape(codes.shape[0], codes.shape[1]) if repo.has(base + n) else None
         return ex.effective_weight(codes, bits, repo.load(base + ".suh", device=device),
-                                   repo.load(base + ".svh", device=device), cb, layout).float()
+                                   repo.load(base + ".svh", device=device), cb, layout, side(".tstart"), side(".tgain")).float()
     if repo.has(base + ".weight_packed"):
         g = 1.0 / float(repo.load(base + ".weight_global_scale").float().reshape(-1)[0])
         return qn.dequantize_nvfp4(repo.load(base + ".weight_packed", device=device),
