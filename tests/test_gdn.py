@@ -287,3 +287,58 @@ def test_gpu_hybrid_mtp_rounds_on_the_device_roll_back_and_match_plain_greedy():
         pos += len(new)
     assert out[:20] == plain[:20], (out, plain)
     assert run._sts[(1, 3)]["graph"] is not None and run.stats["accepted"] < run.stats["proposed"]
+
+
+def test_hybrid_checkpoint_directory_loads_under_the_checkpoint_names(tmp_path):
+    """A directory written under the hybrid checkpoint's tensor names (linear_attn.in_proj_qkv / z / b / a, conv1d, A_log,
+    dt_bias, gated norm, out_proj; self_attn.q_proj carrying the output gate per head; dense or routed FFN; mtp.*) loads,
+    chunked prefill + decode agree with a whole prefill, and a rank of a two-rank layout holds its heads' slices."""
+    from volta_engine_b200.models.factory import TensorSource, load_model
+    from volta_engine_b200.models.hybrid import HybridConfig, HybridModel
+    from volta_engine_b200.models.hybrid_loader import load_hybrid, save_hybrid_checkpoint
+    from volta_engine_b200.parallel.comm import LocalComm
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    from util import cos
+    for moe in (False, True):
+        d = tmp_path / ("moe" if moe else "dense")
+        cfg = HybridConfig.tiny_hybrid(mtp_layers=1, norm_bias=1.0, quant="bf16", shared_gate=moe, first_dense_layers=0 if moe else 4,
+                                      shared_ffn=256)                    # (a two-rank slice of the shared expert keeps 128 rows)
+        t = save_hybrid_checkpoint(d, cfg, seed=3)
+        m, hf = load_model(d, device="cpu")
+        c = m.cfg
+        assert isinstance(m, HybridModel) and ["gdn" if L.gdn is not None else "att" for L in m.layers] == ["gdn", "att", "gdn", "att"]
+        assert (c.gdn_k_heads, c.gdn_v_heads, c.rot_dim, c.norm_bias, c.mtp_layers, c.attn_gate) == (2, 4, 32, 1.0, 1, True)
+        assert all(L.dense_ffn != moe for L in m.layers) and m.mtp is not None and m.mtp["layer"].kv_index == 2 and m.kv_layers == 3
+        P = "model.language_model."
+        L0, L1, dm = m.layers[0], m.layers[1], m.dims
+        w = L0.gdn["in_proj"].weight.float()
+        qkv, z = t[P + "layers.0.linear_attn.in_proj_qkv.weight"].float(), t[P + "layers.0.linear_attn.in_proj_z.weight"].float()
+        C = dm.conv_dim
+        assert torch.equal(w[:C], qkv) and torch.equal(w[C:C + dm.n_v * dm.dv], z)
+        assert torch.equal(w[C + dm.n_v * dm.dv:C + dm.n_v * dm.dv + dm.n_v], t[P + "layers.0.linear_attn.in_proj_b.weight"].float())
+        assert torch.equal(L0.gdn["conv_w"], t[P + "layers.0.linear_attn.conv1d.weight"].float().reshape(C, -1))
+        hd, nq = c.head_dim, c.n_q
+        wq = t[P + "layers.1.self_attn.q_proj.weight"].float().reshape(nq, 2, hd, c.hidden)
+        assert torch.equal(L1.qkv.weight.float()[: nq * hd], wq[:, 0].reshape(nq * hd, -1))
+        assert torch.equal(L1.gate_proj.weight.float(), wq[:, 1].reshape(nq * hd, -1))
+        kv = PagedKVCache(m.kv_layers, m.nkv, hd, 16, 2, 512, "cpu")
+        prompt = list(range(5, 45))
+        out, _ = Engine(m, kv, use_graphs=False, prefill_chunk=16).generate(prompt, 5)
+        m.gdn_states = None
+        kv2 = PagedKVCache(m.kv_layers, m.nkv, hd, 16, 2, 512, "cpu")
+        assert Engine(m, kv2, use_graphs=False, prefill_chunk=1000).prefill(0, prompt + out[:3]) == out[3]
+
+        class Rank1(LocalComm):
+            rank, size = 1, 2
+        m1 = load_hybrid(hf, TensorSource(d), "cpu", Rank1())
+        d1 = m1.dims
+        w1 = m1.layers[0].gdn["in_proj"].weight.float()
+        kq, vv = d1.n_k * d1.dk, d1.n_v * d1.dv
+        Kf, Vf = dm.n_k * dm.dk, dm.n_v * dm.dv
+        assert (d1.n_k, d1.n_v) == (1, 2)
+        assert torch.equal(w1[:kq], qkv[kq:2 * kq]) and torch.equal(w1[kq:2 * kq], qkv[Kf + kq:Kf + 2 * kq])
+        assert torch.equal(w1[2 * kq:2 * kq + vv], qkv[2 * Kf + vv:2 * Kf + 2 * vv]) and torch.equal(w1[2 * kq + vv:2 * kq + 2 * vv], z[vv:2 * vv])
+        assert torch.equal(m1.layers[0].gdn["A_log"], t[P + "layers.0.linear_attn.A_log"][2:4])
+        assert torch.equal(m1.layers[1].gate_proj.weight.float(), wq[2:4, 1].reshape(2 * hd, -1))
+        assert m1.layers[1].o_proj.weight.shape == (c.hidden, 2 * hd)
