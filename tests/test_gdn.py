@@ -342,3 +342,33 @@ def test_hybrid_checkpoint_directory_loads_under_the_checkpoint_names(tmp_path):
         assert torch.equal(m1.layers[0].gdn["A_log"], t[P + "layers.0.linear_attn.A_log"][2:4])
         assert torch.equal(m1.layers[1].gate_proj.weight.float(), wq[2:4, 1].reshape(2 * hd, -1))
         assert m1.layers[1].o_proj.weight.shape == (c.hidden, 2 * hd)
+
+
+def test_flash_next_checkpoint_with_stream_mixers_and_indexer_loads(tmp_path):
+    """qwen4_exp directories: the gated residual-stream mixers of every sublayer, the final mixer and the block-sparse
+    indexer of the full-attention layers come from the checkpoint; n-gram embedding tensors are refused."""
+    from volta_engine_b200.loader.safetensors import write_safetensors
+    from volta_engine_b200.models.factory import load_model
+    from volta_engine_b200.models.hybrid import HybridConfig
+    from volta_engine_b200.models.hybrid_loader import save_hybrid_checkpoint
+    from volta_engine_b200.runtime.engine import Engine
+    from volta_engine_b200.runtime.kv_cache import PagedKVCache
+    cfg = HybridConfig.tiny_hybrid(norm_bias=1.0, quant="bf16", shared_gate=True, first_dense_layers=0, residual="gated", hc_mult=4,
+                                   hc_rank=16, qsa=True, shared_ffn=256)
+    t = save_hybrid_checkpoint(tmp_path, cfg, seed=4)
+    m, hf = load_model(tmp_path, device="cpu")
+    c = m.cfg
+    assert hf["model_type"] == "qwen4_exp" and (c.residual, c.hc_mult, c.hc_rank, c.qsa) == ("gated", 4, 16, True)
+    P = "model.language_model."
+    L1 = m.layers[1]
+    assert torch.equal(L1.attn_hc.down, t[P + "layers.1.attn_hyper_connection.input_mix_weight_down.weight"])
+    assert torch.equal(L1.mlp_hc.inject, t[P + "layers.1.mlp_hyper_connection.block_inject_weight.weight"])
+    assert m.final_hc.inject is None and torch.equal(m.final_hc.up, t["model.language_model.hyper_connection_mixer.input_mix_weight_up.weight"])
+    assert L1.qsa is not None and m.layers[0].qsa is None
+    assert torch.equal(L1.qsa.proj.weight, t[P + "layers.1.self_attn.indexer.index_qk_proj.weight"])
+    kv = PagedKVCache(m.kv_layers, m.nkv, c.head_dim, 16, 2, 512, "cpu")
+    out, _ = Engine(m, kv, use_graphs=False, prefill_chunk=16).generate(list(range(5, 45)), 4)
+    assert len(out) == 4
+    write_safetensors(tmp_path / "ple.safetensors", {P + "layers.0.ple.key_proj.weight": torch.zeros(4, 4)})
+    with pytest.raises(NotImplementedError):
+        load_model(tmp_path, device="cpu")

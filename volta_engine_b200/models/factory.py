@@ -239,7 +239,7 @@ def load_model(model_dir, device="cuda:0", comm=None, gemm_mode="w4a16", quantiz
         groups = {g.strip() for g in nvfp4_dense.split(",") if g.strip()}
         return load_glm5(hf, d, device, comm, gemm_mode, quantize, nvfp4_head=bool(groups & {"head", "all"})), hf
     src = TensorSource(d, prefer)
-    if mt in ("qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_next"):
+    if mt in ("qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_next", "qwen4_exp"):
         from .hybrid_loader import load_hybrid
         groups = {g.strip() for g in nvfp4_dense.split(",") if g.strip()}
         if overlay:

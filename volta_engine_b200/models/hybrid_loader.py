@@ -1,5 +1,5 @@
-"""Hybrid Gated-DeltaNet / gated-attention checkpoints (``model_type`` qwen3_5, qwen3_5_moe, qwen3_next) ->
-:class:`.hybrid.HybridModel`.
+"""Hybrid Gated-DeltaNet / gated-attention checkpoints (``model_type`` qwen3_5, qwen3_5_moe, qwen3_next, and the
+Flash-Next assembly qwen4_exp) -> :class:`.hybrid.HybridModel`.
 
 Names (under ``model.language_model.``; a plain ``model.`` prefix is accepted too), per layer ``layers.<i>.``:
 
@@ -15,9 +15,17 @@ Names (under ``model.language_model.``; a plain ``model.`` prefix is accepted to
   * the MTP head: ``mtp.fc`` ([H, 2 H] over [norm(embedding) | norm(hidden)]), ``mtp.pre_fc_norm_embedding.weight``,
     ``mtp.pre_fc_norm_hidden.weight``, ``mtp.layers.0.*`` (a full-attention block), ``mtp.norm.weight``.
 
+  * qwen4_exp adds, per sublayer, the gated residual-stream mixers ``attn_hyper_connection`` / ``mlp_hyper_connection``
+    (``hc_norm.weight`` [streams, H], ``input_mix_weight_down.weight`` [rank, streams x H], ``input_mix_weight_up.weight``
+    [streams x H, rank], ``block_inject_weight.weight`` [streams, streams x H]), the final ``hyper_connection_mixer`` (no
+    inject), and on the full-attention layers the block-sparse indexer ``self_attn.indexer.index_qk_proj`` /
+    ``q_layernorm.weight`` / ``k_layernorm.weight``. Its n-gram embedding tensors (``layers.<i>.ple.*``) have no counterpart
+    in this model and a checkpoint that carries them is refused.
+
 RMSNorm weights are stored as w - 1 (``norm_bias`` 1), the gated norm of the linear layers as w.
 Reference: src/models/qwen3_5.cpp:330-440 (layer tensors and their tensor-parallel slices), :440-520 (MTP head),
-inc/engine/models/qwen3_5.h:30-52 (shape and norm bias).
+inc/engine/models/qwen3_5.h:30-52 (shape and norm bias); src/models/qwen4_exp.cpp:451-478 (mixers), :576-584 (indexer),
+:82-99 (configuration keys).
 """
 from __future__ import annotations
 
@@ -29,7 +37,7 @@ import torch
 from .glm5_loader import _dense, _maybe
 from .moe_loader import _load_ffn, load_head
 
-HYBRID_TYPES = {"qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_next"}
+HYBRID_TYPES = {"qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_next", "qwen4_exp"}
 
 
 def hybrid_config_from_hf(c: dict):
@@ -52,7 +60,18 @@ def hybrid_config_from_hf(c: dict):
         gdn_dv=int(c.get("linear_value_head_dim", 128)), gdn_conv=int(c.get("linear_conv_kernel_dim", 4)), attn_gate=True,
         mtp_layers=int(c.get("mtp_num_hidden_layers", c.get("num_nextn_predict_layers", 0)) or 0), quant=c.get("volta_quant", "nvfp4"),
         model_type=c.get("model_type", "qwen3_5"))
+    if c.get("model_type") == "qwen4_exp" or int(c.get("hc_count", 0) or 0) > 1:
+        cfg.residual, cfg.hc_mult, cfg.hc_rank = "gated", int(c.get("hc_count", 4)), int(c.get("hc_rank", cfg.hc_rank))
     return cfg
+
+
+def _load_mixer(src, prefix: str, dev, inject: bool):
+    from ..ops.streams import GatedResidualWeights
+    bf = torch.bfloat16
+    return GatedResidualWeights(norm=src.tensor(prefix + ".hc_norm.weight", dev, bf),
+                                down=src.tensor(prefix + ".input_mix_weight_down.weight", dev, bf).contiguous(),
+                                up=src.tensor(prefix + ".input_mix_weight_up.weight", dev, bf).contiguous(),
+                                inject=src.tensor(prefix + ".block_inject_weight.weight", dev, bf).contiguous() if inject else None)
 
 
 def _load_gdn(model, src, L, p: str) -> None:
@@ -123,6 +142,13 @@ def load_hybrid(hf: dict, src, device, comm, gemm_mode: str = "w4a16", quantize=
     if cfg.mtp_layers and not (src.has("mtp.fc.weight") or src.has("mtp.fc.weight_packed") or src.has("mtp.fc.trellis")):
         cfg.mtp_layers = 0                                               # the checkpoint was exported without its MTP head
     cfg.qk_norm = src.has(f"{P}layers.{cfg.full_interval - 1}.self_attn.q_norm.weight")
+    if any(src.has(f"{P}layers.{li}.ple.{n}") for li in range(cfg.n_layers) for n in ("key_proj.weight", "conv1d.weight", "norm_key.weight")):
+        raise NotImplementedError(f"{cfg.model_type}: the checkpoint carries n-gram embedding tensors (layers.<i>.ple.*), which "
+                                  "this model does not implement")
+    cfg.qsa = src.has(f"{P}layers.{cfg.full_interval - 1}.self_attn.indexer.index_qk_proj.weight")
+    gated_streams = cfg.residual == "gated"
+    if gated_streams:
+        cfg.hc_rank = int(src.tensor(f"{P}layers.0.attn_hyper_connection.input_mix_weight_down.weight").shape[0])
     model = HybridModel(cfg, device, comm)
     dev, bf = model.device, torch.bfloat16
     kw = dict(rank=model.comm.rank, world=model.comm.size, device=dev, gemm_mode=gemm_mode, quantize=quantize or "nvfp4")
@@ -142,6 +168,16 @@ def load_hybrid(hf: dict, src, device, comm, gemm_mode: str = "w4a16", quantize=
             _load_gated_attention(model, src, L, p)
             L.kv_index = n_attn
             n_attn += 1
+            if cfg.qsa and src.has(p + "self_attn.indexer.index_qk_proj.weight"):
+                from ..ops import dsa as D
+                from ..ops.linear import LinearBF16
+                L.qsa = D.QSAWeights(proj=LinearBF16(src.tensor(p + "self_attn.indexer.index_qk_proj.weight", dev, bf)),
+                                     q_norm=src.tensor(p + "self_attn.indexer.q_layernorm.weight", dev, bf),
+                                     k_norm=src.tensor(p + "self_attn.indexer.k_layernorm.weight", dev, bf),
+                                     rot=min(64, D.DIM), theta=cfg.rope_theta, eps=cfg.rms_eps)
+        if gated_streams and src.has(p + "attn_hyper_connection.hc_norm.weight"):
+            L.attn_hc = _load_mixer(src, p + "attn_hyper_connection", dev, True)
+            L.mlp_hc = _load_mixer(src, p + "mlp_hyper_connection", dev, True)
         L.attn_norm = src.tensor(p + "input_layernorm.weight", dev, bf)
         L.ffn_norm = src.tensor(p + "post_attention_layernorm.weight", dev, bf)
         _load_ffn(model, src, L, p, li, kw)
@@ -151,6 +187,8 @@ def load_hybrid(hf: dict, src, device, comm, gemm_mode: str = "w4a16", quantize=
         model.layers.append(load_layer(f"{P}layers.{li}.", li, kinds[li]))
     model.final_norm = src.tensor(P + "norm.weight", dev, bf)
     load_head(model, src, P + "embed_tokens.weight", nvfp4_head)
+    if gated_streams:
+        model.final_hc = _load_mixer(src, P.rstrip(".") + ".hyper_connection_mixer", dev, False)
     if cfg.mtp_layers:
         block = load_layer("mtp.layers.0.", cfg.n_layers, False)
         model.mtp = {"layer": block, "fc": model._make_linear(_dense(src, "mtp.fc").to(dev), True),
@@ -212,8 +250,27 @@ def save_hybrid_checkpoint(model_dir, cfg, seed: int = 0, std: float = 0.05, pre
                 t[m + "shared_expert.gate_proj.weight"], t[m + "shared_expert.up_proj.weight"] = rnd(S, H), rnd(S, H)
                 t[m + "shared_expert.down_proj.weight"], t[m + "shared_expert_gate.weight"] = rnd(H, S), rnd(1, H)
 
+    def mixer(pfx: str, inject: bool):
+        hc, rk = cfg.hc_mult, cfg.hc_rank
+        t[pfx + ".hc_norm.weight"] = rnd(hc, H)
+        t[pfx + ".input_mix_weight_down.weight"], t[pfx + ".input_mix_weight_up.weight"] = rnd(rk, hc * H), rnd(hc * H, rk, k=4)
+        if inject:
+            t[pfx + ".block_inject_weight.weight"] = rnd(hc, hc * H)
+
     for li in range(cfg.n_layers):
-        layer(f"{prefix}layers.{li}.", li, not cfg.is_full(li))
+        p = f"{prefix}layers.{li}."
+        layer(p, li, not cfg.is_full(li))
+        if cfg.residual == "gated":
+            mixer(p + "attn_hyper_connection", True)
+            mixer(p + "mlp_hyper_connection", True)
+        if cfg.qsa and cfg.is_full(li):
+            from ..ops import dsa as D
+            t[p + "self_attn.indexer.index_qk_proj.weight"] = rnd(D.QSA_HEADS * D.DIM + D.DIM, H, k=8)
+            t[p + "self_attn.indexer.q_layernorm.weight"], t[p + "self_attn.indexer.k_layernorm.weight"] = zeros(D.DIM), zeros(D.DIM)
+    if cfg.residual == "gated":
+        mixer(prefix.rstrip(".") + ".hyper_connection_mixer", False)
+        hf.update({"model_type": "qwen4_exp", "hc_count": cfg.hc_mult, "hc_rank": cfg.hc_rank})
+        (d / "config.json").write_text(json.dumps(hf, indent=1))
     if cfg.mtp_layers:
         layer("mtp.layers.0.", cfg.n_layers, False)
         t["mtp.fc.weight"] = rnd(H, 2 * H)
